@@ -1,0 +1,80 @@
+"""Seeded synthetic inputs: raw GGUF quant blocks, activations, model weights.
+
+Pure numpy.  The benchmark configurations name no dataset: weights, token ids
+and activations are random with stated distributions, so every generator here
+takes an explicit seed (or derives one from the tensor's name with crc32, which
+is stable across processes, unlike Python's salted ``hash``).
+"""
+import zlib
+import numpy as np
+
+Q4_0, Q8_0, Q6_K = 2, 8, 14
+# {ggml_type: (elements per block, bytes per block)}; same table as tinygrad/llm/gguf.py:20-21
+GGML_QUANT = {Q4_0: (32, 18), Q8_0: (32, 34), Q6_K: (256, 210)}
+
+
+def name_seed(name: str, base: int = 0) -> int:
+  return (zlib.crc32(name.encode()) + base) & 0xFFFFFFFF
+
+
+def q4_0_blocks(n_out: int, n_in: int, rng, scale_std: float = 0.02) -> np.ndarray:
+  """(n_out, n_in) weight as raw Q4_0 bytes: per 32 elements an fp16 scale
+  |N(0, scale_std)| followed by 16 bytes of uniform nibbles (value=(q-8)*d)."""
+  nb = n_out * n_in // 32
+  out = np.empty((nb, 18), dtype=np.uint8)
+  out[:, :2] = np.abs(rng.standard_normal(nb, dtype=np.float32) * scale_std).astype(np.float16).view(np.uint8).reshape(nb, 2)
+  out[:, 2:] = rng.integers(0, 256, (nb, 16), dtype=np.uint8)
+  return out.reshape(-1)
+
+
+def q8_0_blocks(n_out: int, n_in: int, rng, scale_std: float = 0.01) -> np.ndarray:
+  """Raw Q8_0 bytes: fp16 scale |N(0, scale_std)| + 32 int8 uniform in [-127,127]."""
+  nb = n_out * n_in // 32
+  out = np.empty((nb, 34), dtype=np.uint8)
+  out[:, :2] = np.abs(rng.standard_normal(nb, dtype=np.float32) * scale_std).astype(np.float16).view(np.uint8).reshape(nb, 2)
+  out[:, 2:] = rng.integers(-127, 128, (nb, 32), dtype=np.int8).view(np.uint8)
+  return out.reshape(-1)
+
+
+def q6_k_blocks(n_out: int, n_in: int, rng, scale_std: float = 0.001) -> np.ndarray:
+  """Raw Q6_K bytes: 128 B low nibbles, 64 B high 2-bit fields, 16 int8
+  sub-block scales, fp16 super-block scale."""
+  nb = n_out * n_in // 256
+  out = np.empty((nb, 210), dtype=np.uint8)
+  out[:, :192] = rng.integers(0, 256, (nb, 192), dtype=np.uint8)
+  out[:, 192:208] = rng.integers(-64, 64, (nb, 16), dtype=np.int8).view(np.uint8)
+  out[:, 208:] = np.abs(rng.standard_normal(nb, dtype=np.float32) * scale_std).astype(np.float16).view(np.uint8).reshape(nb, 2)
+  return out.reshape(-1)
+
+
+BLOCK_MAKERS = {Q4_0: q4_0_blocks, Q8_0: q8_0_blocks, Q6_K: q6_k_blocks}
+
+
+def linear_names(cfg) -> list:
+  """(state-dict name, out, in) of every quantised Linear of a dense model,
+  named as tinygrad/llm/model.py:105-107,161-164,350 name them."""
+  qd, kvd = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+  names = []
+  for i in range(cfg.num_blocks):
+    names += [(f"blk.{i}.attn_q", qd, cfg.dim), (f"blk.{i}.attn_k", kvd, cfg.dim), (f"blk.{i}.attn_v", kvd, cfg.dim),
+              (f"blk.{i}.attn_output", cfg.dim, qd), (f"blk.{i}.ffn_gate", cfg.hidden_dim, cfg.dim),
+              (f"blk.{i}.ffn_up", cfg.hidden_dim, cfg.dim), (f"blk.{i}.ffn_down", cfg.dim, cfg.hidden_dim)]
+  names.append(("output", cfg.vocab_size, cfg.dim))
+  return names
+
+
+def dense_model_raw(cfg, ggml_type: int = Q4_0, seed: int = 0, embd_std: float = 0.02, bias_std: float = 0.02) -> dict:
+  """Random-init dense model as the loader would see it: every Linear weight
+  as raw quant bytes (key ``name.weight``, uint8), embeddings / norm weights /
+  biases as fp16 arrays.  One seed per tensor, derived from its name."""
+  sd = {}
+  for name, n_out, n_in in linear_names(cfg):
+    sd[name + ".weight"] = BLOCK_MAKERS[ggml_type](n_out, n_in, np.random.default_rng(name_seed(name, seed)))
+    if cfg.qkv_bias and name.split(".")[-1] in ("attn_q", "attn_k", "attn_v"):
+      sd[name + ".bias"] = (np.random.default_rng(name_seed(name + ".bias", seed)).standard_normal(n_out, dtype=np.float32) * bias_std).astype(np.float16)
+  rng = np.random.default_rng(name_seed("token_embd", seed))
+  sd["token_embd.weight"] = (rng.standard_normal((cfg.vocab_size, cfg.dim), dtype=np.float32) * embd_std).astype(np.float16)
+  for name in [f"blk.{i}.{n}" for i in range(cfg.num_blocks) for n in ("attn_norm", "ffn_norm")] + ["output_norm"]:
+    rng = np.random.default_rng(name_seed(name, seed))
+    sd[name + ".weight"] = (1.0 + 0.05 * rng.standard_normal(cfg.dim, dtype=np.float32)).astype(np.float16)
+  return sd
