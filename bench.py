@@ -1,0 +1,255 @@
+"""Headline benchmark: decode tokens/s of a Llama-3-8B-shaped Q4_0 model at batch 1 on B200,
+plus the achieved HBM bandwidth of the quant GEMV kernel against the measured peak.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step (one token through all blocks, head and arg-max).  Weights,
+embeddings, prompt ids are seeded synthetic data of the configuration's shapes (no
+checkpoint or dataset is involved).  For N > 1 (launched by torch.distributed.run) every
+rank decodes its own sequence on its own GPU: replicas, no data-path collective.
+Prints ONE JSON line on rank 0.
+"""
+import argparse, json, os, sys, time, threading, pathlib
+import numpy as np
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC, UNIT = "decode tokens/s (8B-shape Q4_0, bs1)", "tokens/s"
+WORKLOAD = "configs[1]: Llama-3-8B-shaped decode, Q4_0 linears, fp16 embeddings/norms, fp16 KV cache, batch 1, prompt 512 random ids, greedy"
+PROMPT_LEN, MAX_CONTEXT = 512, 2048
+
+
+def llama3_8b_config():
+  from tinygrad_b200.model import TransformerConfig
+  return TransformerConfig(num_blocks=32, dim=4096, hidden_dim=14336, n_heads=32, n_kv_heads=8, norm_eps=1e-5, vocab_size=128256, head_dim=128,
+                           rope_theta=500000.0, rope_dim=128, v_head_dim=128, max_context=MAX_CONTEXT, kv_dtype="float16")
+
+
+def measured_peaks():
+  p = ROOT / "MEASURED_PEAKS.json"
+  if p.exists():
+    return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+  return 6650.0, "fallback (6.65 TB/s, an earlier measurement on this pool)"
+
+
+class ClockSampler:
+  """Samples SM clock and throttle reasons through NVML (read-only) while a timed region runs."""
+  def __init__(self, index: int):
+    self.samples, self.stop_flag, self.thread, self.h = [], False, None, None
+    try:
+      import pynvml
+      pynvml.nvmlInit()
+      self.nv, self.h = pynvml, pynvml.nvmlDeviceGetHandleByIndex(index)
+      self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+    except Exception as e:   # no NVML: report that instead of a number
+      self.err = repr(e)
+
+  def _run(self):
+    nv = self.nv
+    while not self.stop_flag:
+      try:
+        mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+        try: reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+        except Exception: reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+        self.samples.append((mhz, reasons))
+      except Exception: pass
+      time.sleep(0.01)
+
+  def __enter__(self):
+    if self.h is not None:
+      self.thread = threading.Thread(target=self._run, daemon=True); self.thread.start()
+    return self
+
+  def __exit__(self, *a):
+    self.stop_flag = True
+    if self.thread: self.thread.join()
+
+  def summary(self) -> dict:
+    if self.h is None or not self.samples: return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable: " + getattr(self, "err", "no samples")]}
+    names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+    seen = set()
+    for _, r in self.samples:
+      for bit, n in names.items():
+        if r & bit: seen.add(n)
+    return {"sm_mhz": float(np.median([m for m, _ in self.samples])), "sm_max_mhz": float(self.max_mhz), "reasons": sorted(seen),
+            "samples": len(self.samples)}
+
+
+def cpu_port_block_seconds(cfg, reps_budget_s: float, seed: int = 0):
+  """Time the C restatement on the host cores: the 7 linears of one block and the head, raw GGUF blocks.
+  Returns (seconds per block, seconds for the head, threads, repetitions)."""
+  from oracle import cpu_gemv
+  from tinygrad_b200 import synth
+  qd, kvd = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+  shapes = [(qd, cfg.dim), (kvd, cfg.dim), (kvd, cfg.dim), (cfg.dim, qd), (cfg.hidden_dim, cfg.dim), (cfg.hidden_dim, cfg.dim), (cfg.dim, cfg.hidden_dim)]
+  rng = np.random.default_rng(seed)
+  ws = [synth.q4_0_blocks(o, i, rng) for o, i in shapes]
+  head = synth.q4_0_blocks(cfg.vocab_size, cfg.dim, rng)
+  xs = {k: rng.standard_normal(k).astype(np.float32) for k in {i for _, i in shapes}}
+  def block():
+    for w, (o, i) in zip(ws, shapes): cpu_gemv.qgemv(2, w, xs[i], o, i)
+  block(); cpu_gemv.qgemv(2, head, xs[cfg.dim], cfg.vocab_size, cfg.dim)      # warm
+  t0, reps = time.perf_counter(), 0
+  while True:
+    block(); reps += 1
+    if time.perf_counter() - t0 > reps_budget_s * 0.7: break
+  t_blk = (time.perf_counter() - t0) / reps
+  t0, hreps = time.perf_counter(), 0
+  while True:
+    cpu_gemv.qgemv(2, head, xs[cfg.dim], cfg.vocab_size, cfg.dim); hreps += 1
+    if time.perf_counter() - t0 > reps_budget_s * 0.3: break
+  t_head = (time.perf_counter() - t0) / hreps
+  return t_blk, t_head, cpu_gemv.n_threads(), reps
+
+
+def run_reference(args, rank):
+  """The reference arm: the CPU implementation of the same path on the host cores (the C restatement
+  of tinygrad's fused dequant-linear arithmetic; tinygrad's own CPU device needs clang, which this image lacks)."""
+  if rank != 0: return
+  from oracle import cpu_gemv
+  from tinygrad_b200 import synth
+  cfg = llama3_8b_config()
+  qd, kvd = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+  shapes = [(qd, cfg.dim), (kvd, cfg.dim), (kvd, cfg.dim), (cfg.dim, qd), (cfg.hidden_dim, cfg.dim), (cfg.hidden_dim, cfg.dim), (cfg.dim, cfg.hidden_dim)]
+  rng = np.random.default_rng(0)
+  ws = [synth.q4_0_blocks(o, i, rng) for o, i in shapes]
+  head = synth.q4_0_blocks(cfg.vocab_size, cfg.dim, rng)
+  xs = {k: rng.standard_normal(k).astype(np.float32) for k in {i for _, i in shapes}}
+  def sample():
+    t0 = time.perf_counter()
+    for w, (o, i) in zip(ws, shapes): cpu_gemv.qgemv(2, w, xs[i], o, i)
+    t1 = time.perf_counter()
+    cpu_gemv.qgemv(2, head, xs[cfg.dim], cfg.vocab_size, cfg.dim)
+    return (t1 - t0) * cfg.num_blocks + (time.perf_counter() - t1)       # one block's linears x 32 + the head = one token
+  for _ in range(args.warmup): sample()
+  total = sum(sample() for _ in range(args.steps))
+  v = args.steps / total
+  threads = cpu_gemv.n_threads()
+  sample_txt = "each step = the 7 Q4_0 linears of ONE block (timed, x32 blocks) + the vocab head, raw GGUF blocks, fp32 activations; attention/norms omitted"
+  print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                    "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                    "data": "synthetic", "config": {"workload": WORKLOAD},
+                    "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample_txt},
+                    "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=256)
+  ap.add_argument("--warmup", type=int, default=8)
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+  ap.add_argument("--blocks", type=int, default=0, help="debug: fewer transformer blocks (the reported line is then not the headline workload)")
+  ap.add_argument("--no-pdl", action="store_true")
+  ap.add_argument("--skip-cpu-baseline", action="store_true")
+  args = ap.parse_args()
+  rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+  if args.impl == "reference": return run_reference(args, rank)
+  if args.warmup < 3: args.warmup = 3
+
+  from tinygrad_b200 import build, runtime, synth
+  from tinygrad_b200.model import Transformer
+  from dataclasses import replace
+  build.build_lib()
+  dist = None
+  if world > 1:
+    import torch, torch.distributed as dist
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+  runtime.set_device(local)
+  cfg = llama3_8b_config()
+  if args.blocks: cfg = replace(cfg, num_blocks=args.blocks)
+  t_build = time.time()
+  model = Transformer(cfg, synth.LazyDenseState(cfg, synth.Q4_0, seed=rank), ggml_type=synth.Q4_0, use_pdl=not args.no_pdl)
+  t_build = time.time() - t_build
+  prompt = [int(t) for t in np.random.default_rng(1000 + rank).integers(0, cfg.vocab_size, PROMPT_LEN)]
+  # prompt (untimed): one position per step through the same kernels
+  model.set_state(prompt, 0)
+  for _ in range(PROMPT_LEN - 1): model.step(with_head=False)
+  model.stream.synchronize()
+
+  def barrier():
+    runtime.synchronize()
+    if dist is not None: dist.barrier()
+    runtime.synchronize()
+
+  def max_over_ranks(ms: float) -> float:
+    if dist is None: return ms
+    import torch
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+  if PROMPT_LEN + args.warmup + args.steps + 2 > MAX_CONTEXT:
+    raise SystemExit(f"--steps {args.steps} does not fit the {MAX_CONTEXT}-token context after a {PROMPT_LEN}-token prompt")
+  e0, e1 = runtime.Event(), runtime.Event()
+  sampler = ClockSampler(local)
+  with sampler:
+    # ---- device-resident: tokens feed back on the device, K graph replays back to back
+    for _ in range(args.warmup): model.step()
+    barrier()
+    e0.record(model.stream)
+    for _ in range(args.steps): model.step()
+    e1.record(model.stream)
+    barrier()
+    ms_dev = max_over_ranks(e0.elapsed_ms(e1))
+    # ---- end to end: per step, the token id goes host->device from pinned memory, the sampled id comes back
+    pin_in, pin_out = runtime.PinnedBuffer((1,), np.int32), runtime.PinnedBuffer((1,), np.int32)
+    lib = __import__("tinygrad_b200._lib", fromlist=["load"]).load()
+    pos = PROMPT_LEN - 1                      # rewind to the end of the prompt: same positions as the device-resident pass
+    model.set_state([], pos)
+    pin_in.array[0] = prompt[-1]
+    def e2e_step(p):
+      lib.b200q_memcpy_h2d(model.tokens.ptr + 4 * p, pin_in.ptr, 4, model.stream.ptr)
+      model.step()
+      lib.b200q_memcpy_d2h(pin_out.ptr, model.tokens.ptr + 4 * (p + 1), 4, model.stream.ptr)
+      model.stream.synchronize()
+      pin_in.array[0] = pin_out.array[0]
+    for _ in range(args.warmup): e2e_step(pos); pos += 1
+    barrier()
+    e0.record(model.stream)
+    t0 = time.perf_counter()
+    for _ in range(args.steps): e2e_step(pos); pos += 1
+    e1.record(model.stream)
+    barrier()
+    ms_e2e = max_over_ranks(max(e0.elapsed_ms(e1), 1e3 * (time.perf_counter() - t0)))
+    # ---- the dominant kernel alone: every GEMV launch of one step, chained, weights cold (4.2 GB >> L2)
+    g = model.gemv_only_graph()
+    for _ in range(3): g.launch()
+    barrier()
+    reps = 20
+    e0.record(model.stream)
+    for _ in range(reps): g.launch()
+    e1.record(model.stream)
+    barrier()
+    ms_gemv = e0.elapsed_ms(e1) / reps
+  launches = model.gemv_launches()
+  gemv_bytes = sum(o * i // 32 * 18 + 4 * i + 4 * o for o, i in launches)     # Q4_0 blocks + fp32 activations in + out
+  peak, peak_src = measured_peaks()
+  achieved = gemv_bytes / (ms_gemv * 1e-3) / 1e9
+  kv_bytes_per_pos = 2 * cfg.n_kv_heads * cfg.head_dim * 2 * cfg.num_blocks
+  step_bytes = model.weight_bytes + kv_bytes_per_pos * (PROMPT_LEN + args.warmup + args.steps // 2)
+  if rank != 0: return
+  value = world * args.steps / (ms_dev * 1e-3)
+  out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+         "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+         "config": {"workload": WORKLOAD if not args.blocks else f"DEBUG {args.blocks} blocks of: " + WORKLOAD, "parallelism": f"replicas x{world}",
+                    "l2": "inputs larger than L2 (4.2 GB of weights per step vs 126 MB)", "pdl": not args.no_pdl, "n_split": model.n_split,
+                    "step_hbm_gbs": step_bytes / (ms_dev / args.steps * 1e-3) / 1e9, "step_frac_of_peak": step_bytes / (ms_dev / args.steps * 1e-3) / 1e9 / peak,
+                    "model_build_s": round(t_build, 1)},
+         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                      "kernel": "qgemv_kernel<Q4_0>", "peak_source": peak_src, "launches_timed": len(launches) * reps,
+                      "bytes_per_launch_avg": gemv_bytes / len(launches), "us_per_launch_avg": 1e3 * ms_gemv / len(launches)},
+         "e2e": {"value": world * args.steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+         "gpu_launches": model.launches_per_step * args.steps, "clocks": sampler.summary()}
+  if not args.skip_cpu_baseline and world == 1:
+    t_blk, t_head, threads, reps_cpu = cpu_port_block_seconds(cfg, 12.0)
+    out["cpu_baseline"] = {"value": 1.0 / (t_blk * cfg.num_blocks + t_head), "unit": UNIT, "cores": threads, "kind": "port",
+                           "sample": f"C restatement, {reps_cpu} repetitions of one block's 7 Q4_0 linears (x{cfg.num_blocks}) + the vocab head; attention/norms omitted"}
+  print(json.dumps(out))
+  if dist is not None: dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+  main()

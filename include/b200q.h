@@ -1,0 +1,179 @@
+/* b200q -- C ABI of the B200 (sm_100a) quantized-LLM inference kernels.
+ *
+ * Drop-in boundary for tinygrad's quantized-LLM hot path.  File:line citations
+ * are paths inside the tinygrad source tree.  Every pointer named "device" is a
+ * raw CUDA device address (for a tinygrad Tensor: `t.uop.buffer.ensure_allocated()._buf`,
+ * tinygrad/device.py:128); the library never allocates or frees user-visible
+ * memory on the compute entry points.  `stream` is a `cudaStream_t` / `CUstream`
+ * passed as `void*` (NULL = the legacy default stream tinygrad's CUDA backend
+ * launches on, tinygrad/runtime/ops_cuda.py:65).  Every function returns
+ * B200Q_OK (0) or a negative B200Q_ERR_* code, never aborts, and never traps
+ * the device; `b200q_strerror` turns the code into text, as the reference turns
+ * a CUDA status into a RuntimeError (tinygrad/runtime/ops_cuda.py:13-16).
+ */
+#ifndef B200Q_H
+#define B200Q_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define B200Q_OK 0
+#define B200Q_ERR_BAD_ARG (-1)      /* null pointer, non-positive size, unknown enum */
+#define B200Q_ERR_BAD_SHAPE (-2)    /* size not a multiple of the quant block / limit exceeded */
+#define B200Q_ERR_MISALIGNED (-3)   /* pointer not 16-byte aligned where the kernel needs it */
+#define B200Q_ERR_UNSUPPORTED (-4)  /* quant type / dtype combination not built */
+#define B200Q_ERR_CUDA (-5)         /* a CUDA call failed: see b200q_last_cuda_error() */
+#define B200Q_ERR_TOO_LARGE (-6)    /* request exceeds a fixed capacity of the library */
+
+/* ---- enums -------------------------------------------------------------- */
+/* GGML tensor types, numbered as in the GGUF file format (tinygrad/llm/gguf.py:20-21). */
+#define B200Q_Q4_0 2
+#define B200Q_Q8_0 8
+#define B200Q_Q6_K 14
+/* element types of activations / outputs */
+#define B200Q_F32 0
+#define B200Q_F16 1
+/* GEMV epilogues */
+#define B200Q_EPI_LINEAR 0   /* y = W x (+bias) (+residual) */
+#define B200Q_EPI_SILU_MUL 1 /* weights packed with b200q_repack(raw0=gate, raw1=up): y = silu(gate x) * (up x) */
+/* launch flags */
+#define B200Q_FLAG_PDL 1     /* launch with programmatic dependent launch (overlaps the weight prefetch with the previous kernel) */
+
+const char* b200q_strerror(int code);
+const char* b200q_last_cuda_error(void);
+int b200q_version(void);
+
+/* ---- runtime plumbing (so the Python host needs no other CUDA binding) -- */
+int b200q_device_count(int* count);
+int b200q_set_device(int device);
+int b200q_device_props(int device, int* sm_count, int* cc_major, int* cc_minor, size_t* total_mem);
+int b200q_malloc(void** device_ptr, size_t bytes);
+int b200q_free(void* device_ptr);
+int b200q_host_alloc(void** host_ptr, size_t bytes);              /* pinned host memory */
+int b200q_host_free(void* host_ptr);
+int b200q_memcpy_h2d(void* device_dst, const void* host_src, size_t bytes, void* stream);
+int b200q_memcpy_d2h(void* host_dst, const void* device_src, size_t bytes, void* stream);
+int b200q_memcpy_d2d(void* device_dst, const void* device_src, size_t bytes, void* stream);
+int b200q_memset(void* device_dst, int value, size_t bytes, void* stream);
+int b200q_stream_create(void** stream);
+int b200q_stream_destroy(void* stream);
+int b200q_stream_synchronize(void* stream);
+int b200q_device_synchronize(void);
+int b200q_event_create(void** event);
+int b200q_event_destroy(void* event);
+int b200q_event_record(void* event, void* stream);
+int b200q_event_synchronize(void* event);
+int b200q_event_elapsed_ms(void* start, void* stop, float* ms);
+/* Capture everything launched on `stream` between begin and end into a CUDA graph,
+ * the counterpart of the reference's TinyJit -> CUDAGraph replay
+ * (tinygrad/engine/jit.py:241-291, tinygrad/runtime/graph/cuda.py:10-70). */
+int b200q_graph_begin(void* stream);
+int b200q_graph_end(void* stream, void** graph_exec);
+int b200q_graph_launch(void* graph_exec, void* stream);
+int b200q_graph_destroy(void* graph_exec);
+
+/* ---- GGUF block formats -------------------------------------------------
+ * Replaces the lazy dequantisation expression `ggml_data_to_tensor`
+ * (tinygrad/llm/gguf.py:23-72; Q4_0 :46, Q8_0 :56, Q6_K :68-72).
+ *
+ * b200q_dequant_raw: raw GGUF blocks -> n_elems values, fp32 (bit-identical to
+ * the reference's fp32 expression) or fp16 (its round-to-nearest-even cast,
+ * tinygrad/llm/model.py:376). */
+int b200q_dequant_raw(int qtype, const void* device_raw, void* device_out, int64_t n_elems, int out_dtype, void* stream);
+
+/* Packed weight layout used by the GEMV kernels (Q4_0, Q8_0).  A [n_out, n_in]
+ * weight (blocks running along n_in, as GGUF stores a Linear weight,
+ * tinygrad/llm/gguf.py:148) is re-tiled ONCE at load time, losslessly, into
+ * tiles of 16 rows x 128 columns (4 quant blocks per row), ordered
+ * [row_tile][column_group].  Inside a tile the 32 lanes of a warp each own one
+ * (row, block) pair per 16-byte word, so that a warp-wide 128-bit load reads
+ * 512 contiguous bytes, followed by the 64 fp16 block scales of the tile:
+ *   Q4_0 tile = 1152 B: [lane l: 16 quant bytes of (row l/4,   block l%4)] x32,
+ *                       [lane l: 16 quant bytes of (row l/4+8, block l%4)] x32,
+ *                       [entry e=2*(l/4)+h: scales of rows l/4 and l/4+8, blocks 2h and 2h+1] x16 (8 B each)
+ *   Q8_0 tile = 2176 B: as above with 32 quant bytes per (row, block) in two 16-byte halves
+ *                       (each int8 stored with its sign bit flipped), then the same scale entries.
+ * The bytes per weight element are exactly the GGUF format's (18 or 34 bytes per 32).
+ * n_out is padded up to a multiple of 16 and n_in to a multiple of 128 with zero-scale blocks.
+ * With raw1 != NULL two matrices of equal shape are interleaved 8 rows at a
+ * time (rows 0-7 of each tile from raw0, rows 8-15 from raw1) for the fused
+ * SwiGLU epilogue; the packed matrix then has 2*n_out rows. */
+size_t b200q_packed_bytes(int qtype, int n_out, int n_in);
+int b200q_repack(int qtype, const void* device_raw0, const void* device_raw1, void* device_packed, int n_out, int n_in, void* stream);
+/* packed -> row-major [n_out, n_in] fp32/fp16 (same values as b200q_dequant_raw of the original blocks) */
+int b200q_dequant_packed(int qtype, const void* device_packed, void* device_out, int n_out, int n_in, int out_dtype, void* stream);
+
+/* ---- weight-dequant-fused linear ----------------------------------------
+ * Replaces `Linear.__call__` = x.linear(weight.T, bias) on a GGUF-quantised
+ * weight (tinygrad/nn/__init__.py:177, tinygrad/mixin/op.py:1257-1274,
+ * dot with fp32 accumulation tinygrad/mixin/op.py:367-392), optionally fused with
+ * the RMSNorm in front of it (tinygrad/nn/__init__.py:300-304), the residual add
+ * behind it (tinygrad/llm/model.py:149-150) or the SwiGLU product
+ * (tinygrad/llm/model.py:137).  One launch; weights are streamed once per
+ * activation row. */
+typedef struct b200q_gemv_args {
+  int qtype;                /* B200Q_Q4_0 | B200Q_Q8_0 */
+  int n_out;                /* logical output features (for EPI_SILU_MUL: features of gate == up) */
+  int n_in;                 /* input features, multiple of 32 */
+  int m;                    /* activation rows (1 at decode) */
+  const void* w_packed;     /* device, from b200q_repack, 16-byte aligned */
+  const void* x;            /* device [m, n_in], x_dtype */
+  int x_dtype;              /* B200Q_F32 | B200Q_F16 */
+  int y_dtype;              /* B200Q_F32 | B200Q_F16 */
+  const void* norm_weight;  /* device fp16 [n_in] or NULL: y = W (rmsnorm(x) * norm_weight) */
+  float norm_eps;
+  int epilogue;             /* B200Q_EPI_* */
+  const void* bias;         /* device fp16 [n_out] or NULL */
+  const void* residual;     /* device fp32 [m, n_out] or NULL, added to the result */
+  void* y;                  /* device [m, n_out], y_dtype */
+  int flags;                /* B200Q_FLAG_* */
+  int max_ctas;             /* 0 = library default (a multiple of the SM count) */
+} b200q_gemv_args;
+int b200q_gemv(const b200q_gemv_args* args, void* stream);
+
+/* ---- decode-step kernels -------------------------------------------------
+ * Token embedding lookup to the fp32 residual stream:
+ * `token_embd(tokens).float()` (tinygrad/llm/model.py:359).  The token id is read
+ * on the device from tokens[*pos]. */
+int b200q_embed(const void* device_table_f16, const int32_t* device_tokens, const int32_t* device_pos, float* device_x, int dim,
+                int vocab, int flags, void* stream);
+
+/* One-token GQA attention with RoPE and KV-cache update:
+ * tinygrad/llm/model.py:167-198 for T == 1 (`apply_rope` :29-33, cache store
+ * :184-186, scaled_dot_product_attention tinygrad/mixin/rand.py:298-326).
+ * qkv holds this token's [q | k | v] projections in fp32.  K and V caches are
+ * [n_kv_heads][max_context][head_dim] each, fp16 or fp32.  The context is split
+ * over `n_split` CTAs per KV head; partial results go through `scratch`
+ * (b200q_attn_scratch_bytes) and the last CTA of a head merges them. */
+typedef struct b200q_attn_args {
+  const float* qkv;         /* device [n_heads*head_dim + 2*n_kv_heads*head_dim] */
+  void* k_cache;            /* device */
+  void* v_cache;            /* device */
+  int kv_dtype;             /* B200Q_F16 | B200Q_F32 */
+  const float* rope;        /* device [max_context][rope_dim]: cos || sin (tinygrad/llm/model.py:15-19) */
+  const int32_t* pos;       /* device scalar: position of this token (= tokens already cached) */
+  float* out;               /* device [n_heads*head_dim] fp32 */
+  void* scratch;            /* device, b200q_attn_scratch_bytes(), zero-initialised once */
+  int n_heads, n_kv_heads, head_dim, rope_dim, max_context, n_split;
+  int flags;
+} b200q_attn_args;
+size_t b200q_attn_scratch_bytes(int n_heads, int n_kv_heads, int head_dim, int n_split);
+int b200q_attn_decode(const b200q_attn_args* args, void* stream);
+
+/* Greedy sampling: tokens[*pos + 1] = argmax(logits) (lowest index on ties), then
+ * *pos += 1.  At temperature 0 this is what the Gumbel-max expression of
+ * tinygrad/llm/model.py:364 selects.  scratch: b200q_argmax_scratch_bytes(), zeroed once. */
+size_t b200q_argmax_scratch_bytes(void);
+int b200q_argmax_advance(const float* device_logits, int n, int32_t* device_tokens, int32_t* device_pos, void* scratch, int flags,
+                         void* stream);
+/* *pos += 1 (a prompt token whose logits are not needed) */
+int b200q_advance(int32_t* device_pos, int flags, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

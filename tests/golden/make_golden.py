@@ -73,13 +73,9 @@ def run_llm(tag, cfg, typ, kv_half, prompt, n_new, seed):
       new[k] = ref_weight(v, tgt.shape[0], tgt.shape[1], typ).cast(dtypes.float16)
     else: new[k] = Tensor(v)
   nn.state.load_state_dict(model, new, verbose=False, realize=False)
-  if kv_half:
-    # the benchmark configurations ask for an fp16 KV cache; the block creates its cache lazily
-    # (model.py:200-205), so hand it one of the wanted dtype up front
-    from tinygrad.llm.model import precompute_freqs_cis
-    for b in model.blk:
-      b.cache_kv = Tensor.empty(2, 1, cfg.n_kv_heads, cfg.max_context, cfg.head_dim, dtype=dtypes.float16).contiguous().realize()
-      b.freqs_cis = precompute_freqs_cis(cfg.rope_dim, cfg.max_context, cfg.rope_theta)
+  # The cache dtype is the reference's default float (fp32).  Handing the block an fp16 cache up front does not run on the
+  # interpreter device (its store of fp32 rows into a fp16 buffer raises), so fp16-cache streams cannot be generated here.
+  assert not kv_half
   toks, t0 = [], time.time()
   for tok in model.generate(list(prompt), chunk_size=32, temperature=0.0):
     toks.append(tok); print(tag, len(toks), tok, f"{time.time()-t0:.0f}s", flush=True)
@@ -98,14 +94,13 @@ def tiny_cfg(**kw):
 
 
 if "llm_small" in groups:
-  run_llm("llm_small_kv16", tiny_cfg(), 2, True, [1, 5, 9, 13, 17, 21, 25, 29], 64, seed=1)
-  run_llm("llm_small_kv32", tiny_cfg(), 2, False, [3, 1, 4, 1, 5, 9, 2, 6], 24, seed=2)
+  run_llm("llm_small_kv32", tiny_cfg(), 2, False, [1, 5, 9, 13, 17, 21, 25, 29], 64, seed=1)
 if "llm_q8" in groups:
-  run_llm("llm_q8_bias_kv16", tiny_cfg(qkv_bias=True, n_heads=2, n_kv_heads=1, head_dim=32, rope_dim=32, v_head_dim=32), 8, True,
+  run_llm("llm_q8_bias_kv32", tiny_cfg(qkv_bias=True, n_heads=2, n_kv_heads=1, head_dim=32, rope_dim=32, v_head_dim=32), 8, False,
           [7, 7, 3, 90, 41], 32, seed=3)
 if "llm_wide" in groups:
-  run_llm("llm_wide_kv16", tiny_cfg(dim=128, hidden_dim=384, n_heads=4, n_kv_heads=1, head_dim=32, rope_dim=32, v_head_dim=32, vocab_size=160,
-                                    max_context=112), 2, True, list(range(2, 42)), 64, seed=4)
+  run_llm("llm_wide_kv32", tiny_cfg(dim=128, hidden_dim=384, n_heads=4, n_kv_heads=1, head_dim=32, rope_dim=32, v_head_dim=32, vocab_size=160,
+                                    max_context=112), 2, False, list(range(2, 42)), 64, seed=4)
 
 if "moe" in groups:
   rng = np.random.default_rng(300)

@@ -1,0 +1,67 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every symbol the header
+declares, and rejects bad arguments before touching a device."""
+import ctypes, re, pathlib
+import numpy as np
+import pytest
+from tinygrad_b200 import _lib, build
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def lib():
+  build.build_lib()
+  return _lib.load()
+
+
+def test_exports_every_declared_symbol(lib):
+  header = (ROOT / "include" / "b200q.h").read_text()
+  declared = set(re.findall(r"\b(b200q_[a-z0-9_]+)\s*\(", header))
+  assert declared, "no declarations found in include/b200q.h"
+  for name in sorted(declared):
+    assert hasattr(lib, name), f"{name} is declared in b200q.h but not exported by libb200q.so"
+  assert declared == set(_lib.SIGNATURES), "ctypes signatures and header disagree"
+
+
+def test_strerror_and_version(lib):
+  assert lib.b200q_version() >= 1
+  assert lib.b200q_strerror(0) == b"ok"
+  for code in range(-6, 0): assert b"unknown b200q" not in lib.b200q_strerror(code)
+  assert b"unknown b200q" in lib.b200q_strerror(-99)
+
+
+def test_packed_bytes(lib):
+  assert lib.b200q_packed_bytes(_lib.Q4_0, 4096, 4096) == 4096 * 4096 // 32 * 18   # exactly the GGUF bytes
+  assert lib.b200q_packed_bytes(_lib.Q8_0, 4096, 4096) == 4096 * 4096 // 32 * 34
+  assert lib.b200q_packed_bytes(_lib.Q4_0, 17, 96) == 2 * 1 * 1152                 # padded to 32 rows x 128 columns
+  assert lib.b200q_packed_bytes(_lib.Q6_K, 16, 256) == 0
+  assert lib.b200q_packed_bytes(_lib.Q4_0, 0, 128) == 0
+
+
+def test_bad_arguments_are_rejected_without_a_device(lib):
+  assert lib.b200q_dequant_raw(5, 16, 16, 32, _lib.F32, None) == -1          # unknown type
+  assert lib.b200q_dequant_raw(_lib.Q4_0, 16, 16, 33, _lib.F32, None) == -2  # not whole blocks
+  assert lib.b200q_dequant_raw(_lib.Q6_K, 16, 16, 128, _lib.F32, None) == -2
+  assert lib.b200q_dequant_raw(_lib.Q4_0, None, None, 0, _lib.F32, None) == 0  # empty input is fine
+  assert lib.b200q_repack(_lib.Q4_0, None, None, 16, 16, 32, None) == -1
+  assert lib.b200q_repack(_lib.Q4_0, 16, None, 16, 16, 48, None) == -2
+  assert lib.b200q_repack(_lib.Q4_0, 16, None, 8, 16, 32, None) == -3        # packed buffer must be 16-byte aligned
+  assert lib.b200q_repack(_lib.Q6_K, 16, None, 16, 16, 256, None) == -4
+  a = _lib.GemvArgs(_lib.Q4_0, 16, 128, 1, 16, 16, _lib.F32, _lib.F32, None, 0.0, 0, None, None, 16, 0, 0)
+  a.n_in = 100
+  assert lib.b200q_gemv(ctypes.byref(a), None) == -2
+  a.n_in, a.w_packed = 128, 8
+  assert lib.b200q_gemv(ctypes.byref(a), None) == -3
+  a.w_packed, a.y = 16, None
+  assert lib.b200q_gemv(ctypes.byref(a), None) == -1
+  at = _lib.AttnArgs(16, 16, 16, _lib.F16, 16, 16, 16, 16, 6, 4, 128, 128, 64, 4, 0)
+  assert lib.b200q_attn_decode(ctypes.byref(at), None) == -1                 # heads not a multiple of kv heads
+  at.n_heads, at.head_dim = 8, 100
+  assert lib.b200q_attn_decode(ctypes.byref(at), None) == -2
+  assert lib.b200q_graph_begin(None) == -1
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+  monkeypatch.setattr(_lib, "_lib", None)
+  monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
+  with pytest.raises(_lib.B200QError): _lib.load()

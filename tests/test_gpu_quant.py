@@ -1,0 +1,147 @@
+"""GPU parity: dequantisation (bit-exact), packing (lossless) and the fused GEMV, through the C ABI."""
+import numpy as np
+import pytest
+from oracle import ggml_quant as gq, llm
+from tinygrad_b200 import synth
+from gpu_util import need_gpu, assert_close
+
+pytestmark = pytest.mark.gpu
+TAGS = {"q4_0": 2, "q8_0": 8, "q6_k": 14}
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _gpu(): need_gpu()
+
+
+@pytest.mark.parametrize("tag", list(TAGS))
+def test_dequant_golden_bit_exact(golden, tag):
+  from tinygrad_b200 import quant
+  g = golden("dequant")
+  raw, n = g[f"{tag}_raw"], g[f"{tag}_f32"].size
+  np.testing.assert_array_equal(quant.dequantize(raw, n, TAGS[tag], np.float32).numpy().view(np.uint32), g[f"{tag}_f32"].reshape(-1).view(np.uint32))
+  np.testing.assert_array_equal(quant.dequantize(raw, n, TAGS[tag], np.float16).numpy().view(np.uint16), g[f"{tag}_f16"].reshape(-1).view(np.uint16))
+
+
+@pytest.mark.parametrize("tag", list(TAGS))
+def test_dequant_random_bit_exact(tag):
+  from tinygrad_b200 import quant
+  typ = TAGS[tag]
+  rng = np.random.default_rng(7)
+  raw = synth.BLOCK_MAKERS[typ](64, 2048, rng)
+  nby = synth.GGML_QUANT[typ][1]
+  blocks = raw.reshape(-1, nby)
+  sc = 208 if typ == 14 else 0     # every scale bit pattern that is finite, subnormals included
+  pats = rng.integers(0, 0x7C00, len(blocks)).astype(np.uint16) | (rng.integers(0, 2, len(blocks)).astype(np.uint16) << 15)
+  blocks[:, sc:sc + 2] = pats.view(np.uint8).reshape(-1, 2)
+  n = 64 * 2048
+  ref = gq.dequantize(raw, n, typ)
+  np.testing.assert_array_equal(quant.dequantize(raw, n, typ, np.float32).numpy().view(np.uint32), ref.view(np.uint32))
+  np.testing.assert_array_equal(quant.dequantize(raw, n, typ, np.float16).numpy().view(np.uint16), ref.astype(np.float16).view(np.uint16))
+
+
+def test_dequant_empty_and_errors():
+  from tinygrad_b200 import quant, _lib
+  assert quant.dequantize(np.zeros(0, np.uint8), 0, 2).numpy().size == 0
+  with pytest.raises(ValueError): quant.dequantize(np.zeros(18, np.uint8), 32, 5)
+  with pytest.raises(_lib.B200QError): quant.dequantize(np.zeros(18, np.uint8), 31, 2)
+
+
+@pytest.mark.parametrize("tag,n_out,n_in", [("q4_0", 64, 256), ("q4_0", 40, 96), ("q4_0", 16, 32), ("q8_0", 48, 384), ("q8_0", 17, 160)])
+def test_repack_is_lossless(tag, n_out, n_in):
+  from tinygrad_b200 import quant
+  typ = TAGS[tag]
+  raw = synth.BLOCK_MAKERS[typ](n_out, n_in, np.random.default_rng(n_out * 1000 + n_in))
+  ref = gq.weight_matrix(raw, n_out, n_in, typ)
+  pw = quant.repack(raw, n_out, n_in, typ)
+  assert pw.buf.nbytes == -(-n_out // 16) * -(-n_in // 128) * (1152 if typ == 2 else 2176)
+  np.testing.assert_array_equal(pw.dequantize(np.float32).numpy().view(np.uint32), ref.view(np.uint32))
+  np.testing.assert_array_equal(pw.dequantize(np.float16).numpy().view(np.uint16), ref.astype(np.float16).view(np.uint16))
+
+
+def test_repack_interleaved_gate_up():
+  from tinygrad_b200 import quant
+  n_out, n_in = 24, 128
+  g = synth.q4_0_blocks(n_out, n_in, np.random.default_rng(1)); u = synth.q4_0_blocks(n_out, n_in, np.random.default_rng(2))
+  pw = quant.repack(g, n_out, n_in, 2, raw_up=u)
+  got = pw.dequantize().numpy().reshape(-1, 2, 8, n_in)        # [tile][gate|up][8 rows]
+  np.testing.assert_array_equal(got[:, 0].reshape(-1, n_in)[:n_out], gq.weight_matrix(g, n_out, n_in, 2))
+  np.testing.assert_array_equal(got[:, 1].reshape(-1, n_in)[:n_out], gq.weight_matrix(u, n_out, n_in, 2))
+
+
+def _run_linear(typ, n_out, n_in, x, **kw):
+  from tinygrad_b200 import quant
+  from tinygrad_b200.runtime import DeviceBuffer
+  raw = synth.BLOCK_MAKERS[typ](n_out, n_in, np.random.default_rng(0))
+  lin = quant.QuantLinear(n_in, n_out, typ, raw, **kw)
+  return raw, lin(DeviceBuffer.from_numpy(x)).numpy()
+
+
+def test_single_q4_0_linear_4096_fp16():
+  """Config 1: Q4_0 [4096 x 4096], scales |N(0,0.02)|, x fp16 [1,4096] ~ N(0,1), seed 0."""
+  rng = np.random.default_rng(0)
+  raw = synth.q4_0_blocks(4096, 4096, rng)
+  x = rng.standard_normal((1, 4096)).astype(np.float16)
+  from tinygrad_b200 import quant
+  from tinygrad_b200.runtime import DeviceBuffer
+  y = quant.QuantLinear(4096, 4096, 2, raw)(DeviceBuffer.from_numpy(x)).numpy()
+  assert y.dtype == np.float16 and y.shape == (1, 4096)
+  w = gq.weight_matrix(raw, 4096, 4096, 2)
+  assert_close(y, llm.linear_f16(x, w), what="fp16-product reference")
+  assert_close(y, llm.linear(x.astype(np.float32), w), what="fp32 reference")
+
+
+@pytest.mark.parametrize("tag,n_out,n_in,m", [("q4_0", 256, 1024, 1), ("q4_0", 40, 96, 3), ("q4_0", 16, 32, 1), ("q4_0", 4096, 14336, 1),
+                                               ("q8_0", 512, 3584, 1), ("q8_0", 33, 160, 2), ("q4_0", 128, 128 * 9, 1)])
+def test_linear_fp32_matches_oracle(tag, n_out, n_in, m):
+  typ = TAGS[tag]
+  x = np.random.default_rng(3).standard_normal((m, n_in)).astype(np.float32)
+  raw, y = _run_linear(typ, n_out, n_in, x)
+  ref = llm.linear(x, gq.weight_matrix(raw, n_out, n_in, typ))
+  assert y.dtype == np.float32
+  assert_close(y, ref, tol=1e-2)
+  # the hi/lo activation split keeps fp32-grade accuracy, far inside the stated tolerance
+  assert np.abs(y - ref).max() <= 2e-4 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
+def test_linear_golden_from_reference(golden, tag):
+  from tinygrad_b200 import quant
+  from tinygrad_b200.runtime import DeviceBuffer
+  g = golden("linear")
+  n_out, n_in = (int(v) for v in g[f"{tag}_shape"])
+  lin = quant.QuantLinear(n_in, n_out, TAGS[tag], g[f"{tag}_raw"])
+  assert_close(lin(DeviceBuffer.from_numpy(g[f"{tag}_x32"])).numpy(), g[f"{tag}_y32"], what="fp32 activations")
+  assert_close(lin(DeviceBuffer.from_numpy(g[f"{tag}_x16"])).numpy(), g[f"{tag}_y16"], what="fp16 activations")
+
+
+def test_linear_bias_and_empty_batch():
+  bias = np.random.default_rng(4).standard_normal(48).astype(np.float16)
+  x = np.random.default_rng(5).standard_normal((2, 256)).astype(np.float32)
+  raw, y = _run_linear(8, 48, 256, x, bias=bias)
+  assert_close(y, llm.linear(x, gq.weight_matrix(raw, 48, 256, 8), bias))
+  _, y0 = _run_linear(2, 32, 128, np.zeros((0, 128), np.float32))
+  assert y0.shape == (0, 32)
+
+
+def test_fused_norm_residual_and_swiglu():
+  from tinygrad_b200 import quant, _lib
+  from tinygrad_b200.runtime import DeviceBuffer
+  rng = np.random.default_rng(6)
+  dim, hid = 384, 1000
+  x = rng.standard_normal(dim).astype(np.float32) * 3
+  nw = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float16)
+  g, u, d = (synth.q4_0_blocks(*s, rng) for s in ((hid, dim), (hid, dim), (dim, hid + 24)))
+  wg, wu, wd = gq.weight_matrix(g, hid, dim, 2), gq.weight_matrix(u, hid, dim, 2), gq.weight_matrix(d, dim, hid + 24, 2)
+  xn = llm.rmsnorm(x[None], nw, 1e-5)
+  act_ref = (llm.silu(llm.linear(xn, wg)) * llm.linear(xn, wu))[0]
+  pgu = quant.repack(g, hid, dim, 2, raw_up=u)
+  dx, dnw, dact = DeviceBuffer.from_numpy(x), DeviceBuffer.from_numpy(nw), DeviceBuffer.empty((hid + 24,), np.float32, zero=True)
+  quant.gemv(pgu.buf.ptr, 2, hid, dim, dx, dact, norm_weight=dnw, norm_eps=1e-5, epilogue=_lib.EPI_SILU_MUL)
+  act = dact.numpy()
+  assert_close(act[:hid], act_ref, what="norm + gate/up + swiglu")
+  assert (act[hid:] == 0).all()                                  # rows past n_out untouched
+  act_full = np.concatenate([act_ref, np.zeros(24, np.float32)])
+  pd = quant.repack(d, dim, hid + 24, 2)
+  dres, dy = DeviceBuffer.from_numpy(x), DeviceBuffer.empty((dim,), np.float32)
+  quant.gemv(pd.buf.ptr, 2, dim, hid + 24, dact, dres, residual=dres)   # in place on the residual stream
+  assert_close(dres.numpy(), x + llm.linear(act_full[None], wd)[0], what="down + residual")

@@ -108,7 +108,7 @@ def _llm_from_golden(g):
   return cfg, w
 
 
-@pytest.mark.parametrize("name", ["llm_small_kv16", "llm_small_kv32", "llm_q8_bias_kv16", "llm_wide_kv16"])
+@pytest.mark.parametrize("name", ["llm_small_kv32", "llm_q8_bias_kv32", "llm_wide_kv32"])
 def test_greedy_token_stream_matches_reference(golden, name):
   g = golden(name)
   cfg, w = _llm_from_golden(g)

@@ -1,0 +1,95 @@
+"""ctypes binding of libb200q.so.  There is no fallback: if the library is
+missing or a call fails, the Python wrappers raise."""
+import ctypes, pathlib
+from ctypes import c_int, c_int32, c_int64, c_size_t, c_float, c_void_p, c_char_p, POINTER, Structure
+
+LIB_PATH = pathlib.Path(__file__).resolve().parent / "libb200q.so"
+
+Q4_0, Q8_0, Q6_K = 2, 8, 14
+F32, F16 = 0, 1
+EPI_LINEAR, EPI_SILU_MUL = 0, 1
+FLAG_PDL = 1
+
+
+class GemvArgs(Structure):
+  _fields_ = [("qtype", c_int), ("n_out", c_int), ("n_in", c_int), ("m", c_int), ("w_packed", c_void_p), ("x", c_void_p),
+              ("x_dtype", c_int), ("y_dtype", c_int), ("norm_weight", c_void_p), ("norm_eps", c_float), ("epilogue", c_int),
+              ("bias", c_void_p), ("residual", c_void_p), ("y", c_void_p), ("flags", c_int), ("max_ctas", c_int)]
+
+
+class AttnArgs(Structure):
+  _fields_ = [("qkv", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("kv_dtype", c_int), ("rope", c_void_p), ("pos", c_void_p),
+              ("out", c_void_p), ("scratch", c_void_p), ("n_heads", c_int), ("n_kv_heads", c_int), ("head_dim", c_int), ("rope_dim", c_int),
+              ("max_context", c_int), ("n_split", c_int), ("flags", c_int)]
+
+
+# name -> (restype, argtypes); every symbol include/b200q.h declares
+SIGNATURES = {
+  "b200q_strerror": (c_char_p, [c_int]),
+  "b200q_last_cuda_error": (c_char_p, []),
+  "b200q_version": (c_int, []),
+  "b200q_device_count": (c_int, [POINTER(c_int)]),
+  "b200q_set_device": (c_int, [c_int]),
+  "b200q_device_props": (c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_size_t)]),
+  "b200q_malloc": (c_int, [POINTER(c_void_p), c_size_t]),
+  "b200q_free": (c_int, [c_void_p]),
+  "b200q_host_alloc": (c_int, [POINTER(c_void_p), c_size_t]),
+  "b200q_host_free": (c_int, [c_void_p]),
+  "b200q_memcpy_h2d": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
+  "b200q_memcpy_d2h": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
+  "b200q_memcpy_d2d": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
+  "b200q_memset": (c_int, [c_void_p, c_int, c_size_t, c_void_p]),
+  "b200q_stream_create": (c_int, [POINTER(c_void_p)]),
+  "b200q_stream_destroy": (c_int, [c_void_p]),
+  "b200q_stream_synchronize": (c_int, [c_void_p]),
+  "b200q_device_synchronize": (c_int, []),
+  "b200q_event_create": (c_int, [POINTER(c_void_p)]),
+  "b200q_event_destroy": (c_int, [c_void_p]),
+  "b200q_event_record": (c_int, [c_void_p, c_void_p]),
+  "b200q_event_synchronize": (c_int, [c_void_p]),
+  "b200q_event_elapsed_ms": (c_int, [c_void_p, c_void_p, POINTER(c_float)]),
+  "b200q_graph_begin": (c_int, [c_void_p]),
+  "b200q_graph_end": (c_int, [c_void_p, POINTER(c_void_p)]),
+  "b200q_graph_launch": (c_int, [c_void_p, c_void_p]),
+  "b200q_graph_destroy": (c_int, [c_void_p]),
+  "b200q_dequant_raw": (c_int, [c_int, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+  "b200q_packed_bytes": (c_size_t, [c_int, c_int, c_int]),
+  "b200q_repack": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+  "b200q_dequant_packed": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+  "b200q_gemv": (c_int, [POINTER(GemvArgs), c_void_p]),
+  "b200q_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+  "b200q_attn_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+  "b200q_attn_decode": (c_int, [POINTER(AttnArgs), c_void_p]),
+  "b200q_argmax_scratch_bytes": (c_size_t, []),
+  "b200q_argmax_advance": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+  "b200q_advance": (c_int, [c_void_p, c_int, c_void_p]),
+}
+
+_lib = None
+
+
+class B200QError(RuntimeError):
+  pass
+
+
+def load() -> ctypes.CDLL:
+  """Load the shared library (building it is the job of tinygrad_b200.build)."""
+  global _lib
+  if _lib is not None: return _lib
+  if not LIB_PATH.exists():
+    raise B200QError(f"{LIB_PATH} is missing: run `python -m tinygrad_b200.build` (there is no CPU fallback)")
+  lib = ctypes.CDLL(str(LIB_PATH))
+  for name, (res, args) in SIGNATURES.items():
+    fn = getattr(lib, name)
+    fn.restype, fn.argtypes = res, args
+  _lib = lib
+  return lib
+
+
+def check(rc: int) -> None:
+  """Raise on a negative status, like `check(status)` of tinygrad/runtime/ops_cuda.py:13-16."""
+  if rc == 0: return
+  lib = load()
+  msg = lib.b200q_strerror(rc).decode()
+  if rc == -5: msg += ": " + lib.b200q_last_cuda_error().decode()
+  raise B200QError(f"b200q error {rc}: {msg}")

@@ -1,0 +1,64 @@
+// Shared declarations for the sm_100a kernels and their C-ABI launchers.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include "../../include/b200q.h"
+
+#define B200Q_CHECK_CUDA(expr)                                   \
+  do {                                                           \
+    cudaError_t _e = (expr);                                     \
+    if (_e != cudaSuccess) { b200q_set_cuda_error(_e); return B200Q_ERR_CUDA; } \
+  } while (0)
+
+void b200q_set_cuda_error(cudaError_t e);
+
+// ---- packed weight layout (see include/b200q.h for the byte-level description)
+constexpr int TILE_ROWS = 16;       // output rows per tile (one mma.m16n8k16 A operand)
+constexpr int GROUP_ELEMS = 128;    // K elements per tile: 4 quant blocks of 32 (Q4_0/Q8_0)
+
+__host__ __device__ constexpr int tile_bytes(int qtype) {
+  return qtype == B200Q_Q4_0 ? 1152 : qtype == B200Q_Q8_0 ? 2176 : 0;
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// ---- programmatic dependent launch (PDL).  Every kernel calls pdl_wait() before it
+// touches memory another kernel wrote, so a chain of launches stays ordered.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launch with the programmatic-stream-serialization attribute when `pdl` is set.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                                   Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {   // weights are read once: do not keep them in L1
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ldg_stream(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}

@@ -1,0 +1,285 @@
+// The non-GEMV kernels of one decode step: embedding lookup, one-token GQA attention
+// with RoPE and KV-cache update, greedy arg-max.  Semantics follow
+// tinygrad/llm/model.py:167-198 (attention, T == 1), :29-33 (RoPE), :358-364 (forward).
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+
+__global__ void embed_kernel(const __half* __restrict__ table, const int32_t* __restrict__ tokens, const int32_t* __restrict__ pos,
+                             float* __restrict__ x, int dim, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
+  int tok = tokens[*pos];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += gridDim.x * blockDim.x)
+    x[i] = __half2float(table[(size_t)tok * dim + i]);
+}
+
+__global__ void advance_kernel(int32_t* pos) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) *pos += 1;
+}
+
+// ---------------------------------------------------------------------------
+// attention.  grid (n_kv_heads, n_split); one warp per query head of the KV group.
+// Scores: each lane takes whole positions (a full head_dim dot product against the
+// roped query held in shared memory, no shuffles in the loop).  Values: each lane owns
+// 4 consecutive head dims and walks the positions with the probabilities broadcast
+// from shared memory.  Scratch layout:
+//   float partial[n_heads][n_split][head_dim + 4]   (o[head_dim], running max, denominator, 2 pad)
+//   uint  counter[n_kv_heads]                       (arrival count, reset by the last CTA)
+template <typename KV> struct KvIO;
+template <> struct KvIO<__half> {
+  static constexpr int VEC = 8;   // elements per 16-byte load
+  static __device__ __forceinline__ float dot(const __half* k, const float* q) {
+    uint4 r = *reinterpret_cast<const uint4*>(k);
+    float2 a = __half22float2(*reinterpret_cast<__half2*>(&r.x)), b = __half22float2(*reinterpret_cast<__half2*>(&r.y));
+    float2 c = __half22float2(*reinterpret_cast<__half2*>(&r.z)), d = __half22float2(*reinterpret_cast<__half2*>(&r.w));
+    return a.x * q[0] + a.y * q[1] + b.x * q[2] + b.y * q[3] + c.x * q[4] + c.y * q[5] + d.x * q[6] + d.y * q[7];
+  }
+  static __device__ __forceinline__ float4 load4(const __half* p) {
+    uint2 r = *reinterpret_cast<const uint2*>(p);
+    float2 a = __half22float2(*reinterpret_cast<__half2*>(&r.x)), b = __half22float2(*reinterpret_cast<__half2*>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void store(__half* p, float v) { *p = __float2half_rn(v); }
+};
+template <> struct KvIO<float> {
+  static constexpr int VEC = 4;
+  static __device__ __forceinline__ float dot(const float* k, const float* q) {
+    float4 r = *reinterpret_cast<const float4*>(k);
+    return r.x * q[0] + r.y * q[1] + r.z * q[2] + r.w * q[3];
+  }
+  static __device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+
+constexpr int MAX_HD = 128;
+constexpr int MAX_REP = 8;
+constexpr int ATTN_CHUNK = 256;   // positions whose scores are held in shared memory at a time
+
+template <typename KV>
+__global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_attn_args a) {
+  __shared__ __align__(16) float s_q[MAX_REP][MAX_HD];   // roped queries of this KV group
+  __shared__ float s_sc[MAX_REP][ATTN_CHUNK];            // scores, then probabilities
+  __shared__ int s_last;
+  const int kvh = blockIdx.x, split = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int hd = a.head_dim, n_rep = a.n_heads / a.n_kv_heads, half_r = a.rope_dim >> 1;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pos = *a.pos;
+  const int n_ctx = pos + 1;
+  const float* rope = a.rope + (size_t)pos * a.rope_dim;
+  const float* kq = a.qkv + (size_t)a.n_heads * hd + (size_t)kvh * hd;
+  const float* vq = a.qkv + (size_t)(a.n_heads + a.n_kv_heads) * hd + (size_t)kvh * hd;
+  KV* kc = reinterpret_cast<KV*>(a.k_cache) + (size_t)kvh * a.max_context * hd;
+  KV* vc = reinterpret_cast<KV*>(a.v_cache) + (size_t)kvh * a.max_context * hd;
+  const int per = (n_ctx + a.n_split - 1) / a.n_split;
+  const int lo = split * per, hi = min(n_ctx, lo + per);
+
+  // RoPE, half-split layout: (x1 cos - x2 sin) || (x2 cos + x1 sin); dims past rope_dim pass through
+  for (int i = threadIdx.x; i < n_rep * hd; i += blockDim.x) {
+    int r = i / hd, d = i - r * hd;
+    const float* q = a.qkv + (size_t)(kvh * n_rep + r) * hd;
+    float v = q[d];
+    if (d < half_r) v = q[d] * rope[d] - q[d + half_r] * rope[half_r + d];
+    else if (d < a.rope_dim) v = q[d] * rope[d - half_r] + q[d - half_r] * rope[d];
+    s_q[r][d] = v;
+  }
+  if (lo <= pos && pos < hi) {   // the CTA whose slice holds the new position appends it to the cache; nobody else reads it
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+      float v = kq[d];
+      if (d < half_r) v = kq[d] * rope[d] - kq[d + half_r] * rope[half_r + d];
+      else if (d < a.rope_dim) v = kq[d] * rope[d - half_r] + kq[d - half_r] * rope[d];
+      KvIO<KV>::store(kc + (size_t)pos * hd + d, v);
+      KvIO<KV>::store(vc + (size_t)pos * hd + d, vq[d]);
+    }
+  }
+  __syncthreads();   // queries staged; the appended row is visible to this CTA
+
+  const int d0 = lane * 4;
+  const bool dl = d0 < hd;
+  const float scale = 1.0f / sqrtf((float)hd);
+  float* partial = reinterpret_cast<float*>(a.scratch);
+  const int pstride = hd + 4;   // keeps every record 16-byte aligned
+  if (warp < n_rep) {
+    float mx = -INFINITY, den = 0.f;
+    float4 o = make_float4(0, 0, 0, 0);
+    float* sc = s_sc[warp];
+    const float* q = s_q[warp];
+    for (int base = lo; base < hi; base += ATTN_CHUNK) {
+      const int n = min(ATTN_CHUNK, hi - base);
+      float lmax = -INFINITY;
+      for (int i = lane; i < n; i += 32) {
+        const KV* kr = kc + (size_t)(base + i) * hd;
+        float s = 0.f;
+        for (int d = 0; d < hd; d += KvIO<KV>::VEC) s += KvIO<KV>::dot(kr + d, q + d);
+        s *= scale;
+        sc[i] = s;
+        lmax = fmaxf(lmax, s);
+      }
+      float nm = fmaxf(mx, warp_max(lmax));
+      float corr = __expf(mx - nm), lsum = 0.f;
+      for (int i = lane; i < n; i += 32) { float pr = __expf(sc[i] - nm); sc[i] = pr; lsum += pr; }
+      den = den * corr + warp_sum(lsum);
+      o.x *= corr; o.y *= corr; o.z *= corr; o.w *= corr;
+      mx = nm;
+      __syncwarp();
+      if (dl) {
+        const KV* vr = vc + (size_t)base * hd + d0;
+#pragma unroll 4
+        for (int i = 0; i < n; i++) {
+          float pr = sc[i];
+          float4 v = KvIO<KV>::load4(vr + (size_t)i * hd);
+          o.x = fmaf(pr, v.x, o.x); o.y = fmaf(pr, v.y, o.y); o.z = fmaf(pr, v.z, o.z); o.w = fmaf(pr, v.w, o.w);
+        }
+      }
+      __syncwarp();
+    }
+    float* pp = partial + ((size_t)(kvh * n_rep + warp) * a.n_split + split) * pstride;
+    if (dl) *reinterpret_cast<float4*>(pp + d0) = o;
+    if (lane == 0) { pp[hd] = mx; pp[hd + 1] = den; }
+  }
+  // last CTA of this KV head merges the splits
+  __threadfence();
+  __syncthreads();
+  unsigned* counter = reinterpret_cast<unsigned*>(partial + (size_t)a.n_heads * a.n_split * pstride);
+  if (threadIdx.x == 0) {
+    unsigned prev = atomicAdd(&counter[kvh], 1u);
+    s_last = (prev == (unsigned)a.n_split - 1);
+    if (s_last) counter[kvh] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (warp < n_rep) {
+    const float* hp = partial + (size_t)(kvh * n_rep + warp) * a.n_split * pstride;
+    float gm = -INFINITY;
+    for (int s = 0; s < a.n_split; s++) gm = fmaxf(gm, __ldcg(hp + s * pstride + hd));
+    float den = 0.f;
+    float4 o = make_float4(0, 0, 0, 0);
+    for (int s = 0; s < a.n_split; s++) {
+      float m_s = __ldcg(hp + s * pstride + hd), l_s = __ldcg(hp + s * pstride + hd + 1);
+      if (l_s == 0.f) continue;            // empty slice
+      float w = __expf(m_s - gm);
+      den += w * l_s;
+      if (dl) {
+        const float* op = hp + s * pstride + d0;
+        o.x += w * __ldcg(op); o.y += w * __ldcg(op + 1); o.z += w * __ldcg(op + 2); o.w += w * __ldcg(op + 3);
+      }
+    }
+    if (dl) {
+      float inv = 1.f / den;
+      float* out = a.out + (size_t)(kvh * n_rep + warp) * hd + d0;
+      out[0] = o.x * inv; out[1] = o.y * inv; out[2] = o.z * inv; out[3] = o.w * inv;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// arg-max with the lowest index winning ties, then tokens[pos+1] = it and pos += 1.
+// scratch: float val[ARGMAX_CTAS], int idx[ARGMAX_CTAS], uint counter.
+constexpr int ARGMAX_CTAS = 128;
+constexpr int ARGMAX_THREADS = 256;
+
+__device__ __forceinline__ void argmax_combine(float& v, int& i, float ov, int oi) {
+  if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const float* __restrict__ logits, int n, int32_t* tokens, int32_t* pos,
+                                                                float* sval, int* sidx, unsigned* counter) {
+  __shared__ float wv[ARGMAX_THREADS / 32];
+  __shared__ int wi[ARGMAX_THREADS / 32];
+  __shared__ int s_last;
+  pdl_launch_dependents();
+  pdl_wait();
+  float v = -INFINITY; int idx = 0x7fffffff;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) argmax_combine(v, idx, logits[i], i);
+  auto block_reduce = [&]() {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, v, o); int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      argmax_combine(v, idx, ov, oi);
+    }
+    if ((threadIdx.x & 31) == 0) { wv[threadIdx.x >> 5] = v; wi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      v = threadIdx.x < ARGMAX_THREADS / 32 ? wv[threadIdx.x] : -INFINITY;
+      idx = threadIdx.x < ARGMAX_THREADS / 32 ? wi[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, v, o); int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        argmax_combine(v, idx, ov, oi);
+      }
+    }
+  };
+  block_reduce();
+  if (threadIdx.x == 0) {
+    sval[blockIdx.x] = v; sidx[blockIdx.x] = idx;
+    __threadfence();
+    unsigned prev = atomicAdd(counter, 1u);
+    s_last = (prev == gridDim.x - 1);
+    if (s_last) *counter = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  v = -INFINITY; idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) argmax_combine(v, idx, __ldcg(sval + i), __ldcg(sidx + i));
+  __syncthreads();
+  block_reduce();
+  if (threadIdx.x == 0) {
+    int p = *pos;
+    tokens[p + 1] = idx == 0x7fffffff ? 0 : idx;
+    *pos = p + 1;
+  }
+}
+
+}  // namespace
+
+extern "C" int b200q_embed(const void* table, const int32_t* tokens, const int32_t* pos, float* x, int dim, int vocab, int flags, void* stream) {
+  if (!table || !tokens || !pos || !x || dim <= 0 || vocab <= 0) return B200Q_ERR_BAD_ARG;
+  B200Q_CHECK_CUDA(launch_k(embed_kernel, dim3(ceil_div(dim, 256)), dim3(256), 0, (cudaStream_t)stream, (flags & B200Q_FLAG_PDL) != 0,
+                            (const __half*)table, tokens, pos, x, dim, vocab));
+  return B200Q_OK;
+}
+
+extern "C" int b200q_advance(int32_t* pos, int flags, void* stream) {
+  if (!pos) return B200Q_ERR_BAD_ARG;
+  B200Q_CHECK_CUDA(launch_k(advance_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, (flags & B200Q_FLAG_PDL) != 0, pos));
+  return B200Q_OK;
+}
+
+extern "C" size_t b200q_attn_scratch_bytes(int n_heads, int n_kv_heads, int head_dim, int n_split) {
+  if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || n_split <= 0) return 0;
+  return ((size_t)n_heads * n_split * (head_dim + 4)) * sizeof(float) + (size_t)n_kv_heads * sizeof(unsigned);
+}
+
+extern "C" int b200q_attn_decode(const b200q_attn_args* a, void* stream) {
+  if (!a || !a->qkv || !a->k_cache || !a->v_cache || !a->rope || !a->pos || !a->out || !a->scratch) return B200Q_ERR_BAD_ARG;
+  if (a->n_heads <= 0 || a->n_kv_heads <= 0 || a->n_heads % a->n_kv_heads || a->n_split <= 0 || a->max_context <= 0) return B200Q_ERR_BAD_ARG;
+  if (a->head_dim <= 0 || a->head_dim > MAX_HD || a->head_dim % 8 || a->n_heads / a->n_kv_heads > MAX_REP) return B200Q_ERR_BAD_SHAPE;
+  if (a->rope_dim < 0 || a->rope_dim > a->head_dim || a->rope_dim % 2) return B200Q_ERR_BAD_SHAPE;
+  if (a->kv_dtype != B200Q_F16 && a->kv_dtype != B200Q_F32) return B200Q_ERR_BAD_ARG;
+  if (((uintptr_t)a->k_cache | (uintptr_t)a->v_cache | (uintptr_t)a->qkv | (uintptr_t)a->out | (uintptr_t)a->scratch) & 15) return B200Q_ERR_MISALIGNED;
+  int n_rep = a->n_heads / a->n_kv_heads;
+  dim3 grid(a->n_kv_heads, a->n_split), block(n_rep * 32);
+  bool pdl = (a->flags & B200Q_FLAG_PDL) != 0;
+  if (a->kv_dtype == B200Q_F16) B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<__half>, grid, block, 0, (cudaStream_t)stream, pdl, *a));
+  else B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<float>, grid, block, 0, (cudaStream_t)stream, pdl, *a));
+  return B200Q_OK;
+}
+
+extern "C" size_t b200q_argmax_scratch_bytes(void) { return ARGMAX_CTAS * (sizeof(float) + sizeof(int)) + sizeof(unsigned); }
+
+extern "C" int b200q_argmax_advance(const float* logits, int n, int32_t* tokens, int32_t* pos, void* scratch, int flags, void* stream) {
+  if (!logits || !tokens || !pos || !scratch || n <= 0) return B200Q_ERR_BAD_ARG;
+  float* sval = (float*)scratch; int* sidx = (int*)(sval + ARGMAX_CTAS); unsigned* counter = (unsigned*)(sidx + ARGMAX_CTAS);
+  int grid = ceil_div(n, ARGMAX_THREADS); if (grid > ARGMAX_CTAS) grid = ARGMAX_CTAS;
+  B200Q_CHECK_CUDA(launch_k(argmax_kernel, dim3(grid), dim3(ARGMAX_THREADS), 0, (cudaStream_t)stream, (flags & B200Q_FLAG_PDL) != 0,
+                            logits, n, tokens, pos, sval, sidx, counter));
+  return B200Q_OK;
+}

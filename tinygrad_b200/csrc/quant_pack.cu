@@ -1,0 +1,175 @@
+// GGUF block formats: bit-exact dequantisation and the one-time lossless re-tiling
+// into the layout the GEMV kernels stream (layout described in include/b200q.h).
+// Semantics follow tinygrad/llm/gguf.py:38-72 (q_to_uint8, Q4_0 :46, Q8_0 :56, Q6_K :68-72).
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// raw GGUF blocks -> values.  One thread per element; fp32 results are single
+// IEEE multiplies in the reference's order, so they are bit-identical to it.
+template <typename OutT>
+__device__ __forceinline__ void store_val(OutT* out, int64_t i, float v);
+template <> __device__ __forceinline__ void store_val<float>(float* out, int64_t i, float v) { out[i] = v; }
+template <> __device__ __forceinline__ void store_val<__half>(__half* out, int64_t i, float v) { out[i] = __float2half_rn(v); }
+
+__device__ __forceinline__ float load_f16(const uint8_t* p) {
+  return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8))));
+}
+
+template <typename OutT>
+__global__ void dequant_raw_kernel(int qtype, const uint8_t* __restrict__ raw, OutT* __restrict__ out, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v;
+  if (qtype == B200Q_Q4_0) {
+    // element e of a block: low nibble of byte e (e < 16) or high nibble of byte e-16
+    const uint8_t* b = raw + (i >> 5) * 18; int e = (int)(i & 31);
+    int nib = (b[2 + (e & 15)] >> ((e >> 4) * 4)) & 0xF;
+    v = __fmul_rn((float)(nib - 8), load_f16(b));
+  } else if (qtype == B200Q_Q8_0) {
+    const uint8_t* b = raw + (i >> 5) * 34; int e = (int)(i & 31);
+    v = __fmul_rn(load_f16(b), (float)(int8_t)b[2 + e]);
+  } else {  // Q6_K: 256 elements in 210 bytes: ql[128] qh[64] scales[16] d
+    const uint8_t* b = raw + (i >> 8) * 210; int e = (int)(i & 255);
+    int hh = e >> 7, m = e & 127;
+    int xl = (b[hh * 64 + (m & 63)] >> ((m >> 6) * 4)) & 0xF;
+    int xh = (b[128 + hh * 32 + (m & 31)] >> ((m >> 5) * 2)) & 3;
+    int q = (int)(int8_t)(xl | (xh << 4)) - 32;
+    float sc = (float)(int8_t)b[192 + (e >> 4)];
+    v = __fmul_rn(__fmul_rn(load_f16(b + 208), (float)q), sc);   // (d * q) * scales, in that order
+  }
+  store_val<OutT>(out, i, v);
+}
+
+// ---------------------------------------------------------------------------
+// re-tiling.  One thread per (tile, half, lane) = one (row, block) pair.
+__global__ void repack_kernel(int qtype, const uint8_t* __restrict__ raw0, const uint8_t* __restrict__ raw1, uint8_t* __restrict__ packed,
+                              int n_out, int nblk, int n_row_tiles, int kgroups) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t total = (int64_t)n_row_tiles * kgroups * 64;
+  if (idx >= total) return;
+  int l = (int)(idx & 31), h = (int)((idx >> 5) & 1);
+  int64_t tile = idx >> 6;
+  int j = (int)(tile % kgroups), rt = (int)(tile / kgroups);
+  int g = l >> 2, t = l & 3;
+  int blk = j * 4 + t;
+  const uint8_t* src = nullptr;
+  int row;
+  if (raw1 == nullptr) { row = rt * 16 + h * 8 + g; if (row < n_out && blk < nblk) src = raw0; }
+  else { row = rt * 8 + g; if (row < n_out && blk < nblk) src = h ? raw1 : raw0; }
+  const int bbytes = qtype == B200Q_Q4_0 ? 18 : 34;
+  const int tbytes = tile_bytes(qtype);
+  uint8_t* tp = packed + tile * tbytes;
+  unsigned short scale = 0;   // fp16 zero: a padded block contributes nothing
+  if (qtype == B200Q_Q4_0) {
+    uint32_t w[4] = {0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u};   // nibble 8 == value 0
+    if (src) {
+      const uint8_t* b = src + ((int64_t)row * nblk + blk) * bbytes;
+      scale = (unsigned short)(b[0] | (b[1] << 8));
+      for (int i = 0; i < 4; i++) w[i] = b[2 + 4 * i] | (b[3 + 4 * i] << 8) | (b[4 + 4 * i] << 16) | ((uint32_t)b[5 + 4 * i] << 24);
+    }
+    reinterpret_cast<uint4*>(tp)[h * 32 + l] = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    uint32_t w[8];
+    for (int i = 0; i < 8; i++) w[i] = 0x80808080u;                          // biased zero
+    if (src) {
+      const uint8_t* b = src + ((int64_t)row * nblk + blk) * bbytes;
+      scale = (unsigned short)(b[0] | (b[1] << 8));
+      for (int i = 0; i < 8; i++)
+        w[i] = (b[2 + 4 * i] | (b[3 + 4 * i] << 8) | (b[4 + 4 * i] << 16) | ((uint32_t)b[5 + 4 * i] << 24)) ^ 0x80808080u;
+    }
+    reinterpret_cast<uint4*>(tp)[(2 * h) * 32 + l] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4*>(tp)[(2 * h + 1) * 32 + l] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+  unsigned short* sp = reinterpret_cast<unsigned short*>(tp + (tbytes - 128));
+  sp[(2 * g + (t >> 1)) * 4 + h * 2 + (t & 1)] = scale;
+}
+
+// packed -> row-major values, rows in packed order.  One thread per (row, block).
+template <typename OutT>
+__global__ void dequant_packed_kernel(int qtype, const uint8_t* __restrict__ packed, OutT* __restrict__ out, int rows, int n_in,
+                                      int n_row_tiles, int kgroups) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t total = (int64_t)n_row_tiles * kgroups * 64;
+  if (idx >= total) return;
+  int l = (int)(idx & 31), h = (int)((idx >> 5) & 1);
+  int64_t tile = idx >> 6;
+  int j = (int)(tile % kgroups), rt = (int)(tile / kgroups);
+  int g = l >> 2, t = l & 3;
+  int row = rt * 16 + h * 8 + g, blk = j * 4 + t;
+  if (row >= rows || blk * 32 >= n_in) return;
+  const int tbytes = tile_bytes(qtype);
+  const uint8_t* tp = packed + tile * tbytes;
+  const unsigned short* sp = reinterpret_cast<const unsigned short*>(tp + (tbytes - 128));
+  float d = __half2float(__ushort_as_half(sp[(2 * g + (t >> 1)) * 4 + h * 2 + (t & 1)]));
+  OutT* o = out + (int64_t)row * n_in + blk * 32;
+  if (qtype == B200Q_Q4_0) {
+    uint4 q = reinterpret_cast<const uint4*>(tp)[h * 32 + l];
+    uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    for (int e = 0; e < 32; e++) {
+      int byte = e & 15, nib = (w[byte >> 2] >> ((byte & 3) * 8 + (e >> 4) * 4)) & 0xF;
+      store_val<OutT>(o, e, __fmul_rn((float)(nib - 8), d));
+    }
+  } else {
+    for (int half = 0; half < 2; half++) {
+      uint4 q = reinterpret_cast<const uint4*>(tp)[(2 * h + half) * 32 + l];
+      uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      for (int e = 0; e < 16; e++) {
+        int v = (int)(int8_t)(((w[e >> 2] >> ((e & 3) * 8)) & 0xFF) ^ 0x80);
+        store_val<OutT>(o, half * 16 + e, __fmul_rn(d, (float)v));
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+static bool known_qtype(int q) { return q == B200Q_Q4_0 || q == B200Q_Q8_0 || q == B200Q_Q6_K; }
+
+extern "C" int b200q_dequant_raw(int qtype, const void* raw, void* out, int64_t n_elems, int out_dtype, void* stream) {
+  if (!known_qtype(qtype) || (out_dtype != B200Q_F32 && out_dtype != B200Q_F16)) return B200Q_ERR_BAD_ARG;
+  if (n_elems < 0 || (n_elems && (!raw || !out))) return B200Q_ERR_BAD_ARG;
+  if (n_elems % (qtype == B200Q_Q6_K ? 256 : 32)) return B200Q_ERR_BAD_SHAPE;
+  if (n_elems == 0) return B200Q_OK;
+  unsigned blocks = (unsigned)((n_elems + 255) / 256);
+  if (out_dtype == B200Q_F32) dequant_raw_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>(qtype, (const uint8_t*)raw, (float*)out, n_elems);
+  else dequant_raw_kernel<__half><<<blocks, 256, 0, (cudaStream_t)stream>>>(qtype, (const uint8_t*)raw, (__half*)out, n_elems);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+extern "C" size_t b200q_packed_bytes(int qtype, int n_out, int n_in) {
+  if ((qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0) || n_out <= 0 || n_in <= 0) return 0;
+  return (size_t)ceil_div(n_out, TILE_ROWS) * ceil_div(n_in, GROUP_ELEMS) * tile_bytes(qtype);
+}
+
+extern "C" int b200q_repack(int qtype, const void* raw0, const void* raw1, void* packed, int n_out, int n_in, void* stream) {
+  if (qtype == B200Q_Q6_K) return B200Q_ERR_UNSUPPORTED;
+  if (qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
+  if (!raw0 || !packed || n_out <= 0 || n_in <= 0) return B200Q_ERR_BAD_ARG;
+  if (n_in % 32) return B200Q_ERR_BAD_SHAPE;
+  if ((uintptr_t)packed & 15) return B200Q_ERR_MISALIGNED;
+  int rows = raw1 ? 2 * ceil_div(n_out, 8) * 8 : n_out;       // interleaved: tiles of 8+8 rows
+  int n_row_tiles = raw1 ? ceil_div(n_out, 8) : ceil_div(n_out, TILE_ROWS), kgroups = ceil_div(n_in, GROUP_ELEMS);
+  (void)rows;
+  int64_t total = (int64_t)n_row_tiles * kgroups * 64;
+  repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(qtype, (const uint8_t*)raw0, (const uint8_t*)raw1,
+                                                                                  (uint8_t*)packed, n_out, n_in / 32, n_row_tiles, kgroups);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+extern "C" int b200q_dequant_packed(int qtype, const void* packed, void* out, int n_out, int n_in, int out_dtype, void* stream) {
+  if (qtype == B200Q_Q6_K) return B200Q_ERR_UNSUPPORTED;
+  if (qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
+  if (!packed || !out || n_out <= 0 || n_in <= 0 || (out_dtype != B200Q_F32 && out_dtype != B200Q_F16)) return B200Q_ERR_BAD_ARG;
+  if (n_in % 32) return B200Q_ERR_BAD_SHAPE;
+  if ((uintptr_t)packed & 15) return B200Q_ERR_MISALIGNED;
+  int n_row_tiles = ceil_div(n_out, TILE_ROWS), kgroups = ceil_div(n_in, GROUP_ELEMS);
+  int64_t total = (int64_t)n_row_tiles * kgroups * 64;
+  unsigned blocks = (unsigned)((total + 255) / 256);
+  if (out_dtype == B200Q_F32)
+    dequant_packed_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>(qtype, (const uint8_t*)packed, (float*)out, n_out, n_in, n_row_tiles, kgroups);
+  else
+    dequant_packed_kernel<__half><<<blocks, 256, 0, (cudaStream_t)stream>>>(qtype, (const uint8_t*)packed, (__half*)out, n_out, n_in, n_row_tiles, kgroups);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}

@@ -1,0 +1,195 @@
+"""The quantized-LLM decode path on one B200: host-side mirror of tinygrad/llm/model.py.
+
+`TransformerConfig` carries the reference's field names (model.py:52-83);
+`Transformer.generate(tokens)` yields greedy tokens like the reference's
+`generate` at temperature 0 (model.py:464-484).  The forward pass of one token is
+five fused launches per block (norm+QKV GEMV, attention, O GEMV+residual,
+norm+gate/up GEMV+SwiGLU, down GEMV+residual) plus embedding, head GEMV and
+arg-max, chained with programmatic dependent launch and replayed as one CUDA graph.
+"""
+from __future__ import annotations
+from dataclasses import dataclass
+import numpy as np
+from . import _lib, quant
+from ._lib import check, F32, F16, EPI_LINEAR, EPI_SILU_MUL, FLAG_PDL
+from .runtime import DeviceBuffer, Stream, Graph, Event
+import ctypes
+
+
+@dataclass(frozen=True)
+class TransformerConfig:           # field names of tinygrad/llm/model.py:52-83 (dense GQA subset)
+  num_blocks: int
+  dim: int
+  hidden_dim: int
+  n_heads: int
+  n_kv_heads: int
+  norm_eps: float
+  vocab_size: int
+  head_dim: int
+  rope_theta: float
+  rope_dim: int
+  v_head_dim: int = 0
+  max_context: int = 0
+  qkv_bias: bool = False
+  kv_dtype: str = "float16"        # the cache dtype; the reference takes it from DEFAULT_FLOAT (model.py:202-203)
+
+
+def precompute_freqs_cis(dim: int, end: int, theta: float) -> np.ndarray:
+  """cos || sin table of tinygrad/llm/model.py:15-19, fp32 [end, dim]."""
+  f = (1.0 / (np.float32(theta) ** (np.arange(0, dim, 2, dtype=np.float32) / np.float32(dim)))).astype(np.float32)
+  ang = np.arange(end, dtype=np.float32)[:, None] * f[None, :]
+  return np.concatenate([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+
+
+class _Block:
+  pass
+
+
+class Transformer:
+  def __init__(self, config: TransformerConfig, state_dict: dict, ggml_type: int = _lib.Q4_0, n_split: int = 0, use_pdl: bool = True,
+               use_graph: bool = True):
+    """state_dict: the reference's tensor names -> numpy arrays; Linear weights as raw
+    GGUF block bytes (uint8), embeddings / norms / biases as fp16."""
+    c = self.config = config
+    assert c.max_context > 0 and c.n_heads % c.n_kv_heads == 0
+    self.qtype, self.flags, self.use_graph = ggml_type, (FLAG_PDL if use_pdl else 0), use_graph
+    self.q_dim, self.kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
+    self.n_split = n_split or max(1, min(32, c.max_context // 64))
+    self.max_context = c.max_context
+    self.stream = Stream()
+    sd = state_dict
+    qkv_rows = self.q_dim + 2 * self.kv_dim
+    assert self.q_dim % 16 == 0 and self.kv_dim % 16 == 0, "q/k/v are packed back to back in whole 16-row tiles"
+    self.blk = []
+    self.weight_bytes = 0
+    for i in range(c.num_blocks):
+      b = _Block()
+      b.qkv = DeviceBuffer(quant.packed_bytes(ggml_type, qkv_rows, c.dim))
+      off = 0
+      for name, rows in (("attn_q", self.q_dim), ("attn_k", self.kv_dim), ("attn_v", self.kv_dim)):
+        quant.repack(sd[f"blk.{i}.{name}.weight"], rows, c.dim, ggml_type, out=b.qkv, out_offset=off)
+        off += quant.packed_bytes(ggml_type, rows, c.dim)
+      b.qkv_bias = None
+      if c.qkv_bias:
+        b.qkv_bias = DeviceBuffer.from_numpy(np.concatenate([np.asarray(sd[f"blk.{i}.attn_{n}.bias"], dtype=np.float16) for n in "qkv"]))
+      b.attn_output = quant.repack(sd[f"blk.{i}.attn_output.weight"], c.dim, self.q_dim, ggml_type)
+      b.gate_up = quant.repack(sd[f"blk.{i}.ffn_gate.weight"], c.hidden_dim, c.dim, ggml_type, raw_up=sd[f"blk.{i}.ffn_up.weight"])
+      b.ffn_down = quant.repack(sd[f"blk.{i}.ffn_down.weight"], c.dim, c.hidden_dim, ggml_type)
+      b.attn_norm = DeviceBuffer.from_numpy(np.asarray(sd[f"blk.{i}.attn_norm.weight"], dtype=np.float16))
+      b.ffn_norm = DeviceBuffer.from_numpy(np.asarray(sd[f"blk.{i}.ffn_norm.weight"], dtype=np.float16))
+      kvdt = np.float16 if c.kv_dtype == "float16" else np.float32
+      b.k_cache = DeviceBuffer.empty((c.n_kv_heads, c.max_context, c.head_dim), kvdt, zero=True)
+      b.v_cache = DeviceBuffer.empty((c.n_kv_heads, c.max_context, c.head_dim), kvdt, zero=True)
+      self.blk.append(b)
+      nel, nby = quant.GGML_QUANT[ggml_type]
+      self.weight_bytes += (qkv_rows * c.dim + c.dim * self.q_dim + 3 * c.hidden_dim * c.dim) // nel * nby
+    self.output = quant.repack(sd["output.weight"], c.vocab_size, c.dim, ggml_type)
+    self.weight_bytes += c.vocab_size * c.dim // quant.GGML_QUANT[ggml_type][0] * quant.GGML_QUANT[ggml_type][1]
+    self.output_norm = DeviceBuffer.from_numpy(np.asarray(sd["output_norm.weight"], dtype=np.float16))
+    self.token_embd = DeviceBuffer.from_numpy(np.asarray(sd["token_embd.weight"], dtype=np.float16))
+    self.rope = DeviceBuffer.from_numpy(precompute_freqs_cis(c.rope_dim, c.max_context, c.rope_theta))
+    # activations of one token (fp32 residual stream, model.py:359)
+    self.x = DeviceBuffer.empty((c.dim,), np.float32, zero=True)
+    self.qkv = DeviceBuffer.empty((qkv_rows,), np.float32, zero=True)
+    self.attn = DeviceBuffer.empty((self.q_dim,), np.float32, zero=True)
+    self.act = DeviceBuffer.empty((c.hidden_dim,), np.float32, zero=True)
+    self.logits = DeviceBuffer.empty((c.vocab_size,), np.float32, zero=True)
+    self.tokens = DeviceBuffer.empty((c.max_context + 1,), np.int32, zero=True)
+    self.pos = DeviceBuffer.empty((1,), np.int32, zero=True)
+    self.attn_scratch = DeviceBuffer(_lib.load().b200q_attn_scratch_bytes(c.n_heads, c.n_kv_heads, c.head_dim, self.n_split), zero=True)
+    self.argmax_scratch = DeviceBuffer(_lib.load().b200q_argmax_scratch_bytes(), zero=True)
+    self._graphs = {}
+    self._cached_tokens: list = []
+    self.launches_per_step = 5 * c.num_blocks + 3
+
+  # ---- one token through the network (launch sequence; captured into a graph) ----
+  def _enqueue_step(self, with_head: bool) -> None:
+    c, lib, s, fl = self.config, _lib.load(), self.stream.ptr, self.flags
+    kvdt = F16 if c.kv_dtype == "float16" else F32
+    check(lib.b200q_embed(self.token_embd.ptr, self.tokens.ptr, self.pos.ptr, self.x.ptr, c.dim, c.vocab_size, fl, s))
+    for b in self.blk:
+      quant.gemv(b.qkv.ptr, self.qtype, self.q_dim + 2 * self.kv_dim, c.dim, self.x, self.qkv, norm_weight=b.attn_norm, norm_eps=c.norm_eps,
+                 bias=b.qkv_bias, flags=fl, stream=s)
+      a = _lib.AttnArgs(self.qkv.ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, self.pos.ptr, self.attn.ptr, self.attn_scratch.ptr,
+                        c.n_heads, c.n_kv_heads, c.head_dim, c.rope_dim, c.max_context, self.n_split, fl)
+      check(lib.b200q_attn_decode(ctypes.byref(a), s))
+      quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, self.attn, self.x, residual=self.x, flags=fl, stream=s)
+      quant.gemv(b.gate_up.buf.ptr, self.qtype, c.hidden_dim, c.dim, self.x, self.act, norm_weight=b.ffn_norm, norm_eps=c.norm_eps,
+                 epilogue=EPI_SILU_MUL, flags=fl, stream=s)
+      quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, self.act, self.x, residual=self.x, flags=fl, stream=s)
+    if with_head:
+      quant.gemv(self.output.buf.ptr, self.qtype, c.vocab_size, c.dim, self.x, self.logits, norm_weight=self.output_norm, norm_eps=c.norm_eps,
+                 flags=fl, stream=s)
+      check(lib.b200q_argmax_advance(self.logits.ptr, c.vocab_size, self.tokens.ptr, self.pos.ptr, self.argmax_scratch.ptr, fl, s))
+    else:
+      check(lib.b200q_advance(self.pos.ptr, fl, s))
+
+  def gemv_launches(self) -> list:
+    """(n_out rows streamed, n_in) of every GEMV launch of one step with the head, in launch order."""
+    c = self.config
+    per_block = [(self.q_dim + 2 * self.kv_dim, c.dim), (c.dim, self.q_dim), (2 * c.hidden_dim, c.dim), (c.dim, c.hidden_dim)]
+    return per_block * c.num_blocks + [(c.vocab_size, c.dim)]
+
+  def gemv_only_graph(self) -> Graph:
+    """The GEMV launches of one step alone, in order, for timing the weight stream by itself
+    (it overwrites the activation buffers: use it after the real steps)."""
+    c, s, fl = self.config, self.stream.ptr, self.flags
+    g = Graph(self.stream)
+    with g:
+      for b in self.blk:
+        quant.gemv(b.qkv.ptr, self.qtype, self.q_dim + 2 * self.kv_dim, c.dim, self.x, self.qkv, norm_weight=b.attn_norm, norm_eps=c.norm_eps,
+                   bias=b.qkv_bias, flags=fl, stream=s)
+        quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, self.attn, self.x, flags=fl, stream=s)
+        quant.gemv(b.gate_up.buf.ptr, self.qtype, c.hidden_dim, c.dim, self.x, self.act, norm_weight=b.ffn_norm, norm_eps=c.norm_eps,
+                   epilogue=EPI_SILU_MUL, flags=fl, stream=s)
+        quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, self.act, self.x, flags=fl, stream=s)
+      quant.gemv(self.output.buf.ptr, self.qtype, c.vocab_size, c.dim, self.x, self.logits, norm_weight=self.output_norm, norm_eps=c.norm_eps,
+                 flags=fl, stream=s)
+    return g
+
+  def step(self, with_head: bool = True) -> None:
+    """Advance by one token on the device: reads tokens[pos]; with the head, writes tokens[pos+1]."""
+    if not self.use_graph: return self._enqueue_step(with_head)
+    g = self._graphs.get(with_head)
+    if g is None:
+      g = Graph(self.stream)
+      with g: self._enqueue_step(with_head)
+      self._graphs[with_head] = g
+    g.launch()
+
+  # ---- host-visible state ----
+  def set_state(self, tokens: list, pos: int) -> None:
+    self.stream.synchronize()
+    if tokens: self.tokens.copy_from(np.asarray(tokens, dtype=np.int32))
+    self.pos.copy_from(np.array([pos], dtype=np.int32))
+
+  def read_token(self, index: int) -> int:
+    self.stream.synchronize()
+    return int(self.tokens.numpy((1,), np.int32, offset=4 * index)[0])
+
+  def read_logits(self) -> np.ndarray:
+    self.stream.synchronize()
+    return self.logits.numpy()
+
+  def get_start_pos(self, tokens: list) -> int:
+    """How much of the KV cache the new prompt can reuse (model.py:456-462)."""
+    n = 0
+    for a, b in zip(tokens[:-1], self._cached_tokens):
+      if a != b: break
+      n += 1
+    return n
+
+  def generate(self, tokens: list, temperature: float = 0.0):
+    """Greedy generation (model.py:464-484 at temperature 0).  Yields one token id at a time;
+    the prompt is consumed one position per step through the same kernels."""
+    if temperature != 0.0: raise NotImplementedError("only greedy decoding (temperature 0) is implemented")
+    tokens = list(tokens)
+    start_pos = self.get_start_pos(tokens)
+    self.set_state(tokens, start_pos)
+    for _ in range(start_pos, len(tokens) - 1): self.step(with_head=False)
+    while len(tokens) < self.max_context:
+      self.step(with_head=True)
+      tok = self.read_token(len(tokens))
+      tokens.append(tok)
+      self._cached_tokens = tokens[:-1]
+      yield tok

@@ -1,0 +1,103 @@
+"""GGUF-quantised weights on the device: dequantisation, packing, and the fused linear.
+
+Host-side mirror of the reference's interface for this path: `dequantize` is
+`ggml_data_to_tensor` (tinygrad/llm/gguf.py:23-72), `QuantLinear.__call__(x)` is
+`nn.Linear.__call__(x)` on a GGUF weight (tinygrad/nn/__init__.py:177) -- same
+argument meaning, same output dtype rule (the activation's dtype), errors raised
+as exceptions.  All compute happens in libb200q.so.
+"""
+import ctypes
+import numpy as np
+from . import _lib
+from ._lib import check, Q4_0, Q8_0, Q6_K, F32, F16, EPI_LINEAR, EPI_SILU_MUL, FLAG_PDL
+from .runtime import DeviceBuffer, ptr_of, stream_ptr
+
+GGML_QUANT = {Q4_0: (32, 18), Q8_0: (32, 34), Q6_K: (256, 210)}   # tinygrad/llm/gguf.py:20-21
+_DT = {np.dtype(np.float32): F32, np.dtype(np.float16): F16}
+
+
+def _as_device(a):
+  return a if isinstance(a, DeviceBuffer) or a is None else DeviceBuffer.from_numpy(np.ascontiguousarray(a))
+
+
+def dequantize(raw, n: int, ggml_type: int, dtype=np.float32, stream=None) -> DeviceBuffer:
+  """Raw GGUF block bytes -> n values (fp32 bit-exact with the reference; fp16 = its RNE cast)."""
+  if ggml_type not in GGML_QUANT: raise ValueError(f"GGML type '{ggml_type}' is not supported!")   # gguf.py:119
+  raw = _as_device(raw)
+  out = DeviceBuffer.empty((n,), dtype)
+  check(_lib.load().b200q_dequant_raw(ggml_type, raw.ptr, out.ptr, n, _DT[np.dtype(dtype)], stream_ptr(stream)))
+  return out
+
+
+class PackedWeight:
+  """A [n_out, n_in] quantised matrix re-tiled for the GEMV kernels (lossless)."""
+  def __init__(self, qtype: int, n_out: int, n_in: int, buf: DeviceBuffer, interleaved: bool):
+    self.qtype, self.n_out, self.n_in, self.buf, self.interleaved = qtype, n_out, n_in, buf, interleaved
+
+  @property
+  def rows(self) -> int: return 2 * self.n_out if self.interleaved else self.n_out
+
+  @property
+  def algorithmic_bytes(self) -> int:
+    nel, nby = GGML_QUANT[self.qtype]
+    return self.rows * self.n_in // nel * nby
+
+  def dequantize(self, dtype=np.float32) -> DeviceBuffer:
+    """Back to row-major values, rows in packed order (checks that packing lost nothing)."""
+    rows = -(-self.rows // 16) * 16 if self.interleaved else self.n_out
+    out = DeviceBuffer.empty((rows, self.n_in), dtype)
+    check(_lib.load().b200q_dequant_packed(self.qtype, self.buf.ptr, out.ptr, rows, self.n_in, _DT[np.dtype(dtype)], None))
+    return out
+
+
+def packed_bytes(qtype: int, rows: int, n_in: int) -> int:
+  n = _lib.load().b200q_packed_bytes(qtype, rows, n_in)
+  if n == 0: raise ValueError(f"cannot pack GGML type {qtype} of shape ({rows}, {n_in})")
+  return n
+
+
+def repack(raw, n_out: int, n_in: int, qtype: int, raw_up=None, out: DeviceBuffer = None, out_offset: int = 0, stream=None) -> PackedWeight:
+  """Re-tile raw GGUF blocks of a [n_out, n_in] weight.  With `raw_up` the two
+  matrices (gate, up) are interleaved for the fused SwiGLU epilogue.  `out` /
+  `out_offset` place the tiles inside a larger buffer (e.g. q|k|v back to back)."""
+  if n_in % GGML_QUANT[qtype][0]: raise ValueError(f"n_in={n_in} is not a multiple of the block size")
+  raw, raw_up = _as_device(raw), _as_device(raw_up)
+  rows = 2 * (-(-n_out // 8) * 8) if raw_up is not None else n_out
+  nbytes = packed_bytes(qtype, rows, n_in)
+  if out is None: out, out_offset = DeviceBuffer(nbytes), 0
+  assert out_offset % 16 == 0 and out_offset + nbytes <= out.nbytes
+  check(_lib.load().b200q_repack(qtype, raw.ptr, ptr_of(raw_up), out.ptr + out_offset, n_out, n_in, stream_ptr(stream)))
+  if stream is None: check(_lib.load().b200q_device_synchronize())   # raw staging buffers may be freed by the caller
+  pw = PackedWeight(qtype, n_out, n_in, out, raw_up is not None)
+  pw.offset = out_offset
+  return pw
+
+
+def gemv(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int = 1, x_dtype=F32, y_dtype=F32, norm_weight=None, norm_eps: float = 0.0,
+         epilogue: int = EPI_LINEAR, bias=None, residual=None, flags: int = 0, max_ctas: int = 0, stream=None) -> None:
+  """One launch of the fused dequant-GEMV (all pointers raw device addresses or buffers)."""
+  a = _lib.GemvArgs(qtype, n_out, n_in, m, w_ptr, ptr_of(x), x_dtype, y_dtype, ptr_of(norm_weight), norm_eps, epilogue, ptr_of(bias),
+                    ptr_of(residual), ptr_of(y), flags, max_ctas)
+  check(_lib.load().b200q_gemv(ctypes.byref(a), stream_ptr(stream)))
+
+
+class QuantLinear:
+  """Drop-in for `nn.Linear` holding a GGUF-quantised weight.
+
+  `QuantLinear(in_features, out_features, ggml_type, raw_blocks, bias)`; calling it
+  on activations of shape (..., in_features), fp16 or fp32, returns
+  (..., out_features) in the activation dtype, as
+  `x.linear(weight.transpose(), bias)` does (tinygrad/nn/__init__.py:177)."""
+  def __init__(self, in_features: int, out_features: int, ggml_type: int, raw, bias=None):
+    self.in_features, self.out_features, self.ggml_type = in_features, out_features, ggml_type
+    self.weight = repack(raw, out_features, in_features, ggml_type)
+    self.bias = None if bias is None else DeviceBuffer.from_numpy(np.asarray(bias, dtype=np.float16))
+
+  def __call__(self, x: DeviceBuffer, stream=None) -> DeviceBuffer:
+    if x.dtype not in _DT: raise TypeError(f"activations must be float16 or float32, got {x.dtype}")
+    if x.shape[-1] != self.in_features: raise ValueError(f"Input Tensor shapes {x.shape} cannot be multiplied with in_features={self.in_features}")
+    m = int(np.prod(x.shape[:-1], dtype=np.int64))
+    y = DeviceBuffer.empty((*x.shape[:-1], self.out_features), x.dtype)
+    if m: gemv(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m=m, x_dtype=_DT[x.dtype], y_dtype=_DT[x.dtype],
+               bias=self.bias, stream=stream)
+    return y
