@@ -134,18 +134,53 @@ def run_reference(args, rank):
                     "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
+def run_gemv_probe(args):
+  """Micro-benchmark of one GEMV shape (profiling aid; prints its own JSON line, not the headline).
+  Rotates over enough distinct weight buffers that every launch reads HBM-cold weights."""
+  from tinygrad_b200 import build, runtime, synth, quant
+  build.build_lib()
+  runtime.set_device(0)
+  n_out, n_in = (int(v) for v in args.gemv_shape.split("x"))
+  wbytes = n_out * n_in // 32 * 18
+  n_rot = max(2, -(-args.rotate_mb * (1 << 20) // wbytes))
+  raw = synth.q4_0_blocks(n_out, n_in, np.random.default_rng(0))
+  ws = [quant.repack(raw, n_out, n_in, synth.Q4_0) for _ in range(n_rot)]
+  x = runtime.DeviceBuffer.from_numpy(np.random.default_rng(1).standard_normal(n_in).astype(np.float32))
+  y = runtime.DeviceBuffer.empty((n_out,), np.float32)
+  st = runtime.Stream()
+  fl = 0 if args.no_pdl else 1
+  def enqueue(n):
+    for i in range(n): quant.gemv(ws[i % n_rot].buf.ptr, synth.Q4_0, n_out, n_in, x, y, flags=fl, stream=st)
+  enqueue(args.warmup); st.synchronize()
+  g = runtime.Graph(st)
+  with g: enqueue(args.steps)
+  g.launch(); st.synchronize()
+  e0, e1 = runtime.Event(), runtime.Event()
+  e0.record(st); g.launch(); e1.record(st); st.synchronize()
+  us = 1e3 * e0.elapsed_ms(e1) / args.steps
+  peak, src = measured_peaks()
+  gbs = (wbytes + 4 * n_in + 4 * n_out) / us / 1e3
+  print(json.dumps({"workload": f"gemv probe Q4_0 {n_out}x{n_in}, {n_rot} rotating weight buffers", "us_per_launch": us, "gbs": gbs,
+                    "frac_of_peak": gbs / peak, "peak_source": src, "launches": args.steps, "pdl": not args.no_pdl}))
+
+
 def main():
   ap = argparse.ArgumentParser()
+  ap.add_argument("--workload", default="decode", choices=["decode", "gemv"])
+  ap.add_argument("--gemv-shape", default="28672x4096", help="rows x K of the probe (gate+up interleaved = 28672x4096)")
+  ap.add_argument("--rotate-mb", type=int, default=512)
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=256)
   ap.add_argument("--warmup", type=int, default=8)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--blocks", type=int, default=0, help="debug: fewer transformer blocks (the reported line is then not the headline workload)")
   ap.add_argument("--no-pdl", action="store_true")
+  ap.add_argument("--skip-prefill", action="store_true", help="debug/profiling: start at the end of the prompt with an all-zero KV cache")
   ap.add_argument("--skip-cpu-baseline", action="store_true")
   args = ap.parse_args()
   rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
   if args.impl == "reference": return run_reference(args, rank)
+  if args.workload == "gemv": return run_gemv_probe(args)
   if args.warmup < 3: args.warmup = 3
 
   from tinygrad_b200 import build, runtime, synth
@@ -165,8 +200,10 @@ def main():
   t_build = time.time() - t_build
   prompt = [int(t) for t in np.random.default_rng(1000 + rank).integers(0, cfg.vocab_size, PROMPT_LEN)]
   # prompt (untimed): one position per step through the same kernels
-  model.set_state(prompt, 0)
-  for _ in range(PROMPT_LEN - 1): model.step(with_head=False)
+  if args.skip_prefill: model.set_state(prompt, PROMPT_LEN - 1)
+  else:
+    model.set_state(prompt, 0)
+    for _ in range(PROMPT_LEN - 1): model.step(with_head=False)
   model.stream.synchronize()
 
   def barrier():
@@ -234,7 +271,7 @@ def main():
   value = world * args.steps / (ms_dev * 1e-3)
   out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
          "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-         "config": {"workload": WORKLOAD if not args.blocks else f"DEBUG {args.blocks} blocks of: " + WORKLOAD, "parallelism": f"replicas x{world}",
+         "config": {"workload": WORKLOAD if not (args.blocks or args.skip_prefill) else f"DEBUG (blocks={args.blocks}, skip_prefill={args.skip_prefill}) of: " + WORKLOAD, "parallelism": f"replicas x{world}",
                     "l2": "inputs larger than L2 (4.2 GB of weights per step vs 126 MB)", "pdl": not args.no_pdl, "n_split": model.n_split,
                     "step_hbm_gbs": step_bytes / (ms_dev / args.steps * 1e-3) / 1e9, "step_frac_of_peak": step_bytes / (ms_dev / args.steps * 1e-3) / 1e9 / peak,
                     "model_build_s": round(t_build, 1)},

@@ -44,6 +44,9 @@ extern "C" {
 #define B200Q_FLAG_PDL 1     /* launch with programmatic dependent launch (overlaps the weight prefetch with the previous kernel) */
 
 const char* b200q_strerror(int code);
+/* Device-side status word: 0 = fine, 1 = a bounded wait inside a kernel ran out (the kernel then skipped its
+ * remaining work instead of spinning; its output is invalid).  Reads and clears it.  Synchronises the device. */
+int b200q_status_read_clear(int* status);
 const char* b200q_last_cuda_error(void);
 int b200q_version(void);
 
@@ -95,8 +98,8 @@ int b200q_dequant_raw(int qtype, const void* device_raw, void* device_out, int64
  *   Q4_0 tile = 1152 B: [lane l: 16 quant bytes of (row l/4,   block l%4)] x32,
  *                       [lane l: 16 quant bytes of (row l/4+8, block l%4)] x32,
  *                       [entry e=2*(l/4)+h: scales of rows l/4 and l/4+8, blocks 2h and 2h+1] x16 (8 B each)
- *   Q8_0 tile = 2176 B: as above with 32 quant bytes per (row, block) in two 16-byte halves
- *                       (each int8 stored with its sign bit flipped), then the same scale entries.
+ *   Q8_0 tile = 2176 B: as above with the 32 quant bytes of a (row, block) pair in two 16-byte halves
+ *                       (rows 0-7: halves at +0 and +512; rows 8-15: at +1024 and +1536), then the same scale entries.
  * The bytes per weight element are exactly the GGUF format's (18 or 34 bytes per 32).
  * n_out is padded up to a multiple of 16 and n_in to a multiple of 128 with zero-scale blocks.
  * With raw1 != NULL two matrices of equal shape are interleaved 8 rows at a
@@ -114,7 +117,9 @@ int b200q_dequant_packed(int qtype, const void* device_packed, void* device_out,
  * the RMSNorm in front of it (tinygrad/nn/__init__.py:300-304), the residual add
  * behind it (tinygrad/llm/model.py:149-150) or the SwiGLU product
  * (tinygrad/llm/model.py:137).  One launch; weights are streamed once per
- * activation row. */
+ * activation row.  Activations are quantised on the fly to 15-bit integers with one fp32 scale per 32
+ * (error ~3e-5 relative, far inside the 1e-2 tolerance of this path); products and sums inside a block
+ * are exact integers, accumulation across blocks is fp32. */
 typedef struct b200q_gemv_args {
   int qtype;                /* B200Q_Q4_0 | B200Q_Q8_0 */
   int n_out;                /* logical output features (for EPI_SILU_MUL: features of gate == up) */

@@ -99,8 +99,8 @@ def test_linear_fp32_matches_oracle(tag, n_out, n_in, m):
   ref = llm.linear(x, gq.weight_matrix(raw, n_out, n_in, typ))
   assert y.dtype == np.float32
   assert_close(y, ref, tol=1e-2)
-  # the hi/lo activation split keeps fp32-grade accuracy, far inside the stated tolerance
-  assert np.abs(y - ref).max() <= 2e-4 * np.abs(ref).max()
+  # 15-bit activation quantisation with exact integer block sums: far inside the stated tolerance
+  assert np.abs(y - ref).max() <= 5e-4 * np.abs(ref).max()
 
 
 @pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
@@ -145,3 +145,9 @@ def test_fused_norm_residual_and_swiglu():
   dres, dy = DeviceBuffer.from_numpy(x), DeviceBuffer.empty((dim,), np.float32)
   quant.gemv(pd.buf.ptr, 2, dim, hid + 24, dact, dres, residual=dres)   # in place on the residual stream
   assert_close(dres.numpy(), x + llm.linear(act_full[None], wd)[0], what="down + residual")
+
+
+def test_no_kernel_wait_ran_out():
+  """The bounded mbarrier waits of the GEMV pipeline must never expire in normal operation."""
+  from tinygrad_b200 import runtime
+  assert runtime.device_status() == 0

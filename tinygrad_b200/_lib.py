@@ -28,6 +28,7 @@ SIGNATURES = {
   "b200q_strerror": (c_char_p, [c_int]),
   "b200q_last_cuda_error": (c_char_p, []),
   "b200q_version": (c_int, []),
+  "b200q_status_read_clear": (c_int, [POINTER(c_int)]),
   "b200q_device_count": (c_int, [POINTER(c_int)]),
   "b200q_set_device": (c_int, [c_int]),
   "b200q_device_props": (c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_size_t)]),

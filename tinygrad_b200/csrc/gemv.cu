@@ -1,19 +1,26 @@
-// Weight-dequant-fused GEMV for GGUF Q4_0 / Q8_0 weights (decode: one activation row).
+// Weight-dequant-fused GEMV for GGUF Q4_0 / Q8_0 weights (decode: one activation row per CTA row).
 //
-// Replaces the kernels tinygrad generates for `Linear.__call__` on a lazily
-// dequantised GGUF weight (tinygrad/nn/__init__.py:177 over tinygrad/llm/gguf.py:46,56).
+// Replaces the kernels tinygrad generates for `Linear.__call__` on a lazily dequantised
+// GGUF weight (tinygrad/nn/__init__.py:177 over tinygrad/llm/gguf.py:46,56).
 //
-// Data flow per CTA: the activation row is staged once into shared memory as fp16
-// hi + lo halves (x = hi + lo to ~22 bits, so the product keeps fp32-grade accuracy);
-// each warp then streams whole weight tiles (16 rows x 4 quant blocks) with 128-bit
-// coalesced loads, unpacks nibbles/bytes to exact fp16 integers in registers and
-// feeds them to mma.m16n8k16: the 8 accumulator columns are the 4 blocks of the tile
-// times {hi, lo}, i.e. B is block-diagonal, so every block's integer dot product
-// lands in its own column and is scaled by that block's fp16 scale afterwards.
-// The k-reduction happens inside the MMA and across the 4 lanes of a quad (warp
-// shuffles), then across warps through shared memory, in a fixed order
-// (bit-reproducible).  The kernel is HBM-bound: the MMA only removes the
-// per-element FMA from the issue slots.
+// Structure of one CTA (8 consumer warps + 1 producer warp, persistent over row tiles):
+//  * producer: one thread streams the CTA's weight tiles HBM -> shared memory with bulk
+//    async copies (cp.async.bulk + mbarrier transaction counts) through a ring of stages.
+//    Weights do not depend on the previous kernel, so under programmatic dependent launch
+//    the ring fills while the previous kernel is still running.
+//  * consumers: stage the activation row once (optionally times the RMSNorm weight):
+//    every block of 32 activations is quantised to a 15-bit integer with a per-block fp32
+//    scale and split into two int8 digits (hi*128 + lo).  The weight nibbles / bytes are
+//    unpacked with two logic ops per 8 values and fed to int8 tensor-core MMAs
+//    (mma.m16n8k32): the 8 accumulator columns are the tile's 4 quant blocks x {hi, lo}
+//    digit (B is block-diagonal), so each block's exact integer dot product lands in its
+//    own column and is scaled by (activation scale x fp16 weight scale) afterwards; the
+//    Q4_0 offset of 8 is removed with the block's activation sum.  The k-reduction runs
+//    inside the MMA, then across the 4 lanes of a quad (warp shuffles), then across warps
+//    through shared memory in a fixed order: results are bit-reproducible run to run.
+// The kernel is HBM-bound; the tensor core only takes the multiply-adds off the issue slots.
+// Every mbarrier wait is bounded: on expiry the kernel raises a status word
+// (b200q_status_read_clear) and drains its copies instead of spinning.
 #include "common.cuh"
 
 namespace {
@@ -30,247 +37,309 @@ struct GemvParams {
   float eps;
 };
 
-constexpr int NWARPS = 8;
-constexpr int NTHREADS = NWARPS * 32;
+constexpr int CONS_WARPS = 8;
+constexpr int CONS_THREADS = CONS_WARPS * 32;
+constexpr int NTHREADS = CONS_THREADS + 32;      // + producer warp
+constexpr int STAGE_GROUPS = 16;                 // weight tiles (16 rows x 128 columns) per ring stage: two per consumer warp
+constexpr int SPIN_LIMIT = 1 << 20;
 
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {   // (a & b) | c
-  uint32_t d;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
+__device__ int g_status = 0;                     // sticky: 1 = an mbarrier wait ran out
+
+template <int QT> struct Cfg;
+template <> struct Cfg<B200Q_Q4_0> { static constexpr int NS = 4; };   // 4 x 18 KB ring
+template <> struct Cfg<B200Q_Q8_0> { static constexpr int NS = 2; };   // 2 x 34 KB ring
+
+// ---- mbarrier / bulk-copy primitives -------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
-__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
-  uint32_t d; asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t d; asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel)); return d;
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
 }
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// Bounded wait: false (and the status word set) if the phase did not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < SPIN_LIMIT; i++) {
+    if (mbar_test(bar, parity)) return true;
+    if (i > 64) __nanosleep(64);
+  }
+  atomicExch(&g_status, 1);
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void cons_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONS_THREADS) : "memory"); }
+
+// ---- tensor-core pieces ---------------------------------------------------------------
+template <int QT> __device__ __forceinline__ void imma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void imma<B200Q_Q4_0>(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void imma<B200Q_Q8_0>(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Where element e (0..31) of a quant block sits among the 16 B-fragment registers
-// a lane holds for that block: register q (0..15) and half slot (0 = low 16 bits).
-template <int QT> __device__ __forceinline__ void b_slot(int e, int& q, int& hs);
-template <> __device__ __forceinline__ void b_slot<B200Q_Q4_0>(int e, int& q, int& hs) {
-  // byte i of the 16 quant bytes holds element i (low nibble) and i+16 (high nibble); word i/4 feeds
-  // one MMA with its low nibbles and the next with its high nibbles: regs {e0,e2}, {e1,e3}
-  int hl = e >> 4, i = (e & 15) >> 2, r = e & 3;
-  q = (2 * i + hl) * 2 + (r & 1); hs = r >> 1;
-}
-template <> __device__ __forceinline__ void b_slot<B200Q_Q8_0>(int e, int& q, int& hs) { q = e >> 1; hs = e & 1; }
-
-template <int QT> struct Frag;
-template <> struct Frag<B200Q_Q4_0> { uint4 lo, hi; uint2 sc; };            // rows g / g+8
-template <> struct Frag<B200Q_Q8_0> { uint4 lo0, lo1, hi0, hi1; uint2 sc; };
-
-template <int QT> __device__ __forceinline__ void load_frag(Frag<QT>& f, const uint8_t* tile, int lane);
-template <> __device__ __forceinline__ void load_frag<B200Q_Q4_0>(Frag<B200Q_Q4_0>& f, const uint8_t* tile, int lane) {
+// One weight tile (16 rows x 4 blocks) against the staged activation digits.
+// bq: the lane's 8 B-operand words for its block (zeros unless the lane feeds this tile's diagonal),
+// st: {scale_A, offset_A, scale_B, offset_B} of the lane's two accumulator columns.
+template <int QT>
+__device__ __forceinline__ void tile_mac(const uint8_t* tile, int lane, const uint4& bq0, const uint4& bq1, const float4& st, float& acc0, float& acc1) {
   const uint4* tp = reinterpret_cast<const uint4*>(tile);
-  f.lo = ldg_stream(tp + lane); f.hi = ldg_stream(tp + 32 + lane);
-  f.sc = ldg_stream(reinterpret_cast<const uint2*>(tile + 1024) + (2 * (lane >> 2) + (lane & 1)));
-}
-template <> __device__ __forceinline__ void load_frag<B200Q_Q8_0>(Frag<B200Q_Q8_0>& f, const uint8_t* tile, int lane) {
-  const uint4* tp = reinterpret_cast<const uint4*>(tile);
-  f.lo0 = ldg_stream(tp + lane); f.lo1 = ldg_stream(tp + 32 + lane);
-  f.hi0 = ldg_stream(tp + 64 + lane); f.hi1 = ldg_stream(tp + 96 + lane);
-  f.sc = ldg_stream(reinterpret_cast<const uint2*>(tile + 2048) + (2 * (lane >> 2) + (lane & 1)));
-}
-
-// One Q4_0 word pair (rows g and g+8): low-nibble MMA then high-nibble MMA.
-__device__ __forceinline__ void q4_word(float (&c)[4], uint32_t w0, uint32_t w1, uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
-  const uint32_t MAGIC = 0x64006400u;        // half2(1024, 1024): nibble lands in the mantissa
-  const uint32_t SUB_LO = 0x64086408u;       // half2(1032): (1024 + n) - 1032 = n - 8
-  const uint32_t MUL_HI = 0x2C002C00u;       // half2(1/16)
-  const uint32_t ADD_HI = 0xD480D480u;       // half2(-72): (1024 + 16 n) / 16 - 72 = n - 8
-  uint32_t v0 = w0 >> 8, v1 = w1 >> 8;
-  uint32_t a0 = h2_sub(lop3_and_or(w0, 0x000F000Fu, MAGIC), SUB_LO), a1 = h2_sub(lop3_and_or(w1, 0x000F000Fu, MAGIC), SUB_LO);
-  uint32_t a2 = h2_sub(lop3_and_or(v0, 0x000F000Fu, MAGIC), SUB_LO), a3 = h2_sub(lop3_and_or(v1, 0x000F000Fu, MAGIC), SUB_LO);
-  mma16816(c, a0, a1, a2, a3, b0, b1);
-  a0 = h2_fma(lop3_and_or(w0, 0x00F000F0u, MAGIC), MUL_HI, ADD_HI); a1 = h2_fma(lop3_and_or(w1, 0x00F000F0u, MAGIC), MUL_HI, ADD_HI);
-  a2 = h2_fma(lop3_and_or(v0, 0x00F000F0u, MAGIC), MUL_HI, ADD_HI); a3 = h2_fma(lop3_and_or(v1, 0x00F000F0u, MAGIC), MUL_HI, ADD_HI);
-  mma16816(c, a0, a1, a2, a3, b2, b3);
-}
-// One Q8_0 word pair: 4 sign-flipped bytes per row -> exact fp16 integers.
-__device__ __forceinline__ void q8_word(float (&c)[4], uint32_t w0, uint32_t w1, uint32_t b0, uint32_t b1) {
-  const uint32_t HI = 0x64646464u, SUB = 0x64806480u;   // 0x64bb = 1024 + bb; minus 1152 = int8 value
-  uint32_t a0 = h2_sub(prmt(w0, HI, 0x4140u), SUB), a1 = h2_sub(prmt(w1, HI, 0x4140u), SUB);
-  uint32_t a2 = h2_sub(prmt(w0, HI, 0x4342u), SUB), a3 = h2_sub(prmt(w1, HI, 0x4342u), SUB);
-  mma16816(c, a0, a1, a2, a3, b0, b1);
+  int c[4] = {0, 0, 0, 0};
+  uint2 sc;
+  if (QT == B200Q_Q4_0) {
+    // byte i of a block's 16 quant bytes = element i (low nibble) | element i+16 (high nibble)
+    const uint4 r0 = tp[lane], r1 = tp[32 + lane];      // rows g and g+8
+    sc = *(reinterpret_cast<const uint2*>(tile + 1024) + (2 * (lane >> 2) + (lane & 1)));
+    const uint32_t M = 0x0F0F0F0Fu;
+    imma<QT>(c, r0.x & M, r1.x & M, (r0.x >> 4) & M, (r1.x >> 4) & M, bq0.x, bq0.y);
+    imma<QT>(c, r0.y & M, r1.y & M, (r0.y >> 4) & M, (r1.y >> 4) & M, bq0.z, bq0.w);
+    imma<QT>(c, r0.z & M, r1.z & M, (r0.z >> 4) & M, (r1.z >> 4) & M, bq1.x, bq1.y);
+    imma<QT>(c, r0.w & M, r1.w & M, (r0.w >> 4) & M, (r1.w >> 4) & M, bq1.z, bq1.w);
+  } else {
+    const uint4 r0 = tp[lane], r1 = tp[32 + lane], r2 = tp[64 + lane], r3 = tp[96 + lane];   // row g: r0,r1; row g+8: r2,r3
+    sc = *(reinterpret_cast<const uint2*>(tile + 2048) + (2 * (lane >> 2) + (lane & 1)));
+    imma<QT>(c, r0.x, r2.x, r0.y, r2.y, bq0.x, bq0.y);
+    imma<QT>(c, r0.z, r2.z, r0.w, r2.w, bq0.z, bq0.w);
+    imma<QT>(c, r1.x, r3.x, r1.y, r3.y, bq1.x, bq1.y);
+    imma<QT>(c, r1.z, r3.z, r1.w, r3.w, bq1.z, bq1.w);
+  }
+  const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&sc.x)), d1 = __half22float2(*reinterpret_cast<const __half2*>(&sc.y));
+  const float v0 = fmaf((float)c[0], st.x, -st.y), v1 = fmaf((float)c[1], st.z, -st.w);
+  const float v2 = fmaf((float)c[2], st.x, -st.y), v3 = fmaf((float)c[3], st.z, -st.w);
+  acc0 = fmaf(v0, d0.x, fmaf(v1, d0.y, acc0));
+  acc1 = fmaf(v2, d1.x, fmaf(v3, d1.y, acc1));
 }
 
-template <int QT> __device__ __forceinline__ void compute_frag(const Frag<QT>& f, const uint4 (&bf)[4], float& acc0, float& acc1);
-template <> __device__ __forceinline__ void compute_frag<B200Q_Q4_0>(const Frag<B200Q_Q4_0>& f, const uint4 (&bf)[4], float& acc0, float& acc1) {
-  float c[4] = {0.f, 0.f, 0.f, 0.f};
-  q4_word(c, f.lo.x, f.hi.x, bf[0].x, bf[0].y, bf[0].z, bf[0].w);
-  q4_word(c, f.lo.y, f.hi.y, bf[1].x, bf[1].y, bf[1].z, bf[1].w);
-  q4_word(c, f.lo.z, f.hi.z, bf[2].x, bf[2].y, bf[2].z, bf[2].w);
-  q4_word(c, f.lo.w, f.hi.w, bf[3].x, bf[3].y, bf[3].z, bf[3].w);
-  float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&f.sc.x)), d1 = __half22float2(*reinterpret_cast<const __half2*>(&f.sc.y));
-  acc0 = fmaf(c[0], d0.x, fmaf(c[1], d0.y, acc0));
-  acc1 = fmaf(c[2], d1.x, fmaf(c[3], d1.y, acc1));
-}
-template <> __device__ __forceinline__ void compute_frag<B200Q_Q8_0>(const Frag<B200Q_Q8_0>& f, const uint4 (&bf)[4], float& acc0, float& acc1) {
-  float c[4] = {0.f, 0.f, 0.f, 0.f};
-  q8_word(c, f.lo0.x, f.hi0.x, bf[0].x, bf[0].y); q8_word(c, f.lo0.y, f.hi0.y, bf[0].z, bf[0].w);
-  q8_word(c, f.lo0.z, f.hi0.z, bf[1].x, bf[1].y); q8_word(c, f.lo0.w, f.hi0.w, bf[1].z, bf[1].w);
-  q8_word(c, f.lo1.x, f.hi1.x, bf[2].x, bf[2].y); q8_word(c, f.lo1.y, f.hi1.y, bf[2].z, bf[2].w);
-  q8_word(c, f.lo1.z, f.hi1.z, bf[3].x, bf[3].y); q8_word(c, f.lo1.w, f.hi1.w, bf[3].z, bf[3].w);
-  float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&f.sc.x)), d1 = __half22float2(*reinterpret_cast<const __half2*>(&f.sc.y));
-  acc0 = fmaf(c[0], d0.x, fmaf(c[1], d0.y, acc0));
-  acc1 = fmaf(c[2], d1.x, fmaf(c[3], d1.y, acc1));
-}
-
-template <int QT, int U>
-__global__ void __launch_bounds__(NTHREADS) qgemv_kernel(const GemvParams p) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  uint4* xs = reinterpret_cast<uint4*>(smem);                                   // [kgroups][4][8] B-fragment words
-  float* red = reinterpret_cast<float*>(smem + (size_t)p.kgroups * 512);        // [NWARPS][16]
-  float* fin = red + NWARPS * 16;                                               // [16]
-  float* s_ss = fin + 16;                                                       // [NWARPS] + [1]
+// Shared-memory plan (dynamic):
+//   ring   [NS][STAGE_GROUPS * tile_bytes]        weight tiles as they sit in HBM
+//   xq     [kgroups][2][8] uint4                  B operands: per tile, lane g (block g%4, digit g/4), 8 words in MMA order
+//   xsc    [kgroups][2][2] float4                 per (digit, block pair): {scale_A, offset_A, scale_B, offset_B}
+//   zero   uint4                                  B operand of the lanes off the diagonal
+//   red    [2][CONS_WARPS][16] float              cross-warp partial sums, double-buffered over row tiles
+//   ssq    [CONS_WARPS] float
+//   bars   full[NS], empty[NS]
+//   abort  int                                    set by a consumer warp whose wait ran out; all warps leave at the next row tile
+template <int QT>
+__global__ void __launch_bounds__(NTHREADS, 2) qgemv_kernel(const GemvParams p) {
+  constexpr int NS = Cfg<QT>::NS, TB = tile_bytes(QT), STAGE_BYTES = STAGE_GROUPS * TB;
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* ring = smem;
+  uint4* xq = reinterpret_cast<uint4*>(smem + NS * STAGE_BYTES);
+  float4* xsc = reinterpret_cast<float4*>(xq + (size_t)p.kgroups * 16);
+  uint4* zero = reinterpret_cast<uint4*>(xsc + (size_t)p.kgroups * 4);
+  float* red = reinterpret_cast<float*>(zero + 1);
+  float* ssq = red + 2 * CONS_WARPS * 16;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ssq + CONS_WARPS);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 2 * NS);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + NS);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int g = lane >> 2, t = lane & 3;
   const int m = blockIdx.y;
-  constexpr int TB = tile_bytes(QT);
+  const int stages_per_tile = (p.kgroups + STAGE_GROUPS - 1) / STAGE_GROUPS;
 
+  if (tid == 0) {
+    for (int s = 0; s < NS; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, CONS_WARPS); }
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
   pdl_launch_dependents();
 
-  // weights do not depend on the previous kernel: start streaming the first chunk before waiting for it
-  int rt = blockIdx.x;
-  Frag<QT> fr[U];
-#pragma unroll
-  for (int u = 0; u < U; u++) {
-    int j = warp + u * NWARPS;
-    if (rt < p.n_row_tiles && j < p.kgroups) load_frag<QT>(fr[u], p.w + ((size_t)rt * p.kgroups + j) * TB, lane);
-  }
-  pdl_wait();
-
-  // ---- stage the activation row: x (* norm weight) -> fp16 hi/lo B fragments
-  {
-    const int kpad = p.kgroups * GROUP_ELEMS;
-    __half* xh = reinterpret_cast<__half*>(xs);
-    float ss = 0.f;
-    for (int k = tid; k < kpad; k += NTHREADS) {
-      float v = 0.f;
-      if (k < p.n_in) {
-        v = p.x_f16 ? __half2float(reinterpret_cast<const __half*>(p.x)[(size_t)m * p.n_in + k])
-                    : reinterpret_cast<const float*>(p.x)[(size_t)m * p.n_in + k];
-        ss = fmaf(v, v, ss);
-        if (p.norm_w) v *= __half2float(p.norm_w[k]);
+  if (warp == CONS_WARPS) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int rt = blockIdx.x; rt < p.n_row_tiles && ok; rt += gridDim.x) {
+        const uint8_t* src = p.w + (size_t)rt * p.kgroups * TB;
+        for (int s = 0; s < stages_per_tile; s++, it++) {
+          const int slot = it % NS, groups = min(STAGE_GROUPS, p.kgroups - s * STAGE_GROUPS);
+          // The first NS fills need no consumer.  After them the consumers must be running, and they start
+          // only when the previous kernel has finished: wait for it here, outside the bounded wait.
+          if (it == NS) pdl_wait();
+          if (!mbar_wait(empty0 + 8 * slot, ((it / NS) & 1) ^ 1)) { ok = false; break; }
+          mbar_expect_tx(full0 + 8 * slot, groups * TB);
+          bulk_g2s(smem_u32(ring + slot * STAGE_BYTES), src + (size_t)s * STAGE_BYTES, groups * TB, full0 + 8 * slot);
+        }
       }
-      __half hi = __float2half_rn(v), lo = __float2half_rn(v - __half2float(hi));
-      int b = k >> 5, e = k & 31, j = b >> 2, tb = b & 3, q, hs;
-      b_slot<QT>(e, q, hs);
-      int base = ((j * 4 + (q >> 2)) * 8) * 8 + (q & 3) * 2 + hs;   // half index of lane-slot 0
-      xh[base + tb * 8] = hi;
-      xh[base + (tb + 4) * 8] = lo;
+      // nothing may still be landing in this CTA's shared memory when it exits
+      for (int j = max(0, it - NS); j < it; j++) mbar_wait(full0 + 8 * (j % NS), (j / NS) & 1);
+    }
+    pdl_wait();     // keep launch order transitive: this grid is not complete before its predecessor
+    return;
+  }
+
+  // -------------------------------- consumers --------------------------------
+  pdl_wait();
+  const int g = lane >> 2, t = lane & 3;
+  {
+    // stage the activation row: 8 threads per block of 32, 4 elements each
+    if (tid == 0) *zero = make_uint4(0, 0, 0, 0);
+    const int nblk_pad = p.kgroups * 4, q = tid & 7;
+    uint32_t* xw = reinterpret_cast<uint32_t*>(xq);
+    float* sw = reinterpret_cast<float*>(xsc);
+    float ss = 0.f;
+    for (int b = tid >> 3; b < nblk_pad; b += CONS_THREADS / 8) {
+      const int k = b * 32 + 4 * q;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (k < p.n_in) {
+        if (p.x_f16) {
+          const uint2 r = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(p.x) + (size_t)m * p.n_in + k);
+          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x)), c = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+          v = make_float4(a.x, a.y, c.x, c.y);
+        } else {
+          v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (size_t)m * p.n_in + k);
+        }
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        if (p.norm_w) {
+          const uint2 r = *reinterpret_cast<const uint2*>(p.norm_w + k);
+          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x)), c = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+          v.x *= a.x; v.y *= a.y; v.z *= c.x; v.w *= c.y;
+        }
+      }
+      float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+      const bool live = amax > 0.f && amax < INFINITY;
+      const float inv = live ? 16256.f / amax : 0.f, s = live ? amax / 16256.f : 0.f;
+      const int i0 = __float2int_rn(v.x * inv), i1 = __float2int_rn(v.y * inv), i2 = __float2int_rn(v.z * inv), i3 = __float2int_rn(v.w * inv);
+      int xsum = i0 + i1 + i2 + i3;
+      xsum += __shfl_xor_sync(0xffffffffu, xsum, 1);
+      xsum += __shfl_xor_sync(0xffffffffu, xsum, 2);
+      xsum += __shfl_xor_sync(0xffffffffu, xsum, 4);
+      const int h0 = (i0 + 64) >> 7, h1 = (i1 + 64) >> 7, h2 = (i2 + 64) >> 7, h3 = (i3 + 64) >> 7;   // value = 128 * hi + lo, lo in [-64, 63]
+      const uint32_t hiw = (h0 & 0xFF) | ((h1 & 0xFF) << 8) | ((h2 & 0xFF) << 16) | ((uint32_t)(h3 & 0xFF) << 24);
+      const uint32_t low = ((i0 - (h0 << 7)) & 0xFF) | (((i1 - (h1 << 7)) & 0xFF) << 8) | (((i2 - (h2 << 7)) & 0xFF) << 16) |
+                           ((uint32_t)((i3 - (h3 << 7)) & 0xFF) << 24);
+      // word position in the block's MMA order: Q4_0 word j feeds MMA j with elements {4j..4j+3 | 16+4j..}, Q8_0 is in element order
+      const int r = QT == B200Q_Q4_0 ? ((q & 3) * 2 + (q >> 2)) : q;
+      const int j = b >> 2, tb = b & 3;
+      xw[((j * 2 + (r >> 2)) * 8 + tb) * 4 + (r & 3)] = hiw;
+      xw[((j * 2 + (r >> 2)) * 8 + tb + 4) * 4 + (r & 3)] = low;
+      if (q == 0) {
+        const int pr = tb >> 1, sl = (tb & 1) * 2;
+        sw[((j * 2 + 0) * 2 + pr) * 4 + sl] = 128.f * s;
+        sw[((j * 2 + 0) * 2 + pr) * 4 + sl + 1] = QT == B200Q_Q4_0 ? 8.f * s * (float)xsum : 0.f;
+        sw[((j * 2 + 1) * 2 + pr) * 4 + sl] = s;
+        sw[((j * 2 + 1) * 2 + pr) * 4 + sl + 1] = 0.f;
+      }
     }
     if (p.norm_w) {
       ss = warp_sum(ss);
-      if (lane == 0) s_ss[warp] = ss;
+      if (lane == 0) ssq[warp] = ss;
     }
   }
-  __syncthreads();
+  cons_bar_sync();
   float rs = 1.f;
   if (p.norm_w) {
     float tot = 0.f;
 #pragma unroll
-    for (int w = 0; w < NWARPS; w++) tot += s_ss[w];
+    for (int w = 0; w < CONS_WARPS; w++) tot += ssq[w];
     rs = rsqrtf(tot / (float)p.n_in + p.eps);
   }
-  const bool b_active = (t == (g & 3));
-
-  bool first = true;
-  for (; rt < p.n_row_tiles; rt += gridDim.x) {
+  const bool diag = (t == (g & 3));
+  int it = 0, par = 0;
+  for (int rt = blockIdx.x; rt < p.n_row_tiles; rt += gridDim.x, par ^= 1) {
     float acc0 = 0.f, acc1 = 0.f;
-    for (int jb = warp; jb < p.kgroups; jb += NWARPS * U) {
-      if (!first) {
+    for (int s = 0; s < stages_per_tile; s++, it++) {
+      const int slot = it % NS, groups = min(STAGE_GROUPS, p.kgroups - s * STAGE_GROUPS);
+      if (!mbar_wait(full0 + 8 * slot, (it / NS) & 1)) { *s_abort = 1; break; }
+      const uint8_t* stage = ring + slot * STAGE_BYTES;
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-          int j = jb + u * NWARPS;
-          if (j < p.kgroups) load_frag<QT>(fr[u], p.w + ((size_t)rt * p.kgroups + j) * TB, lane);
+      for (int u = 0; u < STAGE_GROUPS / CONS_WARPS; u++) {
+        const int gi = warp + u * CONS_WARPS;
+        if (gi < groups) {
+          const int j = s * STAGE_GROUPS + gi;
+          const uint4 bq0 = diag ? xq[(j * 2 + 0) * 8 + g] : *zero, bq1 = diag ? xq[(j * 2 + 1) * 8 + g] : *zero;
+          const float4 st = xsc[(j * 2 + (t >> 1)) * 2 + (t & 1)];
+          tile_mac<QT>(stage + gi * TB, lane, bq0, bq1, st, acc0, acc1);
         }
       }
-      first = false;
-#pragma unroll
-      for (int u = 0; u < U; u++) {
-        int j = jb + u * NWARPS;
-        if (j < p.kgroups) {
-          uint4 bf[4];
-#pragma unroll
-          for (int c = 0; c < 4; c++) bf[c] = b_active ? xs[(j * 4 + c) * 8 + g] : make_uint4(0, 0, 0, 0);
-          compute_frag<QT>(fr[u], bf, acc0, acc1);
-        }
-      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * slot);
     }
-    first = false;
     // quad lanes hold the columns {blocks 0,1 hi}, {2,3 hi}, {0,1 lo}, {2,3 lo}: add them
     acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1); acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
     acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1); acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
-    if (t == 0) { red[warp * 16 + g] = acc0; red[warp * 16 + 8 + g] = acc1; }
-    __syncthreads();
-    if (tid < 16) {
+    float* rb = red + par * CONS_WARPS * 16;
+    if (t == 0) { rb[warp * 16 + g] = acc0; rb[warp * 16 + 8 + g] = acc1; }
+    cons_bar_sync();
+    const bool ok = *s_abort == 0;      // uniform over the consumer warps: read after the barrier that follows every write
+    if (!ok) break;
+    if (warp == 0) {
       float v = 0.f;
+      if (lane < 16) {
 #pragma unroll
-      for (int w = 0; w < NWARPS; w++) v += red[w * 16 + tid];
-      v *= rs;
+        for (int w = 0; w < CONS_WARPS; w++) v += rb[w * 16 + lane];
+        v *= rs;
+      }
       if (p.epilogue == B200Q_EPI_LINEAR) {
-        int row = rt * 16 + tid;
-        if (row < p.n_out) {
+        const int row = rt * 16 + lane;
+        if (lane < 16 && row < p.n_out && ok) {
           if (p.bias) v += __half2float(p.bias[row]);
           if (p.residual) v += p.residual[(size_t)m * p.n_out + row];
           if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(v);
           else reinterpret_cast<float*>(p.y)[(size_t)m * p.n_out + row] = v;
         }
       } else {
-        fin[tid] = v;
-      }
-    }
-    if (p.epilogue == B200Q_EPI_SILU_MUL) {
-      __syncthreads();
-      if (tid < 8) {
-        int row = rt * 8 + tid;
-        if (row < p.n_out) {
-          float gt = fin[tid], up = fin[tid + 8];
-          float v = (gt / (1.f + __expf(-gt))) * up;
-          if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(v);
-          else reinterpret_cast<float*>(p.y)[(size_t)m * p.n_out + row] = v;
+        const float up = __shfl_down_sync(0xffffffffu, v, 8);     // rows 8..15 of the tile are the `up` rows
+        const int row = rt * 8 + lane;
+        if (lane < 8 && row < p.n_out && ok) {
+          const float o = (v / (1.f + __expf(-v))) * up;
+          if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(o);
+          else reinterpret_cast<float*>(p.y)[(size_t)m * p.n_out + row] = o;
         }
       }
     }
-    __syncthreads();
   }
 }
 
-template <int QT, int U>
+template <int QT>
 int launch_gemv(const b200q_gemv_args* a, const GemvParams& p, cudaStream_t stream) {
-  size_t smem = (size_t)p.kgroups * 512 + (NWARPS * 16 + 16 + NWARPS + 1) * sizeof(float);
+  constexpr int NS = Cfg<QT>::NS;
+  const size_t smem = (size_t)NS * STAGE_GROUPS * tile_bytes(QT) + (size_t)p.kgroups * (16 * 16 + 4 * 16) + 16 +
+                      (2 * CONS_WARPS * 16 + CONS_WARPS) * sizeof(float) + 2 * NS * sizeof(uint64_t) + 16;
   if (smem > 220 * 1024) return B200Q_ERR_TOO_LARGE;
-  auto kern = qgemv_kernel<QT, U>;
-  static int sm_count = 0;
-  static size_t smem_set = 0;
+  auto kern = qgemv_kernel<QT>;
+  static int sm_count = 0, occ_cache_smem = -1, occ_cache = 0;
   if (sm_count == 0) {
     int dev; B200Q_CHECK_CUDA(cudaGetDevice(&dev));
     B200Q_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
-  }
-  if (smem > 48 * 1024 && smem > smem_set) {
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    smem_set = 220 * 1024;
   }
-  int occ = 0;
-  B200Q_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NTHREADS, smem));
-  if (occ < 1) occ = 1;
-  int max_ctas = a->max_ctas > 0 ? a->max_ctas : occ * sm_count;
-  int grid_x = p.n_row_tiles < max_ctas ? p.n_row_tiles : max_ctas;
+  if (occ_cache_smem != (int)smem) {
+    B200Q_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_cache, kern, NTHREADS, smem));
+    if (occ_cache < 1) occ_cache = 1;
+    occ_cache_smem = (int)smem;
+  }
+  const int max_ctas = a->max_ctas > 0 ? a->max_ctas : occ_cache * sm_count;
+  const int grid_x = p.n_row_tiles < max_ctas ? p.n_row_tiles : max_ctas;
   B200Q_CHECK_CUDA(launch_k(kern, dim3(grid_x, a->m), dim3(NTHREADS), smem, stream, (a->flags & B200Q_FLAG_PDL) != 0, p));
   return B200Q_OK;
 }
 
 }  // namespace
+
+extern "C" int b200q_status_read_clear(int* status) {
+  if (!status) return B200Q_ERR_BAD_ARG;
+  int zero = 0;
+  B200Q_CHECK_CUDA(cudaMemcpyFromSymbol(status, g_status, sizeof(int)));
+  B200Q_CHECK_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(int)));
+  return B200Q_OK;
+}
 
 extern "C" int b200q_gemv(const b200q_gemv_args* a, void* stream) {
   if (!a || !a->w_packed || !a->x || !a->y) return B200Q_ERR_BAD_ARG;
@@ -282,13 +351,15 @@ extern "C" int b200q_gemv(const b200q_gemv_args* a, void* stream) {
   if (a->epilogue != B200Q_EPI_LINEAR && a->epilogue != B200Q_EPI_SILU_MUL) return B200Q_ERR_BAD_ARG;
   if (a->epilogue == B200Q_EPI_SILU_MUL && (a->bias || a->residual)) return B200Q_ERR_UNSUPPORTED;
   if ((uintptr_t)a->w_packed & 15) return B200Q_ERR_MISALIGNED;
-  if (((uintptr_t)a->x & (a->x_dtype == B200Q_F32 ? 3 : 1)) || ((uintptr_t)a->y & (a->y_dtype == B200Q_F32 ? 3 : 1))) return B200Q_ERR_MISALIGNED;
+  // activation rows are read 4 elements at a time
+  if (((uintptr_t)a->x & (a->x_dtype == B200Q_F32 ? 15 : 7)) || ((uintptr_t)a->y & (a->y_dtype == B200Q_F32 ? 3 : 1))) return B200Q_ERR_MISALIGNED;
+  if (a->norm_weight && ((uintptr_t)a->norm_weight & 7)) return B200Q_ERR_MISALIGNED;
   GemvParams p;
   p.w = (const uint8_t*)a->w_packed; p.x = a->x; p.norm_w = (const __half*)a->norm_weight; p.bias = (const __half*)a->bias;
   p.residual = (const float*)a->residual; p.y = a->y;
   p.n_out = a->n_out; p.n_in = a->n_in; p.kgroups = ceil_div(a->n_in, GROUP_ELEMS);
   p.n_row_tiles = a->epilogue == B200Q_EPI_SILU_MUL ? ceil_div(a->n_out, 8) : ceil_div(a->n_out, TILE_ROWS);
   p.x_f16 = a->x_dtype == B200Q_F16; p.y_f16 = a->y_dtype == B200Q_F16; p.epilogue = a->epilogue; p.eps = a->norm_eps;
-  if (a->qtype == B200Q_Q4_0) return launch_gemv<B200Q_Q4_0, 4>(a, p, (cudaStream_t)stream);
-  return launch_gemv<B200Q_Q8_0, 2>(a, p, (cudaStream_t)stream);
+  if (a->qtype == B200Q_Q4_0) return launch_gemv<B200Q_Q4_0>(a, p, (cudaStream_t)stream);
+  return launch_gemv<B200Q_Q8_0>(a, p, (cudaStream_t)stream);
 }

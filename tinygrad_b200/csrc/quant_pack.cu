@@ -70,12 +70,12 @@ __global__ void repack_kernel(int qtype, const uint8_t* __restrict__ raw0, const
     reinterpret_cast<uint4*>(tp)[h * 32 + l] = make_uint4(w[0], w[1], w[2], w[3]);
   } else {
     uint32_t w[8];
-    for (int i = 0; i < 8; i++) w[i] = 0x80808080u;                          // biased zero
+    for (int i = 0; i < 8; i++) w[i] = 0u;
     if (src) {
       const uint8_t* b = src + ((int64_t)row * nblk + blk) * bbytes;
       scale = (unsigned short)(b[0] | (b[1] << 8));
       for (int i = 0; i < 8; i++)
-        w[i] = (b[2 + 4 * i] | (b[3 + 4 * i] << 8) | (b[4 + 4 * i] << 16) | ((uint32_t)b[5 + 4 * i] << 24)) ^ 0x80808080u;
+        w[i] = b[2 + 4 * i] | (b[3 + 4 * i] << 8) | (b[4 + 4 * i] << 16) | ((uint32_t)b[5 + 4 * i] << 24);
     }
     reinterpret_cast<uint4*>(tp)[(2 * h) * 32 + l] = make_uint4(w[0], w[1], w[2], w[3]);
     reinterpret_cast<uint4*>(tp)[(2 * h + 1) * 32 + l] = make_uint4(w[4], w[5], w[6], w[7]);
@@ -114,7 +114,7 @@ __global__ void dequant_packed_kernel(int qtype, const uint8_t* __restrict__ pac
       uint4 q = reinterpret_cast<const uint4*>(tp)[(2 * h + half) * 32 + l];
       uint32_t w[4] = {q.x, q.y, q.z, q.w};
       for (int e = 0; e < 16; e++) {
-        int v = (int)(int8_t)(((w[e >> 2] >> ((e & 3) * 8)) & 0xFF) ^ 0x80);
+        int v = (int)(int8_t)((w[e >> 2] >> ((e & 3) * 8)) & 0xFF);
         store_val<OutT>(o, half * 16 + e, __fmul_rn(d, (float)v));
       }
     }

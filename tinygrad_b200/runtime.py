@@ -146,3 +146,10 @@ def device_props(i: int = 0) -> dict:
   sm, ma, mi, mem = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_size_t()
   check(_lib.load().b200q_device_props(i, ctypes.byref(sm), ctypes.byref(ma), ctypes.byref(mi), ctypes.byref(mem)))
   return {"sm_count": sm.value, "cc": (ma.value, mi.value), "total_mem": mem.value}
+
+
+def device_status() -> int:
+  """0 = fine; 1 = a bounded wait inside a kernel ran out since the last call (reads and clears the word)."""
+  st = ctypes.c_int()
+  check(_lib.load().b200q_status_read_clear(ctypes.byref(st)))
+  return st.value

@@ -63,13 +63,14 @@ def linear_names(cfg) -> list:
   return names
 
 
-def dense_model_raw(cfg, ggml_type: int = Q4_0, seed: int = 0, embd_std: float = 0.02, bias_std: float = 0.02) -> dict:
+def dense_model_raw(cfg, ggml_type: int = Q4_0, seed: int = 0, embd_std: float = 0.02, bias_std: float = 0.02, scale_std=None) -> dict:
   """Random-init dense model as the loader would see it: every Linear weight
   as raw quant bytes (key ``name.weight``, uint8), embeddings / norm weights /
   biases as fp16 arrays.  One seed per tensor, derived from its name."""
   sd = {}
   for name, n_out, n_in in linear_names(cfg):
-    sd[name + ".weight"] = BLOCK_MAKERS[ggml_type](n_out, n_in, np.random.default_rng(name_seed(name, seed)))
+    kw = {} if scale_std is None else {"scale_std": scale_std}
+    sd[name + ".weight"] = BLOCK_MAKERS[ggml_type](n_out, n_in, np.random.default_rng(name_seed(name, seed)), **kw)
     if cfg.qkv_bias and name.split(".")[-1] in ("attn_q", "attn_k", "attn_v"):
       sd[name + ".bias"] = (np.random.default_rng(name_seed(name + ".bias", seed)).standard_normal(n_out, dtype=np.float32) * bias_std).astype(np.float16)
   rng = np.random.default_rng(name_seed("token_embd", seed))
