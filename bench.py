@@ -175,6 +175,7 @@ def main():
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--blocks", type=int, default=0, help="debug: fewer transformer blocks (the reported line is then not the headline workload)")
   ap.add_argument("--no-pdl", action="store_true")
+  ap.add_argument("--gemv-ctas", type=int, default=0, help="tuning: cap on the CTAs of one GEMV launch (0 = library default)")
   ap.add_argument("--skip-prefill", action="store_true", help="debug/profiling: start at the end of the prompt with an all-zero KV cache")
   ap.add_argument("--skip-cpu-baseline", action="store_true")
   args = ap.parse_args()
@@ -196,7 +197,7 @@ def main():
   cfg = llama3_8b_config()
   if args.blocks: cfg = replace(cfg, num_blocks=args.blocks)
   t_build = time.time()
-  model = Transformer(cfg, synth.LazyDenseState(cfg, synth.Q4_0, seed=rank), ggml_type=synth.Q4_0, use_pdl=not args.no_pdl)
+  model = Transformer(cfg, synth.LazyDenseState(cfg, synth.Q4_0, seed=rank), ggml_type=synth.Q4_0, use_pdl=not args.no_pdl, gemv_max_ctas=args.gemv_ctas)
   t_build = time.time() - t_build
   prompt = [int(t) for t in np.random.default_rng(1000 + rank).integers(0, cfg.vocab_size, PROMPT_LEN)]
   # prompt (untimed): one position per step through the same kernels

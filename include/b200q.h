@@ -151,9 +151,10 @@ int b200q_embed(const void* device_table_f16, const int32_t* device_tokens, cons
  * tinygrad/llm/model.py:167-198 for T == 1 (`apply_rope` :29-33, cache store
  * :184-186, scaled_dot_product_attention tinygrad/mixin/rand.py:298-326).
  * qkv holds this token's [q | k | v] projections in fp32.  K and V caches are
- * [n_kv_heads][max_context][head_dim] each, fp16 or fp32.  The context is split
- * over `n_split` CTAs per KV head; partial results go through `scratch`
- * (b200q_attn_scratch_bytes) and the last CTA of a head merges them. */
+ * [n_kv_heads][max_context][head_dim] each, fp16 or fp32.  The context is cut
+ * into fixed slices of 64 positions, one CTA per (KV head, slice): `n_split` must be at
+ * least b200q_attn_min_split(max_context).  Partial results go through `scratch`
+ * (b200q_attn_scratch_bytes, zero-initialised once) and the last CTA of a head merges them. */
 typedef struct b200q_attn_args {
   const float* qkv;         /* device [n_heads*head_dim + 2*n_kv_heads*head_dim] */
   void* k_cache;            /* device */
@@ -166,6 +167,7 @@ typedef struct b200q_attn_args {
   int n_heads, n_kv_heads, head_dim, rope_dim, max_context, n_split;
   int flags;
 } b200q_attn_args;
+int b200q_attn_min_split(int max_context);
 size_t b200q_attn_scratch_bytes(int n_heads, int n_kv_heads, int head_dim, int n_split);
 int b200q_attn_decode(const b200q_attn_args* args, void* stream);
 

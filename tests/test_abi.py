@@ -55,8 +55,11 @@ def test_bad_arguments_are_rejected_without_a_device(lib):
   a.w_packed, a.y = 16, None
   assert lib.b200q_gemv(ctypes.byref(a), None) == -1
   at = _lib.AttnArgs(16, 16, 16, _lib.F16, 16, 16, 16, 16, 6, 4, 128, 128, 64, 4, 0)
+  assert lib.b200q_attn_min_split(2048) == 32 and lib.b200q_attn_min_split(65) == 2
   assert lib.b200q_attn_decode(ctypes.byref(at), None) == -1                 # heads not a multiple of kv heads
   at.n_heads, at.head_dim = 8, 100
+  assert lib.b200q_attn_decode(ctypes.byref(at), None) == -2
+  at.head_dim, at.max_context = 128, 1000                                    # 4 slices of 64 do not cover 1000 positions
   assert lib.b200q_attn_decode(ctypes.byref(at), None) == -2
   assert lib.b200q_graph_begin(None) == -1
 

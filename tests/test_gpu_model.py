@@ -72,8 +72,9 @@ def test_mid_size_model_matches_oracle(typ, kv):
 
 
 @pytest.mark.parametrize("kv_dtype,n_heads,n_kv,hd,rope_dim,pos,n_split", [
-  (np.float16, 32, 8, 128, 128, 0, 8), (np.float16, 32, 8, 128, 128, 700, 16), (np.float16, 28, 4, 128, 128, 300, 5),
-  (np.float32, 4, 2, 16, 16, 33, 3), (np.float16, 8, 1, 64, 32, 517, 1), (np.float16, 64, 8, 128, 128, 1023, 32)])
+  (np.float16, 32, 8, 128, 128, 0, 16), (np.float16, 32, 8, 128, 128, 700, 16), (np.float16, 28, 4, 128, 128, 300, 16),
+  (np.float32, 4, 2, 16, 16, 33, 16), (np.float16, 8, 1, 64, 32, 517, 20), (np.float16, 64, 8, 128, 128, 1023, 16),
+  (np.float16, 32, 8, 128, 128, 63, 16), (np.float16, 32, 8, 128, 128, 64, 16), (np.float32, 16, 4, 128, 64, 127, 16)])
 def test_attention_decode_matches_oracle(kv_dtype, n_heads, n_kv, hd, rope_dim, pos, n_split):
   from tinygrad_b200 import _lib
   from tinygrad_b200.runtime import DeviceBuffer

@@ -59,6 +59,7 @@ SIGNATURES = {
   "b200q_dequant_packed": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
   "b200q_gemv": (c_int, [POINTER(GemvArgs), c_void_p]),
   "b200q_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+  "b200q_attn_min_split": (c_int, [c_int]),
   "b200q_attn_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
   "b200q_attn_decode": (c_int, [POINTER(AttnArgs), c_void_p]),
   "b200q_argmax_scratch_bytes": (c_size_t, []),

@@ -23,16 +23,22 @@ __global__ void advance_kernel(int32_t* pos) {
 }
 
 // ---------------------------------------------------------------------------
-// attention.  grid (n_kv_heads, n_split); one warp per query head of the KV group.
-// Scores: each lane takes whole positions (a full head_dim dot product against the
-// roped query held in shared memory, no shuffles in the loop).  Values: each lane owns
-// 4 consecutive head dims and walks the positions with the probabilities broadcast
-// from shared memory.  Scratch layout:
+// attention.  grid (n_kv_heads, n_split); split s owns the fixed position range
+// [s*ATTN_CHUNK, (s+1)*ATTN_CHUNK); CTAs past the current context leave at once.
+// One warp per query head of the KV group.  The CTA first copies its K and V rows to
+// shared memory with every thread's loads in flight together (one global latency), then
+//   scores: each lane takes whole positions (full head_dim dot against the roped query),
+//   values: each lane owns 4 consecutive head dims and walks the positions.
+// Scratch layout:
 //   float partial[n_heads][n_split][head_dim + 4]   (o[head_dim], running max, denominator, 2 pad)
 //   uint  counter[n_kv_heads]                       (arrival count, reset by the last CTA)
+constexpr int MAX_HD = 128;
+constexpr int MAX_REP = 8;
+constexpr int ATTN_CHUNK = 64;    // positions per CTA
+
 template <typename KV> struct KvIO;
 template <> struct KvIO<__half> {
-  static constexpr int VEC = 8;   // elements per 16-byte load
+  static constexpr int VEC = 8;   // elements per 16-byte word
   static __device__ __forceinline__ float dot(const __half* k, const float* q) {
     uint4 r = *reinterpret_cast<const uint4*>(k);
     float2 a = __half22float2(*reinterpret_cast<__half2*>(&r.x)), b = __half22float2(*reinterpret_cast<__half2*>(&r.y));
@@ -44,7 +50,7 @@ template <> struct KvIO<__half> {
     float2 a = __half22float2(*reinterpret_cast<__half2*>(&r.x)), b = __half22float2(*reinterpret_cast<__half2*>(&r.y));
     return make_float4(a.x, a.y, b.x, b.y);
   }
-  static __device__ __forceinline__ void store(__half* p, float v) { *p = __float2half_rn(v); }
+  static __device__ __forceinline__ __half cast(float v) { return __float2half_rn(v); }
 };
 template <> struct KvIO<float> {
   static constexpr int VEC = 4;
@@ -53,52 +59,72 @@ template <> struct KvIO<float> {
     return r.x * q[0] + r.y * q[1] + r.z * q[2] + r.w * q[3];
   }
   static __device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
-  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+  static __device__ __forceinline__ float cast(float v) { return v; }
 };
 
-constexpr int MAX_HD = 128;
-constexpr int MAX_REP = 8;
-constexpr int ATTN_CHUNK = 256;   // positions whose scores are held in shared memory at a time
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
 
 template <typename KV>
 __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_attn_args a) {
-  __shared__ __align__(16) float s_q[MAX_REP][MAX_HD];   // roped queries of this KV group
-  __shared__ float s_sc[MAX_REP][ATTN_CHUNK];            // scores, then probabilities
+  constexpr int VEC = KvIO<KV>::VEC;
+  extern __shared__ __align__(16) unsigned char asmem[];
+  const int hd = a.head_dim, n_rep = a.n_heads / a.n_kv_heads, half_r = a.rope_dim >> 1;
+  const int rstride = hd + VEC;                           // padded row: lanes reading different rows hit different banks
+  KV* s_k = reinterpret_cast<KV*>(asmem);                 // [ATTN_CHUNK][rstride]
+  KV* s_v = s_k + ATTN_CHUNK * rstride;                   // [ATTN_CHUNK][rstride]
+  float* s_q = reinterpret_cast<float*>(s_v + ATTN_CHUNK * rstride);   // [n_rep][hd] roped queries
+  float* s_sc = s_q + n_rep * hd;                         // [n_rep][ATTN_CHUNK] scores, then probabilities
   __shared__ int s_last;
   const int kvh = blockIdx.x, split = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int hd = a.head_dim, n_rep = a.n_heads / a.n_kv_heads, half_r = a.rope_dim >> 1;
   pdl_launch_dependents();
   pdl_wait();
   const int pos = *a.pos;
   const int n_ctx = pos + 1;
-  const float* rope = a.rope + (size_t)pos * a.rope_dim;
-  const float* kq = a.qkv + (size_t)a.n_heads * hd + (size_t)kvh * hd;
-  const float* vq = a.qkv + (size_t)(a.n_heads + a.n_kv_heads) * hd + (size_t)kvh * hd;
+  const int lo = split * ATTN_CHUNK;
+  if (lo >= n_ctx) return;
+  const int n = min(ATTN_CHUNK, n_ctx - lo);
+  const int n_active = (n_ctx + ATTN_CHUNK - 1) / ATTN_CHUNK;
   KV* kc = reinterpret_cast<KV*>(a.k_cache) + (size_t)kvh * a.max_context * hd;
   KV* vc = reinterpret_cast<KV*>(a.v_cache) + (size_t)kvh * a.max_context * hd;
-  const int per = (n_ctx + a.n_split - 1) / a.n_split;
-  const int lo = split * per, hi = min(n_ctx, lo + per);
 
+  // all cached rows of the slice -> shared memory with asynchronous 16-byte copies: every copy of the CTA is in flight
+  // at once (one global latency).  The row at `pos` is not in the cache yet.
+  {
+    const int wpr = hd / VEC, n_old = min(n, pos - lo), words = n_old * wpr;
+    for (int i = threadIdx.x; i < words; i += blockDim.x) {
+      const int r = i / wpr, c = (i - r * wpr) * VEC;
+      cp_async16(s_k + r * rstride + c, kc + (size_t)(lo + r) * hd + c);
+      cp_async16(s_v + r * rstride + c, vc + (size_t)(lo + r) * hd + c);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   // RoPE, half-split layout: (x1 cos - x2 sin) || (x2 cos + x1 sin); dims past rope_dim pass through
+  const float* rope = a.rope + (size_t)pos * a.rope_dim;
   for (int i = threadIdx.x; i < n_rep * hd; i += blockDim.x) {
-    int r = i / hd, d = i - r * hd;
+    const int r = i / hd, d = i - r * hd;
     const float* q = a.qkv + (size_t)(kvh * n_rep + r) * hd;
     float v = q[d];
     if (d < half_r) v = q[d] * rope[d] - q[d + half_r] * rope[half_r + d];
     else if (d < a.rope_dim) v = q[d] * rope[d - half_r] + q[d - half_r] * rope[d];
-    s_q[r][d] = v;
+    s_q[i] = v;
   }
-  if (lo <= pos && pos < hi) {   // the CTA whose slice holds the new position appends it to the cache; nobody else reads it
+  if (lo <= pos && pos < lo + ATTN_CHUNK) {   // this CTA owns the new position: append it to the cache and to its slice
+    const float* kq = a.qkv + (size_t)a.n_heads * hd + (size_t)kvh * hd;
+    const float* vq = a.qkv + (size_t)(a.n_heads + a.n_kv_heads) * hd + (size_t)kvh * hd;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
       float v = kq[d];
       if (d < half_r) v = kq[d] * rope[d] - kq[d + half_r] * rope[half_r + d];
       else if (d < a.rope_dim) v = kq[d] * rope[d - half_r] + kq[d - half_r] * rope[d];
-      KvIO<KV>::store(kc + (size_t)pos * hd + d, v);
-      KvIO<KV>::store(vc + (size_t)pos * hd + d, vq[d]);
+      const KV kk = KvIO<KV>::cast(v), vv = KvIO<KV>::cast(vq[d]);
+      kc[(size_t)pos * hd + d] = kk; vc[(size_t)pos * hd + d] = vv;
+      s_k[(pos - lo) * rstride + d] = kk; s_v[(pos - lo) * rstride + d] = vv;
     }
   }
-  __syncthreads();   // queries staged; the appended row is visible to this CTA
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
 
   const int d0 = lane * 4;
   const bool dl = d0 < hd;
@@ -106,50 +132,52 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
   float* partial = reinterpret_cast<float*>(a.scratch);
   const int pstride = hd + 4;   // keeps every record 16-byte aligned
   if (warp < n_rep) {
-    float mx = -INFINITY, den = 0.f;
-    float4 o = make_float4(0, 0, 0, 0);
-    float* sc = s_sc[warp];
-    const float* q = s_q[warp];
-    for (int base = lo; base < hi; base += ATTN_CHUNK) {
-      const int n = min(ATTN_CHUNK, hi - base);
-      float lmax = -INFINITY;
-      for (int i = lane; i < n; i += 32) {
-        const KV* kr = kc + (size_t)(base + i) * hd;
-        float s = 0.f;
-        for (int d = 0; d < hd; d += KvIO<KV>::VEC) s += KvIO<KV>::dot(kr + d, q + d);
-        s *= scale;
-        sc[i] = s;
-        lmax = fmaxf(lmax, s);
-      }
-      float nm = fmaxf(mx, warp_max(lmax));
-      float corr = __expf(mx - nm), lsum = 0.f;
-      for (int i = lane; i < n; i += 32) { float pr = __expf(sc[i] - nm); sc[i] = pr; lsum += pr; }
-      den = den * corr + warp_sum(lsum);
-      o.x *= corr; o.y *= corr; o.z *= corr; o.w *= corr;
-      mx = nm;
-      __syncwarp();
-      if (dl) {
-        const KV* vr = vc + (size_t)base * hd + d0;
+    float* sc = s_sc + warp * ATTN_CHUNK;
+    const float* q = s_q + warp * hd;
+    float lmax = -INFINITY;
+    for (int i = lane; i < n; i += 32) {
+      const KV* kr = s_k + i * rstride;
+      float s = 0.f;
 #pragma unroll 4
-        for (int i = 0; i < n; i++) {
-          float pr = sc[i];
-          float4 v = KvIO<KV>::load4(vr + (size_t)i * hd);
-          o.x = fmaf(pr, v.x, o.x); o.y = fmaf(pr, v.y, o.y); o.z = fmaf(pr, v.z, o.z); o.w = fmaf(pr, v.w, o.w);
-        }
-      }
-      __syncwarp();
+      for (int d = 0; d < hd; d += VEC) s += KvIO<KV>::dot(kr + d, q + d);
+      s *= scale;
+      sc[i] = s;
+      lmax = fmaxf(lmax, s);
     }
-    float* pp = partial + ((size_t)(kvh * n_rep + warp) * a.n_split + split) * pstride;
-    if (dl) *reinterpret_cast<float4*>(pp + d0) = o;
-    if (lane == 0) { pp[hd] = mx; pp[hd + 1] = den; }
+    const float mx = warp_max(lmax);
+    float lsum = 0.f;
+    for (int i = lane; i < n; i += 32) { const float pr = __expf(sc[i] - mx); sc[i] = pr; lsum += pr; }
+    const float den = warp_sum(lsum);
+    __syncwarp();
+    float4 o = make_float4(0, 0, 0, 0);
+    if (dl) {
+      const KV* vr = s_v + d0;
+#pragma unroll 8
+      for (int i = 0; i < n; i++) {
+        const float pr = sc[i];
+        const float4 v = KvIO<KV>::load4(vr + i * rstride);
+        o.x = fmaf(pr, v.x, o.x); o.y = fmaf(pr, v.y, o.y); o.z = fmaf(pr, v.z, o.z); o.w = fmaf(pr, v.w, o.w);
+      }
+    }
+    if (n_active == 1) {   // short context: this CTA holds the whole softmax
+      if (dl) {
+        const float inv = 1.f / den;
+        *reinterpret_cast<float4*>(a.out + (size_t)(kvh * n_rep + warp) * hd + d0) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+      }
+    } else {
+      float* pp = partial + ((size_t)(kvh * n_rep + warp) * a.n_split + split) * pstride;
+      if (dl) *reinterpret_cast<float4*>(pp + d0) = o;
+      if (lane == 0) { pp[hd] = mx; pp[hd + 1] = den; }
+    }
   }
-  // last CTA of this KV head merges the splits
+  if (n_active == 1) return;
+  // last CTA of this KV head merges the slices
   __threadfence();
   __syncthreads();
   unsigned* counter = reinterpret_cast<unsigned*>(partial + (size_t)a.n_heads * a.n_split * pstride);
   if (threadIdx.x == 0) {
-    unsigned prev = atomicAdd(&counter[kvh], 1u);
-    s_last = (prev == (unsigned)a.n_split - 1);
+    const unsigned prev = atomicAdd(&counter[kvh], 1u);
+    s_last = (prev == (unsigned)n_active - 1);
     if (s_last) counter[kvh] = 0;
   }
   __syncthreads();
@@ -157,24 +185,33 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
   __threadfence();
   if (warp < n_rep) {
     const float* hp = partial + (size_t)(kvh * n_rep + warp) * a.n_split * pstride;
+    // slice statistics: one slice per lane, all loads in flight together
     float gm = -INFINITY;
-    for (int s = 0; s < a.n_split; s++) gm = fmaxf(gm, __ldcg(hp + s * pstride + hd));
+    for (int s0 = 0; s0 < n_active; s0 += 32) {
+      const int s = s0 + lane;
+      gm = fmaxf(gm, s < n_active ? __ldcg(hp + s * pstride + hd) : -INFINITY);
+    }
+    gm = warp_max(gm);
     float den = 0.f;
     float4 o = make_float4(0, 0, 0, 0);
-    for (int s = 0; s < a.n_split; s++) {
-      float m_s = __ldcg(hp + s * pstride + hd), l_s = __ldcg(hp + s * pstride + hd + 1);
-      if (l_s == 0.f) continue;            // empty slice
-      float w = __expf(m_s - gm);
-      den += w * l_s;
-      if (dl) {
-        const float* op = hp + s * pstride + d0;
-        o.x += w * __ldcg(op); o.y += w * __ldcg(op + 1); o.z += w * __ldcg(op + 2); o.w += w * __ldcg(op + 3);
+    for (int s0 = 0; s0 < n_active; s0 += 32) {
+      const int s = s0 + lane;
+      float w = 0.f, l = 0.f;
+      if (s < n_active) { w = __expf(__ldcg(hp + s * pstride + hd) - gm); l = __ldcg(hp + s * pstride + hd + 1); }
+      den += warp_sum(w * l);
+      const int cnt = min(32, n_active - s0);
+#pragma unroll 8
+      for (int j = 0; j < cnt; j++) {
+        const float wj = __shfl_sync(0xffffffffu, w, j);      // every lane takes part in the shuffle
+        if (dl) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(hp + (size_t)(s0 + j) * pstride + d0));
+          o.x = fmaf(wj, v.x, o.x); o.y = fmaf(wj, v.y, o.y); o.z = fmaf(wj, v.z, o.z); o.w = fmaf(wj, v.w, o.w);
+        }
       }
     }
     if (dl) {
-      float inv = 1.f / den;
-      float* out = a.out + (size_t)(kvh * n_rep + warp) * hd + d0;
-      out[0] = o.x * inv; out[1] = o.y * inv; out[2] = o.z * inv; out[3] = o.w * inv;
+      const float inv = 1.f / den;
+      *reinterpret_cast<float4*>(a.out + (size_t)(kvh * n_rep + warp) * hd + d0) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
     }
   }
 }
@@ -253,6 +290,8 @@ extern "C" int b200q_advance(int32_t* pos, int flags, void* stream) {
   return B200Q_OK;
 }
 
+extern "C" int b200q_attn_min_split(int max_context) { return max_context <= 0 ? 0 : ceil_div(max_context, ATTN_CHUNK); }
+
 extern "C" size_t b200q_attn_scratch_bytes(int n_heads, int n_kv_heads, int head_dim, int n_split) {
   if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || n_split <= 0) return 0;
   return ((size_t)n_heads * n_split * (head_dim + 4)) * sizeof(float) + (size_t)n_kv_heads * sizeof(unsigned);
@@ -265,11 +304,19 @@ extern "C" int b200q_attn_decode(const b200q_attn_args* a, void* stream) {
   if (a->rope_dim < 0 || a->rope_dim > a->head_dim || a->rope_dim % 2) return B200Q_ERR_BAD_SHAPE;
   if (a->kv_dtype != B200Q_F16 && a->kv_dtype != B200Q_F32) return B200Q_ERR_BAD_ARG;
   if (((uintptr_t)a->k_cache | (uintptr_t)a->v_cache | (uintptr_t)a->qkv | (uintptr_t)a->out | (uintptr_t)a->scratch) & 15) return B200Q_ERR_MISALIGNED;
+  if ((int64_t)a->n_split * ATTN_CHUNK < a->max_context) return B200Q_ERR_BAD_SHAPE;   // the slices must cover the whole cache
   int n_rep = a->n_heads / a->n_kv_heads;
   dim3 grid(a->n_kv_heads, a->n_split), block(n_rep * 32);
   bool pdl = (a->flags & B200Q_FLAG_PDL) != 0;
-  if (a->kv_dtype == B200Q_F16) B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<__half>, grid, block, 0, (cudaStream_t)stream, pdl, *a));
-  else B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<float>, grid, block, 0, (cudaStream_t)stream, pdl, *a));
+  const int esz = a->kv_dtype == B200Q_F16 ? 2 : 4, vec = 16 / esz;
+  size_t smem = (size_t)2 * ATTN_CHUNK * (a->head_dim + vec) * esz + (size_t)n_rep * (a->head_dim + ATTN_CHUNK) * sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(attn_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    attr_set = true;
+  }
+  if (a->kv_dtype == B200Q_F16) B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<__half>, grid, block, smem, (cudaStream_t)stream, pdl, *a));
+  else B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<float>, grid, block, smem, (cudaStream_t)stream, pdl, *a));
   return B200Q_OK;
 }
 

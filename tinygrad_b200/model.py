@@ -47,14 +47,15 @@ class _Block:
 
 class Transformer:
   def __init__(self, config: TransformerConfig, state_dict: dict, ggml_type: int = _lib.Q4_0, n_split: int = 0, use_pdl: bool = True,
-               use_graph: bool = True):
+               use_graph: bool = True, gemv_max_ctas: int = 0):
     """state_dict: the reference's tensor names -> numpy arrays; Linear weights as raw
     GGUF block bytes (uint8), embeddings / norms / biases as fp16."""
     c = self.config = config
     assert c.max_context > 0 and c.n_heads % c.n_kv_heads == 0
     self.qtype, self.flags, self.use_graph = ggml_type, (FLAG_PDL if use_pdl else 0), use_graph
     self.q_dim, self.kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
-    self.n_split = n_split or max(1, min(32, c.max_context // 64))
+    self.gemv_max_ctas = gemv_max_ctas
+    self.n_split = n_split or _lib.load().b200q_attn_min_split(c.max_context)
     self.max_context = c.max_context
     self.stream = Stream()
     sd = state_dict
@@ -109,17 +110,17 @@ class Transformer:
     check(lib.b200q_embed(self.token_embd.ptr, self.tokens.ptr, self.pos.ptr, self.x.ptr, c.dim, c.vocab_size, fl, s))
     for b in self.blk:
       quant.gemv(b.qkv.ptr, self.qtype, self.q_dim + 2 * self.kv_dim, c.dim, self.x, self.qkv, norm_weight=b.attn_norm, norm_eps=c.norm_eps,
-                 bias=b.qkv_bias, flags=fl, stream=s)
+                 bias=b.qkv_bias, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
       a = _lib.AttnArgs(self.qkv.ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, self.pos.ptr, self.attn.ptr, self.attn_scratch.ptr,
                         c.n_heads, c.n_kv_heads, c.head_dim, c.rope_dim, c.max_context, self.n_split, fl)
       check(lib.b200q_attn_decode(ctypes.byref(a), s))
-      quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, self.attn, self.x, residual=self.x, flags=fl, stream=s)
+      quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, self.attn, self.x, residual=self.x, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
       quant.gemv(b.gate_up.buf.ptr, self.qtype, c.hidden_dim, c.dim, self.x, self.act, norm_weight=b.ffn_norm, norm_eps=c.norm_eps,
-                 epilogue=EPI_SILU_MUL, flags=fl, stream=s)
-      quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, self.act, self.x, residual=self.x, flags=fl, stream=s)
+                 epilogue=EPI_SILU_MUL, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
+      quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, self.act, self.x, residual=self.x, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
     if with_head:
       quant.gemv(self.output.buf.ptr, self.qtype, c.vocab_size, c.dim, self.x, self.logits, norm_weight=self.output_norm, norm_eps=c.norm_eps,
-                 flags=fl, stream=s)
+                 flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
       check(lib.b200q_argmax_advance(self.logits.ptr, c.vocab_size, self.tokens.ptr, self.pos.ptr, self.argmax_scratch.ptr, fl, s))
     else:
       check(lib.b200q_advance(self.pos.ptr, fl, s))
@@ -138,13 +139,13 @@ class Transformer:
     with g:
       for b in self.blk:
         quant.gemv(b.qkv.ptr, self.qtype, self.q_dim + 2 * self.kv_dim, c.dim, self.x, self.qkv, norm_weight=b.attn_norm, norm_eps=c.norm_eps,
-                   bias=b.qkv_bias, flags=fl, stream=s)
-        quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, self.attn, self.x, flags=fl, stream=s)
+                   bias=b.qkv_bias, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
+        quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, self.attn, self.x, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
         quant.gemv(b.gate_up.buf.ptr, self.qtype, c.hidden_dim, c.dim, self.x, self.act, norm_weight=b.ffn_norm, norm_eps=c.norm_eps,
-                   epilogue=EPI_SILU_MUL, flags=fl, stream=s)
-        quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, self.act, self.x, flags=fl, stream=s)
+                   epilogue=EPI_SILU_MUL, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
+        quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, self.act, self.x, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
       quant.gemv(self.output.buf.ptr, self.qtype, c.vocab_size, c.dim, self.x, self.logits, norm_weight=self.output_norm, norm_eps=c.norm_eps,
-                 flags=fl, stream=s)
+                 flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
     return g
 
   def step(self, with_head: bool = True) -> None:
