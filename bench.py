@@ -149,8 +149,11 @@ def run_gemv_probe(args):
   y = runtime.DeviceBuffer.empty((n_out,), np.float32)
   st = runtime.Stream()
   fl = 0 if args.no_pdl else 1
+  lib = __import__("tinygrad_b200._lib", fromlist=["load"]).load()
+  xq = runtime.DeviceBuffer(lib.b200q_xq_bytes(n_in), zero=True) if args.probe_xq else None   # an all-zero record times like any other
+  res = runtime.DeviceBuffer.empty((n_out,), np.float32, zero=True) if args.probe_residual else None
   def enqueue(n):
-    for i in range(n): quant.gemv(ws[i % n_rot].buf.ptr, synth.Q4_0, n_out, n_in, x, y, flags=fl, stream=st)
+    for i in range(n): quant.gemv(ws[i % n_rot].buf.ptr, synth.Q4_0, n_out, n_in, x, y, flags=fl, stream=st, xq_in=xq, residual=res)
   enqueue(args.warmup); st.synchronize()
   g = runtime.Graph(st)
   with g: enqueue(args.steps)
@@ -169,6 +172,8 @@ def main():
   ap.add_argument("--workload", default="decode", choices=["decode", "gemv"])
   ap.add_argument("--gemv-shape", default="28672x4096", help="rows x K of the probe (gate+up interleaved = 28672x4096)")
   ap.add_argument("--rotate-mb", type=int, default=512)
+  ap.add_argument("--probe-xq", action="store_true", help="gemv probe: hand the kernel a ready-made activation record")
+  ap.add_argument("--probe-residual", action="store_true", help="gemv probe: add a residual vector in the epilogue")
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=256)
   ap.add_argument("--warmup", type=int, default=8)
@@ -176,6 +181,7 @@ def main():
   ap.add_argument("--blocks", type=int, default=0, help="debug: fewer transformer blocks (the reported line is then not the headline workload)")
   ap.add_argument("--no-pdl", action="store_true")
   ap.add_argument("--gemv-ctas", type=int, default=0, help="tuning: cap on the CTAs of one GEMV launch (0 = library default)")
+  ap.add_argument("--handover", default=None, help="tuning: comma list of hand-over edges (attn_o,o_gateup,gateup_down,down_qkv), 'none' or 'all'")
   ap.add_argument("--skip-prefill", action="store_true", help="debug/profiling: start at the end of the prompt with an all-zero KV cache")
   ap.add_argument("--skip-cpu-baseline", action="store_true")
   args = ap.parse_args()
@@ -197,7 +203,8 @@ def main():
   cfg = llama3_8b_config()
   if args.blocks: cfg = replace(cfg, num_blocks=args.blocks)
   t_build = time.time()
-  model = Transformer(cfg, synth.LazyDenseState(cfg, synth.Q4_0, seed=rank), ggml_type=synth.Q4_0, use_pdl=not args.no_pdl, gemv_max_ctas=args.gemv_ctas)
+  model = Transformer(cfg, synth.LazyDenseState(cfg, synth.Q4_0, seed=rank), ggml_type=synth.Q4_0, use_pdl=not args.no_pdl, gemv_max_ctas=args.gemv_ctas,
+                      handover={None: None, 'none': False, 'all': True}.get(args.handover, args.handover))
   t_build = time.time() - t_build
   prompt = [int(t) for t in np.random.default_rng(1000 + rank).integers(0, cfg.vocab_size, PROMPT_LEN)]
   # prompt (untimed): one position per step through the same kernels
@@ -273,7 +280,7 @@ def main():
   out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
          "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
          "config": {"workload": WORKLOAD if not (args.blocks or args.skip_prefill) else f"DEBUG (blocks={args.blocks}, skip_prefill={args.skip_prefill}) of: " + WORKLOAD, "parallelism": f"replicas x{world}",
-                    "l2": "inputs larger than L2 (4.2 GB of weights per step vs 126 MB)", "pdl": not args.no_pdl, "n_split": model.n_split,
+                    "l2": "inputs larger than L2 (4.2 GB of weights per step vs 126 MB)", "pdl": not args.no_pdl, "n_split": model.n_split, "activation_handover": sorted(model.edges),
                     "step_hbm_gbs": step_bytes / (ms_dev / args.steps * 1e-3) / 1e9, "step_frac_of_peak": step_bytes / (ms_dev / args.steps * 1e-3) / 1e9 / peak,
                     "model_build_s": round(t_build, 1)},
          "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,

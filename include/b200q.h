@@ -137,15 +137,31 @@ typedef struct b200q_gemv_args {
   void* y;                  /* device [m, n_out], y_dtype */
   int flags;                /* B200Q_FLAG_* */
   int max_ctas;             /* 0 = library default (a multiple of the SM count) */
+  /* Optional hand-over of quantised activations between consecutive launches (m == 1 only), which takes the
+   * activation quantisation off the critical path of the consuming GEMV.  A record is b200q_xq_bytes(n) bytes,
+   * 16-byte aligned, opaque to the caller (layout: tinygrad_b200/csrc/actquant.cuh). */
+  const void* xq_in;        /* device record of the input row written by an upstream kernel (then `x` is ignored and may be
+                               NULL).  If norm_weight is set the record already holds x * norm_weight and ss_in gives the
+                               partial sums of squares of x for the RMSNorm scalar. */
+  const float* ss_in;       /* device [ss_count] or NULL */
+  int ss_count;
+  void* xq_out;             /* device record to fill with THIS launch's output row (n_out % 128 == 0), optionally
+                               multiplied by xq_out_norm_weight first (the next GEMV's RMSNorm weight, fp16 [n_out]);
+                               `y` may then be NULL if nobody needs the fp32 values */
+  const void* xq_out_norm_weight;
+  float* ss_out;            /* device [n_out / 32] partial sums of squares of the output row, or NULL */
 } b200q_gemv_args;
 int b200q_gemv(const b200q_gemv_args* args, void* stream);
+size_t b200q_xq_bytes(int n);
 
 /* ---- decode-step kernels -------------------------------------------------
  * Token embedding lookup to the fp32 residual stream:
  * `token_embd(tokens).float()` (tinygrad/llm/model.py:359).  The token id is read
  * on the device from tokens[*pos]. */
 int b200q_embed(const void* device_table_f16, const int32_t* device_tokens, const int32_t* device_pos, float* device_x, int dim,
-                int vocab, int flags, void* stream);
+                int vocab, void* xq_out /* optional record for the first GEMV (b200q_gemv_args.xq_in), or NULL */,
+                const void* xq_norm_weight /* fp16 [dim], multiplied into the record, or NULL */,
+                float* ss_out /* [dim / 32] partial sums of squares, or NULL */, int flags, void* stream);
 
 /* One-token GQA attention with RoPE and KV-cache update:
  * tinygrad/llm/model.py:167-198 for T == 1 (`apply_rope` :29-33, cache store
@@ -166,6 +182,8 @@ typedef struct b200q_attn_args {
   void* scratch;            /* device, b200q_attn_scratch_bytes(), zero-initialised once */
   int n_heads, n_kv_heads, head_dim, rope_dim, max_context, n_split;
   int flags;
+  void* xq_out;             /* optional: the output row also as a quantised record for the output projection
+                               (b200q_gemv_args.xq_in); needs head_dim == 128 */
 } b200q_attn_args;
 int b200q_attn_min_split(int max_context);
 size_t b200q_attn_scratch_bytes(int n_heads, int n_kv_heads, int head_dim, int n_split);

@@ -47,20 +47,23 @@ def test_bad_arguments_are_rejected_without_a_device(lib):
   assert lib.b200q_repack(_lib.Q4_0, 16, None, 16, 16, 48, None) == -2
   assert lib.b200q_repack(_lib.Q4_0, 16, None, 8, 16, 32, None) == -3        # packed buffer must be 16-byte aligned
   assert lib.b200q_repack(_lib.Q6_K, 16, None, 16, 16, 256, None) == -4
-  a = _lib.GemvArgs(_lib.Q4_0, 16, 128, 1, 16, 16, _lib.F32, _lib.F32, None, 0.0, 0, None, None, 16, 0, 0)
+  a = _lib.GemvArgs(_lib.Q4_0, 16, 128, 1, 16, 16, _lib.F32, _lib.F32, None, 0.0, 0, None, None, 16, 0, 0, None, None, 0, None, None, None)
   a.n_in = 100
   assert lib.b200q_gemv(ctypes.byref(a), None) == -2
   a.n_in, a.w_packed = 128, 8
   assert lib.b200q_gemv(ctypes.byref(a), None) == -3
   a.w_packed, a.y = 16, None
   assert lib.b200q_gemv(ctypes.byref(a), None) == -1
-  at = _lib.AttnArgs(16, 16, 16, _lib.F16, 16, 16, 16, 16, 6, 4, 128, 128, 64, 4, 0)
+  at = _lib.AttnArgs(16, 16, 16, _lib.F16, 16, 16, 16, 16, 6, 4, 128, 128, 64, 4, 0, None)
   assert lib.b200q_attn_min_split(2048) == 32 and lib.b200q_attn_min_split(65) == 2
   assert lib.b200q_attn_decode(ctypes.byref(at), None) == -1                 # heads not a multiple of kv heads
   at.n_heads, at.head_dim = 8, 100
   assert lib.b200q_attn_decode(ctypes.byref(at), None) == -2
   at.head_dim, at.max_context = 128, 1000                                    # 4 slices of 64 do not cover 1000 positions
   assert lib.b200q_attn_decode(ctypes.byref(at), None) == -2
+  a.y, a.xq_out, a.n_out = 16, 32, 200                                       # a record needs whole groups of 128 outputs
+  assert lib.b200q_gemv(ctypes.byref(a), None) == -2
+  assert lib.b200q_xq_bytes(4096) == 32 * 320 and lib.b200q_xq_bytes(100) == 320 and lib.b200q_xq_bytes(0) == 0
   assert lib.b200q_graph_begin(None) == -1
 
 

@@ -44,18 +44,21 @@ def test_greedy_stream_identical_to_reference(golden, name, mode):
   assert got == want
 
 
-@pytest.mark.parametrize("typ,kv", [(2, "float16"), (8, "float16"), (2, "float32")])
-def test_mid_size_model_matches_oracle(typ, kv):
+@pytest.mark.parametrize("typ,kv,hd,handover", [(2, "float16", 64, None), (8, "float16", 64, None), (2, "float32", 64, None),
+                                                 (2, "float16", 128, True), (8, "float16", 128, True), (2, "float16", 128, False),
+                                                 (2, "float16", 128, None), (2, "float16", 128, "gateup_down,down_qkv")])
+def test_mid_size_model_matches_oracle(typ, kv, hd, handover):
   """A model too big for the reference's interpreter: logits within tolerance of the oracle at every step,
   identical greedy stream, and KV-prefix reuse gives the same continuation."""
   from tinygrad_b200.model import Transformer, TransformerConfig
-  kw = dict(num_blocks=3, dim=512, hidden_dim=1408, n_heads=8, n_kv_heads=2, norm_eps=1e-5, vocab_size=2000, head_dim=64, rope_theta=500000.0,
-            rope_dim=64, max_context=160, qkv_bias=(typ == 8), kv_dtype=kv)
+  kw = dict(num_blocks=3, dim=512, hidden_dim=1408, n_heads=512 // hd, n_kv_heads=2, norm_eps=1e-5, vocab_size=2000, head_dim=hd, rope_theta=500000.0,
+            rope_dim=hd, max_context=160, qkv_bias=(typ == 8), kv_dtype=kv)
   cfg = TransformerConfig(**kw)
   sd = synth.dense_model_raw(cfg, typ, seed=11, embd_std=0.3, scale_std=0.02 if typ == 2 else 0.0015)   # weights of rms ~0.1 either way
   prompt = [int(t) for t in np.random.default_rng(1).integers(0, 2000, 70)]
   want, want_logits = llm.Transformer(llm.Config(**kw), _oracle_weights(cfg, sd, typ)).generate(prompt, 24, keep_logits=True)
-  m = Transformer(cfg, sd, ggml_type=typ)
+  m = Transformer(cfg, sd, ggml_type=typ, handover=handover)
+  if handover is not None: assert m.handover == bool(handover)
   got = []
   for i, tok in enumerate(m.generate(list(prompt))):
     # logits after several blocks: the 15-bit activation quantisation (like the fp16 rounding of the KV cache, which moves
@@ -98,7 +101,7 @@ def test_attention_decode_matches_oracle(kv_dtype, n_heads, n_kv, hd, rope_dim, 
   out = DeviceBuffer.empty((n_heads * hd,), np.float32)
   scratch = DeviceBuffer(lib.b200q_attn_scratch_bytes(n_heads, n_kv, hd, n_split), zero=True)
   a = _lib.AttnArgs(d["qkv"].ptr, d["kc"].ptr, d["vc"].ptr, _lib.F16 if kv_dtype == np.float16 else _lib.F32, d["fc"].ptr, d["pos"].ptr, out.ptr,
-                    scratch.ptr, n_heads, n_kv, hd, rope_dim, ctx, n_split, 0)
+                    scratch.ptr, n_heads, n_kv, hd, rope_dim, ctx, n_split, 0, None)
   for _ in range(2):   # the scratch counters must reset themselves
     _lib.check(lib.b200q_attn_decode(ctypes.byref(a), None))
     assert_close(out.numpy(), ref, tol=2e-3, what="attention output")

@@ -14,13 +14,15 @@ FLAG_PDL = 1
 class GemvArgs(Structure):
   _fields_ = [("qtype", c_int), ("n_out", c_int), ("n_in", c_int), ("m", c_int), ("w_packed", c_void_p), ("x", c_void_p),
               ("x_dtype", c_int), ("y_dtype", c_int), ("norm_weight", c_void_p), ("norm_eps", c_float), ("epilogue", c_int),
-              ("bias", c_void_p), ("residual", c_void_p), ("y", c_void_p), ("flags", c_int), ("max_ctas", c_int)]
+              ("bias", c_void_p), ("residual", c_void_p), ("y", c_void_p), ("flags", c_int), ("max_ctas", c_int),
+              ("xq_in", c_void_p), ("ss_in", c_void_p), ("ss_count", c_int), ("xq_out", c_void_p), ("xq_out_norm_weight", c_void_p),
+              ("ss_out", c_void_p)]
 
 
 class AttnArgs(Structure):
   _fields_ = [("qkv", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("kv_dtype", c_int), ("rope", c_void_p), ("pos", c_void_p),
               ("out", c_void_p), ("scratch", c_void_p), ("n_heads", c_int), ("n_kv_heads", c_int), ("head_dim", c_int), ("rope_dim", c_int),
-              ("max_context", c_int), ("n_split", c_int), ("flags", c_int)]
+              ("max_context", c_int), ("n_split", c_int), ("flags", c_int), ("xq_out", c_void_p)]
 
 
 # name -> (restype, argtypes); every symbol include/b200q.h declares
@@ -58,7 +60,8 @@ SIGNATURES = {
   "b200q_repack": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
   "b200q_dequant_packed": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
   "b200q_gemv": (c_int, [POINTER(GemvArgs), c_void_p]),
-  "b200q_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+  "b200q_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+  "b200q_xq_bytes": (c_size_t, [c_int]),
   "b200q_attn_min_split": (c_int, [c_int]),
   "b200q_attn_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
   "b200q_attn_decode": (c_int, [POINTER(AttnArgs), c_void_p]),

@@ -2,18 +2,35 @@
 // with RoPE and KV-cache update, greedy arg-max.  Semantics follow
 // tinygrad/llm/model.py:167-198 (attention, T == 1), :29-33 (RoPE), :358-364 (forward).
 #include "common.cuh"
+#include "actquant.cuh"
 #include <math.h>
 
 namespace {
 
-__global__ void embed_kernel(const __half* __restrict__ table, const int32_t* __restrict__ tokens, const int32_t* __restrict__ pos,
-                             float* __restrict__ x, int dim, int vocab) {
+// Also leaves, for the first GEMV of the step, the row already multiplied by that GEMV's RMSNorm weight and
+// quantised (actquant.cuh), with one partial sum of squares per block of 32.
+__global__ void __launch_bounds__(256) embed_kernel(const __half* __restrict__ table, const int32_t* __restrict__ tokens,
+                                                    const int32_t* __restrict__ pos, float* __restrict__ x, int dim, int vocab, void* xq_out,
+                                                    const __half* __restrict__ norm_w, float* ss_out) {
   pdl_launch_dependents();
   pdl_wait();
   int tok = tokens[*pos];
   tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += gridDim.x * blockDim.x)
-    x[i] = __half2float(table[(size_t)tok * dim + i]);
+  const __half* row = table + (size_t)tok * dim;
+  if (!xq_out) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += gridDim.x * blockDim.x) x[i] = __half2float(row[i]);
+    return;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, kgroups = (dim + GROUP_ELEMS - 1) / GROUP_ELEMS;
+  const int wpb = blockDim.x >> 5;
+  const XqDst dst(xq_out, kgroups);
+  for (int b = blockIdx.x * wpb + warp; b < kgroups * 4; b += gridDim.x * wpb) {      // one warp per block of 32, lane = element
+    const int k = b * 32 + lane;
+    float v = 0.f;
+    if (k < dim) { v = __half2float(row[k]); x[k] = v; }
+    if (ss_out && b * 32 < dim) { const float s2 = warp_sum(v * v); if (lane == 0) ss_out[b] = s2; }
+    quant_block_32x1((norm_w && k < dim) ? v * __half2float(norm_w[k]) : v, lane, b, dst);
+  }
 }
 
 __global__ void advance_kernel(int32_t* pos) {
@@ -160,10 +177,10 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
       }
     }
     if (n_active == 1) {   // short context: this CTA holds the whole softmax
-      if (dl) {
-        const float inv = 1.f / den;
-        *reinterpret_cast<float4*>(a.out + (size_t)(kvh * n_rep + warp) * hd + d0) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
-      }
+      const float inv = 1.f / den;
+      const float4 r = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+      if (dl) *reinterpret_cast<float4*>(a.out + (size_t)(kvh * n_rep + warp) * hd + d0) = r;
+      if (a.xq_out) quant_block_8x4(r, lane & 7, (kvh * n_rep + warp) * 4 + (lane >> 3), XqDst(a.xq_out, a.n_heads));   // head_dim 128: one group per head
     } else {
       float* pp = partial + ((size_t)(kvh * n_rep + warp) * a.n_split + split) * pstride;
       if (dl) *reinterpret_cast<float4*>(pp + d0) = o;
@@ -185,34 +202,34 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
   __threadfence();
   if (warp < n_rep) {
     const float* hp = partial + (size_t)(kvh * n_rep + warp) * a.n_split * pstride;
-    // slice statistics: one slice per lane, all loads in flight together
-    float gm = -INFINITY;
-    for (int s0 = 0; s0 < n_active; s0 += 32) {
-      const int s = s0 + lane;
-      gm = fmaxf(gm, s < n_active ? __ldcg(hp + s * pstride + hd) : -INFINITY);
-    }
-    gm = warp_max(gm);
-    float den = 0.f;
+    // Batches of 16 slices: the statistics (one slice per lane) and every lane's 4 output dims of all 16 slices are
+    // loaded before anything is used, so a batch costs one L2 round trip.  Running max / denominator across batches.
+    float gm = -INFINITY, den = 0.f;
     float4 o = make_float4(0, 0, 0, 0);
-    for (int s0 = 0; s0 < n_active; s0 += 32) {
-      const int s = s0 + lane;
-      float w = 0.f, l = 0.f;
-      if (s < n_active) { w = __expf(__ldcg(hp + s * pstride + hd) - gm); l = __ldcg(hp + s * pstride + hd + 1); }
-      den += warp_sum(w * l);
-      const int cnt = min(32, n_active - s0);
-#pragma unroll 8
-      for (int j = 0; j < cnt; j++) {
+    for (int s0 = 0; s0 < n_active; s0 += 16) {
+      const int cnt = min(16, n_active - s0);
+      float2 ml = make_float2(-INFINITY, 0.f);
+      if (lane < cnt) ml = __ldcg(reinterpret_cast<const float2*>(hp + (size_t)(s0 + lane) * pstride + hd));
+      float4 ov[16];
+#pragma unroll
+      for (int j = 0; j < 16; j++)
+        ov[j] = (dl && j < cnt) ? __ldcg(reinterpret_cast<const float4*>(hp + (size_t)(s0 + j) * pstride + d0)) : make_float4(0, 0, 0, 0);
+      const float nm = fmaxf(gm, warp_max(ml.x));
+      const float corr = __expf(gm - nm);
+      const float w = lane < cnt ? __expf(ml.x - nm) : 0.f;
+      den = den * corr + warp_sum(w * ml.y);
+      o.x *= corr; o.y *= corr; o.z *= corr; o.w *= corr;
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
         const float wj = __shfl_sync(0xffffffffu, w, j);      // every lane takes part in the shuffle
-        if (dl) {
-          const float4 v = __ldcg(reinterpret_cast<const float4*>(hp + (size_t)(s0 + j) * pstride + d0));
-          o.x = fmaf(wj, v.x, o.x); o.y = fmaf(wj, v.y, o.y); o.z = fmaf(wj, v.z, o.z); o.w = fmaf(wj, v.w, o.w);
-        }
+        o.x = fmaf(wj, ov[j].x, o.x); o.y = fmaf(wj, ov[j].y, o.y); o.z = fmaf(wj, ov[j].z, o.z); o.w = fmaf(wj, ov[j].w, o.w);
       }
+      gm = nm;
     }
-    if (dl) {
-      const float inv = 1.f / den;
-      *reinterpret_cast<float4*>(a.out + (size_t)(kvh * n_rep + warp) * hd + d0) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
-    }
+    const float inv = 1.f / den;
+    const float4 r = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+    if (dl) *reinterpret_cast<float4*>(a.out + (size_t)(kvh * n_rep + warp) * hd + d0) = r;
+    if (a.xq_out) quant_block_8x4(r, lane & 7, (kvh * n_rep + warp) * 4 + (lane >> 3), XqDst(a.xq_out, a.n_heads));
   }
 }
 
@@ -277,10 +294,13 @@ __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const float* __r
 
 }  // namespace
 
-extern "C" int b200q_embed(const void* table, const int32_t* tokens, const int32_t* pos, float* x, int dim, int vocab, int flags, void* stream) {
+extern "C" int b200q_embed(const void* table, const int32_t* tokens, const int32_t* pos, float* x, int dim, int vocab, void* xq_out,
+                           const void* xq_norm_weight, float* ss_out, int flags, void* stream) {
   if (!table || !tokens || !pos || !x || dim <= 0 || vocab <= 0) return B200Q_ERR_BAD_ARG;
+  if ((uintptr_t)xq_out & 15) return B200Q_ERR_MISALIGNED;
+  if (xq_out && dim % 32) return B200Q_ERR_BAD_SHAPE;
   B200Q_CHECK_CUDA(launch_k(embed_kernel, dim3(ceil_div(dim, 256)), dim3(256), 0, (cudaStream_t)stream, (flags & B200Q_FLAG_PDL) != 0,
-                            (const __half*)table, tokens, pos, x, dim, vocab));
+                            (const __half*)table, tokens, pos, x, dim, vocab, xq_out, (const __half*)xq_norm_weight, ss_out));
   return B200Q_OK;
 }
 
@@ -303,6 +323,7 @@ extern "C" int b200q_attn_decode(const b200q_attn_args* a, void* stream) {
   if (a->head_dim <= 0 || a->head_dim > MAX_HD || a->head_dim % 8 || a->n_heads / a->n_kv_heads > MAX_REP) return B200Q_ERR_BAD_SHAPE;
   if (a->rope_dim < 0 || a->rope_dim > a->head_dim || a->rope_dim % 2) return B200Q_ERR_BAD_SHAPE;
   if (a->kv_dtype != B200Q_F16 && a->kv_dtype != B200Q_F32) return B200Q_ERR_BAD_ARG;
+  if (a->xq_out && (a->head_dim != 128 || ((uintptr_t)a->xq_out & 15))) return B200Q_ERR_BAD_SHAPE;   // one 128-wide group per head
   if (((uintptr_t)a->k_cache | (uintptr_t)a->v_cache | (uintptr_t)a->qkv | (uintptr_t)a->out | (uintptr_t)a->scratch) & 15) return B200Q_ERR_MISALIGNED;
   if ((int64_t)a->n_split * ATTN_CHUNK < a->max_context) return B200Q_ERR_BAD_SHAPE;   // the slices must cover the whole cache
   int n_rep = a->n_heads / a->n_kv_heads;

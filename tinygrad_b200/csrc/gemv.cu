@@ -22,6 +22,7 @@
 // Every mbarrier wait is bounded: on expiry the kernel raises a status word
 // (b200q_status_read_clear) and drains its copies instead of spinning.
 #include "common.cuh"
+#include "actquant.cuh"
 
 namespace {
 
@@ -35,19 +36,40 @@ struct GemvParams {
   int n_out, n_in, kgroups, n_row_tiles;
   int x_f16, y_f16, epilogue;
   float eps;
+  // activation hand-over between kernels (see actquant.cuh)
+  const void* xq_in;        // ready-made record of the input row (then x is not read)
+  const float* ss_in;       // partial sums of squares of the input row, for the fused RMSNorm
+  int ss_count;
+  void* xq_out;             // record of the OUTPUT row for the next GEMV
+  const __half* out_norm_w; // multiplied into the output before it is quantised (the next GEMV's norm weight)
+  float* ss_out;            // one partial sum of squares per 32 outputs
+  int unit, n_units;        // row tiles are dealt to CTAs in runs of `unit` (one run = 32 outputs when xq_out is set)
 };
 
-constexpr int CONS_WARPS = 8;
+// Tunables (overridable at compile time for experiments).
+#ifndef B200Q_CONS_WARPS
+#define B200Q_CONS_WARPS 16
+#endif
+#ifndef B200Q_STAGE_GROUPS
+#define B200Q_STAGE_GROUPS 32
+#endif
+#ifndef B200Q_NS_Q4
+#define B200Q_NS_Q4 2
+#endif
+#ifndef B200Q_CTAS_PER_SM
+#define B200Q_CTAS_PER_SM 2
+#endif
+constexpr int CONS_WARPS = B200Q_CONS_WARPS;
 constexpr int CONS_THREADS = CONS_WARPS * 32;
 constexpr int NTHREADS = CONS_THREADS + 32;      // + producer warp
-constexpr int STAGE_GROUPS = 16;                 // weight tiles (16 rows x 128 columns) per ring stage: two per consumer warp
+constexpr int STAGE_GROUPS = B200Q_STAGE_GROUPS; // weight tiles (16 rows x 128 columns) per ring stage
 constexpr int SPIN_LIMIT = 1 << 20;
 
 __device__ int g_status = 0;                     // sticky: 1 = an mbarrier wait ran out
 
 template <int QT> struct Cfg;
-template <> struct Cfg<B200Q_Q4_0> { static constexpr int NS = 4; };   // 4 x 18 KB ring
-template <> struct Cfg<B200Q_Q8_0> { static constexpr int NS = 2; };   // 2 x 34 KB ring
+template <> struct Cfg<B200Q_Q4_0> { static constexpr int NS = B200Q_NS_Q4; };   // ring depth (stage = STAGE_GROUPS x 1152 B)
+template <> struct Cfg<B200Q_Q8_0> { static constexpr int NS = 2; };   // stage = STAGE_GROUPS x 2176 B
 
 // ---- mbarrier / bulk-copy primitives -------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -60,16 +82,16 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {   // suspends the thread for a bounded, hardware-chosen time
   uint32_t ok;
-  asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
 // Bounded wait: false (and the status word set) if the phase did not complete in time.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (int i = 0; i < SPIN_LIMIT; i++) {
-    if (mbar_test(bar, parity)) return true;
-    if (i > 64) __nanosleep(64);
+    if (mbar_try(bar, parity)) return true;
+    if (i > 1024) __nanosleep(128);
   }
   atomicExch(&g_status, 1);
   return false;
@@ -81,6 +103,15 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 __device__ __forceinline__ void cons_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONS_THREADS) : "memory"); }
 
 // ---- tensor-core pieces ---------------------------------------------------------------
+// first MMA of a tile: accumulator input is zero (no register clears)
+template <int QT> __device__ __forceinline__ void imma0(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  if (QT == B200Q_Q4_0)
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+  else
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
 template <int QT> __device__ __forceinline__ void imma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1);
 template <> __device__ __forceinline__ void imma<B200Q_Q4_0>(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -97,60 +128,78 @@ template <> __device__ __forceinline__ void imma<B200Q_Q8_0>(int (&c)[4], uint32
 template <int QT>
 __device__ __forceinline__ void tile_mac(const uint8_t* tile, int lane, const uint4& bq0, const uint4& bq1, const float4& st, float& acc0, float& acc1) {
   const uint4* tp = reinterpret_cast<const uint4*>(tile);
-  int c[4] = {0, 0, 0, 0};
+  int c[4];
   uint2 sc;
   if (QT == B200Q_Q4_0) {
     // byte i of a block's 16 quant bytes = element i (low nibble) | element i+16 (high nibble)
     const uint4 r0 = tp[lane], r1 = tp[32 + lane];      // rows g and g+8
     sc = *(reinterpret_cast<const uint2*>(tile + 1024) + (2 * (lane >> 2) + (lane & 1)));
     const uint32_t M = 0x0F0F0F0Fu;
-    imma<QT>(c, r0.x & M, r1.x & M, (r0.x >> 4) & M, (r1.x >> 4) & M, bq0.x, bq0.y);
+    imma0<QT>(c, r0.x & M, r1.x & M, (r0.x >> 4) & M, (r1.x >> 4) & M, bq0.x, bq0.y);
     imma<QT>(c, r0.y & M, r1.y & M, (r0.y >> 4) & M, (r1.y >> 4) & M, bq0.z, bq0.w);
     imma<QT>(c, r0.z & M, r1.z & M, (r0.z >> 4) & M, (r1.z >> 4) & M, bq1.x, bq1.y);
     imma<QT>(c, r0.w & M, r1.w & M, (r0.w >> 4) & M, (r1.w >> 4) & M, bq1.z, bq1.w);
   } else {
     const uint4 r0 = tp[lane], r1 = tp[32 + lane], r2 = tp[64 + lane], r3 = tp[96 + lane];   // row g: r0,r1; row g+8: r2,r3
     sc = *(reinterpret_cast<const uint2*>(tile + 2048) + (2 * (lane >> 2) + (lane & 1)));
-    imma<QT>(c, r0.x, r2.x, r0.y, r2.y, bq0.x, bq0.y);
-    imma<QT>(c, r0.z, r2.z, r0.w, r2.w, bq0.z, bq0.w);
-    imma<QT>(c, r1.x, r3.x, r1.y, r3.y, bq1.x, bq1.y);
-    imma<QT>(c, r1.z, r3.z, r1.w, r3.w, bq1.z, bq1.w);
+    // same B word order as Q4_0: MMA j pairs elements 4j..4j+3 with 16+4j..16+4j+3
+    imma0<QT>(c, r0.x, r2.x, r1.x, r3.x, bq0.x, bq0.y);
+    imma<QT>(c, r0.y, r2.y, r1.y, r3.y, bq0.z, bq0.w);
+    imma<QT>(c, r0.z, r2.z, r1.z, r3.z, bq1.x, bq1.y);
+    imma<QT>(c, r0.w, r2.w, r1.w, r3.w, bq1.z, bq1.w);
   }
   const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&sc.x)), d1 = __half22float2(*reinterpret_cast<const __half2*>(&sc.y));
-  const float v0 = fmaf((float)c[0], st.x, -st.y), v1 = fmaf((float)c[1], st.z, -st.w);
-  const float v2 = fmaf((float)c[2], st.x, -st.y), v3 = fmaf((float)c[3], st.z, -st.w);
+  const float oa = QT == B200Q_Q4_0 ? st.y : 0.f, ob = QT == B200Q_Q4_0 ? st.w : 0.f;   // only Q4_0 stores value + 8
+  const float v0 = fmaf((float)c[0], st.x, -oa), v1 = fmaf((float)c[1], st.z, -ob);
+  const float v2 = fmaf((float)c[2], st.x, -oa), v3 = fmaf((float)c[3], st.z, -ob);
   acc0 = fmaf(v0, d0.x, fmaf(v1, d0.y, acc0));
   acc1 = fmaf(v2, d1.x, fmaf(v3, d1.y, acc1));
 }
 
 // Shared-memory plan (dynamic):
 //   ring   [NS][STAGE_GROUPS * tile_bytes]        weight tiles as they sit in HBM
-//   xq     [kgroups][2][8] uint4                  B operands: per tile, lane g (block g%4, digit g/4), 8 words in MMA order
-//   xsc    [kgroups][2][2] float4                 per (digit, block pair): {scale_A, offset_A, scale_B, offset_B}
+//   xq,xsc the activation record of actquant.cuh  (kgroups * 320 bytes)
 //   zero   uint4                                  B operand of the lanes off the diagonal
 //   red    [2][CONS_WARPS][16] float              cross-warp partial sums, double-buffered over row tiles
 //   ssq    [CONS_WARPS] float
-//   bars   full[NS], empty[NS]
+//   ubuf   [32] float                             the 32 finished outputs of a run, before they are quantised for the next GEMV
+//   bars   full[NS], empty[NS], xbar
 //   abort  int                                    set by a consumer warp whose wait ran out; all warps leave at the next row tile
-template <int QT>
-__global__ void __launch_bounds__(NTHREADS, 2) qgemv_kernel(const GemvParams p) {
+// Hands the 32 finished outputs of a run to the next GEMV already quantised (block index = run index).
+// Kept out of line: it runs once per 32 outputs and must not weigh on the register budget of the MMA loop.
+__device__ __noinline__ void emit_output_record(const GemvParams& p, const float* ubuf, int unit, int lane) {
+  const float u = ubuf[lane];
+  if (p.ss_out) {
+    const float s2 = warp_sum(u * u);
+    if (lane == 0) p.ss_out[unit] = s2;
+  }
+  const float uq = p.out_norm_w ? u * __half2float(p.out_norm_w[unit * 32 + lane]) : u;
+  quant_block_32x1(uq, lane, unit, XqDst(p.xq_out, p.n_out / GROUP_ELEMS));
+}
+
+// XQ_IN / XQ_OUT: compiled-in use of a ready-made input record / production of an output record.
+template <int QT, bool XQ_IN, bool XQ_OUT>
+__global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(const GemvParams p) {
   constexpr int NS = Cfg<QT>::NS, TB = tile_bytes(QT), STAGE_BYTES = STAGE_GROUPS * TB;
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* ring = smem;
-  uint4* xq = reinterpret_cast<uint4*>(smem + NS * STAGE_BYTES);
-  float4* xsc = reinterpret_cast<float4*>(xq + (size_t)p.kgroups * 16);
-  uint4* zero = reinterpret_cast<uint4*>(xsc + (size_t)p.kgroups * 4);
+  unsigned char* record = smem + NS * STAGE_BYTES;
+  const uint4* xq = reinterpret_cast<const uint4*>(record);
+  const float4* xsc = reinterpret_cast<const float4*>(record + (size_t)p.kgroups * 256);
+  uint4* zero = reinterpret_cast<uint4*>(record + (size_t)p.kgroups * XQ_GROUP_BYTES);
   float* red = reinterpret_cast<float*>(zero + 1);
   float* ssq = red + 2 * CONS_WARPS * 16;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ssq + CONS_WARPS);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 2 * NS);
-  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + NS);
+  float* ubuf = ssq + CONS_WARPS;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ubuf + 32);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 2 * NS + 1);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + NS), xbar = smem_u32(bars + 2 * NS);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int m = blockIdx.y;
   const int stages_per_tile = (p.kgroups + STAGE_GROUPS - 1) / STAGE_GROUPS;
 
   if (tid == 0) {
     for (int s = 0; s < NS; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, CONS_WARPS); }
+    mbar_init(xbar, 1);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -161,36 +210,62 @@ __global__ void __launch_bounds__(NTHREADS, 2) qgemv_kernel(const GemvParams p) 
     // ------------------------------ producer ------------------------------
     if (lane == 0) {
       int it = 0;
-      bool ok = true;
-      for (int rt = blockIdx.x; rt < p.n_row_tiles && ok; rt += gridDim.x) {
-        const uint8_t* src = p.w + (size_t)rt * p.kgroups * TB;
-        for (int s = 0; s < stages_per_tile; s++, it++) {
-          const int slot = it % NS, groups = min(STAGE_GROUPS, p.kgroups - s * STAGE_GROUPS);
-          // The first NS fills need no consumer.  After them the consumers must be running, and they start
-          // only when the previous kernel has finished: wait for it here, outside the bounded wait.
-          if (it == NS) pdl_wait();
-          if (!mbar_wait(empty0 + 8 * slot, ((it / NS) & 1) ^ 1)) { ok = false; break; }
-          mbar_expect_tx(full0 + 8 * slot, groups * TB);
-          bulk_g2s(smem_u32(ring + slot * STAGE_BYTES), src + (size_t)s * STAGE_BYTES, groups * TB, full0 + 8 * slot);
+      bool ok = true, x_issued = false;
+      // The first NS fills need no consumer.  After them the consumers must be running, and they start only when the
+      // previous kernel has finished: wait for it outside the bounded waits, then fetch the activation record it left.
+      auto after_prefetch = [&]() {
+        pdl_wait();
+        if (XQ_IN) {
+          const uint32_t bytes = (uint32_t)p.kgroups * XQ_GROUP_BYTES;
+          mbar_expect_tx(xbar, bytes);
+          bulk_g2s(smem_u32(record), p.xq_in, bytes, xbar);
+        }
+        x_issued = true;
+      };
+      const int run = XQ_OUT ? p.unit : 1;
+      for (int unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x) {
+        for (int ti = 0; ti < run && ok; ti++) {
+          const int rt = unit * run + ti;
+          if (rt >= p.n_row_tiles) break;
+          const uint8_t* src = p.w + (size_t)rt * p.kgroups * TB;
+          for (int s = 0; s < stages_per_tile; s++, it++) {
+            const int slot = it % NS, groups = min(STAGE_GROUPS, p.kgroups - s * STAGE_GROUPS);
+            if (it == NS && !x_issued) after_prefetch();
+            if (!mbar_wait(empty0 + 8 * slot, ((it / NS) & 1) ^ 1)) { ok = false; break; }
+            mbar_expect_tx(full0 + 8 * slot, groups * TB);
+            bulk_g2s(smem_u32(ring + slot * STAGE_BYTES), src + (size_t)s * STAGE_BYTES, groups * TB, full0 + 8 * slot);
+          }
         }
       }
+      if (!x_issued) after_prefetch();
       // nothing may still be landing in this CTA's shared memory when it exits
       for (int j = max(0, it - NS); j < it; j++) mbar_wait(full0 + 8 * (j % NS), (j / NS) & 1);
+      if (XQ_IN) mbar_wait(xbar, 0);
+    } else {
+      pdl_wait();   // keep launch order transitive: this grid is not complete before its predecessor
     }
-    pdl_wait();     // keep launch order transitive: this grid is not complete before its predecessor
     return;
   }
 
   // -------------------------------- consumers --------------------------------
   pdl_wait();
   const int g = lane >> 2, t = lane & 3;
-  {
-    // stage the activation row: 8 threads per block of 32, 4 elements each
-    if (tid == 0) *zero = make_uint4(0, 0, 0, 0);
+  // warp 0 finishes every row tile: fetch the addends of the CTA's first tile now, so their latency hides behind the MMAs
+  float pre_add = 0.f;
+  const int first_rt = blockIdx.x * (XQ_OUT ? p.unit : 1);
+  if (warp == 0 && lane < 16 && p.epilogue == B200Q_EPI_LINEAR && first_rt * 16 + lane < p.n_out) {
+    if (p.residual) pre_add = p.residual[(size_t)m * p.n_out + first_rt * 16 + lane];
+    if (p.bias) pre_add += __half2float(p.bias[first_rt * 16 + lane]);
+  }
+  if (tid == 0) *zero = make_uint4(0, 0, 0, 0);
+  float ss = 0.f;
+  if (XQ_IN) {
+    // the row arrives quantised (the producer thread copies the record); only the RMSNorm scalar is computed here
+    if (p.norm_w) for (int i = tid; i < p.ss_count; i += CONS_THREADS) ss += p.ss_in[i];
+  } else {
+    // quantise the activation row here: 8 threads per block of 32, 4 elements each
     const int nblk_pad = p.kgroups * 4, q = tid & 7;
-    uint32_t* xw = reinterpret_cast<uint32_t*>(xq);
-    float* sw = reinterpret_cast<float*>(xsc);
-    float ss = 0.f;
+    const XqDst dst(record, p.kgroups);
     for (int b = tid >> 3; b < nblk_pad; b += CONS_THREADS / 8) {
       const int k = b * 32 + 4 * q;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -209,39 +284,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) qgemv_kernel(const GemvParams p) 
           v.x *= a.x; v.y *= a.y; v.z *= c.x; v.w *= c.y;
         }
       }
-      float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-      const bool live = amax > 0.f && amax < INFINITY;
-      const float inv = live ? 16256.f / amax : 0.f, s = live ? amax / 16256.f : 0.f;
-      const int i0 = __float2int_rn(v.x * inv), i1 = __float2int_rn(v.y * inv), i2 = __float2int_rn(v.z * inv), i3 = __float2int_rn(v.w * inv);
-      int xsum = i0 + i1 + i2 + i3;
-      xsum += __shfl_xor_sync(0xffffffffu, xsum, 1);
-      xsum += __shfl_xor_sync(0xffffffffu, xsum, 2);
-      xsum += __shfl_xor_sync(0xffffffffu, xsum, 4);
-      const int h0 = (i0 + 64) >> 7, h1 = (i1 + 64) >> 7, h2 = (i2 + 64) >> 7, h3 = (i3 + 64) >> 7;   // value = 128 * hi + lo, lo in [-64, 63]
-      const uint32_t hiw = (h0 & 0xFF) | ((h1 & 0xFF) << 8) | ((h2 & 0xFF) << 16) | ((uint32_t)(h3 & 0xFF) << 24);
-      const uint32_t low = ((i0 - (h0 << 7)) & 0xFF) | (((i1 - (h1 << 7)) & 0xFF) << 8) | (((i2 - (h2 << 7)) & 0xFF) << 16) |
-                           ((uint32_t)((i3 - (h3 << 7)) & 0xFF) << 24);
-      // word position in the block's MMA order: Q4_0 word j feeds MMA j with elements {4j..4j+3 | 16+4j..}, Q8_0 is in element order
-      const int r = QT == B200Q_Q4_0 ? ((q & 3) * 2 + (q >> 2)) : q;
-      const int j = b >> 2, tb = b & 3;
-      xw[((j * 2 + (r >> 2)) * 8 + tb) * 4 + (r & 3)] = hiw;
-      xw[((j * 2 + (r >> 2)) * 8 + tb + 4) * 4 + (r & 3)] = low;
-      if (q == 0) {
-        const int pr = tb >> 1, sl = (tb & 1) * 2;
-        sw[((j * 2 + 0) * 2 + pr) * 4 + sl] = 128.f * s;
-        sw[((j * 2 + 0) * 2 + pr) * 4 + sl + 1] = QT == B200Q_Q4_0 ? 8.f * s * (float)xsum : 0.f;
-        sw[((j * 2 + 1) * 2 + pr) * 4 + sl] = s;
-        sw[((j * 2 + 1) * 2 + pr) * 4 + sl + 1] = 0.f;
-      }
-    }
-    if (p.norm_w) {
-      ss = warp_sum(ss);
-      if (lane == 0) ssq[warp] = ss;
+      quant_block_8x4(v, q, b, dst);
     }
   }
+  if (p.norm_w) {
+    ss = warp_sum(ss);
+    if (lane == 0) ssq[warp] = ss;
+  }
+  if (XQ_IN && !mbar_wait(xbar, 0)) *s_abort = 1;
   cons_bar_sync();
   float rs = 1.f;
   if (p.norm_w) {
@@ -252,68 +302,86 @@ __global__ void __launch_bounds__(NTHREADS, 2) qgemv_kernel(const GemvParams p) 
   }
   const bool diag = (t == (g & 3));
   int it = 0, par = 0;
-  for (int rt = blockIdx.x; rt < p.n_row_tiles; rt += gridDim.x, par ^= 1) {
-    float acc0 = 0.f, acc1 = 0.f;
-    for (int s = 0; s < stages_per_tile; s++, it++) {
-      const int slot = it % NS, groups = min(STAGE_GROUPS, p.kgroups - s * STAGE_GROUPS);
-      if (!mbar_wait(full0 + 8 * slot, (it / NS) & 1)) { *s_abort = 1; break; }
-      const uint8_t* stage = ring + slot * STAGE_BYTES;
+  bool live = *s_abort == 0;
+  const int run = XQ_OUT ? p.unit : 1;
+  for (int unit = blockIdx.x; unit < p.n_units && live; unit += gridDim.x) {
+    for (int ti = 0; ti < run; ti++, par ^= 1) {
+      const int rt = unit * run + ti;
+      if (rt >= p.n_row_tiles) break;
+      float acc0 = 0.f, acc1 = 0.f;
+      for (int s = 0; s < stages_per_tile; s++, it++) {
+        const int slot = it % NS, groups = min(STAGE_GROUPS, p.kgroups - s * STAGE_GROUPS);
+        if (!mbar_wait(full0 + 8 * slot, (it / NS) & 1)) { *s_abort = 1; break; }
+        const uint8_t* stage = ring + slot * STAGE_BYTES;
 #pragma unroll
-      for (int u = 0; u < STAGE_GROUPS / CONS_WARPS; u++) {
-        const int gi = warp + u * CONS_WARPS;
-        if (gi < groups) {
-          const int j = s * STAGE_GROUPS + gi;
-          const uint4 bq0 = diag ? xq[(j * 2 + 0) * 8 + g] : *zero, bq1 = diag ? xq[(j * 2 + 1) * 8 + g] : *zero;
-          const float4 st = xsc[(j * 2 + (t >> 1)) * 2 + (t & 1)];
-          tile_mac<QT>(stage + gi * TB, lane, bq0, bq1, st, acc0, acc1);
+        for (int u = 0; u < STAGE_GROUPS / CONS_WARPS; u++) {
+          const int gi = warp + u * CONS_WARPS;
+          if (gi < groups) {
+            const int j = s * STAGE_GROUPS + gi;
+            const uint4 bq0 = diag ? xq[(j * 2 + 0) * 8 + g] : *zero, bq1 = diag ? xq[(j * 2 + 1) * 8 + g] : *zero;
+            const float4 st = xsc[(j * 2 + (t >> 1)) * 2 + (t & 1)];
+            tile_mac<QT>(stage + gi * TB, lane, bq0, bq1, st, acc0, acc1);
+          }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * slot);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty0 + 8 * slot);
-    }
-    // quad lanes hold the columns {blocks 0,1 hi}, {2,3 hi}, {0,1 lo}, {2,3 lo}: add them
-    acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1); acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
-    acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1); acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
-    float* rb = red + par * CONS_WARPS * 16;
-    if (t == 0) { rb[warp * 16 + g] = acc0; rb[warp * 16 + 8 + g] = acc1; }
-    cons_bar_sync();
-    const bool ok = *s_abort == 0;      // uniform over the consumer warps: read after the barrier that follows every write
-    if (!ok) break;
-    if (warp == 0) {
-      float v = 0.f;
-      if (lane < 16) {
+      // quad lanes hold the columns {blocks 0,1 hi}, {2,3 hi}, {0,1 lo}, {2,3 lo}: add them
+      acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1); acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+      acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1); acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+      float* rb = red + par * CONS_WARPS * 16;
+      if (t == 0) { rb[warp * 16 + g] = acc0; rb[warp * 16 + 8 + g] = acc1; }
+      cons_bar_sync();
+      live = *s_abort == 0;      // uniform over the consumer warps: read after the barrier that follows every write
+      if (!live) break;
+      if (warp == 0) {
+        float v = 0.f;
+        if (lane < 16) {
 #pragma unroll
-        for (int w = 0; w < CONS_WARPS; w++) v += rb[w * 16 + lane];
-        v *= rs;
-      }
-      if (p.epilogue == B200Q_EPI_LINEAR) {
-        const int row = rt * 16 + lane;
-        if (lane < 16 && row < p.n_out && ok) {
-          if (p.bias) v += __half2float(p.bias[row]);
-          if (p.residual) v += p.residual[(size_t)m * p.n_out + row];
-          if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(v);
-          else reinterpret_cast<float*>(p.y)[(size_t)m * p.n_out + row] = v;
+          for (int w = 0; w < CONS_WARPS; w++) v += rb[w * 16 + lane];
+          v *= rs;
         }
-      } else {
-        const float up = __shfl_down_sync(0xffffffffu, v, 8);     // rows 8..15 of the tile are the `up` rows
-        const int row = rt * 8 + lane;
-        if (lane < 8 && row < p.n_out && ok) {
+        if (p.epilogue == B200Q_EPI_LINEAR) {
+          const int row = rt * 16 + lane;
+          if (lane < 16 && row < p.n_out) {
+            if (rt == first_rt) v += pre_add;
+            else {
+              if (p.bias) v += __half2float(p.bias[row]);
+              if (p.residual) v += p.residual[(size_t)m * p.n_out + row];
+            }
+            if (p.y) {
+              if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(v);
+              else reinterpret_cast<float*>(p.y)[(size_t)m * p.n_out + row] = v;
+            }
+          }
+          if (XQ_OUT && lane < 16) ubuf[ti * 16 + lane] = v;
+        } else {
+          const float up = __shfl_down_sync(0xffffffffu, v, 8);     // rows 8..15 of the tile are the `up` rows
+          const int row = rt * 8 + lane;
           const float o = (v / (1.f + __expf(-v))) * up;
-          if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(o);
-          else reinterpret_cast<float*>(p.y)[(size_t)m * p.n_out + row] = o;
+          if (lane < 8 && row < p.n_out && p.y) {
+            if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(o);
+            else reinterpret_cast<float*>(p.y)[(size_t)m * p.n_out + row] = o;
+          }
+          if (XQ_OUT && lane < 8) ubuf[ti * 8 + lane] = o;
+        }
+        if (XQ_OUT && ti == run - 1) {
+          __syncwarp();
+          emit_output_record(p, ubuf, unit, lane);     // the run's 32 outputs are complete
+          __syncwarp();
         }
       }
     }
   }
 }
 
-template <int QT>
+template <int QT, bool XQ_IN, bool XQ_OUT>
 int launch_gemv(const b200q_gemv_args* a, const GemvParams& p, cudaStream_t stream) {
   constexpr int NS = Cfg<QT>::NS;
-  const size_t smem = (size_t)NS * STAGE_GROUPS * tile_bytes(QT) + (size_t)p.kgroups * (16 * 16 + 4 * 16) + 16 +
-                      (2 * CONS_WARPS * 16 + CONS_WARPS) * sizeof(float) + 2 * NS * sizeof(uint64_t) + 16;
+  const size_t smem = (size_t)NS * STAGE_GROUPS * tile_bytes(QT) + (size_t)p.kgroups * XQ_GROUP_BYTES + 16 +
+                      (2 * CONS_WARPS * 16 + CONS_WARPS + 32) * sizeof(float) + (2 * NS + 1) * sizeof(uint64_t) + 16;
   if (smem > 220 * 1024) return B200Q_ERR_TOO_LARGE;
-  auto kern = qgemv_kernel<QT>;
+  auto kern = qgemv_kernel<QT, XQ_IN, XQ_OUT>;
   static int sm_count = 0, occ_cache_smem = -1, occ_cache = 0;
   if (sm_count == 0) {
     int dev; B200Q_CHECK_CUDA(cudaGetDevice(&dev));
@@ -326,7 +394,7 @@ int launch_gemv(const b200q_gemv_args* a, const GemvParams& p, cudaStream_t stre
     occ_cache_smem = (int)smem;
   }
   const int max_ctas = a->max_ctas > 0 ? a->max_ctas : occ_cache * sm_count;
-  const int grid_x = p.n_row_tiles < max_ctas ? p.n_row_tiles : max_ctas;
+  const int grid_x = p.n_units < max_ctas ? p.n_units : max_ctas;
   B200Q_CHECK_CUDA(launch_k(kern, dim3(grid_x, a->m), dim3(NTHREADS), smem, stream, (a->flags & B200Q_FLAG_PDL) != 0, p));
   return B200Q_OK;
 }
@@ -341,8 +409,10 @@ extern "C" int b200q_status_read_clear(int* status) {
   return B200Q_OK;
 }
 
+extern "C" size_t b200q_xq_bytes(int n) { return n > 0 ? xq_record_bytes(n) : 0; }
+
 extern "C" int b200q_gemv(const b200q_gemv_args* a, void* stream) {
-  if (!a || !a->w_packed || !a->x || !a->y) return B200Q_ERR_BAD_ARG;
+  if (!a || !a->w_packed || (!a->x && !a->xq_in) || (!a->y && !a->xq_out)) return B200Q_ERR_BAD_ARG;
   if (a->qtype == B200Q_Q6_K) return B200Q_ERR_UNSUPPORTED;
   if (a->qtype != B200Q_Q4_0 && a->qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
   if (a->n_out <= 0 || a->n_in <= 0 || a->m <= 0 || a->m > 65535) return B200Q_ERR_BAD_ARG;
@@ -352,14 +422,28 @@ extern "C" int b200q_gemv(const b200q_gemv_args* a, void* stream) {
   if (a->epilogue == B200Q_EPI_SILU_MUL && (a->bias || a->residual)) return B200Q_ERR_UNSUPPORTED;
   if ((uintptr_t)a->w_packed & 15) return B200Q_ERR_MISALIGNED;
   // activation rows are read 4 elements at a time
-  if (((uintptr_t)a->x & (a->x_dtype == B200Q_F32 ? 15 : 7)) || ((uintptr_t)a->y & (a->y_dtype == B200Q_F32 ? 3 : 1))) return B200Q_ERR_MISALIGNED;
+  if (a->x && ((uintptr_t)a->x & (a->x_dtype == B200Q_F32 ? 15 : 7))) return B200Q_ERR_MISALIGNED;
+  if (a->y && ((uintptr_t)a->y & (a->y_dtype == B200Q_F32 ? 3 : 1))) return B200Q_ERR_MISALIGNED;
   if (a->norm_weight && ((uintptr_t)a->norm_weight & 7)) return B200Q_ERR_MISALIGNED;
+  if (((uintptr_t)a->xq_in | (uintptr_t)a->xq_out) & 15) return B200Q_ERR_MISALIGNED;
+  if ((a->xq_in || a->xq_out) && a->m != 1) return B200Q_ERR_UNSUPPORTED;
+  if (a->xq_in && a->norm_weight && (!a->ss_in || a->ss_count <= 0)) return B200Q_ERR_BAD_ARG;   // the norm weight is already inside the record
+  if (a->xq_out && a->n_out % GROUP_ELEMS) return B200Q_ERR_BAD_SHAPE;
   GemvParams p;
   p.w = (const uint8_t*)a->w_packed; p.x = a->x; p.norm_w = (const __half*)a->norm_weight; p.bias = (const __half*)a->bias;
   p.residual = (const float*)a->residual; p.y = a->y;
   p.n_out = a->n_out; p.n_in = a->n_in; p.kgroups = ceil_div(a->n_in, GROUP_ELEMS);
   p.n_row_tiles = a->epilogue == B200Q_EPI_SILU_MUL ? ceil_div(a->n_out, 8) : ceil_div(a->n_out, TILE_ROWS);
   p.x_f16 = a->x_dtype == B200Q_F16; p.y_f16 = a->y_dtype == B200Q_F16; p.epilogue = a->epilogue; p.eps = a->norm_eps;
-  if (a->qtype == B200Q_Q4_0) return launch_gemv<B200Q_Q4_0>(a, p, (cudaStream_t)stream);
-  return launch_gemv<B200Q_Q8_0>(a, p, (cudaStream_t)stream);
+  p.xq_in = a->xq_in; p.ss_in = a->ss_in; p.ss_count = a->ss_count;
+  p.xq_out = a->xq_out; p.out_norm_w = (const __half*)a->xq_out_norm_weight; p.ss_out = a->ss_out;
+  p.unit = a->xq_out ? (a->epilogue == B200Q_EPI_SILU_MUL ? 4 : 2) : 1;
+  p.n_units = ceil_div(p.n_row_tiles, p.unit);
+  const bool xi = a->xq_in != nullptr, xo = a->xq_out != nullptr;
+  if (a->qtype == B200Q_Q4_0) {
+    if (xi) return xo ? launch_gemv<B200Q_Q4_0, true, true>(a, p, (cudaStream_t)stream) : launch_gemv<B200Q_Q4_0, true, false>(a, p, (cudaStream_t)stream);
+    return xo ? launch_gemv<B200Q_Q4_0, false, true>(a, p, (cudaStream_t)stream) : launch_gemv<B200Q_Q4_0, false, false>(a, p, (cudaStream_t)stream);
+  }
+  if (xi) return xo ? launch_gemv<B200Q_Q8_0, true, true>(a, p, (cudaStream_t)stream) : launch_gemv<B200Q_Q8_0, true, false>(a, p, (cudaStream_t)stream);
+  return xo ? launch_gemv<B200Q_Q8_0, false, true>(a, p, (cudaStream_t)stream) : launch_gemv<B200Q_Q8_0, false, false>(a, p, (cudaStream_t)stream);
 }

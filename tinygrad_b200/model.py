@@ -45,9 +45,13 @@ class _Block:
   pass
 
 
+# hand-over edges used when the caller does not choose (see Transformer.__init__): the ones that measured faster
+DEFAULT_HANDOVER = ("attn_o",)
+
+
 class Transformer:
   def __init__(self, config: TransformerConfig, state_dict: dict, ggml_type: int = _lib.Q4_0, n_split: int = 0, use_pdl: bool = True,
-               use_graph: bool = True, gemv_max_ctas: int = 0):
+               use_graph: bool = True, gemv_max_ctas: int = 0, handover=None):
     """state_dict: the reference's tensor names -> numpy arrays; Linear weights as raw
     GGUF block bytes (uint8), embeddings / norms / biases as fp16."""
     c = self.config = config
@@ -99,30 +103,64 @@ class Transformer:
     self.pos = DeviceBuffer.empty((1,), np.int32, zero=True)
     self.attn_scratch = DeviceBuffer(_lib.load().b200q_attn_scratch_bytes(c.n_heads, c.n_kv_heads, c.head_dim, self.n_split), zero=True)
     self.argmax_scratch = DeviceBuffer(_lib.load().b200q_argmax_scratch_bytes(), zero=True)
+    # Quantised activation hand-over between consecutive kernels (needs whole 128-wide groups everywhere).  Each edge of
+    # the chain can be switched on its own: attn_o (attention -> output projection), o_gateup, gateup_down, down_qkv.
+    can = c.head_dim == 128 and c.dim % 128 == 0 and c.hidden_dim % 128 == 0 and self.q_dim % 128 == 0
+    all_edges = ("attn_o", "o_gateup", "gateup_down", "down_qkv")
+    if handover is None: edges = DEFAULT_HANDOVER
+    elif isinstance(handover, str): edges = tuple(e for e in handover.split(",") if e)
+    else: edges = all_edges if handover else ()
+    assert all(e in all_edges for e in edges), f"unknown hand-over edge in {edges}"
+    self.edges = frozenset(edges) if can else frozenset()
+    self.handover = bool(self.edges)
+    xqb = _lib.load().b200q_xq_bytes
+    if "down_qkv" in self.edges: self.xq_a, self.ss_a = DeviceBuffer(xqb(c.dim), zero=True), DeviceBuffer.empty((c.dim // 32,), np.float32, zero=True)
+    if "o_gateup" in self.edges: self.xq_b, self.ss_b = DeviceBuffer(xqb(c.dim), zero=True), DeviceBuffer.empty((c.dim // 32,), np.float32, zero=True)
+    if "attn_o" in self.edges: self.xq_attn = DeviceBuffer(xqb(self.q_dim), zero=True)
+    if "gateup_down" in self.edges: self.xq_act = DeviceBuffer(xqb(c.hidden_dim), zero=True)
     self._graphs = {}
     self._cached_tokens: list = []
     self.launches_per_step = 5 * c.num_blocks + 3
 
   # ---- one token through the network (launch sequence; captured into a graph) ----
-  def _enqueue_step(self, with_head: bool) -> None:
+  def _enqueue_step(self, with_head: bool, attention: bool = True, tail: bool = True) -> None:
     c, lib, s, fl = self.config, _lib.load(), self.stream.ptr, self.flags
     kvdt = F16 if c.kv_dtype == "float16" else F32
-    check(lib.b200q_embed(self.token_embd.ptr, self.tokens.ptr, self.pos.ptr, self.x.ptr, c.dim, c.vocab_size, fl, s))
-    for b in self.blk:
-      quant.gemv(b.qkv.ptr, self.qtype, self.q_dim + 2 * self.kv_dim, c.dim, self.x, self.qkv, norm_weight=b.attn_norm, norm_eps=c.norm_eps,
-                 bias=b.qkv_bias, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
-      a = _lib.AttnArgs(self.qkv.ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, self.pos.ptr, self.attn.ptr, self.attn_scratch.ptr,
-                        c.n_heads, c.n_kv_heads, c.head_dim, c.rope_dim, c.max_context, self.n_split, fl)
-      check(lib.b200q_attn_decode(ctypes.byref(a), s))
-      quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, self.attn, self.x, residual=self.x, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
-      quant.gemv(b.gate_up.buf.ptr, self.qtype, c.hidden_dim, c.dim, self.x, self.act, norm_weight=b.ffn_norm, norm_eps=c.norm_eps,
-                 epilogue=EPI_SILU_MUL, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
-      quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, self.act, self.x, residual=self.x, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
+    kw = dict(flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
+    e, nss = self.edges, c.dim // 32
+    qkv_rows = self.q_dim + 2 * self.kv_dim
+    # the four hand-over edges: kwargs of the consuming (xq_in...) and of the producing (xq_out...) launch
+    in_a = dict(xq_in=self.xq_a, ss_in=self.ss_a, ss_count=nss) if "down_qkv" in e else {}
+    in_b = dict(xq_in=self.xq_b, ss_in=self.ss_b, ss_count=nss) if "o_gateup" in e else {}
+    in_attn = dict(xq_in=self.xq_attn) if "attn_o" in e else {}
+    in_act = dict(xq_in=self.xq_act) if "gateup_down" in e else {}
+    if attention or tail:
+      ho = "down_qkv" in e
+      check(lib.b200q_embed(self.token_embd.ptr, self.tokens.ptr, self.pos.ptr, self.x.ptr, c.dim, c.vocab_size,
+                            self.xq_a.ptr if ho else None, self.blk[0].attn_norm.ptr if ho else None, self.ss_a.ptr if ho else None, fl, s))
+    for i, b in enumerate(self.blk):
+      nxt_norm = self.blk[i + 1].attn_norm if i + 1 < len(self.blk) else self.output_norm
+      out_b = dict(xq_out=self.xq_b, xq_out_norm_weight=b.ffn_norm, ss_out=self.ss_b) if "o_gateup" in e else {}
+      out_act = dict(xq_out=self.xq_act) if "gateup_down" in e else {}
+      out_a = dict(xq_out=self.xq_a, xq_out_norm_weight=nxt_norm, ss_out=self.ss_a) if "down_qkv" in e else {}
+      quant.gemv(b.qkv.ptr, self.qtype, qkv_rows, c.dim, None if in_a else self.x, self.qkv, norm_weight=b.attn_norm, norm_eps=c.norm_eps,
+                 bias=b.qkv_bias, **in_a, **kw)
+      if attention:
+        a = _lib.AttnArgs(self.qkv.ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, self.pos.ptr, self.attn.ptr, self.attn_scratch.ptr,
+                          c.n_heads, c.n_kv_heads, c.head_dim, c.rope_dim, c.max_context, self.n_split, fl,
+                          self.xq_attn.ptr if "attn_o" in e else None)
+        check(lib.b200q_attn_decode(ctypes.byref(a), s))
+      quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, None if in_attn else self.attn, self.x, residual=self.x,
+                 **in_attn, **out_b, **kw)
+      quant.gemv(b.gate_up.buf.ptr, self.qtype, c.hidden_dim, c.dim, None if in_b else self.x, None if out_act else self.act,
+                 norm_weight=b.ffn_norm, norm_eps=c.norm_eps, epilogue=EPI_SILU_MUL, **in_b, **out_act, **kw)
+      quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, None if in_act else self.act, self.x, residual=self.x,
+                 **in_act, **out_a, **kw)
     if with_head:
-      quant.gemv(self.output.buf.ptr, self.qtype, c.vocab_size, c.dim, self.x, self.logits, norm_weight=self.output_norm, norm_eps=c.norm_eps,
-                 flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
-      check(lib.b200q_argmax_advance(self.logits.ptr, c.vocab_size, self.tokens.ptr, self.pos.ptr, self.argmax_scratch.ptr, fl, s))
-    else:
+      quant.gemv(self.output.buf.ptr, self.qtype, c.vocab_size, c.dim, None if in_a else self.x, self.logits, norm_weight=self.output_norm,
+                 norm_eps=c.norm_eps, **in_a, **kw)
+      if tail: check(lib.b200q_argmax_advance(self.logits.ptr, c.vocab_size, self.tokens.ptr, self.pos.ptr, self.argmax_scratch.ptr, fl, s))
+    elif tail:
       check(lib.b200q_advance(self.pos.ptr, fl, s))
 
   def gemv_launches(self) -> list:
@@ -134,18 +172,8 @@ class Transformer:
   def gemv_only_graph(self) -> Graph:
     """The GEMV launches of one step alone, in order, for timing the weight stream by itself
     (it overwrites the activation buffers: use it after the real steps)."""
-    c, s, fl = self.config, self.stream.ptr, self.flags
     g = Graph(self.stream)
-    with g:
-      for b in self.blk:
-        quant.gemv(b.qkv.ptr, self.qtype, self.q_dim + 2 * self.kv_dim, c.dim, self.x, self.qkv, norm_weight=b.attn_norm, norm_eps=c.norm_eps,
-                   bias=b.qkv_bias, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
-        quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, self.attn, self.x, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
-        quant.gemv(b.gate_up.buf.ptr, self.qtype, c.hidden_dim, c.dim, self.x, self.act, norm_weight=b.ffn_norm, norm_eps=c.norm_eps,
-                   epilogue=EPI_SILU_MUL, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
-        quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, self.act, self.x, flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
-      quant.gemv(self.output.buf.ptr, self.qtype, c.vocab_size, c.dim, self.x, self.logits, norm_weight=self.output_norm, norm_eps=c.norm_eps,
-                 flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
+    with g: self._enqueue_step(with_head=True, attention=False, tail=False)
     return g
 
   def step(self, with_head: bool = True) -> None:
