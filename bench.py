@@ -283,7 +283,8 @@ def main():
                     "l2": "inputs larger than L2 (4.2 GB of weights per step vs 126 MB)", "pdl": not args.no_pdl, "n_split": model.n_split, "activation_handover": sorted(model.edges),
                     "step_hbm_gbs": step_bytes / (ms_dev / args.steps * 1e-3) / 1e9, "step_frac_of_peak": step_bytes / (ms_dev / args.steps * 1e-3) / 1e9 / peak,
                     "model_build_s": round(t_build, 1)},
-         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": 1.007 * gemv_bytes / len(launches),
+                      "traffic_source": "ncu dram bytes on the 28672x4096 launch = 1.007 x algorithmic (profiles/qgemv_q4_0_28672x4096.md), scaled by bytes",
                       "kernel": "qgemv_kernel<Q4_0>", "peak_source": peak_src, "launches_timed": len(launches) * reps,
                       "bytes_per_launch_avg": gemv_bytes / len(launches), "us_per_launch_avg": 1e3 * ms_gemv / len(launches)},
          "e2e": {"value": world * args.steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
