@@ -189,6 +189,19 @@ int b200q_attn_min_split(int max_context);
 size_t b200q_attn_scratch_bytes(int n_heads, int n_kv_heads, int head_dim, int n_split);
 int b200q_attn_decode(const b200q_attn_args* args, void* stream);
 
+/* b200q_attn_decode for callers that must not allocate device memory (no counterpart in the reference, which
+ * always allocates through its own allocator).  Meant for hosts that own all device memory themselves -- a frozen
+ * serving pool, an arena planner that replays captured work, code running under stream capture -- and therefore have
+ * no scratch buffer to pass.  The scratch lives in a fixed array inside the library image instead
+ * (b200q_attn_decode_static_capacity() bytes, 2 MiB, resident on every GPU that loads the library until exit);
+ * `args->scratch` is ignored.  Calls whose geometry needs more (b200q_attn_scratch_bytes) return B200Q_ERR_TOO_LARGE.
+ * The call performs no cudaMalloc/cudaFree.  The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress) with that device current: make that first call outside any stream capture.  All calls on a
+ * device share the one array: two calls that may overlap on the GPU (different streams) race and must be ordered by
+ * the caller.  Always launched fully stream-ordered (B200Q_FLAG_PDL is ignored). */
+size_t b200q_attn_decode_static_capacity(void);
+int b200q_attn_decode_static(const b200q_attn_args* args, void* stream);
+
 /* Greedy sampling: tokens[*pos + 1] = argmax(logits) (lowest index on ties), then
  * *pos += 1.  At temperature 0 this is what the Gumbel-max expression of
  * tinygrad/llm/model.py:364 selects.  scratch: b200q_argmax_scratch_bytes(), zeroed once. */

@@ -65,6 +65,8 @@ SIGNATURES = {
   "b200q_attn_min_split": (c_int, [c_int]),
   "b200q_attn_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
   "b200q_attn_decode": (c_int, [POINTER(AttnArgs), c_void_p]),
+  "b200q_attn_decode_static_capacity": (c_size_t, []),
+  "b200q_attn_decode_static": (c_int, [POINTER(AttnArgs), c_void_p]),
   "b200q_argmax_scratch_bytes": (c_size_t, []),
   "b200q_argmax_advance": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
   "b200q_advance": (c_int, [c_void_p, c_int, c_void_p]),

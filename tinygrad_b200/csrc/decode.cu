@@ -351,3 +351,44 @@ extern "C" int b200q_argmax_advance(const float* logits, int n, int32_t* tokens,
                             logits, n, tokens, pos, sval, sidx, counter));
   return B200Q_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Attention for callers that may not allocate device memory.
+//
+// Some hosts of this library hand out device memory themselves and forbid anything else from doing so: a serving loop
+// that froze its memory pool after warm-up, an engine whose planner owns one arena and replays captured work, or code
+// running while a stream is being captured (the CUDA allocator calls are illegal there).  Such a caller cannot provide
+// the scratch buffer b200q_attn_decode needs unless it planned for it.  This variant brings its own: a fixed array that
+// is part of the library image, so every GPU that loads the library holds these bytes until the process exits.
+constexpr size_t ATTN_STATIC_SCRATCH_BYTES = (size_t)2 << 20;     // 2 MiB: e.g. 64 heads x 62 slices (3968 positions) of head_dim 128
+static __device__ __align__(256) unsigned char g_attn_static_scratch[ATTN_STATIC_SCRATCH_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+static void* g_attn_static_ptr[MAX_DEVICES];   // device address of the array on each device, filled on first use
+
+extern "C" size_t b200q_attn_decode_static_capacity(void) { return ATTN_STATIC_SCRATCH_BYTES; }
+
+extern "C" int b200q_attn_decode_static(const b200q_attn_args* a, void* stream) {
+  if (!a) return B200Q_ERR_BAD_ARG;
+  const size_t need = b200q_attn_scratch_bytes(a->n_heads, a->n_kv_heads, a->head_dim, a->n_split);
+  if (need == 0) return B200Q_ERR_BAD_ARG;
+  if (need > ATTN_STATIC_SCRATCH_BYTES) return B200Q_ERR_TOO_LARGE;   // heads x slices x (head_dim + 4) floats must fit the built-in array
+  int dev = -1;
+  B200Q_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) return B200Q_ERR_TOO_LARGE;
+  if (!g_attn_static_ptr[dev]) {
+    // In host code the array's name is only a handle; the kernel needs the address the array has on THIS device.
+    void* p = nullptr;
+    B200Q_CHECK_CUDA(cudaGetSymbolAddress(&p, g_attn_static_scratch));
+    g_attn_static_ptr[dev] = p;
+  }
+  // The arrival counters sit behind the partial results, at an offset that depends on the geometry, and the array keeps
+  // whatever the last call left there: zero them (stream-ordered, no allocation) before the kernel counts arrivals.
+  unsigned char* base = static_cast<unsigned char*>(g_attn_static_ptr[dev]);
+  const size_t counters_at = need - (size_t)a->n_kv_heads * sizeof(unsigned);
+  B200Q_CHECK_CUDA(cudaMemsetAsync(base + counters_at, 0, (size_t)a->n_kv_heads * sizeof(unsigned), (cudaStream_t)stream));
+  b200q_attn_args b = *a;
+  b.scratch = base;
+  b.flags &= ~B200Q_FLAG_PDL;   // the memset in front is not a kernel: launch the kernel fully ordered behind it
+  return b200q_attn_decode(&b, stream);
+}
