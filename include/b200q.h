@@ -37,6 +37,7 @@ extern "C" {
 /* element types of activations / outputs */
 #define B200Q_F32 0
 #define B200Q_F16 1
+#define B200Q_BF16 2
 /* GEMV epilogues */
 #define B200Q_EPI_LINEAR 0   /* y = W x (+bias) (+residual) */
 #define B200Q_EPI_SILU_MUL 1 /* weights packed with b200q_repack(raw0=gate, raw1=up): y = silu(gate x) * (up x) */
@@ -210,6 +211,34 @@ int b200q_argmax_advance(const float* device_logits, int n, int32_t* device_toke
                          void* stream);
 /* *pos += 1 (a prompt token whose logits are not needed) */
 int b200q_advance(int32_t* device_pos, int flags, void* stream);
+
+/* ---- MXFP8 mixture-of-experts path --------------------------------------
+ * E4M3 values with one E8M0 exponent per 32 along the last axis.
+ *
+ * b200q_quantize_mxfp8: `quantize_mxfp8` (extra/gemm/cdna_asm_gemm.py:149-159; E4M3 rounding tinygrad/dtype.py:237-260):
+ * x [rows, k] (fp32 or bf16) -> q [rows, k] E4M3 codes + e8 [rows, k/32].  With dest_row != NULL the quantised row r is
+ * written to the `fan` rows dest_row[r*fan .. r*fan+fan-1] of the outputs instead (= quantise after `dispatch`,
+ * extra/gemm/moe_routing.py:124-126; zero the outputs first: a zero row quantises to q = 0, e8 = 0). */
+int b200q_quantize_mxfp8(const void* x, int x_dtype, int64_t rows, int k, const int32_t* dest_row, int fan, void* q, void* e8, void* stream);
+/* act = silu(gate) * up from h = [gate | up] (bf16 [rows, 2f], the output of the fused gate/up expert GEMM), rounded to
+ * bf16 and quantised as above (tinygrad/llm/model.py:129 between the expert GEMMs). */
+int b200q_swiglu_quantize_mxfp8(const void* h_bf16, int64_t rows, int f, void* q, void* e8, void* stream);
+/* Routing tables (`route`, extra/gemm/moe_routing.py:109-122): topi / weights [n_tokens, k], dest_row [n_tokens*k],
+ * off [n_experts+1] (group starts, every group padded to 256 rows).  mode 0: top-k of the logits in descending order,
+ * weights = softmax over the k (moe_routing.py:115-116).  mode 1: softmax over all experts, compare-count top-k in
+ * ascending order, weights not renormalised (tinygrad/llm/model.py:35-41,118,123-124, the OLMoE defaults).
+ * Deterministic (stable counting sort).  scratch: b200q_moe_route_scratch_bytes(). */
+size_t b200q_moe_route_scratch_bytes(int n_tokens, int n_experts, int k);
+int b200q_moe_rows_max(int n_tokens, int n_experts, int k);   /* m_max_for, extra/gemm/moe_routing.py:89-90 */
+int b200q_moe_route(const float* logits, int n_tokens, int n_experts, int k, int mode, int32_t* topi, float* weights, int32_t* dest_row,
+                    int32_t* off, void* scratch, void* stream);
+/* `combine` (extra/gemm/moe_routing.py:128-131): out[t] = sum_j weights[t,j] * y[dest_row[t*k+j]], fp32 sum, bf16 in/out. */
+int b200q_moe_combine(const void* y_bf16, const int32_t* dest_row, const float* weights, int n_tokens, int k, int d, void* out_bf16, void* stream);
+/* `grouped_mx_gemm` (extra/gemm/moe_gemm.py:112-134; kernel contract extra/thunder/amd/grouped_mxfp8_gemm.cpp:32-158):
+ * C[m_total, n] bf16 = A_q[m_total, k] x B_q[e][n, k]^T with both operands' E8M0 scales, fp32 accumulation; rows
+ * off[e]..off[e+1] use expert e; rows past off[n_experts] are left untouched.  m_total % 256 == n % 128 == k % 128 == 0. */
+int b200q_grouped_mxfp8_gemm(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts,
+                             int m_total, int n, int k, void* c_bf16, void* stream);
 
 #ifdef __cplusplus
 }

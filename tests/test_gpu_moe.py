@@ -1,0 +1,133 @@
+"""GPU parity of the MXFP8 mixture-of-experts path against the oracle (itself pinned on the reference's goldens)."""
+import numpy as np
+import pytest
+from oracle import mxfp8 as mx, llm
+from gpu_util import need_gpu, assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _gpu(): need_gpu()
+
+
+def _quant(x, dtype_flag):
+  from tinygrad_b200 import moe
+  from tinygrad_b200.runtime import DeviceBuffer
+  rows, k = x.shape
+  q, e8 = moe.quantize_mxfp8(DeviceBuffer.from_numpy(x), rows, k, dtype_flag)
+  return q.numpy(), e8.numpy()
+
+
+def test_quantize_mxfp8_golden_bit_exact(golden):
+  from tinygrad_b200 import _lib
+  g = golden("mxfp8")
+  q, e8 = _quant(g["x"], _lib.F32)
+  np.testing.assert_array_equal(e8, g["e8"])
+  np.testing.assert_array_equal(q, g["q"])
+
+
+def test_quantize_mxfp8_random_and_edges_bit_exact():
+  from tinygrad_b200 import _lib, moe
+  rng = np.random.default_rng(0)
+  x = (rng.standard_normal((257, 96)) * np.exp(rng.uniform(-30, 30, (257, 1)))).astype(np.float32)
+  x[0, :32] = 0.0                                                  # all-zero block
+  x[1, :32] = np.float32(8.0) * (1 - 2.0 ** -24)                   # largest value below a power of two
+  x[2, :32] = [448.0, -448.0, 449.0, 1e30] * 8                     # saturation
+  x[3, :32] = np.float32(2.0) ** np.arange(-16, 16)                # exact powers of two
+  q, e8 = _quant(x, _lib.F32)
+  rq, re8 = mx.quantize_mxfp8(x)
+  np.testing.assert_array_equal(e8, re8)
+  np.testing.assert_array_equal(q, rq)
+  xb = moe.to_bf16_bits(x)                                         # bf16 input: same function of the bf16 values
+  q, e8 = _quant(xb, _lib.BF16)
+  rq, re8 = mx.quantize_mxfp8(moe.from_bf16_bits(xb))
+  np.testing.assert_array_equal(e8, re8)
+  np.testing.assert_array_equal(q, rq)
+
+
+def _route(logits, k, mode):
+  from tinygrad_b200 import moe
+  from tinygrad_b200.runtime import DeviceBuffer
+  T, E = logits.shape
+  r = moe.Routing(DeviceBuffer.from_numpy(logits), T, E, k, mode)
+  return r, r.topi.numpy(), r.weights.numpy(), r.dest_row.numpy(), r.off.numpy()
+
+
+def test_route_golden(golden):
+  g = golden("mxfp8")
+  r, topi, w, dest, off = _route(g["route_logits"], 2, 0)
+  np.testing.assert_array_equal(dest, g["route_dest_row"][0])
+  np.testing.assert_array_equal(off, g["route_off"][0])
+  np.testing.assert_allclose(w, g["route_weights"][0], rtol=1e-6)
+  assert r.m_l == int(g["route_m_l"])
+
+
+@pytest.mark.parametrize("T,E,k", [(4096, 64, 8), (1000, 8, 2), (37, 128, 6), (3000, 256, 4)])
+def test_route_random_matches_oracle(T, E, k):
+  logits = np.random.default_rng(T).standard_normal((T, E)).astype(np.float32)
+  logits[5, :4] = logits[5, 0]                                      # ties: the lower index ranks higher
+  r, topi, w, dest, off = _route(logits, k, 0)
+  rw, rtopi, rdest, roff, m_l = mx.route(logits, k, E)
+  np.testing.assert_array_equal(topi, rtopi)
+  np.testing.assert_array_equal(dest, rdest)
+  np.testing.assert_array_equal(off, roff)
+  np.testing.assert_allclose(w, rw, rtol=2e-6)
+  assert r.m_l == m_l and len(set(dest.tolist())) == T * k           # a permutation into distinct rows
+  # mode 1: softmax over all experts, compare-count top-k in ascending order (tinygrad/llm/model.py:35-41)
+  _, topi1, w1, dest1, off1 = _route(logits, k, 1)
+  scores = llm.softmax(logits)
+  _, sel = llm.pairwise_topk(logits[None], k)
+  np.testing.assert_array_equal(topi1, sel[0])
+  np.testing.assert_allclose(w1, np.take_along_axis(scores, sel[0].astype(np.int64), -1), rtol=2e-6)
+  np.testing.assert_array_equal(off1, roff)
+
+
+def test_grouped_gemm_matches_oracle():
+  from tinygrad_b200 import _lib, moe
+  from tinygrad_b200.runtime import DeviceBuffer
+  rng = np.random.default_rng(1)
+  E, N, K = 4, 256, 384
+  off = np.array([0, 256, 256, 768, 1024], np.int32)                # expert 1 got no rows; 1280 rows allocated, 256 unused
+  M = 1280
+  a = rng.standard_normal((M, K)).astype(np.float32); a[700:768] = 0  # padding rows inside a group are zero
+  w = (rng.standard_normal((E, N, K)) * 0.02).astype(np.float32)
+  a_q, a_e8 = mx.quantize_mxfp8(a); w_q, w_e8 = mx.quantize_mxfp8(w)
+  ref = mx.to_bf16(mx.grouped_mx_gemm(a_q, a_e8, w_q, w_e8, off))
+  d = [DeviceBuffer.from_numpy(v) for v in (a_q, a_e8, w_q, w_e8, off)]
+  c = DeviceBuffer.from_numpy(np.full((M, N), 0x7FC0, np.uint16))     # NaN canary
+  _lib.check(_lib.load().b200q_grouped_mxfp8_gemm(d[0].ptr, d[1].ptr, d[2].ptr, d[3].ptr, d[4].ptr, E, M, N, K, c.ptr, None))
+  got = c.numpy()
+  assert (got[1024:] == 0x7FC0).all()                               # rows past the last group untouched
+  assert_close(moe.from_bf16_bits(got[:1024]), ref[:1024], tol=1e-2, what="grouped MXFP8 GEMM")
+
+
+def test_moe_ffn_matches_composed_oracle():
+  """route -> dispatch+quantise -> GEMM -> SwiGLU+quantise -> GEMM -> combine, against the same chain of oracle pieces."""
+  from tinygrad_b200 import moe
+  from tinygrad_b200.runtime import DeviceBuffer
+  rng = np.random.default_rng(2)
+  T, D, F, E, k = 300, 256, 128, 8, 2
+  wg, wu, wd = ((rng.standard_normal(s) * 0.05).astype(np.float32) for s in ((E, F, D), (E, F, D), (E, D, F)))
+  x = moe.from_bf16_bits(moe.to_bf16_bits(rng.standard_normal((T, D)).astype(np.float32)))
+  logits = rng.standard_normal((T, E)).astype(np.float32)
+  for mode in (0, 1):
+    m = moe.MxMoE(wg, wu, wd, k, mode)
+    out = moe.from_bf16_bits(m(DeviceBuffer.from_numpy(moe.to_bf16_bits(x)), DeviceBuffer.from_numpy(logits), T).numpy())
+    # oracle chain
+    if mode == 0: w, topi, dest, off, m_l = mx.route(logits, k, E)
+    else:
+      _, sel = llm.pairwise_topk(logits[None], k); topi = sel[0]
+      w = np.take_along_axis(llm.softmax(logits), topi.astype(np.int64), -1)
+      _, _, _, off, m_l = mx.route(logits, k, E)
+      dest = m.last_routing.dest_row.numpy()                          # placement checked in test_route_random_matches_oracle
+    xd = mx.dispatch(x, dest, m_l, k)
+    a_q, a_e8 = mx.quantize_mxfp8(xd)
+    gu_q, gu_e8 = mx.quantize_mxfp8(np.concatenate([wg, wu], axis=1))
+    h = mx.to_bf16(mx.grouped_mx_gemm(a_q, a_e8, gu_q, gu_e8, off))
+    act = mx.to_bf16(llm.silu(h[:, :F]) * h[:, F:])
+    act_q, act_e8 = mx.quantize_mxfp8(act)
+    dn_q, dn_e8 = mx.quantize_mxfp8(wd)
+    y = mx.to_bf16(mx.grouped_mx_gemm(act_q, act_e8, dn_q, dn_e8, off))
+    ref = mx.to_bf16(mx.combine(y, dest, w))
+    assert_close(out, ref, tol=1e-2, what=f"MoE FFN mode {mode}")

@@ -6,7 +6,7 @@ from ctypes import c_int, c_int32, c_int64, c_size_t, c_float, c_void_p, c_char_
 LIB_PATH = pathlib.Path(__file__).resolve().parent / "libb200q.so"
 
 Q4_0, Q8_0, Q6_K = 2, 8, 14
-F32, F16 = 0, 1
+F32, F16, BF16 = 0, 1, 2
 EPI_LINEAR, EPI_SILU_MUL = 0, 1
 FLAG_PDL = 1
 
@@ -70,6 +70,13 @@ SIGNATURES = {
   "b200q_argmax_scratch_bytes": (c_size_t, []),
   "b200q_argmax_advance": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
   "b200q_advance": (c_int, [c_void_p, c_int, c_void_p]),
+  "b200q_quantize_mxfp8": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+  "b200q_swiglu_quantize_mxfp8": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+  "b200q_moe_route_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
+  "b200q_moe_rows_max": (c_int, [c_int, c_int, c_int]),
+  "b200q_moe_route": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+  "b200q_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+  "b200q_grouped_mxfp8_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
 }
 
 _lib = None

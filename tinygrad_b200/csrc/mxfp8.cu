@@ -1,0 +1,241 @@
+// MXFP8 (E4M3 values + one E8M0 scale per 32 along K) mixture-of-experts path:
+// activation quantiser, top-k routing tables, row dispatch / combine, SwiGLU + requantise.
+// The grouped expert GEMM is in mxfp8_gemm.cu.
+//
+// Semantics follow extra/gemm/cdna_asm_gemm.py:149-173 (quantize_mxfp8, _mx_block_scale),
+// tinygrad/dtype.py:237-260 (E4M3 round-to-nearest-even, saturating), extra/gemm/moe_routing.py:89-131
+// (route / dispatch / combine, groups padded to 256 rows) and tinygrad/llm/model.py:35-41,110-130
+// (softmax-over-all-experts gating with compare-count top-k, the OLMoE default).
+#include "common.cuh"
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <math.h>
+
+namespace {
+
+constexpr int BLOCK_ROW = 256;   // extra/gemm/moe_routing.py:4
+
+// ---------------------------------------------------------------------------
+// quantize_mxfp8: one warp per block of 32 values, lane = element.
+//   e8 = clamp(floor(log2(max(amax, 1e-38))) + 127, 0, 254);  q = e4m3(clamp(x * 2^(127 - e8), +-448))
+// floor(log2()) is taken the way the reference's fp32 tensor op yields it: log2 rounded to fp32, then floor
+// (so an amax within half an fp32 ulp below a power of two lands on that power).
+__device__ __forceinline__ uint8_t mx_scale_exponent(float amax) {
+  const float lg = (float)log2((double)fmaxf(amax, 1e-38f));
+  const float e = fminf(fmaxf(floorf(lg) + 127.f, 0.f), 254.f);
+  return (uint8_t)e;
+}
+__device__ __forceinline__ uint8_t mx_quant_value(float x, uint8_t e8) {
+  const float xs = fminf(fmaxf(x * ldexpf(1.f, 127 - (int)e8), -448.f), 448.f);
+  return (uint8_t)__nv_cvt_float_to_fp8(xs, __NV_SATFINITE, __NV_E4M3);
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// rows of x go to rows dest[r] of the outputs (dest == nullptr: identity); `fan` consecutive dest entries per input row
+template <typename T>
+__global__ void quantize_mxfp8_kernel(const T* __restrict__ x, int64_t rows, int k, const int32_t* __restrict__ dest, int fan,
+                                      uint8_t* __restrict__ q, uint8_t* __restrict__ e8) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int kb = k >> 5;
+  if (warp >= rows * kb) return;
+  const int64_t r = warp / kb; const int b = (int)(warp - r * kb);
+  const float v = to_f32<T>(x[r * k + b * 32 + lane]);
+  const float amax = warp_max(fabsf(v));
+  const uint8_t e = mx_scale_exponent(amax);
+  const uint8_t qv = mx_quant_value(v, e);
+  for (int f = 0; f < fan; f++) {
+    const int64_t o = dest ? (int64_t)dest[r * fan + f] : r;
+    q[o * k + b * 32 + lane] = qv;
+    if (lane == 0) e8[o * kb + b] = e;
+  }
+}
+
+// SwiGLU between the two expert GEMMs: h = [gate | up] (bf16, [m, 2f]) -> act = silu(gate) * up computed in fp32,
+// rounded to bf16 as a tensor would be stored, then quantised like any activation.
+__global__ void swiglu_quant_kernel(const __nv_bfloat16* __restrict__ h, int64_t rows, int f, uint8_t* __restrict__ q, uint8_t* __restrict__ e8) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int kb = f >> 5;
+  if (warp >= rows * kb) return;
+  const int64_t r = warp / kb; const int b = (int)(warp - r * kb);
+  const float g = __bfloat162float(h[r * 2 * f + b * 32 + lane]), u = __bfloat162float(h[r * 2 * f + f + b * 32 + lane]);
+  const float v = __bfloat162float(__float2bfloat16_rn((g / (1.f + expf(-g))) * u));
+  const uint8_t e = mx_scale_exponent(warp_max(fabsf(v)));
+  q[r * f + b * 32 + lane] = mx_quant_value(v, e);
+  if (lane == 0) e8[r * kb + b] = e;
+}
+
+// ---------------------------------------------------------------------------
+// routing, step 1: one warp per token.  mode 0 (extra/gemm/moe_routing.py:115-116): top-k of the raw logits in
+// descending order, weights = softmax over the k.  mode 1 (tinygrad/llm/model.py:118,123-124 with the OLMoE defaults):
+// scores = softmax over all experts, top-k listed in ascending order of score, weights = the scores, not renormalised.
+// Ties: the lower expert index ranks higher (model.py:35-41).
+constexpr int MAX_E_PER_LANE = 8;   // up to 256 experts
+
+__global__ void route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int k, int mode, int32_t* __restrict__ topi,
+                                  float* __restrict__ weights) {
+  const int lane = threadIdx.x & 31;
+  const int tok = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (tok >= n_tokens) return;
+  float v[MAX_E_PER_LANE];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MAX_E_PER_LANE; i++) {
+    const int e = i * 32 + lane;
+    v[i] = e < n_experts ? logits[(size_t)tok * n_experts + e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+  mx = warp_max(mx);
+  float denom = 0.f;
+  if (mode == 1) {
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; i++) denom += (i * 32 + lane < n_experts) ? expf(v[i] - mx) : 0.f;
+    denom = warp_sum(denom);
+  }
+  float top1 = 0.f, ksum = 0.f;
+  for (int j = 0; j < k; j++) {
+    float bv = -INFINITY; int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; i++) { const int e = i * 32 + lane; if (v[i] > bv) { bv = v[i]; bi = e; } }   // lowest index wins inside a lane
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; i++) if (i * 32 + lane == bi) v[i] = -INFINITY;    // taken
+    if (j == 0) top1 = bv;
+    const int slot = mode == 1 ? k - 1 - j : j;
+    float w;
+    if (mode == 1) w = expf(bv - mx) / denom;
+    else { w = expf(bv - top1); ksum += w; }
+    if (lane == 0) { topi[(size_t)tok * k + slot] = bi; weights[(size_t)tok * k + slot] = w; }
+  }
+  if (mode == 0) {
+    __syncwarp();
+    if (lane < k) weights[(size_t)tok * k + lane] /= ksum;
+  }
+}
+
+// routing, steps 2-4: stable counting sort of the T*k (token, slot) pairs by expert.
+// dest_row[i] = off[e_i] + (number of pairs before i with the same expert); off = cumulative group sizes padded to 256.
+constexpr int ROUTE_CHUNK = 1024;
+
+__global__ void __launch_bounds__(ROUTE_CHUNK) route_count_kernel(const int32_t* __restrict__ topi, int n, int n_experts, int32_t* __restrict__ counts) {
+  extern __shared__ int s_cnt[];
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) s_cnt[e] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * ROUTE_CHUNK + threadIdx.x;
+  if (i < n) atomicAdd(&s_cnt[topi[i]], 1);      // integer counts: the order of the adds does not matter
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[(size_t)blockIdx.x * n_experts + e] = s_cnt[e];
+}
+
+// one thread per expert: exclusive scan of its chunk counts (in place), then thread 0 builds the padded offsets
+__global__ void route_scan_kernel(int32_t* __restrict__ counts, int n_chunks, int n_experts, int32_t* __restrict__ off) {
+  extern __shared__ int s_tot[];
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < n_chunks; c++) { const int v = counts[(size_t)c * n_experts + e]; counts[(size_t)c * n_experts + e] = run; run += v; }
+    s_tot[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    off[0] = 0;
+    for (int e = 0; e < n_experts; e++) { run += (s_tot[e] + BLOCK_ROW - 1) / BLOCK_ROW * BLOCK_ROW; off[e + 1] = run; }
+  }
+}
+
+__global__ void __launch_bounds__(ROUTE_CHUNK) route_place_kernel(const int32_t* __restrict__ topi, int n, int n_experts,
+                                                                  const int32_t* __restrict__ counts, const int32_t* __restrict__ off,
+                                                                  int32_t* __restrict__ dest_row) {
+  extern __shared__ int s_wcnt[];                 // [32 warps][n_experts] pairs of each expert seen by each warp
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int j = threadIdx.x; j < 32 * n_experts; j += blockDim.x) s_wcnt[j] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * ROUTE_CHUNK + threadIdx.x;
+  const int e = i < n ? topi[i] : -1;
+  const unsigned same = __match_any_sync(0xffffffffu, e);
+  const int before_in_warp = __popc(same & ((1u << lane) - 1));
+  if (e >= 0 && before_in_warp == 0) s_wcnt[warp * n_experts + e] = __popc(same);
+  __syncthreads();
+  if (e >= 0) {
+    int before = counts[(size_t)blockIdx.x * n_experts + e] + before_in_warp;
+    for (int w = 0; w < warp; w++) before += s_wcnt[w * n_experts + e];
+    dest_row[i] = off[e] + before;
+  }
+}
+
+// combine (extra/gemm/moe_routing.py:128-131): out[t] = sum_j weights[t, j] * y[dest_row[t*k + j]], fp32 sum in slot order, bf16 out
+__global__ void combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ dest_row, const float* __restrict__ weights,
+                               int n_tokens, int k, int d, __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < k; j++) acc += weights[(size_t)t * k + j] * __bfloat162float(y[(size_t)dest_row[(size_t)t * k + j] * d + c]);
+    out[(size_t)t * d + c] = __float2bfloat16_rn(acc);
+  }
+}
+
+}  // namespace
+
+extern "C" int b200q_quantize_mxfp8(const void* x, int x_dtype, int64_t rows, int k, const int32_t* dest_row, int fan, void* q, void* e8, void* stream) {
+  if (rows < 0 || k <= 0 || (rows && (!x || !q || !e8))) return B200Q_ERR_BAD_ARG;
+  if (x_dtype != B200Q_F32 && x_dtype != B200Q_BF16) return B200Q_ERR_BAD_ARG;
+  if (k % 32) return B200Q_ERR_BAD_SHAPE;
+  if (dest_row ? fan <= 0 : fan != 1) return B200Q_ERR_BAD_ARG;
+  if (rows == 0) return B200Q_OK;
+  const int64_t warps = rows * (k / 32);
+  const unsigned blocks = (unsigned)((warps + 7) / 8);
+  if (x_dtype == B200Q_F32) quantize_mxfp8_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)x, rows, k, dest_row, fan, (uint8_t*)q, (uint8_t*)e8);
+  else quantize_mxfp8_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, rows, k, dest_row, fan, (uint8_t*)q, (uint8_t*)e8);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+extern "C" int b200q_swiglu_quantize_mxfp8(const void* h_bf16, int64_t rows, int f, void* q, void* e8, void* stream) {
+  if (rows < 0 || f <= 0 || (rows && (!h_bf16 || !q || !e8))) return B200Q_ERR_BAD_ARG;
+  if (f % 32) return B200Q_ERR_BAD_SHAPE;
+  if (rows == 0) return B200Q_OK;
+  const int64_t warps = rows * (f / 32);
+  swiglu_quant_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)h_bf16, rows, f, (uint8_t*)q, (uint8_t*)e8);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+extern "C" size_t b200q_moe_route_scratch_bytes(int n_tokens, int n_experts, int k) {
+  if (n_tokens <= 0 || n_experts <= 0 || k <= 0) return 0;
+  return (size_t)ceil_div(n_tokens * k, ROUTE_CHUNK) * n_experts * sizeof(int32_t);
+}
+
+extern "C" int b200q_moe_rows_max(int n_tokens, int n_experts, int k) {   // m_max_for, extra/gemm/moe_routing.py:89-90
+  return (ceil_div(n_tokens * k, BLOCK_ROW) + n_experts) * BLOCK_ROW;
+}
+
+extern "C" int b200q_moe_route(const float* logits, int n_tokens, int n_experts, int k, int mode, int32_t* topi, float* weights, int32_t* dest_row,
+                               int32_t* off, void* scratch, void* stream) {
+  if (!logits || !topi || !weights || !dest_row || !off || !scratch) return B200Q_ERR_BAD_ARG;
+  if (n_tokens <= 0 || n_experts <= 0 || k <= 0 || k > n_experts || (mode != 0 && mode != 1)) return B200Q_ERR_BAD_ARG;
+  if (n_experts > 32 * MAX_E_PER_LANE || k > 32) return B200Q_ERR_BAD_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n = n_tokens * k, n_chunks = ceil_div(n, ROUTE_CHUNK);
+  route_topk_kernel<<<ceil_div(n_tokens, 8), 256, 0, st>>>(logits, n_tokens, n_experts, k, mode, topi, weights);
+  route_count_kernel<<<n_chunks, ROUTE_CHUNK, n_experts * sizeof(int), st>>>(topi, n, n_experts, (int32_t*)scratch);
+  route_scan_kernel<<<1, 256, n_experts * sizeof(int), st>>>((int32_t*)scratch, n_chunks, n_experts, off);
+  route_place_kernel<<<n_chunks, ROUTE_CHUNK, 32 * n_experts * sizeof(int), st>>>(topi, n, n_experts, (const int32_t*)scratch, off, dest_row);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+extern "C" int b200q_moe_combine(const void* y_bf16, const int32_t* dest_row, const float* weights, int n_tokens, int k, int d, void* out_bf16,
+                                 void* stream) {
+  if (!y_bf16 || !dest_row || !weights || !out_bf16 || n_tokens <= 0 || k <= 0 || d <= 0) return B200Q_ERR_BAD_ARG;
+  combine_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)y_bf16, dest_row, weights, n_tokens, k, d, (__nv_bfloat16*)out_bf16);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}

@@ -1,0 +1,70 @@
+"""MXFP8 mixture-of-experts feed-forward on the device: host-side mirror of the reference's grouped path.
+
+`quantize_mxfp8` is extra/gemm/cdna_asm_gemm.py:149-159; `route` / `combine` are extra/gemm/moe_routing.py:109-131;
+`MxMoE.__call__` chains them like examples/mlperf/models/gpt_oss.py:215-226 (route -> dispatch -> grouped_mx_gemm ->
+activation -> grouped_mx_gemm -> combine), with the SwiGLU of tinygrad/llm/model.py:129.  bf16 tensors travel as
+uint16 arrays on the host (numpy has no bfloat16).  All compute is in libb200q.so.
+"""
+import numpy as np
+from . import _lib
+from ._lib import check, F32, BF16
+from .runtime import DeviceBuffer, stream_ptr
+
+ROUTE_TOPK_SOFTMAX, ROUTE_SOFTMAX_TOPK = 0, 1   # weights = softmax over the k best logits | softmax over all experts, not renormalised
+
+
+def to_bf16_bits(x: np.ndarray) -> np.ndarray:
+  """fp32 -> bf16 bit patterns, round-to-nearest-even (tinygrad/dtype.py:222-226)."""
+  u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+  return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def from_bf16_bits(b: np.ndarray) -> np.ndarray:
+  return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def quantize_mxfp8(x: DeviceBuffer, rows: int, k: int, dtype: int, dest_row: DeviceBuffer = None, fan: int = 1, out_rows: int = None, stream=None):
+  """-> (q codes uint8 [out_rows, k], e8 uint8 [out_rows, k/32]).  With dest_row the rows are scattered (dispatch) into zeroed outputs."""
+  out_rows = rows if out_rows is None else out_rows
+  q, e8 = DeviceBuffer.empty((out_rows, k), np.uint8, zero=dest_row is not None), DeviceBuffer.empty((out_rows, k // 32), np.uint8, zero=dest_row is not None)
+  check(_lib.load().b200q_quantize_mxfp8(x.ptr, dtype, rows, k, dest_row.ptr if dest_row else None, fan, q.ptr, e8.ptr, stream_ptr(stream)))
+  return q, e8
+
+
+class Routing:
+  """Device tables of `route` (extra/gemm/moe_routing.py:92-122)."""
+  def __init__(self, logits: DeviceBuffer, n_tokens: int, n_experts: int, k: int, mode: int = ROUTE_TOPK_SOFTMAX, stream=None):
+    lib = _lib.load()
+    self.n_tokens, self.n_experts, self.k = n_tokens, n_experts, k
+    self.m_l = lib.b200q_moe_rows_max(n_tokens, n_experts, k)
+    self.topi, self.weights = DeviceBuffer.empty((n_tokens, k), np.int32), DeviceBuffer.empty((n_tokens, k), np.float32)
+    self.dest_row, self.off = DeviceBuffer.empty((n_tokens * k,), np.int32), DeviceBuffer.empty((n_experts + 1,), np.int32)
+    self._scratch = DeviceBuffer(lib.b200q_moe_route_scratch_bytes(n_tokens, n_experts, k))
+    check(lib.b200q_moe_route(logits.ptr, n_tokens, n_experts, k, mode, self.topi.ptr, self.weights.ptr, self.dest_row.ptr, self.off.ptr,
+                              self._scratch.ptr, stream_ptr(stream)))
+
+
+class MxMoE:
+  """Expert SwiGLU FFN with MXFP8 operands.  w_gate / w_up: (E, F, D), w_down: (E, D, F), fp32 numpy; quantised once along K."""
+  def __init__(self, w_gate: np.ndarray, w_up: np.ndarray, w_down: np.ndarray, k: int, mode: int = ROUTE_SOFTMAX_TOPK):
+    self.E, self.F, self.D = w_gate.shape
+    self.k, self.mode = k, mode
+    gu = np.concatenate([w_gate, w_up], axis=1).astype(np.float32)          # (E, 2F, D): one GEMM yields [gate | up]
+    self.gu_q, self.gu_e8 = quantize_mxfp8(DeviceBuffer.from_numpy(gu), self.E * 2 * self.F, self.D, F32)
+    self.dn_q, self.dn_e8 = quantize_mxfp8(DeviceBuffer.from_numpy(w_down.astype(np.float32)), self.E * self.D, self.F, F32)
+
+  def __call__(self, x_bf16: DeviceBuffer, logits: DeviceBuffer, n_tokens: int, stream=None) -> DeviceBuffer:
+    """x (T, D) bf16, router logits (T, E) fp32 -> (T, D) bf16."""
+    lib, s = _lib.load(), stream_ptr(stream)
+    r = Routing(logits, n_tokens, self.E, self.k, self.mode, stream)
+    a_q, a_e8 = quantize_mxfp8(x_bf16, n_tokens, self.D, BF16, dest_row=r.dest_row, fan=self.k, out_rows=r.m_l, stream=stream)
+    h = DeviceBuffer.empty((r.m_l, 2 * self.F), np.uint16, zero=True)
+    check(lib.b200q_grouped_mxfp8_gemm(a_q.ptr, a_e8.ptr, self.gu_q.ptr, self.gu_e8.ptr, r.off.ptr, self.E, r.m_l, 2 * self.F, self.D, h.ptr, s))
+    act_q, act_e8 = DeviceBuffer.empty((r.m_l, self.F), np.uint8), DeviceBuffer.empty((r.m_l, self.F // 32), np.uint8)
+    check(lib.b200q_swiglu_quantize_mxfp8(h.ptr, r.m_l, self.F, act_q.ptr, act_e8.ptr, s))
+    y = DeviceBuffer.empty((r.m_l, self.D), np.uint16, zero=True)
+    check(lib.b200q_grouped_mxfp8_gemm(act_q.ptr, act_e8.ptr, self.dn_q.ptr, self.dn_e8.ptr, r.off.ptr, self.E, r.m_l, self.D, self.F, y.ptr, s))
+    out = DeviceBuffer.empty((n_tokens, self.D), np.uint16)
+    check(lib.b200q_moe_combine(y.ptr, r.dest_row.ptr, r.weights.ptr, n_tokens, self.k, self.D, out.ptr, s))
+    self.last_routing = r
+    return out
