@@ -153,7 +153,7 @@ def run_gemv_probe(args):
   xq = runtime.DeviceBuffer(lib.b200q_xq_bytes(n_in), zero=True) if args.probe_xq else None   # an all-zero record times like any other
   res = runtime.DeviceBuffer.empty((n_out,), np.float32, zero=True) if args.probe_residual else None
   def enqueue(n):
-    for i in range(n): quant.gemv(ws[i % n_rot].buf.ptr, synth.Q4_0, n_out, n_in, x, y, flags=fl, stream=st, xq_in=xq, residual=res)
+    for i in range(n): quant.gemv(ws[i % n_rot].buf.ptr, synth.Q4_0, n_out, n_in, x, y, flags=fl, stream=st, xq_in=xq, residual=res, max_ctas=args.gemv_ctas)
   enqueue(args.warmup); st.synchronize()
   g = runtime.Graph(st)
   with g: enqueue(args.steps)
@@ -167,9 +167,50 @@ def run_gemv_probe(args):
                     "frac_of_peak": gbs / peak, "peak_source": src, "launches": args.steps, "pdl": not args.no_pdl}))
 
 
+def run_moe_probe(args):
+  """One OLMoE-shaped MXFP8 MoE FFN layer over 4096 tokens (configs[3], single GPU); prints its own JSON line.
+  FLOPs counted on the useful (routed, unpadded) rows only: T * k * 3 * 2 * d * f."""
+  from tinygrad_b200 import build, runtime, moe
+  build.build_lib()
+  runtime.set_device(0)
+  T, D, F, E, k = 4096, 2048, 1024, 64, 8
+  rng = np.random.default_rng(0)
+  wg, wu, wd = ((rng.standard_normal(s, dtype=np.float32) * 0.02) for s in ((E, F, D), (E, F, D), (E, D, F)))
+  m = moe.MxMoE(wg, wu, wd, k, moe.ROUTE_SOFTMAX_TOPK)
+  x = runtime.DeviceBuffer.from_numpy(moe.to_bf16_bits(rng.standard_normal((T, D), dtype=np.float32)))
+  logits = runtime.DeviceBuffer.from_numpy(rng.standard_normal((T, E), dtype=np.float32))
+  st = runtime.Stream()
+  for _ in range(max(3, args.warmup)): m(x, logits, T, stream=st)
+  st.synchronize()
+  e0, e1 = runtime.Event(), runtime.Event()
+  steps = min(args.steps, 50)
+  e0.record(st)
+  for _ in range(steps): m(x, logits, T, stream=st)
+  e1.record(st); st.synchronize()
+  ms = e0.elapsed_ms(e1) / steps
+  # the two grouped GEMMs alone
+  lib = __import__("tinygrad_b200._lib", fromlist=["load"]).load()
+  r = m.last_routing
+  a_q, a_e8 = moe.quantize_mxfp8(x, T, D, 2, dest_row=r.dest_row, fan=k, out_rows=r.m_l)
+  h = runtime.DeviceBuffer.empty((r.m_l, 2 * F), np.uint16, zero=True)
+  runtime.synchronize()
+  e0.record(st)
+  for _ in range(steps): lib.b200q_grouped_mxfp8_gemm(a_q.ptr, a_e8.ptr, m.gu_q.ptr, m.gu_e8.ptr, r.off.ptr, E, r.m_l, 2 * F, D, h.ptr, st.ptr)
+  e1.record(st); st.synchronize()
+  ms_gemm1 = e0.elapsed_ms(e1) / steps
+  flops = T * k * 3 * 2 * D * F
+  peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {"bf16_tflops": 1590.0}
+  fp8_peak = 2 * peaks["bf16_tflops"]
+  print(json.dumps({"workload": "configs[3] one layer: OLMoE-shaped MXFP8 MoE FFN, 4096 tokens, 64 experts top-8, d 2048, f 1024",
+                    "ms_per_layer": ms, "tflops": flops / ms / 1e9, "frac_of_fp8_peak": flops / ms / 1e9 / fp8_peak,
+                    "fp8_peak": f"2 x measured bf16 burst = {fp8_peak} TFLOP/s (no fp8 entry in MEASURED_PEAKS.json)",
+                    "gate_up_gemm_ms": ms_gemm1, "gate_up_gemm_tflops": T * k * 2 * 2 * D * F / ms_gemm1 / 1e9,
+                    "contraction": "fp8 mma.sync m16n8k32 with fp32 block scaling (not yet tcgen05 block-scaled MMA)"}))
+
+
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("--workload", default="decode", choices=["decode", "gemv"])
+  ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "moe"])
   ap.add_argument("--gemv-shape", default="28672x4096", help="rows x K of the probe (gate+up interleaved = 28672x4096)")
   ap.add_argument("--rotate-mb", type=int, default=512)
   ap.add_argument("--probe-xq", action="store_true", help="gemv probe: hand the kernel a ready-made activation record")
@@ -188,6 +229,7 @@ def main():
   rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
   if args.impl == "reference": return run_reference(args, rank)
   if args.workload == "gemv": return run_gemv_probe(args)
+  if args.workload == "moe": return run_moe_probe(args)
   if args.warmup < 3: args.warmup = 3
 
   from tinygrad_b200 import build, runtime, synth

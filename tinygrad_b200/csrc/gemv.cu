@@ -63,6 +63,10 @@ constexpr int CONS_WARPS = B200Q_CONS_WARPS;
 constexpr int CONS_THREADS = CONS_WARPS * 32;
 constexpr int NTHREADS = CONS_THREADS + 32;      // + producer warp
 constexpr int STAGE_GROUPS = B200Q_STAGE_GROUPS; // weight tiles (16 rows x 128 columns) per ring stage
+#ifndef B200Q_COPY_GROUPS
+#define B200Q_COPY_GROUPS 4
+#endif
+constexpr int COPY_GROUPS = B200Q_COPY_GROUPS;   // weight tiles per bulk copy
 constexpr int SPIN_LIMIT = 1 << 20;
 
 __device__ int g_status = 0;                     // sticky: 1 = an mbarrier wait ran out
@@ -233,7 +237,11 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
             if (it == NS && !x_issued) after_prefetch();
             if (!mbar_wait(empty0 + 8 * slot, ((it / NS) & 1) ^ 1)) { ok = false; break; }
             mbar_expect_tx(full0 + 8 * slot, groups * TB);
-            bulk_g2s(smem_u32(ring + slot * STAGE_BYTES), src + (size_t)s * STAGE_BYTES, groups * TB, full0 + 8 * slot);
+            // one stage = several bulk copies on the same barrier: a single copy is served slowly, several overlap
+            for (int g0 = 0; g0 < groups; g0 += COPY_GROUPS) {
+              const int gn = min(COPY_GROUPS, groups - g0);
+              bulk_g2s(smem_u32(ring + slot * STAGE_BYTES + g0 * TB), src + (size_t)s * STAGE_BYTES + (size_t)g0 * TB, gn * TB, full0 + 8 * slot);
+            }
           }
         }
       }
