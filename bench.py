@@ -76,9 +76,16 @@ class ClockSampler:
             "samples": len(self.samples)}
 
 
+def _use_all_host_threads():
+  """torch.distributed.run exports OMP_NUM_THREADS=1; the CPU arm uses every thread this process may run on."""
+  n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+  os.environ["OMP_NUM_THREADS"] = str(n)
+
+
 def cpu_port_block_seconds(cfg, reps_budget_s: float, seed: int = 0):
   """Time the C restatement on the host cores: the 7 linears of one block and the head, raw GGUF blocks.
   Returns (seconds per block, seconds for the head, threads, repetitions)."""
+  _use_all_host_threads()
   from oracle import cpu_gemv
   from tinygrad_b200 import synth
   qd, kvd = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
@@ -107,6 +114,7 @@ def run_reference(args, rank):
   """The reference arm: the CPU implementation of the same path on the host cores (the C restatement
   of tinygrad's fused dequant-linear arithmetic; tinygrad's own CPU device needs clang, which this image lacks)."""
   if rank != 0: return
+  _use_all_host_threads()
   from oracle import cpu_gemv
   from tinygrad_b200 import synth
   cfg = llama3_8b_config()
@@ -236,11 +244,8 @@ def main():
   from tinygrad_b200.model import Transformer
   from dataclasses import replace
   build.build_lib()
-  dist = None
-  if world > 1:
-    import torch, torch.distributed as dist
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+  from tinygrad_b200.replicas import Ranks
+  ranks = Ranks(backend="nccl")
   runtime.set_device(local)
   cfg = llama3_8b_config()
   if args.blocks: cfg = replace(cfg, num_blocks=args.blocks)
@@ -258,15 +263,10 @@ def main():
 
   def barrier():
     runtime.synchronize()
-    if dist is not None: dist.barrier()
+    ranks.barrier()
     runtime.synchronize()
 
-  def max_over_ranks(ms: float) -> float:
-    if dist is None: return ms
-    import torch
-    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+  max_over_ranks = ranks.max
 
   if PROMPT_LEN + args.warmup + args.steps + 2 > MAX_CONTEXT:
     raise SystemExit(f"--steps {args.steps} does not fit the {MAX_CONTEXT}-token context after a {PROMPT_LEN}-token prompt")
@@ -317,7 +317,9 @@ def main():
   achieved = gemv_bytes / (ms_gemv * 1e-3) / 1e9
   kv_bytes_per_pos = 2 * cfg.n_kv_heads * cfg.head_dim * 2 * cfg.num_blocks
   step_bytes = model.weight_bytes + kv_bytes_per_pos * (PROMPT_LEN + args.warmup + args.steps // 2)
-  if rank != 0: return
+  if rank != 0:
+    ranks.close()
+    return
   value = world * args.steps / (ms_dev * 1e-3)
   out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
          "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -336,7 +338,7 @@ def main():
     out["cpu_baseline"] = {"value": 1.0 / (t_blk * cfg.num_blocks + t_head), "unit": UNIT, "cores": threads, "kind": "port",
                            "sample": f"C restatement, {reps_cpu} repetitions of one block's 7 Q4_0 linears (x{cfg.num_blocks}) + the vocab head; attention/norms omitted"}
   print(json.dumps(out))
-  if dist is not None: dist.destroy_process_group()
+  ranks.close()
 
 
 if __name__ == "__main__":
