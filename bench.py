@@ -216,9 +216,53 @@ def run_moe_probe(args):
                     "contraction": "fp8 mma.sync m16n8k32 with fp32 block scaling (not yet tcgen05 block-scaled MMA)"}))
 
 
+def run_tp_probe(args):
+  """configs[4]: Llama-3-70B-shaped Q4_0 decode, batch 1, tensor-parallel over all ranks (column QKV/gate/up/head, row O/down,
+  NCCL all-reduce).  Launch under torch.distributed.run; prints its own JSON line on rank 0.  Shards are generated per rank."""
+  from tinygrad_b200 import build, runtime, synth, tensor_parallel as tpar
+  from tinygrad_b200.replicas import Ranks
+  from tinygrad_b200.model import Transformer, TransformerConfig
+  build.build_lib()
+  ranks = Ranks(backend="nccl")
+  runtime.set_device(ranks.local)
+  tp = tpar.TPGroup(ranks)
+  prompt_len, ctx = (1024, 2048) if not args.blocks else (64, 256)
+  cfg = TransformerConfig(num_blocks=args.blocks or 80, dim=8192, hidden_dim=28672, n_heads=64, n_kv_heads=8, norm_eps=1e-5, vocab_size=128256,
+                          head_dim=128, rope_theta=500000.0, rope_dim=128, v_head_dim=128, max_context=ctx, kv_dtype="float16")
+  lc = tpar.local_config(cfg, ranks.world)
+  t0 = time.time()
+  sd = synth.LazyDenseState(lc, synth.Q4_0, seed=0, embd_vocab=cfg.vocab_size, linear_seed=1 + ranks.rank)
+  model = Transformer(cfg, sd, ggml_type=synth.Q4_0, tp=tp, use_pdl=not args.no_pdl)
+  t_build = time.time() - t0
+  prompt = [int(t) for t in np.random.default_rng(7).integers(0, cfg.vocab_size, prompt_len)]
+  if args.skip_prefill: model.set_state(prompt, prompt_len - 1)
+  else:
+    model.set_state(prompt, 0)
+    for _ in range(prompt_len - 1): model.step(with_head=False)
+  for _ in range(max(3, args.warmup)): model.step()
+  runtime.synchronize(); ranks.barrier()
+  e0, e1 = runtime.Event(), runtime.Event()
+  e0.record(model.stream)
+  for _ in range(args.steps): model.step()
+  e1.record(model.stream)
+  runtime.synchronize(); ranks.barrier()
+  ms = ranks.max(e0.elapsed_ms(e1))
+  toks = [model.read_token(prompt_len + i) for i in range(4)]
+  same = ranks.max(float(toks[0])) == ranks.sum(float(toks[0])) / ranks.world       # every rank sampled the same token
+  peak, src = measured_peaks()
+  total_bytes = model.weight_bytes * ranks.world
+  if ranks.rank == 0:
+    print(json.dumps({"workload": f"configs[4]: Llama-3-70B-shaped Q4_0 decode bs1, prompt {prompt_len}, tensor-parallel x{ranks.world}" +
+                      (f" DEBUG {args.blocks} blocks" if args.blocks else ""), "tokens_per_s": args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
+                      "n_gpus": ranks.world, "weight_gb_total": total_bytes / 1e9, "hbm_gbs_per_gpu": model.weight_bytes / (ms / args.steps * 1e-3) / 1e9,
+                      "frac_of_hbm_peak_per_gpu": model.weight_bytes / (ms / args.steps * 1e-3) / 1e9 / peak, "collectives_per_step": 2 * cfg.num_blocks + 1,
+                      "ranks_agree": bool(same), "model_build_s": round(t_build, 1)}), flush=True)
+  os._exit(0)
+
+
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "moe"])
+  ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "moe", "tp70b"])
   ap.add_argument("--gemv-shape", default="28672x4096", help="rows x K of the probe (gate+up interleaved = 28672x4096)")
   ap.add_argument("--rotate-mb", type=int, default=512)
   ap.add_argument("--probe-xq", action="store_true", help="gemv probe: hand the kernel a ready-made activation record")
@@ -238,6 +282,7 @@ def main():
   if args.impl == "reference": return run_reference(args, rank)
   if args.workload == "gemv": return run_gemv_probe(args)
   if args.workload == "moe": return run_moe_probe(args)
+  if args.workload == "tp70b": return run_tp_probe(args)
   if args.warmup < 3: args.warmup = 3
 
   from tinygrad_b200 import build, runtime, synth

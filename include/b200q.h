@@ -151,6 +151,9 @@ typedef struct b200q_gemv_args {
                                `y` may then be NULL if nobody needs the fp32 values */
   const void* xq_out_norm_weight;
   float* ss_out;            /* device [n_out / 32] partial sums of squares of the output row, or NULL */
+  float residual_scale;     /* the residual is multiplied by this before it is added; 0 means 1.  A row-parallel shard of a
+                               tensor-parallel linear adds residual / n_ranks so that the all-reduce of the shards yields
+                               W x + residual (tinygrad shards the same linears by axis, examples/llama3.py:233-243) */
 } b200q_gemv_args;
 int b200q_gemv(const b200q_gemv_args* args, void* stream);
 size_t b200q_xq_bytes(int n);

@@ -47,7 +47,7 @@ def test_bad_arguments_are_rejected_without_a_device(lib):
   assert lib.b200q_repack(_lib.Q4_0, 16, None, 16, 16, 48, None) == -2
   assert lib.b200q_repack(_lib.Q4_0, 16, None, 8, 16, 32, None) == -3        # packed buffer must be 16-byte aligned
   assert lib.b200q_repack(_lib.Q6_K, 16, None, 16, 16, 256, None) == -4
-  a = _lib.GemvArgs(_lib.Q4_0, 16, 128, 1, 16, 16, _lib.F32, _lib.F32, None, 0.0, 0, None, None, 16, 0, 0, None, None, 0, None, None, None)
+  a = _lib.GemvArgs(_lib.Q4_0, 16, 128, 1, 16, 16, _lib.F32, _lib.F32, None, 0.0, 0, None, None, 16, 0, 0, None, None, 0, None, None, None, 0.0)
   a.n_in = 100
   assert lib.b200q_gemv(ctypes.byref(a), None) == -2
   a.n_in, a.w_packed = 128, 8

@@ -32,6 +32,7 @@ struct GemvParams {
   const __half* norm_w;
   const __half* bias;
   const float* residual;
+  float residual_scale;
   void* y;
   int n_out, n_in, kgroups, n_row_tiles;
   int x_f16, y_f16, epilogue;
@@ -262,7 +263,7 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
   float pre_add = 0.f;
   const int first_rt = blockIdx.x * (XQ_OUT ? p.unit : 1);
   if (warp == 0 && lane < 16 && p.epilogue == B200Q_EPI_LINEAR && first_rt * 16 + lane < p.n_out) {
-    if (p.residual) pre_add = p.residual[(size_t)m * p.n_out + first_rt * 16 + lane];
+    if (p.residual) pre_add = p.residual[(size_t)m * p.n_out + first_rt * 16 + lane] * p.residual_scale;
     if (p.bias) pre_add += __half2float(p.bias[first_rt * 16 + lane]);
   }
   if (tid == 0) *zero = make_uint4(0, 0, 0, 0);
@@ -355,7 +356,7 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
             if (rt == first_rt) v += pre_add;
             else {
               if (p.bias) v += __half2float(p.bias[row]);
-              if (p.residual) v += p.residual[(size_t)m * p.n_out + row];
+              if (p.residual) v = fmaf(p.residual[(size_t)m * p.n_out + row], p.residual_scale, v);
             }
             if (p.y) {
               if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(v);
@@ -439,7 +440,7 @@ extern "C" int b200q_gemv(const b200q_gemv_args* a, void* stream) {
   if (a->xq_out && a->n_out % GROUP_ELEMS) return B200Q_ERR_BAD_SHAPE;
   GemvParams p;
   p.w = (const uint8_t*)a->w_packed; p.x = a->x; p.norm_w = (const __half*)a->norm_weight; p.bias = (const __half*)a->bias;
-  p.residual = (const float*)a->residual; p.y = a->y;
+  p.residual = (const float*)a->residual; p.residual_scale = a->residual_scale == 0.f ? 1.f : a->residual_scale; p.y = a->y;
   p.n_out = a->n_out; p.n_in = a->n_in; p.kgroups = ceil_div(a->n_in, GROUP_ELEMS);
   p.n_row_tiles = a->epilogue == B200Q_EPI_SILU_MUL ? ceil_div(a->n_out, 8) : ceil_div(a->n_out, TILE_ROWS);
   p.x_f16 = a->x_dtype == B200Q_F16; p.y_f16 = a->y_dtype == B200Q_F16; p.epilogue = a->epilogue; p.eps = a->norm_eps;

@@ -51,17 +51,23 @@ DEFAULT_HANDOVER = ("attn_o",)
 
 class Transformer:
   def __init__(self, config: TransformerConfig, state_dict: dict, ggml_type: int = _lib.Q4_0, n_split: int = 0, use_pdl: bool = True,
-               use_graph: bool = True, gemv_max_ctas: int = 0, handover=None):
+               use_graph: bool = True, gemv_max_ctas: int = 0, handover=None, tp=None):
     """state_dict: the reference's tensor names -> numpy arrays; Linear weights as raw
-    GGUF block bytes (uint8), embeddings / norms / biases as fp16."""
+    GGUF block bytes (uint8), embeddings / norms / biases as fp16.
+    tp: a tensor_parallel.TPGroup; `config` is then the FULL model and `state_dict` this rank's shard (shard_state_dict)."""
+    self.tp, self.full_config = tp, config
+    if tp is not None:
+      from .tensor_parallel import local_config
+      config = local_config(config, tp.size)
     c = self.config = config
+    vocab_full = self.full_config.vocab_size
     assert c.max_context > 0 and c.n_heads % c.n_kv_heads == 0
     self.qtype, self.flags, self.use_graph = ggml_type, (FLAG_PDL if use_pdl else 0), use_graph
     self.q_dim, self.kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
     self.gemv_max_ctas = gemv_max_ctas
     self.n_split = n_split or _lib.load().b200q_attn_min_split(c.max_context)
     self.max_context = c.max_context
-    self.stream = Stream()
+    self.stream = Stream(tp.stream_ptr()) if tp is not None else Stream()
     sd = state_dict
     qkv_rows = self.q_dim + 2 * self.kv_dim
     assert self.q_dim % 16 == 0 and self.kv_dim % 16 == 0, "q/k/v are packed back to back in whole 16-row tiles"
@@ -94,11 +100,12 @@ class Transformer:
     self.token_embd = DeviceBuffer.from_numpy(np.asarray(sd["token_embd.weight"], dtype=np.float16))
     self.rope = DeviceBuffer.from_numpy(precompute_freqs_cis(c.rope_dim, c.max_context, c.rope_theta))
     # activations of one token (fp32 residual stream, model.py:359)
-    self.x = DeviceBuffer.empty((c.dim,), np.float32, zero=True)
+    self.x = tp.empty_f32(c.dim) if tp is not None else DeviceBuffer.empty((c.dim,), np.float32, zero=True)   # NCCL reduces it in place
     self.qkv = DeviceBuffer.empty((qkv_rows,), np.float32, zero=True)
     self.attn = DeviceBuffer.empty((self.q_dim,), np.float32, zero=True)
     self.act = DeviceBuffer.empty((c.hidden_dim,), np.float32, zero=True)
-    self.logits = DeviceBuffer.empty((c.vocab_size,), np.float32, zero=True)
+    if tp is not None: self.logits_part, self.logits = tp.empty_f32(c.vocab_size), tp.empty_f32(vocab_full)
+    else: self.logits = self.logits_part = DeviceBuffer.empty((c.vocab_size,), np.float32, zero=True)
     self.tokens = DeviceBuffer.empty((c.max_context + 1,), np.int32, zero=True)
     self.pos = DeviceBuffer.empty((1,), np.int32, zero=True)
     self.attn_scratch = DeviceBuffer(_lib.load().b200q_attn_scratch_bytes(c.n_heads, c.n_kv_heads, c.head_dim, self.n_split), zero=True)
@@ -111,6 +118,7 @@ class Transformer:
     elif isinstance(handover, str): edges = tuple(e for e in handover.split(",") if e)
     else: edges = all_edges if handover else ()
     assert all(e in all_edges for e in edges), f"unknown hand-over edge in {edges}"
+    if tp is not None: edges = tuple(e for e in edges if e in ("attn_o", "gateup_down"))   # records of all-reduced vectors would hold partial sums
     self.edges = frozenset(edges) if can else frozenset()
     self.handover = bool(self.edges)
     xqb = _lib.load().b200q_xq_bytes
@@ -127,6 +135,12 @@ class Transformer:
     c, lib, s, fl = self.config, _lib.load(), self.stream.ptr, self.flags
     kvdt = F16 if c.kv_dtype == "float16" else F32
     kw = dict(flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
+    tp = self.tp
+    # A launch that follows an NCCL call is fully stream-ordered: the programmatic-launch attribute right behind the
+    # event waits NCCL leaves in the stream was measured to let the kernel start before the reduced vector is there.
+    kw_after_coll = dict(kw, flags=0) if tp is not None else kw
+    rkw = dict(residual=self.x, residual_scale=1.0 / tp.size) if tp is not None else dict(residual=self.x)   # row-split shards add residual / n_ranks
+    vocab_full = self.full_config.vocab_size
     e, nss = self.edges, c.dim // 32
     qkv_rows = self.q_dim + 2 * self.kv_dim
     # the four hand-over edges: kwargs of the consuming (xq_in...) and of the producing (xq_out...) launch
@@ -136,7 +150,7 @@ class Transformer:
     in_act = dict(xq_in=self.xq_act) if "gateup_down" in e else {}
     if attention or tail:
       ho = "down_qkv" in e
-      check(lib.b200q_embed(self.token_embd.ptr, self.tokens.ptr, self.pos.ptr, self.x.ptr, c.dim, c.vocab_size,
+      check(lib.b200q_embed(self.token_embd.ptr, self.tokens.ptr, self.pos.ptr, self.x.ptr, c.dim, vocab_full,
                             self.xq_a.ptr if ho else None, self.blk[0].attn_norm.ptr if ho else None, self.ss_a.ptr if ho else None, fl, s))
     for i, b in enumerate(self.blk):
       nxt_norm = self.blk[i + 1].attn_norm if i + 1 < len(self.blk) else self.output_norm
@@ -144,24 +158,28 @@ class Transformer:
       out_act = dict(xq_out=self.xq_act) if "gateup_down" in e else {}
       out_a = dict(xq_out=self.xq_a, xq_out_norm_weight=nxt_norm, ss_out=self.ss_a) if "down_qkv" in e else {}
       quant.gemv(b.qkv.ptr, self.qtype, qkv_rows, c.dim, None if in_a else self.x, self.qkv, norm_weight=b.attn_norm, norm_eps=c.norm_eps,
-                 bias=b.qkv_bias, **in_a, **kw)
+                 bias=b.qkv_bias, **in_a, **(kw_after_coll if i > 0 else kw))
       if attention:
         a = _lib.AttnArgs(self.qkv.ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, self.pos.ptr, self.attn.ptr, self.attn_scratch.ptr,
                           c.n_heads, c.n_kv_heads, c.head_dim, c.rope_dim, c.max_context, self.n_split, fl,
                           self.xq_attn.ptr if "attn_o" in e else None)
         check(lib.b200q_attn_decode(ctypes.byref(a), s))
-      quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, None if in_attn else self.attn, self.x, residual=self.x,
+      quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, None if in_attn else self.attn, self.x, **rkw,
                  **in_attn, **out_b, **kw)
+      if tp is not None: tp.all_reduce(self.x)
       quant.gemv(b.gate_up.buf.ptr, self.qtype, c.hidden_dim, c.dim, None if in_b else self.x, None if out_act else self.act,
-                 norm_weight=b.ffn_norm, norm_eps=c.norm_eps, epilogue=EPI_SILU_MUL, **in_b, **out_act, **kw)
-      quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, None if in_act else self.act, self.x, residual=self.x,
+                 norm_weight=b.ffn_norm, norm_eps=c.norm_eps, epilogue=EPI_SILU_MUL, **in_b, **out_act, **kw_after_coll)
+      quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, None if in_act else self.act, self.x, **rkw,
                  **in_act, **out_a, **kw)
+      if tp is not None: tp.all_reduce(self.x)
     if with_head:
-      quant.gemv(self.output.buf.ptr, self.qtype, c.vocab_size, c.dim, None if in_a else self.x, self.logits, norm_weight=self.output_norm,
-                 norm_eps=c.norm_eps, **in_a, **kw)
-      if tail: check(lib.b200q_argmax_advance(self.logits.ptr, c.vocab_size, self.tokens.ptr, self.pos.ptr, self.argmax_scratch.ptr, fl, s))
+      quant.gemv(self.output.buf.ptr, self.qtype, c.vocab_size, c.dim, None if in_a else self.x, self.logits_part, norm_weight=self.output_norm,
+                 norm_eps=c.norm_eps, **in_a, **kw_after_coll)
+      if tp is not None: tp.all_gather(self.logits, self.logits_part)
+      if tail: check(lib.b200q_argmax_advance(self.logits.ptr, vocab_full, self.tokens.ptr, self.pos.ptr, self.argmax_scratch.ptr,
+                                              0 if tp is not None else fl, s))
     elif tail:
-      check(lib.b200q_advance(self.pos.ptr, fl, s))
+      check(lib.b200q_advance(self.pos.ptr, 0 if tp is not None else fl, s))
 
   def gemv_launches(self) -> list:
     """(n_out rows streamed, n_in) of every GEMV launch of one step with the head, in launch order."""

@@ -16,6 +16,7 @@ def ptr_of(obj) -> int:
   if obj is None: return 0
   if isinstance(obj, int): return obj
   if isinstance(obj, DeviceBuffer): return obj.ptr
+  if hasattr(obj, "ptr"): return int(obj.ptr)
   if hasattr(obj, "data_ptr"): return int(obj.data_ptr())
   if hasattr(obj, "__cuda_array_interface__"): return int(obj.__cuda_array_interface__["data"][0])
   raise TypeError(f"cannot take a device pointer from {type(obj)}")
@@ -92,7 +93,11 @@ def stream_ptr(stream) -> int:
 
 
 class Stream:
-  def __init__(self):
+  def __init__(self, ptr: int = None):
+    """A new non-blocking stream, or a view of an existing `cudaStream_t` (e.g. the stream NCCL calls are issued on)."""
+    if ptr is not None:
+      self.ptr = int(ptr)
+      return
     p = ctypes.c_void_p()
     check(_lib.load().b200q_stream_create(ctypes.byref(p)))
     self.ptr = int(p.value)

@@ -84,15 +84,21 @@ def dense_model_raw(cfg, ggml_type: int = Q4_0, seed: int = 0, embd_std: float =
 class LazyDenseState:
   """Mapping view of `dense_model_raw` that makes each tensor when it is asked for, so a
   multi-GB model never sits in host memory as a whole."""
-  def __init__(self, cfg, ggml_type: int = Q4_0, seed: int = 0, embd_std: float = 0.02, bias_std: float = 0.02):
+  def __init__(self, cfg, ggml_type: int = Q4_0, seed: int = 0, embd_std: float = 0.02, bias_std: float = 0.02, embd_vocab: int = 0,
+               linear_seed: int = None):
+    """embd_vocab: rows of the embedding table when it differs from cfg.vocab_size (a tensor-parallel shard keeps the whole
+    table but only a slice of the vocabulary head); linear_seed: seed of the Linear weights / biases only (per-rank shards
+    differ, replicated tensors must not)."""
     self.cfg, self.ggml_type, self.seed, self.embd_std, self.bias_std = cfg, ggml_type, seed, embd_std, bias_std
+    self.embd_vocab, self.linear_seed = embd_vocab or cfg.vocab_size, seed if linear_seed is None else linear_seed
     self.shapes = {n: (o, i) for n, o, i in linear_names(cfg)}
 
   def __getitem__(self, key: str) -> np.ndarray:
     name, kind = key.rsplit(".", 1)
-    rng = np.random.default_rng(name_seed(name if kind == "weight" else key, self.seed))
+    is_linear = (kind == "weight" and name in self.shapes) or kind == "bias"
+    rng = np.random.default_rng(name_seed(name if kind == "weight" else key, self.linear_seed if is_linear else self.seed))
     if kind == "weight" and name in self.shapes: return BLOCK_MAKERS[self.ggml_type](*self.shapes[name], rng)
     if kind == "bias": return (rng.standard_normal(self.shapes[name][0], dtype=np.float32) * self.bias_std).astype(np.float16)
-    if name == "token_embd": return (rng.standard_normal((self.cfg.vocab_size, self.cfg.dim), dtype=np.float32) * self.embd_std).astype(np.float16)
+    if name == "token_embd": return (rng.standard_normal((self.embd_vocab, self.cfg.dim), dtype=np.float32) * self.embd_std).astype(np.float16)
     if name.endswith("_norm"): return (1.0 + 0.05 * rng.standard_normal(self.cfg.dim, dtype=np.float32)).astype(np.float16)
     raise KeyError(key)
