@@ -215,6 +215,13 @@ int b200q_argmax_advance(const float* device_logits, int n, int32_t* device_toke
 /* *pos += 1 (a prompt token whose logits are not needed) */
 int b200q_advance(int32_t* device_pos, int flags, void* stream);
 
+/* ---- batched / prefill linear on tcgen05 tensor cores --------------------------------
+ * C[m, n] fp32 = A[m, k] fp16 x W[n, k]^T fp16 with fp32 accumulation in tensor memory: `Linear.__call__` for more than
+ * one activation row (tinygrad/nn/__init__.py:177), as the prefill chunks of tinygrad/llm/model.py:464-481 need it.
+ * k % 64 == 0; a and w 16-byte aligned.  b200q_tc_status_read_clear: like b200q_status_read_clear for these kernels. */
+int b200q_gemm_f16(const void* a_f16, const void* w_f16, float* c, int m, int n, int k, void* stream);
+int b200q_tc_status_read_clear(int* status);
+
 /* ---- MXFP8 mixture-of-experts path --------------------------------------
  * E4M3 values with one E8M0 exponent per 32 along the last axis.
  *

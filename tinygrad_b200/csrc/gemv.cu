@@ -272,28 +272,38 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
     // the row arrives quantised (the producer thread copies the record); only the RMSNorm scalar is computed here
     if (p.norm_w) for (int i = tid; i < p.ss_count; i += CONS_THREADS) ss += p.ss_in[i];
   } else {
-    // quantise the activation row here: 8 threads per block of 32, 4 elements each
+    // quantise the activation row here: 8 threads per block of 32, 4 elements each.  The loads of PF blocks are issued
+    // before any is used, so a batch costs one L2 round trip instead of one per block.
+    constexpr int PF = 4, BSTEP = CONS_THREADS / 8;
     const int nblk_pad = p.kgroups * 4, q = tid & 7;
     const XqDst dst(record, p.kgroups);
-    for (int b = tid >> 3; b < nblk_pad; b += CONS_THREADS / 8) {
-      const int k = b * 32 + 4 * q;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (k < p.n_in) {
-        if (p.x_f16) {
-          const uint2 r = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(p.x) + (size_t)m * p.n_in + k);
-          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x)), c = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
-          v = make_float4(a.x, a.y, c.x, c.y);
-        } else {
-          v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (size_t)m * p.n_in + k);
-        }
-        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
-        if (p.norm_w) {
-          const uint2 r = *reinterpret_cast<const uint2*>(p.norm_w + k);
-          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x)), c = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
-          v.x *= a.x; v.y *= a.y; v.z *= c.x; v.w *= c.y;
+    for (int b0 = tid >> 3; b0 < nblk_pad; b0 += PF * BSTEP) {
+      float4 v[PF];
+      uint2 nw[PF];
+#pragma unroll
+      for (int u = 0; u < PF; u++) {
+        const int k = (b0 + u * BSTEP) * 32 + 4 * q;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        nw[u] = make_uint2(0x3C003C00u, 0x3C003C00u);      // fp16 ones
+        if (b0 + u * BSTEP < nblk_pad && k < p.n_in) {
+          if (p.x_f16) {
+            const uint2 r = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(p.x) + (size_t)m * p.n_in + k);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x)), c = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+            v[u] = make_float4(a.x, a.y, c.x, c.y);
+          } else {
+            v[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (size_t)m * p.n_in + k);
+          }
+          if (p.norm_w) nw[u] = *reinterpret_cast<const uint2*>(p.norm_w + k);
         }
       }
-      quant_block_8x4(v, q, b, dst);
+#pragma unroll
+      for (int u = 0; u < PF; u++) {
+        if (b0 + u * BSTEP < nblk_pad) {      // uniform over the 8 lanes of a block (and over the warp: 4 consecutive blocks)
+          ss = fmaf(v[u].x, v[u].x, fmaf(v[u].y, v[u].y, fmaf(v[u].z, v[u].z, fmaf(v[u].w, v[u].w, ss))));
+          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&nw[u].x)), c = __half22float2(*reinterpret_cast<const __half2*>(&nw[u].y));
+          quant_block_8x4(make_float4(v[u].x * a.x, v[u].y * a.y, v[u].z * c.x, v[u].w * c.y), q, b0 + u * BSTEP, dst);
+        }
+      }
     }
   }
   if (p.norm_w) {
