@@ -220,6 +220,13 @@ int b200q_advance(int32_t* device_pos, int flags, void* stream);
  * one activation row (tinygrad/nn/__init__.py:177), as the prefill chunks of tinygrad/llm/model.py:464-481 need it.
  * k % 64 == 0; a and w 16-byte aligned.  b200q_tc_status_read_clear: like b200q_status_read_clear for these kernels. */
 int b200q_gemm_f16(const void* a_f16, const void* w_f16, float* c, int m, int n, int k, void* stream);
+/* The same contraction with W as packed Q4_0 / Q8_0 tiles (b200q_repack, not interleaved), dequantised to fp16 on the way
+ * into shared memory -- bit-identical to the reference's materialised fp16 weight (tinygrad/llm/model.py:376) --, x [m, n_in]
+ * fp16 or fp32 (rounded to fp16 for the tensor core), optional fp16 bias [n_out], y [m, n_out] fp32 or fp16.
+ * The weights are streamed once per 128 activation rows: the prefill / batched-decode counterpart of b200q_gemv.
+ * x rows must be 16-byte aligned (n_in % 8 == 0 for fp16, % 4 for fp32: any n_in % 32 == 0 is). */
+int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, void* y, int y_dtype, int m, int n_out,
+                int n_in, void* stream);
 int b200q_tc_status_read_clear(int* status);
 
 /* ---- MXFP8 mixture-of-experts path --------------------------------------

@@ -1,4 +1,5 @@
 """GPU parity: dequantisation (bit-exact), packing (lossless) and the fused GEMV, through the C ABI."""
+import ctypes
 import numpy as np
 import pytest
 from oracle import ggml_quant as gq, llm
@@ -70,6 +71,7 @@ def test_repack_interleaved_gate_up():
 
 def _run_linear(typ, n_out, n_in, x, **kw):
   from tinygrad_b200 import quant
+  quant.GEMM_MIN_ROWS = 1 << 30          # these cases test the GEMV kernel, also for a few rows
   from tinygrad_b200.runtime import DeviceBuffer
   raw = synth.BLOCK_MAKERS[typ](n_out, n_in, np.random.default_rng(0))
   lin = quant.QuantLinear(n_in, n_out, typ, raw, **kw)
@@ -151,3 +153,30 @@ def test_no_kernel_wait_ran_out():
   """The bounded mbarrier waits of the GEMV pipeline must never expire in normal operation."""
   from tinygrad_b200 import runtime
   assert runtime.device_status() == 0
+
+
+@pytest.mark.parametrize("tag,m,n_out,n_in,x_dtype,bias", [("q4_0", 4, 64, 128, np.float32, False), ("q4_0", 37, 200, 96, np.float16, True),
+                                                           ("q4_0", 130, 4096, 4096, np.float32, False), ("q8_0", 8, 512, 3584, np.float32, True),
+                                                           ("q8_0", 32, 48, 160, np.float16, False), ("q4_0", 32, 14336, 4096, np.float32, False)])
+def test_tensor_core_gemm_matches_fp16_operand_reference(tag, m, n_out, n_in, x_dtype, bias):
+  """tcgen05 path (several activation rows): operands are the fp16 activations and the materialised fp16 weights."""
+  from tinygrad_b200 import quant, _lib
+  quant.GEMM_MIN_ROWS = 4
+  from tinygrad_b200.runtime import DeviceBuffer
+  typ = TAGS[tag]
+  rng = np.random.default_rng(m * 7 + n_out)
+  raw = synth.BLOCK_MAKERS[typ](n_out, n_in, rng)
+  x = rng.standard_normal((m, n_in)).astype(x_dtype)
+  b = rng.standard_normal(n_out).astype(np.float16) if bias else None
+  lin = quant.QuantLinear(n_in, n_out, typ, raw, bias=b)
+  y = lin(DeviceBuffer.from_numpy(x)).numpy()
+  w16 = gq.weight_matrix(raw, n_out, n_in, typ).astype(np.float16).astype(np.float32)
+  ref = x.astype(np.float16).astype(np.float32) @ w16.T + (b.astype(np.float32) if bias else 0.0)
+  assert y.dtype == x_dtype and y.shape == (m, n_out)
+  assert_close(y, ref, tol=2e-3 if x_dtype == np.float32 else 4e-3, what="tcgen05 GEMM vs fp16-operand reference")
+  # against the exact-weight fp32 product the only difference is the fp16 rounding of both operands (what the reference
+  # itself computes with when a Linear is called on fp16 activations): a few 1e-3 of the output scale
+  ref32 = llm.linear(x.astype(np.float32), gq.weight_matrix(raw, n_out, n_in, typ), b)
+  assert np.abs(y.astype(np.float32) - ref32).max() <= 4e-3 * max(1.0, np.abs(ref32).max())
+  st = ctypes.c_int(); _lib.check(_lib.load().b200q_tc_status_read_clear(ctypes.byref(st)))
+  assert st.value == 0

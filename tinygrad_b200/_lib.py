@@ -71,6 +71,7 @@ SIGNATURES = {
   "b200q_argmax_advance": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
   "b200q_advance": (c_int, [c_void_p, c_int, c_void_p]),
   "b200q_gemm_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+  "b200q_qgemm": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
   "b200q_tc_status_read_clear": (c_int, [POINTER(c_int)]),
   "b200q_quantize_mxfp8": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
   "b200q_swiglu_quantize_mxfp8": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),

@@ -127,6 +127,176 @@ __global__ void __launch_bounds__(GEMM_THREADS) tc_gemm_f16_kernel(const __half*
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(BN) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Quantised weights: W arrives as packed Q4_0 / Q8_0 tiles (include/b200q.h) and is dequantised to fp16 on its way into
+// shared memory: (q - 8) * d or q * d as one fp16 multiply of two exactly representable factors, i.e. the same value as
+// the reference's materialised fp16 weight (tinygrad/llm/gguf.py:46,56 then .cast('float16'), tinygrad/llm/model.py:376).
+// K order inside every 8-element core is [0,2,1,3,4,6,5,7] for both operands (that is how the nibble / byte unpack
+// delivers pairs); a contraction does not care as long as A and W agree.
+constexpr int QBK = 128;                          // one packed column group per K step
+constexpr int QGEMM_SMEM = (BM + BN) * QBK * 2;   // 64 KB
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) { uint32_t d; asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
+__device__ __forceinline__ uint32_t h2sub(uint32_t a, uint32_t b) { uint32_t d; asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ uint32_t h2mul(uint32_t a, uint32_t b) { uint32_t d; asm("mul.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ uint32_t h2fma(uint32_t a, uint32_t b, uint32_t c) { uint32_t d; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) { uint32_t d; asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel)); return d; }
+
+// 8 nibbles of two words (bytes 0..7 of a 16-byte half) -> one core row of 8 fp16 weights, low (HI = false) or high nibbles
+template <bool HI>
+__device__ __forceinline__ uint4 q4_core(uint32_t wa, uint32_t wb, uint32_t d2) {
+  const uint32_t MAGIC = 0x64006400u;
+  uint32_t r[4];
+  const uint32_t w[2] = {wa, wb};
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    const uint32_t v = w[i] >> 8;
+    if (!HI) {   // (1024 + n) - 1032 = n - 8
+      r[2 * i] = h2sub(lop3_and_or(w[i], 0x000F000Fu, MAGIC), 0x64086408u);
+      r[2 * i + 1] = h2sub(lop3_and_or(v, 0x000F000Fu, MAGIC), 0x64086408u);
+    } else {     // (1024 + 16 n) / 16 - 72 = n - 8
+      r[2 * i] = h2fma(lop3_and_or(w[i], 0x00F000F0u, MAGIC), 0x2C002C00u, 0xD480D480u);
+      r[2 * i + 1] = h2fma(lop3_and_or(v, 0x00F000F0u, MAGIC), 0x2C002C00u, 0xD480D480u);
+    }
+  }
+  return make_uint4(h2mul(r[0], d2), h2mul(r[1], d2), h2mul(r[2], d2), h2mul(r[3], d2));
+}
+// 8 int8 of two words -> one core row of 8 fp16 weights
+__device__ __forceinline__ uint4 q8_core(uint32_t wa, uint32_t wb, uint32_t d2) {
+  const uint32_t HIB = 0x64646464u, SUB = 0x64806480u;     // 0x64bb = 1024 + (b ^ 0x80) = 1152 + b
+  const uint32_t xa = wa ^ 0x80808080u, xb = wb ^ 0x80808080u;
+  return make_uint4(h2mul(h2sub(prmt(xa, HIB, 0x4240u), SUB), d2), h2mul(h2sub(prmt(xa, HIB, 0x4341u), SUB), d2),
+                    h2mul(h2sub(prmt(xb, HIB, 0x4240u), SUB), d2), h2mul(h2sub(prmt(xb, HIB, 0x4341u), SUB), d2));
+}
+
+struct QGemmParams {
+  const uint8_t* w; const void* x; const __half* bias; void* y;
+  int m, n_out, n_in, kgroups, n_row_tiles, x_f16, y_f16;
+};
+
+template <int QT>
+__global__ void __launch_bounds__(GEMM_THREADS) tc_qgemm_kernel(const QGemmParams p) {
+  extern __shared__ __align__(128) unsigned char qsm[];
+  unsigned char* sA = qsm;
+  unsigned char* sB = qsm + BM * QBK * 2;
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t tmem_base;
+  constexpr int TB = tile_bytes(QT);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int m0 = blockIdx.y * BM, rt0 = blockIdx.x * (BN / 16);
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&tmem_base)), "r"(BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bar)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = tid; i < QGEMM_SMEM / 16; i += GEMM_THREADS) reinterpret_cast<uint4*>(qsm)[i] = make_uint4(0, 0, 0, 0);   // rows past m / n stay zero
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t taddr = tmem_base;
+  const uint32_t idesc = make_idesc(BM, BN);
+  const int m_valid = min(BM, p.m - m0);
+  bool ok = true;
+  uint32_t phase = 0;
+  for (int kg = 0; kg < p.kgroups; kg++) {
+    // activations: rows m0 .. m0+m_valid, columns kg*128 .. +128, as fp16 in the cores' element order
+    for (int i = tid; i < m_valid * (QBK / 8); i += GEMM_THREADS) {
+      const int r = i / (QBK / 8), kc = (i % (QBK / 8)) * 8, k = kg * QBK + kc;
+      float f[8];
+      if (k < p.n_in) {
+        if (p.x_f16) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.x) + (size_t)(m0 + r) * p.n_in + k);
+          const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 4; j++) { const float2 t2 = __half22float2(h[j]); f[2 * j] = t2.x; f[2 * j + 1] = t2.y; }
+        } else {
+          const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (size_t)(m0 + r) * p.n_in + k);
+          const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (size_t)(m0 + r) * p.n_in + k + 4);
+          f[0] = lo.x; f[1] = lo.y; f[2] = lo.z; f[3] = lo.w; f[4] = hi.x; f[5] = hi.y; f[6] = hi.z; f[7] = hi.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) f[j] = 0.f;
+      }
+      __half2 o[4] = {__floats2half2_rn(f[0], f[2]), __floats2half2_rn(f[1], f[3]), __floats2half2_rn(f[4], f[6]), __floats2half2_rn(f[5], f[7])};
+      *reinterpret_cast<uint4*>(sA + tile_off(r, kc, BM)) = *reinterpret_cast<const uint4*>(o);
+    }
+    // weights: 8 packed tiles (16 rows x 4 blocks each); one (row, block) pair per thread per step
+    for (int ch = tid; ch < (BN / 16) * 64; ch += GEMM_THREADS) {
+      const int tl = ch >> 6, h = (ch >> 5) & 1, l = ch & 31, g = l >> 2, t = l & 3;
+      if (rt0 + tl >= p.n_row_tiles) continue;
+      const uint8_t* tile = p.w + ((size_t)(rt0 + tl) * p.kgroups + kg) * TB;
+      const unsigned short dbits = reinterpret_cast<const unsigned short*>(tile + (TB - 128))[(2 * g + (t >> 1)) * 4 + h * 2 + (t & 1)];
+      const uint32_t d2 = (uint32_t)dbits | ((uint32_t)dbits << 16);
+      const int r = tl * 16 + h * 8 + g;
+      if (QT == B200Q_Q4_0) {
+        const uint4 qv = reinterpret_cast<const uint4*>(tile)[h * 32 + l];
+        // element e < 16 = low nibble of byte e, e >= 16 = high nibble of byte e - 16: cores 0,1 low, cores 2,3 high
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32, BN)) = q4_core<false>(qv.x, qv.y, d2);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 8, BN)) = q4_core<false>(qv.z, qv.w, d2);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 16, BN)) = q4_core<true>(qv.x, qv.y, d2);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 24, BN)) = q4_core<true>(qv.z, qv.w, d2);
+      } else {
+        const uint4 q0 = reinterpret_cast<const uint4*>(tile)[(2 * h) * 32 + l], q1 = reinterpret_cast<const uint4*>(tile)[(2 * h + 1) * 32 + l];
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32, BN)) = q8_core(q0.x, q0.y, d2);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 8, BN)) = q8_core(q0.z, q0.w, d2);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 16, BN)) = q8_core(q1.x, q1.y, d2);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 24, BN)) = q8_core(q1.z, q1.w, d2);
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int kk = 0; kk < QBK / 16; kk++) {
+        const uint64_t da = make_desc(s32(sA) + kk * 2 * (BM * 16), BM * 16, 128);
+        const uint64_t db = make_desc(s32(sB) + kk * 2 * (BN * 16), BN * 16, 128);
+        const uint32_t acc = (kg > 0 || kk > 0) ? 1u : 0u;
+        asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                     ::"r"(taddr), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&bar)) : "memory");
+    }
+    if (!wait_bar(s32(&bar), phase)) { ok = false; break; }
+    phase ^= 1;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }
+  if (ok) {
+    const int row = m0 + warp * 32 + (tid & 31);
+#pragma unroll 1
+    for (int j0 = 0; j0 < BN; j0 += 32) {
+      uint32_t v[32];
+      const uint32_t ta = taddr + ((uint32_t)(warp * 32) << 16) + j0;
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                   : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+                     "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+                     "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+                     "=r"(v[31])
+                   : "r"(ta));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (row < p.m) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+          const int col = rt0 * 16 + j0 + j;
+          if (col < p.n_out) {
+            float o = __uint_as_float(v[j]);
+            if (p.bias) o += __half2float(p.bias[col]);
+            if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)row * p.n_out + col] = __float2half_rn(o);
+            else reinterpret_cast<float*>(p.y)[(size_t)row * p.n_out + col] = o;
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(BN) : "memory");
+}
+
 }  // namespace
 
 extern "C" int b200q_tc_status_read_clear(int* status) {
@@ -143,6 +313,31 @@ extern "C" int b200q_gemm_f16(const void* a_f16, const void* w_f16, float* c, in
   if (((uintptr_t)a_f16 | (uintptr_t)w_f16) & 15) return B200Q_ERR_MISALIGNED;
   dim3 grid(ceil_div(n, BN), ceil_div(m, BM));
   tc_gemm_f16_kernel<<<grid, GEMM_THREADS, 0, (cudaStream_t)stream>>>((const __half*)a_f16, (const __half*)w_f16, c, m, n, k);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+extern "C" int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, void* y, int y_dtype, int m, int n_out,
+                           int n_in, void* stream) {
+  if (!w_packed || !x || !y || m <= 0 || n_out <= 0 || n_in <= 0) return B200Q_ERR_BAD_ARG;
+  if (qtype == B200Q_Q6_K) return B200Q_ERR_UNSUPPORTED;
+  if (qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
+  if ((x_dtype != B200Q_F32 && x_dtype != B200Q_F16) || (y_dtype != B200Q_F32 && y_dtype != B200Q_F16)) return B200Q_ERR_BAD_ARG;
+  if (n_in % 32) return B200Q_ERR_BAD_SHAPE;
+  if (((uintptr_t)w_packed | (uintptr_t)x) & 15) return B200Q_ERR_MISALIGNED;
+  QGemmParams p;
+  p.w = (const uint8_t*)w_packed; p.x = x; p.bias = (const __half*)bias_f16; p.y = y;
+  p.m = m; p.n_out = n_out; p.n_in = n_in; p.kgroups = ceil_div(n_in, GROUP_ELEMS); p.n_row_tiles = ceil_div(n_out, TILE_ROWS);
+  p.x_f16 = x_dtype == B200Q_F16; p.y_f16 = y_dtype == B200Q_F16;
+  dim3 grid(ceil_div(p.n_row_tiles, BN / 16), ceil_div(m, BM));
+  static bool attr = false;
+  if (!attr) {
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_kernel<B200Q_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, QGEMM_SMEM));
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_kernel<B200Q_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, QGEMM_SMEM));
+    attr = true;
+  }
+  if (qtype == B200Q_Q4_0) tc_qgemm_kernel<B200Q_Q4_0><<<grid, GEMM_THREADS, QGEMM_SMEM, (cudaStream_t)stream>>>(p);
+  else tc_qgemm_kernel<B200Q_Q8_0><<<grid, GEMM_THREADS, QGEMM_SMEM, (cudaStream_t)stream>>>(p);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -83,6 +83,14 @@ def gemv(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int = 1, x_dtyp
   check(_lib.load().b200q_gemv(ctypes.byref(a), stream_ptr(stream)))
 
 
+def qgemm(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int, x_dtype=F32, y_dtype=F32, bias=None, stream=None) -> None:
+  """Batched / prefill linear on the tcgen05 tensor cores: the weights are streamed once per 128 activation rows."""
+  check(_lib.load().b200q_qgemm(qtype, w_ptr, ptr_of(x), x_dtype, ptr_of(bias), ptr_of(y), y_dtype, m, n_out, n_in, stream_ptr(stream)))
+
+
+GEMM_MIN_ROWS = 4   # from this many activation rows on, QuantLinear uses the tensor-core GEMM instead of one GEMV per row
+
+
 class QuantLinear:
   """Drop-in for `nn.Linear` holding a GGUF-quantised weight.
 
@@ -100,6 +108,10 @@ class QuantLinear:
     if x.shape[-1] != self.in_features: raise ValueError(f"Input Tensor shapes {x.shape} cannot be multiplied with in_features={self.in_features}")
     m = int(np.prod(x.shape[:-1], dtype=np.int64))
     y = DeviceBuffer.empty((*x.shape[:-1], self.out_features), x.dtype)
-    if m: gemv(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m=m, x_dtype=_DT[x.dtype], y_dtype=_DT[x.dtype],
-               bias=self.bias, stream=stream)
+    if m >= GEMM_MIN_ROWS:
+      qgemm(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m, x_dtype=_DT[x.dtype], y_dtype=_DT[x.dtype],
+            bias=self.bias, stream=stream)
+    elif m:
+      gemv(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m=m, x_dtype=_DT[x.dtype], y_dtype=_DT[x.dtype],
+           bias=self.bias, stream=stream)
     return y
