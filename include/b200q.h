@@ -253,7 +253,10 @@ int b200q_moe_route(const float* logits, int n_tokens, int n_experts, int k, int
 int b200q_moe_combine(const void* y_bf16, const int32_t* dest_row, const float* weights, int n_tokens, int k, int d, void* out_bf16, void* stream);
 /* `grouped_mx_gemm` (extra/gemm/moe_gemm.py:112-134; kernel contract extra/thunder/amd/grouped_mxfp8_gemm.cpp:32-158):
  * C[m_total, n] bf16 = A_q[m_total, k] x B_q[e][n, k]^T with both operands' E8M0 scales, fp32 accumulation; rows
- * off[e]..off[e+1] use expert e; rows past off[n_experts] are left untouched.  m_total % 256 == n % 128 == k % 128 == 0. */
+ * off[e]..off[e+1] use expert e; rows past off[n_experts] are left untouched.  m_total % 256 == n % 256 == k % 128 == 0
+ * (the reference's own constraint, moe_gemm.py:120).  Runs on tcgen05 block-scaled MMAs (kind::mxf8f6f4.block_scale).
+ * b200q_mx_status_read_clear: like b200q_status_read_clear for this kernel's bounded waits. */
+int b200q_mx_status_read_clear(int* status);
 int b200q_grouped_mxfp8_gemm(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts,
                              int m_total, int n, int k, void* c_bf16, void* stream);
 

@@ -131,3 +131,11 @@ def test_moe_ffn_matches_composed_oracle():
     y = mx.to_bf16(mx.grouped_mx_gemm(act_q, act_e8, dn_q, dn_e8, off))
     ref = mx.to_bf16(mx.combine(y, dest, w))
     assert_close(out, ref, tol=1e-2, what=f"MoE FFN mode {mode}")
+
+
+def test_no_tensor_core_wait_ran_out():
+  import ctypes
+  from tinygrad_b200 import _lib
+  st = ctypes.c_int()
+  _lib.check(_lib.load().b200q_mx_status_read_clear(ctypes.byref(st)))
+  assert st.value == 0
