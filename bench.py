@@ -196,24 +196,35 @@ def run_moe_probe(args):
   for _ in range(steps): m(x, logits, T, stream=st)
   e1.record(st); st.synchronize()
   ms = e0.elapsed_ms(e1) / steps
-  # the two grouped GEMMs alone
+  # each phase alone, back to back on the same buffers
   lib = __import__("tinygrad_b200._lib", fromlist=["load"]).load()
-  r = m.last_routing
-  a_q, a_e8 = moe.quantize_mxfp8(x, T, D, 2, dest_row=r.dest_row, fan=k, out_rows=r.m_l)
-  h = runtime.DeviceBuffer.empty((r.m_l, 2 * F), np.uint16, zero=True)
-  runtime.synchronize()
-  e0.record(st)
-  for _ in range(steps): lib.b200q_grouped_mxfp8_gemm(a_q.ptr, a_e8.ptr, m.gu_q.ptr, m.gu_e8.ptr, r.off.ptr, E, r.m_l, 2 * F, D, h.ptr, st.ptr)
-  e1.record(st); st.synchronize()
-  ms_gemm1 = e0.elapsed_ms(e1) / steps
+  from tinygrad_b200._lib import BF16
+  r, ws = m.last_routing, m._ws
+  phases = {
+    "route": lambda: ws["r"].run(logits, st),
+    "zero_fill": lambda: (ws["a_q"].zero_(st), ws["a_e8"].zero_(st)),
+    "dispatch_quantize": lambda: lib.b200q_quantize_mxfp8(x.ptr, BF16, T, D, r.dest_row.ptr, k, ws["a_q"].ptr, ws["a_e8"].ptr, st.ptr),
+    "gate_up_gemm": lambda: lib.b200q_grouped_mxfp8_gemm(ws["a_q"].ptr, ws["a_e8"].ptr, m.gu_q.ptr, m.gu_e8.ptr, r.off.ptr, E, r.m_l, 2 * F, D, ws["h"].ptr, st.ptr),
+    "swiglu_quantize": lambda: lib.b200q_swiglu_quantize_mxfp8(ws["h"].ptr, r.m_l, F, ws["act_q"].ptr, ws["act_e8"].ptr, st.ptr),
+    "down_gemm": lambda: lib.b200q_grouped_mxfp8_gemm(ws["act_q"].ptr, ws["act_e8"].ptr, m.dn_q.ptr, m.dn_e8.ptr, r.off.ptr, E, r.m_l, D, F, ws["y"].ptr, st.ptr),
+    "combine": lambda: lib.b200q_moe_combine(ws["y"].ptr, r.dest_row.ptr, r.weights.ptr, T, k, D, ws["out"].ptr, st.ptr),
+  }
+  phase_ms = {}
+  for name, fn in phases.items():
+    runtime.synchronize()
+    e0.record(st)
+    for _ in range(steps): fn()
+    e1.record(st); st.synchronize()
+    phase_ms[name] = round(e0.elapsed_ms(e1) / steps, 4)
+  ms_gemm1 = phase_ms["gate_up_gemm"]
   flops = T * k * 3 * 2 * D * F
   peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {"bf16_tflops": 1590.0}
   fp8_peak = 2 * peaks["bf16_tflops"]
   print(json.dumps({"workload": "configs[3] one layer: OLMoE-shaped MXFP8 MoE FFN, 4096 tokens, 64 experts top-8, d 2048, f 1024",
                     "ms_per_layer": ms, "tflops": flops / ms / 1e9, "frac_of_fp8_peak": flops / ms / 1e9 / fp8_peak,
                     "fp8_peak": f"2 x measured bf16 burst = {fp8_peak} TFLOP/s (no fp8 entry in MEASURED_PEAKS.json)",
-                    "gate_up_gemm_ms": ms_gemm1, "gate_up_gemm_tflops": T * k * 2 * 2 * D * F / ms_gemm1 / 1e9,
-                    "contraction": "fp8 mma.sync m16n8k32 with fp32 block scaling (not yet tcgen05 block-scaled MMA)"}))
+                    "phase_ms": phase_ms, "gate_up_gemm_ms": ms_gemm1, "gate_up_gemm_tflops": T * k * 2 * 2 * D * F / ms_gemm1 / 1e9,
+                    "contraction": "tcgen05.mma kind::mxf8f6f4.block_scale, 128x256x128 tiles, TMEM accumulators"}))
 
 
 def run_tp_probe(args):

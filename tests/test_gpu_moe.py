@@ -50,7 +50,7 @@ def _route(logits, k, mode):
   from tinygrad_b200 import moe
   from tinygrad_b200.runtime import DeviceBuffer
   T, E = logits.shape
-  r = moe.Routing(DeviceBuffer.from_numpy(logits), T, E, k, mode)
+  r = moe.Routing(T, E, k, mode).run(DeviceBuffer.from_numpy(logits))
   return r, r.topi.numpy(), r.weights.numpy(), r.dest_row.numpy(), r.off.numpy()
 
 

@@ -32,39 +32,53 @@ def quantize_mxfp8(x: DeviceBuffer, rows: int, k: int, dtype: int, dest_row: Dev
 
 
 class Routing:
-  """Device tables of `route` (extra/gemm/moe_routing.py:92-122)."""
-  def __init__(self, logits: DeviceBuffer, n_tokens: int, n_experts: int, k: int, mode: int = ROUTE_TOPK_SOFTMAX, stream=None):
+  """Device tables of `route` (extra/gemm/moe_routing.py:92-122).  Buffers are allocated once and reused by `run`."""
+  def __init__(self, n_tokens: int, n_experts: int, k: int, mode: int = ROUTE_TOPK_SOFTMAX):
     lib = _lib.load()
-    self.n_tokens, self.n_experts, self.k = n_tokens, n_experts, k
+    self.n_tokens, self.n_experts, self.k, self.mode = n_tokens, n_experts, k, mode
     self.m_l = lib.b200q_moe_rows_max(n_tokens, n_experts, k)
     self.topi, self.weights = DeviceBuffer.empty((n_tokens, k), np.int32), DeviceBuffer.empty((n_tokens, k), np.float32)
     self.dest_row, self.off = DeviceBuffer.empty((n_tokens * k,), np.int32), DeviceBuffer.empty((n_experts + 1,), np.int32)
     self._scratch = DeviceBuffer(lib.b200q_moe_route_scratch_bytes(n_tokens, n_experts, k))
-    check(lib.b200q_moe_route(logits.ptr, n_tokens, n_experts, k, mode, self.topi.ptr, self.weights.ptr, self.dest_row.ptr, self.off.ptr,
-                              self._scratch.ptr, stream_ptr(stream)))
+
+  def run(self, logits: DeviceBuffer, stream=None) -> "Routing":
+    check(_lib.load().b200q_moe_route(logits.ptr, self.n_tokens, self.n_experts, self.k, self.mode, self.topi.ptr, self.weights.ptr,
+                                      self.dest_row.ptr, self.off.ptr, self._scratch.ptr, stream_ptr(stream)))
+    return self
 
 
 class MxMoE:
-  """Expert SwiGLU FFN with MXFP8 operands.  w_gate / w_up: (E, F, D), w_down: (E, D, F), fp32 numpy; quantised once along K."""
+  """Expert SwiGLU FFN with MXFP8 operands.  w_gate / w_up: (E, F, D), w_down: (E, D, F), fp32 numpy; quantised once along K.
+  The workspace for `n_tokens` tokens is allocated on the first call and reused: a call launches kernels only."""
   def __init__(self, w_gate: np.ndarray, w_up: np.ndarray, w_down: np.ndarray, k: int, mode: int = ROUTE_SOFTMAX_TOPK):
     self.E, self.F, self.D = w_gate.shape
     self.k, self.mode = k, mode
     gu = np.concatenate([w_gate, w_up], axis=1).astype(np.float32)          # (E, 2F, D): one GEMM yields [gate | up]
     self.gu_q, self.gu_e8 = quantize_mxfp8(DeviceBuffer.from_numpy(gu), self.E * 2 * self.F, self.D, F32)
     self.dn_q, self.dn_e8 = quantize_mxfp8(DeviceBuffer.from_numpy(w_down.astype(np.float32)), self.E * self.D, self.F, F32)
+    self._ws = None
+
+  def _workspace(self, n_tokens: int):
+    if self._ws is None or self._ws["T"] != n_tokens:
+      r = Routing(n_tokens, self.E, self.k, self.mode)
+      m = r.m_l
+      self._ws = dict(T=n_tokens, r=r, a_q=DeviceBuffer.empty((m, self.D), np.uint8), a_e8=DeviceBuffer.empty((m, self.D // 32), np.uint8),
+                      h=DeviceBuffer.empty((m, 2 * self.F), np.uint16, zero=True), act_q=DeviceBuffer.empty((m, self.F), np.uint8),
+                      act_e8=DeviceBuffer.empty((m, self.F // 32), np.uint8), y=DeviceBuffer.empty((m, self.D), np.uint16, zero=True),
+                      out=DeviceBuffer.empty((n_tokens, self.D), np.uint16))
+    return self._ws
 
   def __call__(self, x_bf16: DeviceBuffer, logits: DeviceBuffer, n_tokens: int, stream=None) -> DeviceBuffer:
     """x (T, D) bf16, router logits (T, E) fp32 -> (T, D) bf16."""
-    lib, s = _lib.load(), stream_ptr(stream)
-    r = Routing(logits, n_tokens, self.E, self.k, self.mode, stream)
-    a_q, a_e8 = quantize_mxfp8(x_bf16, n_tokens, self.D, BF16, dest_row=r.dest_row, fan=self.k, out_rows=r.m_l, stream=stream)
-    h = DeviceBuffer.empty((r.m_l, 2 * self.F), np.uint16, zero=True)
-    check(lib.b200q_grouped_mxfp8_gemm(a_q.ptr, a_e8.ptr, self.gu_q.ptr, self.gu_e8.ptr, r.off.ptr, self.E, r.m_l, 2 * self.F, self.D, h.ptr, s))
-    act_q, act_e8 = DeviceBuffer.empty((r.m_l, self.F), np.uint8), DeviceBuffer.empty((r.m_l, self.F // 32), np.uint8)
-    check(lib.b200q_swiglu_quantize_mxfp8(h.ptr, r.m_l, self.F, act_q.ptr, act_e8.ptr, s))
-    y = DeviceBuffer.empty((r.m_l, self.D), np.uint16, zero=True)
-    check(lib.b200q_grouped_mxfp8_gemm(act_q.ptr, act_e8.ptr, self.dn_q.ptr, self.dn_e8.ptr, r.off.ptr, self.E, r.m_l, self.D, self.F, y.ptr, s))
-    out = DeviceBuffer.empty((n_tokens, self.D), np.uint16)
-    check(lib.b200q_moe_combine(y.ptr, r.dest_row.ptr, r.weights.ptr, n_tokens, self.k, self.D, out.ptr, s))
+    lib, s, w = _lib.load(), stream_ptr(stream), self._workspace(n_tokens)
+    r = w["r"].run(logits, stream)
+    w["a_q"].zero_(stream); w["a_e8"].zero_(stream)                        # rows nobody is routed to stay zero (dispatch zero-fills)
+    check(lib.b200q_quantize_mxfp8(x_bf16.ptr, BF16, n_tokens, self.D, r.dest_row.ptr, self.k, w["a_q"].ptr, w["a_e8"].ptr, s))
+    check(lib.b200q_grouped_mxfp8_gemm(w["a_q"].ptr, w["a_e8"].ptr, self.gu_q.ptr, self.gu_e8.ptr, r.off.ptr, self.E, r.m_l, 2 * self.F, self.D,
+                                       w["h"].ptr, s))
+    check(lib.b200q_swiglu_quantize_mxfp8(w["h"].ptr, r.m_l, self.F, w["act_q"].ptr, w["act_e8"].ptr, s))
+    check(lib.b200q_grouped_mxfp8_gemm(w["act_q"].ptr, w["act_e8"].ptr, self.dn_q.ptr, self.dn_e8.ptr, r.off.ptr, self.E, r.m_l, self.D, self.F,
+                                       w["y"].ptr, s))
+    check(lib.b200q_moe_combine(w["y"].ptr, r.dest_row.ptr, r.weights.ptr, n_tokens, self.k, self.D, w["out"].ptr, s))
     self.last_routing = r
-    return out
+    return w["out"]
