@@ -238,8 +238,9 @@ int b200q_tc_status_read_clear(int* status);
  * extra/gemm/moe_routing.py:124-126; zero the outputs first: a zero row quantises to q = 0, e8 = 0). */
 int b200q_quantize_mxfp8(const void* x, int x_dtype, int64_t rows, int k, const int32_t* dest_row, int fan, void* q, void* e8, void* stream);
 /* act = silu(gate) * up from h = [gate | up] (bf16 [rows, 2f], the output of the fused gate/up expert GEMM), rounded to
- * bf16 and quantised as above (tinygrad/llm/model.py:129 between the expert GEMMs). */
-int b200q_swiglu_quantize_mxfp8(const void* h_bf16, int64_t rows, int f, void* q, void* e8, void* stream);
+ * bf16 and quantised as above (tinygrad/llm/model.py:129 between the expert GEMMs).  rows_used (device, may be NULL):
+ * only the first min(rows, *rows_used) rows are processed; pass off + n_experts to skip the unused tail of the row table. */
+int b200q_swiglu_quantize_mxfp8(const void* h_bf16, int64_t rows, const int32_t* rows_used, int f, void* q, void* e8, void* stream);
 /* Routing tables (`route`, extra/gemm/moe_routing.py:109-122): topi / weights [n_tokens, k], dest_row [n_tokens*k],
  * off [n_experts+1] (group starts, every group padded to 256 rows).  mode 0: top-k of the logits in descending order,
  * weights = softmax over the k (moe_routing.py:115-116).  mode 1: softmax over all experts, compare-count top-k in

@@ -74,7 +74,7 @@ SIGNATURES = {
   "b200q_qgemm": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
   "b200q_tc_status_read_clear": (c_int, [POINTER(c_int)]),
   "b200q_quantize_mxfp8": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
-  "b200q_swiglu_quantize_mxfp8": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+  "b200q_swiglu_quantize_mxfp8": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
   "b200q_moe_route_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
   "b200q_moe_rows_max": (c_int, [c_int, c_int, c_int]),
   "b200q_moe_route": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -21,52 +21,103 @@ constexpr int BLOCK_ROW = 256;   // extra/gemm/moe_routing.py:4
 // floor(log2()) is taken the way the reference's fp32 tensor op yields it: log2 rounded to fp32, then floor
 // (so an amax within half an fp32 ulp below a power of two lands on that power).
 __device__ __forceinline__ uint8_t mx_scale_exponent(float amax) {
+  const uint32_t bits = __float_as_uint(amax);
+  // at most 10 mantissa bits (any bf16 / fp16 value): log2 stays more than half an fp32 ulp below the next integer, so the
+  // floor is the exponent field itself (0 for everything below 2^-126, like the 1e-38 clamp; 255 = inf/nan clamps to 254)
+  if ((bits & 0x1FFFu) == 0) return (uint8_t)min((bits >> 23) & 0xFFu, 254u);
   const float lg = (float)log2((double)fmaxf(amax, 1e-38f));
   const float e = fminf(fmaxf(floorf(lg) + 127.f, 0.f), 254.f);
   return (uint8_t)e;
 }
-__device__ __forceinline__ uint8_t mx_quant_value(float x, uint8_t e8) {
-  const float xs = fminf(fmaxf(x * ldexpf(1.f, 127 - (int)e8), -448.f), 448.f);
-  return (uint8_t)__nv_cvt_float_to_fp8(xs, __NV_SATFINITE, __NV_E4M3);
+__device__ __forceinline__ float mx_inv_scale(uint8_t e8) {     // 2^(127 - e8), exact (2^-127 is a denormal)
+  return e8 < 254 ? __uint_as_float((uint32_t)(254 - e8) << 23) : __uint_as_float(0x00400000u);
+}
+// eight values -> eight E4M3 codes (round to nearest even, saturating), element i in byte i
+__device__ __forceinline__ uint2 mx_quant8(const float (&v)[8], uint8_t e8) {
+  const float sc = mx_inv_scale(e8);
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    uint32_t acc = 0;
+#pragma unroll
+    for (int p = 0; p < 2; p++) {
+      const float a = fminf(fmaxf(v[h * 4 + p * 2] * sc, -448.f), 448.f), b = fminf(fmaxf(v[h * 4 + p * 2 + 1] * sc, -448.f), 448.f);
+      acc |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3) << (16 * p);
+    }
+    w[h] = acc;
+  }
+  return make_uint2(w[0], w[1]);
+}
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& u, float (&v)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+}
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  bf16x8_to_f32(*reinterpret_cast<const uint4*>(p), v);
+}
+__device__ __forceinline__ float amax8_quad(const float (&v)[8]) {      // |max| over the 32 values held by 4 neighbouring lanes
+  float m = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) m = fmaxf(m, fabsf(v[i]));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+  return fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
 }
 
-template <typename T> __device__ __forceinline__ float to_f32(T v);
-template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
-template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-
-// rows of x go to rows dest[r] of the outputs (dest == nullptr: identity); `fan` consecutive dest entries per input row
+// One warp per 256 consecutive values of a row: 4 lanes share a block of 32, a lane holds 8 values (16-byte loads, 8-byte stores).
+// Rows of x go to rows dest[r] of the outputs (dest == nullptr: identity); `fan` consecutive dest entries per input row.
 template <typename T>
 __global__ void quantize_mxfp8_kernel(const T* __restrict__ x, int64_t rows, int k, const int32_t* __restrict__ dest, int fan,
                                       uint8_t* __restrict__ q, uint8_t* __restrict__ e8) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int kb = k >> 5;
-  if (warp >= rows * kb) return;
-  const int64_t r = warp / kb; const int b = (int)(warp - r * kb);
-  const float v = to_f32<T>(x[r * k + b * 32 + lane]);
-  const float amax = warp_max(fabsf(v));
-  const uint8_t e = mx_scale_exponent(amax);
-  const uint8_t qv = mx_quant_value(v, e);
+  const int kb = k >> 5, chunks = (kb + 7) >> 3;
+  if (warp >= rows * chunks) return;
+  const int64_t r = warp / chunks;
+  const int b = (int)(warp - r * chunks) * 8 + (lane >> 2), col = b * 32 + (lane & 3) * 8;
+  const bool valid = b < kb;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (valid) load8<T>(x + r * k + col, v);
+  const uint8_t e = mx_scale_exponent(amax8_quad(v));
+  const uint2 pk = mx_quant8(v, e);
+  if (!valid) return;
   for (int f = 0; f < fan; f++) {
     const int64_t o = dest ? (int64_t)dest[r * fan + f] : r;
-    q[o * k + b * 32 + lane] = qv;
-    if (lane == 0) e8[o * kb + b] = e;
+    *reinterpret_cast<uint2*>(q + o * k + col) = pk;
+    if ((lane & 3) == 0) e8[o * kb + b] = e;
   }
 }
 
 // SwiGLU between the two expert GEMMs: h = [gate | up] (bf16, [m, 2f]) -> act = silu(gate) * up computed in fp32,
-// rounded to bf16 as a tensor would be stored, then quantised like any activation.
-__global__ void swiglu_quant_kernel(const __nv_bfloat16* __restrict__ h, int64_t rows, int f, uint8_t* __restrict__ q, uint8_t* __restrict__ e8) {
+// rounded to bf16 as a tensor would be stored, then quantised like any activation.  Same work split as the quantiser.
+__global__ void swiglu_quant_kernel(const __nv_bfloat16* __restrict__ h, int64_t rows, const int32_t* __restrict__ rows_used, int f,
+                                    uint8_t* __restrict__ q, uint8_t* __restrict__ e8) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int kb = f >> 5;
-  if (warp >= rows * kb) return;
-  const int64_t r = warp / kb; const int b = (int)(warp - r * kb);
-  const float g = __bfloat162float(h[r * 2 * f + b * 32 + lane]), u = __bfloat162float(h[r * 2 * f + f + b * 32 + lane]);
-  const float v = __bfloat162float(__float2bfloat16_rn((g / (1.f + expf(-g))) * u));
-  const uint8_t e = mx_scale_exponent(warp_max(fabsf(v)));
-  q[r * f + b * 32 + lane] = mx_quant_value(v, e);
-  if (lane == 0) e8[r * kb + b] = e;
+  const int kb = f >> 5, chunks = (kb + 7) >> 3;
+  if (rows_used) rows = min(rows, (int64_t)*rows_used);
+  if (warp >= rows * chunks) return;
+  const int64_t r = warp / chunks;
+  const int b = (int)(warp - r * chunks) * 8 + (lane >> 2), col = b * 32 + (lane & 3) * 8;
+  const bool valid = b < kb;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (valid) {
+    float g[8], u[8];
+    load8<__nv_bfloat16>(h + r * 2 * f + col, g);
+    load8<__nv_bfloat16>(h + r * 2 * f + f + col, u);
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __bfloat162float(__float2bfloat16_rn((g[i] / (1.f + expf(-g[i]))) * u[i]));
+  }
+  const uint8_t e = mx_scale_exponent(amax8_quad(v));
+  const uint2 pk = mx_quant8(v, e);
+  if (!valid) return;
+  *reinterpret_cast<uint2*>(q + r * f + col) = pk;
+  if ((lane & 3) == 0) e8[r * kb + b] = e;
 }
 
 // ---------------------------------------------------------------------------
@@ -181,6 +232,26 @@ __global__ void combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_
     out[(size_t)t * d + c] = __float2bfloat16_rn(acc);
   }
 }
+// d % 8 == 0: a thread sums 8 neighbouring columns over the k rows (16-byte loads), same order of additions
+__global__ void combine8_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ dest_row, const float* __restrict__ weights,
+                                int n_tokens, int k, int d, __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; j++) {
+      const float w = weights[(size_t)t * k + j];
+      float v[8];
+      load8<__nv_bfloat16>(y + (size_t)dest_row[(size_t)t * k + j] * d + c, v);
+#pragma unroll
+      for (int i = 0; i < 8; i++) acc[i] += w * v[i];
+    }
+    uint4 pk;
+    __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+    for (int i = 0; i < 4; i++) hp[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    *reinterpret_cast<uint4*>(out + (size_t)t * d + c) = pk;
+  }
+}
 
 }  // namespace
 
@@ -190,7 +261,8 @@ extern "C" int b200q_quantize_mxfp8(const void* x, int x_dtype, int64_t rows, in
   if (k % 32) return B200Q_ERR_BAD_SHAPE;
   if (dest_row ? fan <= 0 : fan != 1) return B200Q_ERR_BAD_ARG;
   if (rows == 0) return B200Q_OK;
-  const int64_t warps = rows * (k / 32);
+  if (((uintptr_t)x | (uintptr_t)q) & 15) return B200Q_ERR_MISALIGNED;
+  const int64_t warps = rows * ((k / 32 + 7) / 8);
   const unsigned blocks = (unsigned)((warps + 7) / 8);
   if (x_dtype == B200Q_F32) quantize_mxfp8_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)x, rows, k, dest_row, fan, (uint8_t*)q, (uint8_t*)e8);
   else quantize_mxfp8_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, rows, k, dest_row, fan, (uint8_t*)q, (uint8_t*)e8);
@@ -198,12 +270,14 @@ extern "C" int b200q_quantize_mxfp8(const void* x, int x_dtype, int64_t rows, in
   return B200Q_OK;
 }
 
-extern "C" int b200q_swiglu_quantize_mxfp8(const void* h_bf16, int64_t rows, int f, void* q, void* e8, void* stream) {
+extern "C" int b200q_swiglu_quantize_mxfp8(const void* h_bf16, int64_t rows, const int32_t* rows_used, int f, void* q, void* e8, void* stream) {
   if (rows < 0 || f <= 0 || (rows && (!h_bf16 || !q || !e8))) return B200Q_ERR_BAD_ARG;
   if (f % 32) return B200Q_ERR_BAD_SHAPE;
+  if (((uintptr_t)h_bf16 | (uintptr_t)q) & 15) return B200Q_ERR_MISALIGNED;
   if (rows == 0) return B200Q_OK;
-  const int64_t warps = rows * (f / 32);
-  swiglu_quant_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)h_bf16, rows, f, (uint8_t*)q, (uint8_t*)e8);
+  const int64_t warps = rows * ((f / 32 + 7) / 8);
+  swiglu_quant_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)h_bf16, rows, rows_used, f, (uint8_t*)q,
+                                                                                       (uint8_t*)e8);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -235,7 +309,10 @@ extern "C" int b200q_moe_route(const float* logits, int n_tokens, int n_experts,
 extern "C" int b200q_moe_combine(const void* y_bf16, const int32_t* dest_row, const float* weights, int n_tokens, int k, int d, void* out_bf16,
                                  void* stream) {
   if (!y_bf16 || !dest_row || !weights || !out_bf16 || n_tokens <= 0 || k <= 0 || d <= 0) return B200Q_ERR_BAD_ARG;
-  combine_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)y_bf16, dest_row, weights, n_tokens, k, d, (__nv_bfloat16*)out_bf16);
+  if (d % 8 == 0 && !(((uintptr_t)y_bf16 | (uintptr_t)out_bf16) & 15))
+    combine8_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)y_bf16, dest_row, weights, n_tokens, k, d, (__nv_bfloat16*)out_bf16);
+  else
+    combine_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)y_bf16, dest_row, weights, n_tokens, k, d, (__nv_bfloat16*)out_bf16);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

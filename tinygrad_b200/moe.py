@@ -76,7 +76,7 @@ class MxMoE:
     check(lib.b200q_quantize_mxfp8(x_bf16.ptr, BF16, n_tokens, self.D, r.dest_row.ptr, self.k, w["a_q"].ptr, w["a_e8"].ptr, s))
     check(lib.b200q_grouped_mxfp8_gemm(w["a_q"].ptr, w["a_e8"].ptr, self.gu_q.ptr, self.gu_e8.ptr, r.off.ptr, self.E, r.m_l, 2 * self.F, self.D,
                                        w["h"].ptr, s))
-    check(lib.b200q_swiglu_quantize_mxfp8(w["h"].ptr, r.m_l, self.F, w["act_q"].ptr, w["act_e8"].ptr, s))
+    check(lib.b200q_swiglu_quantize_mxfp8(w["h"].ptr, r.m_l, r.off.ptr + 4 * self.E, self.F, w["act_q"].ptr, w["act_e8"].ptr, s))
     check(lib.b200q_grouped_mxfp8_gemm(w["act_q"].ptr, w["act_e8"].ptr, self.dn_q.ptr, self.dn_e8.ptr, r.off.ptr, self.E, r.m_l, self.D, self.F,
                                        w["y"].ptr, s))
     check(lib.b200q_moe_combine(w["y"].ptr, r.dest_row.ptr, r.weights.ptr, n_tokens, self.k, self.D, w["out"].ptr, s))
