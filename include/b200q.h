@@ -151,7 +151,16 @@ typedef struct b200q_gemv_args {
                                `y` may then be NULL if nobody needs the fp32 values */
   const void* xq_out_norm_weight;
   float* ss_out;            /* device [n_out / 32] partial sums of squares of the output row, or NULL */
-  float residual_scale;     /* the residual is multiplied by this before it is added; 0 means 1.  A row-parallel shard of a
+  float residual_scale;     /* Dense (unquantised) Linear at decode: y[m, n_out] = f(x)[m, n_in] . W[n_out, n_in]^T for a weight stored row-major
+ * as fp16, bf16 or fp32 (w_dtype) - the Linears a GGUF file leaves unquantised (router ffn_gate_inp, F16 models) or in a
+ * block format without a fused kernel (Q6_K output heads, after b200q_dequant_raw to fp16).  Replaces Linear.__call__
+ * (tinygrad/nn/__init__.py:177) for those; f = optional RMSNorm with norm_weight (fp16 [n_in]) as in b200q_gemv; bias fp16
+ * [n_out]; residual / y in y_dtype.  fp32 products and accumulation.  m <= 4, n_in % 8 == 0, m * n_in * 4 <= 200 KiB.
+ * flags: B200Q_FLAG_PDL. */
+int b200q_gemv_dense(const void* w, int w_dtype, int n_out, int n_in, int m, const void* x, int x_dtype, const void* norm_weight,
+                     float norm_eps, const void* bias, const void* residual, void* y, int y_dtype, int flags, void* stream);
+
+/* the residual is multiplied by this before it is added; 0 means 1.  A row-parallel shard of a
                                tensor-parallel linear adds residual / n_ranks so that the all-reduce of the shards yields
                                W x + residual (tinygrad shards the same linears by axis, examples/llama3.py:233-243) */
 } b200q_gemv_args;
@@ -220,13 +229,29 @@ int b200q_advance(int32_t* device_pos, int flags, void* stream);
  * one activation row (tinygrad/nn/__init__.py:177), as the prefill chunks of tinygrad/llm/model.py:464-481 need it.
  * k % 64 == 0; a and w 16-byte aligned.  b200q_tc_status_read_clear: like b200q_status_read_clear for these kernels. */
 int b200q_gemm_f16(const void* a_f16, const void* w_f16, float* c, int m, int n, int k, void* stream);
-/* The same contraction with W as packed Q4_0 / Q8_0 tiles (b200q_repack, not interleaved), dequantised to fp16 on the way
- * into shared memory -- bit-identical to the reference's materialised fp16 weight (tinygrad/llm/model.py:376) --, x [m, n_in]
- * fp16 or fp32 (rounded to fp16 for the tensor core), optional fp16 bias [n_out], y [m, n_out] fp32 or fp16.
- * The weights are streamed once per 128 activation rows: the prefill / batched-decode counterpart of b200q_gemv.
- * x rows must be 16-byte aligned (n_in % 8 == 0 for fp16, % 4 for fp32: any n_in % 32 == 0 is). */
-int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, void* y, int y_dtype, int m, int n_out,
-                int n_in, void* stream);
+/* The same contraction with W as packed Q4_0 / Q8_0 tiles (b200q_repack), dequantised to fp16 on the way into shared
+ * memory -- bit-identical to the reference's materialised fp16 weight (tinygrad/llm/model.py:376) --, x [m, n_in] fp16 or
+ * fp32, y fp32 or fp16.  fp16 x: one MMA pass with the fp16-rounded weight (the reference's fp16-activation numerics).  fp32 x:
+ * x and the weight both go in as fp16 hi + lo pairs (three MMA passes), which reproduces the reference's fp32 x times unrounded
+ * dequantised weight (tinygrad/codegen/late/coalesce.py:100 elides the fp16 cast there) to about 2^-22.  epilogue B200Q_EPI_LINEAR: y [m, n_out] = result + optional
+ * fp16 bias [n_out] + optional residual [m, n_out] in y_dtype (may alias y).  B200Q_EPI_SILU_MUL: W is the interleaved
+ * gate/up matrix (n_out = its 2 * hidden rows) and y [m, n_out / 2] = silu(gate) * up (tinygrad/llm/model.py:137); no bias or
+ * residual.  The weights are streamed once per 128 activation rows: the prefill / batched counterpart of b200q_gemv.
+ * x rows must be 16-byte aligned (any n_in % 32 == 0 is). */
+int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue, void* y,
+                int y_dtype, int m, int n_out, int n_in, void* stream);
+/* ---- prompt processing: the row-wise pieces of Transformer.forward for T > 1 tokens (tinygrad/llm/model.py:358-364,167-198)
+ * b200q_embed_rows:   x [n_rows, dim] fp32 = token_embd[tokens[t]] (tokens on the device).
+ * b200q_rmsnorm_rows: out [n_rows, dim] (out_dtype fp16 / fp32) = RMSNorm(x) * weight (tinygrad/nn/__init__.py:300-304).
+ * b200q_attn_prefill: qkv [n_rows, (n_heads + 2 n_kv_heads) * head_dim] fp32 holds the projections of the tokens at
+ *   positions start_pos .. start_pos + n_rows - 1.  Rotates q and k (half-split RoPE table [max_context, rope_dim] = cos || sin),
+ *   appends k / v to the caches [n_kv_heads, max_context, head_dim] (kv_dtype) and writes the causal attention of every new
+ *   query over cache rows 0 .. its own position to out [n_rows, n_heads * head_dim] (out_dtype fp16 / fp32).  q_scratch: n_rows * n_heads * head_dim
+ *   floats.  Queries and probabilities enter the tensor core as fp16 hi + lo pairs, keys / values as cached.  head_dim in {16, 32, 64, 128}. */
+int b200q_embed_rows(const void* table_f16, const int32_t* tokens, int n_rows, int dim, int vocab, float* x, void* stream);
+int b200q_rmsnorm_rows(const float* x, const void* weight_f16, float eps, int n_rows, int dim, void* out, int out_dtype, void* stream);
+int b200q_attn_prefill(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int start_pos, int n_rows, int n_heads,
+                       int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out, int out_dtype, void* stream);
 int b200q_tc_status_read_clear(int* status);
 
 /* ---- MXFP8 mixture-of-experts path --------------------------------------

@@ -146,3 +146,22 @@ if "mxfp8" in groups:
   out.update({"route_logits": logits, "route_weights": r.weights.numpy(), "route_dest_row": r.dest_row.numpy(),
               "route_off": r.off.numpy(), "route_m_l": np.array(r.m_l)})
   save("mxfp8", **out)
+
+if "gguf" in groups:
+  # a GGUF file image of a tiny llama-family model: the reference's parser output and its greedy stream from Transformer.from_gguf
+  # (which applies the family's q/k RoPE row permutation and the fp16 cast of every tensor)
+  import json
+  from tinygrad.llm.gguf import gguf_load
+  cfg = tiny_cfg()
+  img = synth.dense_model_gguf(cfg, 2, seed=5, embd_std=0.5, output="f16")
+  kv, sd = gguf_load(Tensor(np.frombuffer(img, dtype=np.uint8)))
+  out = {"image": np.frombuffer(img, dtype=np.uint8), "kv_json": np.frombuffer(json.dumps({k: v for k, v in kv.items()}).encode(), dtype=np.uint8)}
+  for name in ("blk.0.attn_q.weight", "blk.1.ffn_down.weight", "token_embd.weight", "output.weight", "blk.0.attn_norm.weight"):
+    out["t:" + name] = sd[name].numpy()
+  model, _ = Transformer.from_gguf(Tensor(np.frombuffer(img, dtype=np.uint8)), max_context=80)
+  toks, t0 = [], time.time()
+  for tok in model.generate([3, 14, 15, 92, 65, 35], chunk_size=32, temperature=0.0):
+    toks.append(tok); print("gguf", len(toks), tok, f"{time.time()-t0:.0f}s", flush=True)
+    if len(toks) >= 48: break
+  out["prompt"], out["tokens"] = np.array([3, 14, 15, 92, 65, 35]), np.array(toks)
+  save("gguf_llama_tiny", **out)

@@ -132,3 +132,44 @@ def test_argmax_lowest_index_wins_ties_and_advances():
 def test_no_kernel_wait_ran_out():
   from tinygrad_b200 import runtime
   assert runtime.device_status() == 0
+
+
+def test_from_gguf_stream_identical_to_reference(golden):
+  """A GGUF file image through the loader (metadata -> config, llama q/k RoPE row permutation, F16 head on the dense GEMV):
+  the same greedy stream as the reference's Transformer.from_gguf on the same image."""
+  from tinygrad_b200 import gguf
+  g = golden("gguf_llama_tiny")
+  m, kv = gguf.transformer_from_gguf(g["image"].tobytes(), max_context=80, kv_dtype="float32")
+  assert kv["general.architecture"] == "llama" and m.output_type == 1
+  want, got = [int(t) for t in g["tokens"]], []
+  for tok in m.generate([int(t) for t in g["prompt"]]):
+    got.append(tok)
+    if len(got) == len(want): break
+  assert got == want
+
+
+@pytest.mark.parametrize("output", ["q6_k", "tied", "same"])
+def test_from_gguf_output_head_variants(output):
+  """Q6_K, tied (token_embd) and same-type output heads of a qwen2-family file against the oracle."""
+  from tinygrad_b200 import gguf
+  from tinygrad_b200.model import TransformerConfig
+  kw = dict(num_blocks=2, dim=256, hidden_dim=512, n_heads=4, n_kv_heads=2, norm_eps=1e-6, vocab_size=320, head_dim=64, rope_theta=10000.0,
+            rope_dim=64, max_context=64, qkv_bias=True)
+  cfg = TransformerConfig(**kw)
+  img = synth.dense_model_gguf(cfg, 8, seed=21, arch="qwen2", embd_std=0.3, output=output)
+  kv, t = gguf.gguf_load(img)
+  sd = synth.dense_model_raw(cfg, 8, seed=21, embd_std=0.3)
+  w = _oracle_weights(cfg, sd, 8)
+  head = t.get("output.weight", t["token_embd.weight"])
+  if output != "same":
+    w["output.weight"] = (gq.dequantize(head.data, head.n_elems, 14).astype(np.float16) if head.ggml_type == 14 else head.numpy()) \
+                           .astype(np.float32).reshape(cfg.vocab_size, cfg.dim)
+  prompt = [5, 17, 300, 2, 9]
+  want = llm.Transformer(llm.Config(**kw, kv_dtype="float16"), w).generate(prompt, 16)
+  m, _ = gguf.transformer_from_gguf(img)
+  assert m.config.qkv_bias and m.output_type == {"q6_k": 14, "tied": 1, "same": 8}[output]
+  got = []
+  for tok in m.generate(prompt):
+    got.append(tok)
+    if len(got) == 16: break
+  assert got == want

@@ -159,7 +159,9 @@ def test_no_kernel_wait_ran_out():
                                                            ("q4_0", 130, 4096, 4096, np.float32, False), ("q8_0", 8, 512, 3584, np.float32, True),
                                                            ("q8_0", 32, 48, 160, np.float16, False), ("q4_0", 32, 14336, 4096, np.float32, False)])
 def test_tensor_core_gemm_matches_fp16_operand_reference(tag, m, n_out, n_in, x_dtype, bias):
-  """tcgen05 path (several activation rows): operands are the fp16 activations and the materialised fp16 weights."""
+  """tcgen05 path (several activation rows).  fp16 activations: the operands are the activations and the materialised fp16
+  weights, as in the reference's fp16 Linear.  fp32 activations: hi + lo halves of both operands, i.e. the fp32 activation times
+  the unrounded dequantised weight, as in the reference's fused fp32 kernels."""
   from tinygrad_b200 import quant, _lib
   quant.GEMM_MIN_ROWS = 4
   from tinygrad_b200.runtime import DeviceBuffer
@@ -170,13 +172,58 @@ def test_tensor_core_gemm_matches_fp16_operand_reference(tag, m, n_out, n_in, x_
   b = rng.standard_normal(n_out).astype(np.float16) if bias else None
   lin = quant.QuantLinear(n_in, n_out, typ, raw, bias=b)
   y = lin(DeviceBuffer.from_numpy(x)).numpy()
-  w16 = gq.weight_matrix(raw, n_out, n_in, typ).astype(np.float16).astype(np.float32)
-  ref = x.astype(np.float16).astype(np.float32) @ w16.T + (b.astype(np.float32) if bias else 0.0)
   assert y.dtype == x_dtype and y.shape == (m, n_out)
-  assert_close(y, ref, tol=2e-3 if x_dtype == np.float32 else 4e-3, what="tcgen05 GEMM vs fp16-operand reference")
-  # against the exact-weight fp32 product the only difference is the fp16 rounding of both operands (what the reference
-  # itself computes with when a Linear is called on fp16 activations): a few 1e-3 of the output scale
   ref32 = llm.linear(x.astype(np.float32), gq.weight_matrix(raw, n_out, n_in, typ), b)
-  assert np.abs(y.astype(np.float32) - ref32).max() <= 4e-3 * max(1.0, np.abs(ref32).max())
+  if x_dtype == np.float32:
+    assert_close(y, ref32, tol=1e-2, what="tcgen05 GEMM vs fp32 reference")
+    assert np.abs(y - ref32).max() <= 2e-5 * max(1.0, np.abs(ref32).max())       # only the accumulation order differs
+  else:
+    w16 = gq.weight_matrix(raw, n_out, n_in, typ).astype(np.float16).astype(np.float32)
+    ref = x.astype(np.float32) @ w16.T + (b.astype(np.float32) if bias else 0.0)
+    assert_close(y, ref, tol=4e-3, what="tcgen05 GEMM vs fp16-operand reference")
+    # against the exact-weight product the difference is the fp16 rounding of the weight and of the fp16 result
+    assert np.abs(y.astype(np.float32) - ref32).max() <= 4e-3 * max(1.0, np.abs(ref32).max())
   st = ctypes.c_int(); _lib.check(_lib.load().b200q_tc_status_read_clear(ctypes.byref(st)))
   assert st.value == 0
+
+
+@pytest.mark.parametrize("kind,n_out,n_in,m", [("f16", 64, 2048, 1), ("f32", 100, 256, 3), ("bf16", 37, 512, 4), ("q6_k", 48, 1024, 2),
+                                              ("f16", 8, 4096, 6)])
+def test_dense_weight_linear(kind, n_out, n_in, m):
+  """Linears whose weights stay unquantised (F16 / F32 / BF16 tensors) or are Q6_K: the dense GEMV against the oracle's linear."""
+  from tinygrad_b200 import quant, moe
+  from tinygrad_b200.runtime import DeviceBuffer
+  rng = np.random.default_rng(11)
+  if kind == "q6_k":
+    raw, typ = synth.q6_k_blocks(n_out, n_in, rng), 14
+    w = gq.dequantize(raw, n_out * n_in, 14).astype(np.float16).astype(np.float32).reshape(n_out, n_in)
+  else:
+    w = (rng.standard_normal((n_out, n_in)) * 0.05).astype(np.float32)
+    if kind == "f16": raw, typ, w = w.astype(np.float16), quant.GGML_F16, w.astype(np.float16).astype(np.float32)
+    elif kind == "bf16": raw, typ = moe.to_bf16_bits(w), quant.GGML_BF16; w = moe.from_bf16_bits(raw)
+    else: raw, typ = w, quant.GGML_F32
+  bias = rng.standard_normal(n_out).astype(np.float16)
+  lin = quant.QuantLinear(n_in, n_out, typ, raw, bias=bias)
+  for dt in (np.float32, np.float16):
+    x = rng.standard_normal((m, n_in)).astype(dt)
+    y = lin(DeviceBuffer.from_numpy(x)).numpy()
+    assert y.dtype == dt and y.shape == (m, n_out)
+    ref = llm.linear(x.astype(np.float32), w, bias)
+    assert_close(y, ref, tol=1e-2)
+    assert np.abs(y.astype(np.float32) - ref).max() <= (2e-3 if dt == np.float16 else 1e-5) * max(1.0, np.abs(ref).max())
+
+
+def test_dense_fused_norm_and_residual():
+  from tinygrad_b200 import quant, _lib
+  from tinygrad_b200.runtime import DeviceBuffer
+  rng = np.random.default_rng(12)
+  n_out, n_in = 72, 768
+  w = (rng.standard_normal((n_out, n_in)) * 0.05).astype(np.float16)
+  x = rng.standard_normal(n_in).astype(np.float32) * 2
+  nw = (1 + 0.1 * rng.standard_normal(n_in)).astype(np.float16)
+  res = rng.standard_normal(n_out).astype(np.float32)
+  dy = DeviceBuffer.from_numpy(res)
+  quant.gemv_dense(DeviceBuffer.from_numpy(w), _lib.F16, n_out, n_in, DeviceBuffer.from_numpy(x), dy, norm_weight=DeviceBuffer.from_numpy(nw),
+                   norm_eps=1e-5, residual=dy)
+  ref = res + llm.linear(llm.rmsnorm(x[None], nw, 1e-5), w.astype(np.float32))[0]
+  assert np.abs(dy.numpy() - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max())

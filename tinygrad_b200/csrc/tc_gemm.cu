@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) tc_gemm_f16_kernel(const __half*
 // K order inside every 8-element core is [0,2,1,3,4,6,5,7] for both operands (that is how the nibble / byte unpack
 // delivers pairs); a contraction does not care as long as A and W agree.
 constexpr int QBK = 128;                          // one packed column group per K step
-constexpr int QGEMM_SMEM = (BM + BN) * QBK * 2;   // 64 KB
+constexpr int QGEMM_SMEM = 2 * (BM + BN) * QBK * 2;     // activations and weights, each as a high and a low fp16 half: 128 KB
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) { uint32_t d; asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
 __device__ __forceinline__ uint32_t h2sub(uint32_t a, uint32_t b) { uint32_t d; asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
@@ -142,9 +142,18 @@ __device__ __forceinline__ uint32_t h2mul(uint32_t a, uint32_t b) { uint32_t d; 
 __device__ __forceinline__ uint32_t h2fma(uint32_t a, uint32_t b, uint32_t c) { uint32_t d; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d; }
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) { uint32_t d; asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel)); return d; }
 
+// q * d for four pairs: the fp16 product (hi, = the reference's materialised fp16 weight) and its exact remainder
+// lo = q * d - hi (one fused multiply-add: the remainder has at most 8 significant bits, so it is exact).  hi + lo is the
+// fp32 value the reference's fused kernels use when the activations are fp32 (tinygrad/codegen/late/coalesce.py:100).
+__device__ __forceinline__ uint4 hi_lo(const uint32_t (&r)[4], uint32_t d2, uint4& lo) {
+  const uint4 hi = make_uint4(h2mul(r[0], d2), h2mul(r[1], d2), h2mul(r[2], d2), h2mul(r[3], d2));
+  lo = make_uint4(h2fma(r[0], d2, hi.x ^ 0x80008000u), h2fma(r[1], d2, hi.y ^ 0x80008000u), h2fma(r[2], d2, hi.z ^ 0x80008000u),
+                  h2fma(r[3], d2, hi.w ^ 0x80008000u));
+  return hi;
+}
 // 8 nibbles of two words (bytes 0..7 of a 16-byte half) -> one core row of 8 fp16 weights, low (HI = false) or high nibbles
 template <bool HI>
-__device__ __forceinline__ uint4 q4_core(uint32_t wa, uint32_t wb, uint32_t d2) {
+__device__ __forceinline__ uint4 q4_core(uint32_t wa, uint32_t wb, uint32_t d2, uint4& lo) {
   const uint32_t MAGIC = 0x64006400u;
   uint32_t r[4];
   const uint32_t w[2] = {wa, wb};
@@ -159,19 +168,20 @@ __device__ __forceinline__ uint4 q4_core(uint32_t wa, uint32_t wb, uint32_t d2) 
       r[2 * i + 1] = h2fma(lop3_and_or(v, 0x00F000F0u, MAGIC), 0x2C002C00u, 0xD480D480u);
     }
   }
-  return make_uint4(h2mul(r[0], d2), h2mul(r[1], d2), h2mul(r[2], d2), h2mul(r[3], d2));
+  return hi_lo(r, d2, lo);
 }
 // 8 int8 of two words -> one core row of 8 fp16 weights
-__device__ __forceinline__ uint4 q8_core(uint32_t wa, uint32_t wb, uint32_t d2) {
+__device__ __forceinline__ uint4 q8_core(uint32_t wa, uint32_t wb, uint32_t d2, uint4& lo) {
   const uint32_t HIB = 0x64646464u, SUB = 0x64806480u;     // 0x64bb = 1024 + (b ^ 0x80) = 1152 + b
   const uint32_t xa = wa ^ 0x80808080u, xb = wb ^ 0x80808080u;
-  return make_uint4(h2mul(h2sub(prmt(xa, HIB, 0x4240u), SUB), d2), h2mul(h2sub(prmt(xa, HIB, 0x4341u), SUB), d2),
-                    h2mul(h2sub(prmt(xb, HIB, 0x4240u), SUB), d2), h2mul(h2sub(prmt(xb, HIB, 0x4341u), SUB), d2));
+  const uint32_t r[4] = {h2sub(prmt(xa, HIB, 0x4240u), SUB), h2sub(prmt(xa, HIB, 0x4341u), SUB), h2sub(prmt(xb, HIB, 0x4240u), SUB),
+                         h2sub(prmt(xb, HIB, 0x4341u), SUB)};
+  return hi_lo(r, d2, lo);
 }
 
 struct QGemmParams {
-  const uint8_t* w; const void* x; const __half* bias; void* y;
-  int m, n_out, n_in, kgroups, n_row_tiles, x_f16, y_f16;
+  const uint8_t* w; const void* x; const __half* bias; const void* residual; void* y;
+  int m, n_out, n_in, kgroups, n_row_tiles, x_f16, y_f16, silu_mul;
 };
 
 template <int QT>
@@ -179,6 +189,10 @@ __global__ void __launch_bounds__(GEMM_THREADS) tc_qgemm_kernel(const QGemmParam
   extern __shared__ __align__(128) unsigned char qsm[];
   unsigned char* sA = qsm;
   unsigned char* sB = qsm + BM * QBK * 2;
+  // fp32 activations: x = hi + lo and w = hi + lo (all fp16), y = xh wh + xl wh + xh wl: what the reference's fused fp32 kernels
+  // compute (fp32 x times the unrounded dequantised weight) to about 2^-22.  fp16 activations: hi halves only (fp16-rounded weight).
+  unsigned char* sA2 = sB + BN * QBK * 2;
+  unsigned char* sB2 = sA2 + BM * QBK * 2;
   __shared__ __align__(8) uint64_t bar;
   __shared__ uint32_t tmem_base;
   constexpr int TB = tile_bytes(QT);
@@ -223,6 +237,12 @@ __global__ void __launch_bounds__(GEMM_THREADS) tc_qgemm_kernel(const QGemmParam
       }
       __half2 o[4] = {__floats2half2_rn(f[0], f[2]), __floats2half2_rn(f[1], f[3]), __floats2half2_rn(f[4], f[6]), __floats2half2_rn(f[5], f[7])};
       *reinterpret_cast<uint4*>(sA + tile_off(r, kc, BM)) = *reinterpret_cast<const uint4*>(o);
+      if (!p.x_f16) {
+        const float2 h0 = __half22float2(o[0]), h1 = __half22float2(o[1]), h2 = __half22float2(o[2]), h3 = __half22float2(o[3]);
+        __half2 lo2[4] = {__floats2half2_rn(f[0] - h0.x, f[2] - h0.y), __floats2half2_rn(f[1] - h1.x, f[3] - h1.y),
+                          __floats2half2_rn(f[4] - h2.x, f[6] - h2.y), __floats2half2_rn(f[5] - h3.x, f[7] - h3.y)};
+        *reinterpret_cast<uint4*>(sA2 + tile_off(r, kc, BM)) = *reinterpret_cast<const uint4*>(lo2);
+      }
     }
     // weights: 8 packed tiles (16 rows x 4 blocks each); one (row, block) pair per thread per step
     for (int ch = tid; ch < (BN / 16) * 64; ch += GEMM_THREADS) {
@@ -235,16 +255,26 @@ __global__ void __launch_bounds__(GEMM_THREADS) tc_qgemm_kernel(const QGemmParam
       if (QT == B200Q_Q4_0) {
         const uint4 qv = reinterpret_cast<const uint4*>(tile)[h * 32 + l];
         // element e < 16 = low nibble of byte e, e >= 16 = high nibble of byte e - 16: cores 0,1 low, cores 2,3 high
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32, BN)) = q4_core<false>(qv.x, qv.y, d2);
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 8, BN)) = q4_core<false>(qv.z, qv.w, d2);
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 16, BN)) = q4_core<true>(qv.x, qv.y, d2);
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 24, BN)) = q4_core<true>(qv.z, qv.w, d2);
+        uint4 lo[4];
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32, BN)) = q4_core<false>(qv.x, qv.y, d2, lo[0]);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 8, BN)) = q4_core<false>(qv.z, qv.w, d2, lo[1]);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 16, BN)) = q4_core<true>(qv.x, qv.y, d2, lo[2]);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 24, BN)) = q4_core<true>(qv.z, qv.w, d2, lo[3]);
+        if (!p.x_f16) {
+#pragma unroll
+          for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(sB2 + tile_off(r, t * 32 + 8 * c, BN)) = lo[c];
+        }
       } else {
         const uint4 q0 = reinterpret_cast<const uint4*>(tile)[(2 * h) * 32 + l], q1 = reinterpret_cast<const uint4*>(tile)[(2 * h + 1) * 32 + l];
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32, BN)) = q8_core(q0.x, q0.y, d2);
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 8, BN)) = q8_core(q0.z, q0.w, d2);
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 16, BN)) = q8_core(q1.x, q1.y, d2);
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 24, BN)) = q8_core(q1.z, q1.w, d2);
+        uint4 lo[4];
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32, BN)) = q8_core(q0.x, q0.y, d2, lo[0]);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 8, BN)) = q8_core(q0.z, q0.w, d2, lo[1]);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 16, BN)) = q8_core(q1.x, q1.y, d2, lo[2]);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 24, BN)) = q8_core(q1.z, q1.w, d2, lo[3]);
+        if (!p.x_f16) {
+#pragma unroll
+          for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(sB2 + tile_off(r, t * 32 + 8 * c, BN)) = lo[c];
+        }
       }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -258,6 +288,14 @@ __global__ void __launch_bounds__(GEMM_THREADS) tc_qgemm_kernel(const QGemmParam
         const uint32_t acc = (kg > 0 || kk > 0) ? 1u : 0u;
         asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                      ::"r"(taddr), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+        if (!p.x_f16) {
+          const uint64_t da2 = make_desc(s32(sA2) + kk * 2 * (BM * 16), BM * 16, 128);
+          const uint64_t db2 = make_desc(s32(sB2) + kk * 2 * (BN * 16), BN * 16, 128);
+          asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                       ::"r"(taddr), "l"(da2), "l"(db), "r"(idesc), "r"(1u) : "memory");
+          asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                       ::"r"(taddr), "l"(da), "l"(db2), "r"(idesc), "r"(1u) : "memory");
+        }
       }
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&bar)) : "memory");
     }
@@ -278,15 +316,31 @@ __global__ void __launch_bounds__(GEMM_THREADS) tc_qgemm_kernel(const QGemmParam
                      "=r"(v[31])
                    : "r"(ta));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (row < p.m) {
+      if (row < p.m && p.silu_mul) {
+        // gate / up rows interleaved 8 + 8 per 16-row tile: 32 columns = 2 tiles -> 16 activations silu(gate) * up
+#pragma unroll
+        for (int t2 = 0; t2 < 2; t2++)
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const int acol = (rt0 + j0 / 16 + t2) * 8 + j;
+            if (acol < p.n_out / 2) {
+              const float gte = __uint_as_float(v[t2 * 16 + j]), up = __uint_as_float(v[t2 * 16 + 8 + j]);
+              const float o = (gte / (1.f + expf(-gte))) * up;
+              if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)row * (p.n_out / 2) + acol] = __float2half_rn(o);
+              else reinterpret_cast<float*>(p.y)[(size_t)row * (p.n_out / 2) + acol] = o;
+            }
+          }
+      } else if (row < p.m) {
 #pragma unroll
         for (int j = 0; j < 32; j++) {
           const int col = rt0 * 16 + j0 + j;
           if (col < p.n_out) {
             float o = __uint_as_float(v[j]);
             if (p.bias) o += __half2float(p.bias[col]);
-            if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)row * p.n_out + col] = __float2half_rn(o);
-            else reinterpret_cast<float*>(p.y)[(size_t)row * p.n_out + col] = o;
+            const size_t at = (size_t)row * p.n_out + col;
+            if (p.residual) o += p.y_f16 ? __half2float(reinterpret_cast<const __half*>(p.residual)[at]) : reinterpret_cast<const float*>(p.residual)[at];
+            if (p.y_f16) reinterpret_cast<__half*>(p.y)[at] = __float2half_rn(o);
+            else reinterpret_cast<float*>(p.y)[at] = o;
           }
         }
       }
@@ -317,16 +371,19 @@ extern "C" int b200q_gemm_f16(const void* a_f16, const void* w_f16, float* c, in
   return B200Q_OK;
 }
 
-extern "C" int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, void* y, int y_dtype, int m, int n_out,
-                           int n_in, void* stream) {
+extern "C" int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue,
+                           void* y, int y_dtype, int m, int n_out, int n_in, void* stream) {
   if (!w_packed || !x || !y || m <= 0 || n_out <= 0 || n_in <= 0) return B200Q_ERR_BAD_ARG;
+  if (epilogue != B200Q_EPI_LINEAR && epilogue != B200Q_EPI_SILU_MUL) return B200Q_ERR_BAD_ARG;
+  if (epilogue == B200Q_EPI_SILU_MUL && (bias_f16 || residual || n_out % 16)) return B200Q_ERR_BAD_ARG;
   if (qtype == B200Q_Q6_K) return B200Q_ERR_UNSUPPORTED;
   if (qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
   if ((x_dtype != B200Q_F32 && x_dtype != B200Q_F16) || (y_dtype != B200Q_F32 && y_dtype != B200Q_F16)) return B200Q_ERR_BAD_ARG;
   if (n_in % 32) return B200Q_ERR_BAD_SHAPE;
   if (((uintptr_t)w_packed | (uintptr_t)x) & 15) return B200Q_ERR_MISALIGNED;
   QGemmParams p;
-  p.w = (const uint8_t*)w_packed; p.x = x; p.bias = (const __half*)bias_f16; p.y = y;
+  p.w = (const uint8_t*)w_packed; p.x = x; p.bias = (const __half*)bias_f16; p.residual = residual; p.y = y;
+  p.silu_mul = epilogue == B200Q_EPI_SILU_MUL;
   p.m = m; p.n_out = n_out; p.n_in = n_in; p.kgroups = ceil_div(n_in, GROUP_ELEMS); p.n_row_tiles = ceil_div(n_out, TILE_ROWS);
   p.x_f16 = x_dtype == B200Q_F16; p.y_f16 = y_dtype == B200Q_F16;
   dim3 grid(ceil_div(p.n_row_tiles, BN / 16), ceil_div(m, BM));

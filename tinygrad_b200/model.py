@@ -51,10 +51,14 @@ DEFAULT_HANDOVER = ("attn_o",)
 
 class Transformer:
   def __init__(self, config: TransformerConfig, state_dict: dict, ggml_type: int = _lib.Q4_0, n_split: int = 0, use_pdl: bool = True,
-               use_graph: bool = True, gemv_max_ctas: int = 0, handover=None, tp=None):
+               use_graph: bool = True, gemv_max_ctas: int = 0, handover=None, tp=None, output_type: int = None, prefill_rows: int = 64,
+               prefill_chunk: int = 512):
     """state_dict: the reference's tensor names -> numpy arrays; Linear weights as raw
     GGUF block bytes (uint8), embeddings / norms / biases as fp16.
-    tp: a tensor_parallel.TPGroup; `config` is then the FULL model and `state_dict` this rank's shard (shard_state_dict)."""
+    tp: a tensor_parallel.TPGroup; `config` is then the FULL model and `state_dict` this rank's shard (shard_state_dict).
+    output_type: GGML type of `output.weight` when it differs from the block Linears' (Q6_K / F16 / F32 heads run the dense GEMV).
+    prefill_rows: prompts with at least this many uncached tokens go through the tensor-core GEMM path, `prefill_chunk` rows at a
+    time (0: always one token per step, whose fp32-activation numerics are the reference's own); shorter ones take decode steps."""
     self.tp, self.full_config = tp, config
     if tp is not None:
       from .tensor_parallel import local_config
@@ -94,8 +98,13 @@ class Transformer:
       self.blk.append(b)
       nel, nby = quant.GGML_QUANT[ggml_type]
       self.weight_bytes += (qkv_rows * c.dim + c.dim * self.q_dim + 3 * c.hidden_dim * c.dim) // nel * nby
-    self.output = quant.repack(sd["output.weight"], c.vocab_size, c.dim, ggml_type)
-    self.weight_bytes += c.vocab_size * c.dim // quant.GGML_QUANT[ggml_type][0] * quant.GGML_QUANT[ggml_type][1]
+    self.output_type = ggml_type if output_type is None else output_type
+    if self.output_type in (_lib.Q4_0, _lib.Q8_0):
+      self.output = quant.repack(sd["output.weight"], c.vocab_size, c.dim, self.output_type)
+      self.weight_bytes += c.vocab_size * c.dim // quant.GGML_QUANT[self.output_type][0] * quant.GGML_QUANT[self.output_type][1]
+    else:
+      self.output = quant.DenseWeight(sd["output.weight"], c.vocab_size, c.dim, self.output_type)
+      self.weight_bytes += self.output.algorithmic_bytes
     self.output_norm = DeviceBuffer.from_numpy(np.asarray(sd["output_norm.weight"], dtype=np.float16))
     self.token_embd = DeviceBuffer.from_numpy(np.asarray(sd["token_embd.weight"], dtype=np.float16))
     self.rope = DeviceBuffer.from_numpy(precompute_freqs_cis(c.rope_dim, c.max_context, c.rope_theta))
@@ -128,6 +137,8 @@ class Transformer:
     if "gateup_down" in self.edges: self.xq_act = DeviceBuffer(xqb(c.hidden_dim), zero=True)
     self._graphs = {}
     self._cached_tokens: list = []
+    self.prefill_rows = prefill_rows if (tp is None and c.hidden_dim % 8 == 0 and c.head_dim in (16, 32, 64, 128)) else 0
+    self.prefill_chunk, self._pf = max(1, prefill_chunk), None
     self.launches_per_step = 5 * c.num_blocks + 3
 
   # ---- one token through the network (launch sequence; captured into a graph) ----
@@ -173,13 +184,50 @@ class Transformer:
                  **in_act, **out_a, **kw)
       if tp is not None: tp.all_reduce(self.x)
     if with_head:
-      quant.gemv(self.output.buf.ptr, self.qtype, c.vocab_size, c.dim, None if in_a else self.x, self.logits_part, norm_weight=self.output_norm,
-                 norm_eps=c.norm_eps, **in_a, **kw_after_coll)
+      if isinstance(self.output, quant.DenseWeight):
+        quant.gemv_dense(self.output.buf, self.output.dtype, c.vocab_size, c.dim, self.x, self.logits_part, norm_weight=self.output_norm,
+                         norm_eps=c.norm_eps, flags=kw_after_coll["flags"], stream=s)
+      else:
+        quant.gemv(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, None if in_a else self.x, self.logits_part,
+                   norm_weight=self.output_norm, norm_eps=c.norm_eps, **in_a, **kw_after_coll)
       if tp is not None: tp.all_gather(self.logits, self.logits_part)
       if tail: check(lib.b200q_argmax_advance(self.logits.ptr, vocab_full, self.tokens.ptr, self.pos.ptr, self.argmax_scratch.ptr,
                                               0 if tp is not None else fl, s))
     elif tail:
       check(lib.b200q_advance(self.pos.ptr, 0 if tp is not None else fl, s))
+
+  # ---- several prompt tokens at once: tcgen05 dequant GEMMs + batched causal attention ----
+  def _prefill_buffers(self):
+    if self._pf is None:
+      c, T = self.config, self.prefill_chunk
+      self._pf = dict(x=DeviceBuffer.empty((T, c.dim), np.float32), xn=DeviceBuffer.empty((T, c.dim), np.float32),
+                      qkv=DeviceBuffer.empty((T, self.q_dim + 2 * self.kv_dim), np.float32), q16=DeviceBuffer.empty((T, self.q_dim), np.float32),
+                      att=DeviceBuffer.empty((T, self.q_dim), np.float32), act=DeviceBuffer.empty((T, c.hidden_dim), np.float32))
+    return self._pf
+
+  def prefill(self, start_pos: int, n: int) -> None:
+    """Run tokens[start_pos : start_pos + n] (already on the device) through every block and fill the KV cache; no logits.
+    The forward of tinygrad/llm/model.py:358-362 for T = n, in chunks: per block rmsnorm -> QKV GEMM -> RoPE + cache append +
+    causal attention -> O GEMM (+residual) -> rmsnorm -> gate/up GEMM with SwiGLU epilogue -> down GEMM (+residual).
+    Activations stay fp32 between the kernels; the GEMMs split them into fp16 hi + lo halves for the tensor core."""
+    c, lib, s, f = self.config, _lib.load(), self.stream.ptr, self._prefill_buffers()
+    kvdt = F16 if c.kv_dtype == "float16" else F32
+    qkv_rows = self.q_dim + 2 * self.kv_dim
+    for p0 in range(start_pos, start_pos + n, self.prefill_chunk):
+      T = min(self.prefill_chunk, start_pos + n - p0)
+      check(lib.b200q_embed_rows(self.token_embd.ptr, self.tokens.ptr + 4 * p0, T, c.dim, self.full_config.vocab_size, f["x"].ptr, s))
+      for b in self.blk:
+        check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.attn_norm.ptr, c.norm_eps, T, c.dim, f["xn"].ptr, F32, s))
+        quant.qgemm(b.qkv.ptr, self.qtype, qkv_rows, c.dim, f["xn"], f["qkv"], T, x_dtype=F32, y_dtype=F32, bias=b.qkv_bias, stream=s)
+        check(lib.b200q_attn_prefill(f["qkv"].ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, p0, T, c.n_heads, c.n_kv_heads, c.head_dim,
+                                     c.rope_dim, c.max_context, f["q16"].ptr, f["att"].ptr, F32, s))
+        quant.qgemm(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, f["att"], f["x"], T, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s)
+        check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.ffn_norm.ptr, c.norm_eps, T, c.dim, f["xn"].ptr, F32, s))
+        quant.qgemm(b.gate_up.buf.ptr, self.qtype, 2 * c.hidden_dim, c.dim, f["xn"], f["act"], T, x_dtype=F32, y_dtype=F32, epilogue=EPI_SILU_MUL,
+                    stream=s)
+        quant.qgemm(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, f["act"], f["x"], T, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s)
+    self.stream.synchronize()
+    self.pos.copy_from(np.array([start_pos + n], dtype=np.int32))
 
   def gemv_launches(self) -> list:
     """(n_out rows streamed, n_in) of every GEMV launch of one step with the head, in launch order."""
@@ -233,7 +281,10 @@ class Transformer:
     tokens = list(tokens)
     start_pos = self.get_start_pos(tokens)
     self.set_state(tokens, start_pos)
-    for _ in range(start_pos, len(tokens) - 1): self.step(with_head=False)
+    n_pre = len(tokens) - 1 - start_pos
+    if self.prefill_rows and n_pre >= self.prefill_rows: self.prefill(start_pos, n_pre)
+    else:
+      for _ in range(n_pre): self.step(with_head=False)
     while len(tokens) < self.max_context:
       self.step(with_head=True)
       tok = self.read_token(len(tokens))

@@ -83,24 +83,61 @@ def gemv(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int = 1, x_dtyp
   check(_lib.load().b200q_gemv(ctypes.byref(a), stream_ptr(stream)))
 
 
-def qgemm(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int, x_dtype=F32, y_dtype=F32, bias=None, stream=None) -> None:
+def qgemm(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int, x_dtype=F32, y_dtype=F32, bias=None, residual=None,
+          epilogue: int = EPI_LINEAR, stream=None) -> None:
   """Batched / prefill linear on the tcgen05 tensor cores: the weights are streamed once per 128 activation rows."""
-  check(_lib.load().b200q_qgemm(qtype, w_ptr, ptr_of(x), x_dtype, ptr_of(bias), ptr_of(y), y_dtype, m, n_out, n_in, stream_ptr(stream)))
+  check(_lib.load().b200q_qgemm(qtype, w_ptr, ptr_of(x), x_dtype, ptr_of(bias), ptr_of(residual), epilogue, ptr_of(y), y_dtype, m, n_out, n_in,
+                                stream_ptr(stream)))
 
 
 GEMM_MIN_ROWS = 4   # from this many activation rows on, QuantLinear uses the tensor-core GEMM instead of one GEMV per row
 
 
+GGML_F32, GGML_F16, GGML_BF16 = 0, 1, 30                # unquantised GGUF tensor types (tinygrad/llm/gguf.py:25-27)
+_DENSE_DT = {GGML_F32: (_lib.F32, np.float32), GGML_F16: (_lib.F16, np.float16), GGML_BF16: (_lib.BF16, np.uint16)}
+DENSE_MAX_ROWS = 4
+
+
+def gemv_dense(w, w_dtype: int, n_out: int, n_in: int, x, y, m: int = 1, x_dtype=F32, y_dtype=F32, norm_weight=None, norm_eps: float = 0.0,
+               bias=None, residual=None, flags: int = 0, stream=None) -> None:
+  """One launch of the dense-weight GEMV (weight row-major fp16 / bf16 / fp32 on the device)."""
+  check(_lib.load().b200q_gemv_dense(ptr_of(w), w_dtype, n_out, n_in, m, ptr_of(x), x_dtype, ptr_of(norm_weight), norm_eps, ptr_of(bias),
+                                     ptr_of(residual), ptr_of(y), y_dtype, flags, stream_ptr(stream)))
+
+
+class DenseWeight:
+  """A [n_out, n_in] weight kept as plain values on the device.  F32 / F16 / BF16 tensors stay as stored; Q6_K blocks are
+  dequantised once to fp16 (the cast the reference applies to every loaded tensor, tinygrad/llm/model.py:376)."""
+  def __init__(self, raw, n_out: int, n_in: int, ggml_type: int):
+    self.n_out, self.n_in = n_out, n_in
+    if ggml_type in _DENSE_DT:
+      self.dtype, npdt = _DENSE_DT[ggml_type]
+      a = np.ascontiguousarray(raw)
+      a = a.view(npdt) if a.dtype == np.uint8 else a.astype(npdt) if ggml_type != GGML_BF16 else a.view(np.uint16)
+      if a.size != n_out * n_in: raise ValueError(f"weight has {a.size} values, expected {n_out}x{n_in}")
+      self.buf = DeviceBuffer.from_numpy(a.reshape(n_out, n_in))
+    elif ggml_type in GGML_QUANT:
+      self.dtype, self.buf = _lib.F16, dequantize(raw, n_out * n_in, ggml_type, np.float16)
+    else:
+      raise ValueError(f"GGML type '{ggml_type}' is not supported!")
+
+  @property
+  def algorithmic_bytes(self) -> int: return self.buf.nbytes
+
+
 class QuantLinear:
-  """Drop-in for `nn.Linear` holding a GGUF-quantised weight.
+  """Drop-in for `nn.Linear` holding a GGUF weight.
 
   `QuantLinear(in_features, out_features, ggml_type, raw_blocks, bias)`; calling it
   on activations of shape (..., in_features), fp16 or fp32, returns
   (..., out_features) in the activation dtype, as
-  `x.linear(weight.transpose(), bias)` does (tinygrad/nn/__init__.py:177)."""
+  `x.linear(weight.transpose(), bias)` does (tinygrad/nn/__init__.py:177).
+  Q4_0 / Q8_0 weights run the fused dequant kernels (GEMV below 4 rows, tcgen05 GEMM from 4 rows on); F32 / F16 / BF16 and
+  Q6_K weights run the dense GEMV, 4 activation rows per launch."""
   def __init__(self, in_features: int, out_features: int, ggml_type: int, raw, bias=None):
     self.in_features, self.out_features, self.ggml_type = in_features, out_features, ggml_type
-    self.weight = repack(raw, out_features, in_features, ggml_type)
+    self.fused = ggml_type in (Q4_0, Q8_0)
+    self.weight = repack(raw, out_features, in_features, ggml_type) if self.fused else DenseWeight(raw, out_features, in_features, ggml_type)
     self.bias = None if bias is None else DeviceBuffer.from_numpy(np.asarray(bias, dtype=np.float16))
 
   def __call__(self, x: DeviceBuffer, stream=None) -> DeviceBuffer:
@@ -108,10 +145,13 @@ class QuantLinear:
     if x.shape[-1] != self.in_features: raise ValueError(f"Input Tensor shapes {x.shape} cannot be multiplied with in_features={self.in_features}")
     m = int(np.prod(x.shape[:-1], dtype=np.int64))
     y = DeviceBuffer.empty((*x.shape[:-1], self.out_features), x.dtype)
-    if m >= GEMM_MIN_ROWS:
-      qgemm(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m, x_dtype=_DT[x.dtype], y_dtype=_DT[x.dtype],
-            bias=self.bias, stream=stream)
+    dt, isz = _DT[x.dtype], x.dtype.itemsize
+    if not self.fused:
+      for r in range(0, m, DENSE_MAX_ROWS):
+        gemv_dense(self.weight.buf, self.weight.dtype, self.out_features, self.in_features, x.ptr + r * self.in_features * isz,
+                   y.ptr + r * self.out_features * isz, m=min(DENSE_MAX_ROWS, m - r), x_dtype=dt, y_dtype=dt, bias=self.bias, stream=stream)
+    elif m >= GEMM_MIN_ROWS:
+      qgemm(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m, x_dtype=dt, y_dtype=dt, bias=self.bias, stream=stream)
     elif m:
-      gemv(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m=m, x_dtype=_DT[x.dtype], y_dtype=_DT[x.dtype],
-           bias=self.bias, stream=stream)
+      gemv(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m=m, x_dtype=dt, y_dtype=dt, bias=self.bias, stream=stream)
     return y

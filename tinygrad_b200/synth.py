@@ -102,3 +102,59 @@ class LazyDenseState:
     if name == "token_embd": return (rng.standard_normal((self.embd_vocab, self.cfg.dim), dtype=np.float32) * self.embd_std).astype(np.float16)
     if name.endswith("_norm"): return (1.0 + 0.05 * rng.standard_normal(self.cfg.dim, dtype=np.float32)).astype(np.float16)
     raise KeyError(key)
+
+
+# ---- GGUF container images of synthetic models (the file format of tinygrad/llm/gguf.py:132-149) ----
+def _gguf_value(v) -> bytes:
+  import struct
+  if isinstance(v, bool): return struct.pack("<i?", 7, v)
+  if isinstance(v, int): return struct.pack("<iI", 4, v) if 0 <= v < 2**32 else struct.pack("<iq", 11, v)
+  if isinstance(v, float): return struct.pack("<if", 6, v)
+  if isinstance(v, str): b = v.encode(); return struct.pack("<iQ", 8, len(b)) + b
+  if isinstance(v, (list, tuple)):
+    items = [_gguf_value(x) for x in v]
+    typ = items[0][:4] if items else struct.pack("<i", 4)
+    assert all(it[:4] == typ for it in items), "GGUF arrays hold one value type"
+    return struct.pack("<i", 9) + typ + struct.pack("<Q", len(items)) + b"".join(it[4:] for it in items)
+  raise TypeError(f"no GGUF value type for {type(v)}")
+
+
+def write_gguf(kv: dict, tensors: list, version: int = 3) -> bytes:
+  """kv: metadata; tensors: (name, shape outermost-first, ggml_type, raw bytes / array).  Returns the file image."""
+  import struct
+  align = kv.get("general.alignment", 32)
+  head = b"GGUF" + struct.pack("<iqq", version, len(tensors), len(kv))
+  for k, v in kv.items(): head += struct.pack("<Q", len(k.encode())) + k.encode() + _gguf_value(v)
+  blobs, off = [], 0
+  for name, shape, typ, data in tensors:
+    raw = np.ascontiguousarray(data).view(np.uint8).reshape(-1).tobytes()
+    head += struct.pack("<Q", len(name.encode())) + name.encode() + struct.pack("<I", len(shape))
+    head += b"".join(struct.pack("<Q", d) for d in reversed(shape)) + struct.pack("<iQ", typ, off)     # dims innermost-first
+    pad = (-len(raw)) % align
+    blobs.append(raw + b"\0" * pad)
+    off += len(raw) + pad
+  return head + b"\0" * ((-len(head)) % align) + b"".join(blobs)
+
+
+def dense_model_gguf(cfg, ggml_type: int = Q4_0, seed: int = 0, arch: str = "llama", embd_std: float = 0.02, output: str = "same") -> bytes:
+  """A random-init dense model as a GGUF file image.  output: "same" (head in ggml_type), "f16", "q6_k", or "tied" (no output.weight).
+  For arch "llama" the q/k rows are stored as given; the loader applies the family's RoPE row permutation."""
+  sd = dense_model_raw(cfg, ggml_type, seed=seed, embd_std=embd_std)
+  shapes = {n + ".weight": (o, i) for n, o, i in linear_names(cfg)}
+  kv = {"general.architecture": arch, "general.alignment": 32, f"{arch}.context_length": cfg.max_context, f"{arch}.block_count": cfg.num_blocks,
+        f"{arch}.embedding_length": cfg.dim, f"{arch}.feed_forward_length": cfg.hidden_dim, f"{arch}.attention.head_count": cfg.n_heads,
+        f"{arch}.attention.head_count_kv": cfg.n_kv_heads, f"{arch}.attention.layer_norm_rms_epsilon": float(cfg.norm_eps),
+        f"{arch}.rope.freq_base": float(cfg.rope_theta), f"{arch}.rope.dimension_count": cfg.rope_dim,
+        f"{arch}.attention.key_length": cfg.head_dim, f"{arch}.attention.value_length": cfg.head_dim,
+        "tokenizer.ggml.tokens": [f"t{i}" for i in range(cfg.vocab_size)]}
+  tensors = []
+  for name, arr in sd.items():
+    if name == "output.weight" and output != "same":
+      if output == "tied": continue
+      rng = np.random.default_rng(name_seed("output", seed))
+      if output == "q6_k": arr, typ = q6_k_blocks(cfg.vocab_size, cfg.dim, rng), Q6_K
+      else: arr, typ = (rng.standard_normal((cfg.vocab_size, cfg.dim), dtype=np.float32) * 0.05).astype(np.float16), 1
+      tensors.append((name, (cfg.vocab_size, cfg.dim), typ, arr))
+    elif name in shapes: tensors.append((name, shapes[name], ggml_type, arr))
+    else: tensors.append((name, arr.shape, 1, arr))                  # fp16 embeddings / norms / biases
+  return write_gguf(kv, tensors)
