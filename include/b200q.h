@@ -155,7 +155,8 @@ typedef struct b200q_gemv_args {
  * as fp16, bf16 or fp32 (w_dtype) - the Linears a GGUF file leaves unquantised (router ffn_gate_inp, F16 models) or in a
  * block format without a fused kernel (Q6_K output heads, after b200q_dequant_raw to fp16).  Replaces Linear.__call__
  * (tinygrad/nn/__init__.py:177) for those; f = optional RMSNorm with norm_weight (fp16 [n_in]) as in b200q_gemv; bias fp16
- * [n_out]; residual / y in y_dtype.  fp32 products and accumulation.  m <= 4, n_in % 8 == 0, m * n_in * 4 <= 200 KiB.
+ * [n_out]; residual / y in y_dtype.  fp32 products and accumulation.  n_in % 8 == 0, min(m, 4) * n_in * 4 <= 200 KiB; the weight is streamed once per 4 rows
+ * (decode and router sizes; large m with large n_out belongs to a GEMM).
  * flags: B200Q_FLAG_PDL. */
 int b200q_gemv_dense(const void* w, int w_dtype, int n_out, int n_in, int m, const void* x, int x_dtype, const void* norm_weight,
                      float norm_eps, const void* bias, const void* residual, void* y, int y_dtype, int flags, void* stream);
@@ -242,7 +243,8 @@ int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x_dtype, con
                 int y_dtype, int m, int n_out, int n_in, void* stream);
 /* ---- prompt processing: the row-wise pieces of Transformer.forward for T > 1 tokens (tinygrad/llm/model.py:358-364,167-198)
  * b200q_embed_rows:   x [n_rows, dim] fp32 = token_embd[tokens[t]] (tokens on the device).
- * b200q_rmsnorm_rows: out [n_rows, dim] (out_dtype fp16 / fp32) = RMSNorm(x) * weight (tinygrad/nn/__init__.py:300-304).
+ * b200q_rmsnorm_rows: out [n_rows, dim] (out_dtype fp16 / fp32 / bf16) = RMSNorm(x) * weight (tinygrad/nn/__init__.py:300-304).
+ * b200q_add_rows_bf16: x[i] += y[i] over n values, x fp32, y bf16 (the residual add behind the bf16 output of the expert FFN).
  * b200q_attn_prefill: qkv [n_rows, (n_heads + 2 n_kv_heads) * head_dim] fp32 holds the projections of the tokens at
  *   positions start_pos .. start_pos + n_rows - 1.  Rotates q and k (half-split RoPE table [max_context, rope_dim] = cos || sin),
  *   appends k / v to the caches [n_kv_heads, max_context, head_dim] (kv_dtype) and writes the causal attention of every new
@@ -250,6 +252,7 @@ int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x_dtype, con
  *   floats.  Queries and probabilities enter the tensor core as fp16 hi + lo pairs, keys / values as cached.  head_dim in {16, 32, 64, 128}. */
 int b200q_embed_rows(const void* table_f16, const int32_t* tokens, int n_rows, int dim, int vocab, float* x, void* stream);
 int b200q_rmsnorm_rows(const float* x, const void* weight_f16, float eps, int n_rows, int dim, void* out, int out_dtype, void* stream);
+int b200q_add_rows_bf16(float* x, const void* y_bf16, int64_t n, void* stream);
 int b200q_attn_prefill(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int start_pos, int n_rows, int n_heads,
                        int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out, int out_dtype, void* stream);
 int b200q_tc_status_read_clear(int* status);

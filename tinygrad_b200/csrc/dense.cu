@@ -15,7 +15,6 @@ constexpr int THREADS = 256, WARPS = THREADS / 32, MAX_M = 4;
 
 template <typename W> struct WLoad;
 template <> struct WLoad<__half> {
-  static constexpr int VEC = 8;       // elements per 16-byte load
   static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
     const uint4 u = ldg_stream(reinterpret_cast<const uint4*>(p));
     const __half2* h = reinterpret_cast<const __half2*>(&u);
@@ -24,7 +23,6 @@ template <> struct WLoad<__half> {
   }
 };
 template <> struct WLoad<__nv_bfloat16> {
-  static constexpr int VEC = 8;
   static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
     const uint4 u = ldg_stream(reinterpret_cast<const uint4*>(p));
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -33,7 +31,6 @@ template <> struct WLoad<__nv_bfloat16> {
   }
 };
 template <> struct WLoad<float> {
-  static constexpr int VEC = 8;
   static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
     const uint4 a = ldg_stream(reinterpret_cast<const uint4*>(p)), b = ldg_stream(reinterpret_cast<const uint4*>(p + 4));
     v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y); v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
@@ -51,6 +48,7 @@ __global__ void __launch_bounds__(THREADS) dense_gemv_kernel(const DenseParams p
   extern __shared__ float xs[];                    // [M][n_in]
   __shared__ float red[WARPS];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const size_t row0 = (size_t)blockIdx.y * MAX_M;        // this CTA's group of activation rows
   pdl_launch_dependents();
   pdl_wait();
   // stage the activations (normalised like RMSNorm: fp32 x * rsqrt(mean(x^2) + eps), cast to the input dtype, times the weight)
@@ -58,7 +56,7 @@ __global__ void __launch_bounds__(THREADS) dense_gemv_kernel(const DenseParams p
   for (int r = 0; r < M; r++) {
     float ss = 0.f;
     for (int i = tid; i < p.n_in; i += THREADS) {
-      const float v = p.x_f16 ? __half2float(reinterpret_cast<const __half*>(p.x)[(size_t)r * p.n_in + i]) : reinterpret_cast<const float*>(p.x)[(size_t)r * p.n_in + i];
+      const float v = p.x_f16 ? __half2float(reinterpret_cast<const __half*>(p.x)[(row0 + r) * p.n_in + i]) : reinterpret_cast<const float*>(p.x)[(row0 + r) * p.n_in + i];
       xs[r * p.n_in + i] = v;
       ss += v * v;
     }
@@ -112,7 +110,7 @@ __global__ void __launch_bounds__(THREADS) dense_gemv_kernel(const DenseParams p
       float s = warp_sum(acc[r]);
       if (lane == 0) {
         if (p.bias) s += __half2float(p.bias[row]);
-        const size_t o = (size_t)r * p.n_out + row;
+        const size_t o = (row0 + r) * p.n_out + row;
         if (p.residual) s += p.y_f16 ? __half2float(reinterpret_cast<const __half*>(p.residual)[o]) : reinterpret_cast<const float*>(p.residual)[o];
         if (p.y_f16) reinterpret_cast<__half*>(p.y)[o] = __float2half_rn(s); else reinterpret_cast<float*>(p.y)[o] = s;
       }
@@ -120,14 +118,29 @@ __global__ void __launch_bounds__(THREADS) dense_gemv_kernel(const DenseParams p
   }
 }
 
+// m rows = full groups of MAX_M rows (grid.y of them, M = MAX_M) and one launch for the remainder
 template <typename W>
-cudaError_t launch_dense(const DenseParams& p, int grid, size_t smem, cudaStream_t st, bool pdl) {
-  switch (p.m) {
-    case 1: cudaFuncSetAttribute(dense_gemv_kernel<W, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); return launch_k(dense_gemv_kernel<W, 1>, dim3(grid), dim3(THREADS), smem, st, pdl, p);
-    case 2: cudaFuncSetAttribute(dense_gemv_kernel<W, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); return launch_k(dense_gemv_kernel<W, 2>, dim3(grid), dim3(THREADS), smem, st, pdl, p);
-    case 3: cudaFuncSetAttribute(dense_gemv_kernel<W, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); return launch_k(dense_gemv_kernel<W, 3>, dim3(grid), dim3(THREADS), smem, st, pdl, p);
-    default: cudaFuncSetAttribute(dense_gemv_kernel<W, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); return launch_k(dense_gemv_kernel<W, 4>, dim3(grid), dim3(THREADS), smem, st, pdl, p);
+cudaError_t launch_dense_m(const DenseParams& p, int mrows, int groups, int grid, size_t smem, cudaStream_t st, bool pdl) {
+  switch (mrows) {
+    case 1: cudaFuncSetAttribute(dense_gemv_kernel<W, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); return launch_k(dense_gemv_kernel<W, 1>, dim3(grid, groups), dim3(THREADS), smem, st, pdl, p);
+    case 2: cudaFuncSetAttribute(dense_gemv_kernel<W, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); return launch_k(dense_gemv_kernel<W, 2>, dim3(grid, groups), dim3(THREADS), smem, st, pdl, p);
+    case 3: cudaFuncSetAttribute(dense_gemv_kernel<W, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); return launch_k(dense_gemv_kernel<W, 3>, dim3(grid, groups), dim3(THREADS), smem, st, pdl, p);
+    default: cudaFuncSetAttribute(dense_gemv_kernel<W, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); return launch_k(dense_gemv_kernel<W, 4>, dim3(grid, groups), dim3(THREADS), smem, st, pdl, p);
   }
+}
+template <typename W>
+cudaError_t launch_dense(const DenseParams& p0, int grid, size_t smem, cudaStream_t st, bool pdl) {
+  DenseParams p = p0;
+  const int full = p.m / MAX_M, rem = p.m % MAX_M;
+  const size_t xsz = p.x_f16 ? 2 : 4, ysz = p.y_f16 ? 2 : 4;
+  if (full) {
+    cudaError_t e = launch_dense_m<W>(p, MAX_M, full, grid, smem, st, pdl);
+    if (e != cudaSuccess) return e;
+    p.x = (const char*)p.x + (size_t)full * MAX_M * p.n_in * xsz;
+    p.y = (char*)p.y + (size_t)full * MAX_M * p.n_out * ysz;
+    if (p.residual) p.residual = (const char*)p.residual + (size_t)full * MAX_M * p.n_out * ysz;
+  }
+  return rem ? launch_dense_m<W>(p, rem, 1, grid, smem, st, pdl && !full) : cudaSuccess;
 }
 
 }  // namespace
@@ -138,8 +151,7 @@ extern "C" int b200q_gemv_dense(const void* w, int w_dtype, int n_out, int n_in,
   if (w_dtype != B200Q_F16 && w_dtype != B200Q_F32 && w_dtype != B200Q_BF16) return B200Q_ERR_BAD_ARG;
   if ((x_dtype != B200Q_F16 && x_dtype != B200Q_F32) || (y_dtype != B200Q_F16 && y_dtype != B200Q_F32)) return B200Q_ERR_BAD_ARG;
   if (n_in % 8) return B200Q_ERR_BAD_SHAPE;                                // 16-byte loads of 8 fp16 weights
-  if (m > MAX_M) return B200Q_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)m * n_in * sizeof(float);
+  const size_t smem = (size_t)(m < MAX_M ? m : MAX_M) * n_in * sizeof(float);
   if (smem > 200 * 1024) return B200Q_ERR_TOO_LARGE;
   if (((uintptr_t)w & 15) || ((uintptr_t)x & 3)) return B200Q_ERR_MISALIGNED;
   static int n_sm = 0;
@@ -153,7 +165,7 @@ extern "C" int b200q_gemv_dense(const void* w, int w_dtype, int n_out, int n_in,
   p.w = w; p.x = x; p.norm_w = (const __half*)norm_weight; p.bias = (const __half*)bias; p.residual = residual; p.y = y;
   p.n_out = n_out; p.n_in = n_in; p.m = m; p.eps = norm_eps; p.x_f16 = x_dtype == B200Q_F16; p.y_f16 = y_dtype == B200Q_F16;
   const int per_sm = smem > 96 * 1024 ? 1 : smem > 48 * 1024 ? 2 : 4;
-  const int grid = min(ceil_div(n_out, WARPS), n_sm * per_sm);
+  const int grid = min(ceil_div(n_out, WARPS), m > MAX_M ? 8 : n_sm * per_sm);      // many row groups already fill the GPU
   const bool pdl = flags & B200Q_FLAG_PDL;
   cudaError_t e = w_dtype == B200Q_F16 ? launch_dense<__half>(p, grid, smem, (cudaStream_t)stream, pdl)
                 : w_dtype == B200Q_BF16 ? launch_dense<__nv_bfloat16>(p, grid, smem, (cudaStream_t)stream, pdl)

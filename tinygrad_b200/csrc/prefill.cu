@@ -8,6 +8,7 @@
 // Attention FLOPs are a few percent of a prompt's GEMM FLOPs at these context lengths, so this kernel uses the warp-level
 // MMA; the projections around it run on tcgen05 (tc_gemm.cu).
 #include "common.cuh"
+#include <cuda_bf16.h>
 
 namespace {
 
@@ -24,6 +25,18 @@ __global__ void embed_rows_kernel(const __half* __restrict__ table, const int32_
 template <typename O> __device__ __forceinline__ O out_cast(float v);
 template <> __device__ __forceinline__ __half out_cast<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ float out_cast<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 out_cast<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// x[i] += y[i] (bf16): the residual add behind a bf16 expert output (model.py:360 `h + self._feed_forward(...)`)
+__global__ void add_rows_bf16_kernel(float* __restrict__ x, const __nv_bfloat16* __restrict__ y, size_t n) {
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (i + 1 < n) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(y + i));
+    float2 a = *reinterpret_cast<float2*>(x + i);
+    a.x += v.x; a.y += v.y;
+    *reinterpret_cast<float2*>(x + i) = a;
+  } else if (i < n) x[i] += __bfloat162float(y[i]);
+}
 
 template <typename O>
 __global__ void rmsnorm_rows_kernel(const float* __restrict__ x, const __half* __restrict__ w, float eps, int dim, O* __restrict__ out) {
@@ -272,9 +285,21 @@ extern "C" int b200q_embed_rows(const void* table_f16, const int32_t* tokens, in
 }
 
 extern "C" int b200q_rmsnorm_rows(const float* x, const void* weight_f16, float eps, int n_rows, int dim, void* out, int out_dtype, void* stream) {
-  if (!x || !weight_f16 || !out || n_rows <= 0 || dim <= 0 || (out_dtype != B200Q_F16 && out_dtype != B200Q_F32)) return B200Q_ERR_BAD_ARG;
-  if (out_dtype == B200Q_F16) rmsnorm_rows_kernel<__half><<<n_rows, 256, 0, (cudaStream_t)stream>>>(x, (const __half*)weight_f16, eps, dim, (__half*)out);
+  if (!x || !weight_f16 || !out || n_rows <= 0 || dim <= 0) return B200Q_ERR_BAD_ARG;
+  if (out_dtype != B200Q_F16 && out_dtype != B200Q_F32 && out_dtype != B200Q_BF16) return B200Q_ERR_BAD_ARG;
+  if (out_dtype == B200Q_BF16) rmsnorm_rows_kernel<__nv_bfloat16><<<n_rows, 256, 0, (cudaStream_t)stream>>>(x, (const __half*)weight_f16, eps, dim,
+                                                                                                           (__nv_bfloat16*)out);
+  else if (out_dtype == B200Q_F16) rmsnorm_rows_kernel<__half><<<n_rows, 256, 0, (cudaStream_t)stream>>>(x, (const __half*)weight_f16, eps, dim, (__half*)out);
   else rmsnorm_rows_kernel<float><<<n_rows, 256, 0, (cudaStream_t)stream>>>(x, (const __half*)weight_f16, eps, dim, (float*)out);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+extern "C" int b200q_add_rows_bf16(float* x, const void* y_bf16, int64_t n, void* stream) {
+  if (!x || !y_bf16 || n < 0) return B200Q_ERR_BAD_ARG;
+  if (((uintptr_t)x & 7) || ((uintptr_t)y_bf16 & 3)) return B200Q_ERR_MISALIGNED;
+  if (n == 0) return B200Q_OK;
+  add_rows_bf16_kernel<<<(unsigned)((n / 2 + 256) / 256), 256, 0, (cudaStream_t)stream>>>(x, (const __nv_bfloat16*)y_bf16, (size_t)n);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -32,6 +32,11 @@ class TransformerConfig:           # field names of tinygrad/llm/model.py:52-83 
   max_context: int = 0
   qkv_bias: bool = False
   kv_dtype: str = "float16"        # the cache dtype; the reference takes it from DEFAULT_FLOAT (model.py:202-203)
+  num_experts: int = 0             # > 0: every block's FFN is a routed mixture of experts (model.py:94-98,110-135) with MXFP8 expert weights
+  num_experts_per_tok: int = 0
+  norm_topk_prob: bool = False
+  expert_gating_func: str = "softmax"
+  routed_scaling_factor: float = 1.0
 
 
 def precompute_freqs_cis(dim: int, end: int, theta: float) -> np.ndarray:
@@ -88,8 +93,20 @@ class Transformer:
       if c.qkv_bias:
         b.qkv_bias = DeviceBuffer.from_numpy(np.concatenate([np.asarray(sd[f"blk.{i}.attn_{n}.bias"], dtype=np.float16) for n in "qkv"]))
       b.attn_output = quant.repack(sd[f"blk.{i}.attn_output.weight"], c.dim, self.q_dim, ggml_type)
-      b.gate_up = quant.repack(sd[f"blk.{i}.ffn_gate.weight"], c.hidden_dim, c.dim, ggml_type, raw_up=sd[f"blk.{i}.ffn_up.weight"])
-      b.ffn_down = quant.repack(sd[f"blk.{i}.ffn_down.weight"], c.dim, c.hidden_dim, ggml_type)
+      b.moe = b.router = None
+      if c.num_experts:
+        # routed experts: fp32 (E, out, in) weights quantised to MXFP8 on the device; the router stays a dense Linear (model.py:94-98)
+        from . import moe
+        if c.expert_gating_func != "softmax" or c.routed_scaling_factor != 1.0:
+          raise NotImplementedError("expert gating other than softmax (with or without top-k renormalisation) is outside this path")
+        # softmax gating with renormalised top-k = softmax over the k selected logits (model.py:116-117); without: softmax over all experts
+        mode = moe.ROUTE_TOPK_SOFTMAX if c.norm_topk_prob else moe.ROUTE_SOFTMAX_TOPK
+        b.moe = moe.MxMoE(*(np.asarray(sd[f"blk.{i}.ffn_{n}_exps.weight"], dtype=np.float32) for n in ("gate", "up", "down")), c.num_experts_per_tok, mode)
+        r = np.asarray(sd[f"blk.{i}.ffn_gate_inp.weight"])
+        b.router = quant.DenseWeight(r, c.num_experts, c.dim, quant.GGML_F16 if r.dtype == np.float16 else quant.GGML_F32)
+      else:
+        b.gate_up = quant.repack(sd[f"blk.{i}.ffn_gate.weight"], c.hidden_dim, c.dim, ggml_type, raw_up=sd[f"blk.{i}.ffn_up.weight"])
+        b.ffn_down = quant.repack(sd[f"blk.{i}.ffn_down.weight"], c.dim, c.hidden_dim, ggml_type)
       b.attn_norm = DeviceBuffer.from_numpy(np.asarray(sd[f"blk.{i}.attn_norm.weight"], dtype=np.float16))
       b.ffn_norm = DeviceBuffer.from_numpy(np.asarray(sd[f"blk.{i}.ffn_norm.weight"], dtype=np.float16))
       kvdt = np.float16 if c.kv_dtype == "float16" else np.float32
@@ -97,7 +114,7 @@ class Transformer:
       b.v_cache = DeviceBuffer.empty((c.n_kv_heads, c.max_context, c.head_dim), kvdt, zero=True)
       self.blk.append(b)
       nel, nby = quant.GGML_QUANT[ggml_type]
-      self.weight_bytes += (qkv_rows * c.dim + c.dim * self.q_dim + 3 * c.hidden_dim * c.dim) // nel * nby
+      self.weight_bytes += (qkv_rows * c.dim + c.dim * self.q_dim + (0 if c.num_experts else 3 * c.hidden_dim * c.dim)) // nel * nby
     self.output_type = ggml_type if output_type is None else output_type
     if self.output_type in (_lib.Q4_0, _lib.Q8_0):
       self.output = quant.repack(sd["output.weight"], c.vocab_size, c.dim, self.output_type)
@@ -139,6 +156,10 @@ class Transformer:
     self._cached_tokens: list = []
     self.prefill_rows = prefill_rows if (tp is None and c.hidden_dim % 8 == 0 and c.head_dim in (16, 32, 64, 128)) else 0
     self.prefill_chunk, self._pf = max(1, prefill_chunk), None
+    self.is_moe, self._host_pos = c.num_experts > 0, 0
+    if self.is_moe:
+      assert tp is None and c.head_dim in (16, 32, 64, 128), "the mixture-of-experts model runs on the row path of one GPU"
+      self.prefill_rows = 1
     self.launches_per_step = 5 * c.num_blocks + 3
 
   # ---- one token through the network (launch sequence; captured into a graph) ----
@@ -202,10 +223,12 @@ class Transformer:
       c, T = self.config, self.prefill_chunk
       self._pf = dict(x=DeviceBuffer.empty((T, c.dim), np.float32), xn=DeviceBuffer.empty((T, c.dim), np.float32),
                       qkv=DeviceBuffer.empty((T, self.q_dim + 2 * self.kv_dim), np.float32), q16=DeviceBuffer.empty((T, self.q_dim), np.float32),
-                      att=DeviceBuffer.empty((T, self.q_dim), np.float32), act=DeviceBuffer.empty((T, c.hidden_dim), np.float32))
+                      att=DeviceBuffer.empty((T, self.q_dim), np.float32), act=DeviceBuffer.empty((T, max(c.hidden_dim, 1)), np.float32))
+      if self.is_moe:
+        self._pf.update(xb=DeviceBuffer.empty((T, c.dim), np.uint16), logits=DeviceBuffer.empty((T, c.num_experts), np.float32))
     return self._pf
 
-  def prefill(self, start_pos: int, n: int) -> None:
+  def prefill(self, start_pos: int, n: int, sync: bool = True) -> None:
     """Run tokens[start_pos : start_pos + n] (already on the device) through every block and fill the KV cache; no logits.
     The forward of tinygrad/llm/model.py:358-362 for T = n, in chunks: per block rmsnorm -> QKV GEMM -> RoPE + cache append +
     causal attention -> O GEMM (+residual) -> rmsnorm -> gate/up GEMM with SwiGLU epilogue -> down GEMM (+residual).
@@ -223,11 +246,37 @@ class Transformer:
                                      c.rope_dim, c.max_context, f["q16"].ptr, f["att"].ptr, F32, s))
         quant.qgemm(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, f["att"], f["x"], T, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s)
         check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.ffn_norm.ptr, c.norm_eps, T, c.dim, f["xn"].ptr, F32, s))
+        if b.moe is not None:
+          # router on the fp32 normed rows, experts on their bf16 rounding (the activation dtype of the MXFP8 path); bf16 result + residual
+          quant.gemv_dense(b.router.buf, b.router.dtype, c.num_experts, c.dim, f["xn"], f["logits"], m=T, stream=s)
+          check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.ffn_norm.ptr, c.norm_eps, T, c.dim, f["xb"].ptr, _lib.BF16, s))
+          y = b.moe(f["xb"], f["logits"], T, stream=s)
+          check(lib.b200q_add_rows_bf16(f["x"].ptr, y.ptr, T * c.dim, s))
+          continue
         quant.qgemm(b.gate_up.buf.ptr, self.qtype, 2 * c.hidden_dim, c.dim, f["xn"], f["act"], T, x_dtype=F32, y_dtype=F32, epilogue=EPI_SILU_MUL,
                     stream=s)
         quant.qgemm(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, f["act"], f["x"], T, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s)
-    self.stream.synchronize()
-    self.pos.copy_from(np.array([start_pos + n], dtype=np.int32))
+    if sync:
+      self.stream.synchronize()
+      self.pos.copy_from(np.array([start_pos + n], dtype=np.int32))
+      self._host_pos = start_pos + n
+
+  def _step_rows(self, with_head: bool) -> None:
+    """One token through the row path (mixture-of-experts models: their FFN is not part of the fused one-token chain)."""
+    c, lib, s = self.config, _lib.load(), self.stream.ptr
+    self.prefill(self._host_pos, 1, sync=False)
+    if with_head:
+      x_last = self._pf["x"]
+      if isinstance(self.output, quant.DenseWeight):
+        quant.gemv_dense(self.output.buf, self.output.dtype, c.vocab_size, c.dim, x_last, self.logits, norm_weight=self.output_norm, norm_eps=c.norm_eps,
+                         stream=s)
+      else:
+        quant.gemv(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, x_last, self.logits, norm_weight=self.output_norm, norm_eps=c.norm_eps,
+                   stream=s)
+      check(lib.b200q_argmax_advance(self.logits.ptr, c.vocab_size, self.tokens.ptr, self.pos.ptr, self.argmax_scratch.ptr, 0, s))
+    else:
+      check(lib.b200q_advance(self.pos.ptr, 0, s))
+    self._host_pos += 1
 
   def gemv_launches(self) -> list:
     """(n_out rows streamed, n_in) of every GEMV launch of one step with the head, in launch order."""
@@ -244,6 +293,7 @@ class Transformer:
 
   def step(self, with_head: bool = True) -> None:
     """Advance by one token on the device: reads tokens[pos]; with the head, writes tokens[pos+1]."""
+    if self.is_moe: return self._step_rows(with_head)
     if not self.use_graph: return self._enqueue_step(with_head)
     g = self._graphs.get(with_head)
     if g is None:
@@ -257,6 +307,7 @@ class Transformer:
     self.stream.synchronize()
     if tokens: self.tokens.copy_from(np.asarray(tokens, dtype=np.int32))
     self.pos.copy_from(np.array([pos], dtype=np.int32))
+    self._host_pos = pos
 
   def read_token(self, index: int) -> int:
     self.stream.synchronize()

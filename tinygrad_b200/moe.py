@@ -56,13 +56,14 @@ class MxMoE:
     gu = np.concatenate([w_gate, w_up], axis=1).astype(np.float32)          # (E, 2F, D): one GEMM yields [gate | up]
     self.gu_q, self.gu_e8 = quantize_mxfp8(DeviceBuffer.from_numpy(gu), self.E * 2 * self.F, self.D, F32)
     self.dn_q, self.dn_e8 = quantize_mxfp8(DeviceBuffer.from_numpy(w_down.astype(np.float32)), self.E * self.D, self.F, F32)
-    self._ws = None
+    self._wss, self._ws = {}, None
 
   def _workspace(self, n_tokens: int):
-    if self._ws is None or self._ws["T"] != n_tokens:
+    self._ws = self._wss.get(n_tokens)
+    if self._ws is None:
       r = Routing(n_tokens, self.E, self.k, self.mode)
       m = r.m_l
-      self._ws = dict(T=n_tokens, r=r, a_q=DeviceBuffer.empty((m, self.D), np.uint8), a_e8=DeviceBuffer.empty((m, self.D // 32), np.uint8),
+      self._ws = self._wss[n_tokens] = dict(T=n_tokens, r=r, a_q=DeviceBuffer.empty((m, self.D), np.uint8), a_e8=DeviceBuffer.empty((m, self.D // 32), np.uint8),
                       h=DeviceBuffer.empty((m, 2 * self.F), np.uint16, zero=True), act_q=DeviceBuffer.empty((m, self.F), np.uint8),
                       act_e8=DeviceBuffer.empty((m, self.F // 32), np.uint8), y=DeviceBuffer.empty((m, self.D), np.uint16, zero=True),
                       out=DeviceBuffer.empty((n_tokens, self.D), np.uint16))

@@ -95,7 +95,6 @@ GEMM_MIN_ROWS = 4   # from this many activation rows on, QuantLinear uses the te
 
 GGML_F32, GGML_F16, GGML_BF16 = 0, 1, 30                # unquantised GGUF tensor types (tinygrad/llm/gguf.py:25-27)
 _DENSE_DT = {GGML_F32: (_lib.F32, np.float32), GGML_F16: (_lib.F16, np.float16), GGML_BF16: (_lib.BF16, np.uint16)}
-DENSE_MAX_ROWS = 4
 
 
 def gemv_dense(w, w_dtype: int, n_out: int, n_in: int, x, y, m: int = 1, x_dtype=F32, y_dtype=F32, norm_weight=None, norm_eps: float = 0.0,
@@ -145,11 +144,10 @@ class QuantLinear:
     if x.shape[-1] != self.in_features: raise ValueError(f"Input Tensor shapes {x.shape} cannot be multiplied with in_features={self.in_features}")
     m = int(np.prod(x.shape[:-1], dtype=np.int64))
     y = DeviceBuffer.empty((*x.shape[:-1], self.out_features), x.dtype)
-    dt, isz = _DT[x.dtype], x.dtype.itemsize
+    dt = _DT[x.dtype]
     if not self.fused:
-      for r in range(0, m, DENSE_MAX_ROWS):
-        gemv_dense(self.weight.buf, self.weight.dtype, self.out_features, self.in_features, x.ptr + r * self.in_features * isz,
-                   y.ptr + r * self.out_features * isz, m=min(DENSE_MAX_ROWS, m - r), x_dtype=dt, y_dtype=dt, bias=self.bias, stream=stream)
+      if m: gemv_dense(self.weight.buf, self.weight.dtype, self.out_features, self.in_features, x, y, m=m, x_dtype=dt, y_dtype=dt, bias=self.bias,
+                       stream=stream)
     elif m >= GEMM_MIN_ROWS:
       qgemm(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m, x_dtype=dt, y_dtype=dt, bias=self.bias, stream=stream)
     elif m:
