@@ -97,27 +97,35 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
   const int kvh = blockIdx.x, split = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   pdl_launch_dependents();
-  pdl_wait();
-  const int pos = *a.pos;
-  const int n_ctx = pos + 1;
   const int lo = split * ATTN_CHUNK;
-  if (lo >= n_ctx) return;
-  const int n = min(ATTN_CHUNK, n_ctx - lo);
-  const int n_active = (n_ctx + ATTN_CHUNK - 1) / ATTN_CHUNK;
   KV* kc = reinterpret_cast<KV*>(a.k_cache) + (size_t)kvh * a.max_context * hd;
   KV* vc = reinterpret_cast<KV*>(a.v_cache) + (size_t)kvh * a.max_context * hd;
-
-  // all cached rows of the slice -> shared memory with asynchronous 16-byte copies: every copy of the CTA is in flight
-  // at once (one global latency).  The row at `pos` is not in the cache yet.
-  {
-    const int wpr = hd / VEC, n_old = min(n, pos - lo), words = n_old * wpr;
+  // All cached rows of the slice -> shared memory with asynchronous 16-byte copies: every copy of the CTA is in flight at once
+  // (one global latency).  The rows were written by earlier steps, so the copies are issued BEFORE the wait for the previous
+  // kernel (they overlap its tail); only the position counter they are sized by could, in principle, still be the previous
+  // step's, so it is read again after the wait and the copies are redone in the (never observed) case that it moved.
+  auto fetch_rows = [&](int pos_now) {
+    const int wpr = hd / VEC, n_old = max(0, min(min(ATTN_CHUNK, a.max_context - lo), pos_now - lo)), words = n_old * wpr;
     for (int i = threadIdx.x; i < words; i += blockDim.x) {
       const int r = i / wpr, c = (i - r * wpr) * VEC;
       cp_async16(s_k + r * rstride + c, kc + (size_t)(lo + r) * hd + c);
       cp_async16(s_v + r * rstride + c, vc + (size_t)(lo + r) * hd + c);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int pos_early = min(max(__ldcg(a.pos), 0), a.max_context - 1);
+  fetch_rows(pos_early);
+  pdl_wait();
+  const int pos = __ldcg(a.pos);
+  if (pos != pos_early) {                       // uniform over the CTA
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    fetch_rows(pos);
   }
+  const int n_ctx = pos + 1;
+  if (lo >= n_ctx) { asm volatile("cp.async.wait_group 0;" ::: "memory"); return; }
+  const int n = min(ATTN_CHUNK, n_ctx - lo);
+  const int n_active = (n_ctx + ATTN_CHUNK - 1) / ATTN_CHUNK;
   // RoPE, half-split layout: (x1 cos - x2 sin) || (x2 cos + x1 sin); dims past rope_dim pass through
   const float* rope = a.rope + (size_t)pos * a.rope_dim;
   for (int i = threadIdx.x; i < n_rep * hd; i += blockDim.x) {
