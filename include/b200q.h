@@ -278,6 +278,14 @@ size_t b200q_moe_route_scratch_bytes(int n_tokens, int n_experts, int k);
 int b200q_moe_rows_max(int n_tokens, int n_experts, int k);   /* m_max_for, extra/gemm/moe_routing.py:89-90 */
 int b200q_moe_route(const float* logits, int n_tokens, int n_experts, int k, int mode, int32_t* topi, float* weights, int32_t* dest_row,
                     int32_t* off, void* scratch, void* stream);
+/* The same with the group padding as a parameter (pad = 1: compact expert-sorted order, what an expert-parallel sender wants: its
+ * rows for one destination rank are one contiguous run) and the per-expert row counts [n_experts] as an optional output. */
+int b200q_moe_route_pad(const float* logits, int n_tokens, int n_experts, int k, int mode, int pad, int32_t* topi, float* weights,
+                        int32_t* dest_row, int32_t* off, int32_t* counts, void* scratch, void* stream);
+/* Rows of row_bytes bytes (a multiple of 4) moved through an index table: gather = 0: dst[idx[i]] = src[i]; gather = 1:
+ * dst[i] = src[idx[i]]; negative entries are skipped.  The regrouping step on both sides of the expert-parallel exchange
+ * (`dispatch` / `combine` across ranks, extra/gemm/moe_routing.py:124-131). */
+int b200q_permute_rows(const void* src, const int32_t* idx, int64_t n_rows, int row_bytes, void* dst, int gather, void* stream);
 /* `combine` (extra/gemm/moe_routing.py:128-131): out[t] = sum_j weights[t,j] * y[dest_row[t*k+j]], fp32 sum, bf16 in/out. */
 int b200q_moe_combine(const void* y_bf16, const int32_t* dest_row, const float* weights, int n_tokens, int k, int d, void* out_bf16, void* stream);
 /* `grouped_mx_gemm` (extra/gemm/moe_gemm.py:112-134; kernel contract extra/thunder/amd/grouped_mxfp8_gemm.cpp:32-158):

@@ -85,6 +85,8 @@ SIGNATURES = {
   "b200q_moe_route_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
   "b200q_moe_rows_max": (c_int, [c_int, c_int, c_int]),
   "b200q_moe_route": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+  "b200q_moe_route_pad": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+  "b200q_permute_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int, c_void_p]),
   "b200q_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
   "b200q_mx_status_read_clear": (c_int, [POINTER(c_int)]),
   "b200q_grouped_mxfp8_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),

@@ -187,19 +187,33 @@ __global__ void __launch_bounds__(ROUTE_CHUNK) route_count_kernel(const int32_t*
 }
 
 // one thread per expert: exclusive scan of its chunk counts (in place), then thread 0 builds the padded offsets
-__global__ void route_scan_kernel(int32_t* __restrict__ counts, int n_chunks, int n_experts, int32_t* __restrict__ off) {
+__global__ void route_scan_kernel(int32_t* __restrict__ counts, int n_chunks, int n_experts, int32_t* __restrict__ off, int pad,
+                                  int32_t* __restrict__ counts_out) {
   extern __shared__ int s_tot[];
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
     int run = 0;
     for (int c = 0; c < n_chunks; c++) { const int v = counts[(size_t)c * n_experts + e]; counts[(size_t)c * n_experts + e] = run; run += v; }
     s_tot[e] = run;
+    if (counts_out) counts_out[e] = run;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
     off[0] = 0;
-    for (int e = 0; e < n_experts; e++) { run += (s_tot[e] + BLOCK_ROW - 1) / BLOCK_ROW * BLOCK_ROW; off[e + 1] = run; }
+    for (int e = 0; e < n_experts; e++) { run += (s_tot[e] + pad - 1) / pad * pad; off[e + 1] = run; }
   }
+}
+
+// rows of `row_bytes` bytes moved by an index table: scatter dst[idx[i]] = src[i] or gather dst[i] = src[idx[i]]; idx < 0 skips
+template <typename V>
+__global__ void permute_rows_kernel(const V* __restrict__ src, const int32_t* __restrict__ idx, int64_t n_rows, int row_vecs, V* __restrict__ dst,
+                                    int gather) {
+  const int64_t r = blockIdx.x;
+  const int j = idx[r];
+  if (j < 0) return;
+  const V* s = src + (gather ? (int64_t)j : r) * row_vecs;
+  V* d = dst + (gather ? r : (int64_t)j) * row_vecs;
+  for (int i = threadIdx.x; i < row_vecs; i += blockDim.x) d[i] = s[i];
 }
 
 __global__ void __launch_bounds__(ROUTE_CHUNK) route_place_kernel(const int32_t* __restrict__ topi, int n, int n_experts,
@@ -293,14 +307,31 @@ extern "C" int b200q_moe_rows_max(int n_tokens, int n_experts, int k) {   // m_m
 
 extern "C" int b200q_moe_route(const float* logits, int n_tokens, int n_experts, int k, int mode, int32_t* topi, float* weights, int32_t* dest_row,
                                int32_t* off, void* scratch, void* stream) {
-  if (!logits || !topi || !weights || !dest_row || !off || !scratch) return B200Q_ERR_BAD_ARG;
+  return b200q_moe_route_pad(logits, n_tokens, n_experts, k, mode, BLOCK_ROW, topi, weights, dest_row, off, nullptr, scratch, stream);
+}
+
+extern "C" int b200q_permute_rows(const void* src, const int32_t* idx, int64_t n_rows, int row_bytes, void* dst, int gather, void* stream) {
+  if (n_rows < 0 || row_bytes <= 0 || (n_rows && (!src || !idx || !dst))) return B200Q_ERR_BAD_ARG;
+  if (row_bytes % 4) return B200Q_ERR_BAD_SHAPE;
+  if (n_rows == 0) return B200Q_OK;
+  if (row_bytes % 16 == 0 && !(((uintptr_t)src | (uintptr_t)dst) & 15))
+    permute_rows_kernel<uint4><<<(unsigned)n_rows, 128, 0, (cudaStream_t)stream>>>((const uint4*)src, idx, n_rows, row_bytes / 16, (uint4*)dst, gather);
+  else
+    permute_rows_kernel<uint32_t><<<(unsigned)n_rows, 128, 0, (cudaStream_t)stream>>>((const uint32_t*)src, idx, n_rows, row_bytes / 4, (uint32_t*)dst, gather);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+extern "C" int b200q_moe_route_pad(const float* logits, int n_tokens, int n_experts, int k, int mode, int pad, int32_t* topi, float* weights,
+                                   int32_t* dest_row, int32_t* off, int32_t* counts, void* scratch, void* stream) {
+  if (!logits || !topi || !weights || !dest_row || !off || !scratch || pad <= 0) return B200Q_ERR_BAD_ARG;
   if (n_tokens <= 0 || n_experts <= 0 || k <= 0 || k > n_experts || (mode != 0 && mode != 1)) return B200Q_ERR_BAD_ARG;
   if (n_experts > 32 * MAX_E_PER_LANE || k > 32) return B200Q_ERR_BAD_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
   const int n = n_tokens * k, n_chunks = ceil_div(n, ROUTE_CHUNK);
   route_topk_kernel<<<ceil_div(n_tokens, 8), 256, 0, st>>>(logits, n_tokens, n_experts, k, mode, topi, weights);
   route_count_kernel<<<n_chunks, ROUTE_CHUNK, n_experts * sizeof(int), st>>>(topi, n, n_experts, (int32_t*)scratch);
-  route_scan_kernel<<<1, 256, n_experts * sizeof(int), st>>>((int32_t*)scratch, n_chunks, n_experts, off);
+  route_scan_kernel<<<1, 256, n_experts * sizeof(int), st>>>((int32_t*)scratch, n_chunks, n_experts, off, pad, counts);
   route_place_kernel<<<n_chunks, ROUTE_CHUNK, 32 * n_experts * sizeof(int), st>>>(topi, n, n_experts, (const int32_t*)scratch, off, dest_row);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;

@@ -12,6 +12,7 @@ namespace {
 
 constexpr int BM = 128, BN = 128, BK = 64;      // tile; BK = 4 MMAs of K = 16
 constexpr int GEMM_THREADS = 128;
+constexpr int QGEMM_THREADS = 512;      // the dequant GEMM stages with 16 warps: unpacking the weights is its ALU-heavy part
 constexpr int SPIN = 1 << 22;
 
 __device__ int g_tc_status = 0;
@@ -185,7 +186,7 @@ struct QGemmParams {
 };
 
 template <int QT>
-__global__ void __launch_bounds__(GEMM_THREADS) tc_qgemm_kernel(const QGemmParams p) {
+__global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_kernel(const QGemmParams p) {
   extern __shared__ __align__(128) unsigned char qsm[];
   unsigned char* sA = qsm;
   unsigned char* sB = qsm + BM * QBK * 2;
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) tc_qgemm_kernel(const QGemmParam
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bar)));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int i = tid; i < QGEMM_SMEM / 16; i += GEMM_THREADS) reinterpret_cast<uint4*>(qsm)[i] = make_uint4(0, 0, 0, 0);   // rows past m / n stay zero
+  for (int i = tid; i < QGEMM_SMEM / 16; i += QGEMM_THREADS) reinterpret_cast<uint4*>(qsm)[i] = make_uint4(0, 0, 0, 0);   // rows past m / n stay zero
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -217,7 +218,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) tc_qgemm_kernel(const QGemmParam
   uint32_t phase = 0;
   for (int kg = 0; kg < p.kgroups; kg++) {
     // activations: rows m0 .. m0+m_valid, columns kg*128 .. +128, as fp16 in the cores' element order
-    for (int i = tid; i < m_valid * (QBK / 8); i += GEMM_THREADS) {
+    for (int i = tid; i < m_valid * (QBK / 8); i += QGEMM_THREADS) {
       const int r = i / (QBK / 8), kc = (i % (QBK / 8)) * 8, k = kg * QBK + kc;
       float f[8];
       if (k < p.n_in) {
@@ -245,7 +246,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) tc_qgemm_kernel(const QGemmParam
       }
     }
     // weights: 8 packed tiles (16 rows x 4 blocks each); one (row, block) pair per thread per step
-    for (int ch = tid; ch < (BN / 16) * 64; ch += GEMM_THREADS) {
+    for (int ch = tid; ch < (BN / 16) * 64; ch += QGEMM_THREADS) {
       const int tl = ch >> 6, h = (ch >> 5) & 1, l = ch & 31, g = l >> 2, t = l & 3;
       if (rt0 + tl >= p.n_row_tiles) continue;
       const uint8_t* tile = p.w + ((size_t)(rt0 + tl) * p.kgroups + kg) * TB;
@@ -304,11 +305,13 @@ __global__ void __launch_bounds__(GEMM_THREADS) tc_qgemm_kernel(const QGemmParam
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   }
   if (ok) {
-    const int row = m0 + warp * 32 + (tid & 31);
+    // 16 warps: warp % 4 is its tensor-memory sub-partition (32 rows), warp / 4 its quarter of the 128 columns
+    const int sub = warp & 3;
+    const int row = m0 + sub * 32 + (tid & 31);
 #pragma unroll 1
-    for (int j0 = 0; j0 < BN; j0 += 32) {
+    for (int j0 = (warp >> 2) * 32; j0 < (warp >> 2) * 32 + 32; j0 += 32) {
       uint32_t v[32];
-      const uint32_t ta = taddr + ((uint32_t)(warp * 32) << 16) + j0;
+      const uint32_t ta = taddr + ((uint32_t)(sub * 32) << 16) + j0;
       asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
                      "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
@@ -393,8 +396,8 @@ extern "C" int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_kernel<B200Q_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, QGEMM_SMEM));
     attr = true;
   }
-  if (qtype == B200Q_Q4_0) tc_qgemm_kernel<B200Q_Q4_0><<<grid, GEMM_THREADS, QGEMM_SMEM, (cudaStream_t)stream>>>(p);
-  else tc_qgemm_kernel<B200Q_Q8_0><<<grid, GEMM_THREADS, QGEMM_SMEM, (cudaStream_t)stream>>>(p);
+  if (qtype == B200Q_Q4_0) tc_qgemm_kernel<B200Q_Q4_0><<<grid, QGEMM_THREADS, QGEMM_SMEM, (cudaStream_t)stream>>>(p);
+  else tc_qgemm_kernel<B200Q_Q8_0><<<grid, QGEMM_THREADS, QGEMM_SMEM, (cudaStream_t)stream>>>(p);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -1,0 +1,147 @@
+"""Expert-parallel MXFP8 MoE FFN: experts split contiguously over the ranks, tokens split over the ranks at the input.
+
+The reference's grouped path on one device is route -> dispatch -> grouped_mx_gemm -> activation -> grouped_mx_gemm -> combine
+(extra/gemm/moe_routing.py:109-131, examples/mlperf/models/gpt_oss.py:215-226).  Across ranks `dispatch` and `combine` become an
+all-to-all each: a rank routes its own tokens over ALL experts, quantises every routed row once (E4M3 + E8M0, so the wire carries
+33/32 bytes per value instead of 2), lays the rows out sorted by expert (= sorted by destination rank, experts being contiguous),
+and exchanges them; the receiver regroups what it got by local expert (groups padded to 256 rows), runs the two grouped GEMMs on
+its expert shard and sends the bf16 results back the same way; the sender combines them with its routing weights.
+Every row's arithmetic is the single-GPU path's, so the result equals `MxMoE` on the concatenated tokens bit for bit.
+
+`exchange_plan` is the host-side index arithmetic (pure numpy, tested on CPU); the payload exchange is torch.distributed
+(`all_to_all_single` on NCCL; point-to-point sends elsewhere, for the CPU tests); all compute is in libb200q.so.
+"""
+from __future__ import annotations
+import numpy as np
+
+BLOCK_ROW = 256   # extra/gemm/moe_routing.py:4
+
+
+def exchange_plan(counts: np.ndarray, rank: int) -> dict:
+  """counts[s, e] = rows rank s routes to expert e (every rank holds the whole matrix after an all-gather).
+  Experts are split contiguously: rank r owns experts r*E_l .. (r+1)*E_l-1.  Returns for `rank`:
+    send_rows[r]   rows this rank sends to rank r (its compact expert-sorted buffer is cut at these sizes)
+    recv_rows[s]   rows it receives from rank s (arrival order: by source rank, inside a source by expert)
+    off_local      [E_l+1] group starts of the local expert groups, each padded to 256 rows
+    place          [sum(recv_rows)] row of the grouped buffer for every received row (a stable placement: source-major inside an expert)
+    m_local        rows of the grouped buffer (= off_local[-1])"""
+  counts = np.asarray(counts, dtype=np.int64)
+  n_ranks, n_experts = counts.shape
+  assert n_experts % n_ranks == 0, "experts must split evenly over the ranks"
+  e_l = n_experts // n_ranks
+  send_rows = counts[rank].reshape(n_ranks, e_l).sum(1)
+  mine = counts[:, rank * e_l:(rank + 1) * e_l]                  # [source, local expert]
+  recv_rows = mine.sum(1)
+  tot = mine.sum(0)
+  off_local = np.concatenate([[0], np.cumsum((tot + BLOCK_ROW - 1) // BLOCK_ROW * BLOCK_ROW)])
+  before = np.cumsum(mine, axis=0) - mine                         # rows of the same expert from earlier sources
+  place = np.empty(int(recv_rows.sum()), dtype=np.int32)
+  p = 0
+  for s in range(n_ranks):
+    for e in range(e_l):
+      c = int(mine[s, e])
+      place[p:p + c] = off_local[e] + before[s, e] + np.arange(c)
+      p += c
+  return dict(send_rows=send_rows.astype(np.int64), recv_rows=recv_rows.astype(np.int64), off_local=off_local.astype(np.int32), place=place,
+              m_local=int(off_local[-1]))
+
+
+def m_local_max(n_tokens_total: int, n_experts_local: int, k: int) -> int:
+  """Upper bound of the grouped rows one rank can receive (all routed rows of all ranks on its experts), m_max_for of
+  extra/gemm/moe_routing.py:89-90 for its shard."""
+  return (-(-n_tokens_total * k // BLOCK_ROW) + n_experts_local) * BLOCK_ROW
+
+
+def all_to_all_rows(dist, torch, send, send_rows, recv, recv_rows) -> None:
+  """Rows of `send` (cut at send_rows) to every rank, rows from every rank into `recv` (cut at recv_rows).  torch tensors [rows, width]."""
+  if dist.get_backend() == "nccl":
+    dist.all_to_all_single(recv, send, output_split_sizes=[int(x) for x in recv_rows], input_split_sizes=[int(x) for x in send_rows])
+    return
+  rank, ops, so, ro = dist.get_rank(), [], np.concatenate([[0], np.cumsum(send_rows)]), np.concatenate([[0], np.cumsum(recv_rows)])
+  for r in range(dist.get_world_size()):
+    if r == rank: recv[ro[r]:ro[r + 1]] = send[so[r]:so[r + 1]]
+    else:
+      if send_rows[r]: ops.append(dist.P2POp(dist.isend, send[so[r]:so[r + 1]].contiguous(), r))
+      if recv_rows[r]: ops.append(dist.P2POp(dist.irecv, recv[ro[r]:ro[r + 1]], r))
+  if ops:
+    for w in dist.batch_isend_irecv(ops): w.wait()
+
+
+class ExpertParallelMoE:
+  """One rank's part of an expert-parallel MXFP8 MoE FFN.  w_gate / w_up: (E_l, F, D), w_down: (E_l, D, F) fp32: THIS rank's experts
+  (rank r owns experts r*E_l ..).  Call it with this rank's tokens (T_l, D) bf16 and their router logits (T_l, E) fp32."""
+  def __init__(self, ranks, w_gate: np.ndarray, w_up: np.ndarray, w_down: np.ndarray, n_experts: int, k: int, n_tokens_total: int, mode: int = 1):
+    import torch
+    from . import moe
+    from .runtime import DeviceBuffer
+    self.torch, self.dist, self.rank, self.size = torch, ranks.dist, ranks.rank, ranks.world
+    self.E, self.k, self.mode = n_experts, k, mode
+    self.E_l, self.F, self.D = w_gate.shape
+    assert self.E_l * self.size == n_experts
+    self.local = moe.MxMoE(w_gate, w_up, w_down, k, mode)          # holds the quantised expert shard; its own routing is not used
+    self.m_max = m_local_max(n_tokens_total, self.E_l, k)
+    dev = "cuda"
+    u8 = torch.uint8
+    self.recv_q, self.recv_e8 = torch.empty((self.m_max, self.D), dtype=u8, device=dev), torch.empty((self.m_max, self.D // 32), dtype=u8, device=dev)
+    self.a_q, self.a_e8 = torch.zeros((self.m_max, self.D), dtype=u8, device=dev), torch.zeros((self.m_max, self.D // 32), dtype=u8, device=dev)
+    self.h = torch.zeros((self.m_max, 2 * self.F), dtype=torch.int16, device=dev)
+    self.act_q, self.act_e8 = torch.empty((self.m_max, self.F), dtype=u8, device=dev), torch.empty((self.m_max, self.F // 32), dtype=u8, device=dev)
+    self.y = torch.zeros((self.m_max, self.D), dtype=torch.int16, device=dev)
+    self.y_send = torch.empty((self.m_max, self.D), dtype=torch.int16, device=dev)
+    self._per_T = {}
+
+  def _buffers(self, T: int):
+    b = self._per_T.get(T)
+    if b is None:
+      from . import _lib
+      from .runtime import DeviceBuffer
+      t, n = self.torch, T * self.k
+      b = dict(topi=DeviceBuffer.empty((T, self.k), np.int32), w=DeviceBuffer.empty((T, self.k), np.float32), dest=DeviceBuffer.empty((n,), np.int32),
+               off=DeviceBuffer.empty((self.E + 1,), np.int32), scratch=DeviceBuffer(_lib.load().b200q_moe_route_scratch_bytes(T, self.E, self.k)),
+               counts=t.zeros(self.E, dtype=t.int32, device="cuda"), send_q=t.empty((n, self.D), dtype=t.uint8, device="cuda"),
+               send_e8=t.empty((n, self.D // 32), dtype=t.uint8, device="cuda"), y_back=t.empty((n, self.D), dtype=t.int16, device="cuda"),
+               out=DeviceBuffer.empty((T, self.D), np.uint16))
+      self._per_T[T] = b
+    return b
+
+  def __call__(self, x_bf16, logits, n_tokens: int):
+    """-> DeviceBuffer (T_l, D) bf16.  Runs on the default stream; the host reads the routing counts (the exchange sizes) in between."""
+    from . import _lib
+    from ._lib import check, BF16
+    from .runtime import ptr_of
+    lib, t, dist, T = _lib.load(), self.torch, self.dist, n_tokens
+    b = self._buffers(T)
+    # 1. route over all experts, compact expert-sorted order (= sorted by destination rank); quantise every routed row into it
+    check(lib.b200q_moe_route_pad(ptr_of(logits), T, self.E, self.k, self.mode, 1, b["topi"].ptr, b["w"].ptr, b["dest"].ptr, b["off"].ptr,
+                                  b["counts"].data_ptr(), b["scratch"].ptr, None))
+    check(lib.b200q_quantize_mxfp8(ptr_of(x_bf16), BF16, T, self.D, b["dest"].ptr, self.k, b["send_q"].data_ptr(), b["send_e8"].data_ptr(), None))
+    # 2. everybody's per-expert counts -> the exchange sizes and the receiver's grouping
+    t.cuda.synchronize()
+    allc = [t.empty_like(b["counts"]) for _ in range(self.size)]
+    dist.all_gather(allc, b["counts"])
+    plan = exchange_plan(np.stack([c.cpu().numpy() for c in allc]), self.rank)
+    n_recv = int(plan["recv_rows"].sum())
+    assert plan["m_local"] <= self.m_max
+    # 3. dispatch across ranks: the quantised rows and their scale bytes
+    all_to_all_rows(dist, t, b["send_q"], plan["send_rows"], self.recv_q[:n_recv], plan["recv_rows"])
+    all_to_all_rows(dist, t, b["send_e8"], plan["send_rows"], self.recv_e8[:n_recv], plan["recv_rows"])
+    # 4. regroup by local expert (256-padded groups, zero rows in the padding), expert FFN on the shard
+    place, off_l = t.from_numpy(plan["place"]).cuda(), t.from_numpy(plan["off_local"]).cuda()
+    self.a_q.zero_(); self.a_e8.zero_()
+    check(lib.b200q_permute_rows(self.recv_q.data_ptr(), place.data_ptr(), n_recv, self.D, self.a_q.data_ptr(), 0, None))
+    check(lib.b200q_permute_rows(self.recv_e8.data_ptr(), place.data_ptr(), n_recv, self.D // 32, self.a_e8.data_ptr(), 0, None))
+    m, loc = self.local, plan["m_local"]
+    if loc:
+      check(lib.b200q_grouped_mxfp8_gemm(self.a_q.data_ptr(), self.a_e8.data_ptr(), m.gu_q.ptr, m.gu_e8.ptr, off_l.data_ptr(), self.E_l, loc, 2 * self.F,
+                                         self.D, self.h.data_ptr(), None))
+      check(lib.b200q_swiglu_quantize_mxfp8(self.h.data_ptr(), loc, None, self.F, self.act_q.data_ptr(), self.act_e8.data_ptr(), None))
+      check(lib.b200q_grouped_mxfp8_gemm(self.act_q.data_ptr(), self.act_e8.data_ptr(), m.dn_q.ptr, m.dn_e8.ptr, off_l.data_ptr(), self.E_l, loc, self.D,
+                                         self.F, self.y.data_ptr(), None))
+    # 5. results back in arrival order, combine on the rank that owns the tokens
+    check(lib.b200q_permute_rows(self.y.data_ptr(), place.data_ptr(), n_recv, 2 * self.D, self.y_send.data_ptr(), 1, None))
+    t.cuda.synchronize()
+    all_to_all_rows(dist, t, self.y_send[:n_recv], plan["recv_rows"], b["y_back"], plan["send_rows"])
+    check(lib.b200q_moe_combine(b["y_back"].data_ptr(), b["dest"].ptr, b["w"].ptr, T, self.k, self.D, b["out"].ptr, None))
+    t.cuda.synchronize()
+    self.last_plan = plan
+    return b["out"]
