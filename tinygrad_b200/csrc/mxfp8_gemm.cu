@@ -13,8 +13,12 @@
 //              32-lane sub-partition, column r / 32: the layout the MMA reads), issues tcgen05.mma kind::mxf8f6f4.block_scale
 //              (scale_vec::1X, 128 x 256 x 32 per instruction, the tensor core applies both block scales), four per K step, and
 //              commits each step to the stage's "empty" mbarrier;
-//   warps 0-3  epilogue: tcgen05.ld the fp32 accumulator (256 tensor-memory columns), round to bf16, store.
+//   warps 0-3, 9-12  epilogue: tcgen05.ld the fp32 accumulator (256 tensor-memory columns; two warps per 32-lane sub-partition,
+//              128 columns each), round to bf16, store.
 // Loaders run ahead across tile boundaries; only the accumulator hand-over (one buffer) serialises epilogue and next tile.
+// Measured and not kept: a warp that prefetched the next tile's rows into L2 (bulk or per-line prefetch) fell behind the tiles
+// under the load of the ring's own copies; the ring's ~150 KB in flight per SM against the loaded L2's latency is what bounds
+// the kernel (tensor pipe 39 % active, L2 43 %, HBM 28 % under ncu).
 // Every mbarrier wait is bounded; a wait that runs out raises a status word and makes every role leave.
 #include "common.cuh"
 #include <cuda_bf16.h>
@@ -23,8 +27,7 @@
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 128, STAGES = 4;
-constexpr int EPI_WARPS = 4, LOAD_WARPS = 4, THREADS = (2 * EPI_WARPS + LOAD_WARPS + 2) * 32;   // warps 0-3 and 9-12 share the epilogue
-constexpr int PREFETCH_WARP = 2 * EPI_WARPS + LOAD_WARPS + 1;                              // warp 13 pulls the next tile's operands into L2
+constexpr int EPI_WARPS = 4, LOAD_WARPS = 4, THREADS = (2 * EPI_WARPS + LOAD_WARPS + 1) * 32;   // warps 0-3 and 9-12 share the epilogue
 constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, SF_BYTES = 2048;                    // scale chunks: A 512 B, B 2 x 512 B
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;                               // 50 KB, a multiple of 1024
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;                                 // + room to align the ring to 1024 B
@@ -84,7 +87,7 @@ __device__ __forceinline__ void arrive(uint32_t bar) { asm volatile("mbarrier.ar
 __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint8_t* __restrict__ a_q, const uint8_t* __restrict__ a_e8,
                                                                       const uint8_t* __restrict__ b_q, const uint8_t* __restrict__ b_e8,
                                                                       const int32_t* __restrict__ off, int n_experts, int m_total, int n, int k,
-                                                                      __nv_bfloat16* __restrict__ c, int pf_mode) {
+                                                                      __nv_bfloat16* __restrict__ c) {
   extern __shared__ unsigned char sm_raw[];
   __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_acc_full, bar_acc_empty, bar_drain;
   __shared__ uint32_t tmem_base;
@@ -194,27 +197,6 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
           if (done) break;
         }
       }
-    }
-  } else if (warp == PREFETCH_WARP) {
-    // ---------------------------------------------------------------- L2 prefetch of the operands one tile ahead
-    // The ring holds about 150 KB in flight per SM, which covers an L2 hit but not a trip to HBM; first touches of A / B rows
-    // are therefore requested a whole tile early (bulk prefetch of the rows' full K extent: they are contiguous), so that the
-    // ring's copies find them in L2.  Unique data one tile ahead is a few tens of MB over the whole GPU, well inside the L2.
-    auto prefetch_tile = [&](int t) {
-      const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
-      int lo = 0, hi = n_experts - 1;
-      while (lo < hi) { const int mid = (lo + hi) >> 1; if (s_off[mid + 1] <= m0) lo = mid + 1; else hi = mid; }
-      for (int r = lane; r < BM + BN; r += 32) {
-        const uint8_t* row = r < BM ? a_q + (size_t)(m0 + r) * k : b_q + ((size_t)lo * n + n0 + (r - BM)) * k;
-        if (pf_mode >= 2) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"(k) : "memory");
-      }
-    };
-    uint32_t tile_i = 0;
-    int t = pf_mode >= 1 ? blockIdx.x : n_tiles;
-    if (t < n_tiles) prefetch_tile(t);
-    for (; t < n_tiles; t += gridDim.x, tile_i++) {
-      if (tile_i > 0 && !wait_bar(s32(&bar_acc_full), (tile_i - 1) & 1, abort_flag)) break;      // tile i-1 is done: tile i runs now
-      if (t + (int)gridDim.x < n_tiles) prefetch_tile(t + gridDim.x);
     }
   } else {
     // ---------------------------------------------------------------- epilogue: accumulator row r = tensor-memory lane r
@@ -409,8 +391,6 @@ grouped_mxfp8_pair_kernel(const uint8_t* __restrict__ a_q, const uint8_t* __rest
         }
       }
     }
-  } else if (warp == PREFETCH_WARP) {
-    // (no prefetch role in the pair kernel)
   } else {
     // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
     uint32_t tile_i = 0;
@@ -504,10 +484,8 @@ extern "C" int b200q_grouped_mxfp8_gemm(const void* a_q, const void* a_e8, const
   }
   const long long tiles = (long long)(m_total / BM) * (n / BN);
   const int grid = (int)(tiles < n_sm ? tiles : n_sm);
-  static int pf_mode = -1;
-  if (pf_mode < 0) { const char* e = getenv("B200Q_MX_PF"); pf_mode = e ? atoi(e) : 2; }
   grouped_mxfp8_tc_kernel<<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>((const uint8_t*)a_q, (const uint8_t*)a_e8, (const uint8_t*)b_q, (const uint8_t*)b_e8, off,
-                                                            n_experts, m_total, n, k, (__nv_bfloat16*)c_bf16, pf_mode);
+                                                            n_experts, m_total, n, k, (__nv_bfloat16*)c_bf16);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
