@@ -313,7 +313,7 @@ def main():
   runtime.set_device(local)
   global METRIC, WORKLOAD
   cfg, qtype = llama3_8b_config(), synth.Q4_0
-  if args.model == "qwen7b_q8":       # configs[2] at batch 1 (a probe: the judged default is configs[1])
+  if args.model == "qwen7b_q8":       # configs[2] at batch 1 (a probe: the benchmark proper is configs[1])
     cfg, qtype = qwen2_7b_config(), synth.Q8_0
     METRIC = "decode tokens/s (Qwen2-7B-shape Q8_0, bs1)"
     WORKLOAD = "configs[2] at batch 1: Qwen2-7B-shaped decode, Q8_0 linears with q/k/v bias, fp16 embeddings/norms, fp16 KV cache, prompt 512 random ids, greedy"

@@ -84,10 +84,10 @@ class ExpertParallelMoE:
     u8 = torch.uint8
     self.recv_q, self.recv_e8 = torch.empty((self.m_max, self.D), dtype=u8, device=dev), torch.empty((self.m_max, self.D // 32), dtype=u8, device=dev)
     self.a_q, self.a_e8 = torch.zeros((self.m_max, self.D), dtype=u8, device=dev), torch.zeros((self.m_max, self.D // 32), dtype=u8, device=dev)
-    self.h = torch.zeros((self.m_max, 2 * self.F), dtype=torch.int16, device=dev)
+    self.h = torch.zeros((self.m_max, 4 * self.F), dtype=u8, device=dev)                 # bf16 values as bytes (NCCL has no 16-bit integer type)
     self.act_q, self.act_e8 = torch.empty((self.m_max, self.F), dtype=u8, device=dev), torch.empty((self.m_max, self.F // 32), dtype=u8, device=dev)
-    self.y = torch.zeros((self.m_max, self.D), dtype=torch.int16, device=dev)
-    self.y_send = torch.empty((self.m_max, self.D), dtype=torch.int16, device=dev)
+    self.y = torch.zeros((self.m_max, 2 * self.D), dtype=u8, device=dev)
+    self.y_send = torch.empty((self.m_max, 2 * self.D), dtype=u8, device=dev)
     self._per_T = {}
 
   def _buffers(self, T: int):
@@ -99,7 +99,7 @@ class ExpertParallelMoE:
       b = dict(topi=DeviceBuffer.empty((T, self.k), np.int32), w=DeviceBuffer.empty((T, self.k), np.float32), dest=DeviceBuffer.empty((n,), np.int32),
                off=DeviceBuffer.empty((self.E + 1,), np.int32), scratch=DeviceBuffer(_lib.load().b200q_moe_route_scratch_bytes(T, self.E, self.k)),
                counts=t.zeros(self.E, dtype=t.int32, device="cuda"), send_q=t.empty((n, self.D), dtype=t.uint8, device="cuda"),
-               send_e8=t.empty((n, self.D // 32), dtype=t.uint8, device="cuda"), y_back=t.empty((n, self.D), dtype=t.int16, device="cuda"),
+               send_e8=t.empty((n, self.D // 32), dtype=t.uint8, device="cuda"), y_back=t.empty((n, 2 * self.D), dtype=t.uint8, device="cuda"),
                out=DeviceBuffer.empty((T, self.D), np.uint16))
       self._per_T[T] = b
     return b
