@@ -216,25 +216,51 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_kernel(const QGemmPara
   const int m_valid = min(BM, p.m - m0);
   bool ok = true;
   uint32_t phase = 0;
-  for (int kg = 0; kg < p.kgroups; kg++) {
-    // activations: rows m0 .. m0+m_valid, columns kg*128 .. +128, as fp16 in the cores' element order
-    for (int i = tid; i < m_valid * (QBK / 8); i += QGEMM_THREADS) {
-      const int r = i / (QBK / 8), kc = (i % (QBK / 8)) * 8, k = kg * QBK + kc;
-      float f[8];
-      if (k < p.n_in) {
-        if (p.x_f16) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.x) + (size_t)(m0 + r) * p.n_in + k);
-          const __half2* h = reinterpret_cast<const __half2*>(&raw);
+  // Software pipeline over the K groups: the global loads of group kg+1 (activations and packed weights, into registers) are
+  // issued right after the MMAs of group kg and complete while the tensor core works; conversion + shared-memory stores follow
+  // the wait for those MMAs (the operand tiles are single-buffered: 128 KB of fp16 hi / lo halves).
+  constexpr int A_ITEMS = BM * (QBK / 8) / QGEMM_THREADS;          // 8-element activation chunks per thread (4)
+  static_assert(BM * (QBK / 8) % QGEMM_THREADS == 0 && (BN / 16) * 64 == QGEMM_THREADS, "one weight (row, block) pair per thread");
+  float4 xa[A_ITEMS][2];                                            // fp32: 8 values; fp16: the 16 raw bytes in xa[.][0]
+  uint4 wq0 = make_uint4(0, 0, 0, 0), wq1 = make_uint4(0, 0, 0, 0);
+  uint32_t wd2 = 0;
+  const int w_tl = tid >> 6, w_h = (tid >> 5) & 1, w_l = tid & 31, w_g = w_l >> 2, w_t = w_l & 3;
+  const bool w_on = rt0 + w_tl < p.n_row_tiles;
+  auto load_regs = [&](int kg) {
 #pragma unroll
-          for (int j = 0; j < 4; j++) { const float2 t2 = __half22float2(h[j]); f[2 * j] = t2.x; f[2 * j + 1] = t2.y; }
-        } else {
-          const float4 lo = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (size_t)(m0 + r) * p.n_in + k);
-          const float4 hi = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + (size_t)(m0 + r) * p.n_in + k + 4);
-          f[0] = lo.x; f[1] = lo.y; f[2] = lo.z; f[3] = lo.w; f[4] = hi.x; f[5] = hi.y; f[6] = hi.z; f[7] = hi.w;
+    for (int j = 0; j < A_ITEMS; j++) {
+      const int i = tid + j * QGEMM_THREADS, r = i / (QBK / 8), k = kg * QBK + (i % (QBK / 8)) * 8;
+      xa[j][0] = xa[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < m_valid && k < p.n_in) {
+        if (p.x_f16) xa[j][0] = *reinterpret_cast<const float4*>(reinterpret_cast<const __half*>(p.x) + (size_t)(m0 + r) * p.n_in + k);
+        else {
+          const float* src = reinterpret_cast<const float*>(p.x) + (size_t)(m0 + r) * p.n_in + k;
+          xa[j][0] = *reinterpret_cast<const float4*>(src); xa[j][1] = *reinterpret_cast<const float4*>(src + 4);
         }
-      } else {
+      }
+    }
+    if (w_on) {
+      const uint8_t* tile = p.w + ((size_t)(rt0 + w_tl) * p.kgroups + kg) * TB;
+      const unsigned short dbits = reinterpret_cast<const unsigned short*>(tile + (TB - 128))[(2 * w_g + (w_t >> 1)) * 4 + w_h * 2 + (w_t & 1)];
+      wd2 = (uint32_t)dbits | ((uint32_t)dbits << 16);
+      if (QT == B200Q_Q4_0) wq0 = ldg_stream(reinterpret_cast<const uint4*>(tile) + w_h * 32 + w_l);
+      else { wq0 = ldg_stream(reinterpret_cast<const uint4*>(tile) + (2 * w_h) * 32 + w_l); wq1 = ldg_stream(reinterpret_cast<const uint4*>(tile) + (2 * w_h + 1) * 32 + w_l); }
+    }
+  };
+  load_regs(0);
+  for (int kg = 0; kg < p.kgroups; kg++) {
+    // activations: rows m0 .. m0+m_valid, columns kg*128 .. +128, as fp16 in the cores' element order (rows past m stay zero)
 #pragma unroll
-        for (int j = 0; j < 8; j++) f[j] = 0.f;
+    for (int j = 0; j < A_ITEMS; j++) {
+      const int i = tid + j * QGEMM_THREADS, r = i / (QBK / 8), kc = (i % (QBK / 8)) * 8;
+      if (r >= m_valid) continue;
+      float f[8];
+      if (p.x_f16) {
+        const __half2* h = reinterpret_cast<const __half2*>(&xa[j][0]);
+#pragma unroll
+        for (int q = 0; q < 4; q++) { const float2 t2 = __half22float2(h[q]); f[2 * q] = t2.x; f[2 * q + 1] = t2.y; }
+      } else {
+        f[0] = xa[j][0].x; f[1] = xa[j][0].y; f[2] = xa[j][0].z; f[3] = xa[j][0].w; f[4] = xa[j][1].x; f[5] = xa[j][1].y; f[6] = xa[j][1].z; f[7] = xa[j][1].w;
       }
       __half2 o[4] = {__floats2half2_rn(f[0], f[2]), __floats2half2_rn(f[1], f[3]), __floats2half2_rn(f[4], f[6]), __floats2half2_rn(f[5], f[7])};
       *reinterpret_cast<uint4*>(sA + tile_off(r, kc, BM)) = *reinterpret_cast<const uint4*>(o);
@@ -245,37 +271,26 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_kernel(const QGemmPara
         *reinterpret_cast<uint4*>(sA2 + tile_off(r, kc, BM)) = *reinterpret_cast<const uint4*>(lo2);
       }
     }
-    // weights: 8 packed tiles (16 rows x 4 blocks each); one (row, block) pair per thread per step
-    for (int ch = tid; ch < (BN / 16) * 64; ch += QGEMM_THREADS) {
-      const int tl = ch >> 6, h = (ch >> 5) & 1, l = ch & 31, g = l >> 2, t = l & 3;
-      if (rt0 + tl >= p.n_row_tiles) continue;
-      const uint8_t* tile = p.w + ((size_t)(rt0 + tl) * p.kgroups + kg) * TB;
-      const unsigned short dbits = reinterpret_cast<const unsigned short*>(tile + (TB - 128))[(2 * g + (t >> 1)) * 4 + h * 2 + (t & 1)];
-      const uint32_t d2 = (uint32_t)dbits | ((uint32_t)dbits << 16);
-      const int r = tl * 16 + h * 8 + g;
+    // weights: 8 packed tiles (16 rows x 4 blocks each); this thread's (row, block) pair
+    if (w_on) {
+      const int r = w_tl * 16 + w_h * 8 + w_g, t = w_t;
+      const uint32_t d2 = wd2;
+      uint4 lo[4];
       if (QT == B200Q_Q4_0) {
-        const uint4 qv = reinterpret_cast<const uint4*>(tile)[h * 32 + l];
         // element e < 16 = low nibble of byte e, e >= 16 = high nibble of byte e - 16: cores 0,1 low, cores 2,3 high
-        uint4 lo[4];
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32, BN)) = q4_core<false>(qv.x, qv.y, d2, lo[0]);
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 8, BN)) = q4_core<false>(qv.z, qv.w, d2, lo[1]);
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 16, BN)) = q4_core<true>(qv.x, qv.y, d2, lo[2]);
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 24, BN)) = q4_core<true>(qv.z, qv.w, d2, lo[3]);
-        if (!p.x_f16) {
-#pragma unroll
-          for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(sB2 + tile_off(r, t * 32 + 8 * c, BN)) = lo[c];
-        }
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32, BN)) = q4_core<false>(wq0.x, wq0.y, d2, lo[0]);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 8, BN)) = q4_core<false>(wq0.z, wq0.w, d2, lo[1]);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 16, BN)) = q4_core<true>(wq0.x, wq0.y, d2, lo[2]);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 24, BN)) = q4_core<true>(wq0.z, wq0.w, d2, lo[3]);
       } else {
-        const uint4 q0 = reinterpret_cast<const uint4*>(tile)[(2 * h) * 32 + l], q1 = reinterpret_cast<const uint4*>(tile)[(2 * h + 1) * 32 + l];
-        uint4 lo[4];
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32, BN)) = q8_core(q0.x, q0.y, d2, lo[0]);
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 8, BN)) = q8_core(q0.z, q0.w, d2, lo[1]);
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 16, BN)) = q8_core(q1.x, q1.y, d2, lo[2]);
-        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 24, BN)) = q8_core(q1.z, q1.w, d2, lo[3]);
-        if (!p.x_f16) {
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32, BN)) = q8_core(wq0.x, wq0.y, d2, lo[0]);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 8, BN)) = q8_core(wq0.z, wq0.w, d2, lo[1]);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 16, BN)) = q8_core(wq1.x, wq1.y, d2, lo[2]);
+        *reinterpret_cast<uint4*>(sB + tile_off(r, t * 32 + 24, BN)) = q8_core(wq1.z, wq1.w, d2, lo[3]);
+      }
+      if (!p.x_f16) {
 #pragma unroll
-          for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(sB2 + tile_off(r, t * 32 + 8 * c, BN)) = lo[c];
-        }
+        for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(sB2 + tile_off(r, t * 32 + 8 * c, BN)) = lo[c];
       }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -300,6 +315,7 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_kernel(const QGemmPara
       }
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&bar)) : "memory");
     }
+    if (kg + 1 < p.kgroups) load_regs(kg + 1);
     if (!wait_bar(s32(&bar), phase)) { ok = false; break; }
     phase ^= 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
