@@ -233,6 +233,36 @@ def run_moe_probe(args):
                     "contraction": "tcgen05.mma kind::mxf8f6f4.block_scale, 128x256x128 tiles, TMEM accumulators"}))
 
 
+def run_batch_probe(args):
+  """configs[2] batched decode: B sequences in lock-step through the tensor-core GEMM path; prints its own JSON line."""
+  from tinygrad_b200 import build, runtime, synth
+  from tinygrad_b200.model import Transformer
+  from dataclasses import replace
+  build.build_lib()
+  runtime.set_device(0)
+  cfg, qtype = (qwen2_7b_config(), synth.Q8_0) if args.model == "qwen7b_q8" else (llama3_8b_config(), synth.Q4_0)
+  if args.blocks: cfg = replace(cfg, num_blocks=args.blocks)
+  B, plen = args.batch, 128
+  model = Transformer(cfg, synth.LazyDenseState(cfg, qtype, seed=0), ggml_type=qtype, batch=B)
+  rng = np.random.default_rng(5)
+  prompts = [[int(t) for t in rng.integers(0, cfg.vocab_size, plen)] for _ in range(B)]
+  gen = model.generate_batch(prompts)
+  for _ in range(max(3, args.warmup)): next(gen)
+  e0, e1 = runtime.Event(), runtime.Event()
+  steps = min(args.steps, 64)
+  model.stream.synchronize()
+  e0.record(model.stream)
+  for _ in range(steps): model.decode_batch_step()
+  e1.record(model.stream); model.stream.synchronize()
+  ms = e0.elapsed_ms(e1) / steps
+  peak, src = measured_peaks()
+  kv = 2 * cfg.n_kv_heads * cfg.head_dim * 2 * cfg.num_blocks * (plen + args.warmup + steps // 2) * B
+  print(json.dumps({"workload": f"configs[2]-style batched decode, {args.model}, batch {B}, prompt {plen} per sequence, greedy, lock-step",
+                    "ms_per_step": ms, "tokens_per_s": B * 1e3 / ms, "step_hbm_gbs": (model.weight_bytes + kv) / ms / 1e6,
+                    "step_frac_of_peak": (model.weight_bytes + kv) / ms / 1e6 / peak, "peak_source": src,
+                    "path": "tcgen05 dequant GEMM over the batch rows (weights streamed once per step), per-sequence attention and arg-max"}))
+
+
 def run_tp_probe(args):
   """configs[4]: Llama-3-70B-shaped Q4_0 decode, batch 1, tensor-parallel over all ranks (column QKV/gate/up/head, row O/down,
   NCCL all-reduce).  Launch under torch.distributed.run; prints its own JSON line on rank 0.  Shards are generated per rank."""
@@ -279,7 +309,8 @@ def run_tp_probe(args):
 
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "moe", "tp70b"])
+  ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "moe", "tp70b", "batch"])
+  ap.add_argument("--batch", type=int, default=8, help="sequences of the batched-decode probe (--workload batch)")
   ap.add_argument("--gemv-shape", default="28672x4096", help="rows x K of the probe (gate+up interleaved = 28672x4096)")
   ap.add_argument("--rotate-mb", type=int, default=512)
   ap.add_argument("--probe-xq", action="store_true", help="gemv probe: hand the kernel a ready-made activation record")
@@ -302,6 +333,7 @@ def main():
   if args.workload == "gemv": return run_gemv_probe(args)
   if args.workload == "moe": return run_moe_probe(args)
   if args.workload == "tp70b": return run_tp_probe(args)
+  if args.workload == "batch": return run_batch_probe(args)
   if args.warmup < 3: args.warmup = 3
 
   from tinygrad_b200 import build, runtime, synth

@@ -182,3 +182,24 @@ def test_moe_transformer_matches_mx_oracle(norm_topk):
     if tok != want[i]: break
     got.append(tok)
     if len(got) == 6: break
+
+
+@pytest.mark.parametrize("typ,B", [(2, 3), (8, 5)])
+def test_batched_decode_matches_oracle_per_sequence(typ, B):
+  """B sequences in lock-step (tokens [B, 1] per step): each stream equals the oracle's own run of that sequence."""
+  from tinygrad_b200.model import Transformer, TransformerConfig
+  kw = dict(num_blocks=2, dim=512, hidden_dim=1408, n_heads=8, n_kv_heads=2, norm_eps=1e-5, vocab_size=2000, head_dim=64, rope_theta=500000.0,
+            rope_dim=64, max_context=96, qkv_bias=(typ == 8), kv_dtype="float16")
+  cfg = TransformerConfig(**kw)
+  sd = synth.dense_model_raw(cfg, typ, seed=19, embd_std=0.3, scale_std=0.02 if typ == 2 else 0.0015)
+  shapes = {n: (o, i) for n, o, i in synth.linear_names(cfg)}
+  w = {k: (gq.weight_matrix(v, *shapes[k[:-len(".weight")]], typ) if v.dtype == np.uint8 else v) for k, v in sd.items()}
+  rng = np.random.default_rng(4)
+  prompts = [[int(t) for t in rng.integers(0, 2000, 24)] for _ in range(B)]
+  want = [llm.Transformer(llm.Config(**kw), w).generate(p, 10) for p in prompts]
+  m = Transformer(cfg, sd, ggml_type=typ, batch=B)
+  got = [[] for _ in range(B)]
+  for step, toks in enumerate(m.generate_batch(prompts)):
+    for i, t in enumerate(toks): got[i].append(t)
+    if step == 9: break
+  assert got == want

@@ -12,10 +12,10 @@
 
 namespace {
 
-__global__ void embed_rows_kernel(const __half* __restrict__ table, const int32_t* __restrict__ tokens, int n_rows, int dim, int vocab,
+__global__ void embed_rows_kernel(const __half* __restrict__ table, const int32_t* __restrict__ tokens, int token_stride, int n_rows, int dim, int vocab,
                                   float* __restrict__ x) {
   const int t = blockIdx.x;
-  int tok = tokens[t];
+  int tok = tokens[(size_t)t * token_stride];
   tok = min(max(tok, 0), vocab - 1);
   const __half2* src = reinterpret_cast<const __half2*>(table + (size_t)tok * dim);
   float2* dst = reinterpret_cast<float2*>(x + (size_t)t * dim);
@@ -61,8 +61,10 @@ template <> __device__ __forceinline__ float kv_cast<float>(float v) { return v;
 // qkv [T][(n_heads + 2 n_kv) * hd] fp32 -> q_out [T][n_heads * hd] fp32 (rotated), cache rows start_pos + t
 template <typename KV>
 __global__ void rope_kv_rows_kernel(const float* __restrict__ qkv, const float* __restrict__ rope, int start_pos, int n_heads, int n_kv, int hd,
-                                    int rope_dim, int max_context, KV* __restrict__ k_cache, KV* __restrict__ v_cache, float* __restrict__ q_out) {
-  const int t = blockIdx.x, pos = start_pos + t, half_r = rope_dim >> 1;
+                                    int rope_dim, int max_context, KV* __restrict__ k_cache, KV* __restrict__ v_cache, float* __restrict__ q_out, int batch) {
+  // batch = 0: row t is the token at position start_pos + t of one sequence; batch = 1: row t is sequence t's token at start_pos
+  const int t = blockIdx.x, pos = start_pos + (batch ? 0 : t), half_r = rope_dim >> 1;
+  if (batch) { k_cache += (size_t)t * n_kv * max_context * hd; v_cache += (size_t)t * n_kv * max_context * hd; }
   const int row = (n_heads + 2 * n_kv) * hd;
   const float* src = qkv + (size_t)t * row;
   const float* rp = rope + (size_t)pos * rope_dim;
@@ -99,21 +101,25 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 template <int HD, typename KV, typename O>
 __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const float* __restrict__ q, const KV* __restrict__ k_cache, const KV* __restrict__ v_cache,
                                                                   int start_pos, int n_rows, int n_heads, int n_kv, int max_context,
-                                                                  O* __restrict__ out) {
+                                                                  O* __restrict__ out, int batch) {
   constexpr int STRIDE = HD + 8;                         // halves per shared row: 32-bit fragment loads hit distinct banks
   extern __shared__ __align__(16) unsigned char psm[];
   __half* s_q = reinterpret_cast<__half*>(psm);          // [2][PQ][STRIDE]: fp16 high and low halves of the fp32 queries
   __half* s_k = s_q + 2 * PQ * STRIDE;                   // [PK][STRIDE]
   __half* s_v = s_k + PK * STRIDE;                       // [PK][STRIDE]
-  const int head = blockIdx.x, q0 = blockIdx.y * PQ, kvh = head / (n_heads / n_kv);
+  // batch = 1 (one new token per sequence, all at start_pos): the CTA serves row blockIdx.y alone, on that sequence's cache
+  const int head = blockIdx.x, q0 = batch ? blockIdx.y : blockIdx.y * PQ, kvh = head / (n_heads / n_kv);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
-  const KV* kc = k_cache + (size_t)kvh * max_context * HD;
-  const KV* vc = v_cache + (size_t)kvh * max_context * HD;
+  const int rows_end = batch ? q0 + 1 : n_rows;                       // rows of this tile are q0 .. min(q0 + PQ, rows_end) - 1
+  const int pos0 = start_pos + (batch ? 0 : q0);                     // position of the tile's first row
+  const size_t seq_off = batch ? (size_t)q0 * n_kv * max_context * HD : 0;
+  const KV* kc = k_cache + seq_off + (size_t)kvh * max_context * HD;
+  const KV* vc = v_cache + seq_off + (size_t)kvh * max_context * HD;
   // queries of this tile (rows past n_rows read as zero)
   for (int i = tid; i < PQ * (HD / 8); i += PF_THREADS) {
     const int r = i / (HD / 8), c = (i - r * (HD / 8)) * 8;
     uint4 hi4 = make_uint4(0, 0, 0, 0), lo4 = make_uint4(0, 0, 0, 0);
-    if (q0 + r < n_rows) {
+    if (q0 + r < rows_end) {
       const float* src = q + ((size_t)(q0 + r) * n_heads + head) * HD + c;
       const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
       const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
@@ -152,8 +158,8 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const float* _
 #pragma unroll
   for (int j = 0; j < HD / 8; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-  const int qpos0 = start_pos + q0 + warp * 16 + g, qpos1 = qpos0 + 8;     // positions of this lane's two rows
-  const int n_keys = start_pos + min(n_rows, q0 + PQ);                      // keys any row of the tile may see
+  const int qpos0 = pos0 + warp * 16 + g, qpos1 = qpos0 + 8;                // positions of this lane's two rows
+  const int n_keys = pos0 + min(rows_end - q0, PQ);                          // keys any row of the tile may see
   const float scale = 1.0f / sqrtf((float)HD);
 
   for (int k0 = 0; k0 < n_keys; k0 += PK) {
@@ -176,7 +182,7 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const float* _
       *reinterpret_cast<uint4*>(s_v + r * STRIDE + c) = vv4;
     }
     __syncthreads();
-    if (k0 > start_pos + q0 + warp * 16 + 15) continue;  // every key of the chunk is after this warp's last query
+    if (k0 > pos0 + warp * 16 + 15) continue;  // every key of the chunk is after this warp's last query
     // S = Q K^T for 16 rows x 64 keys
     float s[PK / 8][4];
 #pragma unroll
@@ -252,34 +258,34 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const float* _
 #pragma unroll
   for (int j = 0; j < HD / 8; j++) {
     const int d = j * 8 + tq * 2;
-    if (r0 < n_rows) { O* dst = out + ((size_t)r0 * n_heads + head) * HD + d; dst[0] = out_cast<O>(o[j][0] * i0); dst[1] = out_cast<O>(o[j][1] * i0); }
-    if (r1 < n_rows) { O* dst = out + ((size_t)r1 * n_heads + head) * HD + d; dst[0] = out_cast<O>(o[j][2] * i1); dst[1] = out_cast<O>(o[j][3] * i1); }
+    if (r0 < rows_end) { O* dst = out + ((size_t)r0 * n_heads + head) * HD + d; dst[0] = out_cast<O>(o[j][0] * i0); dst[1] = out_cast<O>(o[j][1] * i0); }
+    if (r1 < rows_end) { O* dst = out + ((size_t)r1 * n_heads + head) * HD + d; dst[0] = out_cast<O>(o[j][2] * i1); dst[1] = out_cast<O>(o[j][3] * i1); }
   }
 }
 
 template <int HD, typename KV, typename O>
 cudaError_t launch_prefill_attn2(const void* q, const void* kc, const void* vc, int start_pos, int n_rows, int n_heads, int n_kv, int max_context, void* out,
-                                 cudaStream_t st) {
+                                 int batch, cudaStream_t st) {
   const size_t smem = (size_t)(2 * PQ + 2 * PK) * (HD + 8) * sizeof(__half);
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD, KV, O>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  attn_prefill_kernel<HD, KV, O><<<dim3(n_heads, ceil_div(n_rows, PQ)), PF_THREADS, smem, st>>>((const float*)q, (const KV*)kc, (const KV*)vc, start_pos,
-                                                                                                   n_rows, n_heads, n_kv, max_context, (O*)out);
+  attn_prefill_kernel<HD, KV, O><<<dim3(n_heads, batch ? n_rows : ceil_div(n_rows, PQ)), PF_THREADS, smem, st>>>(
+      (const float*)q, (const KV*)kc, (const KV*)vc, start_pos, n_rows, n_heads, n_kv, max_context, (O*)out, batch);
   return cudaGetLastError();
 }
 template <int HD, typename KV>
 cudaError_t launch_prefill_attn(const void* q, const void* kc, const void* vc, int start_pos, int n_rows, int n_heads, int n_kv, int max_context, void* out,
-                                bool out_f16, cudaStream_t st) {
-  return out_f16 ? launch_prefill_attn2<HD, KV, __half>(q, kc, vc, start_pos, n_rows, n_heads, n_kv, max_context, out, st)
-                 : launch_prefill_attn2<HD, KV, float>(q, kc, vc, start_pos, n_rows, n_heads, n_kv, max_context, out, st);
+                                bool out_f16, int batch, cudaStream_t st) {
+  return out_f16 ? launch_prefill_attn2<HD, KV, __half>(q, kc, vc, start_pos, n_rows, n_heads, n_kv, max_context, out, batch, st)
+                 : launch_prefill_attn2<HD, KV, float>(q, kc, vc, start_pos, n_rows, n_heads, n_kv, max_context, out, batch, st);
 }
 
 }  // namespace
 
-extern "C" int b200q_embed_rows(const void* table_f16, const int32_t* tokens, int n_rows, int dim, int vocab, float* x, void* stream) {
-  if (!table_f16 || !tokens || !x || n_rows <= 0 || dim <= 0 || vocab <= 0) return B200Q_ERR_BAD_ARG;
+extern "C" int b200q_embed_rows(const void* table_f16, const int32_t* tokens, int token_stride, int n_rows, int dim, int vocab, float* x, void* stream) {
+  if (!table_f16 || !tokens || !x || n_rows <= 0 || dim <= 0 || vocab <= 0 || token_stride < 0) return B200Q_ERR_BAD_ARG;
   if (dim % 2) return B200Q_ERR_BAD_SHAPE;
-  embed_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>((const __half*)table_f16, tokens, n_rows, dim, vocab, x);
+  embed_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>((const __half*)table_f16, tokens, token_stride, n_rows, dim, vocab, x);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -304,29 +310,41 @@ extern "C" int b200q_add_rows_bf16(float* x, const void* y_bf16, int64_t n, void
   return B200Q_OK;
 }
 
-extern "C" int b200q_attn_prefill(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int start_pos, int n_rows,
-                                  int n_heads, int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out,
-                                  int out_dtype, void* stream) {
+static int attn_rows(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int start_pos, int n_rows, int n_heads,
+                     int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out, int out_dtype, int batch, void* stream) {
   if (!qkv || !k_cache || !v_cache || !rope || !q_scratch || !out || (out_dtype != B200Q_F16 && out_dtype != B200Q_F32)) return B200Q_ERR_BAD_ARG;
   const bool of16 = out_dtype == B200Q_F16;
   if (n_rows <= 0 || start_pos < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return B200Q_ERR_BAD_ARG;
   if (kv_dtype != B200Q_F16 && kv_dtype != B200Q_F32) return B200Q_ERR_BAD_ARG;
-  if (start_pos + n_rows > max_context) return B200Q_ERR_TOO_LARGE;
+  if (start_pos + (batch ? 1 : n_rows) > max_context) return B200Q_ERR_TOO_LARGE;
   if (rope_dim < 0 || rope_dim > head_dim || rope_dim % 2) return B200Q_ERR_BAD_SHAPE;
   if (head_dim != 16 && head_dim != 32 && head_dim != 64 && head_dim != 128) return B200Q_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   const bool h = kv_dtype == B200Q_F16;
   if (h) rope_kv_rows_kernel<__half><<<n_rows, 256, 0, st>>>(qkv, rope, start_pos, n_heads, n_kv_heads, head_dim, rope_dim, max_context, (__half*)k_cache,
-                                                           (__half*)v_cache, (float*)q_scratch);
+                                                           (__half*)v_cache, (float*)q_scratch, batch);
   else rope_kv_rows_kernel<float><<<n_rows, 256, 0, st>>>(qkv, rope, start_pos, n_heads, n_kv_heads, head_dim, rope_dim, max_context, (float*)k_cache,
-                                                        (float*)v_cache, (float*)q_scratch);
+                                                        (float*)v_cache, (float*)q_scratch, batch);
   B200Q_CHECK_CUDA(cudaGetLastError());
   cudaError_t e;
 #define PF_CASE(HD)                                                                                                                     \
-  case HD: e = h ? launch_prefill_attn<HD, __half>(q_scratch, k_cache, v_cache, start_pos, n_rows, n_heads, n_kv_heads, max_context, out, of16, st)  \
-                 : launch_prefill_attn<HD, float>(q_scratch, k_cache, v_cache, start_pos, n_rows, n_heads, n_kv_heads, max_context, out, of16, st); break;
+  case HD: e = h ? launch_prefill_attn<HD, __half>(q_scratch, k_cache, v_cache, start_pos, n_rows, n_heads, n_kv_heads, max_context, out, of16, batch, st)  \
+                 : launch_prefill_attn<HD, float>(q_scratch, k_cache, v_cache, start_pos, n_rows, n_heads, n_kv_heads, max_context, out, of16, batch, st); break;
   switch (head_dim) { PF_CASE(16) PF_CASE(32) PF_CASE(64) default: PF_CASE(128) }
 #undef PF_CASE
   B200Q_CHECK_CUDA(e);
   return B200Q_OK;
+}
+
+extern "C" int b200q_attn_prefill(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int start_pos, int n_rows,
+                                  int n_heads, int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out,
+                                  int out_dtype, void* stream) {
+  return attn_rows(qkv, k_cache, v_cache, kv_dtype, rope, start_pos, n_rows, n_heads, n_kv_heads, head_dim, rope_dim, max_context, q_scratch, out, out_dtype, 0,
+                   stream);
+}
+
+extern "C" int b200q_attn_decode_batch(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int pos, int n_seqs, int n_heads,
+                                       int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out, int out_dtype,
+                                       void* stream) {
+  return attn_rows(qkv, k_cache, v_cache, kv_dtype, rope, pos, n_seqs, n_heads, n_kv_heads, head_dim, rope_dim, max_context, q_scratch, out, out_dtype, 1, stream);
 }

@@ -57,13 +57,15 @@ DEFAULT_HANDOVER = ("attn_o",)
 class Transformer:
   def __init__(self, config: TransformerConfig, state_dict: dict, ggml_type: int = _lib.Q4_0, n_split: int = 0, use_pdl: bool = True,
                use_graph: bool = True, gemv_max_ctas: int = 0, handover=None, tp=None, output_type: int = None, prefill_rows: int = 64,
-               prefill_chunk: int = 512):
+               prefill_chunk: int = 512, batch: int = 1):
     """state_dict: the reference's tensor names -> numpy arrays; Linear weights as raw
     GGUF block bytes (uint8), embeddings / norms / biases as fp16.
     tp: a tensor_parallel.TPGroup; `config` is then the FULL model and `state_dict` this rank's shard (shard_state_dict).
     output_type: GGML type of `output.weight` when it differs from the block Linears' (Q6_K / F16 / F32 heads run the dense GEMV).
     prefill_rows: prompts with at least this many uncached tokens go through the tensor-core GEMM path, `prefill_chunk` rows at a
-    time (0: always one token per step, whose fp32-activation numerics are the reference's own); shorter ones take decode steps."""
+    time (0: always one token per step, whose fp32-activation numerics are the reference's own); shorter ones take decode steps.
+    batch: sequences decoded in lock-step (`generate_batch`): one KV cache per sequence, every Linear a tensor-core GEMM over the
+    batch rows (the reference's forward on tokens [B, T], model.py:358-364; its cache is sized by the first call's batch, model.py:200-203)."""
     self.tp, self.full_config = tp, config
     if tp is not None:
       from .tensor_parallel import local_config
@@ -110,8 +112,8 @@ class Transformer:
       b.attn_norm = DeviceBuffer.from_numpy(np.asarray(sd[f"blk.{i}.attn_norm.weight"], dtype=np.float16))
       b.ffn_norm = DeviceBuffer.from_numpy(np.asarray(sd[f"blk.{i}.ffn_norm.weight"], dtype=np.float16))
       kvdt = np.float16 if c.kv_dtype == "float16" else np.float32
-      b.k_cache = DeviceBuffer.empty((c.n_kv_heads, c.max_context, c.head_dim), kvdt, zero=True)
-      b.v_cache = DeviceBuffer.empty((c.n_kv_heads, c.max_context, c.head_dim), kvdt, zero=True)
+      b.k_cache = DeviceBuffer.empty((batch, c.n_kv_heads, c.max_context, c.head_dim), kvdt, zero=True)
+      b.v_cache = DeviceBuffer.empty((batch, c.n_kv_heads, c.max_context, c.head_dim), kvdt, zero=True)
       self.blk.append(b)
       nel, nby = quant.GGML_QUANT[ggml_type]
       self.weight_bytes += (qkv_rows * c.dim + c.dim * self.q_dim + (0 if c.num_experts else 3 * c.hidden_dim * c.dim)) // nel * nby
@@ -132,8 +134,11 @@ class Transformer:
     self.act = DeviceBuffer.empty((c.hidden_dim,), np.float32, zero=True)
     if tp is not None: self.logits_part, self.logits = tp.empty_f32(c.vocab_size), tp.empty_f32(vocab_full)
     else: self.logits = self.logits_part = DeviceBuffer.empty((c.vocab_size,), np.float32, zero=True)
-    self.tokens = DeviceBuffer.empty((c.max_context + 1,), np.int32, zero=True)
-    self.pos = DeviceBuffer.empty((1,), np.int32, zero=True)
+    self.batch = batch
+    assert batch >= 1 and (batch == 1 or tp is None), "batched decode runs on one GPU"
+    self.tokens = DeviceBuffer.empty((batch, c.max_context + 1), np.int32, zero=True)     # sequence 0 is the single-sequence state
+    self.pos = DeviceBuffer.empty((batch,), np.int32, zero=True)
+    self.seq_cache_bytes = c.n_kv_heads * c.max_context * c.head_dim * np.dtype(kvdt).itemsize
     self.attn_scratch = DeviceBuffer(_lib.load().b200q_attn_scratch_bytes(c.n_heads, c.n_kv_heads, c.head_dim, self.n_split), zero=True)
     self.argmax_scratch = DeviceBuffer(_lib.load().b200q_argmax_scratch_bytes(), zero=True)
     # Quantised activation hand-over between consecutive kernels (needs whole 128-wide groups everywhere).  Each edge of
@@ -155,7 +160,7 @@ class Transformer:
     self._graphs = {}
     self._cached_tokens: list = []
     self.prefill_rows = prefill_rows if (tp is None and c.hidden_dim % 8 == 0 and c.head_dim in (16, 32, 64, 128)) else 0
-    self.prefill_chunk, self._pf = max(1, prefill_chunk), None
+    self.prefill_chunk, self._pf, self._batch_logits = max(1, prefill_chunk), None, None
     self.is_moe, self._host_pos = c.num_experts > 0, 0
     if self.is_moe:
       assert tp is None and c.head_dim in (16, 32, 64, 128), "the mixture-of-experts model runs on the row path of one GPU"
@@ -228,7 +233,7 @@ class Transformer:
         self._pf.update(xb=DeviceBuffer.empty((T, c.dim), np.uint16), logits=DeviceBuffer.empty((T, c.num_experts), np.float32))
     return self._pf
 
-  def prefill(self, start_pos: int, n: int, sync: bool = True) -> None:
+  def prefill(self, start_pos: int, n: int, sync: bool = True, seq: int = 0) -> None:
     """Run tokens[start_pos : start_pos + n] (already on the device) through every block and fill the KV cache; no logits.
     The forward of tinygrad/llm/model.py:358-362 for T = n, in chunks: per block rmsnorm -> QKV GEMM -> RoPE + cache append +
     causal attention -> O GEMM (+residual) -> rmsnorm -> gate/up GEMM with SwiGLU epilogue -> down GEMM (+residual).
@@ -238,11 +243,13 @@ class Transformer:
     qkv_rows = self.q_dim + 2 * self.kv_dim
     for p0 in range(start_pos, start_pos + n, self.prefill_chunk):
       T = min(self.prefill_chunk, start_pos + n - p0)
-      check(lib.b200q_embed_rows(self.token_embd.ptr, self.tokens.ptr + 4 * p0, T, c.dim, self.full_config.vocab_size, f["x"].ptr, s))
+      check(lib.b200q_embed_rows(self.token_embd.ptr, self.tokens.ptr + 4 * (seq * (c.max_context + 1) + p0), 1, T, c.dim, self.full_config.vocab_size,
+                                 f["x"].ptr, s))
       for b in self.blk:
         check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.attn_norm.ptr, c.norm_eps, T, c.dim, f["xn"].ptr, F32, s))
         quant.qgemm(b.qkv.ptr, self.qtype, qkv_rows, c.dim, f["xn"], f["qkv"], T, x_dtype=F32, y_dtype=F32, bias=b.qkv_bias, stream=s)
-        check(lib.b200q_attn_prefill(f["qkv"].ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, p0, T, c.n_heads, c.n_kv_heads, c.head_dim,
+        check(lib.b200q_attn_prefill(f["qkv"].ptr, b.k_cache.ptr + seq * self.seq_cache_bytes, b.v_cache.ptr + seq * self.seq_cache_bytes, kvdt,
+                                     self.rope.ptr, p0, T, c.n_heads, c.n_kv_heads, c.head_dim,
                                      c.rope_dim, c.max_context, f["q16"].ptr, f["att"].ptr, F32, s))
         quant.qgemm(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, f["att"], f["x"], T, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s)
         check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.ffn_norm.ptr, c.norm_eps, T, c.dim, f["xn"].ptr, F32, s))
@@ -258,8 +265,56 @@ class Transformer:
         quant.qgemm(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, f["act"], f["x"], T, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s)
     if sync:
       self.stream.synchronize()
-      self.pos.copy_from(np.array([start_pos + n], dtype=np.int32))
+      self.pos.copy_from(np.array([start_pos + n], dtype=np.int32), offset=4 * seq)
       self._host_pos = start_pos + n
+
+  # ---- several sequences in lock-step ----
+  def decode_batch_step(self) -> None:
+    """One new token for each of the `batch` sequences, all at the same position: every Linear is one GEMM over the batch rows
+    (weights streamed once per step), attention runs per sequence on its own cache, the arg-max per sequence."""
+    c, lib, s, f, B = self.config, _lib.load(), self.stream.ptr, self._prefill_buffers(), self.batch
+    assert B <= self.prefill_chunk and not self.is_moe
+    kvdt = F16 if c.kv_dtype == "float16" else F32
+    qkv_rows, pos = self.q_dim + 2 * self.kv_dim, self._host_pos
+    check(lib.b200q_embed_rows(self.token_embd.ptr, self.tokens.ptr + 4 * pos, c.max_context + 1, B, c.dim, c.vocab_size, f["x"].ptr, s))
+    for b in self.blk:
+      check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.attn_norm.ptr, c.norm_eps, B, c.dim, f["xn"].ptr, F32, s))
+      quant.qgemm(b.qkv.ptr, self.qtype, qkv_rows, c.dim, f["xn"], f["qkv"], B, x_dtype=F32, y_dtype=F32, bias=b.qkv_bias, stream=s)
+      check(lib.b200q_attn_decode_batch(f["qkv"].ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, pos, B, c.n_heads, c.n_kv_heads, c.head_dim,
+                                        c.rope_dim, c.max_context, f["q16"].ptr, f["att"].ptr, F32, s))
+      quant.qgemm(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, f["att"], f["x"], B, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s)
+      check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.ffn_norm.ptr, c.norm_eps, B, c.dim, f["xn"].ptr, F32, s))
+      quant.qgemm(b.gate_up.buf.ptr, self.qtype, 2 * c.hidden_dim, c.dim, f["xn"], f["act"], B, x_dtype=F32, y_dtype=F32, epilogue=EPI_SILU_MUL, stream=s)
+      quant.qgemm(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, f["act"], f["x"], B, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s)
+    check(lib.b200q_rmsnorm_rows(f["x"].ptr, self.output_norm.ptr, c.norm_eps, B, c.dim, f["xn"].ptr, F32, s))
+    if self._batch_logits is None: self._batch_logits = DeviceBuffer.empty((B, c.vocab_size), np.float32)
+    if isinstance(self.output, quant.DenseWeight):
+      quant.gemv_dense(self.output.buf, self.output.dtype, c.vocab_size, c.dim, f["xn"], self._batch_logits, m=B, stream=s)
+    else:
+      quant.qgemm(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, f["xn"], self._batch_logits, B, x_dtype=F32, y_dtype=F32, stream=s)
+    for i in range(B):
+      check(lib.b200q_argmax_advance(self._batch_logits.ptr + 4 * i * c.vocab_size, c.vocab_size, self.tokens.ptr + 4 * i * (c.max_context + 1),
+                                     self.pos.ptr + 4 * i, self.argmax_scratch.ptr, 0, s))
+    self._host_pos += 1
+
+  def generate_batch(self, prompts: list):
+    """Greedy generation for `batch` prompts of equal length; yields the list of the sequences' next tokens per step."""
+    c, B = self.config, self.batch
+    assert len(prompts) == B and len({len(p) for p in prompts}) == 1 and len(prompts[0]) >= 1
+    L = len(prompts[0])
+    self.stream.synchronize()
+    tok = np.zeros((B, c.max_context + 1), np.int32)
+    for i, p in enumerate(prompts): tok[i, :L] = p
+    self.tokens.copy_from(tok)
+    for i in range(B):
+      if L > 1: self.prefill(0, L - 1, seq=i)
+    self.pos.copy_from(np.full((B,), L - 1, dtype=np.int32))
+    self._host_pos, n = L - 1, L
+    while n < c.max_context:
+      self.decode_batch_step()
+      self.stream.synchronize()
+      yield [int(t) for t in self.tokens.numpy((B, c.max_context + 1), np.int32)[:, n]]
+      n += 1
 
   def _step_rows(self, with_head: bool) -> None:
     """One token through the row path (mixture-of-experts models: their FFN is not part of the fused one-token chain)."""
