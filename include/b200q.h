@@ -241,9 +241,16 @@ int b200q_gemm_f16(const void* a_f16, const void* w_f16, float* c, int m, int n,
  * x rows must be 16-byte aligned (any n_in % 32 == 0 is). */
 int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue, void* y,
                 int y_dtype, int m, int n_out, int n_in, void* stream);
+/* The same Linear for a few activation rows (m <= 32: batched decode), the weight-streaming shape: the operands swap roles on the
+ * tensor core (weight rows = M, activation rows = N = 32), K is split over CTAs so that every layer fills the GPU, partial sums go
+ * through `workspace` (b200q_qgemm_skinny_workspace_bytes) and are added in a fixed order by a second kernel that also applies
+ * bias / residual / SwiGLU.  Same operands, numerics and epilogue rules as b200q_qgemm. */
+size_t b200q_qgemm_skinny_workspace_bytes(int m, int n_out, int n_in);
+int b200q_qgemm_skinny(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue, void* y,
+                       int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes, void* stream);
 /* ---- prompt processing: the row-wise pieces of Transformer.forward for T > 1 tokens (tinygrad/llm/model.py:358-364,167-198)
  * b200q_embed_rows:   x [n_rows, dim] fp32 = token_embd[tokens[t * token_stride]] (tokens on the device; stride 1: consecutive
- *   positions of one sequence, stride = row length of a [n_seqs, max_context + 1] table: the same position of every sequence).
+ *   positions of one sequence, stride = row length of a [n_seqs, max_context + 1] table: the same position of every sequence); pos_dev (device, may be NULL) is added to the index, so a captured graph follows the position.
  * b200q_rmsnorm_rows: out [n_rows, dim] (out_dtype fp16 / fp32 / bf16) = RMSNorm(x) * weight (tinygrad/nn/__init__.py:300-304).
  * b200q_add_rows_bf16: x[i] += y[i] over n values, x fp32, y bf16 (the residual add behind the bf16 output of the expert FFN).
  * b200q_attn_prefill: qkv [n_rows, (n_heads + 2 n_kv_heads) * head_dim] fp32 holds the projections of the tokens at
@@ -251,14 +258,16 @@ int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x_dtype, con
  *   appends k / v to the caches [n_kv_heads, max_context, head_dim] (kv_dtype) and writes the causal attention of every new
  *   query over cache rows 0 .. its own position to out [n_rows, n_heads * head_dim] (out_dtype fp16 / fp32).  q_scratch: n_rows * n_heads * head_dim
  *   floats.  Queries and probabilities enter the tensor core as fp16 hi + lo pairs, keys / values as cached.  head_dim in {16, 32, 64, 128}. */
-int b200q_embed_rows(const void* table_f16, const int32_t* tokens, int token_stride, int n_rows, int dim, int vocab, float* x, void* stream);
+int b200q_embed_rows(const void* table_f16, const int32_t* tokens, int token_stride, const int32_t* pos_dev, int n_rows, int dim, int vocab, float* x,
+                     void* stream);
 int b200q_rmsnorm_rows(const float* x, const void* weight_f16, float eps, int n_rows, int dim, void* out, int out_dtype, void* stream);
 int b200q_add_rows_bf16(float* x, const void* y_bf16, int64_t n, void* stream);
 int b200q_attn_prefill(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int start_pos, int n_rows, int n_heads,
                        int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out, int out_dtype, void* stream);
 /* Batched decode (the reference's forward on tokens [B, 1], tinygrad/llm/model.py:358-364 with B > 1): row b of qkv is sequence b's
- * new token, every sequence at position pos; caches [n_seqs, n_kv_heads, max_context, head_dim]; otherwise as b200q_attn_prefill. */
-int b200q_attn_decode_batch(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int pos, int n_seqs, int n_heads,
+ * new token, every sequence at position pos (or *pos_dev when that device pointer is given: graph replay); caches
+ * [n_seqs, n_kv_heads, max_context, head_dim]; otherwise as b200q_attn_prefill. */
+int b200q_attn_decode_batch(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int pos, const int32_t* pos_dev, int n_seqs, int n_heads,
                             int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out, int out_dtype, void* stream);
 int b200q_tc_status_read_clear(int* status);
 

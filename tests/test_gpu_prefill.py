@@ -203,3 +203,42 @@ def test_batched_decode_matches_oracle_per_sequence(typ, B):
     for i, t in enumerate(toks): got[i].append(t)
     if step == 9: break
   assert got == want
+
+
+@pytest.mark.parametrize("tag,m,n_out,n_in,x_dtype,epi", [("q4_0", 8, 4096, 4096, np.float32, "res"), ("q8_0", 32, 512, 18944, np.float32, "bias"),
+                                                        ("q4_0", 5, 200, 96, np.float16, "lin"), ("q8_0", 17, 48, 1536, np.float32, "silu"),
+                                                        ("q4_0", 1, 14336 * 2, 4096, np.float32, "silu")])
+def test_skinny_split_k_gemm(tag, m, n_out, n_in, x_dtype, epi):
+  """Few-row GEMM (swapped operands, split K, fixed-order reduction) against the fp32 product; bit-reproducible across runs."""
+  from tinygrad_b200 import quant, _lib
+  from tinygrad_b200.runtime import DeviceBuffer
+  typ = {"q4_0": 2, "q8_0": 8}[tag]
+  rng = np.random.default_rng(m + n_out)
+  x = rng.standard_normal((m, n_in)).astype(x_dtype)
+  dx = DeviceBuffer.from_numpy(x)
+  ws = DeviceBuffer(quant.qgemm_skinny_workspace_bytes(m, n_out, n_in))
+  if epi == "silu":
+    hid = n_out // 2
+    g, u = synth.BLOCK_MAKERS[typ](hid, n_in, rng), synth.BLOCK_MAKERS[typ](hid, n_in, rng)
+    pw = quant.repack(g, hid, n_in, typ, raw_up=u)
+    y = DeviceBuffer.empty((m, hid), np.float32)
+    quant.qgemm_skinny(pw.buf.ptr, typ, n_out, n_in, dx, y, m, ws, x_dtype=quant._DT[np.dtype(x_dtype)], epilogue=_lib.EPI_SILU_MUL)
+    xf = x.astype(np.float32)
+    ref = llm.silu(xf @ gq.weight_matrix(g, hid, n_in, typ).T) * (xf @ gq.weight_matrix(u, hid, n_in, typ).T)
+  else:
+    raw = synth.BLOCK_MAKERS[typ](n_out, n_in, rng)
+    pw = quant.repack(raw, n_out, n_in, typ)
+    bias = rng.standard_normal(n_out).astype(np.float16) if epi == "bias" else None
+    res = rng.standard_normal((m, n_out)).astype(np.float32) if epi == "res" else None
+    db = DeviceBuffer.from_numpy(bias) if bias is not None else None
+    y = DeviceBuffer.from_numpy(res) if res is not None else DeviceBuffer.empty((m, n_out), np.float32)
+    quant.qgemm_skinny(pw.buf.ptr, typ, n_out, n_in, dx, y, m, ws, x_dtype=quant._DT[np.dtype(x_dtype)], bias=db, residual=y if res is not None else None)
+    w = gq.weight_matrix(raw, n_out, n_in, typ)
+    if x_dtype == np.float16: w = w.astype(np.float16).astype(np.float32)
+    ref = x.astype(np.float32) @ w.T + (bias.astype(np.float32) if bias is not None else 0.0) + (res if res is not None else 0.0)
+  got = y.numpy()
+  assert np.abs(got - ref).max() <= 3e-5 * max(1.0, np.abs(ref).max())
+  if epi == "lin":
+    y2 = DeviceBuffer.empty((m, n_out), np.float32)
+    quant.qgemm_skinny(pw.buf.ptr, typ, n_out, n_in, dx, y2, m, ws, x_dtype=quant._DT[np.dtype(x_dtype)])
+    np.testing.assert_array_equal(y2.numpy(), got)

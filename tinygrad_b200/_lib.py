@@ -72,13 +72,16 @@ SIGNATURES = {
   "b200q_advance": (c_int, [c_void_p, c_int, c_void_p]),
   "b200q_gemm_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
   "b200q_qgemm": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
-  "b200q_embed_rows": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+  "b200q_qgemm_skinny_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+  "b200q_qgemm_skinny": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
+                                c_void_p]),
+  "b200q_embed_rows": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
   "b200q_rmsnorm_rows": (c_int, [c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_int, c_void_p]),
   "b200q_add_rows_bf16": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
   "b200q_attn_prefill": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                 c_int, c_void_p]),
-  "b200q_attn_decode_batch": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                c_int, c_void_p]),
+  "b200q_attn_decode_batch": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                     c_void_p, c_int, c_void_p]),
   "b200q_tc_status_read_clear": (c_int, [POINTER(c_int)]),
   "b200q_quantize_mxfp8": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
   "b200q_gemv_dense": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int,

@@ -12,10 +12,10 @@
 
 namespace {
 
-__global__ void embed_rows_kernel(const __half* __restrict__ table, const int32_t* __restrict__ tokens, int token_stride, int n_rows, int dim, int vocab,
-                                  float* __restrict__ x) {
+__global__ void embed_rows_kernel(const __half* __restrict__ table, const int32_t* __restrict__ tokens, int token_stride, const int32_t* __restrict__ pos_dev,
+                                  int n_rows, int dim, int vocab, float* __restrict__ x) {
   const int t = blockIdx.x;
-  int tok = tokens[(size_t)t * token_stride];
+  int tok = tokens[(size_t)t * token_stride + (pos_dev ? *pos_dev : 0)];
   tok = min(max(tok, 0), vocab - 1);
   const __half2* src = reinterpret_cast<const __half2*>(table + (size_t)tok * dim);
   float2* dst = reinterpret_cast<float2*>(x + (size_t)t * dim);
@@ -61,7 +61,9 @@ template <> __device__ __forceinline__ float kv_cast<float>(float v) { return v;
 // qkv [T][(n_heads + 2 n_kv) * hd] fp32 -> q_out [T][n_heads * hd] fp32 (rotated), cache rows start_pos + t
 template <typename KV>
 __global__ void rope_kv_rows_kernel(const float* __restrict__ qkv, const float* __restrict__ rope, int start_pos, int n_heads, int n_kv, int hd,
-                                    int rope_dim, int max_context, KV* __restrict__ k_cache, KV* __restrict__ v_cache, float* __restrict__ q_out, int batch) {
+                                    int rope_dim, int max_context, KV* __restrict__ k_cache, KV* __restrict__ v_cache, float* __restrict__ q_out, int batch,
+                                    const int32_t* __restrict__ pos_dev) {
+  if (pos_dev) start_pos = min(max(*pos_dev, 0), max_context - 1);      // position kept on the device (graph replay)
   // batch = 0: row t is the token at position start_pos + t of one sequence; batch = 1: row t is sequence t's token at start_pos
   const int t = blockIdx.x, pos = start_pos + (batch ? 0 : t), half_r = rope_dim >> 1;
   if (batch) { k_cache += (size_t)t * n_kv * max_context * hd; v_cache += (size_t)t * n_kv * max_context * hd; }
@@ -101,7 +103,8 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 template <int HD, typename KV, typename O>
 __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const float* __restrict__ q, const KV* __restrict__ k_cache, const KV* __restrict__ v_cache,
                                                                   int start_pos, int n_rows, int n_heads, int n_kv, int max_context,
-                                                                  O* __restrict__ out, int batch) {
+                                                                  O* __restrict__ out, int batch, const int32_t* __restrict__ pos_dev) {
+  if (pos_dev) start_pos = min(max(*pos_dev, 0), max_context - 1);
   constexpr int STRIDE = HD + 8;                         // halves per shared row: 32-bit fragment loads hit distinct banks
   extern __shared__ __align__(16) unsigned char psm[];
   __half* s_q = reinterpret_cast<__half*>(psm);          // [2][PQ][STRIDE]: fp16 high and low halves of the fp32 queries
@@ -265,27 +268,28 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const float* _
 
 template <int HD, typename KV, typename O>
 cudaError_t launch_prefill_attn2(const void* q, const void* kc, const void* vc, int start_pos, int n_rows, int n_heads, int n_kv, int max_context, void* out,
-                                 int batch, cudaStream_t st) {
+                                 int batch, const int32_t* pos_dev, cudaStream_t st) {
   const size_t smem = (size_t)(2 * PQ + 2 * PK) * (HD + 8) * sizeof(__half);
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD, KV, O>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   attn_prefill_kernel<HD, KV, O><<<dim3(n_heads, batch ? n_rows : ceil_div(n_rows, PQ)), PF_THREADS, smem, st>>>(
-      (const float*)q, (const KV*)kc, (const KV*)vc, start_pos, n_rows, n_heads, n_kv, max_context, (O*)out, batch);
+      (const float*)q, (const KV*)kc, (const KV*)vc, start_pos, n_rows, n_heads, n_kv, max_context, (O*)out, batch, pos_dev);
   return cudaGetLastError();
 }
 template <int HD, typename KV>
 cudaError_t launch_prefill_attn(const void* q, const void* kc, const void* vc, int start_pos, int n_rows, int n_heads, int n_kv, int max_context, void* out,
-                                bool out_f16, int batch, cudaStream_t st) {
-  return out_f16 ? launch_prefill_attn2<HD, KV, __half>(q, kc, vc, start_pos, n_rows, n_heads, n_kv, max_context, out, batch, st)
-                 : launch_prefill_attn2<HD, KV, float>(q, kc, vc, start_pos, n_rows, n_heads, n_kv, max_context, out, batch, st);
+                                bool out_f16, int batch, const int32_t* pos_dev, cudaStream_t st) {
+  return out_f16 ? launch_prefill_attn2<HD, KV, __half>(q, kc, vc, start_pos, n_rows, n_heads, n_kv, max_context, out, batch, pos_dev, st)
+                 : launch_prefill_attn2<HD, KV, float>(q, kc, vc, start_pos, n_rows, n_heads, n_kv, max_context, out, batch, pos_dev, st);
 }
 
 }  // namespace
 
-extern "C" int b200q_embed_rows(const void* table_f16, const int32_t* tokens, int token_stride, int n_rows, int dim, int vocab, float* x, void* stream) {
+extern "C" int b200q_embed_rows(const void* table_f16, const int32_t* tokens, int token_stride, const int32_t* pos_dev, int n_rows, int dim, int vocab,
+                                float* x, void* stream) {
   if (!table_f16 || !tokens || !x || n_rows <= 0 || dim <= 0 || vocab <= 0 || token_stride < 0) return B200Q_ERR_BAD_ARG;
   if (dim % 2) return B200Q_ERR_BAD_SHAPE;
-  embed_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>((const __half*)table_f16, tokens, token_stride, n_rows, dim, vocab, x);
+  embed_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>((const __half*)table_f16, tokens, token_stride, pos_dev, n_rows, dim, vocab, x);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -311,7 +315,8 @@ extern "C" int b200q_add_rows_bf16(float* x, const void* y_bf16, int64_t n, void
 }
 
 static int attn_rows(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int start_pos, int n_rows, int n_heads,
-                     int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out, int out_dtype, int batch, void* stream) {
+                     int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out, int out_dtype, int batch,
+                     const int32_t* pos_dev, void* stream) {
   if (!qkv || !k_cache || !v_cache || !rope || !q_scratch || !out || (out_dtype != B200Q_F16 && out_dtype != B200Q_F32)) return B200Q_ERR_BAD_ARG;
   const bool of16 = out_dtype == B200Q_F16;
   if (n_rows <= 0 || start_pos < 0 || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return B200Q_ERR_BAD_ARG;
@@ -322,14 +327,14 @@ static int attn_rows(const float* qkv, void* k_cache, void* v_cache, int kv_dtyp
   cudaStream_t st = (cudaStream_t)stream;
   const bool h = kv_dtype == B200Q_F16;
   if (h) rope_kv_rows_kernel<__half><<<n_rows, 256, 0, st>>>(qkv, rope, start_pos, n_heads, n_kv_heads, head_dim, rope_dim, max_context, (__half*)k_cache,
-                                                           (__half*)v_cache, (float*)q_scratch, batch);
+                                                           (__half*)v_cache, (float*)q_scratch, batch, pos_dev);
   else rope_kv_rows_kernel<float><<<n_rows, 256, 0, st>>>(qkv, rope, start_pos, n_heads, n_kv_heads, head_dim, rope_dim, max_context, (float*)k_cache,
-                                                        (float*)v_cache, (float*)q_scratch, batch);
+                                                        (float*)v_cache, (float*)q_scratch, batch, pos_dev);
   B200Q_CHECK_CUDA(cudaGetLastError());
   cudaError_t e;
 #define PF_CASE(HD)                                                                                                                     \
-  case HD: e = h ? launch_prefill_attn<HD, __half>(q_scratch, k_cache, v_cache, start_pos, n_rows, n_heads, n_kv_heads, max_context, out, of16, batch, st)  \
-                 : launch_prefill_attn<HD, float>(q_scratch, k_cache, v_cache, start_pos, n_rows, n_heads, n_kv_heads, max_context, out, of16, batch, st); break;
+  case HD: e = h ? launch_prefill_attn<HD, __half>(q_scratch, k_cache, v_cache, start_pos, n_rows, n_heads, n_kv_heads, max_context, out, of16, batch, pos_dev, st)  \
+                 : launch_prefill_attn<HD, float>(q_scratch, k_cache, v_cache, start_pos, n_rows, n_heads, n_kv_heads, max_context, out, of16, batch, pos_dev, st); break;
   switch (head_dim) { PF_CASE(16) PF_CASE(32) PF_CASE(64) default: PF_CASE(128) }
 #undef PF_CASE
   B200Q_CHECK_CUDA(e);
@@ -340,11 +345,12 @@ extern "C" int b200q_attn_prefill(const float* qkv, void* k_cache, void* v_cache
                                   int n_heads, int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out,
                                   int out_dtype, void* stream) {
   return attn_rows(qkv, k_cache, v_cache, kv_dtype, rope, start_pos, n_rows, n_heads, n_kv_heads, head_dim, rope_dim, max_context, q_scratch, out, out_dtype, 0,
-                   stream);
+                   nullptr, stream);
 }
 
-extern "C" int b200q_attn_decode_batch(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int pos, int n_seqs, int n_heads,
-                                       int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out, int out_dtype,
-                                       void* stream) {
-  return attn_rows(qkv, k_cache, v_cache, kv_dtype, rope, pos, n_seqs, n_heads, n_kv_heads, head_dim, rope_dim, max_context, q_scratch, out, out_dtype, 1, stream);
+extern "C" int b200q_attn_decode_batch(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int pos, const int32_t* pos_dev,
+                                       int n_seqs, int n_heads, int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out,
+                                       int out_dtype, void* stream) {
+  return attn_rows(qkv, k_cache, v_cache, kv_dtype, rope, pos_dev ? 0 : pos, n_seqs, n_heads, n_kv_heads, head_dim, rope_dim, max_context, q_scratch, out,
+                   out_dtype, 1, pos_dev, stream);
 }

@@ -370,6 +370,191 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_kernel(const QGemmPara
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(BN) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Few activation rows (batched decode, m <= 32): the weight-streaming shape.  Operands swap roles: the 128 weight rows of a
+// tile are the MMA's M, the (up to 32) activation rows its N, so the tensor core does 128 x 32 x 16 per instruction instead of
+// 128 x 128 x 16 on mostly zero rows; the K range is split over blockIdx.y so that layers with few row tiles still fill the GPU;
+// the operand stage is 80 KB (weights hi / lo 64 KB + activations hi / lo 16 KB), double-buffered, so unpacking group kg+1 runs
+// under the MMAs of group kg.  Every CTA writes its fp32 partial [split][act row][weight row] to a workspace; a second kernel
+// sums the splits in a fixed order and applies bias / residual / SwiGLU (deterministic: no floating-point atomics).
+constexpr int SK_N = 32;                                        // activation rows per MMA (N)
+constexpr int SK_STAGE = 2 * (BN + SK_N) * QBK * 2;             // weights 128 rows + activations 32 rows, hi and lo: 80 KB
+constexpr int SK_SMEM = 2 * SK_STAGE;
+
+struct SkinnyParams {
+  const uint8_t* w; const void* x; float* part;
+  int m, n_out, n_in, kgroups, n_row_tiles, x_f16, groups_per_split;
+};
+
+template <int QT>
+__global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_skinny_kernel(const SkinnyParams p) {
+  extern __shared__ __align__(128) unsigned char ssm[];
+  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ uint32_t tmem_base;
+  constexpr int TB = tile_bytes(QT);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int rt0 = blockIdx.x * (BN / 16), split = blockIdx.y;
+  const int kg0 = split * p.groups_per_split, kg1 = min(p.kgroups, kg0 + p.groups_per_split);
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&tmem_base)), "r"(SK_N) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bars[0])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bars[1])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = tid; i < SK_SMEM / 16; i += QGEMM_THREADS) reinterpret_cast<uint4*>(ssm)[i] = make_uint4(0, 0, 0, 0);   // rows past m / n_out stay zero
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t taddr = tmem_base;
+  const uint32_t idesc = make_idesc(BN, SK_N);                   // M = 128 weight rows, N = 32 activation rows
+  // this thread's pieces: one (weight row, block) pair, and one 8-value chunk of the activations (32 rows x 16 chunks = 512)
+  const int w_tl = tid >> 6, w_h = (tid >> 5) & 1, w_l = tid & 31, w_g = w_l >> 2, w_t = w_l & 3;
+  const bool w_on = rt0 + w_tl < p.n_row_tiles;
+  const int a_r = tid >> 4, a_kc = (tid & 15) * 8;
+  float4 xa0, xa1;
+  uint4 wq0 = make_uint4(0, 0, 0, 0), wq1 = make_uint4(0, 0, 0, 0);
+  uint32_t wd2 = 0;
+  auto load_regs = [&](int kg) {
+    xa0 = xa1 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int k = kg * QBK + a_kc;
+    if (a_r < p.m && k < p.n_in) {
+      if (p.x_f16) xa0 = *reinterpret_cast<const float4*>(reinterpret_cast<const __half*>(p.x) + (size_t)a_r * p.n_in + k);
+      else {
+        const float* src = reinterpret_cast<const float*>(p.x) + (size_t)a_r * p.n_in + k;
+        xa0 = *reinterpret_cast<const float4*>(src); xa1 = *reinterpret_cast<const float4*>(src + 4);
+      }
+    }
+    if (w_on) {
+      const uint8_t* tile = p.w + ((size_t)(rt0 + w_tl) * p.kgroups + kg) * TB;
+      const unsigned short dbits = reinterpret_cast<const unsigned short*>(tile + (TB - 128))[(2 * w_g + (w_t >> 1)) * 4 + w_h * 2 + (w_t & 1)];
+      wd2 = (uint32_t)dbits | ((uint32_t)dbits << 16);
+      if (QT == B200Q_Q4_0) wq0 = ldg_stream(reinterpret_cast<const uint4*>(tile) + w_h * 32 + w_l);
+      else { wq0 = ldg_stream(reinterpret_cast<const uint4*>(tile) + (2 * w_h) * 32 + w_l); wq1 = ldg_stream(reinterpret_cast<const uint4*>(tile) + (2 * w_h + 1) * 32 + w_l); }
+    }
+  };
+  bool ok = true;
+  if (kg0 < kg1) load_regs(kg0);
+  for (int kg = kg0, it = 0; kg < kg1; kg++, it++) {
+    const int st = it & 1;
+    unsigned char* sW = ssm + st * SK_STAGE;                    // weights hi
+    unsigned char* sW2 = sW + BN * QBK * 2;                     // weights lo
+    unsigned char* sX = sW2 + BN * QBK * 2;                     // activations hi
+    unsigned char* sX2 = sX + SK_N * QBK * 2;                   // activations lo
+    if (it >= 2 && !wait_bar(s32(&bars[st]), ((it >> 1) - 1) & 1)) { ok = false; break; }     // the MMAs that read this stage are done
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (a_r < p.m) {
+      float f[8];
+      if (p.x_f16) {
+        const __half2* h = reinterpret_cast<const __half2*>(&xa0);
+#pragma unroll
+        for (int q = 0; q < 4; q++) { const float2 t2 = __half22float2(h[q]); f[2 * q] = t2.x; f[2 * q + 1] = t2.y; }
+      } else { f[0] = xa0.x; f[1] = xa0.y; f[2] = xa0.z; f[3] = xa0.w; f[4] = xa1.x; f[5] = xa1.y; f[6] = xa1.z; f[7] = xa1.w; }
+      __half2 o[4] = {__floats2half2_rn(f[0], f[2]), __floats2half2_rn(f[1], f[3]), __floats2half2_rn(f[4], f[6]), __floats2half2_rn(f[5], f[7])};
+      *reinterpret_cast<uint4*>(sX + tile_off(a_r, a_kc, SK_N)) = *reinterpret_cast<const uint4*>(o);
+      if (!p.x_f16) {
+        const float2 h0 = __half22float2(o[0]), h1 = __half22float2(o[1]), h2 = __half22float2(o[2]), h3 = __half22float2(o[3]);
+        __half2 lo2[4] = {__floats2half2_rn(f[0] - h0.x, f[2] - h0.y), __floats2half2_rn(f[1] - h1.x, f[3] - h1.y),
+                          __floats2half2_rn(f[4] - h2.x, f[6] - h2.y), __floats2half2_rn(f[5] - h3.x, f[7] - h3.y)};
+        *reinterpret_cast<uint4*>(sX2 + tile_off(a_r, a_kc, SK_N)) = *reinterpret_cast<const uint4*>(lo2);
+      }
+    }
+    if (w_on) {
+      const int r = w_tl * 16 + w_h * 8 + w_g, t = w_t;
+      uint4 lo[4];
+      if (QT == B200Q_Q4_0) {
+        *reinterpret_cast<uint4*>(sW + tile_off(r, t * 32, BN)) = q4_core<false>(wq0.x, wq0.y, wd2, lo[0]);
+        *reinterpret_cast<uint4*>(sW + tile_off(r, t * 32 + 8, BN)) = q4_core<false>(wq0.z, wq0.w, wd2, lo[1]);
+        *reinterpret_cast<uint4*>(sW + tile_off(r, t * 32 + 16, BN)) = q4_core<true>(wq0.x, wq0.y, wd2, lo[2]);
+        *reinterpret_cast<uint4*>(sW + tile_off(r, t * 32 + 24, BN)) = q4_core<true>(wq0.z, wq0.w, wd2, lo[3]);
+      } else {
+        *reinterpret_cast<uint4*>(sW + tile_off(r, t * 32, BN)) = q8_core(wq0.x, wq0.y, wd2, lo[0]);
+        *reinterpret_cast<uint4*>(sW + tile_off(r, t * 32 + 8, BN)) = q8_core(wq0.z, wq0.w, wd2, lo[1]);
+        *reinterpret_cast<uint4*>(sW + tile_off(r, t * 32 + 16, BN)) = q8_core(wq1.x, wq1.y, wd2, lo[2]);
+        *reinterpret_cast<uint4*>(sW + tile_off(r, t * 32 + 24, BN)) = q8_core(wq1.z, wq1.w, wd2, lo[3]);
+      }
+      if (!p.x_f16) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(sW2 + tile_off(r, t * 32 + 8 * c, BN)) = lo[c];
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int kk = 0; kk < QBK / 16; kk++) {
+        const uint64_t dw = make_desc(s32(sW) + kk * 2 * (BN * 16), BN * 16, 128), dx = make_desc(s32(sX) + kk * 2 * (SK_N * 16), SK_N * 16, 128);
+        const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
+        asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                     ::"r"(taddr), "l"(dw), "l"(dx), "r"(idesc), "r"(acc) : "memory");
+        if (!p.x_f16) {
+          const uint64_t dw2 = make_desc(s32(sW2) + kk * 2 * (BN * 16), BN * 16, 128), dx2 = make_desc(s32(sX2) + kk * 2 * (SK_N * 16), SK_N * 16, 128);
+          asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                       ::"r"(taddr), "l"(dw), "l"(dx2), "r"(idesc), "r"(1u) : "memory");
+          asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                       ::"r"(taddr), "l"(dw2), "l"(dx), "r"(idesc), "r"(1u) : "memory");
+        }
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&bars[st])) : "memory");
+    }
+    if (kg + 1 < kg1) load_regs(kg + 1);
+  }
+  // the last commit covers every MMA issued before it
+  const int n_it = kg1 - kg0;
+  if (ok && n_it > 0) ok = wait_bar(s32(&bars[(n_it - 1) & 1]), ((n_it - 1) >> 1) & 1);
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (ok && warp < 4) {
+    // accumulator row = weight row (tensor-memory lane), column = activation row
+    uint32_t v[32];
+    const uint32_t ta = taddr + ((uint32_t)(warp * 32) << 16);
+    if (n_it > 0) {
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                   : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+                     "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+                     "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+                     "=r"(v[31])
+                   : "r"(ta));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j++) v[j] = 0u;
+    }
+    const int col = rt0 * 16 + tid;                              // weight row = output column of y
+    if (col < p.n_out) {
+#pragma unroll
+      for (int j = 0; j < 32; j++)
+        if (j < p.m) p.part[((size_t)split * p.m + j) * p.n_out + col] = __uint_as_float(v[j]);       // consecutive lanes: consecutive addresses
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(SK_N) : "memory");
+}
+
+// y = sum over splits (fixed order) + bias + residual, or the SwiGLU product of interleaved gate / up columns
+__global__ void skinny_reduce_kernel(const float* __restrict__ part, int n_splits, int m, int n_out, const __half* __restrict__ bias,
+                                     const void* __restrict__ residual, void* __restrict__ y, int y_f16, int silu_mul) {
+  const int n_y = silu_mul ? n_out / 2 : n_out;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)m * n_y) return;
+  const int row = (int)(i / n_y), c = (int)(i - (size_t)row * n_y);
+  auto total = [&](int col) { float s = 0.f; for (int z = 0; z < n_splits; z++) s += part[((size_t)z * m + row) * n_out + col]; return s; };
+  float o;
+  if (silu_mul) {
+    const int col = (c >> 3) * 16 + (c & 7);                     // 8 gate rows then 8 up rows per 16-row tile
+    const float g = total(col), u = total(col + 8);
+    o = (g / (1.f + expf(-g))) * u;
+  } else {
+    o = total(c);
+    if (bias) o += __half2float(bias[c]);
+    if (residual) o += y_f16 ? __half2float(reinterpret_cast<const __half*>(residual)[i]) : reinterpret_cast<const float*>(residual)[i];
+  }
+  if (y_f16) reinterpret_cast<__half*>(y)[i] = __float2half_rn(o); else reinterpret_cast<float*>(y)[i] = o;
+}
+
 }  // namespace
 
 extern "C" int b200q_tc_status_read_clear(int* status) {
@@ -414,6 +599,70 @@ extern "C" int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x
   }
   if (qtype == B200Q_Q4_0) tc_qgemm_kernel<B200Q_Q4_0><<<grid, QGEMM_THREADS, QGEMM_SMEM, (cudaStream_t)stream>>>(p);
   else tc_qgemm_kernel<B200Q_Q8_0><<<grid, QGEMM_THREADS, QGEMM_SMEM, (cudaStream_t)stream>>>(p);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+static int skinny_splits(int n_row_tiles, int kgroups, int n_sm) {
+  const int tiles = ceil_div(n_row_tiles, BN / 16);
+  int splits = ceil_div(2 * n_sm, tiles);                         // about two CTAs per SM over the whole launch
+  const int max_splits = kgroups / 4 > 0 ? kgroups / 4 : 1;       // at least 4 K groups per CTA
+  if (splits > max_splits) splits = max_splits;
+  return splits < 1 ? 1 : splits;
+}
+
+static int sm_count_cached() {
+  static int n_sm = 0;
+  if (!n_sm) {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    n_sm = sms;
+  }
+  return n_sm;
+}
+
+extern "C" size_t b200q_qgemm_skinny_workspace_bytes(int m, int n_out, int n_in) {
+  if (m <= 0 || n_out <= 0 || n_in <= 0) return 0;
+  const int n_sm = sm_count_cached();
+  if (!n_sm) return 0;
+  const int kgroups = ceil_div(n_in, GROUP_ELEMS);
+  const int gps = ceil_div(kgroups, skinny_splits(ceil_div(n_out, TILE_ROWS), kgroups, n_sm));
+  return (size_t)ceil_div(kgroups, gps) * m * n_out * sizeof(float);
+}
+
+extern "C" int b200q_qgemm_skinny(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue,
+                                  void* y, int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!w_packed || !x || !y || !workspace || m <= 0 || n_out <= 0 || n_in <= 0) return B200Q_ERR_BAD_ARG;
+  if (m > SK_N) return B200Q_ERR_UNSUPPORTED;
+  if (qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
+  if ((x_dtype != B200Q_F32 && x_dtype != B200Q_F16) || (y_dtype != B200Q_F32 && y_dtype != B200Q_F16)) return B200Q_ERR_BAD_ARG;
+  if (epilogue != B200Q_EPI_LINEAR && epilogue != B200Q_EPI_SILU_MUL) return B200Q_ERR_BAD_ARG;
+  if (epilogue == B200Q_EPI_SILU_MUL && (bias_f16 || residual || n_out % 16)) return B200Q_ERR_BAD_ARG;
+  if (n_in % 32) return B200Q_ERR_BAD_SHAPE;
+  if (((uintptr_t)w_packed | (uintptr_t)x | (uintptr_t)workspace) & 15) return B200Q_ERR_MISALIGNED;
+  const int n_sm = sm_count_cached();
+  if (!n_sm) return B200Q_ERR_CUDA;
+  static bool attr = false;
+  if (!attr) {
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_skinny_kernel<B200Q_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM));
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_skinny_kernel<B200Q_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM));
+    attr = true;
+  }
+  SkinnyParams p;
+  p.w = (const uint8_t*)w_packed; p.x = x; p.part = (float*)workspace;
+  p.m = m; p.n_out = n_out; p.n_in = n_in; p.kgroups = ceil_div(n_in, GROUP_ELEMS); p.n_row_tiles = ceil_div(n_out, TILE_ROWS);
+  p.x_f16 = x_dtype == B200Q_F16;
+  int splits = skinny_splits(p.n_row_tiles, p.kgroups, n_sm);
+  p.groups_per_split = ceil_div(p.kgroups, splits);
+  splits = ceil_div(p.kgroups, p.groups_per_split);              // no empty split
+  if ((size_t)splits * m * n_out * sizeof(float) > workspace_bytes) return B200Q_ERR_TOO_LARGE;
+  dim3 grid(ceil_div(p.n_row_tiles, BN / 16), splits);
+  if (qtype == B200Q_Q4_0) tc_qgemm_skinny_kernel<B200Q_Q4_0><<<grid, QGEMM_THREADS, SK_SMEM, (cudaStream_t)stream>>>(p);
+  else tc_qgemm_skinny_kernel<B200Q_Q8_0><<<grid, QGEMM_THREADS, SK_SMEM, (cudaStream_t)stream>>>(p);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  const size_t n_y = (size_t)m * (epilogue == B200Q_EPI_SILU_MUL ? n_out / 2 : n_out);
+  skinny_reduce_kernel<<<(unsigned)((n_y + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const float*)workspace, splits, m, n_out, (const __half*)bias_f16,
+                                                                                         residual, y, y_dtype == B200Q_F16, epilogue == B200Q_EPI_SILU_MUL);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -160,7 +160,7 @@ class Transformer:
     self._graphs = {}
     self._cached_tokens: list = []
     self.prefill_rows = prefill_rows if (tp is None and c.hidden_dim % 8 == 0 and c.head_dim in (16, 32, 64, 128)) else 0
-    self.prefill_chunk, self._pf, self._batch_logits = max(1, prefill_chunk), None, None
+    self.prefill_chunk, self._pf, self._batch_logits, self._skinny_ws, self._batch_graph = max(1, prefill_chunk), None, None, None, None
     self.is_moe, self._host_pos = c.num_experts > 0, 0
     if self.is_moe:
       assert tp is None and c.head_dim in (16, 32, 64, 128), "the mixture-of-experts model runs on the row path of one GPU"
@@ -243,8 +243,8 @@ class Transformer:
     qkv_rows = self.q_dim + 2 * self.kv_dim
     for p0 in range(start_pos, start_pos + n, self.prefill_chunk):
       T = min(self.prefill_chunk, start_pos + n - p0)
-      check(lib.b200q_embed_rows(self.token_embd.ptr, self.tokens.ptr + 4 * (seq * (c.max_context + 1) + p0), 1, T, c.dim, self.full_config.vocab_size,
-                                 f["x"].ptr, s))
+      check(lib.b200q_embed_rows(self.token_embd.ptr, self.tokens.ptr + 4 * (seq * (c.max_context + 1) + p0), 1, None, T, c.dim,
+                                 self.full_config.vocab_size, f["x"].ptr, s))
       for b in self.blk:
         check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.attn_norm.ptr, c.norm_eps, T, c.dim, f["xn"].ptr, F32, s))
         quant.qgemm(b.qkv.ptr, self.qtype, qkv_rows, c.dim, f["xn"], f["qkv"], T, x_dtype=F32, y_dtype=F32, bias=b.qkv_bias, stream=s)
@@ -271,31 +271,49 @@ class Transformer:
   # ---- several sequences in lock-step ----
   def decode_batch_step(self) -> None:
     """One new token for each of the `batch` sequences, all at the same position: every Linear is one GEMM over the batch rows
-    (weights streamed once per step), attention runs per sequence on its own cache, the arg-max per sequence."""
+    (weights streamed once per step), attention runs per sequence on its own cache, the arg-max per sequence.  Captured once into a
+    CUDA graph (positions and tokens live on the device) and replayed."""
+    if not self.use_graph: return self._enqueue_batch_step()
+    if self._batch_graph is None:
+      self._enqueue_batch_step()                       # allocates the buffers outside the capture (and is a real step)
+      self._batch_graph = Graph(self.stream)
+      with self._batch_graph: self._enqueue_batch_step(count=False)
+      return
+    self._batch_graph.launch()
+    self._host_pos += 1
+
+  def _enqueue_batch_step(self, count: bool = True) -> None:
     c, lib, s, f, B = self.config, _lib.load(), self.stream.ptr, self._prefill_buffers(), self.batch
     assert B <= self.prefill_chunk and not self.is_moe
     kvdt = F16 if c.kv_dtype == "float16" else F32
-    qkv_rows, pos = self.q_dim + 2 * self.kv_dim, self._host_pos
-    check(lib.b200q_embed_rows(self.token_embd.ptr, self.tokens.ptr + 4 * pos, c.max_context + 1, B, c.dim, c.vocab_size, f["x"].ptr, s))
+    qkv_rows = self.q_dim + 2 * self.kv_dim
+    head_q = not isinstance(self.output, quant.DenseWeight)
+    if B <= 32:      # the weight-streaming GEMM shape (swapped operands, split K); its partial sums go through one workspace
+      if self._skinny_ws is None:
+        shapes = [(qkv_rows, c.dim), (c.dim, self.q_dim), (2 * c.hidden_dim, c.dim), (c.dim, c.hidden_dim)] + ([(c.vocab_size, c.dim)] if head_q else [])
+        self._skinny_ws = DeviceBuffer(max(quant.qgemm_skinny_workspace_bytes(B, o, i) for o, i in shapes))
+      def gemm(w, qt, n_out, n_in, x, y, **kw): quant.qgemm_skinny(w, qt, n_out, n_in, x, y, B, self._skinny_ws, x_dtype=F32, y_dtype=F32, stream=s, **kw)
+    else:
+      def gemm(w, qt, n_out, n_in, x, y, **kw): quant.qgemm(w, qt, n_out, n_in, x, y, B, x_dtype=F32, y_dtype=F32, stream=s, **kw)
+    # the position comes from the device (sequence 0's counter; all sequences move together), so the launch sequence can be replayed as a graph
+    check(lib.b200q_embed_rows(self.token_embd.ptr, self.tokens.ptr, c.max_context + 1, self.pos.ptr, B, c.dim, c.vocab_size, f["x"].ptr, s))
     for b in self.blk:
       check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.attn_norm.ptr, c.norm_eps, B, c.dim, f["xn"].ptr, F32, s))
-      quant.qgemm(b.qkv.ptr, self.qtype, qkv_rows, c.dim, f["xn"], f["qkv"], B, x_dtype=F32, y_dtype=F32, bias=b.qkv_bias, stream=s)
-      check(lib.b200q_attn_decode_batch(f["qkv"].ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, pos, B, c.n_heads, c.n_kv_heads, c.head_dim,
+      gemm(b.qkv.ptr, self.qtype, qkv_rows, c.dim, f["xn"], f["qkv"], bias=b.qkv_bias)
+      check(lib.b200q_attn_decode_batch(f["qkv"].ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, 0, self.pos.ptr, B, c.n_heads, c.n_kv_heads, c.head_dim,
                                         c.rope_dim, c.max_context, f["q16"].ptr, f["att"].ptr, F32, s))
-      quant.qgemm(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, f["att"], f["x"], B, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s)
+      gemm(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, f["att"], f["x"], residual=f["x"])
       check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.ffn_norm.ptr, c.norm_eps, B, c.dim, f["xn"].ptr, F32, s))
-      quant.qgemm(b.gate_up.buf.ptr, self.qtype, 2 * c.hidden_dim, c.dim, f["xn"], f["act"], B, x_dtype=F32, y_dtype=F32, epilogue=EPI_SILU_MUL, stream=s)
-      quant.qgemm(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, f["act"], f["x"], B, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s)
+      gemm(b.gate_up.buf.ptr, self.qtype, 2 * c.hidden_dim, c.dim, f["xn"], f["act"], epilogue=EPI_SILU_MUL)
+      gemm(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, f["act"], f["x"], residual=f["x"])
     check(lib.b200q_rmsnorm_rows(f["x"].ptr, self.output_norm.ptr, c.norm_eps, B, c.dim, f["xn"].ptr, F32, s))
     if self._batch_logits is None: self._batch_logits = DeviceBuffer.empty((B, c.vocab_size), np.float32)
-    if isinstance(self.output, quant.DenseWeight):
-      quant.gemv_dense(self.output.buf, self.output.dtype, c.vocab_size, c.dim, f["xn"], self._batch_logits, m=B, stream=s)
-    else:
-      quant.qgemm(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, f["xn"], self._batch_logits, B, x_dtype=F32, y_dtype=F32, stream=s)
+    if head_q: gemm(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, f["xn"], self._batch_logits)
+    else: quant.gemv_dense(self.output.buf, self.output.dtype, c.vocab_size, c.dim, f["xn"], self._batch_logits, m=B, stream=s)
     for i in range(B):
       check(lib.b200q_argmax_advance(self._batch_logits.ptr + 4 * i * c.vocab_size, c.vocab_size, self.tokens.ptr + 4 * i * (c.max_context + 1),
                                      self.pos.ptr + 4 * i, self.argmax_scratch.ptr, 0, s))
-    self._host_pos += 1
+    if count: self._host_pos += 1
 
   def generate_batch(self, prompts: list):
     """Greedy generation for `batch` prompts of equal length; yields the list of the sequences' next tokens per step."""

@@ -90,6 +90,17 @@ def qgemm(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int, x_dtype=F
                                 stream_ptr(stream)))
 
 
+def qgemm_skinny_workspace_bytes(m: int, n_out: int, n_in: int) -> int:
+  return int(_lib.load().b200q_qgemm_skinny_workspace_bytes(m, n_out, n_in))
+
+
+def qgemm_skinny(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int, workspace: DeviceBuffer, x_dtype=F32, y_dtype=F32, bias=None, residual=None,
+                 epilogue: int = EPI_LINEAR, stream=None) -> None:
+  """The same Linear for at most 32 activation rows (batched decode): swapped operands, split K, partial sums through `workspace`."""
+  check(_lib.load().b200q_qgemm_skinny(qtype, w_ptr, ptr_of(x), x_dtype, ptr_of(bias), ptr_of(residual), epilogue, ptr_of(y), y_dtype, m, n_out, n_in,
+                                       workspace.ptr, workspace.nbytes, stream_ptr(stream)))
+
+
 GEMM_MIN_ROWS = 4   # from this many activation rows on, QuantLinear uses the tensor-core GEMM instead of one GEMV per row
 
 
