@@ -316,7 +316,7 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_kernel(const QGemmPara
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&bar)) : "memory");
     }
     if (kg + 1 < p.kgroups) load_regs(kg + 1);
-    if (!wait_bar(s32(&bar), phase)) { ok = false; break; }
+    if (!__syncthreads_and(wait_bar(s32(&bar), phase))) { ok = false; break; }      // all threads leave together if a wait ran out
     phase ^= 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   }
@@ -380,6 +380,8 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_kernel(const QGemmPara
 constexpr int SK_N = 32;                                        // activation rows per MMA (N)
 constexpr int SK_STAGE = 2 * (BN + SK_N) * QBK * 2;             // weights 128 rows + activations 32 rows, hi and lo: 80 KB
 constexpr int SK_SMEM = 2 * SK_STAGE;
+__host__ __device__ constexpr int sk_raw_stages(int qtype) { return qtype == B200Q_Q4_0 ? 6 : 3; }   // K groups of packed tiles in flight: 54 KB / 51 KB
+__host__ __device__ constexpr int sk_smem_total(int qtype) { return SK_SMEM + sk_raw_stages(qtype) * (BN / 16) * tile_bytes(qtype); }
 
 struct SkinnyParams {
   const uint8_t* w; const void* x; float* part;
@@ -389,9 +391,10 @@ struct SkinnyParams {
 template <int QT>
 __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_skinny_kernel(const SkinnyParams p) {
   extern __shared__ __align__(128) unsigned char ssm[];
-  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ __align__(8) uint64_t bars[2], raw_full[8];
   __shared__ uint32_t tmem_base;
-  constexpr int TB = tile_bytes(QT);
+  constexpr int TB = tile_bytes(QT), RAW_STAGES = sk_raw_stages(QT), RAW_STAGE = (BN / 16) * TB;
+  unsigned char* raw = ssm + SK_SMEM;                            // ring of packed weight tiles as they sit in HBM, filled by bulk copies
   const int tid = threadIdx.x, warp = tid >> 5;
   const int rt0 = blockIdx.x * (BN / 16), split = blockIdx.y;
   const int kg0 = split * p.groups_per_split, kg1 = min(p.kgroups, kg0 + p.groups_per_split);
@@ -402,6 +405,7 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_skinny_kernel(const Sk
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bars[0])));
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bars[1])));
+    for (int i = 0; i < RAW_STAGES; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&raw_full[i])));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int i = tid; i < SK_SMEM / 16; i += QGEMM_THREADS) reinterpret_cast<uint4*>(ssm)[i] = make_uint4(0, 0, 0, 0);   // rows past m / n_out stay zero
@@ -427,15 +431,22 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_skinny_kernel(const Sk
         xa0 = *reinterpret_cast<const float4*>(src); xa1 = *reinterpret_cast<const float4*>(src + 4);
       }
     }
-    if (w_on) {
-      const uint8_t* tile = p.w + ((size_t)(rt0 + w_tl) * p.kgroups + kg) * TB;
-      const unsigned short dbits = reinterpret_cast<const unsigned short*>(tile + (TB - 128))[(2 * w_g + (w_t >> 1)) * 4 + w_h * 2 + (w_t & 1)];
-      wd2 = (uint32_t)dbits | ((uint32_t)dbits << 16);
-      if (QT == B200Q_Q4_0) wq0 = ldg_stream(reinterpret_cast<const uint4*>(tile) + w_h * 32 + w_l);
-      else { wq0 = ldg_stream(reinterpret_cast<const uint4*>(tile) + (2 * w_h) * 32 + w_l); wq1 = ldg_stream(reinterpret_cast<const uint4*>(tile) + (2 * w_h + 1) * 32 + w_l); }
-    }
+  };
+  // The weight stream: thread 0 keeps RAW_STAGES K groups of packed tiles in flight (one bulk copy per row tile, completion counted in
+  // bytes on the slot's mbarrier), which is what hides the HBM latency; a slot is refilled right after the block-wide barrier that
+  // follows its last read.
+  const int n_tiles_here = min(BN / 16, p.n_row_tiles - rt0);
+  auto issue_raw = [&](int it) {
+    const int slot = it % RAW_STAGES, kg = kg0 + it;
+    const uint32_t bar = s32(&raw_full[slot]);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(n_tiles_here * TB)) : "memory");
+    for (int tl = 0; tl < n_tiles_here; tl++)
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(s32(raw + slot * RAW_STAGE + tl * TB)), "l"(p.w + ((size_t)(rt0 + tl) * p.kgroups + kg) * TB), "r"((uint32_t)TB), "r"(bar) : "memory");
   };
   bool ok = true;
+  const int n_it = kg1 - kg0;
+  if (tid == 0) for (int it = 0; it < RAW_STAGES && it < n_it; it++) issue_raw(it);
   if (kg0 < kg1) load_regs(kg0);
   for (int kg = kg0, it = 0; kg < kg1; kg++, it++) {
     const int st = it & 1;
@@ -443,9 +454,18 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_skinny_kernel(const Sk
     unsigned char* sW2 = sW + BN * QBK * 2;                     // weights lo
     unsigned char* sX = sW2 + BN * QBK * 2;                     // activations hi
     unsigned char* sX2 = sX + SK_N * QBK * 2;                   // activations lo
-    if (it >= 2 && !wait_bar(s32(&bars[st]), ((it >> 1) - 1) & 1)) { ok = false; break; }     // the MMAs that read this stage are done
+    // a wait that ran out makes the whole CTA leave at the block-wide barrier below (never a thread on its own)
+    bool good = it < 2 || wait_bar(s32(&bars[st]), ((it >> 1) - 1) & 1);                          // the MMAs that read this stage are done
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (a_r < p.m) {
+    good = good && wait_bar(s32(&raw_full[it % RAW_STAGES]), (it / RAW_STAGES) & 1);                // this group's packed tiles have landed
+    if (w_on && good) {
+      const unsigned char* tile = raw + (it % RAW_STAGES) * RAW_STAGE + w_tl * TB;
+      const unsigned short dbits = reinterpret_cast<const unsigned short*>(tile + (TB - 128))[(2 * w_g + (w_t >> 1)) * 4 + w_h * 2 + (w_t & 1)];
+      wd2 = (uint32_t)dbits | ((uint32_t)dbits << 16);
+      if (QT == B200Q_Q4_0) wq0 = reinterpret_cast<const uint4*>(tile)[w_h * 32 + w_l];
+      else { wq0 = reinterpret_cast<const uint4*>(tile)[(2 * w_h) * 32 + w_l]; wq1 = reinterpret_cast<const uint4*>(tile)[(2 * w_h + 1) * 32 + w_l]; }
+    }
+    if (a_r < p.m && good) {
       float f[8];
       if (p.x_f16) {
         const __half2* h = reinterpret_cast<const __half2*>(&xa0);
@@ -461,7 +481,7 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_skinny_kernel(const Sk
         *reinterpret_cast<uint4*>(sX2 + tile_off(a_r, a_kc, SK_N)) = *reinterpret_cast<const uint4*>(lo2);
       }
     }
-    if (w_on) {
+    if (w_on && good) {
       const int r = w_tl * 16 + w_h * 8 + w_g, t = w_t;
       uint4 lo[4];
       if (QT == B200Q_Q4_0) {
@@ -481,7 +501,12 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_skinny_kernel(const Sk
       }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
+    if (!__syncthreads_and(good)) {
+      ok = false;
+      if (tid == 0)        // bulk copies still in flight must land before the CTA gives up its shared memory
+        for (int j = it; j < n_it && j < it + RAW_STAGES; j++) wait_bar(s32(&raw_full[j % RAW_STAGES]), (j / RAW_STAGES) & 1);
+      break;
+    }
     if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -499,12 +524,15 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_skinny_kernel(const Sk
         }
       }
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&bars[st])) : "memory");
+      if (it + RAW_STAGES < n_it) issue_raw(it + RAW_STAGES);     // every thread has read this slot (the barrier above)
     }
     if (kg + 1 < kg1) load_regs(kg + 1);
   }
   // the last commit covers every MMA issued before it
-  const int n_it = kg1 - kg0;
-  if (ok && n_it > 0) ok = wait_bar(s32(&bars[(n_it - 1) & 1]), ((n_it - 1) >> 1) & 1);
+  if (n_it > 0) {     // also on the way out after a failed wait: MMAs that were issued must be done before tensor memory is freed
+    const bool done = wait_bar(s32(&bars[(n_it - 1) & 1]), ((n_it - 1) >> 1) & 1);
+    ok = ok && done;
+  }
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   if (ok && warp < 4) {
     // accumulator row = weight row (tensor-memory lane), column = activation row
@@ -644,8 +672,8 @@ extern "C" int b200q_qgemm_skinny(int qtype, const void* w_packed, const void* x
   if (!n_sm) return B200Q_ERR_CUDA;
   static bool attr = false;
   if (!attr) {
-    B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_skinny_kernel<B200Q_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM));
-    B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_skinny_kernel<B200Q_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM));
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_skinny_kernel<B200Q_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, sk_smem_total(B200Q_Q4_0)));
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_skinny_kernel<B200Q_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, sk_smem_total(B200Q_Q8_0)));
     attr = true;
   }
   SkinnyParams p;
@@ -657,8 +685,8 @@ extern "C" int b200q_qgemm_skinny(int qtype, const void* w_packed, const void* x
   splits = ceil_div(p.kgroups, p.groups_per_split);              // no empty split
   if ((size_t)splits * m * n_out * sizeof(float) > workspace_bytes) return B200Q_ERR_TOO_LARGE;
   dim3 grid(ceil_div(p.n_row_tiles, BN / 16), splits);
-  if (qtype == B200Q_Q4_0) tc_qgemm_skinny_kernel<B200Q_Q4_0><<<grid, QGEMM_THREADS, SK_SMEM, (cudaStream_t)stream>>>(p);
-  else tc_qgemm_skinny_kernel<B200Q_Q8_0><<<grid, QGEMM_THREADS, SK_SMEM, (cudaStream_t)stream>>>(p);
+  if (qtype == B200Q_Q4_0) tc_qgemm_skinny_kernel<B200Q_Q4_0><<<grid, QGEMM_THREADS, sk_smem_total(B200Q_Q4_0), (cudaStream_t)stream>>>(p);
+  else tc_qgemm_skinny_kernel<B200Q_Q8_0><<<grid, QGEMM_THREADS, sk_smem_total(B200Q_Q8_0), (cudaStream_t)stream>>>(p);
   B200Q_CHECK_CUDA(cudaGetLastError());
   const size_t n_y = (size_t)m * (epilogue == B200Q_EPI_SILU_MUL ? n_out / 2 : n_out);
   skinny_reduce_kernel<<<(unsigned)((n_y + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const float*)workspace, splits, m, n_out, (const __half*)bias_f16,
