@@ -3,7 +3,8 @@ missing or a call fails, the Python wrappers raise."""
 import ctypes, pathlib
 from ctypes import c_int, c_int32, c_int64, c_size_t, c_float, c_void_p, c_char_p, POINTER, Structure
 
-LIB_PATH = pathlib.Path(__file__).resolve().parent / "libb200q.so"
+import os
+LIB_PATH = pathlib.Path(os.environ.get("B200Q_LIB") or pathlib.Path(__file__).resolve().parent / "libb200q.so")   # B200Q_LIB: another build of the library
 
 Q4_0, Q8_0, Q6_K = 2, 8, 14
 F32, F16, BF16 = 0, 1, 2

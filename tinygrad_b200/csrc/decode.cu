@@ -51,7 +51,10 @@ __global__ void advance_kernel(int32_t* pos) {
 //   uint  counter[n_kv_heads]                       (arrival count, reset by the last CTA)
 constexpr int MAX_HD = 128;
 constexpr int MAX_REP = 8;
-constexpr int ATTN_CHUNK = 64;    // positions per CTA
+#ifndef B200Q_ATTN_CHUNK
+#define B200Q_ATTN_CHUNK 64
+#endif
+constexpr int ATTN_CHUNK = B200Q_ATTN_CHUNK;    // positions per CTA
 
 template <typename KV> struct KvIO;
 template <> struct KvIO<__half> {

@@ -510,13 +510,16 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_skinny_kernel(const Sk
     if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
+      // descriptors of K step kk = the stage's base descriptor + the step's byte offset >> 4 in the address field
+      const uint64_t dw0 = make_desc(s32(sW), BN * 16, 128), dx0 = make_desc(s32(sX), SK_N * 16, 128);
+      const uint64_t dwl0 = make_desc(s32(sW2), BN * 16, 128), dxl0 = make_desc(s32(sX2), SK_N * 16, 128);
       for (int kk = 0; kk < QBK / 16; kk++) {
-        const uint64_t dw = make_desc(s32(sW) + kk * 2 * (BN * 16), BN * 16, 128), dx = make_desc(s32(sX) + kk * 2 * (SK_N * 16), SK_N * 16, 128);
+        const uint64_t dw = dw0 + (uint64_t)((kk * 2 * (BN * 16)) >> 4), dx = dx0 + (uint64_t)((kk * 2 * (SK_N * 16)) >> 4);
         const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
         asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                      ::"r"(taddr), "l"(dw), "l"(dx), "r"(idesc), "r"(acc) : "memory");
         if (!p.x_f16) {
-          const uint64_t dw2 = make_desc(s32(sW2) + kk * 2 * (BN * 16), BN * 16, 128), dx2 = make_desc(s32(sX2) + kk * 2 * (SK_N * 16), SK_N * 16, 128);
+          const uint64_t dw2 = dwl0 + (uint64_t)((kk * 2 * (BN * 16)) >> 4), dx2 = dxl0 + (uint64_t)((kk * 2 * (SK_N * 16)) >> 4);
           asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                        ::"r"(taddr), "l"(dw), "l"(dx2), "r"(idesc), "r"(1u) : "memory");
           asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
