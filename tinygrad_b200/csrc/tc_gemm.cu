@@ -316,7 +316,11 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_kernel(const QGemmPara
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&bar)) : "memory");
     }
     if (kg + 1 < p.kgroups) load_regs(kg + 1);
-    if (!__syncthreads_and(wait_bar(s32(&bar), phase))) { ok = false; break; }      // all threads leave together if a wait ran out
+    // one thread polls the MMA-completion barrier, the others sleep in the block barrier (512 pollers cost issue slots); all
+    // threads leave together if the wait ran out
+    bool mma_done = true;
+    if (tid == 0) mma_done = wait_bar(s32(&bar), phase);
+    if (!__syncthreads_and(mma_done)) { ok = false; break; }
     phase ^= 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   }
