@@ -211,7 +211,9 @@ def run_moe_probe(args):
     "zero_fill": lambda: (ws["a_q"].zero_(st), ws["a_e8"].zero_(st)),
     "dispatch_quantize": lambda: lib.b200q_quantize_mxfp8(x.ptr, BF16, T, D, r.dest_row.ptr, k, ws["a_q"].ptr, ws["a_e8"].ptr, st.ptr),
     "gate_up_gemm": lambda: lib.b200q_grouped_mxfp8_gemm(ws["a_q"].ptr, ws["a_e8"].ptr, m.gu_q.ptr, m.gu_e8.ptr, r.off.ptr, E, r.m_l, 2 * F, D, ws["h"].ptr, st.ptr),
-    "swiglu_quantize": lambda: lib.b200q_swiglu_quantize_mxfp8(ws["h"].ptr, r.m_l, r.off.ptr + 4 * E, F, ws["act_q"].ptr, ws["act_e8"].ptr, st.ptr),
+    "gate_up_gemm_swiglu_fused": lambda: lib.b200q_grouped_mxfp8_gemm_swiglu(ws["a_q"].ptr, ws["a_e8"].ptr, m.gu_q.ptr, m.gu_e8.ptr, r.off.ptr, E, r.m_l, 2 * F, D,
+                                                                             ws["act_q"].ptr, ws["act_e8"].ptr, st.ptr),
+    "swiglu_quantize_unfused": lambda: lib.b200q_swiglu_quantize_mxfp8(ws["h"].ptr, r.m_l, r.off.ptr + 4 * E, F, ws["act_q"].ptr, ws["act_e8"].ptr, st.ptr),
     "down_gemm": lambda: lib.b200q_grouped_mxfp8_gemm(ws["act_q"].ptr, ws["act_e8"].ptr, m.dn_q.ptr, m.dn_e8.ptr, r.off.ptr, E, r.m_l, D, F, ws["y"].ptr, st.ptr),
     "combine": lambda: lib.b200q_moe_combine(ws["y"].ptr, r.dest_row.ptr, r.weights.ptr, T, k, D, ws["out"].ptr, st.ptr),
   }

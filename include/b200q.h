@@ -308,6 +308,11 @@ int b200q_moe_combine(const void* y_bf16, const int32_t* dest_row, const float* 
  * (the reference's own constraint, moe_gemm.py:120).  Runs on tcgen05 block-scaled MMAs (kind::mxf8f6f4.block_scale).
  * b200q_mx_status_read_clear: like b200q_status_read_clear for this kernel's bounded waits. */
 int b200q_mx_status_read_clear(int* status);
+/* The gate/up expert GEMM with the activation fused into its epilogue: B holds, per 256 rows, 128 gate rows followed by the 128
+ * matching up rows (n = 2 f); instead of C the kernel writes act = silu(gate) * up already quantised, act_q [m_total, f] E4M3 +
+ * act_e8 [m_total, f/32] -- the same values as b200q_grouped_mxfp8_gemm followed by b200q_swiglu_quantize_mxfp8 on [gate | up]. */
+int b200q_grouped_mxfp8_gemm_swiglu(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts,
+                                    int m_total, int n, int k, void* act_q, void* act_e8, void* stream);
 int b200q_grouped_mxfp8_gemm(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts,
                              int m_total, int n, int k, void* c_bf16, void* stream);
 

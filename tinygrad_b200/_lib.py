@@ -96,6 +96,8 @@ SIGNATURES = {
   "b200q_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
   "b200q_mx_status_read_clear": (c_int, [POINTER(c_int)]),
   "b200q_grouped_mxfp8_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+  "b200q_grouped_mxfp8_gemm_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                             c_void_p]),
 }
 
 _lib = None

@@ -17,7 +17,7 @@ def nvcc_path() -> str:
 
 def build_lib(force: bool = False, verbose: bool = False) -> pathlib.Path:
   srcs = [CSRC / s for s in SOURCES]
-  deps = srcs + [CSRC / "common.cuh", CSRC / "actquant.cuh", PKG.parent / "include" / "b200q.h"]
+  deps = srcs + [CSRC / "common.cuh", CSRC / "actquant.cuh", CSRC / "mxq.cuh", PKG.parent / "include" / "b200q.h"]
   if not force and LIB.exists() and all(LIB.stat().st_mtime >= d.stat().st_mtime for d in deps): return LIB
   cmd = [nvcc_path(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", str(LIB), *map(str, srcs)]
   r = subprocess.run(cmd, capture_output=True, text=True)

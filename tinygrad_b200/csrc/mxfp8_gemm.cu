@@ -21,6 +21,7 @@
 // the kernel (tensor pipe 39 % active, L2 43 %, HBM 28 % under ncu).
 // Every mbarrier wait is bounded; a wait that runs out raises a status word and makes every role leave.
 #include "common.cuh"
+#include "mxq.cuh"
 #include <cuda_bf16.h>
 #include <stdlib.h>
 
@@ -87,7 +88,8 @@ __device__ __forceinline__ void arrive(uint32_t bar) { asm volatile("mbarrier.ar
 __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint8_t* __restrict__ a_q, const uint8_t* __restrict__ a_e8,
                                                                       const uint8_t* __restrict__ b_q, const uint8_t* __restrict__ b_e8,
                                                                       const int32_t* __restrict__ off, int n_experts, int m_total, int n, int k,
-                                                                      __nv_bfloat16* __restrict__ c) {
+                                                                      __nv_bfloat16* __restrict__ c, uint8_t* __restrict__ act_q,
+                                                                      uint8_t* __restrict__ act_e8) {
   extern __shared__ unsigned char sm_raw[];
   __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_acc_full, bar_acc_empty, bar_drain;
   __shared__ uint32_t tmem_base;
@@ -206,6 +208,51 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
       const int sub = warp & 3, cbase = warp < EPI_WARPS ? 0 : BN / 2;     // sub-partition = warp % 4; two warps split its 256 columns
+      if (act_q) {
+        // Fused activation between the expert GEMMs: the B rows of this tile are 128 gate rows followed by the 128 matching up rows
+        // (the caller interleaves them so), so accumulator columns c and 128 + c belong together.  A thread holds 32 consecutive
+        // outputs of its row = one MX block: bf16-round gate and up (what the unfused path stores), silu(gate) * up in fp32,
+        // bf16-round, block exponent from the amax, E4M3 codes -- the arithmetic of swiglu_quant_kernel, with no trip through HBM.
+        const int f = n >> 1, c_lo = warp < EPI_WARPS ? 0 : 64;
+        const size_t row = (size_t)(m0 + sub * 32 + lane);
+#pragma unroll 1
+        for (int c0 = c_lo; c0 < c_lo + 64; c0 += 32) {
+          uint32_t vg[32], vu[32];
+          const uint32_t ta = taddr + ((uint32_t)(sub * 32) << 16);
+          asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                       : "=r"(vg[0]), "=r"(vg[1]), "=r"(vg[2]), "=r"(vg[3]), "=r"(vg[4]), "=r"(vg[5]), "=r"(vg[6]), "=r"(vg[7]), "=r"(vg[8]), "=r"(vg[9]), "=r"(vg[10]), "=r"(vg[11]), "=r"(vg[12]), "=r"(vg[13]), "=r"(vg[14]), "=r"(vg[15]), "=r"(vg[16]), "=r"(vg[17]), "=r"(vg[18]), "=r"(vg[19]), "=r"(vg[20]), "=r"(vg[21]), "=r"(vg[22]), "=r"(vg[23]), "=r"(vg[24]), "=r"(vg[25]), "=r"(vg[26]), "=r"(vg[27]), "=r"(vg[28]), "=r"(vg[29]), "=r"(vg[30]), "=r"(vg[31])
+                       : "r"(ta + c0));
+          asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                       : "=r"(vu[0]), "=r"(vu[1]), "=r"(vu[2]), "=r"(vu[3]), "=r"(vu[4]), "=r"(vu[5]), "=r"(vu[6]), "=r"(vu[7]), "=r"(vu[8]), "=r"(vu[9]), "=r"(vu[10]), "=r"(vu[11]), "=r"(vu[12]), "=r"(vu[13]), "=r"(vu[14]), "=r"(vu[15]), "=r"(vu[16]), "=r"(vu[17]), "=r"(vu[18]), "=r"(vu[19]), "=r"(vu[20]), "=r"(vu[21]), "=r"(vu[22]), "=r"(vu[23]), "=r"(vu[24]), "=r"(vu[25]), "=r"(vu[26]), "=r"(vu[27]), "=r"(vu[28]), "=r"(vu[29]), "=r"(vu[30]), "=r"(vu[31])
+                       : "r"(ta + BN / 2 + c0));
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (c0 + 32 == c_lo + 64) {      // this warp's part of the accumulator is in registers
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            arrive(s32(&bar_acc_empty));
+          }
+          float v[32];
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vg[j]))), u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vu[j])));
+            v[j] = __bfloat162float(__float2bfloat16_rn((g / (1.f + expf(-g))) * u));
+            amax = fmaxf(amax, fabsf(v[j]));
+          }
+          const uint8_t e = mx_scale_exponent(amax);
+          uint2 pk[4];
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            const float v8[8] = {v[8 * q], v[8 * q + 1], v[8 * q + 2], v[8 * q + 3], v[8 * q + 4], v[8 * q + 5], v[8 * q + 6], v[8 * q + 7]};
+            pk[q] = mx_quant8(v8, e);
+          }
+          const int col = (n0 >> 1) + c0;                              // column of the activation matrix [m, f]
+          uint4* dst = reinterpret_cast<uint4*>(act_q + row * f + col);
+          dst[0] = make_uint4(pk[0].x, pk[0].y, pk[1].x, pk[1].y);
+          dst[1] = make_uint4(pk[2].x, pk[2].y, pk[3].x, pk[3].y);
+          act_e8[row * (f >> 5) + (col >> 5)] = e;
+        }
+        continue;
+      }
       __nv_bfloat16* out_row = c + (size_t)(m0 + sub * 32 + lane) * n + n0;
 #pragma unroll 1
       for (int j0 = cbase; j0 < cbase + BN / 2; j0 += 32) {
@@ -447,9 +494,10 @@ extern "C" int b200q_mx_status_read_clear(int* status) {
   return B200Q_OK;
 }
 
-extern "C" int b200q_grouped_mxfp8_gemm(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts,
-                                        int m_total, int n, int k, void* c_bf16, void* stream) {
-  if (!a_q || !a_e8 || !b_q || !b_e8 || !off || !c_bf16 || n_experts <= 0 || m_total <= 0 || n <= 0 || k <= 0) return B200Q_ERR_BAD_ARG;
+static int grouped_launch(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts, int m_total, int n, int k,
+                          void* c_bf16, void* act_q, void* act_e8, void* stream) {
+  if (!a_q || !a_e8 || !b_q || !b_e8 || !off || (!c_bf16 && !act_q) || n_experts <= 0 || m_total <= 0 || n <= 0 || k <= 0) return B200Q_ERR_BAD_ARG;
+  if (act_q && (!act_e8 || (((uintptr_t)act_q) & 15))) return B200Q_ERR_BAD_ARG;
   if (m_total % 256 || n % BN || k % BK) return B200Q_ERR_BAD_SHAPE;       // the reference asks M % 256 == N % 256 == K % 128 == 0 (moe_gemm.py:120)
   if (n_experts > MAX_EXPERTS) return B200Q_ERR_UNSUPPORTED;
   if (((uintptr_t)a_q | (uintptr_t)b_q | (uintptr_t)c_bf16) & 15 || ((uintptr_t)a_e8 | (uintptr_t)b_e8) & 3) return B200Q_ERR_MISALIGNED;
@@ -473,7 +521,7 @@ extern "C" int b200q_grouped_mxfp8_gemm(const void* a_q, const void* a_e8, const
     if (e) use_pairs = atoi(e);
     n_sm = sms;
   }
-  if (use_pairs && n_clusters > 0) {
+  if (use_pairs && n_clusters > 0 && !act_q) {
     const long long ptiles = (long long)(m_total / 256) * (n / BN);
     const int pairs = (int)(ptiles < n_clusters ? ptiles : n_clusters);
     grouped_mxfp8_pair_kernel<<<2 * pairs, THREADS, P_SMEM_BYTES, (cudaStream_t)stream>>>((const uint8_t*)a_q, (const uint8_t*)a_e8, (const uint8_t*)b_q,
@@ -485,7 +533,19 @@ extern "C" int b200q_grouped_mxfp8_gemm(const void* a_q, const void* a_e8, const
   const long long tiles = (long long)(m_total / BM) * (n / BN);
   const int grid = (int)(tiles < n_sm ? tiles : n_sm);
   grouped_mxfp8_tc_kernel<<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>((const uint8_t*)a_q, (const uint8_t*)a_e8, (const uint8_t*)b_q, (const uint8_t*)b_e8, off,
-                                                            n_experts, m_total, n, k, (__nv_bfloat16*)c_bf16);
+                                                            n_experts, m_total, n, k, (__nv_bfloat16*)c_bf16, (uint8_t*)act_q, (uint8_t*)act_e8);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
+}
+
+extern "C" int b200q_grouped_mxfp8_gemm(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts,
+                                        int m_total, int n, int k, void* c_bf16, void* stream) {
+  if (!c_bf16) return B200Q_ERR_BAD_ARG;
+  return grouped_launch(a_q, a_e8, b_q, b_e8, off, n_experts, m_total, n, k, c_bf16, nullptr, nullptr, stream);
+}
+
+extern "C" int b200q_grouped_mxfp8_gemm_swiglu(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts,
+                                               int m_total, int n, int k, void* act_q, void* act_e8, void* stream) {
+  if (!act_q || !act_e8) return B200Q_ERR_BAD_ARG;
+  return grouped_launch(a_q, a_e8, b_q, b_e8, off, n_experts, m_total, n, k, nullptr, act_q, act_e8, stream);
 }

@@ -132,9 +132,13 @@ class ExpertParallelMoE:
     check(lib.b200q_permute_rows(self.recv_e8.data_ptr(), place.data_ptr(), n_recv, self.D // 32, self.a_e8.data_ptr(), 0, None))
     m, loc = self.local, plan["m_local"]
     if loc:
-      check(lib.b200q_grouped_mxfp8_gemm(self.a_q.data_ptr(), self.a_e8.data_ptr(), m.gu_q.ptr, m.gu_e8.ptr, off_l.data_ptr(), self.E_l, loc, 2 * self.F,
-                                         self.D, self.h.data_ptr(), None))
-      check(lib.b200q_swiglu_quantize_mxfp8(self.h.data_ptr(), loc, None, self.F, self.act_q.data_ptr(), self.act_e8.data_ptr(), None))
+      if m.fused:
+        check(lib.b200q_grouped_mxfp8_gemm_swiglu(self.a_q.data_ptr(), self.a_e8.data_ptr(), m.gu_q.ptr, m.gu_e8.ptr, off_l.data_ptr(), self.E_l, loc,
+                                                  2 * self.F, self.D, self.act_q.data_ptr(), self.act_e8.data_ptr(), None))
+      else:
+        check(lib.b200q_grouped_mxfp8_gemm(self.a_q.data_ptr(), self.a_e8.data_ptr(), m.gu_q.ptr, m.gu_e8.ptr, off_l.data_ptr(), self.E_l, loc, 2 * self.F,
+                                           self.D, self.h.data_ptr(), None))
+        check(lib.b200q_swiglu_quantize_mxfp8(self.h.data_ptr(), loc, None, self.F, self.act_q.data_ptr(), self.act_e8.data_ptr(), None))
       check(lib.b200q_grouped_mxfp8_gemm(self.act_q.data_ptr(), self.act_e8.data_ptr(), m.dn_q.ptr, m.dn_e8.ptr, off_l.data_ptr(), self.E_l, loc, self.D,
                                          self.F, self.y.data_ptr(), None))
     # 5. results back in arrival order, combine on the rank that owns the tokens

@@ -53,7 +53,14 @@ class MxMoE:
   def __init__(self, w_gate: np.ndarray, w_up: np.ndarray, w_down: np.ndarray, k: int, mode: int = ROUTE_SOFTMAX_TOPK):
     self.E, self.F, self.D = w_gate.shape
     self.k, self.mode = k, mode
-    gu = np.concatenate([w_gate, w_up], axis=1).astype(np.float32)          # (E, 2F, D): one GEMM yields [gate | up]
+    # one GEMM yields gate and up.  F % 128 == 0: rows interleaved 128 gate / 128 up per 256-row tile, so that the GEMM's epilogue
+    # can apply silu(gate) * up and requantise (b200q_grouped_mxfp8_gemm_swiglu); else [gate | up] halves and a separate kernel
+    self.fused = self.F % 128 == 0
+    if self.fused:
+      gu = np.stack([w_gate.reshape(self.E, self.F // 128, 128, self.D), w_up.reshape(self.E, self.F // 128, 128, self.D)], axis=2)
+      gu = np.ascontiguousarray(gu.reshape(self.E, 2 * self.F, self.D), dtype=np.float32)
+    else:
+      gu = np.concatenate([w_gate, w_up], axis=1).astype(np.float32)
     self.gu_q, self.gu_e8 = quantize_mxfp8(DeviceBuffer.from_numpy(gu), self.E * 2 * self.F, self.D, F32)
     self.dn_q, self.dn_e8 = quantize_mxfp8(DeviceBuffer.from_numpy(w_down.astype(np.float32)), self.E * self.D, self.F, F32)
     self._wss, self._ws = {}, None
@@ -75,9 +82,13 @@ class MxMoE:
     r = w["r"].run(logits, stream)
     w["a_q"].zero_(stream); w["a_e8"].zero_(stream)                        # rows nobody is routed to stay zero (dispatch zero-fills)
     check(lib.b200q_quantize_mxfp8(x_bf16.ptr, BF16, n_tokens, self.D, r.dest_row.ptr, self.k, w["a_q"].ptr, w["a_e8"].ptr, s))
-    check(lib.b200q_grouped_mxfp8_gemm(w["a_q"].ptr, w["a_e8"].ptr, self.gu_q.ptr, self.gu_e8.ptr, r.off.ptr, self.E, r.m_l, 2 * self.F, self.D,
-                                       w["h"].ptr, s))
-    check(lib.b200q_swiglu_quantize_mxfp8(w["h"].ptr, r.m_l, r.off.ptr + 4 * self.E, self.F, w["act_q"].ptr, w["act_e8"].ptr, s))
+    if self.fused:
+      check(lib.b200q_grouped_mxfp8_gemm_swiglu(w["a_q"].ptr, w["a_e8"].ptr, self.gu_q.ptr, self.gu_e8.ptr, r.off.ptr, self.E, r.m_l, 2 * self.F, self.D,
+                                                w["act_q"].ptr, w["act_e8"].ptr, s))
+    else:
+      check(lib.b200q_grouped_mxfp8_gemm(w["a_q"].ptr, w["a_e8"].ptr, self.gu_q.ptr, self.gu_e8.ptr, r.off.ptr, self.E, r.m_l, 2 * self.F, self.D,
+                                         w["h"].ptr, s))
+      check(lib.b200q_swiglu_quantize_mxfp8(w["h"].ptr, r.m_l, r.off.ptr + 4 * self.E, self.F, w["act_q"].ptr, w["act_e8"].ptr, s))
     check(lib.b200q_grouped_mxfp8_gemm(w["act_q"].ptr, w["act_e8"].ptr, self.dn_q.ptr, self.dn_e8.ptr, r.off.ptr, self.E, r.m_l, self.D, self.F,
                                        w["y"].ptr, s))
     check(lib.b200q_moe_combine(w["y"].ptr, r.dest_row.ptr, r.weights.ptr, n_tokens, self.k, self.D, w["out"].ptr, s))
