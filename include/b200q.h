@@ -46,7 +46,8 @@ extern "C" {
 
 const char* b200q_strerror(int code);
 /* Device-side status word: 0 = fine, 1 = a bounded wait inside a kernel ran out (the kernel then skipped its
- * remaining work instead of spinning; its output is invalid).  Reads and clears it.  Synchronises the device. */
+ * remaining work instead of spinning; its output is invalid), 2 = a decode-step kernel was handed a position outside
+ * [0, max_context) and skipped its cache / token-table access.  Reads and clears it.  Synchronises the device. */
 int b200q_status_read_clear(int* status);
 const char* b200q_last_cuda_error(void);
 int b200q_version(void);
@@ -151,29 +152,28 @@ typedef struct b200q_gemv_args {
                                `y` may then be NULL if nobody needs the fp32 values */
   const void* xq_out_norm_weight;
   float* ss_out;            /* device [n_out / 32] partial sums of squares of the output row, or NULL */
-  float residual_scale;     /* Dense (unquantised) Linear at decode: y[m, n_out] = f(x)[m, n_in] . W[n_out, n_in]^T for a weight stored row-major
- * as fp16, bf16 or fp32 (w_dtype) - the Linears a GGUF file leaves unquantised (router ffn_gate_inp, F16 models) or in a
- * block format without a fused kernel (Q6_K output heads, after b200q_dequant_raw to fp16).  Replaces Linear.__call__
- * (tinygrad/nn/__init__.py:177) for those; f = optional RMSNorm with norm_weight (fp16 [n_in]) as in b200q_gemv; bias fp16
- * [n_out]; residual / y in y_dtype.  fp32 products and accumulation.  n_in % 8 == 0, min(m, 4) * n_in * 4 <= 200 KiB; the weight is streamed once per 4 rows
- * (decode and router sizes; large m with large n_out belongs to a GEMM).
- * flags: B200Q_FLAG_PDL. */
-int b200q_gemv_dense(const void* w, int w_dtype, int n_out, int n_in, int m, const void* x, int x_dtype, const void* norm_weight,
-                     float norm_eps, const void* bias, const void* residual, void* y, int y_dtype, int flags, void* stream);
-
-/* the residual is multiplied by this before it is added; 0 means 1.  A row-parallel shard of a
+  float residual_scale;     /* the residual is multiplied by this before it is added; 0 means 1.  A row-parallel shard of a
                                tensor-parallel linear adds residual / n_ranks so that the all-reduce of the shards yields
                                W x + residual (tinygrad shards the same linears by axis, examples/llama3.py:233-243) */
 } b200q_gemv_args;
 int b200q_gemv(const b200q_gemv_args* args, void* stream);
 size_t b200q_xq_bytes(int n);
 
+/* Dense (unquantised) Linear at decode: y[m, n_out] = f(x)[m, n_in] . W[n_out, n_in]^T for a weight stored row-major
+ * as fp16, bf16 or fp32 (w_dtype) - the Linears a GGUF file leaves unquantised (router ffn_gate_inp, F16 models).
+ * Replaces Linear.__call__ (tinygrad/nn/__init__.py:177) for those; f = optional RMSNorm with norm_weight (fp16 [n_in])
+ * as in b200q_gemv; bias fp16 [n_out]; residual / y in y_dtype.  fp32 products and accumulation.  n_in % 8 == 0,
+ * min(m, 4) * n_in * 4 <= 200 KiB; the weight is streamed once per 4 rows (decode and router sizes; large m with large
+ * n_out belongs to a GEMM).  flags: B200Q_FLAG_PDL. */
+int b200q_gemv_dense(const void* w, int w_dtype, int n_out, int n_in, int m, const void* x, int x_dtype, const void* norm_weight,
+                     float norm_eps, const void* bias, const void* residual, void* y, int y_dtype, int flags, void* stream);
+
 /* ---- decode-step kernels -------------------------------------------------
  * Token embedding lookup to the fp32 residual stream:
  * `token_embd(tokens).float()` (tinygrad/llm/model.py:359).  The token id is read
  * on the device from tokens[*pos]. */
-int b200q_embed(const void* device_table_f16, const int32_t* device_tokens, const int32_t* device_pos, float* device_x, int dim,
-                int vocab, void* xq_out /* optional record for the first GEMV (b200q_gemv_args.xq_in), or NULL */,
+int b200q_embed(const void* device_table_f16, const int32_t* device_tokens /* [max_context + 1] */, const int32_t* device_pos, float* device_x, int dim,
+                int vocab, int max_context, void* xq_out /* optional record for the first GEMV (b200q_gemv_args.xq_in), or NULL */,
                 const void* xq_norm_weight /* fp16 [dim], multiplied into the record, or NULL */,
                 float* ss_out /* [dim / 32] partial sums of squares, or NULL */, int flags, void* stream);
 
@@ -218,12 +218,13 @@ int b200q_attn_decode_static(const b200q_attn_args* args, void* stream);
 
 /* Greedy sampling: tokens[*pos + 1] = argmax(logits) (lowest index on ties), then
  * *pos += 1.  At temperature 0 this is what the Gumbel-max expression of
- * tinygrad/llm/model.py:364 selects.  scratch: b200q_argmax_scratch_bytes(), zeroed once. */
+ * tinygrad/llm/model.py:364 selects.  scratch: b200q_argmax_scratch_bytes(), zeroed once.  tokens has max_context + 1
+ * entries; at *pos >= max_context nothing is written and the status word is set to 2. */
 size_t b200q_argmax_scratch_bytes(void);
-int b200q_argmax_advance(const float* device_logits, int n, int32_t* device_tokens, int32_t* device_pos, void* scratch, int flags,
-                         void* stream);
-/* *pos += 1 (a prompt token whose logits are not needed) */
-int b200q_advance(int32_t* device_pos, int flags, void* stream);
+int b200q_argmax_advance(const float* device_logits, int n, int32_t* device_tokens, int32_t* device_pos, int max_context, void* scratch,
+                         int flags, void* stream);
+/* *pos += 1 (a prompt token whose logits are not needed); stops at max_context like b200q_argmax_advance */
+int b200q_advance(int32_t* device_pos, int max_context, int flags, void* stream);
 
 /* ---- batched / prefill linear on tcgen05 tensor cores --------------------------------
  * C[m, n] fp32 = A[m, k] fp16 x W[n, k]^T fp16 with fp32 accumulation in tensor memory: `Linear.__call__` for more than

@@ -23,6 +23,30 @@ def test_exports_every_declared_symbol(lib):
   assert declared == set(_lib.SIGNATURES), "ctypes signatures and header disagree"
 
 
+def test_header_is_plain_c_and_structs_match_ctypes(tmp_path):
+  """include/b200q.h must be accepted by a C compiler (not only by nvcc reading it as C++), and the two argument structs
+  must have the layout the ctypes mirrors in tinygrad_b200/_lib.py assume."""
+  import shutil, subprocess
+  cc, cxx = shutil.which("gcc") or shutil.which("cc"), shutil.which("g++") or shutil.which("c++")
+  if not cc or not cxx: pytest.skip("no host C/C++ compiler")
+  hdr = ROOT / "include" / "b200q.h"
+  subprocess.run([cc, "-std=c11", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", str(hdr)], check=True)
+  subprocess.run([cxx, "-std=c++17", "-fsyntax-only", "-x", "c++", str(hdr)], check=True)
+  structs = {"b200q_gemv_args": _lib.GemvArgs, "b200q_attn_args": _lib.AttnArgs}
+  lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{hdr}"', 'int main(void) {']
+  for cname, ct in structs.items():
+    lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
+    for fname, _ in ct._fields_: lines.append(f'  printf("{cname}.{fname} %zu\\n", offsetof({cname}, {fname}));')
+  lines += ['  return 0;', '}']
+  src = tmp_path / "layout.c"
+  src.write_text("\n".join(lines))
+  subprocess.run([cc, "-std=c11", "-o", str(tmp_path / "layout"), str(src)], check=True)
+  got = dict(l.split() for l in subprocess.run([str(tmp_path / "layout")], check=True, capture_output=True, text=True).stdout.splitlines())
+  for cname, ct in structs.items():
+    assert int(got[cname]) == ctypes.sizeof(ct), cname
+    for fname, _ in ct._fields_: assert int(got[f"{cname}.{fname}"]) == getattr(ct, fname).offset, f"{cname}.{fname}"
+
+
 def test_strerror_and_version(lib):
   assert lib.b200q_version() >= 1
   assert lib.b200q_strerror(0) == b"ok"
@@ -71,3 +95,14 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
   monkeypatch.setattr(_lib, "_lib", None)
   monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
   with pytest.raises(_lib.B200QError): _lib.load()
+
+
+def test_step_past_the_context_end_raises_before_any_launch():
+  """The host mirrors the device position: a step with no KV-cache row left raises and launches nothing
+  (the object below has no device state at all, so any launch attempt would fail differently)."""
+  from tinygrad_b200.model import Transformer
+  m = Transformer.__new__(Transformer)
+  m.max_context, m._host_pos, m.is_moe, m.use_graph = 64, 64, False, True
+  with pytest.raises(RuntimeError, match="context full"): m.step()
+  with pytest.raises(RuntimeError, match="context full"): m.decode_batch_step()
+  assert m._host_pos == 64

@@ -114,6 +114,53 @@ def test_attention_decode_matches_oracle(kv_dtype, n_heads, n_kv, hd, rope_dim, 
   np.testing.assert_array_equal(d["kc"].numpy()[:, mask], kc[:, mask])        # nothing else touched
 
 
+def test_attention_at_the_last_cache_row_and_refusal_past_it():
+  """pos == max_context - 1 with a context that is not a multiple of the 64-position slice is served; pos == max_context
+  touches nothing (cache and output unchanged) and raises status 2; embed / arg-max / advance stop at the table's end."""
+  from tinygrad_b200 import _lib, runtime
+  from tinygrad_b200.runtime import DeviceBuffer
+  from tinygrad_b200.model import precompute_freqs_cis
+  lib = _lib.load()
+  rng = np.random.default_rng(3)
+  n_heads, n_kv, hd, ctx = 8, 2, 128, 100
+  n_split = lib.b200q_attn_min_split(ctx)
+  qkv = rng.standard_normal((n_heads + 2 * n_kv) * hd).astype(np.float32)
+  kc = (rng.standard_normal((n_kv, ctx, hd)) * 0.5).astype(np.float16); vc = rng.standard_normal((n_kv, ctx, hd)).astype(np.float16)
+  fc = precompute_freqs_cis(hd, ctx, 10000.0)
+  assert runtime.device_status() == 0
+  for pos in (ctx - 1, ctx):
+    d = {n: DeviceBuffer.from_numpy(a) for n, a in (("qkv", qkv), ("kc", kc), ("vc", vc), ("fc", fc), ("pos", np.array([pos], np.int32)))}
+    out = DeviceBuffer.from_numpy(np.full(n_heads * hd, 7.0, np.float32))
+    scratch = DeviceBuffer(lib.b200q_attn_scratch_bytes(n_heads, n_kv, hd, n_split), zero=True)
+    a = _lib.AttnArgs(d["qkv"].ptr, d["kc"].ptr, d["vc"].ptr, _lib.F16, d["fc"].ptr, d["pos"].ptr, out.ptr, scratch.ptr, n_heads, n_kv, hd, hd, ctx, n_split,
+                      0, None)
+    _lib.check(lib.b200q_attn_decode(ctypes.byref(a), None))
+    if pos == ctx:
+      assert runtime.device_status() == 2
+      np.testing.assert_array_equal(d["kc"].numpy(), kc); np.testing.assert_array_equal(d["vc"].numpy(), vc)
+      np.testing.assert_array_equal(out.numpy(), np.full(n_heads * hd, 7.0, np.float32))
+      continue
+    q = qkv[:n_heads * hd].reshape(1, n_heads, 1, hd); k = qkv[n_heads * hd:(n_heads + n_kv) * hd].reshape(1, n_kv, 1, hd)
+    v = qkv[(n_heads + n_kv) * hd:].reshape(n_kv, hd)
+    kr, vr = kc.copy(), vc.copy()
+    kr[:, pos] = llm.apply_rope(k, fc[pos:pos + 1])[0, :, 0].astype(np.float16); vr[:, pos] = v.astype(np.float16)
+    kk, vv = np.repeat(kr.astype(np.float32), n_heads // n_kv, axis=0), np.repeat(vr.astype(np.float32), n_heads // n_kv, axis=0)
+    sc = np.einsum("hd,hpd->hp", llm.apply_rope(q, fc[pos:pos + 1])[0, :, 0], kk) / np.float32(np.sqrt(hd))
+    assert_close(out.numpy(), np.einsum("hp,hpd->hd", llm.softmax(sc), vv).reshape(-1), tol=2e-3, what="attention at the last row")
+    np.testing.assert_array_equal(d["kc"].numpy()[:, pos], kr[:, pos])
+    assert runtime.device_status() == 0
+  # token table of max_context + 1 entries: the arg-max writes entry max_context at most
+  toks, logits = DeviceBuffer.from_numpy(np.arange(9, dtype=np.int32)), DeviceBuffer.from_numpy(np.array([0.0, 3.0, 1.0], np.float32))
+  scratch = DeviceBuffer(lib.b200q_argmax_scratch_bytes(), zero=True)
+  p = DeviceBuffer.from_numpy(np.array([7], np.int32))
+  _lib.check(lib.b200q_argmax_advance(logits.ptr, 3, toks.ptr, p.ptr, 8, scratch.ptr, 0, None))
+  assert int(p.numpy()[0]) == 8 and int(toks.numpy()[8]) == 1 and runtime.device_status() == 0
+  _lib.check(lib.b200q_argmax_advance(logits.ptr, 3, toks.ptr, p.ptr, 8, scratch.ptr, 0, None))
+  _lib.check(lib.b200q_advance(p.ptr, 8, 0, None))
+  assert int(p.numpy()[0]) == 8 and runtime.device_status() == 2
+  np.testing.assert_array_equal(toks.numpy(), [0, 1, 2, 3, 4, 5, 6, 7, 1])
+
+
 def test_argmax_lowest_index_wins_ties_and_advances():
   from tinygrad_b200 import _lib
   from tinygrad_b200.runtime import DeviceBuffer
@@ -124,7 +171,7 @@ def test_argmax_lowest_index_wins_ties_and_advances():
     logits = rng.standard_normal(n).astype(np.float32)
     if n > 1000: logits[[77777, 5000, 90000]] = logits.max() + 1.0          # a three-way tie
     d, toks, pos = DeviceBuffer.from_numpy(logits), DeviceBuffer.empty((8,), np.int32, zero=True), DeviceBuffer.from_numpy(np.array([3], np.int32))
-    _lib.check(lib.b200q_argmax_advance(d.ptr, n, toks.ptr, pos.ptr, scratch.ptr, 0, None))
+    _lib.check(lib.b200q_argmax_advance(d.ptr, n, toks.ptr, pos.ptr, 7, scratch.ptr, 0, None))
     assert int(pos.numpy()[0]) == 4
     assert int(toks.numpy()[4]) == int(np.argmax(logits))
 

@@ -61,7 +61,7 @@ SIGNATURES = {
   "b200q_repack": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
   "b200q_dequant_packed": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
   "b200q_gemv": (c_int, [POINTER(GemvArgs), c_void_p]),
-  "b200q_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+  "b200q_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
   "b200q_xq_bytes": (c_size_t, [c_int]),
   "b200q_attn_min_split": (c_int, [c_int]),
   "b200q_attn_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
@@ -69,8 +69,8 @@ SIGNATURES = {
   "b200q_attn_decode_static_capacity": (c_size_t, []),
   "b200q_attn_decode_static": (c_int, [POINTER(AttnArgs), c_void_p]),
   "b200q_argmax_scratch_bytes": (c_size_t, []),
-  "b200q_argmax_advance": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
-  "b200q_advance": (c_int, [c_void_p, c_int, c_void_p]),
+  "b200q_argmax_advance": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]),
+  "b200q_advance": (c_int, [c_void_p, c_int, c_int, c_void_p]),
   "b200q_gemm_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
   "b200q_qgemm": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
   "b200q_qgemm_skinny_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),

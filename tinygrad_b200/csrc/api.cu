@@ -10,6 +10,26 @@ void b200q_set_cuda_error(cudaError_t e) {
   cudaGetLastError();   // clear the sticky-free error state so later calls report their own status
 }
 
+int b200q_current_device() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { b200q_set_cuda_error(e); return -1; }
+  if (dev < 0 || dev >= B200Q_MAX_DEVICES) { b200q_set_cuda_error(cudaErrorInvalidDevice); return -1; }
+  return dev;
+}
+
+int b200q_sm_count() {
+  static std::atomic<int> n_sm[B200Q_MAX_DEVICES];
+  const int dev = b200q_current_device();
+  if (dev < 0) return 0;
+  int n = n_sm[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    n_sm[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
 extern "C" const char* b200q_last_cuda_error(void) { return g_cuda_err; }
 extern "C" int b200q_version(void) { return 1; }
 

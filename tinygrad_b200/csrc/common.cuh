@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
+#include <atomic>
 #include "../../include/b200q.h"
 
 #define B200Q_CHECK_CUDA(expr)                                   \
@@ -12,6 +13,24 @@
   } while (0)
 
 void b200q_set_cuda_error(cudaError_t e);
+
+// ---- per-device launcher state ---------------------------------------------------------
+// One host process may drive several GPUs (tinygrad does: one process, one context per device,
+// tinygrad/runtime/ops_cuda.py:97-134), and cudaFuncSetAttribute / the SM count belong to the device that is current.
+// Launchers therefore keep what they cache in tables indexed by the current device.  Setting an attribute twice is
+// harmless, so a relaxed atomic flag per device is all the thread safety the tables need.
+constexpr int B200Q_MAX_DEVICES = 64;
+struct PerDeviceFlag {
+  std::atomic<int> v[B200Q_MAX_DEVICES];
+  bool test(int dev) const { return v[dev].load(std::memory_order_acquire) != 0; }
+  void set(int dev) { v[dev].store(1, std::memory_order_release); }
+};
+// reads and clears the status word of the decode-step kernels (decode.cu); folded into b200q_status_read_clear
+int b200q_decode_status_take(int* status);
+// current device index, or -1 (with the CUDA error recorded) if it cannot be had or is past the tables
+int b200q_current_device();
+// SM count of the current device (cached per device); 0 on error
+int b200q_sm_count();
 
 // ---- packed weight layout (see include/b200q.h for the byte-level description)
 constexpr int TILE_ROWS = 16;       // output rows per tile (one mma.m16n8k16 A operand)

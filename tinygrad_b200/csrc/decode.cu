@@ -7,14 +7,23 @@
 
 namespace {
 
+// Sticky status of this file's kernels: 2 = a position outside [0, max_context) reached a kernel, which then skipped
+// its work instead of reading or writing past the token table / KV cache.  b200q_status_read_clear reports it.
+__device__ int g_decode_status = 0;
+
 // Also leaves, for the first GEMV of the step, the row already multiplied by that GEMV's RMSNorm weight and
 // quantised (actquant.cuh), with one partial sum of squares per block of 32.
 __global__ void __launch_bounds__(256) embed_kernel(const __half* __restrict__ table, const int32_t* __restrict__ tokens,
-                                                    const int32_t* __restrict__ pos, float* __restrict__ x, int dim, int vocab, void* xq_out,
-                                                    const __half* __restrict__ norm_w, float* ss_out) {
+                                                    const int32_t* __restrict__ pos, float* __restrict__ x, int dim, int vocab, int max_context,
+                                                    void* xq_out, const __half* __restrict__ norm_w, float* ss_out) {
   pdl_launch_dependents();
   pdl_wait();
-  int tok = tokens[*pos];
+  int p = *pos;
+  if (p < 0 || p > max_context) {      // the token table has max_context + 1 entries
+    if (threadIdx.x == 0 && blockIdx.x == 0) atomicExch(&g_decode_status, 2);
+    p = p < 0 ? 0 : max_context;       // keep the activations finite; the step's result is flagged invalid
+  }
+  int tok = tokens[p];
   tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
   const __half* row = table + (size_t)tok * dim;
   if (!xq_out) {
@@ -33,10 +42,14 @@ __global__ void __launch_bounds__(256) embed_kernel(const __half* __restrict__ t
   }
 }
 
-__global__ void advance_kernel(int32_t* pos) {
+__global__ void advance_kernel(int32_t* pos, int max_context) {
   pdl_launch_dependents();
   pdl_wait();
-  if (threadIdx.x == 0) *pos += 1;
+  if (threadIdx.x == 0) {
+    const int p = *pos;
+    if (p < 0 || p >= max_context) atomicExch(&g_decode_status, 2);
+    else *pos = p + 1;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -120,6 +133,11 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
   fetch_rows(pos_early);
   pdl_wait();
   const int pos = __ldcg(a.pos);
+  if (pos < 0 || pos >= a.max_context) {        // no cache row for this position: touch nothing (uniform over the grid)
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (threadIdx.x == 0) atomicExch(&g_decode_status, 2);
+    return;
+  }
   if (pos != pos_early) {                       // uniform over the CTA
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
@@ -255,7 +273,7 @@ __device__ __forceinline__ void argmax_combine(float& v, int& i, float ov, int o
 }
 
 __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const float* __restrict__ logits, int n, int32_t* tokens, int32_t* pos,
-                                                                float* sval, int* sidx, unsigned* counter) {
+                                                                int max_context, float* sval, int* sidx, unsigned* counter) {
   __shared__ float wv[ARGMAX_THREADS / 32];
   __shared__ int wi[ARGMAX_THREADS / 32];
   __shared__ int s_last;
@@ -297,27 +315,34 @@ __global__ void __launch_bounds__(ARGMAX_THREADS) argmax_kernel(const float* __r
   __syncthreads();
   block_reduce();
   if (threadIdx.x == 0) {
-    int p = *pos;
-    tokens[p + 1] = idx == 0x7fffffff ? 0 : idx;
-    *pos = p + 1;
+    const int p = *pos;
+    if (p < 0 || p >= max_context) atomicExch(&g_decode_status, 2);      // tokens[max_context] is the last entry
+    else { tokens[p + 1] = idx == 0x7fffffff ? 0 : idx; *pos = p + 1; }
   }
 }
 
 }  // namespace
 
-extern "C" int b200q_embed(const void* table, const int32_t* tokens, const int32_t* pos, float* x, int dim, int vocab, void* xq_out,
-                           const void* xq_norm_weight, float* ss_out, int flags, void* stream) {
-  if (!table || !tokens || !pos || !x || dim <= 0 || vocab <= 0) return B200Q_ERR_BAD_ARG;
-  if ((uintptr_t)xq_out & 15) return B200Q_ERR_MISALIGNED;
-  if (xq_out && dim % 32) return B200Q_ERR_BAD_SHAPE;
-  B200Q_CHECK_CUDA(launch_k(embed_kernel, dim3(ceil_div(dim, 256)), dim3(256), 0, (cudaStream_t)stream, (flags & B200Q_FLAG_PDL) != 0,
-                            (const __half*)table, tokens, pos, x, dim, vocab, xq_out, (const __half*)xq_norm_weight, ss_out));
+int b200q_decode_status_take(int* status) {
+  int zero = 0;
+  B200Q_CHECK_CUDA(cudaMemcpyFromSymbol(status, g_decode_status, sizeof(int)));
+  B200Q_CHECK_CUDA(cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int)));
   return B200Q_OK;
 }
 
-extern "C" int b200q_advance(int32_t* pos, int flags, void* stream) {
-  if (!pos) return B200Q_ERR_BAD_ARG;
-  B200Q_CHECK_CUDA(launch_k(advance_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, (flags & B200Q_FLAG_PDL) != 0, pos));
+extern "C" int b200q_embed(const void* table, const int32_t* tokens, const int32_t* pos, float* x, int dim, int vocab, int max_context, void* xq_out,
+                           const void* xq_norm_weight, float* ss_out, int flags, void* stream) {
+  if (!table || !tokens || !pos || !x || dim <= 0 || vocab <= 0 || max_context <= 0) return B200Q_ERR_BAD_ARG;
+  if ((uintptr_t)xq_out & 15) return B200Q_ERR_MISALIGNED;
+  if (xq_out && dim % 32) return B200Q_ERR_BAD_SHAPE;
+  B200Q_CHECK_CUDA(launch_k(embed_kernel, dim3(ceil_div(dim, 256)), dim3(256), 0, (cudaStream_t)stream, (flags & B200Q_FLAG_PDL) != 0,
+                            (const __half*)table, tokens, pos, x, dim, vocab, max_context, xq_out, (const __half*)xq_norm_weight, ss_out));
+  return B200Q_OK;
+}
+
+extern "C" int b200q_advance(int32_t* pos, int max_context, int flags, void* stream) {
+  if (!pos || max_context <= 0) return B200Q_ERR_BAD_ARG;
+  B200Q_CHECK_CUDA(launch_k(advance_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, (flags & B200Q_FLAG_PDL) != 0, pos, max_context));
   return B200Q_OK;
 }
 
@@ -342,10 +367,13 @@ extern "C" int b200q_attn_decode(const b200q_attn_args* a, void* stream) {
   bool pdl = (a->flags & B200Q_FLAG_PDL) != 0;
   const int esz = a->kv_dtype == B200Q_F16 ? 2 : 4, vec = 16 / esz;
   size_t smem = (size_t)2 * ATTN_CHUNK * (a->head_dim + vec) * esz + (size_t)n_rep * (a->head_dim + ATTN_CHUNK) * sizeof(float);
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceFlag attr_set;
+  const int dev = b200q_current_device();
+  if (dev < 0) return B200Q_ERR_CUDA;
+  if (!attr_set.test(dev)) {
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(attn_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-    attr_set = true;
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(attn_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    attr_set.set(dev);
   }
   if (a->kv_dtype == B200Q_F16) B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<__half>, grid, block, smem, (cudaStream_t)stream, pdl, *a));
   else B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<float>, grid, block, smem, (cudaStream_t)stream, pdl, *a));
@@ -354,12 +382,12 @@ extern "C" int b200q_attn_decode(const b200q_attn_args* a, void* stream) {
 
 extern "C" size_t b200q_argmax_scratch_bytes(void) { return ARGMAX_CTAS * (sizeof(float) + sizeof(int)) + sizeof(unsigned); }
 
-extern "C" int b200q_argmax_advance(const float* logits, int n, int32_t* tokens, int32_t* pos, void* scratch, int flags, void* stream) {
-  if (!logits || !tokens || !pos || !scratch || n <= 0) return B200Q_ERR_BAD_ARG;
+extern "C" int b200q_argmax_advance(const float* logits, int n, int32_t* tokens, int32_t* pos, int max_context, void* scratch, int flags, void* stream) {
+  if (!logits || !tokens || !pos || !scratch || n <= 0 || max_context <= 0) return B200Q_ERR_BAD_ARG;
   float* sval = (float*)scratch; int* sidx = (int*)(sval + ARGMAX_CTAS); unsigned* counter = (unsigned*)(sidx + ARGMAX_CTAS);
   int grid = ceil_div(n, ARGMAX_THREADS); if (grid > ARGMAX_CTAS) grid = ARGMAX_CTAS;
   B200Q_CHECK_CUDA(launch_k(argmax_kernel, dim3(grid), dim3(ARGMAX_THREADS), 0, (cudaStream_t)stream, (flags & B200Q_FLAG_PDL) != 0,
-                            logits, n, tokens, pos, sval, sidx, counter));
+                            logits, n, tokens, pos, max_context, sval, sidx, counter));
   return B200Q_OK;
 }
 
@@ -374,7 +402,7 @@ extern "C" int b200q_argmax_advance(const float* logits, int n, int32_t* tokens,
 constexpr size_t ATTN_STATIC_SCRATCH_BYTES = (size_t)2 << 20;     // 2 MiB: e.g. 64 heads x 62 slices (3968 positions) of head_dim 128
 static __device__ __align__(256) unsigned char g_attn_static_scratch[ATTN_STATIC_SCRATCH_BYTES];
 
-constexpr int MAX_DEVICES = 64;
+constexpr int MAX_DEVICES = B200Q_MAX_DEVICES;
 static void* g_attn_static_ptr[MAX_DEVICES];   // device address of the array on each device, filled on first use
 
 extern "C" size_t b200q_attn_decode_static_capacity(void) { return ATTN_STATIC_SCRATCH_BYTES; }

@@ -154,13 +154,8 @@ extern "C" int b200q_gemv_dense(const void* w, int w_dtype, int n_out, int n_in,
   const size_t smem = (size_t)(m < MAX_M ? m : MAX_M) * n_in * sizeof(float);
   if (smem > 200 * 1024) return B200Q_ERR_TOO_LARGE;
   if (((uintptr_t)w & 15) || ((uintptr_t)x & 3)) return B200Q_ERR_MISALIGNED;
-  static int n_sm = 0;
-  if (!n_sm) {
-    int dev = 0, sms = 0;
-    B200Q_CHECK_CUDA(cudaGetDevice(&dev));
-    B200Q_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    n_sm = sms;
-  }
+  const int n_sm = b200q_sm_count();
+  if (n_sm <= 0) return B200Q_ERR_CUDA;
   DenseParams p;
   p.w = w; p.x = x; p.norm_w = (const __half*)norm_weight; p.bias = (const __half*)bias; p.residual = residual; p.y = y;
   p.n_out = n_out; p.n_in = n_in; p.m = m; p.eps = norm_eps; p.x_f16 = x_dtype == B200Q_F16; p.y_f16 = y_dtype == B200Q_F16;

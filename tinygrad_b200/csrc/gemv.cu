@@ -401,18 +401,24 @@ int launch_gemv(const b200q_gemv_args* a, const GemvParams& p, cudaStream_t stre
                       (2 * CONS_WARPS * 16 + CONS_WARPS + 32) * sizeof(float) + (2 * NS + 1) * sizeof(uint64_t) + 16;
   if (smem > 220 * 1024) return B200Q_ERR_TOO_LARGE;
   auto kern = qgemv_kernel<QT, XQ_IN, XQ_OUT>;
-  static int sm_count = 0, occ_cache_smem = -1, occ_cache = 0;
-  if (sm_count == 0) {
-    int dev; B200Q_CHECK_CUDA(cudaGetDevice(&dev));
-    B200Q_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  // per device (and per instantiation): the shared-memory attribute, and the last occupancy answer packed as (smem << 8) | blocks
+  static PerDeviceFlag attr_set;
+  static std::atomic<long long> occ_cache[B200Q_MAX_DEVICES];
+  const int dev = b200q_current_device(), sm_count = b200q_sm_count();
+  if (dev < 0 || sm_count <= 0) return B200Q_ERR_CUDA;
+  if (!attr_set.test(dev)) {
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    attr_set.set(dev);
   }
-  if (occ_cache_smem != (int)smem) {
-    B200Q_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_cache, kern, NTHREADS, smem));
-    if (occ_cache < 1) occ_cache = 1;
-    occ_cache_smem = (int)smem;
+  long long oc = occ_cache[dev].load(std::memory_order_relaxed);
+  if (oc == 0 || (oc >> 8) != (long long)smem) {
+    int occ = 0;
+    B200Q_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NTHREADS, smem));
+    if (occ < 1) occ = 1;
+    oc = ((long long)smem << 8) | occ;
+    occ_cache[dev].store(oc, std::memory_order_relaxed);
   }
-  const int max_ctas = a->max_ctas > 0 ? a->max_ctas : occ_cache * sm_count;
+  const int max_ctas = a->max_ctas > 0 ? a->max_ctas : (int)(oc & 0xFF) * sm_count;
   const int grid_x = p.n_units < max_ctas ? p.n_units : max_ctas;
   B200Q_CHECK_CUDA(launch_k(kern, dim3(grid_x, a->m), dim3(NTHREADS), smem, stream, (a->flags & B200Q_FLAG_PDL) != 0, p));
   return B200Q_OK;
@@ -425,6 +431,10 @@ extern "C" int b200q_status_read_clear(int* status) {
   int zero = 0;
   B200Q_CHECK_CUDA(cudaMemcpyFromSymbol(status, g_status, sizeof(int)));
   B200Q_CHECK_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(int)));
+  int dec = 0;
+  const int rc = b200q_decode_status_take(&dec);
+  if (rc != B200Q_OK) return rc;
+  if (dec && !*status) *status = dec;
   return B200Q_OK;
 }
 

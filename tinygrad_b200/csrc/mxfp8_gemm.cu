@@ -16,14 +16,10 @@
 //   warps 0-3, 9-12  epilogue: tcgen05.ld the fp32 accumulator (256 tensor-memory columns; two warps per 32-lane sub-partition,
 //              128 columns each), round to bf16, store.
 // Loaders run ahead across tile boundaries; only the accumulator hand-over (one buffer) serialises epilogue and next tile.
-// Measured and not kept: a warp that prefetched the next tile's rows into L2 (bulk or per-line prefetch) fell behind the tiles
-// under the load of the ring's own copies; the ring's ~150 KB in flight per SM against the loaded L2's latency is what bounds
-// the kernel (tensor pipe 39 % active, L2 43 %, HBM 28 % under ncu).
 // Every mbarrier wait is bounded; a wait that runs out raises a status word and makes every role leave.
 #include "common.cuh"
 #include "mxq.cuh"
 #include <cuda_bf16.h>
-#include <stdlib.h>
 
 namespace {
 
@@ -64,18 +60,6 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
   for (int i = 0; i < SPIN; i++) {
     uint32_t ok;
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-    if ((i & 255) == 255 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  atomicExch(&g_mx_status, 1);
-  return false;
-}
-// the same wait for a barrier another CTA of the cluster arrives on (acquire at cluster scope)
-__device__ __forceinline__ bool wait_bar_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (int i = 0; i < SPIN; i++) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     if (ok) return true;
     if ((i & 255) == 255 && *abort_flag) return false;
   }
@@ -289,201 +273,6 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
   }
 }
 
-// ---------------------------------------------------------------------------------------------------------------
-// The same GEMM on CTA pairs (tcgen05 cta_group::2): a cluster of two CTAs computes a 256 x 256 tile, CTA r holding rows
-// r*128.. of A and of the B tile (its half of N) in its own shared memory and its 128 accumulator rows in its own tensor memory.
-// The leader (cluster rank 0) issues the MMAs for both; every B byte is loaded by one CTA of the pair only, which cuts the
-// L2 -> SM traffic per flop by a third against the one-CTA kernel (the measured limiter there).  Scale factors: each CTA loads
-// the A scales of its rows and the B scales of all 256 columns.  Synchronisation on top of the one-CTA kernel's: the peer's
-// warp 8 forwards "my stage landed" to the leader with a remote mbarrier arrive; tcgen05.commit multicasts "stage free" and
-// "accumulator ready" to both CTAs; the peer's epilogue threads arrive remotely on the leader's "accumulator drained" barrier.
-constexpr int P_STAGES = 6;
-constexpr int P_A_BYTES = 128 * BK, P_B_BYTES = 128 * BK, P_STAGE_BYTES = P_A_BYTES + P_B_BYTES + SF_BYTES;   // 34 KB
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024;
-constexpr int P_SFA_COL = 256, P_SFB_COL = 256 + 4 * P_STAGES;
-
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void arrive_remote(uint32_t local_bar, uint32_t cta_rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_bar), "r"(cta_rank));
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
-}
-
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-grouped_mxfp8_pair_kernel(const uint8_t* __restrict__ a_q, const uint8_t* __restrict__ a_e8, const uint8_t* __restrict__ b_q,
-                          const uint8_t* __restrict__ b_e8, const int32_t* __restrict__ off, int n_experts, int m_total, int n, int k,
-                          __nv_bfloat16* __restrict__ c) {
-  extern __shared__ unsigned char sm_raw[];
-  __shared__ __align__(8) uint64_t bar_full[P_STAGES], bar_peer_full[P_STAGES], bar_empty[P_STAGES], bar_acc_full, bar_acc_empty, bar_drain;
-  __shared__ uint32_t tmem_base;
-  __shared__ int s_abort;
-  __shared__ int s_off[MAX_EXPERTS + 1];
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  uint32_t rank;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-  if (tid == 0) {
-    for (int s = 0; s < P_STAGES; s++) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&bar_full[s])), "r"(LOAD_WARPS * 32));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bar_peer_full[s])));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bar_empty[s])));
-    }
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bar_acc_full)));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&bar_acc_empty)), "r"(4 * EPI_WARPS * 32));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bar_drain)));
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    s_abort = 0;
-  }
-  for (int i = tid; i <= n_experts; i += THREADS) s_off[i] = off[i];
-  if (warp == EPI_WARPS + LOAD_WARPS) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&tmem_base)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  cluster_sync_all();                       // both CTAs' barriers exist before anyone arrives remotely
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t taddr = tmem_base;
-  volatile int* abort_flag = &s_abort;
-  const int kb_total = k >> 5, ktiles = k / BK;
-  const int m_used = min(max(s_off[n_experts], 0), m_total);
-  const int tiles_n = n / BN, n_tiles = (m_used / 256) * tiles_n;
-  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const uint32_t ring = (s32(sm_raw) + 1023u) & ~1023u;
-
-  if (warp >= EPI_WARPS && warp < EPI_WARPS + LOAD_WARPS) {
-    // ---------------------------------------------------------------- loaders (both CTAs)
-    const int lt = tid - EPI_WARPS * 32;
-    const int r0 = lt >> 3, ch = lt & 7;
-    const uint32_t t_off = (uint32_t)(r0 * 128 + ((ch ^ (r0 & 7)) << 4));
-    const uint32_t sf_off = (uint32_t)((lt & 31) * 16 + (lt >> 5) * 4);
-    uint32_t g = 0;
-    bool ok = true;
-    for (int t = pair; t < n_tiles && ok; t += n_pairs) {
-      const int m0 = (t / tiles_n) * 256 + (int)rank * 128, n0 = (t % tiles_n) * BN;
-      int lo = 0, hi = n_experts - 1;
-      while (lo < hi) { const int mid = (lo + hi) >> 1; if (s_off[mid + 1] <= m0) lo = mid + 1; else hi = mid; }
-      const uint8_t* ap = a_q + (size_t)(m0 + r0) * k + ch * 16;
-      const uint8_t* bp = b_q + ((size_t)lo * n + n0 + rank * 128 + r0) * k + ch * 16;
-      const uint8_t* ae = a_e8 + (size_t)(m0 + lt) * kb_total;
-      const uint8_t* be = b_e8 + ((size_t)lo * n + n0 + lt) * kb_total;
-      for (int kt = 0; kt < ktiles; kt++, g++) {
-        const uint32_t slot = g % P_STAGES;
-        if (g >= P_STAGES && !wait_bar(s32(&bar_empty[slot]), ((g / P_STAGES) - 1) & 1, abort_flag)) { ok = false; break; }
-        const uint32_t sA = ring + slot * P_STAGE_BYTES, sB = sA + P_A_BYTES, sF = sB + P_B_BYTES;
-        const uint8_t* pa = ap + kt * BK;
-        const uint8_t* pb = bp + kt * BK;
-#pragma unroll
-        for (int j = 0; j < 8; j++) cp16(sA + t_off + j * 2048, pa + (size_t)(16 * j) * k);
-#pragma unroll
-        for (int j = 0; j < 8; j++) cp16(sB + t_off + j * 2048, pb + (size_t)(16 * j) * k);
-        cp4(sF + sf_off, ae + kt * 4);
-        cp4(sF + 512 + sf_off, be + kt * 4);
-        cp4(sF + 1024 + sf_off, be + (size_t)128 * kb_total + kt * 4);
-        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(s32(&bar_full[slot])) : "memory");
-      }
-    }
-    asm volatile("cp.async.wait_all;" ::: "memory");
-  } else if (warp == EPI_WARPS + LOAD_WARPS) {
-    if (lane == 0 && rank == 1) {
-      // ---------------------------------------------------------------- peer: forward "stage landed" to the leader
-      uint32_t g = 0;
-      bool ok = true;
-      for (int t = pair; t < n_tiles && ok; t += n_pairs)
-        for (int kt = 0; kt < ktiles; kt++, g++) {
-          const uint32_t slot = g % P_STAGES;
-          if (!wait_bar(s32(&bar_full[slot]), (g / P_STAGES) & 1, abort_flag)) { ok = false; break; }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          arrive_remote(s32(&bar_peer_full[slot]), 0);
-        }
-    } else if (lane == 0) {
-      // ---------------------------------------------------------------- leader: MMA issue for the pair
-      uint32_t g = 0, tile_i = 0;
-      bool ok = true;
-      for (int t = pair; t < n_tiles && ok; t += n_pairs, tile_i++) {
-        if (tile_i > 0 && !wait_bar_cluster(s32(&bar_acc_empty), (tile_i - 1) & 1, abort_flag)) { ok = false; break; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        for (int kt = 0; kt < ktiles; kt++, g++) {
-          const uint32_t slot = g % P_STAGES, par = (g / P_STAGES) & 1;
-          if (!wait_bar(s32(&bar_full[slot]), par, abort_flag) || !wait_bar_cluster(s32(&bar_peer_full[slot]), par, abort_flag)) { ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          const uint32_t sA = ring + slot * P_STAGE_BYTES, sB = sA + P_A_BYTES, sF = sB + P_B_BYTES;
-          const uint32_t sfa = taddr + P_SFA_COL + slot * 4, sfb = taddr + P_SFB_COL + slot * 8;
-          asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(sfa), "l"(desc_plain(sF, 128, 128)) : "memory");
-          asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(sfb), "l"(desc_plain(sF + 512, 128, 128)) : "memory");
-          asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(sfb + 4), "l"(desc_plain(sF + 1024, 128, 128)) : "memory");
-#pragma unroll
-          for (int kb = 0; kb < 4; kb++) {
-            const uint64_t da = desc_sw128(sA + kb * 32), db = desc_sw128(sB + kb * 32);
-            const uint32_t idesc = ((uint32_t)kb << 4) | ((uint32_t)(BN >> 3) << 17) | (1u << 23) | ((uint32_t)(256 >> 7) << 27) | ((uint32_t)kb << 29);
-            const uint32_t acc = (kt > 0 || kb > 0) ? 1u : 0u;
-            asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %6, 0;\n"
-                         "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n}"
-                         ::"r"(taddr), "l"(da), "l"(db), "r"(idesc), "r"(sfa), "r"(sfb), "r"(acc) : "memory");
-          }
-          asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                       ::"r"(s32(&bar_empty[slot])), "h"((uint16_t)3) : "memory");
-        }
-        if (ok) asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                             ::"r"(s32(&bar_acc_full)), "h"((uint16_t)3) : "memory");
-      }
-      if (!ok) {     // leave nothing in flight before the tensor memory is given back
-        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&bar_drain)) : "memory");
-        for (int i = 0; i < SPIN; i++) {
-          uint32_t done;
-          asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(done) : "r"(s32(&bar_drain)) : "memory");
-          if (done) break;
-        }
-      }
-    }
-  } else {
-    // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
-    uint32_t tile_i = 0;
-    for (int t = pair; t < n_tiles; t += n_pairs, tile_i++) {
-      if (!wait_bar(s32(&bar_acc_full), tile_i & 1, abort_flag)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int m0 = (t / tiles_n) * 256 + (int)rank * 128, n0 = (t % tiles_n) * BN;
-      const int sub = warp & 3, cbase = warp < EPI_WARPS ? 0 : BN / 2;     // sub-partition = warp % 4; two warps split its 256 columns
-      __nv_bfloat16* out_row = c + (size_t)(m0 + sub * 32 + lane) * n + n0;
-#pragma unroll 1
-      for (int j0 = cbase; j0 < cbase + BN / 2; j0 += 32) {
-        uint32_t v[32];
-        const uint32_t ta = taddr + ((uint32_t)(sub * 32) << 16) + j0;
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
-                       "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-                       "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
-                       "=r"(v[31])
-                     : "r"(ta));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (j0 + 32 == cbase + BN / 2) {      // this CTA's part of the accumulator is in registers
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          if (rank == 0) arrive(s32(&bar_acc_empty)); else arrive_remote(s32(&bar_acc_empty), 0);
-        }
-#pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          uint4 pk;
-          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-          for (int q = 0; q < 4; q++) h[q] = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * q]), __uint_as_float(v[j + 2 * q + 1]));
-          *reinterpret_cast<uint4*>(out_row + j0 + j) = pk;
-        }
-      }
-    }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  __syncwarp();
-  cluster_sync_all();                       // the peer's shared and tensor memory stay alive until the leader's MMAs are done
-  if (warp == EPI_WARPS + LOAD_WARPS) {
-    __syncwarp();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(TMEM_COLS) : "memory");
-  }
-}
-
 }  // namespace
 
 extern "C" int b200q_mx_status_read_clear(int* status) {
@@ -501,34 +290,12 @@ static int grouped_launch(const void* a_q, const void* a_e8, const void* b_q, co
   if (m_total % 256 || n % BN || k % BK) return B200Q_ERR_BAD_SHAPE;       // the reference asks M % 256 == N % 256 == K % 128 == 0 (moe_gemm.py:120)
   if (n_experts > MAX_EXPERTS) return B200Q_ERR_UNSUPPORTED;
   if (((uintptr_t)a_q | (uintptr_t)b_q | (uintptr_t)c_bf16) & 15 || ((uintptr_t)a_e8 | (uintptr_t)b_e8) & 3) return B200Q_ERR_MISALIGNED;
-  static int n_sm = 0, n_clusters = 0, use_pairs = 0;      // the CTA-pair kernel is opt-in: correct, but measured slower so far
-  if (!n_sm) {
-    int dev = 0, sms = 0;
-    B200Q_CHECK_CUDA(cudaGetDevice(&dev));
-    B200Q_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  static PerDeviceFlag attr_set;
+  const int dev = b200q_current_device(), n_sm = b200q_sm_count();
+  if (dev < 0 || n_sm <= 0) return B200Q_ERR_CUDA;
+  if (!attr_set.test(dev)) {
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(grouped_mxfp8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    B200Q_CHECK_CUDA(cudaFuncSetAttribute(grouped_mxfp8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
-    // how many CTA pairs can be resident at once (a persistent kernel must not be larger than that)
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(sms & ~1); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = P_SMEM_BYTES;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
-    int nc = 0;
-    if (cudaOccupancyMaxActiveClusters(&nc, grouped_mxfp8_pair_kernel, &cfg) != cudaSuccess) { nc = 0; (void)cudaGetLastError(); }
-    n_clusters = nc;
-    const char* e = getenv("B200Q_MX_PAIRS");
-    if (e) use_pairs = atoi(e);
-    n_sm = sms;
-  }
-  if (use_pairs && n_clusters > 0 && !act_q) {
-    const long long ptiles = (long long)(m_total / 256) * (n / BN);
-    const int pairs = (int)(ptiles < n_clusters ? ptiles : n_clusters);
-    grouped_mxfp8_pair_kernel<<<2 * pairs, THREADS, P_SMEM_BYTES, (cudaStream_t)stream>>>((const uint8_t*)a_q, (const uint8_t*)a_e8, (const uint8_t*)b_q,
-                                                                                          (const uint8_t*)b_e8, off, n_experts, m_total, n, k,
-                                                                                          (__nv_bfloat16*)c_bf16);
-    B200Q_CHECK_CUDA(cudaGetLastError());
-    return B200Q_OK;
+    attr_set.set(dev);
   }
   const long long tiles = (long long)(m_total / BM) * (n / BN);
   const int grid = (int)(tiles < n_sm ? tiles : n_sm);

@@ -626,11 +626,13 @@ extern "C" int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x
   p.m = m; p.n_out = n_out; p.n_in = n_in; p.kgroups = ceil_div(n_in, GROUP_ELEMS); p.n_row_tiles = ceil_div(n_out, TILE_ROWS);
   p.x_f16 = x_dtype == B200Q_F16; p.y_f16 = y_dtype == B200Q_F16;
   dim3 grid(ceil_div(p.n_row_tiles, BN / 16), ceil_div(m, BM));
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceFlag attr;
+  const int dev = b200q_current_device();
+  if (dev < 0) return B200Q_ERR_CUDA;
+  if (!attr.test(dev)) {
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_kernel<B200Q_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, QGEMM_SMEM));
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_kernel<B200Q_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, QGEMM_SMEM));
-    attr = true;
+    attr.set(dev);
   }
   if (qtype == B200Q_Q4_0) tc_qgemm_kernel<B200Q_Q4_0><<<grid, QGEMM_THREADS, QGEMM_SMEM, (cudaStream_t)stream>>>(p);
   else tc_qgemm_kernel<B200Q_Q8_0><<<grid, QGEMM_THREADS, QGEMM_SMEM, (cudaStream_t)stream>>>(p);
@@ -646,15 +648,7 @@ static int skinny_splits(int n_row_tiles, int kgroups, int n_sm) {
   return splits < 1 ? 1 : splits;
 }
 
-static int sm_count_cached() {
-  static int n_sm = 0;
-  if (!n_sm) {
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-    n_sm = sms;
-  }
-  return n_sm;
-}
+static int sm_count_cached() { return b200q_sm_count(); }
 
 extern "C" size_t b200q_qgemm_skinny_workspace_bytes(int m, int n_out, int n_in) {
   if (m <= 0 || n_out <= 0 || n_in <= 0) return 0;
@@ -677,11 +671,13 @@ extern "C" int b200q_qgemm_skinny(int qtype, const void* w_packed, const void* x
   if (((uintptr_t)w_packed | (uintptr_t)x | (uintptr_t)workspace) & 15) return B200Q_ERR_MISALIGNED;
   const int n_sm = sm_count_cached();
   if (!n_sm) return B200Q_ERR_CUDA;
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceFlag attr;
+  const int dev = b200q_current_device();
+  if (dev < 0) return B200Q_ERR_CUDA;
+  if (!attr.test(dev)) {
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_skinny_kernel<B200Q_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, sk_smem_total(B200Q_Q4_0)));
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_skinny_kernel<B200Q_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, sk_smem_total(B200Q_Q8_0)));
-    attr = true;
+    attr.set(dev);
   }
   SkinnyParams p;
   p.w = (const uint8_t*)w_packed; p.x = x; p.part = (float*)workspace;

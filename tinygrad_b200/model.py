@@ -187,7 +187,7 @@ class Transformer:
     in_act = dict(xq_in=self.xq_act) if "gateup_down" in e else {}
     if attention or tail:
       ho = "down_qkv" in e
-      check(lib.b200q_embed(self.token_embd.ptr, self.tokens.ptr, self.pos.ptr, self.x.ptr, c.dim, vocab_full,
+      check(lib.b200q_embed(self.token_embd.ptr, self.tokens.ptr, self.pos.ptr, self.x.ptr, c.dim, vocab_full, c.max_context,
                             self.xq_a.ptr if ho else None, self.blk[0].attn_norm.ptr if ho else None, self.ss_a.ptr if ho else None, fl, s))
     for i, b in enumerate(self.blk):
       nxt_norm = self.blk[i + 1].attn_norm if i + 1 < len(self.blk) else self.output_norm
@@ -217,10 +217,10 @@ class Transformer:
         quant.gemv(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, None if in_a else self.x, self.logits_part,
                    norm_weight=self.output_norm, norm_eps=c.norm_eps, **in_a, **kw_after_coll)
       if tp is not None: tp.all_gather(self.logits, self.logits_part)
-      if tail: check(lib.b200q_argmax_advance(self.logits.ptr, vocab_full, self.tokens.ptr, self.pos.ptr, self.argmax_scratch.ptr,
+      if tail: check(lib.b200q_argmax_advance(self.logits.ptr, vocab_full, self.tokens.ptr, self.pos.ptr, c.max_context, self.argmax_scratch.ptr,
                                               0 if tp is not None else fl, s))
     elif tail:
-      check(lib.b200q_advance(self.pos.ptr, 0 if tp is not None else fl, s))
+      check(lib.b200q_advance(self.pos.ptr, c.max_context, 0 if tp is not None else fl, s))
 
   # ---- several prompt tokens at once: tcgen05 dequant GEMMs + batched causal attention ----
   def _prefill_buffers(self):
@@ -273,6 +273,7 @@ class Transformer:
     """One new token for each of the `batch` sequences, all at the same position: every Linear is one GEMM over the batch rows
     (weights streamed once per step), attention runs per sequence on its own cache, the arg-max per sequence.  Captured once into a
     CUDA graph (positions and tokens live on the device) and replayed."""
+    self._check_room()
     if not self.use_graph: return self._enqueue_batch_step()
     if self._batch_graph is None:
       self._enqueue_batch_step()                       # allocates the buffers outside the capture (and is a real step)
@@ -312,7 +313,7 @@ class Transformer:
     else: quant.gemv_dense(self.output.buf, self.output.dtype, c.vocab_size, c.dim, f["xn"], self._batch_logits, m=B, stream=s)
     for i in range(B):
       check(lib.b200q_argmax_advance(self._batch_logits.ptr + 4 * i * c.vocab_size, c.vocab_size, self.tokens.ptr + 4 * i * (c.max_context + 1),
-                                     self.pos.ptr + 4 * i, self.argmax_scratch.ptr, 0, s))
+                                     self.pos.ptr + 4 * i, c.max_context, self.argmax_scratch.ptr, 0, s))
     if count: self._host_pos += 1
 
   def generate_batch(self, prompts: list):
@@ -346,10 +347,14 @@ class Transformer:
       else:
         quant.gemv(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, x_last, self.logits, norm_weight=self.output_norm, norm_eps=c.norm_eps,
                    stream=s)
-      check(lib.b200q_argmax_advance(self.logits.ptr, c.vocab_size, self.tokens.ptr, self.pos.ptr, self.argmax_scratch.ptr, 0, s))
+      check(lib.b200q_argmax_advance(self.logits.ptr, c.vocab_size, self.tokens.ptr, self.pos.ptr, c.max_context, self.argmax_scratch.ptr, 0, s))
     else:
-      check(lib.b200q_advance(self.pos.ptr, 0, s))
+      check(lib.b200q_advance(self.pos.ptr, c.max_context, 0, s))
     self._host_pos += 1
+
+  def _check_room(self) -> None:
+    if self._host_pos >= self.max_context:
+      raise RuntimeError(f"context full: position {self._host_pos} has no KV-cache row (max_context {self.max_context})")
 
   def gemv_launches(self) -> list:
     """(n_out rows streamed, n_in) of every GEMV launch of one step with the head, in launch order."""
@@ -365,8 +370,11 @@ class Transformer:
     return g
 
   def step(self, with_head: bool = True) -> None:
-    """Advance by one token on the device: reads tokens[pos]; with the head, writes tokens[pos+1]."""
+    """Advance by one token on the device: reads tokens[pos]; with the head, writes tokens[pos+1].
+    The host mirrors the device position and refuses a step that has no KV-cache row left (nothing is launched then)."""
+    self._check_room()
     if self.is_moe: return self._step_rows(with_head)
+    self._host_pos += 1
     if not self.use_graph: return self._enqueue_step(with_head)
     g = self._graphs.get(with_head)
     if g is None:
