@@ -165,3 +165,17 @@ if "gguf" in groups:
     if len(toks) >= 48: break
   out["prompt"], out["tokens"] = np.array([3, 14, 15, 92, 65, 35]), np.array(toks)
   save("gguf_llama_tiny", **out)
+
+if "mxgemm" in groups:
+  # The reference's one MXFP8 contraction that runs without AMD hardware: matmul_mx of examples/mlperf/models/gpt_oss.py:64-83
+  # (its portable branch: quantise-dequantise the activations per 32, dequantise the weight, bf16 matmul with fp32 accumulation).
+  from extra.gemm.cdna_asm_gemm import quantize_mxfp8
+  from examples.mlperf.models.gpt_oss import matmul_mx
+  rng = np.random.default_rng(500)
+  M, N, K = 6, 16, 96
+  x = (rng.standard_normal((M, K)) * np.array([0.05, 1.0, 1.0, 30.0, 1.0, 1.0])[:, None]).astype(np.float32)
+  w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+  xb = Tensor(x).cast(dtypes.bfloat16)
+  w_q, w_e8, _ = quantize_mxfp8(Tensor(w))
+  y = matmul_mx(xb, w_q, w_e8)
+  save("mxgemm", x_bf16=xb.float().numpy(), w=w, w_q=w_q.bitcast(dtypes.uint8).numpy(), w_e8=w_e8.numpy(), y=y.float().numpy())

@@ -195,7 +195,7 @@ def test_from_gguf_stream_identical_to_reference(golden):
   assert got == want
 
 
-@pytest.mark.parametrize("output", ["q6_k", "tied", "same"])
+@pytest.mark.parametrize("output", ["q6_k", "tied", "same", "bf16", "f32"])
 def test_from_gguf_output_head_variants(output):
   """Q6_K, tied (token_embd) and same-type output heads of a qwen2-family file against the oracle."""
   from tinygrad_b200 import gguf
@@ -214,7 +214,7 @@ def test_from_gguf_output_head_variants(output):
   prompt = [5, 17, 300, 2, 9]
   want = llm.Transformer(llm.Config(**kw, kv_dtype="float16"), w).generate(prompt, 16)
   m, _ = gguf.transformer_from_gguf(img)
-  assert m.config.qkv_bias and m.output_type == {"q6_k": 14, "tied": 1, "same": 8}[output]
+  assert m.config.qkv_bias and m.output_type == {"q6_k": 14, "tied": 1, "same": 8, "bf16": 30, "f32": 0}[output]
   got = []
   for tok in m.generate(prompt):
     got.append(tok)

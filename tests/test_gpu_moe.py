@@ -102,6 +102,26 @@ def test_grouped_gemm_matches_oracle():
   assert_close(moe.from_bf16_bits(got[:1024]), ref[:1024], tol=1e-2, what="grouped MXFP8 GEMM")
 
 
+def test_grouped_gemm_matches_reference_matmul_mx(golden):
+  """The contraction against the reference's own portable MXFP8 matmul (matmul_mx, examples/mlperf/models/gpt_oss.py:64-83):
+  its inputs, padded with zero rows / columns to the kernel's 256 / 256 / 128 granularity, as one expert group."""
+  from tinygrad_b200 import _lib, moe
+  from tinygrad_b200.runtime import DeviceBuffer
+  g = golden("mxgemm")
+  (M, K), N = g["x_bf16"].shape, g["w"].shape[0]
+  x, w = np.zeros((256, 128), np.float32), np.zeros((256, 128), np.float32)
+  x[:M, :K], w[:N, :K] = g["x_bf16"], g["w"]
+  xq, xe = moe.quantize_mxfp8(DeviceBuffer.from_numpy(moe.to_bf16_bits(x)), 256, 128, _lib.BF16)
+  wq, we = moe.quantize_mxfp8(DeviceBuffer.from_numpy(w), 256, 128, _lib.F32)
+  np.testing.assert_array_equal(wq.numpy()[:N, :K], g["w_q"]); np.testing.assert_array_equal(we.numpy()[:N, :K // 32], g["w_e8"])
+  off = DeviceBuffer.from_numpy(np.array([0, 256], np.int32))
+  c = DeviceBuffer.empty((256, 256), np.uint16, zero=True)
+  _lib.check(_lib.load().b200q_grouped_mxfp8_gemm(xq.ptr, xe.ptr, wq.ptr, we.ptr, off.ptr, 1, 256, 256, 128, c.ptr, None))
+  y = moe.from_bf16_bits(c.numpy())[:M, :N]
+  np.testing.assert_allclose(y, g["y"], rtol=2 ** -7, atol=1e-6)          # bf16: one unit in the last place (summation order)
+  assert (y == g["y"]).mean() > 0.9
+
+
 def test_moe_ffn_matches_composed_oracle():
   """route -> dispatch+quantise -> GEMM -> SwiGLU+quantise -> GEMM -> combine, against the same chain of oracle pieces."""
   from tinygrad_b200 import moe

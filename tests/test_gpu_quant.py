@@ -105,7 +105,7 @@ def test_linear_fp32_matches_oracle(tag, n_out, n_in, m):
   assert np.abs(y - ref).max() <= 5e-4 * np.abs(ref).max()
 
 
-@pytest.mark.parametrize("tag", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("tag", ["q4_0", "q8_0", "q6_k"])
 def test_linear_golden_from_reference(golden, tag):
   from tinygrad_b200 import quant
   from tinygrad_b200.runtime import DeviceBuffer

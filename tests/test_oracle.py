@@ -114,3 +114,43 @@ def test_greedy_token_stream_matches_reference(golden, name):
   cfg, w = _llm_from_golden(g)
   toks = llm.Transformer(cfg, w).generate([int(t) for t in g["prompt"]], len(g["tokens"]))
   assert toks == [int(t) for t in g["tokens"]]
+
+
+@pytest.mark.parametrize("tag", list(TAGS))
+def test_c_dequant_equals_numpy_restatement(golden, tag):
+  """The C restatement (used where the numpy one is too slow: full-size matrices, the timed CPU baseline) gives the same
+  bits as the numpy restatement, on the reference's golden blocks and on random ones."""
+  from oracle import cpu_gemv
+  typ, g = TAGS[tag], golden("dequant")
+  raw, n = g[f"{tag}_raw"], g[f"{tag}_f32"].size
+  np.testing.assert_array_equal(cpu_gemv.dequantize(raw, n, typ).view(np.uint32), g[f"{tag}_f32"].reshape(-1).view(np.uint32))
+  raw = synth.BLOCK_MAKERS[typ](16, 1024, np.random.default_rng(9))
+  np.testing.assert_array_equal(cpu_gemv.dequantize(raw, 16 * 1024, typ).view(np.uint32), gq.dequantize(raw, 16 * 1024, typ).view(np.uint32))
+
+
+@pytest.mark.parametrize("tag", list(TAGS))
+def test_c_gemv_matches_linear(golden, tag):
+  """The timed CPU baseline (oracle/qgemv_cpu.c) against `Linear` as the reference computed it (golden) and against the
+  numpy restatement on a larger random case."""
+  from oracle import cpu_gemv
+  typ, g = TAGS[tag], golden("linear")
+  n_out, n_in = (int(v) for v in g[f"{tag}_shape"])
+  for row, want in zip(g[f"{tag}_x32"], g[f"{tag}_y32"]):
+    np.testing.assert_allclose(cpu_gemv.qgemv(typ, g[f"{tag}_raw"], row, n_out, n_in), want, rtol=1e-5, atol=1e-5)
+  rng = np.random.default_rng(4)
+  raw, x = synth.BLOCK_MAKERS[typ](64, 2048, rng), rng.standard_normal(2048).astype(np.float32)
+  ref = llm.linear(x[None], gq.weight_matrix(raw, 64, 2048, typ))[0]
+  np.testing.assert_allclose(cpu_gemv.qgemv(typ, raw, x, 64, 2048), ref, rtol=1e-4, atol=1e-4 * float(np.abs(ref).max()))
+
+
+def test_mxfp8_matmul_matches_reference(golden):
+  """The reference's own runnable MXFP8 contraction (matmul_mx, examples/mlperf/models/gpt_oss.py:64-83) pins the oracle's
+  quantise -> dequantise -> matmul chain and the weight quantiser."""
+  g = golden("mxgemm")
+  w_q, w_e8 = mxfp8.quantize_mxfp8(g["w"])
+  np.testing.assert_array_equal(w_q, g["w_q"]); np.testing.assert_array_equal(w_e8, g["w_e8"])
+  x_q, x_e8 = mxfp8.quantize_mxfp8(g["x_bf16"])
+  y = mxfp8.to_bf16(mxfp8.mxfp8_matmul(x_q, x_e8, w_q, w_e8))
+  # bf16 output: at most one unit in the last place apart (fp32 summation order), most entries identical
+  np.testing.assert_allclose(y, g["y"], rtol=2 ** -7, atol=1e-6)
+  assert (y == g["y"]).mean() > 0.9

@@ -353,15 +353,24 @@ extern "C" size_t b200q_attn_scratch_bytes(int n_heads, int n_kv_heads, int head
   return ((size_t)n_heads * n_split * (head_dim + 4)) * sizeof(float) + (size_t)n_kv_heads * sizeof(unsigned);
 }
 
-extern "C" int b200q_attn_decode(const b200q_attn_args* a, void* stream) {
-  if (!a || !a->qkv || !a->k_cache || !a->v_cache || !a->rope || !a->pos || !a->out || !a->scratch) return B200Q_ERR_BAD_ARG;
+// Argument checks shared by both attention entry points (`scratch` is checked by the caller that needs it).
+static int attn_validate(const b200q_attn_args* a) {
+  if (!a || !a->qkv || !a->k_cache || !a->v_cache || !a->rope || !a->pos || !a->out) return B200Q_ERR_BAD_ARG;
   if (a->n_heads <= 0 || a->n_kv_heads <= 0 || a->n_heads % a->n_kv_heads || a->n_split <= 0 || a->max_context <= 0) return B200Q_ERR_BAD_ARG;
   if (a->head_dim <= 0 || a->head_dim > MAX_HD || a->head_dim % 8 || a->n_heads / a->n_kv_heads > MAX_REP) return B200Q_ERR_BAD_SHAPE;
   if (a->rope_dim < 0 || a->rope_dim > a->head_dim || a->rope_dim % 2) return B200Q_ERR_BAD_SHAPE;
   if (a->kv_dtype != B200Q_F16 && a->kv_dtype != B200Q_F32) return B200Q_ERR_BAD_ARG;
   if (a->xq_out && (a->head_dim != 128 || ((uintptr_t)a->xq_out & 15))) return B200Q_ERR_BAD_SHAPE;   // one 128-wide group per head
-  if (((uintptr_t)a->k_cache | (uintptr_t)a->v_cache | (uintptr_t)a->qkv | (uintptr_t)a->out | (uintptr_t)a->scratch) & 15) return B200Q_ERR_MISALIGNED;
+  if (((uintptr_t)a->k_cache | (uintptr_t)a->v_cache | (uintptr_t)a->qkv | (uintptr_t)a->out) & 15) return B200Q_ERR_MISALIGNED;
   if ((int64_t)a->n_split * ATTN_CHUNK < a->max_context) return B200Q_ERR_BAD_SHAPE;   // the slices must cover the whole cache
+  return B200Q_OK;
+}
+
+extern "C" int b200q_attn_decode(const b200q_attn_args* a, void* stream) {
+  const int rc = attn_validate(a);
+  if (rc != B200Q_OK) return rc;
+  if (!a->scratch) return B200Q_ERR_BAD_ARG;
+  if ((uintptr_t)a->scratch & 15) return B200Q_ERR_MISALIGNED;
   int n_rep = a->n_heads / a->n_kv_heads;
   dim3 grid(a->n_kv_heads, a->n_split), block(n_rep * 32);
   bool pdl = (a->flags & B200Q_FLAG_PDL) != 0;
@@ -411,7 +420,9 @@ extern "C" int b200q_attn_decode_static(const b200q_attn_args* a, void* stream) 
   if (!a) return B200Q_ERR_BAD_ARG;
   const size_t need = b200q_attn_scratch_bytes(a->n_heads, a->n_kv_heads, a->head_dim, a->n_split);
   if (need == 0) return B200Q_ERR_BAD_ARG;
-  if (need > ATTN_STATIC_SCRATCH_BYTES) return B200Q_ERR_TOO_LARGE;   // heads x slices x (head_dim + 4) floats must fit the built-in array
+  if (need > ATTN_STATIC_SCRATCH_BYTES) return B200Q_ERR_TOO_LARGE;
+  const int rc = attn_validate(a);      // before anything is put on the stream
+  if (rc != B200Q_OK) return rc;   // heads x slices x (head_dim + 4) floats must fit the built-in array
   int dev = -1;
   B200Q_CHECK_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= MAX_DEVICES) return B200Q_ERR_TOO_LARGE;

@@ -115,6 +115,12 @@ def gemv_dense(w, w_dtype: int, n_out: int, n_in: int, x, y, m: int = 1, x_dtype
                                      ptr_of(residual), ptr_of(y), y_dtype, flags, stream_ptr(stream)))
 
 
+def _to_bf16_bits(a: np.ndarray) -> np.ndarray:
+  """fp32 -> bf16 bit patterns, round to nearest even (tinygrad/dtype.py:222-226)."""
+  u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+  return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
 class DenseWeight:
   """A [n_out, n_in] weight kept as plain values on the device.  F32 / F16 / BF16 tensors stay as stored; Q6_K blocks are
   dequantised once to fp16 (the cast the reference applies to every loaded tensor, tinygrad/llm/model.py:376)."""
@@ -123,7 +129,10 @@ class DenseWeight:
     if ggml_type in _DENSE_DT:
       self.dtype, npdt = _DENSE_DT[ggml_type]
       a = np.ascontiguousarray(raw)
-      a = a.view(npdt) if a.dtype == np.uint8 else a.astype(npdt) if ggml_type != GGML_BF16 else a.view(np.uint16)
+      if a.dtype == np.uint8: a = a.view(npdt)                     # raw tensor bytes
+      elif ggml_type != GGML_BF16: a = a.astype(npdt)
+      elif a.dtype == np.uint16: pass                              # bf16 bit patterns
+      else: a = _to_bf16_bits(a.astype(np.float32))                # values (GGUFTensor.numpy widens BF16 to fp32: exact round trip)
       if a.size != n_out * n_in: raise ValueError(f"weight has {a.size} values, expected {n_out}x{n_in}")
       self.buf = DeviceBuffer.from_numpy(a.reshape(n_out, n_in))
     elif ggml_type in GGML_QUANT:

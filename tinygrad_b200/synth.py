@@ -137,7 +137,7 @@ def write_gguf(kv: dict, tensors: list, version: int = 3) -> bytes:
 
 
 def dense_model_gguf(cfg, ggml_type: int = Q4_0, seed: int = 0, arch: str = "llama", embd_std: float = 0.02, output: str = "same") -> bytes:
-  """A random-init dense model as a GGUF file image.  output: "same" (head in ggml_type), "f16", "q6_k", or "tied" (no output.weight).
+  """A random-init dense model as a GGUF file image.  output: "same" (head in ggml_type), "f16", "bf16", "f32", "q6_k", or "tied" (no output.weight).
   For arch "llama" the q/k rows are stored as given; the loader applies the family's RoPE row permutation."""
   sd = dense_model_raw(cfg, ggml_type, seed=seed, embd_std=embd_std)
   shapes = {n + ".weight": (o, i) for n, o, i in linear_names(cfg)}
@@ -153,6 +153,9 @@ def dense_model_gguf(cfg, ggml_type: int = Q4_0, seed: int = 0, arch: str = "lla
       if output == "tied": continue
       rng = np.random.default_rng(name_seed("output", seed))
       if output == "q6_k": arr, typ = q6_k_blocks(cfg.vocab_size, cfg.dim, rng), Q6_K
+      elif output == "f32": arr, typ = rng.standard_normal((cfg.vocab_size, cfg.dim), dtype=np.float32) * 0.05, 0
+      elif output == "bf16":      # bf16 bit patterns (type 30): the upper halves of random fp32 values
+        arr, typ = ((rng.standard_normal((cfg.vocab_size, cfg.dim), dtype=np.float32) * 0.05).view(np.uint32) >> 16).astype(np.uint16), 30
       else: arr, typ = (rng.standard_normal((cfg.vocab_size, cfg.dim), dtype=np.float32) * 0.05).astype(np.float16), 1
       tensors.append((name, (cfg.vocab_size, cfg.dim), typ, arr))
     elif name in shapes: tensors.append((name, shapes[name], ggml_type, arr))
