@@ -226,6 +226,59 @@ int b200q_argmax_advance(const float* device_logits, int n, int32_t* device_toke
 /* *pos += 1 (a prompt token whose logits are not needed); stops at max_context like b200q_argmax_advance */
 int b200q_advance(int32_t* device_pos, int max_context, int flags, void* stream);
 
+/* ---- one whole decode step as one persistent kernel ------------------------------------------------------------------
+ * The forward pass of `Transformer.forward` for one new token (tinygrad/llm/model.py:358-364; per block :144-151,167-198,137)
+ * followed by the greedy sample: what the reference replays as a captured CUDA graph of ~13 kernels per block
+ * (tinygrad/engine/jit.py:241-291).  One cooperative kernel, one CTA per SM, walks every stage itself: the packed weights of
+ * every Linear are dealt to the CTAs as equal contiguous byte ranges and streamed through per-warp rings of bulk-async copies
+ * that keep running across the stage boundaries; stages meet at a grid barrier; attention runs on (KV head, 64-position slice)
+ * units in between.  Dense llama / qwen2 family only: all Linears (the vocabulary head included) in one of Q4_0 / Q8_0.
+ * Reads tokens[*pos]; with_head != 0: logits [vocab] and tokens[*pos + 1] = argmax; *pos += 1.
+ * b200q_decode_layer: the device pointers of one block (weights from b200q_repack: q | k | v packed back to back, gate / up
+ * interleaved).  The array of them lives in DEVICE memory.
+ * workspace: b200q_decode_step_workspace_bytes(args) bytes, 256-byte aligned, zero-filled once before the first step (and
+ * again after a step that raised the status word: its counters are then out of step).  It carries state from step to step:
+ * one workspace per model instance, steps of one instance stream-ordered.
+ * Returns B200Q_ERR_UNSUPPORTED / B200Q_ERR_TOO_LARGE (also from b200q_decode_step_supported, which launches nothing) for shapes
+ * this kernel does not take (head_dim not a multiple of 32 or above 128, more than 8 query heads per KV head, ...): the
+ * per-launch entry points above cover those. */
+typedef struct b200q_decode_layer {
+  const void* qkv;          /* packed [q_dim + 2 kv_dim, dim] */
+  const void* qkv_bias;     /* fp16 [q_dim + 2 kv_dim] or NULL */
+  const void* attn_output;  /* packed [dim, q_dim] */
+  const void* gate_up;      /* packed, interleaved, [2 hidden_dim, dim] */
+  const void* ffn_down;     /* packed [dim, hidden_dim] */
+  const void* attn_norm;    /* fp16 [dim] */
+  const void* ffn_norm;     /* fp16 [dim] */
+  void* k_cache;            /* [n_kv_heads][max_context][head_dim], kv_dtype */
+  void* v_cache;
+} b200q_decode_layer;
+typedef struct b200q_decode_step_args {
+  const b200q_decode_layer* layers;   /* device array [n_layers] */
+  int n_layers, qtype, dim, hidden_dim, n_heads, n_kv_heads, head_dim, rope_dim, max_context;
+  int vocab;                /* rows of `output` */
+  int embd_vocab;           /* rows of token_embd */
+  int kv_dtype;             /* B200Q_F16 | B200Q_F32 */
+  float norm_eps;
+  const void* token_embd;   /* fp16 [embd_vocab, dim] */
+  const void* output_norm;  /* fp16 [dim] */
+  const void* output;       /* packed [vocab, dim]; may be NULL when with_head == 0 */
+  const float* rope;        /* [max_context][rope_dim] cos || sin */
+  int32_t* tokens;          /* [max_context + 1] */
+  int32_t* pos;             /* scalar */
+  float* x;                 /* [dim] residual stream */
+  float* qkv;               /* [q_dim + 2 kv_dim] */
+  float* attn;              /* [q_dim] */
+  float* act;               /* [hidden_dim] */
+  float* logits;            /* [vocab] */
+  void* workspace;
+  size_t workspace_bytes;
+  int with_head;
+} b200q_decode_step_args;
+int b200q_decode_step_supported(const b200q_decode_step_args* args);
+size_t b200q_decode_step_workspace_bytes(const b200q_decode_step_args* args);
+int b200q_decode_step(const b200q_decode_step_args* args, void* stream);
+
 /* ---- batched / prefill linear on tcgen05 tensor cores --------------------------------
  * C[m, n] fp32 = A[m, k] fp16 x W[n, k]^T fp16 with fp32 accumulation in tensor memory: `Linear.__call__` for more than
  * one activation row (tinygrad/nn/__init__.py:177), as the prefill chunks of tinygrad/llm/model.py:464-481 need it.

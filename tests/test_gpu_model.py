@@ -147,7 +147,9 @@ def test_attention_at_the_last_cache_row_and_refusal_past_it():
     kk, vv = np.repeat(kr.astype(np.float32), n_heads // n_kv, axis=0), np.repeat(vr.astype(np.float32), n_heads // n_kv, axis=0)
     sc = np.einsum("hd,hpd->hp", llm.apply_rope(q, fc[pos:pos + 1])[0, :, 0], kk) / np.float32(np.sqrt(hd))
     assert_close(out.numpy(), np.einsum("hp,hpd->hd", llm.softmax(sc), vv).reshape(-1), tol=2e-3, what="attention at the last row")
-    np.testing.assert_array_equal(d["kc"].numpy()[:, pos], kr[:, pos])
+    # the rotation may be contracted into FMAs on the device: the appended row is the oracle's up to one fp16 rounding step
+    np.testing.assert_allclose(d["kc"].numpy()[:, pos].astype(np.float32), kr[:, pos].astype(np.float32), rtol=1e-3, atol=1e-6)
+    np.testing.assert_array_equal(d["vc"].numpy()[:, pos], vr[:, pos])
     assert runtime.device_status() == 0
   # token table of max_context + 1 entries: the arg-max writes entry max_context at most
   toks, logits = DeviceBuffer.from_numpy(np.arange(9, dtype=np.int32)), DeviceBuffer.from_numpy(np.array([0.0, 3.0, 1.0], np.float32))

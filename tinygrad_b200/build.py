@@ -4,7 +4,7 @@ import os, pathlib, shutil, subprocess, sys
 PKG = pathlib.Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libb200q.so"
-SOURCES = ["api.cu", "quant_pack.cu", "gemv.cu", "decode.cu", "mxfp8.cu", "mxfp8_gemm.cu", "tc_gemm.cu", "dense.cu", "prefill.cu"]
+SOURCES = ["api.cu", "quant_pack.cu", "gemv.cu", "decode.cu", "decode_step.cu", "mxfp8.cu", "mxfp8_gemm.cu", "tc_gemm.cu", "dense.cu", "prefill.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
               "-Xcompiler", "-fPIC", "-cudart", "shared"]
 
@@ -17,7 +17,7 @@ def nvcc_path() -> str:
 
 def build_lib(force: bool = False, verbose: bool = False) -> pathlib.Path:
   srcs = [CSRC / s for s in SOURCES]
-  deps = srcs + [CSRC / "common.cuh", CSRC / "actquant.cuh", CSRC / "mxq.cuh", PKG.parent / "include" / "b200q.h"]
+  deps = srcs + [CSRC / "common.cuh", CSRC / "actquant.cuh", CSRC / "mxq.cuh", CSRC / "qgemv_core.cuh", PKG.parent / "include" / "b200q.h"]
   if not force and LIB.exists() and all(LIB.stat().st_mtime >= d.stat().st_mtime for d in deps): return LIB
   cmd = [nvcc_path(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", str(LIB), *map(str, srcs)]
   r = subprocess.run(cmd, capture_output=True, text=True)

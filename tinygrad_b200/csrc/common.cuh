@@ -27,6 +27,7 @@ struct PerDeviceFlag {
 };
 // reads and clears the status word of the decode-step kernels (decode.cu); folded into b200q_status_read_clear
 int b200q_decode_status_take(int* status);
+int b200q_decode_step_status_take(int* status);   // the same for the whole-step kernel (decode_step.cu)
 // current device index, or -1 (with the CUDA error recorded) if it cannot be had or is past the tables
 int b200q_current_device();
 // SM count of the current device (cached per device); 0 on error
