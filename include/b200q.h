@@ -168,6 +168,13 @@ size_t b200q_xq_bytes(int n);
 int b200q_gemv_dense(const void* w, int w_dtype, int n_out, int n_in, int m, const void* x, int x_dtype, const void* norm_weight,
                      float norm_eps, const void* bias, const void* residual, void* y, int y_dtype, int flags, void* stream);
 
+/* The Linear as tinygrad's own runtime launches it (the in-graph seam, tinygrad/tensor.py:390-396: `Tensor.custom_kernel` with a
+ * prebuilt PROGRAM, precedent extra/gemm/moe_gemm.py:30-48).  The kernels b200q_tg_gemv_q4_0 / _q8_0(float* y, const float* x,
+ * const uint8_t* w_packed, const int32_t* meta) take pointers only (tinygrad passes one per tensor, tinygrad/runtime/ops_cuda.py:18-24),
+ * read meta = {n_out, n_in, m} from the device, use static shared memory, and ship as tinygrad_b200/tg_kernels.cubin; block 256, grid
+ * (ceil(ceil(n_out / 16) / 8), m).  This entry launches the same kernels with that geometry from the library (parity tests). */
+int b200q_tg_gemv(int qtype, float* y, const float* x, const void* w_packed, const int32_t* meta_dev, int n_out, int m, void* stream);
+
 /* ---- decode-step kernels -------------------------------------------------
  * Token embedding lookup to the fp32 residual stream:
  * `token_embd(tokens).float()` (tinygrad/llm/model.py:359).  The token id is read
@@ -274,6 +281,10 @@ typedef struct b200q_decode_step_args {
   void* workspace;
   size_t workspace_bytes;
   int with_head;
+  int profile_stamps;       /* diagnostics, with `profile`: time stamps kept per CTA */
+  void* profile;            /* NULL, or device uint64 [number of SMs][profile_stamps]: thread 0 of every CTA stores the global nanosecond
+                               timer at each stage boundary (start; per stage: input staged, tiles multiplied, rows finished, barrier
+                               passed; after a QKV stage also: attention done, barrier passed) */
 } b200q_decode_step_args;
 int b200q_decode_step_supported(const b200q_decode_step_args* args);
 size_t b200q_decode_step_workspace_bytes(const b200q_decode_step_args* args);
@@ -350,6 +361,14 @@ int b200q_moe_route(const float* logits, int n_tokens, int n_experts, int k, int
  * rows for one destination rank are one contiguous run) and the per-expert row counts [n_experts] as an optional output. */
 int b200q_moe_route_pad(const float* logits, int n_tokens, int n_experts, int k, int mode, int pad, int32_t* topi, float* weights,
                         int32_t* dest_row, int32_t* off, int32_t* counts, void* scratch, void* stream);
+/* The gating of tinygrad's own mixture-of-experts block (tinygrad/llm/model.py:110-128): gating = 1 softmax, 2 sigmoid, 3 softmax over
+ * the selected logits, 4 sqrt(softplus) (`ExpertGating`, model.py:9-13); sel_bias (fp32 [n_experts] or NULL) is added for the selection
+ * only (exp_probs_b); the k experts are listed in ascending order of rank with the lower index winning ties (`pairwise_topk`,
+ * model.py:35-41); weights = the scores of the selected experts, renormalised over the k if `normalize`, times `scale`
+ * (routed_scaling_factor).  The caller applies the reference's shortcut (softmax + normalize + no bias == gating 3, model.py:116-117).
+ * Tables and scratch as b200q_moe_route_pad. */
+int b200q_moe_route_gating(const float* logits, const float* sel_bias, int n_tokens, int n_experts, int k, int gating, int normalize, float scale,
+                           int pad, int32_t* topi, float* weights, int32_t* dest_row, int32_t* off, int32_t* counts, void* scratch, void* stream);
 /* Rows of row_bytes bytes (a multiple of 4) moved through an index table: gather = 0: dst[idx[i]] = src[i]; gather = 1:
  * dst[i] = src[idx[i]]; negative entries are skipped.  The regrouping step on both sides of the expert-parallel exchange
  * (`dispatch` / `combine` across ranks, extra/gemm/moe_routing.py:124-131). */

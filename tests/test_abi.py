@@ -32,7 +32,8 @@ def test_header_is_plain_c_and_structs_match_ctypes(tmp_path):
   hdr = ROOT / "include" / "b200q.h"
   subprocess.run([cc, "-std=c11", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", str(hdr)], check=True)
   subprocess.run([cxx, "-std=c++17", "-fsyntax-only", "-x", "c++", str(hdr)], check=True)
-  structs = {"b200q_gemv_args": _lib.GemvArgs, "b200q_attn_args": _lib.AttnArgs}
+  structs = {"b200q_gemv_args": _lib.GemvArgs, "b200q_attn_args": _lib.AttnArgs, "b200q_decode_layer": _lib.DecodeLayer,
+             "b200q_decode_step_args": _lib.DecodeStepArgs}
   lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{hdr}"', 'int main(void) {']
   for cname, ct in structs.items():
     lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')

@@ -28,14 +28,16 @@ def _cfgs(g):
 
 
 @pytest.mark.parametrize("name", ["llm_small_kv32", "llm_q8_bias_kv32", "llm_wide_kv32"])
-@pytest.mark.parametrize("mode", ["graph_pdl", "eager"])
+@pytest.mark.parametrize("mode", ["step", "graph_pdl", "eager"])
 def test_greedy_stream_identical_to_reference(golden, name, mode):
-  """Identical greedy token stream to tinygrad's own run of the same seeded model (64 tokens where the fixture holds 64)."""
+  """Identical greedy token stream to tinygrad's own run of the same seeded model (64 tokens where the fixture holds 64), through the
+  whole-step kernel (the models whose head_dim it takes), the chained launches replayed as a graph, and the same launches eagerly."""
   from tinygrad_b200.model import Transformer
   g = golden(name)
   cfg, _, typ = _cfgs(g)
   sd = {k[2:]: g[k] for k in g.files if k.startswith("w:")}
-  m = Transformer(cfg, sd, ggml_type=typ, use_pdl=(mode == "graph_pdl"), use_graph=(mode == "graph_pdl"))
+  m = Transformer(cfg, sd, ggml_type=typ, use_pdl=(mode == "graph_pdl"), use_graph=(mode == "graph_pdl"), engine=None if mode == "step" else "chain")
+  assert m.engine == ("step" if mode == "step" and cfg.head_dim % 32 == 0 else "chain")
   want = [int(t) for t in g["tokens"]]
   got = []
   for tok in m.generate([int(t) for t in g["prompt"]]):
@@ -46,7 +48,9 @@ def test_greedy_stream_identical_to_reference(golden, name, mode):
 
 @pytest.mark.parametrize("typ,kv,hd,handover", [(2, "float16", 64, None), (8, "float16", 64, None), (2, "float32", 64, None),
                                                  (2, "float16", 128, True), (8, "float16", 128, True), (2, "float16", 128, False),
-                                                 (2, "float16", 128, None), (2, "float16", 128, "gateup_down,down_qkv")])
+                                                 (2, "float16", 128, None), (2, "float16", 128, "gateup_down,down_qkv"),
+                                                 (2, "float16", 64, "step"), (8, "float16", 64, "step"), (2, "float32", 64, "step"),
+                                                 (2, "float16", 128, "step"), (8, "float32", 128, "step"), (8, "float16", 32, "step")])
 def test_mid_size_model_matches_oracle(typ, kv, hd, handover):
   """A model too big for the reference's interpreter: logits within tolerance of the oracle at every step,
   identical greedy stream, and KV-prefix reuse gives the same continuation."""
@@ -57,8 +61,11 @@ def test_mid_size_model_matches_oracle(typ, kv, hd, handover):
   sd = synth.dense_model_raw(cfg, typ, seed=11, embd_std=0.3, scale_std=0.02 if typ == 2 else 0.0015)   # weights of rms ~0.1 either way
   prompt = [int(t) for t in np.random.default_rng(1).integers(0, 2000, 70)]
   want, want_logits = llm.Transformer(llm.Config(**kw), _oracle_weights(cfg, sd, typ)).generate(prompt, 24, keep_logits=True)
-  m = Transformer(cfg, sd, ggml_type=typ, handover=handover)
-  if handover is not None: assert m.handover == bool(handover)
+  if handover == "step":      # the whole-step kernel instead of the chained launches
+    m = Transformer(cfg, sd, ggml_type=typ, engine="step")
+  else:
+    m = Transformer(cfg, sd, ggml_type=typ, handover=handover, engine="chain")
+    if handover is not None: assert m.handover == bool(handover)
   got = []
   for i, tok in enumerate(m.generate(list(prompt))):
     # logits after several blocks: the 15-bit activation quantisation (like the fp16 rounding of the KV cache, which moves

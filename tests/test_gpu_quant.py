@@ -227,3 +227,22 @@ def test_dense_fused_norm_and_residual():
                    norm_eps=1e-5, residual=dy)
   ref = res + llm.linear(llm.rmsnorm(x[None], nw, 1e-5), w.astype(np.float32))[0]
   assert np.abs(dy.numpy() - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("tag,n_out,n_in,m", [("q4_0", 4096, 4096, 1), ("q8_0", 200, 3584, 3), ("q4_0", 48, 14336 + 2048, 2)])
+def test_in_graph_kernels_match_oracle(tag, n_out, n_in, m):
+  """The entry kernels tinygrad's runtime launches (tinygrad_b200/tg_op.py), run here with the same launch geometry through the library."""
+  from tinygrad_b200 import _lib, quant, tg_op
+  from tinygrad_b200.runtime import DeviceBuffer
+  typ = TAGS[tag]
+  rng = np.random.default_rng(n_out)
+  raw, x = synth.BLOCK_MAKERS[typ](n_out, n_in, rng), rng.standard_normal((m, n_in)).astype(np.float32)
+  w = quant.repack(raw, n_out, n_in, typ)
+  y = DeviceBuffer.from_numpy(np.full((m, n_out), np.nan, np.float32))
+  meta = DeviceBuffer.from_numpy(np.array([n_out, n_in, m], np.int32))
+  (gx, gy, _), _ = tg_op.launch_dims(n_out, m)
+  assert gx == -(-(-(-n_out // 16)) // 8) and gy == m
+  _lib.check(_lib.load().b200q_tg_gemv(typ, y.ptr, DeviceBuffer.from_numpy(x).ptr, w.buf.ptr, meta.ptr, n_out, m, None))
+  ref = llm.linear(x, gq.weight_matrix(raw, n_out, n_in, typ))
+  assert_close(y.numpy(), ref, tol=1e-2)
+  assert np.abs(y.numpy() - ref).max() <= 5e-4 * np.abs(ref).max()

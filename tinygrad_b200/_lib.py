@@ -26,6 +26,19 @@ class AttnArgs(Structure):
               ("max_context", c_int), ("n_split", c_int), ("flags", c_int), ("xq_out", c_void_p)]
 
 
+class DecodeLayer(Structure):
+  _fields_ = [("qkv", c_void_p), ("qkv_bias", c_void_p), ("attn_output", c_void_p), ("gate_up", c_void_p), ("ffn_down", c_void_p),
+              ("attn_norm", c_void_p), ("ffn_norm", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p)]
+
+
+class DecodeStepArgs(Structure):
+  _fields_ = [("layers", c_void_p), ("n_layers", c_int), ("qtype", c_int), ("dim", c_int), ("hidden_dim", c_int), ("n_heads", c_int),
+              ("n_kv_heads", c_int), ("head_dim", c_int), ("rope_dim", c_int), ("max_context", c_int), ("vocab", c_int), ("embd_vocab", c_int),
+              ("kv_dtype", c_int), ("norm_eps", c_float), ("token_embd", c_void_p), ("output_norm", c_void_p), ("output", c_void_p),
+              ("rope", c_void_p), ("tokens", c_void_p), ("pos", c_void_p), ("x", c_void_p), ("qkv", c_void_p), ("attn", c_void_p),
+              ("act", c_void_p), ("logits", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("with_head", c_int), ("profile_stamps", c_int), ("profile", c_void_p)]
+
+
 # name -> (restype, argtypes); every symbol include/b200q.h declares
 SIGNATURES = {
   "b200q_strerror": (c_char_p, [c_int]),
@@ -61,6 +74,7 @@ SIGNATURES = {
   "b200q_repack": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
   "b200q_dequant_packed": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
   "b200q_gemv": (c_int, [POINTER(GemvArgs), c_void_p]),
+  "b200q_tg_gemv": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
   "b200q_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
   "b200q_xq_bytes": (c_size_t, [c_int]),
   "b200q_attn_min_split": (c_int, [c_int]),
@@ -68,6 +82,9 @@ SIGNATURES = {
   "b200q_attn_decode": (c_int, [POINTER(AttnArgs), c_void_p]),
   "b200q_attn_decode_static_capacity": (c_size_t, []),
   "b200q_attn_decode_static": (c_int, [POINTER(AttnArgs), c_void_p]),
+  "b200q_decode_step_supported": (c_int, [POINTER(DecodeStepArgs)]),
+  "b200q_decode_step_workspace_bytes": (c_size_t, [POINTER(DecodeStepArgs)]),
+  "b200q_decode_step": (c_int, [POINTER(DecodeStepArgs), c_void_p]),
   "b200q_argmax_scratch_bytes": (c_size_t, []),
   "b200q_argmax_advance": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]),
   "b200q_advance": (c_int, [c_void_p, c_int, c_int, c_void_p]),
@@ -92,6 +109,8 @@ SIGNATURES = {
   "b200q_moe_rows_max": (c_int, [c_int, c_int, c_int]),
   "b200q_moe_route": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
   "b200q_moe_route_pad": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+  "b200q_moe_route_gating": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_void_p]),
   "b200q_permute_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int, c_void_p]),
   "b200q_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
   "b200q_mx_status_read_clear": (c_int, [POINTER(c_int)]),

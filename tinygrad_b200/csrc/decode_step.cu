@@ -33,6 +33,7 @@ constexpr int DS_MAX_TILES = 512;     // row tiles the range of one CTA may touc
 constexpr int DS_CHUNK = 64;          // positions per attention unit
 constexpr int DS_MAX_REP = 8;         // query heads per KV head
 constexpr int DS_MAX_DEPTH = 4;       // ring slots per warp
+constexpr int DS_SMEM_BUDGET = 226 * 1024;   // dynamic shared memory: the 227 KB a CTA can opt into, less the kernel's static variables
 constexpr int DS_GRID_SPIN = 1 << 21; // polls of a grid-level wait before it gives up (each poll is an L2 round trip)
 
 struct DsParams {
@@ -53,6 +54,7 @@ struct DsParams {
   float* cand_val; int* cand_idx;    // [grid] arg-max candidates
   int with_head, depth;
   int rec_off, attn_off, wred_off, misc_off;     // shared-memory plan (bytes)
+  unsigned long long* prof; int prof_n;          // optional: [grid][prof_n] nanosecond stamps of thread 0 at the stage boundaries
 };
 
 enum { K_QKV = 0, K_O = 1, K_GU = 2, K_DOWN = 3, K_HEAD = 4 };
@@ -176,6 +178,14 @@ template <> struct KvT<float> {
   static __device__ __forceinline__ float get(const float* p) { return *p; }
   static __device__ __forceinline__ float cast(float v) { return v; }
 };
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// diagnostics: thread 0 of every CTA notes the time at each stage boundary (the host reads them to see where a step's time goes)
+#define DS_STAMP() do { if (p.prof && threadIdx.x == 0 && n_stamp < p.prof_n) p.prof[(size_t)blockIdx.x * p.prof_n + n_stamp++] = global_ns(); } while (0)
 
 __device__ __forceinline__ void argmax_combine2(float& v, int& i, float ov, int oi) {
   if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
@@ -383,6 +393,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
   for (int s = 0; s < p.depth; s++) stream_issue<QT>(ws, p, n_ph, cta, n_ctas, warp, lane, ring_u, bars_u);
   int c_slot = 0, c_par = 0, consumed = 0;       // consumer side of the ring
   bool live = true;
+  int n_stamp = 0;
+  DS_STAMP();
 
   for (int ph = 0; ph < n_ph && live; ph++) {
     const Stage f = stage_of(p, ph);
@@ -418,6 +430,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
     const int rt_first = rt;
     if (lane == 0) { wt_first[warp] = rt_first; wt_n[warp] = w1 > w0 ? (w1 - 1) / f.KG - rt_first + 1 : 0; }
     __syncthreads();                              // record complete
+    DS_STAMP();
     float rs = 1.f;
     if (norm_w) {
       float tot = 0.f;
@@ -456,6 +469,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
       }
     }
     __syncthreads();
+    DS_STAMP();
     if (*s_abort) { live = false; break; }
     // ---- finish the CTA's row tiles: thread (tile, row), 64 tiles per pass.  Tiles cut by a CTA boundary: the CTA holding the
     // tile's first atom finishes it, the others leave their partial sums in global memory behind a flag.
@@ -528,7 +542,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
         }
       }
     }
+    __syncthreads();
+    DS_STAMP();
     if (!grid_barrier(p, bar_target, s_abort)) { live = false; break; }
+    DS_STAMP();
     // ---- attention between the QKV and the output projection
     if (f.kind == K_QKV) {
       bool first = true;
@@ -537,7 +554,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
         attention_unit<KV>(p, L, pos, kvh, slice, n_slices, first, asmem);
         __syncthreads();
       }
+      DS_STAMP();
       if (!grid_barrier(p, bar_target, s_abort)) { live = false; break; }
+      DS_STAMP();
     }
   }
 
@@ -583,7 +602,7 @@ int launch_decode_step(const DsParams& p, int grid, size_t smem, cudaStream_t st
   const int dev = b200q_current_device();
   if (dev < 0) return B200Q_ERR_CUDA;
   if (!attr_set.test(dev)) {
-    B200Q_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DS_SMEM_BUDGET));
     attr_set.set(dev);
   }
   cudaLaunchConfig_t cfg = {};
@@ -641,7 +660,7 @@ int plan_decode_step(const b200q_decode_step_args* a, DsPlan& pl) {
   const size_t attn = (((size_t)2 * DS_CHUNK * (a->head_dim + vec) * esz + (size_t)n_rep * (a->head_dim + DS_CHUNK + 2) * sizeof(float)) + 127) & ~(size_t)127;
   const size_t wred = (size_t)DS_WARPS * DS_MAXT * 16 * sizeof(float);
   const size_t misc = (size_t)DS_WARPS * DS_MAX_DEPTH * 8 + 5 * DS_WARPS * 4 + 16 + 16;
-  const size_t fixed = rec + attn + wred + misc, budget = 227 * 1024;
+  const size_t fixed = rec + attn + wred + misc, budget = DS_SMEM_BUDGET;
   if (fixed + (size_t)2 * DS_WARPS * tb > budget) return B200Q_ERR_TOO_LARGE;
   int depth = (int)((budget - fixed) / ((size_t)DS_WARPS * tb));
   pl.depth = depth > DS_MAX_DEPTH ? DS_MAX_DEPTH : depth;
@@ -696,6 +715,7 @@ extern "C" int b200q_decode_step(const b200q_decode_step_args* a, void* stream) 
   p.cand_val = (float*)(ws + pl.ws_cand); p.cand_idx = (int*)(ws + pl.ws_cand + (size_t)pl.grid * 4);
   p.with_head = a->with_head ? 1 : 0; p.depth = pl.depth;
   p.rec_off = pl.rec_off; p.attn_off = pl.attn_off; p.wred_off = pl.wred_off; p.misc_off = pl.misc_off;
+  p.prof = (unsigned long long*)a->profile; p.prof_n = a->profile ? a->profile_stamps : 0;
   const bool f16 = a->kv_dtype == B200Q_F16;
   if (a->qtype == B200Q_Q4_0) return f16 ? launch_decode_step<B200Q_Q4_0, __half>(p, pl.grid, pl.smem, (cudaStream_t)stream)
                                          : launch_decode_step<B200Q_Q4_0, float>(p, pl.grid, pl.smem, (cudaStream_t)stream);

@@ -140,6 +140,74 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int n_tokens
   }
 }
 
+
+// The gating of tinygrad's own MoE block (tinygrad/llm/model.py:110-128), one warp per token:
+//   scores = logits (SOFTMAX_WEIGHT) | softmax(logits) | sigmoid(logits) | sqrt(softplus(logits));
+//   sel    = the k best of scores (+ sel_bias), listed in ascending order, the lower expert index ranking higher on ties
+//            (`pairwise_topk`, model.py:35-41);
+//   probs  = scores[sel]; SOFTMAX_WEIGHT: softmax over the k; normalize: / sum; times `scale`.
+// The reference's own shortcut is applied by the caller: SOFTMAX with normalize and no bias is run as SOFTMAX_WEIGHT (model.py:116-117).
+enum { GATE_SOFTMAX = 1, GATE_SIGMOID = 2, GATE_SOFTMAX_WEIGHT = 3, GATE_SQRT_SOFTPLUS = 4 };     // ExpertGating, model.py:9-13
+
+__global__ void route_gating_kernel(const float* __restrict__ logits, const float* __restrict__ sel_bias, int n_tokens, int n_experts, int k, int gating,
+                                    int normalize, float scale, int32_t* __restrict__ topi, float* __restrict__ weights) {
+  const int lane = threadIdx.x & 31;
+  const int tok = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (tok >= n_tokens) return;
+  float sc[MAX_E_PER_LANE], key[MAX_E_PER_LANE];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MAX_E_PER_LANE; i++) {
+    const int e = i * 32 + lane;
+    sc[i] = e < n_experts ? logits[(size_t)tok * n_experts + e] : -INFINITY;
+    mx = fmaxf(mx, sc[i]);
+  }
+  if (gating == GATE_SOFTMAX) {
+    mx = warp_max(mx);
+    float denom = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; i++) { if (i * 32 + lane < n_experts) { sc[i] = expf(sc[i] - mx); denom += sc[i]; } }
+    denom = warp_sum(denom);
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; i++) if (i * 32 + lane < n_experts) sc[i] /= denom;
+  } else if (gating == GATE_SIGMOID) {
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; i++) if (i * 32 + lane < n_experts) sc[i] = 1.f / (1.f + expf(-sc[i]));
+  } else if (gating == GATE_SQRT_SOFTPLUS) {
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; i++) if (i * 32 + lane < n_experts) sc[i] = sqrtf(sc[i] > 20.f ? sc[i] : log1pf(expf(sc[i])));
+  }
+#pragma unroll
+  for (int i = 0; i < MAX_E_PER_LANE; i++) {
+    const int e = i * 32 + lane;
+    key[i] = e < n_experts ? (sel_bias ? sc[i] + sel_bias[e] : sc[i]) : -INFINITY;
+  }
+  float pv = 0.f;                        // lane j < k keeps the probability of slot j
+  for (int j = 0; j < k; j++) {
+    float bv = -INFINITY, bs = 0.f; int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; i++) { const int e = i * 32 + lane; if (key[i] > bv) { bv = key[i]; bs = sc[i]; bi = e; } }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o), os = __shfl_xor_sync(0xffffffffu, bs, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bs = os; bi = oi; }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_E_PER_LANE; i++) if (i * 32 + lane == bi) key[i] = -INFINITY;    // taken
+    const int slot = k - 1 - j;          // ascending order of rank
+    if (lane == slot) pv = bs;
+    if (lane == 0) topi[(size_t)tok * k + slot] = bi;
+  }
+  const bool mine = lane < k;
+  if (gating == GATE_SOFTMAX_WEIGHT) {
+    const float m2 = warp_max(mine ? pv : -INFINITY);
+    const float ev = mine ? expf(pv - m2) : 0.f;
+    pv = ev / warp_sum(ev);
+  }
+  if (normalize) pv = pv / warp_sum(mine ? pv : 0.f);
+  if (mine) weights[(size_t)tok * k + lane] = pv * scale;
+}
+
 // routing, steps 2-4: stable counting sort of the T*k (token, slot) pairs by expert.
 // dest_row[i] = off[e_i] + (number of pairs before i with the same expert); off = cumulative group sizes padded to 256.
 constexpr int ROUTE_CHUNK = 1024;
@@ -298,6 +366,21 @@ extern "C" int b200q_moe_route_pad(const float* logits, int n_tokens, int n_expe
   cudaStream_t st = (cudaStream_t)stream;
   const int n = n_tokens * k, n_chunks = ceil_div(n, ROUTE_CHUNK);
   route_topk_kernel<<<ceil_div(n_tokens, 8), 256, 0, st>>>(logits, n_tokens, n_experts, k, mode, topi, weights);
+  route_count_kernel<<<n_chunks, ROUTE_CHUNK, n_experts * sizeof(int), st>>>(topi, n, n_experts, (int32_t*)scratch);
+  route_scan_kernel<<<1, 256, n_experts * sizeof(int), st>>>((int32_t*)scratch, n_chunks, n_experts, off, pad, counts);
+  route_place_kernel<<<n_chunks, ROUTE_CHUNK, 32 * n_experts * sizeof(int), st>>>(topi, n, n_experts, (const int32_t*)scratch, off, dest_row);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+extern "C" int b200q_moe_route_gating(const float* logits, const float* sel_bias, int n_tokens, int n_experts, int k, int gating, int normalize, float scale,
+                                      int pad, int32_t* topi, float* weights, int32_t* dest_row, int32_t* off, int32_t* counts, void* scratch, void* stream) {
+  if (!logits || !topi || !weights || !dest_row || !off || !scratch || pad <= 0) return B200Q_ERR_BAD_ARG;
+  if (n_tokens <= 0 || n_experts <= 0 || k <= 0 || k > n_experts || gating < GATE_SOFTMAX || gating > GATE_SQRT_SOFTPLUS) return B200Q_ERR_BAD_ARG;
+  if (n_experts > 32 * MAX_E_PER_LANE || k > 32) return B200Q_ERR_BAD_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n = n_tokens * k, n_chunks = ceil_div(n, ROUTE_CHUNK);
+  route_gating_kernel<<<ceil_div(n_tokens, 8), 256, 0, st>>>(logits, sel_bias, n_tokens, n_experts, k, gating, normalize, scale, topi, weights);
   route_count_kernel<<<n_chunks, ROUTE_CHUNK, n_experts * sizeof(int), st>>>(topi, n, n_experts, (int32_t*)scratch);
   route_scan_kernel<<<1, 256, n_experts * sizeof(int), st>>>((int32_t*)scratch, n_chunks, n_experts, off, pad, counts);
   route_place_kernel<<<n_chunks, ROUTE_CHUNK, 32 * n_experts * sizeof(int), st>>>(topi, n, n_experts, (const int32_t*)scratch, off, dest_row);

@@ -90,6 +90,18 @@ class ExpertParallelMoE:
     self.y_send = torch.empty((self.m_max, 2 * self.D), dtype=u8, device=dev)
     self._per_T = {}
 
+  exchange_kind = "host-planned: counts all-gather, two all_to_all_single (NCCL) each way"
+
+  def timed(self, x_bf16, logits, n_tokens: int, reps: int) -> float:
+    """Milliseconds per call over `reps` calls, CUDA events on the stream the layer runs on (the default stream)."""
+    from .runtime import Event
+    e0, e1 = Event(), Event()
+    e0.record(None)
+    for _ in range(reps): self(x_bf16, logits, n_tokens)
+    e1.record(None)
+    e1.synchronize()
+    return e0.elapsed_ms(e1) / reps
+
   def _buffers(self, T: int):
     b = self._per_T.get(T)
     if b is None:

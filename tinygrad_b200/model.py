@@ -57,13 +57,16 @@ DEFAULT_HANDOVER = ("attn_o",)
 class Transformer:
   def __init__(self, config: TransformerConfig, state_dict: dict, ggml_type: int = _lib.Q4_0, n_split: int = 0, use_pdl: bool = True,
                use_graph: bool = True, gemv_max_ctas: int = 0, handover=None, tp=None, output_type: int = None, prefill_rows: int = 64,
-               prefill_chunk: int = 512, batch: int = 1):
+               prefill_chunk: int = 512, batch: int = 1, engine: str = None):
     """state_dict: the reference's tensor names -> numpy arrays; Linear weights as raw
     GGUF block bytes (uint8), embeddings / norms / biases as fp16.
     tp: a tensor_parallel.TPGroup; `config` is then the FULL model and `state_dict` this rank's shard (shard_state_dict).
     output_type: GGML type of `output.weight` when it differs from the block Linears' (Q6_K / F16 / F32 heads run the dense GEMV).
     prefill_rows: prompts with at least this many uncached tokens go through the tensor-core GEMM path, `prefill_chunk` rows at a
     time (0: always one token per step, whose fp32-activation numerics are the reference's own); shorter ones take decode steps.
+    engine: how a one-token step runs.  "step": one persistent kernel for the whole step (b200q_decode_step); "chain": five launches per
+    block chained with programmatic dependent launch and replayed as a CUDA graph; None: "step" where that kernel takes the model
+    (dense, Q4_0 / Q8_0 head, head_dim a multiple of 32, one GPU), else "chain".
     batch: sequences decoded in lock-step (`generate_batch`): one KV cache per sequence, every Linear a tensor-core GEMM over the
     batch rows (the reference's forward on tokens [B, T], model.py:358-364; its cache is sized by the first call's batch, model.py:200-203)."""
     self.tp, self.full_config = tp, config
@@ -166,6 +169,34 @@ class Transformer:
       assert tp is None and c.head_dim in (16, 32, 64, 128), "the mixture-of-experts model runs on the row path of one GPU"
       self.prefill_rows = 1
     self.launches_per_step = 5 * c.num_blocks + 3
+    # ---- the whole-step kernel: a device table of the blocks' pointers, its workspace, and the two argument blocks (with / without head)
+    self._step_args = None
+    if engine not in (None, "step", "chain"): raise ValueError(f"unknown engine {engine!r}")
+    if engine != "chain" and tp is None and not self.is_moe and batch == 1 and not isinstance(self.output, quant.DenseWeight) and self.output_type == ggml_type:
+      lib = _lib.load()
+      table = (_lib.DecodeLayer * c.num_blocks)(*[_lib.DecodeLayer(b.qkv.ptr, b.qkv_bias.ptr if b.qkv_bias else None, b.attn_output.buf.ptr, b.gate_up.buf.ptr,
+                                                                  b.ffn_down.buf.ptr, b.attn_norm.ptr, b.ffn_norm.ptr, b.k_cache.ptr, b.v_cache.ptr) for b in self.blk])
+      self._layer_table = DeviceBuffer.from_numpy(np.frombuffer(bytes(table), dtype=np.uint8))
+      def mk(with_head):
+        return _lib.DecodeStepArgs(self._layer_table.ptr, c.num_blocks, ggml_type, c.dim, c.hidden_dim, c.n_heads, c.n_kv_heads, c.head_dim, c.rope_dim,
+                                   c.max_context, c.vocab_size, c.vocab_size, F16 if c.kv_dtype == "float16" else F32, c.norm_eps, self.token_embd.ptr,
+                                   self.output_norm.ptr, self.output.buf.ptr, self.rope.ptr, self.tokens.ptr, self.pos.ptr, self.x.ptr, self.qkv.ptr,
+                                   self.attn.ptr, self.act.ptr, self.logits.ptr, None, 0, with_head, 0, None)
+      probe = mk(1)
+      rc = lib.b200q_decode_step_supported(ctypes.byref(probe))
+      if rc == 0:
+        self._step_ws = DeviceBuffer(lib.b200q_decode_step_workspace_bytes(ctypes.byref(probe)), zero=True)
+        self._step_args = {}
+        for wh in (0, 1):
+          a = mk(wh)
+          a.workspace, a.workspace_bytes = self._step_ws.ptr, self._step_ws.nbytes
+          self._step_args[bool(wh)] = a
+        self.launches_per_step = 1
+      elif engine == "step":
+        check(rc)
+    elif engine == "step":
+      raise ValueError("the whole-step kernel takes dense single-GPU models whose head has the block Linears' quant type")
+    self.engine = "step" if self._step_args else "chain"
 
   # ---- one token through the network (launch sequence; captured into a graph) ----
   def _enqueue_step(self, with_head: bool, attention: bool = True, tail: bool = True) -> None:
@@ -375,6 +406,7 @@ class Transformer:
     self._check_room()
     if self.is_moe: return self._step_rows(with_head)
     self._host_pos += 1
+    if self._step_args: return check(_lib.load().b200q_decode_step(ctypes.byref(self._step_args[bool(with_head)]), self.stream.ptr))
     if not self.use_graph: return self._enqueue_step(with_head)
     g = self._graphs.get(with_head)
     if g is None:

@@ -5,12 +5,30 @@
 activation -> grouped_mx_gemm -> combine), with the SwiGLU of tinygrad/llm/model.py:129.  bf16 tensors travel as
 uint16 arrays on the host (numpy has no bfloat16).  All compute is in libb200q.so.
 """
+from dataclasses import dataclass
 import numpy as np
 from . import _lib
 from ._lib import check, F32, BF16
 from .runtime import DeviceBuffer, stream_ptr
 
 ROUTE_TOPK_SOFTMAX, ROUTE_SOFTMAX_TOPK = 0, 1   # weights = softmax over the k best logits | softmax over all experts, not renormalised
+GATING = {"softmax": 1, "sigmoid": 2, "softmax_weight": 3, "sqrt_softplus": 4}     # ExpertGating, tinygrad/llm/model.py:9-13
+
+
+@dataclass(frozen=True)
+class Gating:
+  """The gating of tinygrad's MoE block (tinygrad/llm/model.py:110-128): scoring function, renormalisation over the selected k,
+  scaling factor and optional selection bias (fp32 [n_experts], added to the scores for the selection only)."""
+  func: str = "softmax"
+  norm_topk_prob: bool = False
+  routed_scaling_factor: float = 1.0
+  sel_bias: object = None
+
+  def resolved(self):
+    """(gating id, normalize) after the reference's shortcut: softmax + normalize + no bias is softmax over the k selected logits."""
+    g, n = GATING[self.func], bool(self.norm_topk_prob)
+    if g == 1 and n and self.sel_bias is None: g, n = 3, False
+    return g, n
 
 
 def to_bf16_bits(x: np.ndarray) -> np.ndarray:
@@ -33,15 +51,25 @@ def quantize_mxfp8(x: DeviceBuffer, rows: int, k: int, dtype: int, dest_row: Dev
 
 class Routing:
   """Device tables of `route` (extra/gemm/moe_routing.py:92-122).  Buffers are allocated once and reused by `run`."""
-  def __init__(self, n_tokens: int, n_experts: int, k: int, mode: int = ROUTE_TOPK_SOFTMAX):
+  def __init__(self, n_tokens: int, n_experts: int, k: int, mode=ROUTE_TOPK_SOFTMAX):
+    """mode: ROUTE_TOPK_SOFTMAX (`route` of extra/gemm/moe_routing.py), ROUTE_SOFTMAX_TOPK (the OLMoE defaults of tinygrad/llm), or a `Gating`."""
     lib = _lib.load()
     self.n_tokens, self.n_experts, self.k, self.mode = n_tokens, n_experts, k, mode
+    self._bias = None
+    if isinstance(mode, Gating) and mode.sel_bias is not None:
+      self._bias = DeviceBuffer.from_numpy(np.asarray(mode.sel_bias, dtype=np.float32).reshape(n_experts))
     self.m_l = lib.b200q_moe_rows_max(n_tokens, n_experts, k)
     self.topi, self.weights = DeviceBuffer.empty((n_tokens, k), np.int32), DeviceBuffer.empty((n_tokens, k), np.float32)
     self.dest_row, self.off = DeviceBuffer.empty((n_tokens * k,), np.int32), DeviceBuffer.empty((n_experts + 1,), np.int32)
     self._scratch = DeviceBuffer(lib.b200q_moe_route_scratch_bytes(n_tokens, n_experts, k))
 
   def run(self, logits: DeviceBuffer, stream=None) -> "Routing":
+    if isinstance(self.mode, Gating):
+      g, norm = self.mode.resolved()
+      check(_lib.load().b200q_moe_route_gating(logits.ptr, self._bias.ptr if self._bias else None, self.n_tokens, self.n_experts, self.k, g, int(norm),
+                                               float(self.mode.routed_scaling_factor), 256, self.topi.ptr, self.weights.ptr, self.dest_row.ptr,
+                                               self.off.ptr, None, self._scratch.ptr, stream_ptr(stream)))
+      return self
     check(_lib.load().b200q_moe_route(logits.ptr, self.n_tokens, self.n_experts, self.k, self.mode, self.topi.ptr, self.weights.ptr,
                                       self.dest_row.ptr, self.off.ptr, self._scratch.ptr, stream_ptr(stream)))
     return self
@@ -94,3 +122,22 @@ class MxMoE:
     check(lib.b200q_moe_combine(w["y"].ptr, r.dest_row.ptr, r.weights.ptr, n_tokens, self.k, self.D, w["out"].ptr, s))
     self.last_routing = r
     return w["out"]
+
+  def phases(self, x_bf16: DeviceBuffer, logits: DeviceBuffer, n_tokens: int, stream=None) -> dict:
+    """name -> a callable that enqueues that phase of `__call__` alone on `stream` (for timing them one by one; call the layer once first)."""
+    lib, s, w, T = _lib.load(), stream_ptr(stream), self._workspace(n_tokens), n_tokens
+    r = w["r"]
+    ph = {"route": lambda: r.run(logits, stream),
+          "zero_fill": lambda: (w["a_q"].zero_(stream), w["a_e8"].zero_(stream)),
+          "dispatch_quantize": lambda: lib.b200q_quantize_mxfp8(x_bf16.ptr, BF16, T, self.D, r.dest_row.ptr, self.k, w["a_q"].ptr, w["a_e8"].ptr, s)}
+    if self.fused:
+      ph["gate_up_gemm_swiglu"] = lambda: lib.b200q_grouped_mxfp8_gemm_swiglu(w["a_q"].ptr, w["a_e8"].ptr, self.gu_q.ptr, self.gu_e8.ptr, r.off.ptr, self.E,
+                                                                             r.m_l, 2 * self.F, self.D, w["act_q"].ptr, w["act_e8"].ptr, s)
+    else:
+      ph["gate_up_gemm"] = lambda: lib.b200q_grouped_mxfp8_gemm(w["a_q"].ptr, w["a_e8"].ptr, self.gu_q.ptr, self.gu_e8.ptr, r.off.ptr, self.E, r.m_l,
+                                                               2 * self.F, self.D, w["h"].ptr, s)
+      ph["swiglu_quantize"] = lambda: lib.b200q_swiglu_quantize_mxfp8(w["h"].ptr, r.m_l, r.off.ptr + 4 * self.E, self.F, w["act_q"].ptr, w["act_e8"].ptr, s)
+    ph["down_gemm"] = lambda: lib.b200q_grouped_mxfp8_gemm(w["act_q"].ptr, w["act_e8"].ptr, self.dn_q.ptr, self.dn_e8.ptr, r.off.ptr, self.E, r.m_l, self.D,
+                                                          self.F, w["y"].ptr, s)
+    ph["combine"] = lambda: lib.b200q_moe_combine(w["y"].ptr, r.dest_row.ptr, r.weights.ptr, T, self.k, self.D, w["out"].ptr, s)
+    return ph

@@ -158,3 +158,10 @@ def device_status() -> int:
   st = ctypes.c_int()
   check(_lib.load().b200q_status_read_clear(ctypes.byref(st)))
   return st.value
+
+
+def mx_status() -> int:
+  """The same word for the tcgen05 MXFP8 kernels (reads and clears it)."""
+  st = ctypes.c_int()
+  check(_lib.load().b200q_mx_status_read_clear(ctypes.byref(st)))
+  return st.value

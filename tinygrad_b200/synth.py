@@ -85,15 +85,25 @@ class LazyDenseState:
   """Mapping view of `dense_model_raw` that makes each tensor when it is asked for, so a
   multi-GB model never sits in host memory as a whole."""
   def __init__(self, cfg, ggml_type: int = Q4_0, seed: int = 0, embd_std: float = 0.02, bias_std: float = 0.02, embd_vocab: int = 0,
-               linear_seed: int = None):
+               linear_seed: int = None, distinct_blocks: int = 0):
     """embd_vocab: rows of the embedding table when it differs from cfg.vocab_size (a tensor-parallel shard keeps the whole
     table but only a slice of the vocabulary head); linear_seed: seed of the Linear weights / biases only (per-rank shards
-    differ, replicated tensors must not)."""
+    differ, replicated tensors must not); distinct_blocks > 0: block i takes the values of block i % distinct_blocks (memoised), which
+    bounds the host time of generating a very large model; every block still gets its own device memory."""
+    self.distinct_blocks, self._memo = distinct_blocks, {}
     self.cfg, self.ggml_type, self.seed, self.embd_std, self.bias_std = cfg, ggml_type, seed, embd_std, bias_std
     self.embd_vocab, self.linear_seed = embd_vocab or cfg.vocab_size, seed if linear_seed is None else linear_seed
     self.shapes = {n: (o, i) for n, o, i in linear_names(cfg)}
 
   def __getitem__(self, key: str) -> np.ndarray:
+    if self.distinct_blocks and key.startswith("blk."):
+      _, i, rest = key.split(".", 2)
+      src = f"blk.{int(i) % self.distinct_blocks}.{rest}"
+      if src not in self._memo: self._memo[src] = self._make(src)
+      return self._memo[src]
+    return self._make(key)
+
+  def _make(self, key: str) -> np.ndarray:
     name, kind = key.rsplit(".", 1)
     is_linear = (kind == "weight" and name in self.shapes) or kind == "bias"
     rng = np.random.default_rng(name_seed(name if kind == "weight" else key, self.linear_seed if is_linear else self.seed))

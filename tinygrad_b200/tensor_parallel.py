@@ -69,6 +69,8 @@ class TPGroup:
       self.dist.all_gather_into_tensor(warm, part)
     self.tstream.synchronize()
 
+  kind = "NCCL all-reduce per row-parallel linear (torch.distributed), captured into the step's CUDA graph"
+
   def stream_ptr(self) -> int: return int(self.tstream.cuda_stream)
 
   def empty_f32(self, n: int) -> TorchBuffer:
