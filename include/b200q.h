@@ -283,8 +283,8 @@ typedef struct b200q_decode_step_args {
   int with_head;
   int profile_stamps;       /* diagnostics, with `profile`: time stamps kept per CTA */
   void* profile;            /* NULL, or device uint64 [number of SMs][profile_stamps]: thread 0 of every CTA stores the global nanosecond
-                               timer at each stage boundary (start; per stage: input staged, tiles multiplied, rows finished, barrier
-                               passed; after a QKV stage also: attention done, barrier passed) */
+                               timer at the start and, per stage: input staged, tiles multiplied, rows finished, barrier passed (after a QKV
+                               stage also: attention done, barrier passed) */
 } b200q_decode_step_args;
 int b200q_decode_step_supported(const b200q_decode_step_args* args);
 size_t b200q_decode_step_workspace_bytes(const b200q_decode_step_args* args);
@@ -327,6 +327,9 @@ int b200q_embed_rows(const void* table_f16, const int32_t* tokens, int token_str
                      void* stream);
 int b200q_rmsnorm_rows(const float* x, const void* weight_f16, float eps, int n_rows, int dim, void* out, int out_dtype, void* stream);
 int b200q_add_rows_bf16(float* x, const void* y_bf16, int64_t n, void* stream);
+/* x[r, c] += y[r, c] * (gate_logit ? sigmoid(gate_logit[r]) : 1), fp32 [n_rows, dim]: the shared expert of a mixture-of-experts block
+ * joining the residual stream, with its optional per-token gate (tinygrad/llm/model.py:131-134). */
+int b200q_add_rows_gated(float* x, const float* y, const float* gate_logit, int n_rows, int dim, void* stream);
 int b200q_attn_prefill(const float* qkv, void* k_cache, void* v_cache, int kv_dtype, const float* rope, int start_pos, int n_rows, int n_heads,
                        int n_kv_heads, int head_dim, int rope_dim, int max_context, void* q_scratch, void* out, int out_dtype, void* stream);
 /* Batched decode (the reference's forward on tokens [B, 1], tinygrad/llm/model.py:358-364 with B > 1): row b of qkv is sequence b's

@@ -99,6 +99,20 @@ def pairwise_topk(x: np.ndarray, k: int):
   return np.take_along_axis(x, sel, axis=-1), sel
 
 
+def moe_gate(logits: np.ndarray, gating: int, normalize: bool, k: int, scale: float = 1.0, bias=None):
+  """Router logits (..., E) -> (sel (..., k) int32 in ascending rank order, probs (..., k)): tinygrad/llm/model.py:112-128."""
+  if gating == SOFTMAX and normalize and bias is None: gating, normalize = SOFTMAX_WEIGHT, False      # model.py:116-117
+  if gating == SOFTMAX_WEIGHT: scores = logits
+  elif gating == SOFTMAX: scores = softmax(logits)
+  elif gating == SIGMOID: scores = (1.0 / (1.0 + np.exp(-logits))).astype(np.float32)
+  else: scores = np.sqrt(np.log1p(np.exp(logits))).astype(np.float32)
+  _, sel = pairwise_topk(scores if bias is None else scores + bias.astype(np.float32), k)           # the bias only steers the selection
+  probs = np.take_along_axis(scores, sel.astype(np.int64), axis=-1)
+  if gating == SOFTMAX_WEIGHT: probs = softmax(probs)
+  if normalize: probs = probs / probs.sum(-1, keepdims=True)
+  return sel, (probs * np.float32(scale)).astype(np.float32)
+
+
 class Transformer:
   def __init__(self, cfg: Config, weights: dict):
     self.cfg, self.w = cfg, weights
@@ -138,23 +152,22 @@ class Transformer:
     if c.num_experts == 0:
       return self._lin(f"blk.{i}.ffn_down", silu(self._lin(f"blk.{i}.ffn_gate", x)) * self._lin(f"blk.{i}.ffn_up", x))
     logits = self._lin(f"blk.{i}.ffn_gate_inp", x)
-    gating, normalize = c.expert_gating_func, c.norm_topk_prob
-    if gating == SOFTMAX and normalize: gating, normalize = SOFTMAX_WEIGHT, False
-    if gating == SOFTMAX_WEIGHT: scores = logits
-    elif gating == SOFTMAX: scores = softmax(logits)
-    elif gating == SIGMOID: scores = 1.0 / (1.0 + np.exp(-logits))
-    else: scores = np.sqrt(np.log1p(np.exp(logits)))
-    _, sel = pairwise_topk(scores, c.num_experts_per_tok)
-    probs = np.take_along_axis(scores, sel.astype(np.int64), axis=-1)
-    if gating == SOFTMAX_WEIGHT: probs = softmax(probs)
-    if normalize: probs = probs / probs.sum(-1, keepdims=True)
-    probs = probs * np.float32(c.routed_scaling_factor)
+    sel, probs = moe_gate(logits, c.expert_gating_func, c.norm_topk_prob, c.num_experts_per_tok, c.routed_scaling_factor,
+                          self.w.get(f"blk.{i}.exp_probs_b.bias"))
     wg, wu, wd = (self.w[f"blk.{i}.ffn_{n}_exps.weight"] for n in ("gate", "up", "down"))
     h = x[:, :, None, :]                                         # (B,T,1,D)
     g = np.einsum("btid,btkod->btko", h, wg[sel])                 # model.py:25-27
     u = np.einsum("btid,btkod->btko", h, wu[sel])
     d = np.einsum("btkh,btkoh->btko", (silu(g) * u).astype(np.float32), wd[sel])
-    return (d * probs[..., None]).sum(2).astype(np.float32)
+    out = (d * probs[..., None]).sum(2).astype(np.float32)
+    return out + self._shared_expert(i, x)
+
+  def _shared_expert(self, i, x):                                # model.py:131-134
+    if f"blk.{i}.ffn_gate_shexp.weight" not in self.w: return np.float32(0.0)
+    sh = self._lin(f"blk.{i}.ffn_down_shexp", silu(self._lin(f"blk.{i}.ffn_gate_shexp", x)) * self._lin(f"blk.{i}.ffn_up_shexp", x))
+    gate = self.w.get(f"blk.{i}.ffn_gate_inp_shexp.weight")
+    if gate is not None: sh = sh * (1.0 / (1.0 + np.exp(-(x * gate.astype(np.float32)).sum(-1, keepdims=True, dtype=np.float32))))
+    return sh.astype(np.float32)
 
   def forward_logits(self, tokens: np.ndarray, start_pos: int) -> np.ndarray:
     """model.py:358-362 up to the logits of the last token.  tokens (1,T)."""

@@ -179,3 +179,37 @@ if "mxgemm" in groups:
   w_q, w_e8, _ = quantize_mxfp8(Tensor(w))
   y = matmul_mx(xb, w_q, w_e8)
   save("mxgemm", x_bf16=xb.float().numpy(), w=w, w_q=w_q.bitcast(dtypes.uint8).numpy(), w_e8=w_e8.numpy(), y=y.float().numpy())
+
+
+if "moe2" in groups:
+  # the remaining gating paths of tinygrad/llm/model.py:110-134: sqrt(softplus) scores, a selection bias, a (gated) shared expert
+  rng = np.random.default_rng(600)
+  out = {}
+  for tag, kwargs in (("softplus_bias", dict(expert_gating_func=ExpertGating.SQRT_SOFTPLUS, norm_topk_prob=True, routed_scaling_factor=2.5, expert_bias=True)),
+                      ("softmax_bias_norm", dict(expert_gating_func=ExpertGating.SOFTMAX, norm_topk_prob=True, expert_bias=True)),
+                      ("sigmoid_shared", dict(expert_gating_func=ExpertGating.SIGMOID, norm_topk_prob=True, shared_expert_dim=48, shared_expert_gate=True)),
+                      ("softmax_shared_plain", dict(expert_gating_func=ExpertGating.SOFTMAX, shared_expert_dim=32, shared_expert_gate=False))):
+    dim, hidden, E, k = 32, 64, 8, 3
+    cfg = TransformerConfig(num_blocks=1, dim=dim, hidden_dim=hidden, n_heads=2, n_kv_heads=2, norm_eps=1e-5, vocab_size=32, head_dim=16,
+                            rope_theta=10000, rope_dim=16, v_head_dim=16, max_context=16, num_experts=E, num_experts_per_tok=k, **kwargs)
+    blk = TransformerBlock(cfg)
+    sh = cfg.shared_expert_dim
+    ws = {n: (rng.standard_normal(shape) * 0.3).astype(np.float32) for n, shape in
+          (("gate", (E, hidden, dim)), ("up", (E, hidden, dim)), ("down", (E, dim, hidden)), ("router", (E, dim)))}
+    blk.ffn_gate_exps.weight, blk.ffn_up_exps.weight = Tensor(ws["gate"]), Tensor(ws["up"])
+    blk.ffn_down_exps.weight, blk.ffn_gate_inp.weight = Tensor(ws["down"]), Tensor(ws["router"])
+    if cfg.expert_bias:
+      ws["bias"] = (rng.standard_normal(E) * 0.5).astype(np.float32)
+      blk.exp_probs_b["bias"] = Tensor(ws["bias"])
+    if sh:
+      for n, shape in (("sh_gate", (sh, dim)), ("sh_up", (sh, dim)), ("sh_down", (dim, sh))): ws[n] = (rng.standard_normal(shape) * 0.3).astype(np.float32)
+      blk.ffn_gate_shexp.weight, blk.ffn_up_shexp.weight, blk.ffn_down_shexp.weight = Tensor(ws["sh_gate"]), Tensor(ws["sh_up"]), Tensor(ws["sh_down"])
+      if cfg.shared_expert_gate:
+        ws["sh_inp"] = (rng.standard_normal(dim) * 0.3).astype(np.float32)
+        blk.ffn_gate_inp_shexp["weight"] = Tensor(ws["sh_inp"])
+    h = rng.standard_normal((1, 5, dim)).astype(np.float32)
+    y = blk._feed_forward(Tensor(h)).numpy()
+    out.update({f"{tag}_{n}": a for n, a in ws.items()})
+    out.update({f"{tag}_h": h, f"{tag}_y": y, f"{tag}_cfg": np.array([dim, hidden, E, k, int(cfg.expert_gating_func), int(cfg.norm_topk_prob)]),
+                f"{tag}_scale": np.array(cfg.routed_scaling_factor)})
+  save("moe2", **out)

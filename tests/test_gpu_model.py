@@ -36,7 +36,7 @@ def test_greedy_stream_identical_to_reference(golden, name, mode):
   g = golden(name)
   cfg, _, typ = _cfgs(g)
   sd = {k[2:]: g[k] for k in g.files if k.startswith("w:")}
-  m = Transformer(cfg, sd, ggml_type=typ, use_pdl=(mode == "graph_pdl"), use_graph=(mode == "graph_pdl"), engine=None if mode == "step" else "chain")
+  m = Transformer(cfg, sd, ggml_type=typ, use_pdl=(mode == "graph_pdl"), use_graph=(mode == "graph_pdl"), engine="step" if mode == "step" and cfg.head_dim % 32 == 0 else "chain")
   assert m.engine == ("step" if mode == "step" and cfg.head_dim % 32 == 0 else "chain")
   want = [int(t) for t in g["tokens"]]
   got = []

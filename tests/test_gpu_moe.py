@@ -83,6 +83,35 @@ def test_route_random_matches_oracle(T, E, k):
   np.testing.assert_array_equal(off1, roff)
 
 
+@pytest.mark.parametrize("func,norm,scale,with_bias", [("softmax", False, 1.0, False), ("softmax", True, 1.0, False), ("softmax", True, 1.0, True),
+                                                       ("sigmoid", True, 2.5, False), ("sigmoid", False, 1.0, True), ("softmax_weight", False, 1.0, False),
+                                                       ("sqrt_softplus", True, 1.5, True), ("sqrt_softplus", False, 1.0, False)])
+def test_route_gating_matches_oracle(func, norm, scale, with_bias):
+  """Every gating of tinygrad's MoE block (tinygrad/llm/model.py:110-128): selection (with ties and a selection bias), weights, placement."""
+  from tinygrad_b200 import moe
+  from tinygrad_b200.runtime import DeviceBuffer
+  T, E, k = 777, 64, 6
+  rng = np.random.default_rng(E + k)
+  logits = (rng.standard_normal((T, E)) * 2).astype(np.float32)
+  logits[3, 10:14] = logits[3, 10]                                  # ties: the lower index ranks higher
+  logits[4, :] = 30.0; logits[5, :] = -30.0                         # saturated scores
+  bias = (rng.standard_normal(E) * 0.5).astype(np.float32) if with_bias else None
+  g = moe.Gating(func, norm, scale, bias)
+  r = moe.Routing(T, E, k, g).run(DeviceBuffer.from_numpy(logits))
+  sel, probs = llm.moe_gate(logits, moe.GATING[func], norm, k, scale, bias)
+  topi, w, dest, off = r.topi.numpy(), r.weights.numpy(), r.dest_row.numpy(), r.off.numpy()
+  rows = [t for t in range(T) if t not in (4, 5)]                  # all-equal scores: any consistent order of float ties is checked below
+  np.testing.assert_array_equal(topi[rows], sel[rows])
+  np.testing.assert_allclose(w[rows], probs[rows], rtol=2e-5, atol=1e-7)
+  if not with_bias: np.testing.assert_array_equal(topi[4], np.arange(k)[::-1])      # equal scores: experts k-1 .. 0 in ascending rank
+  np.testing.assert_allclose(w[[4, 5]].sum(-1), probs[[4, 5]].sum(-1), rtol=1e-4)
+  counts = np.bincount(topi.reshape(-1), minlength=E)
+  np.testing.assert_array_equal(off, np.concatenate([[0], np.cumsum((counts + 255) // 256 * 256)]))
+  assert len(set(dest.tolist())) == T * k
+  e_of_row = np.searchsorted(off, dest, side="right") - 1
+  np.testing.assert_array_equal(e_of_row, topi.reshape(-1))         # every pair sits inside its expert's group
+
+
 def test_grouped_gemm_matches_oracle():
   from tinygrad_b200 import _lib, moe
   from tinygrad_b200.runtime import DeviceBuffer

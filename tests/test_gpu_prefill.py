@@ -121,13 +121,8 @@ class _MxOracle(llm.Transformer):
     B, T, D = x.shape
     xr = x.reshape(T, D).astype(np.float32)
     logits = llm.linear(xr, self.w[f"blk.{i}.ffn_gate_inp.weight"].astype(np.float32))
-    if c.norm_topk_prob:
-      _, sel = llm.pairwise_topk(logits, c.num_experts_per_tok)
-      probs = llm.softmax(np.take_along_axis(logits, sel.astype(np.int64), -1))
-    else:
-      scores = llm.softmax(logits)
-      _, sel = llm.pairwise_topk(scores, c.num_experts_per_tok)
-      probs = np.take_along_axis(scores, sel.astype(np.int64), -1)
+    sel, probs = llm.moe_gate(logits, c.expert_gating_func, c.norm_topk_prob, c.num_experts_per_tok, c.routed_scaling_factor,
+                              self.w.get(f"blk.{i}.exp_probs_b.bias"))
     xa = mx.dequantize_mxfp8(*mx.quantize_mxfp8(mx.to_bf16(xr)))
     wg, wu, wd = (self.w[f"blk.{i}.ffn_{n}_exps.weight"] for n in ("gate", "up", "down"))
     if not hasattr(self, "_deq"): self._deq = {}
@@ -145,15 +140,20 @@ class _MxOracle(llm.Transformer):
         aq = mx.dequantize_mxfp8(*mx.quantize_mxfp8(act[None]))[0]
         acc += probs[t, j] * mx.to_bf16(dn[e] @ aq)
       out[t] = mx.to_bf16(acc)
-    return out.reshape(B, T, D)
+    return out.reshape(B, T, D) + self._shared_expert(i, x)
 
 
-@pytest.mark.parametrize("norm_topk", [False, True])
-def test_moe_transformer_matches_mx_oracle(norm_topk):
-  """A routed-experts model (MXFP8 expert GEMMs inside the Transformer): prompt through the row path, then one-token steps."""
+@pytest.mark.parametrize("variant", ["softmax", "softmax_norm", "sigmoid_norm_scaled_shared_gate", "sqrt_softplus_bias_shared"])
+def test_moe_transformer_matches_mx_oracle(variant):
+  """A routed-experts model (MXFP8 expert GEMMs inside the Transformer): prompt through the row path, then one-token steps; the gating
+  functions, selection bias, scaling factor and shared expert of tinygrad/llm/model.py:110-134."""
   from tinygrad_b200.model import Transformer, TransformerConfig
+  from tinygrad_b200 import moe
+  extra = {"softmax": dict(), "softmax_norm": dict(norm_topk_prob=True),
+           "sigmoid_norm_scaled_shared_gate": dict(expert_gating_func="sigmoid", norm_topk_prob=True, routed_scaling_factor=2.0, shared_expert_dim=128),
+           "sqrt_softplus_bias_shared": dict(expert_gating_func="sqrt_softplus", expert_bias=True, shared_expert_dim=96, shared_expert_gate=False)}[variant]
   kw = dict(num_blocks=2, dim=256, hidden_dim=128, n_heads=4, n_kv_heads=2, norm_eps=1e-5, vocab_size=500, head_dim=64, rope_theta=10000.0, rope_dim=64,
-            max_context=96, num_experts=8, num_experts_per_tok=2, norm_topk_prob=norm_topk)
+            max_context=96, num_experts=8, num_experts_per_tok=2, **extra)
   cfg = TransformerConfig(**kw)
   sd = {k: v for k, v in synth.dense_model_raw(cfg, 8, seed=17, embd_std=0.3, scale_std=0.0015).items() if ".ffn_gate." not in k and ".ffn_up." not in k
         and ".ffn_down." not in k}
@@ -162,9 +162,17 @@ def test_moe_transformer_matches_mx_oracle(norm_topk):
     sd[f"blk.{i}.ffn_gate_inp.weight"] = (rng.standard_normal((8, 256)) * 0.1).astype(np.float32)
     for n, shape in (("gate", (8, 128, 256)), ("up", (8, 128, 256)), ("down", (8, 256, 128))):
       sd[f"blk.{i}.ffn_{n}_exps.weight"] = (rng.standard_normal(shape) * 0.08).astype(np.float32)
+    if cfg.expert_bias: sd[f"blk.{i}.exp_probs_b.bias"] = (rng.standard_normal(8) * 0.3).astype(np.float32)
   shapes = {n: (o, i) for n, o, i in synth.linear_names(cfg)}
+  sh = cfg.shared_expert_dim
+  for i in range(cfg.num_blocks if sh else 0):       # the shared expert: Q8_0 blocks like the attention Linears
+    for n, (o, ii) in (("ffn_gate_shexp", (sh, 256)), ("ffn_up_shexp", (sh, 256)), ("ffn_down_shexp", (256, sh))):
+      sd[f"blk.{i}.{n}.weight"] = synth.q8_0_blocks(o, ii, np.random.default_rng(synth.name_seed(f"{i}{n}", 3)), scale_std=0.0015)
+      shapes[f"blk.{i}.{n}"] = (o, ii)
+    if cfg.shared_expert_gate: sd[f"blk.{i}.ffn_gate_inp_shexp.weight"] = (rng.standard_normal(256) * 0.1).astype(np.float32)
   w = {k: (gq.weight_matrix(v, *shapes[k[:-len(".weight")]], 8) if v.dtype == np.uint8 else v) for k, v in sd.items()}
-  okw = {k: v for k, v in kw.items()}
+  okw = {k: v for k, v in kw.items() if k not in ("shared_expert_dim", "shared_expert_gate", "expert_bias")}
+  okw["expert_gating_func"] = moe.GATING[cfg.expert_gating_func]
   oracle = _MxOracle(llm.Config(**okw, kv_dtype="float16"), w)
   prompt = [int(t) for t in np.random.default_rng(6).integers(0, 500, 40)]
   want, want_logits = oracle.generate(prompt, 6, chunk_size=64, keep_logits=True)

@@ -154,3 +154,19 @@ def test_mxfp8_matmul_matches_reference(golden):
   # bf16 output: at most one unit in the last place apart (fp32 summation order), most entries identical
   np.testing.assert_allclose(y, g["y"], rtol=2 ** -7, atol=1e-6)
   assert (y == g["y"]).mean() > 0.9
+
+
+@pytest.mark.parametrize("tag", ["softplus_bias", "softmax_bias_norm", "sigmoid_shared", "softmax_shared_plain"])
+def test_moe_ffn_gating_paths_match_reference(golden, tag):
+  """sqrt(softplus) scores, a selection bias, scaling factor, shared expert with and without its gate (tinygrad/llm/model.py:110-134)."""
+  g = golden("moe2")
+  dim, hidden, E, k, gating, norm = (int(v) for v in g[f"{tag}_cfg"])
+  cfg = llm.Config(num_blocks=1, dim=dim, hidden_dim=hidden, n_heads=2, n_kv_heads=2, norm_eps=1e-5, vocab_size=32, head_dim=16,
+                   rope_theta=10000.0, rope_dim=16, max_context=16, num_experts=E, num_experts_per_tok=k, norm_topk_prob=bool(norm),
+                   expert_gating_func=gating, routed_scaling_factor=float(g[f"{tag}_scale"]))
+  names = {"gate": "ffn_gate_exps.weight", "up": "ffn_up_exps.weight", "down": "ffn_down_exps.weight", "router": "ffn_gate_inp.weight",
+           "bias": "exp_probs_b.bias", "sh_gate": "ffn_gate_shexp.weight", "sh_up": "ffn_up_shexp.weight", "sh_down": "ffn_down_shexp.weight",
+           "sh_inp": "ffn_gate_inp_shexp.weight"}
+  w = {"blk.0." + full: g[f"{tag}_{short}"] for short, full in names.items() if f"{tag}_{short}" in g.files}
+  m = llm.Transformer.__new__(llm.Transformer); m.cfg, m.w = cfg, w
+  np.testing.assert_allclose(m._feed_forward(0, g[f"{tag}_h"]), g[f"{tag}_y"], rtol=1e-4, atol=1e-5)

@@ -36,7 +36,8 @@ class DecodeStepArgs(Structure):
               ("n_kv_heads", c_int), ("head_dim", c_int), ("rope_dim", c_int), ("max_context", c_int), ("vocab", c_int), ("embd_vocab", c_int),
               ("kv_dtype", c_int), ("norm_eps", c_float), ("token_embd", c_void_p), ("output_norm", c_void_p), ("output", c_void_p),
               ("rope", c_void_p), ("tokens", c_void_p), ("pos", c_void_p), ("x", c_void_p), ("qkv", c_void_p), ("attn", c_void_p),
-              ("act", c_void_p), ("logits", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("with_head", c_int), ("profile_stamps", c_int), ("profile", c_void_p)]
+              ("act", c_void_p), ("logits", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("with_head", c_int), ("profile_stamps", c_int),
+              ("profile", c_void_p)]
 
 
 # name -> (restype, argtypes); every symbol include/b200q.h declares
@@ -95,6 +96,7 @@ SIGNATURES = {
                                 c_void_p]),
   "b200q_embed_rows": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
   "b200q_rmsnorm_rows": (c_int, [c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_int, c_void_p]),
+  "b200q_add_rows_gated": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
   "b200q_add_rows_bf16": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
   "b200q_attn_prefill": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                 c_int, c_void_p]),

@@ -305,6 +305,21 @@ extern "C" int b200q_rmsnorm_rows(const float* x, const void* weight_f16, float 
   return B200Q_OK;
 }
 
+// x[r][c] += y[r][c] * (gate ? sigmoid(gate[r]) : 1): the shared expert's output joining the residual stream (tinygrad/llm/model.py:131-134)
+__global__ void add_rows_gated_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gate, int n_rows, int dim) {
+  const int r = blockIdx.x;
+  const float g = gate ? 1.f / (1.f + expf(-gate[r])) : 1.f;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) x[(size_t)r * dim + c] += y[(size_t)r * dim + c] * g;
+}
+
+extern "C" int b200q_add_rows_gated(float* x, const float* y, const float* gate_logit, int n_rows, int dim, void* stream) {
+  if (!x || !y || n_rows < 0 || dim <= 0) return B200Q_ERR_BAD_ARG;
+  if (n_rows == 0) return B200Q_OK;
+  add_rows_gated_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(x, y, gate_logit, n_rows, dim);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
 extern "C" int b200q_add_rows_bf16(float* x, const void* y_bf16, int64_t n, void* stream) {
   if (!x || !y_bf16 || n < 0) return B200Q_ERR_BAD_ARG;
   if (((uintptr_t)x & 7) || ((uintptr_t)y_bf16 & 3)) return B200Q_ERR_MISALIGNED;

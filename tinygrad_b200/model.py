@@ -35,8 +35,11 @@ class TransformerConfig:           # field names of tinygrad/llm/model.py:52-83 
   num_experts: int = 0             # > 0: every block's FFN is a routed mixture of experts (model.py:94-98,110-135) with MXFP8 expert weights
   num_experts_per_tok: int = 0
   norm_topk_prob: bool = False
-  expert_gating_func: str = "softmax"
+  expert_gating_func: str = "softmax"   # "softmax" | "sigmoid" | "softmax_weight" | "sqrt_softplus" (ExpertGating, model.py:9-13)
   routed_scaling_factor: float = 1.0
+  shared_expert_dim: int = 0            # > 0: a dense SwiGLU expert every token also goes through (model.py:99-103,131-134)
+  shared_expert_gate: bool = True       # its output is scaled by sigmoid(x . ffn_gate_inp_shexp) when that tensor is present
+  expert_bias: bool = False             # exp_probs_b: a bias added to the scores for the selection only (model.py:113,123)
 
 
 def precompute_freqs_cis(dim: int, end: int, theta: float) -> np.ndarray:
@@ -65,8 +68,8 @@ class Transformer:
     prefill_rows: prompts with at least this many uncached tokens go through the tensor-core GEMM path, `prefill_chunk` rows at a
     time (0: always one token per step, whose fp32-activation numerics are the reference's own); shorter ones take decode steps.
     engine: how a one-token step runs.  "step": one persistent kernel for the whole step (b200q_decode_step); "chain": five launches per
-    block chained with programmatic dependent launch and replayed as a CUDA graph; None: "step" where that kernel takes the model
-    (dense, Q4_0 / Q8_0 head, head_dim a multiple of 32, one GPU), else "chain".
+    block chained with programmatic dependent launch and replayed as a CUDA graph (the default: at batch 1 it measured faster, the
+    grid-wide waits inside one kernel costing more than kernel boundaries do).
     batch: sequences decoded in lock-step (`generate_batch`): one KV cache per sequence, every Linear a tensor-core GEMM over the
     batch rows (the reference's forward on tokens [B, T], model.py:358-364; its cache is sized by the first call's batch, model.py:200-203)."""
     self.tp, self.full_config = tp, config
@@ -102,13 +105,19 @@ class Transformer:
       if c.num_experts:
         # routed experts: fp32 (E, out, in) weights quantised to MXFP8 on the device; the router stays a dense Linear (model.py:94-98)
         from . import moe
-        if c.expert_gating_func != "softmax" or c.routed_scaling_factor != 1.0:
-          raise NotImplementedError("expert gating other than softmax (with or without top-k renormalisation) is outside this path")
-        # softmax gating with renormalised top-k = softmax over the k selected logits (model.py:116-117); without: softmax over all experts
-        mode = moe.ROUTE_TOPK_SOFTMAX if c.norm_topk_prob else moe.ROUTE_SOFTMAX_TOPK
-        b.moe = moe.MxMoE(*(np.asarray(sd[f"blk.{i}.ffn_{n}_exps.weight"], dtype=np.float32) for n in ("gate", "up", "down")), c.num_experts_per_tok, mode)
+        if c.expert_gating_func not in moe.GATING: raise ValueError(f"unknown expert gating function {c.expert_gating_func!r}")
+        gating = moe.Gating(c.expert_gating_func, c.norm_topk_prob, c.routed_scaling_factor,
+                            np.asarray(sd[f"blk.{i}.exp_probs_b.bias"], dtype=np.float32) if c.expert_bias else None)
+        b.moe = moe.MxMoE(*(np.asarray(sd[f"blk.{i}.ffn_{n}_exps.weight"], dtype=np.float32) for n in ("gate", "up", "down")), c.num_experts_per_tok, gating)
         r = np.asarray(sd[f"blk.{i}.ffn_gate_inp.weight"])
         b.router = quant.DenseWeight(r, c.num_experts, c.dim, quant.GGML_F16 if r.dtype == np.float16 else quant.GGML_F32)
+        b.sh_gate_up = b.sh_down = b.sh_inp = None
+        if c.shared_expert_dim:      # the shared expert is an ordinary quantised SwiGLU FFN; its optional gate a [dim] vector
+          b.sh_gate_up = quant.repack(sd[f"blk.{i}.ffn_gate_shexp.weight"], c.shared_expert_dim, c.dim, ggml_type, raw_up=sd[f"blk.{i}.ffn_up_shexp.weight"])
+          b.sh_down = quant.repack(sd[f"blk.{i}.ffn_down_shexp.weight"], c.dim, c.shared_expert_dim, ggml_type)
+          if c.shared_expert_gate and f"blk.{i}.ffn_gate_inp_shexp.weight" in sd:
+            gw = np.asarray(sd[f"blk.{i}.ffn_gate_inp_shexp.weight"])
+            b.sh_inp = quant.DenseWeight(gw.reshape(1, c.dim), 1, c.dim, quant.GGML_F16 if gw.dtype == np.float16 else quant.GGML_F32)
       else:
         b.gate_up = quant.repack(sd[f"blk.{i}.ffn_gate.weight"], c.hidden_dim, c.dim, ggml_type, raw_up=sd[f"blk.{i}.ffn_up.weight"])
         b.ffn_down = quant.repack(sd[f"blk.{i}.ffn_down.weight"], c.dim, c.hidden_dim, ggml_type)
@@ -172,7 +181,7 @@ class Transformer:
     # ---- the whole-step kernel: a device table of the blocks' pointers, its workspace, and the two argument blocks (with / without head)
     self._step_args = None
     if engine not in (None, "step", "chain"): raise ValueError(f"unknown engine {engine!r}")
-    if engine != "chain" and tp is None and not self.is_moe and batch == 1 and not isinstance(self.output, quant.DenseWeight) and self.output_type == ggml_type:
+    if engine == "step" and tp is None and not self.is_moe and batch == 1 and not isinstance(self.output, quant.DenseWeight) and self.output_type == ggml_type:
       lib = _lib.load()
       table = (_lib.DecodeLayer * c.num_blocks)(*[_lib.DecodeLayer(b.qkv.ptr, b.qkv_bias.ptr if b.qkv_bias else None, b.attn_output.buf.ptr, b.gate_up.buf.ptr,
                                                                   b.ffn_down.buf.ptr, b.attn_norm.ptr, b.ffn_norm.ptr, b.k_cache.ptr, b.v_cache.ptr) for b in self.blk])
@@ -259,9 +268,11 @@ class Transformer:
       c, T = self.config, self.prefill_chunk
       self._pf = dict(x=DeviceBuffer.empty((T, c.dim), np.float32), xn=DeviceBuffer.empty((T, c.dim), np.float32),
                       qkv=DeviceBuffer.empty((T, self.q_dim + 2 * self.kv_dim), np.float32), q16=DeviceBuffer.empty((T, self.q_dim), np.float32),
-                      att=DeviceBuffer.empty((T, self.q_dim), np.float32), act=DeviceBuffer.empty((T, max(c.hidden_dim, 1)), np.float32))
+                      att=DeviceBuffer.empty((T, self.q_dim), np.float32),
+                      act=DeviceBuffer.empty((T, max(c.hidden_dim, c.shared_expert_dim, 1)), np.float32))
       if self.is_moe:
         self._pf.update(xb=DeviceBuffer.empty((T, c.dim), np.uint16), logits=DeviceBuffer.empty((T, c.num_experts), np.float32))
+        if c.shared_expert_dim: self._pf.update(sh=DeviceBuffer.empty((T, c.dim), np.float32), shg=DeviceBuffer.empty((T,), np.float32))
     return self._pf
 
   def prefill(self, start_pos: int, n: int, sync: bool = True, seq: int = 0) -> None:
@@ -289,6 +300,12 @@ class Transformer:
           quant.gemv_dense(b.router.buf, b.router.dtype, c.num_experts, c.dim, f["xn"], f["logits"], m=T, stream=s)
           check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.ffn_norm.ptr, c.norm_eps, T, c.dim, f["xb"].ptr, _lib.BF16, s))
           y = b.moe(f["xb"], f["logits"], T, stream=s)
+          if b.sh_gate_up is not None:      # shared expert on the fp32 normed rows (model.py:131-134), added before x moves
+            quant.qgemm(b.sh_gate_up.buf.ptr, self.qtype, 2 * c.shared_expert_dim, c.dim, f["xn"], f["act"], T, x_dtype=F32, y_dtype=F32,
+                        epilogue=EPI_SILU_MUL, stream=s)
+            quant.qgemm(b.sh_down.buf.ptr, self.qtype, c.dim, c.shared_expert_dim, f["act"], f["sh"], T, x_dtype=F32, y_dtype=F32, stream=s)
+            if b.sh_inp is not None: quant.gemv_dense(b.sh_inp.buf, b.sh_inp.dtype, 1, c.dim, f["xn"], f["shg"], m=T, stream=s)
+            check(lib.b200q_add_rows_gated(f["x"].ptr, f["sh"].ptr, f["shg"].ptr if b.sh_inp is not None else None, T, c.dim, s))
           check(lib.b200q_add_rows_bf16(f["x"].ptr, y.ptr, T * c.dim, s))
           continue
         quant.qgemm(b.gate_up.buf.ptr, self.qtype, 2 * c.hidden_dim, c.dim, f["xn"], f["act"], T, x_dtype=F32, y_dtype=F32, epilogue=EPI_SILU_MUL,
