@@ -32,7 +32,12 @@ extern "C" {
 /* ---- enums -------------------------------------------------------------- */
 /* GGML tensor types, numbered as in the GGUF file format (tinygrad/llm/gguf.py:20-21). */
 #define B200Q_Q4_0 2
+#define B200Q_Q4_1 3
+#define B200Q_Q5_0 6
+#define B200Q_Q5_1 7
 #define B200Q_Q8_0 8
+#define B200Q_Q4_K 12
+#define B200Q_Q5_K 13
 #define B200Q_Q6_K 14
 /* element types of activations / outputs */
 #define B200Q_F32 0
@@ -83,7 +88,7 @@ int b200q_graph_destroy(void* graph_exec);
 
 /* ---- GGUF block formats -------------------------------------------------
  * Replaces the lazy dequantisation expression `ggml_data_to_tensor`
- * (tinygrad/llm/gguf.py:23-72; Q4_0 :46, Q8_0 :56, Q6_K :68-72).
+ * (tinygrad/llm/gguf.py:23-72; Q4_0 :46, Q4_1 :47-49, Q5_0 / Q5_1 :50-55, Q8_0 :56, Q4_K / Q5_K :57-67, Q6_K :68-72).
  *
  * b200q_dequant_raw: raw GGUF blocks -> n_elems values, fp32 (bit-identical to
  * the reference's fp32 expression) or fp16 (its round-to-nearest-even cast,
@@ -167,6 +172,9 @@ size_t b200q_xq_bytes(int n);
  * n_out belongs to a GEMM).  flags: B200Q_FLAG_PDL. */
 int b200q_gemv_dense(const void* w, int w_dtype, int n_out, int n_in, int m, const void* x, int x_dtype, const void* norm_weight,
                      float norm_eps, const void* bias, const void* residual, void* y, int y_dtype, int flags, void* stream);
+
+/* out[i] = silu(gate[i]) * up[i], fp32: the SwiGLU product (tinygrad/llm/model.py:137) behind two separate b200q_gemv_dense calls. */
+int b200q_silu_mul(const float* gate, const float* up, float* out, int64_t n, int flags, void* stream);
 
 /* The Linear as tinygrad's own runtime launches it (the in-graph seam, tinygrad/tensor.py:390-396: `Tensor.custom_kernel` with a
  * prebuilt PROGRAM, precedent extra/gemm/moe_gemm.py:30-48).  The kernels b200q_tg_gemv_q4_0 / _q8_0(float* y, const float* x,

@@ -213,3 +213,15 @@ if "moe2" in groups:
     out.update({f"{tag}_h": h, f"{tag}_y": y, f"{tag}_cfg": np.array([dim, hidden, E, k, int(cfg.expert_gating_func), int(cfg.norm_topk_prob)]),
                 f"{tag}_scale": np.array(cfg.routed_scaling_factor)})
   save("moe2", **out)
+
+
+if "dequant2" in groups:
+  # the other block formats of real GGUF files: Q4_1, Q5_0, Q5_1, Q4_K, Q5_K (tinygrad/llm/gguf.py:47-67), 3 blocks each
+  out = {}
+  for typ, tag in ((3, "q4_1"), (6, "q5_0"), (7, "q5_1"), (12, "q4_k"), (13, "q5_k")):
+    nel, nby = synth.GGML_SIZES[typ]
+    raw = synth.random_blocks(typ, 1, 3 * nel, np.random.default_rng(700 + typ), scale_std=0.05)
+    t = ggml_data_to_tensor(Tensor(raw), 3 * nel, typ)
+    out[f"{tag}_raw"], out[f"{tag}_f32"] = raw, t.numpy()
+    out[f"{tag}_f16"] = t.cast(dtypes.float16).numpy()
+  save("dequant2", **out)

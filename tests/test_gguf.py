@@ -49,8 +49,10 @@ def test_invalid_files_raise_like_the_reference():
   img = synth.write_gguf({"general.architecture": "llama"}, [("d", (4,), 0, np.zeros(4, np.float32))])
   for bad in (b"GGML" + img[4:], img[:4] + struct.pack("<i", 1) + img[8:], img[:10], img[:-20]):
     with pytest.raises(ValueError, match="Invalid GGUF format!"): gguf.gguf_parse(bad)
-  with pytest.raises(ValueError, match="is not supported"):                       # a block type outside this path (Q4_K = 12)
-    gguf.gguf_parse(synth.write_gguf({}, [("w", (256,), 12, np.zeros(144, np.uint8))]))
+  with pytest.raises(ValueError, match="is not supported"):                       # a block type outside this path (IQ3_XXS = 18)
+    gguf.gguf_parse(synth.write_gguf({}, [("w", (256,), 18, np.zeros(98, np.uint8))]))
+  kv, t = gguf.gguf_parse(synth.write_gguf({}, [("w", (256,), 12, np.zeros(144, np.uint8))]))      # Q4_K: sized and listed
+  assert t["w"].ggml_type == 12 and t["w"].data.size == 144
 
 
 def test_split_file_names():

@@ -229,3 +229,31 @@ def test_from_gguf_output_head_variants(output):
     got.append(tok)
     if len(got) == 16: break
   assert got == want
+
+
+def test_from_gguf_mixed_block_formats():
+  """A file that mixes block formats like the K-quant files of the reference's model zoo (Q4_K blocks with Q6_K for attn_v / ffn_down / the
+  head, a Q5_K output projection, Q4_1 / Q5_0 / Q5_1 elsewhere, a Q4_K embedding): loads onto the dense fp16 path and decodes like the oracle."""
+  from tinygrad_b200 import gguf
+  from tinygrad_b200.model import TransformerConfig
+  kw = dict(num_blocks=2, dim=256, hidden_dim=512, n_heads=4, n_kv_heads=2, norm_eps=1e-6, vocab_size=320, head_dim=64, rope_theta=10000.0,
+            rope_dim=64, max_context=64)
+  cfg = TransformerConfig(**kw)
+  mixed = {"attn_q": 12, "attn_k": 3, "attn_v": 14, "attn_output": 13, "ffn_gate": 6, "ffn_up": 7, "ffn_down": 14}
+  img = synth.dense_model_gguf(cfg, 12, seed=23, arch="qwen2", embd_std=0.3, output="q6_k", mixed=mixed, embd_type=12)
+  kv, t = gguf.gguf_load(img)
+  assert {t[f"blk.0.{n}.weight"].ggml_type for n in mixed} == set(mixed.values())
+  w = {}
+  for name, g in t.items():
+    if g.ggml_type in (0, 1, 30): w[name] = g.numpy().astype(np.float32)
+    else: w[name] = gq.dequantize(g.data, g.n_elems, g.ggml_type).astype(np.float16).astype(np.float32).reshape(g.shape)      # model.py:376: every tensor is cast to fp16
+  prompt = [5, 17, 300, 2, 9, 44]
+  want, want_logits = llm.Transformer(llm.Config(**kw, kv_dtype="float16"), w).generate(prompt, 12, keep_logits=True)
+  m, _ = gguf.transformer_from_gguf(img)
+  assert m.dense_blocks and m.output_type == 14
+  got = []
+  for i, tok in enumerate(m.generate(prompt)):
+    assert_close(m.read_logits(), want_logits[i], tol=3e-2, what=f"mixed-format logits at step {i}")
+    got.append(tok)
+    if len(got) == 12: break
+  assert got == want

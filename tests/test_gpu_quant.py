@@ -246,3 +246,18 @@ def test_in_graph_kernels_match_oracle(tag, n_out, n_in, m):
   ref = llm.linear(x, gq.weight_matrix(raw, n_out, n_in, typ))
   assert_close(y.numpy(), ref, tol=1e-2)
   assert np.abs(y.numpy() - ref).max() <= 5e-4 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("tag,typ", [("q4_1", 3), ("q5_0", 6), ("q5_1", 7), ("q4_k", 12), ("q5_k", 13)])
+def test_other_block_formats_bit_exact(golden, tag, typ):
+  """Q4_1, Q5_0, Q5_1, Q4_K, Q5_K dequantisation: the reference's own output (golden) and random blocks against the oracle, fp32 and fp16."""
+  from tinygrad_b200 import quant
+  g = golden("dequant2")
+  raw, n = g[f"{tag}_raw"], g[f"{tag}_f32"].size
+  np.testing.assert_array_equal(quant.dequantize(raw, n, typ, np.float32).numpy().view(np.uint32), g[f"{tag}_f32"].reshape(-1).view(np.uint32))
+  np.testing.assert_array_equal(quant.dequantize(raw, n, typ, np.float16).numpy().view(np.uint16), g[f"{tag}_f16"].reshape(-1).view(np.uint16))
+  nel, _ = synth.GGML_SIZES[typ]
+  blocks = synth.random_blocks(typ, 64, 8 * nel, np.random.default_rng(typ + 1))
+  ref = gq.dequantize(blocks, 64 * 8 * nel, typ)
+  np.testing.assert_array_equal(quant.dequantize(blocks, ref.size, typ, np.float32).numpy().view(np.uint32), ref.view(np.uint32))
+  np.testing.assert_array_equal(quant.dequantize(blocks, ref.size, typ, np.float16).numpy().view(np.uint16), ref.astype(np.float16).view(np.uint16))

@@ -170,3 +170,25 @@ def test_moe_ffn_gating_paths_match_reference(golden, tag):
   w = {"blk.0." + full: g[f"{tag}_{short}"] for short, full in names.items() if f"{tag}_{short}" in g.files}
   m = llm.Transformer.__new__(llm.Transformer); m.cfg, m.w = cfg, w
   np.testing.assert_allclose(m._feed_forward(0, g[f"{tag}_h"]), g[f"{tag}_y"], rtol=1e-4, atol=1e-5)
+
+
+TAGS2 = {"q4_1": 3, "q5_0": 6, "q5_1": 7, "q4_k": 12, "q5_k": 13}
+
+
+@pytest.mark.parametrize("tag", list(TAGS2))
+def test_other_block_formats_match_reference_and_gguf_py(golden, tag):
+  """Q4_1, Q5_0, Q5_1, Q4_K, Q5_K (tinygrad/llm/gguf.py:47-67): the numpy and the C restatement against the reference's own output,
+  bit for bit, and against gguf-py on random blocks as the reference's tests do (test/unit/test_gguf.py:50-62)."""
+  from oracle import cpu_gemv
+  typ, g = TAGS2[tag], golden("dequant2")
+  raw, n = g[f"{tag}_raw"], g[f"{tag}_f32"].size
+  want = g[f"{tag}_f32"].reshape(-1).view(np.uint32)
+  np.testing.assert_array_equal(gq.dequantize(raw, n, typ).view(np.uint32), want)
+  np.testing.assert_array_equal(cpu_gemv.dequantize(raw, n, typ).view(np.uint32), want)
+  np.testing.assert_array_equal(gq.dequantize_f16(raw, n, typ).view(np.uint16), g[f"{tag}_f16"].reshape(-1).view(np.uint16))
+  gguf = pytest.importorskip("gguf")
+  nel, nby = synth.GGML_SIZES[typ]
+  blocks = synth.random_blocks(typ, 16, 2 * nel, np.random.default_rng(typ))
+  ref = gguf.dequantize(blocks.reshape(-1, nby), gguf.GGMLQuantizationType(typ)).reshape(-1).astype(np.float32)
+  np.testing.assert_array_equal(gq.dequantize(blocks, 32 * nel, typ), ref)
+  np.testing.assert_array_equal(cpu_gemv.dequantize(blocks, 32 * nel, typ), ref)

@@ -75,6 +75,7 @@ SIGNATURES = {
   "b200q_repack": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
   "b200q_dequant_packed": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
   "b200q_gemv": (c_int, [POINTER(GemvArgs), c_void_p]),
+  "b200q_silu_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
   "b200q_tg_gemv": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
   "b200q_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
   "b200q_xq_bytes": (c_size_t, [c_int]),

@@ -143,7 +143,26 @@ cudaError_t launch_dense(const DenseParams& p0, int grid, size_t smem, cudaStrea
   return rem ? launch_dense_m<W>(p, rem, 1, grid, smem, st, pdl && !full) : cudaSuccess;
 }
 
+// out[i] = silu(gate[i]) * up[i]: the SwiGLU product behind two separate dense Linears (tinygrad/llm/model.py:137)
+__global__ void silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ out, int64_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float g = gate[i];
+    out[i] = (g / (1.f + __expf(-g))) * up[i];
+  }
+}
+
 }  // namespace
+
+extern "C" int b200q_silu_mul(const float* gate, const float* up, float* out, int64_t n, int flags, void* stream) {
+  if (!gate || !up || !out || n < 0) return B200Q_ERR_BAD_ARG;
+  if (n == 0) return B200Q_OK;
+  const int64_t blocks = (n + 255) / 256;
+  B200Q_CHECK_CUDA(launch_k(silu_mul_kernel, dim3((unsigned)(blocks < 1024 ? blocks : 1024)), dim3(256), 0, (cudaStream_t)stream, (flags & B200Q_FLAG_PDL) != 0,
+                            gate, up, out, n));
+  return B200Q_OK;
+}
 
 extern "C" int b200q_gemv_dense(const void* w, int w_dtype, int n_out, int n_in, int m, const void* x, int x_dtype, const void* norm_weight,
                                 float norm_eps, const void* bias, const void* residual, void* y, int y_dtype, int flags, void* stream) {

@@ -1,6 +1,6 @@
 // GGUF block formats: bit-exact dequantisation and the one-time lossless re-tiling
 // into the layout the GEMV kernels stream (layout described in include/b200q.h).
-// Semantics follow tinygrad/llm/gguf.py:38-72 (q_to_uint8, Q4_0 :46, Q8_0 :56, Q6_K :68-72).
+// Semantics follow tinygrad/llm/gguf.py:38-72 (q_to_uint8, Q4_0 :46, Q4_1 :47-49, Q5_0 / Q5_1 :50-55, Q8_0 :56, Q4_K / Q5_K :57-67, Q6_K :68-72).
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------
@@ -28,6 +28,28 @@ __global__ void dequant_raw_kernel(int qtype, const uint8_t* __restrict__ raw, O
   } else if (qtype == B200Q_Q8_0) {
     const uint8_t* b = raw + (i >> 5) * 34; int e = (int)(i & 31);
     v = __fmul_rn(load_f16(b), (float)(int8_t)b[2 + e]);
+  } else if (qtype == B200Q_Q4_1) {     // gguf.py:47-49: nibble * d + m; block = d, m, 16 quant bytes
+    const uint8_t* b = raw + (i >> 5) * 20; int e = (int)(i & 31);
+    int nib = (b[4 + (e & 15)] >> ((e >> 4) * 4)) & 0xF;
+    v = __fadd_rn(__fmul_rn((float)nib, load_f16(b)), load_f16(b + 2));
+  } else if (qtype == B200Q_Q5_0 || qtype == B200Q_Q5_1) {      // gguf.py:50-55: (nibble + 16 * high bit) * d + (m | -16 d)
+    const int off = qtype == B200Q_Q5_0 ? 2 : 4;
+    const uint8_t* b = raw + (i >> 5) * (qtype == B200Q_Q5_0 ? 22 : 24); int e = (int)(i & 31);
+    const uint32_t qh = b[off] | (b[off + 1] << 8) | (b[off + 2] << 16) | ((uint32_t)b[off + 3] << 24);
+    int q = ((b[off + 4 + (e & 15)] >> ((e >> 4) * 4)) & 0xF) + 16 * (int)((qh >> e) & 1);
+    const float d = load_f16(b);
+    v = __fadd_rn(__fmul_rn((float)q, d), qtype == B200Q_Q5_1 ? load_f16(b + 2) : __fmul_rn(-16.f, d));
+  } else if (qtype == B200Q_Q4_K || qtype == B200Q_Q5_K) {      // gguf.py:57-67: (d * sc) * q - dmin * mn; 8 groups of 32 with 6-bit scales / mins
+    const uint8_t* b = raw + (i >> 8) * (qtype == B200Q_Q4_K ? 144 : 176); int e = (int)(i & 255);
+    const int grp = e >> 5, j = e & 31;
+    const uint8_t* s = b + 4;
+    int sc, mn;
+    if (grp < 4) { sc = s[grp] & 63; mn = s[4 + grp] & 63; }
+    else { sc = (s[4 + grp] & 0xF) | ((s[grp - 4] >> 6) << 4); mn = (s[4 + grp] >> 4) | ((s[grp] >> 6) << 4); }
+    const uint8_t* qs = b + (qtype == B200Q_Q5_K ? 48 : 16);
+    int q = (qs[(grp >> 1) * 32 + j] >> ((grp & 1) * 4)) & 0xF;
+    if (qtype == B200Q_Q5_K) q += 16 * ((b[16 + j] >> grp) & 1);
+    v = __fsub_rn(__fmul_rn(__fmul_rn(load_f16(b), (float)sc), (float)q), __fmul_rn(load_f16(b + 2), (float)mn));
   } else {  // Q6_K: 256 elements in 210 bytes: ql[128] qh[64] scales[16] d
     const uint8_t* b = raw + (i >> 8) * 210; int e = (int)(i & 255);
     int hh = e >> 7, m = e & 127;
@@ -122,12 +144,15 @@ __global__ void dequant_packed_kernel(int qtype, const uint8_t* __restrict__ pac
 }
 
 // ---------------------------------------------------------------------------
-static bool known_qtype(int q) { return q == B200Q_Q4_0 || q == B200Q_Q8_0 || q == B200Q_Q6_K; }
+static bool known_qtype(int q) {
+  return q == B200Q_Q4_0 || q == B200Q_Q4_1 || q == B200Q_Q5_0 || q == B200Q_Q5_1 || q == B200Q_Q8_0 || q == B200Q_Q4_K || q == B200Q_Q5_K || q == B200Q_Q6_K;
+}
+static int block_elems(int q) { return (q == B200Q_Q4_K || q == B200Q_Q5_K || q == B200Q_Q6_K) ? 256 : 32; }
 
 extern "C" int b200q_dequant_raw(int qtype, const void* raw, void* out, int64_t n_elems, int out_dtype, void* stream) {
   if (!known_qtype(qtype) || (out_dtype != B200Q_F32 && out_dtype != B200Q_F16)) return B200Q_ERR_BAD_ARG;
   if (n_elems < 0 || (n_elems && (!raw || !out))) return B200Q_ERR_BAD_ARG;
-  if (n_elems % (qtype == B200Q_Q6_K ? 256 : 32)) return B200Q_ERR_BAD_SHAPE;
+  if (n_elems % block_elems(qtype)) return B200Q_ERR_BAD_SHAPE;
   if (n_elems == 0) return B200Q_OK;
   unsigned blocks = (unsigned)((n_elems + 255) / 256);
   if (out_dtype == B200Q_F32) dequant_raw_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>(qtype, (const uint8_t*)raw, (float*)out, n_elems);

@@ -13,8 +13,9 @@ import numpy as np
 
 # (elements per block, bytes per block) of the tensor types this path handles (gguf.py:20-21,25-27); other types parse
 # (so that a file can be listed) but cannot be sized here and raise like the reference's ggml_data_to_tensor does
-GGML_SIZES = {0: (1, 4), 1: (1, 2), 30: (1, 2), 2: (32, 18), 8: (32, 34), 14: (256, 210)}
-GGML_NAMES = {0: "F32", 1: "F16", 30: "BF16", 2: "Q4_0", 8: "Q8_0", 14: "Q6_K"}
+GGML_SIZES = {0: (1, 4), 1: (1, 2), 30: (1, 2), 2: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24), 8: (32, 34), 12: (256, 144), 13: (256, 176),
+              14: (256, 210)}
+GGML_NAMES = {0: "F32", 1: "F16", 30: "BF16", 2: "Q4_0", 3: "Q4_1", 6: "Q5_0", 7: "Q5_1", 8: "Q8_0", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K"}
 
 
 @dataclass
@@ -135,8 +136,10 @@ SUPPORTED_ARCH = ("llama", "qwen2")
 
 
 def transformer_from_gguf(fn, max_context: int = None, kv_dtype: str = "float16", **kwargs):
-  """-> (Transformer, kv_data), the dense decoder families this path covers (model.py:369-452).  Block Linears must be Q4_0 or
-  Q8_0 (one type for all of them); the output head may also be Q6_K / F16 / F32 (it then runs the dense GEMV).  kv_dtype is the
+  """-> (Transformer, kv_data), the dense decoder families this path covers (model.py:369-452).  Files whose block Linears are all
+  Q4_0 or all Q8_0 run the fused dequant kernels; files that mix block formats or use Q4_1 / Q5_0 / Q5_1 / Q4_K / Q5_K / Q6_K / F16 /
+  BF16 / F32 Linears (what the reference's model zoo mostly ships, tinygrad/llm/cli.py:76-94) run on dense fp16 blocks, every weight
+  dequantised once on the device.  The output head may be of any of these types.  kv_dtype is the
   cache dtype (the reference takes it from DEFAULT_FLOAT, model.py:202-203); other keyword arguments go to Transformer."""
   from .model import Transformer, TransformerConfig
   kv, t = gguf_load(fn)
@@ -152,13 +155,17 @@ def transformer_from_gguf(fn, max_context: int = None, kv_dtype: str = "float16"
                           vocab_size=len(kv["tokenizer.ggml.tokens"]), head_dim=head_dim, rope_theta=kv[f"{arch}.rope.freq_base"], rope_dim=rope_dim,
                           v_head_dim=kv.get(f"{arch}.attention.value_length", head_dim), max_context=max_context,
                           qkv_bias="blk.0.attn_q.bias" in t, kv_dtype=kv_dtype)
-  lin_types = {t[f"blk.{i}.{n}.weight"].ggml_type for i in range(cfg.num_blocks)
-               for n in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")}
-  if len(lin_types) != 1 or not lin_types <= {2, 8}:
-    raise NotImplementedError(f"block Linears must share one of Q4_0 / Q8_0, found {sorted(GGML_NAMES.get(x, x) for x in lin_types)}")
+  lin_names = [f"blk.{i}.{n}.weight" for i in range(cfg.num_blocks) for n in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")]
+  lin_types = {n: t[n].ggml_type for n in lin_names}
+  unknown = sorted({GGML_NAMES.get(x, x) for x in lin_types.values() if x not in GGML_SIZES})
+  if unknown: raise NotImplementedError(f"block Linears in formats without a dequantiser here: {unknown}")
+  # one fused type for every block Linear -> the fused kernels; anything else (mixed files, K-quants, F16 models) -> dense fp16 blocks
+  kinds = set(lin_types.values())
+  block_type = kinds.pop() if len(kinds) == 1 and kinds <= {2, 8} else max(set(lin_types.values()), key=list(lin_types.values()).count)
+  quantised = {k for k, (nel, _) in GGML_SIZES.items() if nel > 1}
   sd = {}
   for name, g in t.items():
-    if name.endswith(".weight") and g.ggml_type in (2, 8, 14) and len(g.shape) == 2:
+    if name.endswith(".weight") and g.ggml_type in quantised and len(g.shape) == 2:
       rows = g.rows()
       if arch == "llama" and "attn_q.weight" in name: rows = _permute_rope_rows(rows, n_heads, head_dim - rope_dim)
       elif arch == "llama" and "attn_k.weight" in name: rows = _permute_rope_rows(rows, n_kv)
@@ -176,6 +183,6 @@ def transformer_from_gguf(fn, max_context: int = None, kv_dtype: str = "float16"
   if emb.ggml_type not in (0, 1, 30):
     from .quant import dequantize
     sd["token_embd.weight"] = dequantize(np.ascontiguousarray(emb.data), emb.n_elems, emb.ggml_type, np.float16).numpy().reshape(emb.shape)
-  if "output.weight" not in t: sd["output.weight"] = np.ascontiguousarray(out_t.data) if out_t.ggml_type in (2, 8, 14) else out_t.numpy()
-  model = Transformer(cfg, sd, ggml_type=lin_types.pop(), output_type=out_t.ggml_type, **kwargs)
+  if "output.weight" not in t: sd["output.weight"] = np.ascontiguousarray(out_t.data) if out_t.ggml_type in quantised else out_t.numpy()
+  model = Transformer(cfg, sd, ggml_type=block_type, output_type=out_t.ggml_type, linear_types=lin_types, **kwargs)
   return model, kv

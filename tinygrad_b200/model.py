@@ -12,7 +12,7 @@ from dataclasses import dataclass
 import numpy as np
 from . import _lib, quant
 from ._lib import check, F32, F16, EPI_LINEAR, EPI_SILU_MUL, FLAG_PDL
-from .runtime import DeviceBuffer, Stream, Graph, Event
+from .runtime import DeviceBuffer, Stream, Graph, Event, synchronize as runtime_sync
 import ctypes
 
 
@@ -60,7 +60,7 @@ DEFAULT_HANDOVER = ("attn_o",)
 class Transformer:
   def __init__(self, config: TransformerConfig, state_dict: dict, ggml_type: int = _lib.Q4_0, n_split: int = 0, use_pdl: bool = True,
                use_graph: bool = True, gemv_max_ctas: int = 0, handover=None, tp=None, output_type: int = None, prefill_rows: int = 64,
-               prefill_chunk: int = 512, batch: int = 1, engine: str = None):
+               prefill_chunk: int = 512, batch: int = 1, engine: str = None, linear_types: dict = None):
     """state_dict: the reference's tensor names -> numpy arrays; Linear weights as raw
     GGUF block bytes (uint8), embeddings / norms / biases as fp16.
     tp: a tensor_parallel.TPGroup; `config` is then the FULL model and `state_dict` this rank's shard (shard_state_dict).
@@ -70,6 +70,9 @@ class Transformer:
     engine: how a one-token step runs.  "step": one persistent kernel for the whole step (b200q_decode_step); "chain": five launches per
     block chained with programmatic dependent launch and replayed as a CUDA graph (the default: at batch 1 it measured faster, the
     grid-wide waits inside one kernel costing more than kernel boundaries do).
+    linear_types: state-dict name -> GGML type of block Linear weights whose type is not `ggml_type` (files that mix block formats, e.g.
+    Q4_K with Q6_K).  Unless every block Linear is of one fused type (Q4_0 / Q8_0) the blocks run on the dense-weight GEMV: every
+    weight is dequantised once to fp16 on the device -- the cast the reference applies to every loaded tensor (model.py:376).
     batch: sequences decoded in lock-step (`generate_batch`): one KV cache per sequence, every Linear a tensor-core GEMM over the
     batch rows (the reference's forward on tokens [B, T], model.py:358-364; its cache is sized by the first call's batch, model.py:200-203)."""
     self.tp, self.full_config = tp, config
@@ -90,7 +93,37 @@ class Transformer:
     assert self.q_dim % 16 == 0 and self.kv_dim % 16 == 0, "q/k/v are packed back to back in whole 16-row tiles"
     self.blk = []
     self.weight_bytes = 0
-    for i in range(c.num_blocks):
+    lt = dict(linear_types or {})
+    names7 = ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")
+    self.dense_blocks = ggml_type not in (_lib.Q4_0, _lib.Q8_0) or any(lt.get(f"blk.{i}.{n}.weight", ggml_type) != ggml_type
+                                                                      for i in range(c.num_blocks) for n in names7 if f"blk.{i}.{n}.weight" in sd)
+    if self.dense_blocks:
+      assert tp is None and batch == 1 and not c.num_experts, "the dense-weight path serves single-sequence dense models on one GPU"
+      def dense16(name, n_out, n_in):       # -> fp16 [n_out, n_in] on the device, whatever the tensor's type
+        raw, typ = sd[name], lt.get(name, ggml_type)
+        if typ in quant.GGML_QUANT: return quant.dequantize(np.ascontiguousarray(raw).view(np.uint8).reshape(-1), n_out * n_in, typ, np.float16)
+        return DeviceBuffer.from_numpy(np.asarray(raw).astype(np.float16).reshape(n_out, n_in))
+    for i in range(c.num_blocks if self.dense_blocks else 0):
+      b = _Block()
+      parts = [dense16(f"blk.{i}.attn_{n}.weight", rows, c.dim) for n, rows in (("q", self.q_dim), ("k", self.kv_dim), ("v", self.kv_dim))]
+      b.qkv = DeviceBuffer(2 * qkv_rows * c.dim)
+      off = 0
+      for part in parts:
+        check(_lib.load().b200q_memcpy_d2d(b.qkv.ptr + off, part.ptr, part.nbytes, None)); off += part.nbytes
+      runtime_sync()
+      b.qkv_bias = DeviceBuffer.from_numpy(np.concatenate([np.asarray(sd[f"blk.{i}.attn_{n}.bias"], dtype=np.float16) for n in "qkv"])) if c.qkv_bias else None
+      b.o_w = dense16(f"blk.{i}.attn_output.weight", c.dim, self.q_dim)
+      b.gate_w, b.up_w = dense16(f"blk.{i}.ffn_gate.weight", c.hidden_dim, c.dim), dense16(f"blk.{i}.ffn_up.weight", c.hidden_dim, c.dim)
+      b.down_w = dense16(f"blk.{i}.ffn_down.weight", c.dim, c.hidden_dim)
+      b.moe = b.router = None
+      b.attn_norm = DeviceBuffer.from_numpy(np.asarray(sd[f"blk.{i}.attn_norm.weight"], dtype=np.float16))
+      b.ffn_norm = DeviceBuffer.from_numpy(np.asarray(sd[f"blk.{i}.ffn_norm.weight"], dtype=np.float16))
+      kvdt = np.float16 if c.kv_dtype == "float16" else np.float32
+      b.k_cache = DeviceBuffer.empty((batch, c.n_kv_heads, c.max_context, c.head_dim), kvdt, zero=True)
+      b.v_cache = DeviceBuffer.empty((batch, c.n_kv_heads, c.max_context, c.head_dim), kvdt, zero=True)
+      self.blk.append(b)
+      self.weight_bytes += 2 * (qkv_rows * c.dim + c.dim * self.q_dim + 3 * c.hidden_dim * c.dim)
+    for i in range(0 if self.dense_blocks else c.num_blocks):
       b = _Block()
       b.qkv = DeviceBuffer(quant.packed_bytes(ggml_type, qkv_rows, c.dim))
       off = 0
@@ -129,6 +162,7 @@ class Transformer:
       self.blk.append(b)
       nel, nby = quant.GGML_QUANT[ggml_type]
       self.weight_bytes += (qkv_rows * c.dim + c.dim * self.q_dim + (0 if c.num_experts else 3 * c.hidden_dim * c.dim)) // nel * nby
+    if self.dense_blocks: self.up_buf = DeviceBuffer.empty((c.hidden_dim,), np.float32, zero=True)
     self.output_type = ggml_type if output_type is None else output_type
     if self.output_type in (_lib.Q4_0, _lib.Q8_0):
       self.output = quant.repack(sd["output.weight"], c.vocab_size, c.dim, self.output_type)
@@ -155,7 +189,7 @@ class Transformer:
     self.argmax_scratch = DeviceBuffer(_lib.load().b200q_argmax_scratch_bytes(), zero=True)
     # Quantised activation hand-over between consecutive kernels (needs whole 128-wide groups everywhere).  Each edge of
     # the chain can be switched on its own: attn_o (attention -> output projection), o_gateup, gateup_down, down_qkv.
-    can = c.head_dim == 128 and c.dim % 128 == 0 and c.hidden_dim % 128 == 0 and self.q_dim % 128 == 0
+    can = c.head_dim == 128 and c.dim % 128 == 0 and c.hidden_dim % 128 == 0 and self.q_dim % 128 == 0 and not self.dense_blocks
     all_edges = ("attn_o", "o_gateup", "gateup_down", "down_qkv")
     if handover is None: edges = DEFAULT_HANDOVER
     elif isinstance(handover, str): edges = tuple(e for e in handover.split(",") if e)
@@ -171,17 +205,17 @@ class Transformer:
     if "gateup_down" in self.edges: self.xq_act = DeviceBuffer(xqb(c.hidden_dim), zero=True)
     self._graphs = {}
     self._cached_tokens: list = []
-    self.prefill_rows = prefill_rows if (tp is None and c.hidden_dim % 8 == 0 and c.head_dim in (16, 32, 64, 128)) else 0
+    self.prefill_rows = prefill_rows if (tp is None and not self.dense_blocks and c.hidden_dim % 8 == 0 and c.head_dim in (16, 32, 64, 128)) else 0
     self.prefill_chunk, self._pf, self._batch_logits, self._skinny_ws, self._batch_graph = max(1, prefill_chunk), None, None, None, None
     self.is_moe, self._host_pos = c.num_experts > 0, 0
     if self.is_moe:
       assert tp is None and c.head_dim in (16, 32, 64, 128), "the mixture-of-experts model runs on the row path of one GPU"
       self.prefill_rows = 1
-    self.launches_per_step = 5 * c.num_blocks + 3
+    self.launches_per_step = (7 if self.dense_blocks else 5) * c.num_blocks + 3
     # ---- the whole-step kernel: a device table of the blocks' pointers, its workspace, and the two argument blocks (with / without head)
     self._step_args = None
     if engine not in (None, "step", "chain"): raise ValueError(f"unknown engine {engine!r}")
-    if engine == "step" and tp is None and not self.is_moe and batch == 1 and not isinstance(self.output, quant.DenseWeight) and self.output_type == ggml_type:
+    if engine == "step" and tp is None and not self.is_moe and not self.dense_blocks and batch == 1 and not isinstance(self.output, quant.DenseWeight) and self.output_type == ggml_type:
       lib = _lib.load()
       table = (_lib.DecodeLayer * c.num_blocks)(*[_lib.DecodeLayer(b.qkv.ptr, b.qkv_bias.ptr if b.qkv_bias else None, b.attn_output.buf.ptr, b.gate_up.buf.ptr,
                                                                   b.ffn_down.buf.ptr, b.attn_norm.ptr, b.ffn_norm.ptr, b.k_cache.ptr, b.v_cache.ptr) for b in self.blk])
@@ -229,7 +263,18 @@ class Transformer:
       ho = "down_qkv" in e
       check(lib.b200q_embed(self.token_embd.ptr, self.tokens.ptr, self.pos.ptr, self.x.ptr, c.dim, vocab_full, c.max_context,
                             self.xq_a.ptr if ho else None, self.blk[0].attn_norm.ptr if ho else None, self.ss_a.ptr if ho else None, fl, s))
-    for i, b in enumerate(self.blk):
+    for i, b in enumerate(self.blk if self.dense_blocks else ()):
+      # dense-weight blocks: the same step on fp16 matrices, one launch per Linear (norm / bias / residual fused as in the quantised GEMV)
+      quant.gemv_dense(b.qkv, F16, qkv_rows, c.dim, self.x, self.qkv, norm_weight=b.attn_norm, norm_eps=c.norm_eps, bias=b.qkv_bias, flags=fl, stream=s)
+      a = _lib.AttnArgs(self.qkv.ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, self.pos.ptr, self.attn.ptr, self.attn_scratch.ptr,
+                        c.n_heads, c.n_kv_heads, c.head_dim, c.rope_dim, c.max_context, self.n_split, fl, None)
+      check(lib.b200q_attn_decode(ctypes.byref(a), s))
+      quant.gemv_dense(b.o_w, F16, c.dim, self.q_dim, self.attn, self.x, residual=self.x, flags=fl, stream=s)
+      quant.gemv_dense(b.gate_w, F16, c.hidden_dim, c.dim, self.x, self.act, norm_weight=b.ffn_norm, norm_eps=c.norm_eps, flags=fl, stream=s)
+      quant.gemv_dense(b.up_w, F16, c.hidden_dim, c.dim, self.x, self.up_buf, norm_weight=b.ffn_norm, norm_eps=c.norm_eps, flags=fl, stream=s)
+      check(lib.b200q_silu_mul(self.act.ptr, self.up_buf.ptr, self.act.ptr, c.hidden_dim, fl, s))
+      quant.gemv_dense(b.down_w, F16, c.dim, c.hidden_dim, self.act, self.x, residual=self.x, flags=fl, stream=s)
+    for i, b in enumerate(() if self.dense_blocks else self.blk):
       nxt_norm = self.blk[i + 1].attn_norm if i + 1 < len(self.blk) else self.output_norm
       out_b = dict(xq_out=self.xq_b, xq_out_norm_weight=b.ffn_norm, ss_out=self.ss_b) if "o_gateup" in e else {}
       out_act = dict(xq_out=self.xq_act) if "gateup_down" in e else {}

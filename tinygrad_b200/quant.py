@@ -12,7 +12,8 @@ from . import _lib
 from ._lib import check, Q4_0, Q8_0, Q6_K, F32, F16, EPI_LINEAR, EPI_SILU_MUL, FLAG_PDL
 from .runtime import DeviceBuffer, ptr_of, stream_ptr
 
-GGML_QUANT = {Q4_0: (32, 18), Q8_0: (32, 34), Q6_K: (256, 210)}   # tinygrad/llm/gguf.py:20-21
+# (elements, bytes) per block of the formats the dequantiser covers (tinygrad/llm/gguf.py:20-21); Q4_0 and Q8_0 also have fused kernels
+GGML_QUANT = {Q4_0: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24), Q8_0: (32, 34), 12: (256, 144), 13: (256, 176), Q6_K: (256, 210)}
 _DT = {np.dtype(np.float32): F32, np.dtype(np.float16): F16}
 
 

@@ -47,6 +47,19 @@ def q6_k_blocks(n_out: int, n_in: int, rng, scale_std: float = 0.001) -> np.ndar
   return out.reshape(-1)
 
 
+def random_blocks(ggml_type: int, n_out: int, n_in: int, rng, scale_std: float = 0.01) -> np.ndarray:
+  """Raw blocks of any of the sized block types: random bytes, with sane (finite, small) fp16 values where the format keeps scales."""
+  nel, nby = GGML_SIZES[ggml_type]
+  nb = n_out * n_in // nel
+  out = rng.integers(0, 256, (nb, nby), dtype=np.uint8)
+  for off in F16_FIELDS[ggml_type]:
+    out[:, off:off + 2] = np.abs(rng.standard_normal(nb, dtype=np.float32) * scale_std).astype(np.float16).view(np.uint8).reshape(nb, 2)
+  return out.reshape(-1)
+
+
+# {ggml_type: (elements, bytes)} of every block format the dequantisers cover (tinygrad/llm/gguf.py:20-21), and where their fp16 fields sit
+GGML_SIZES = {2: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24), 8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210)}
+F16_FIELDS = {2: (0,), 3: (0, 2), 6: (0,), 7: (0, 2), 8: (0,), 12: (0, 2), 13: (0, 2), 14: (208,)}
 BLOCK_MAKERS = {Q4_0: q4_0_blocks, Q8_0: q8_0_blocks, Q6_K: q6_k_blocks}
 
 
@@ -146,9 +159,12 @@ def write_gguf(kv: dict, tensors: list, version: int = 3) -> bytes:
   return head + b"\0" * ((-len(head)) % align) + b"".join(blobs)
 
 
-def dense_model_gguf(cfg, ggml_type: int = Q4_0, seed: int = 0, arch: str = "llama", embd_std: float = 0.02, output: str = "same") -> bytes:
+def dense_model_gguf(cfg, ggml_type: int = Q4_0, seed: int = 0, arch: str = "llama", embd_std: float = 0.02, output: str = "same", mixed: dict = None,
+                     embd_type: int = 1) -> bytes:
   """A random-init dense model as a GGUF file image.  output: "same" (head in ggml_type), "f16", "bf16", "f32", "q6_k", or "tied" (no output.weight).
-  For arch "llama" the q/k rows are stored as given; the loader applies the family's RoPE row permutation."""
+  For arch "llama" the q/k rows are stored as given; the loader applies the family's RoPE row permutation.
+  mixed: Linear short name ("attn_v", "ffn_down", "output", ...) -> GGML type for those Linears (random blocks of that format), as real
+  files mix K-quants; embd_type: GGML type of token_embd (1 = F16; a block format: random blocks)."""
   sd = dense_model_raw(cfg, ggml_type, seed=seed, embd_std=embd_std)
   shapes = {n + ".weight": (o, i) for n, o, i in linear_names(cfg)}
   kv = {"general.architecture": arch, "general.alignment": 32, f"{arch}.context_length": cfg.max_context, f"{arch}.block_count": cfg.num_blocks,
@@ -168,6 +184,15 @@ def dense_model_gguf(cfg, ggml_type: int = Q4_0, seed: int = 0, arch: str = "lla
         arr, typ = ((rng.standard_normal((cfg.vocab_size, cfg.dim), dtype=np.float32) * 0.05).view(np.uint32) >> 16).astype(np.uint16), 30
       else: arr, typ = (rng.standard_normal((cfg.vocab_size, cfg.dim), dtype=np.float32) * 0.05).astype(np.float16), 1
       tensors.append((name, (cfg.vocab_size, cfg.dim), typ, arr))
-    elif name in shapes: tensors.append((name, shapes[name], ggml_type, arr))
+    elif name in shapes:
+      short = name[:-len(".weight")].split(".")[-1]
+      if mixed and short in mixed:
+        typ = mixed[short]
+        arr = random_blocks(typ, *shapes[name], np.random.default_rng(name_seed(name, seed + 7)), scale_std=0.004 if typ in (12, 13) else (0.0008 if typ == 14 else 0.02))
+        tensors.append((name, shapes[name], typ, arr))
+      else: tensors.append((name, shapes[name], ggml_type, arr))
+    elif name == "token_embd.weight" and embd_type != 1:
+      arr = random_blocks(embd_type, cfg.vocab_size, cfg.dim, np.random.default_rng(name_seed(name, seed + 7)), scale_std=0.05)
+      tensors.append((name, (cfg.vocab_size, cfg.dim), embd_type, arr))
     else: tensors.append((name, arr.shape, 1, arr))                  # fp16 embeddings / norms / biases
   return write_gguf(kv, tensors)
