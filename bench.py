@@ -192,18 +192,32 @@ def ep_moe_record(ranks, reps: int = 10) -> dict:
   x = moe.to_bf16_bits(rng.standard_normal((T, D), dtype=np.float32))
   logits = rng.standard_normal((T, E), dtype=np.float32)
   T_l, E_l = T // G, E // G
-  shard = ep.ExpertParallelMoE(ranks, wg[r * E_l:(r + 1) * E_l], wu[r * E_l:(r + 1) * E_l], wd[r * E_l:(r + 1) * E_l], E, k, T, 1)
+  from tinygrad_b200 import tensor_parallel as tpar
+  sl = slice(r * E_l, (r + 1) * E_l)
   dx, dl = DeviceBuffer.from_numpy(x[r * T_l:(r + 1) * T_l]), DeviceBuffer.from_numpy(logits[r * T_l:(r + 1) * T_l])
-  out = shard(dx, dl, T_l).numpy()
-  for _ in range(3): shard(dx, dl, T_l)
-  runtime.synchronize(); ranks.barrier()
-  ms = ranks.max(shard.timed(dx, dl, T_l, reps))
   full = moe.MxMoE(wg, wu, wd, k, 1)
   ref = full(DeviceBuffer.from_numpy(x), DeviceBuffer.from_numpy(logits), T).numpy()[r * T_l:(r + 1) * T_l]
-  same = ranks.sum(float(np.array_equal(out, ref))) == G
+  del full
+  res = {}
+  for name in ("peer", "nccl"):
+    if name == "peer":
+      shard = ep.PeerExpertParallelMoE(tpar.TPGroup(ranks, "peer"), wg[sl], wu[sl], wd[sl], E, k, T, 1)
+      shard.connect()
+    else: shard = ep.ExpertParallelMoE(ranks, wg[sl], wu[sl], wd[sl], E, k, T, 1)
+    runtime.synchronize(); ranks.barrier()
+    out = shard(dx, dl, T_l).numpy()
+    for _ in range(3): shard(dx, dl, T_l)
+    runtime.synchronize(); ranks.barrier()
+    ms = ranks.max(shard.timed(dx, dl, T_l, reps))
+    same = ranks.sum(float(np.array_equal(out, ref))) == G
+    status = ranks.max(float(runtime.mx_status()))
+    res[name] = {"ms_per_layer": round(ms, 4), "bit_identical_to_one_gpu": bool(same), "wait_status": int(status), "exchange": shard.exchange_kind}
+    del shard
   flops = T * k * 3 * 2 * D * F
-  return {"workload": f"configs[3] one layer, expert-parallel x{G}: {E_l} experts and {T_l} tokens per rank", "ms_per_layer": round(ms, 4),
-          "tflops": round(flops / ms / 1e9, 1), "bit_identical_to_one_gpu": bool(same), "exchange": shard.exchange_kind}
+  best = res["peer"]
+  return {"workload": f"configs[3] one layer, expert-parallel x{G}: {E_l} experts and {T_l} tokens per rank", "ms_per_layer": best["ms_per_layer"],
+          "tflops": round(flops / best["ms_per_layer"] / 1e9, 1), "bit_identical_to_one_gpu": best["bit_identical_to_one_gpu"] and res["nccl"]["bit_identical_to_one_gpu"],
+          "exchange": best["exchange"], "by_exchange": res}
 
 
 def tp70b_record(ranks, steps: int, warmup: int) -> dict:

@@ -46,6 +46,7 @@ extern "C" {
 /* GEMV epilogues */
 #define B200Q_EPI_LINEAR 0   /* y = W x (+bias) (+residual) */
 #define B200Q_EPI_SILU_MUL 1 /* weights packed with b200q_repack(raw0=gate, raw1=up): y = silu(gate x) * (up x) */
+#define B200Q_MAX_PEERS 8    /* ranks of one tensor- / expert-parallel group (the GPUs of one node) */
 /* launch flags */
 #define B200Q_FLAG_PDL 1     /* launch with programmatic dependent launch (overlaps the weight prefetch with the previous kernel) */
 
@@ -160,9 +161,33 @@ typedef struct b200q_gemv_args {
   float residual_scale;     /* the residual is multiplied by this before it is added; 0 means 1.  A row-parallel shard of a
                                tensor-parallel linear adds residual / n_ranks so that the all-reduce of the shards yields
                                W x + residual (tinygrad shards the same linears by axis, examples/llama3.py:233-243) */
+  /* Sharded linears without a collective library: with n_peers > 0 the output row (m == 1, EPI_LINEAR, bias and residual as
+   * given) is ALSO stored into slot `peer_rank` of a mailbox on every rank, peer_mailboxes[d] being rank d's mailbox (fp32 words
+   * [n_peers][n_out], this rank's own included) as mapped into this process (b200q_ipc_open).  b200q_mailbox_reduce on each rank
+   * then sums the slots (row-split linear: all-reduce) or copies them out (column-split: all-gather).  `y` may be NULL. */
+  void* const* peer_mailboxes;   /* host array [n_peers] of device pointers */
+  int n_peers, peer_rank;
 } b200q_gemv_args;
 int b200q_gemv(const b200q_gemv_args* args, void* stream);
 size_t b200q_xq_bytes(int n);
+
+/* ---- collectives over peer memory (NVLink), no communication library in the data path ---------------------------------
+ * Replaces what the reference expands a sharded reduce into: copies of every shard to every device plus add kernels
+ * (`handle_allreduce`, tinygrad/schedule/allreduce.py:6-58, over `CUDAAllocator._transfer`, tinygrad/runtime/ops_cuda.py:88-94).
+ * A mailbox is a device buffer of 32-bit words [n_slots][n]; a producer (b200q_gemv with n_peers > 0, running on any rank) stores
+ * finished fp32 values into slot = its rank, on every rank; an untouched word holds the all-ones pattern.  The consumer polls
+ * the words themselves (each is empty or complete: no flag, no fence) and puts the empty pattern back as it reads, so the same
+ * mailbox serves the next step; two collectives in a row must use two different mailboxes.
+ * b200q_mailbox_reduce: out[i] = (residual ? residual[i] : 0) + slot 0 [i] + slot 1 [i] + ... in slot order (bit-identical on all ranks).
+ *   With n_slots == 1 it is a plain hand-over (all-gather: every rank's producer fills its own part of the one slot).
+ *   spin_limit: polls per word before the kernel gives up (0 = default, about a second); on expiry the word counts as 0 and the
+ *   status word (b200q_status_read_clear) is set to 1.  The mailbox starts out filled with 0xFF bytes (b200q_memset).
+ * b200q_ipc_export / _open / _close: a device allocation (b200q_malloc) made visible to the other processes of the node
+ * (cudaIpcGetMemHandle / cudaIpcOpenMemHandle); the 64-byte handle travels by any host channel. */
+int b200q_mailbox_reduce(void* mailbox, int n_slots, int n, const float* residual, float* out, int spin_limit, int flags, void* stream);
+int b200q_ipc_export(void* device_ptr, void* handle64_out);
+int b200q_ipc_open(const void* handle64, void** device_ptr);
+int b200q_ipc_close(void* device_ptr);
 
 /* Dense (unquantised) Linear at decode: y[m, n_out] = f(x)[m, n_in] . W[n_out, n_in]^T for a weight stored row-major
  * as fp16, bf16 or fp32 (w_dtype) - the Linears a GGUF file leaves unquantised (router ffn_gate_inp, F16 models).
@@ -399,6 +424,49 @@ int b200q_grouped_mxfp8_gemm_swiglu(const void* a_q, const void* a_e8, const voi
                                     int m_total, int n, int k, void* act_q, void* act_e8, void* stream);
 int b200q_grouped_mxfp8_gemm(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts,
                              int m_total, int n, int k, void* c_bf16, void* stream);
+
+/* ---- expert-parallel exchange over peer memory (NVLink), planned on the device ------------------------------------------
+ * `dispatch` / `combine` (extra/gemm/moe_routing.py:124-131) ACROSS ranks: experts split contiguously over the ranks (rank r owns
+ * experts r * E / R ...), tokens split over the ranks at the input.  No communication library and no host read in the data path.
+ * Per layer and rank, on one stream:
+ *   b200q_moe_route_pad(pad = 1)   this rank's tokens over ALL experts, compact expert-sorted order, per-expert counts
+ *   b200q_ep_publish_counts        the counts into slot `rank` of every rank's counts mailbox
+ *   b200q_ep_plan                  waits for all ranks' counts; send_base[e] = first row, inside the owning rank's grouped buffer, of
+ *                                  this rank's rows for expert e (groups padded to 256 rows, sources in rank order -- the placement the
+ *                                  single-device `route` gives the concatenated tokens); off_local [E/R + 1] = this rank's group starts
+ *   b200q_ep_dispatch              quantises each token row once (E4M3 + E8M0) and stores it into the owners' a_q / a_e8 buffers,
+ *                                  records remote_row[t * k + j], then raises "rows landed" on every rank
+ *   b200q_ep_wait(which = 0)       consumes the "rows landed" flags of all ranks
+ *   b200q_grouped_mxfp8_gemm[_swiglu] x 2 on (a_q, a_e8, off_local, E / R, m_max) -> y [m_max, d] bf16
+ *   b200q_ep_signal_results        raises "results ready" on every rank
+ *   b200q_ep_wait(which = 1)       consumes the "results ready" flags
+ *   b200q_ep_combine               out[t] = sum_j weights[t, j] * y_owner[remote_row[t, j]] pulled from the owners' y buffers
+ * The peer-visible buffers (b200q_malloc + b200q_ipc_export / _open) are given as arrays of n_ranks pointers, this rank's own included:
+ * counts_all uint32 [n_ranks][n_experts], filled with 0xFF bytes at set-up; flags uint32 [2][n_ranks], zeroed at set-up; a_q / a_e8 /
+ * y as the grouped GEMM takes them, m_max rows, zeroed at set-up (rows between the groups are never written).  Waits are bounded; on
+ * expiry the kernels carry on with zeros and b200q_mx_status_read_clear reports 1; a plan that does not fit m_max reports 2. */
+typedef struct b200q_ep_args {
+  int n_ranks, rank, n_experts, k, d_model, n_tokens, m_max;
+  const int32_t* topi;       /* routing tables of THIS rank's tokens (b200q_moe_route_pad, pad = 1) */
+  const int32_t* dest;
+  const int32_t* off;
+  const int32_t* counts;
+  void* const* counts_all;   /* [n_ranks] pointers, likewise the next four */
+  void* const* a_q;
+  void* const* a_e8;
+  void* const* y;
+  void* const* flags;
+  int32_t* send_base;        /* [n_experts], written by the plan */
+  int32_t* off_local;        /* [n_experts / n_ranks + 1] */
+  int32_t* remote_row;       /* [n_tokens * k], written by dispatch */
+  void* scratch;             /* 4 zeroed bytes */
+} b200q_ep_args;
+int b200q_ep_publish_counts(const b200q_ep_args* args, void* stream);
+int b200q_ep_plan(const b200q_ep_args* args, void* stream);
+int b200q_ep_dispatch(const b200q_ep_args* args, const void* x_bf16, void* stream);
+int b200q_ep_wait(const b200q_ep_args* args, int which, int spin_limit, void* stream);
+int b200q_ep_signal_results(const b200q_ep_args* args, void* stream);
+int b200q_ep_combine(const b200q_ep_args* args, const float* weights, void* out_bf16, void* stream);
 
 #ifdef __cplusplus
 }

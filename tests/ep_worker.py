@@ -20,8 +20,14 @@ def main():
   x = moe.to_bf16_bits(rng.standard_normal((T, D), dtype=np.float32))
   logits = rng.standard_normal((T, E), dtype=np.float32)
   T_l, E_l = T // G, E // G
-  for mode in ((1,) if big else (0, 1)):
-    shard = ep.ExpertParallelMoE(ranks, wg[r * E_l:(r + 1) * E_l], wu[r * E_l:(r + 1) * E_l], wd[r * E_l:(r + 1) * E_l], E, k, T, mode)
+  from tinygrad_b200 import tensor_parallel as tpar
+  sl = slice(r * E_l, (r + 1) * E_l)
+  for mode, kind in ([(1, "peer"), (1, "nccl")] if big else [(0, "peer"), (1, "peer"), (0, "nccl"), (1, "nccl")]):
+    if kind == "peer":
+      shard = ep.PeerExpertParallelMoE(tpar.TPGroup(ranks, "peer"), wg[sl], wu[sl], wd[sl], E, k, T, mode)
+      shard.connect()
+    else: shard = ep.ExpertParallelMoE(ranks, wg[sl], wu[sl], wd[sl], E, k, T, mode)
+    ranks.barrier()
     dx, dl = DeviceBuffer.from_numpy(x[r * T_l:(r + 1) * T_l]), DeviceBuffer.from_numpy(logits[r * T_l:(r + 1) * T_l])
     out = shard(dx, dl, T_l).numpy()
     if big:
@@ -32,12 +38,15 @@ def main():
       for _ in range(10): shard(dx, dl, T_l)
       torch.cuda.synchronize(); ranks.barrier()
       ms = ranks.max((time.perf_counter() - t0) * 1e3 / 10)
-      if r == 0: print(f"ep bench: {G} ranks, {T} tokens, {ms:.3f} ms per layer, {T * k * 3 * 2 * D * F / ms / 1e9:.1f} TFLOP/s useful (host-synchronised exchange)", flush=True)
+      if r == 0: print(f"ep bench [{kind}]: {G} ranks, {T} tokens, {ms:.3f} ms per layer, {T * k * 3 * 2 * D * F / ms / 1e9:.1f} TFLOP/s useful", flush=True)
     full = moe.MxMoE(wg, wu, wd, k, mode)
     ref = full(DeviceBuffer.from_numpy(x), DeviceBuffer.from_numpy(logits), T).numpy()[r * T_l:(r + 1) * T_l]
     if not np.array_equal(out, ref):
       bad = int((out != ref).sum())
-      print(f"rank {r} mode {mode}: {bad} of {out.size} bf16 values differ from the single-GPU result", flush=True)
+      print(f"rank {r} mode {mode} kind {kind}: status {runtime.mx_status()}, {bad} of {out.size} bf16 values differ from the single-GPU result", flush=True)
+      os._exit(1)
+    if runtime.mx_status() != 0:
+      print(f"rank {r} mode {mode} kind {kind}: a bounded wait ran out", flush=True)
       os._exit(1)
   ranks.barrier()
   if r == 0: print(f"ep ok {G}", flush=True)

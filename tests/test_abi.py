@@ -33,7 +33,7 @@ def test_header_is_plain_c_and_structs_match_ctypes(tmp_path):
   subprocess.run([cc, "-std=c11", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", str(hdr)], check=True)
   subprocess.run([cxx, "-std=c++17", "-fsyntax-only", "-x", "c++", str(hdr)], check=True)
   structs = {"b200q_gemv_args": _lib.GemvArgs, "b200q_attn_args": _lib.AttnArgs, "b200q_decode_layer": _lib.DecodeLayer,
-             "b200q_decode_step_args": _lib.DecodeStepArgs}
+             "b200q_decode_step_args": _lib.DecodeStepArgs, "b200q_ep_args": _lib.EpArgs}
   lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{hdr}"', 'int main(void) {']
   for cname, ct in structs.items():
     lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')

@@ -1,5 +1,6 @@
-"""Run under torch.distributed.run with >= 2 ranks (one per GPU): tensor-parallel greedy decode of a mid-size model,
-checked on every rank against the numpy oracle of the unsharded model.  Exit code 0 = identical token stream."""
+"""Run under torch.distributed.run with >= 2 ranks (one per GPU): tensor-parallel greedy decode of a mid-size model, with the
+library's own peer-memory collectives and with NCCL, checked on every rank against the numpy oracle of the unsharded model.
+Exit code 0 = identical token stream."""
 import os, sys, pathlib
 sys.path.insert(0, str(pathlib.Path(__file__).resolve().parent.parent))
 import numpy as np
@@ -13,8 +14,9 @@ def main():
   build.build_lib()
   ranks = Ranks(backend="nccl")
   runtime.set_device(ranks.local)
-  tp = tpar.TPGroup(ranks)
-  for typ, blk_bytes, use_graph in ((2, 18, False), (2, 18, True), (8, 34, True)):
+  kinds = [k for k in ("peer", "nccl") if f"--only-{k}" in sys.argv] or ["peer", "nccl"]
+  for kind, typ, blk_bytes, use_graph in [(k, *cfg3) for k in kinds for cfg3 in ((2, 18, False), (2, 18, True), (8, 34, True))]:
+    tp = tpar.TPGroup(ranks, kind)
     kw = dict(num_blocks=3, dim=512, hidden_dim=1536, n_heads=8, n_kv_heads=4, norm_eps=1e-5, vocab_size=2048, head_dim=64, rope_theta=500000.0,
               rope_dim=64, max_context=128, qkv_bias=(typ == 8), kv_dtype="float16")
     cfg = TransformerConfig(**kw)
@@ -33,7 +35,7 @@ def main():
       if len(got) == 12: break
     assert got == want, f"rank {ranks.rank} type {typ}: {got} != {want}"
     assert runtime.device_status() == 0
-    if ranks.rank == 0: print("config ok", typ, use_graph, flush=True)
+    if ranks.rank == 0: print("config ok", kind, typ, use_graph, flush=True)
   ranks.barrier()
   if ranks.rank == 0: print("tp ok", ranks.world, flush=True)
   os._exit(0)     # captured graphs hold NCCL work: leave without tearing the process group down

@@ -17,7 +17,7 @@ class GemvArgs(Structure):
               ("x_dtype", c_int), ("y_dtype", c_int), ("norm_weight", c_void_p), ("norm_eps", c_float), ("epilogue", c_int),
               ("bias", c_void_p), ("residual", c_void_p), ("y", c_void_p), ("flags", c_int), ("max_ctas", c_int),
               ("xq_in", c_void_p), ("ss_in", c_void_p), ("ss_count", c_int), ("xq_out", c_void_p), ("xq_out_norm_weight", c_void_p),
-              ("ss_out", c_void_p), ("residual_scale", c_float)]
+              ("ss_out", c_void_p), ("residual_scale", c_float), ("peer_mailboxes", POINTER(c_void_p)), ("n_peers", c_int), ("peer_rank", c_int)]
 
 
 class AttnArgs(Structure):
@@ -38,6 +38,13 @@ class DecodeStepArgs(Structure):
               ("rope", c_void_p), ("tokens", c_void_p), ("pos", c_void_p), ("x", c_void_p), ("qkv", c_void_p), ("attn", c_void_p),
               ("act", c_void_p), ("logits", c_void_p), ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("with_head", c_int), ("profile_stamps", c_int),
               ("profile", c_void_p)]
+
+
+class EpArgs(Structure):
+  _fields_ = [("n_ranks", c_int), ("rank", c_int), ("n_experts", c_int), ("k", c_int), ("d_model", c_int), ("n_tokens", c_int), ("m_max", c_int),
+              ("topi", c_void_p), ("dest", c_void_p), ("off", c_void_p), ("counts", c_void_p), ("counts_all", POINTER(c_void_p)),
+              ("a_q", POINTER(c_void_p)), ("a_e8", POINTER(c_void_p)), ("y", POINTER(c_void_p)), ("flags", POINTER(c_void_p)),
+              ("send_base", c_void_p), ("off_local", c_void_p), ("remote_row", c_void_p), ("scratch", c_void_p)]
 
 
 # name -> (restype, argtypes); every symbol include/b200q.h declares
@@ -75,6 +82,16 @@ SIGNATURES = {
   "b200q_repack": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
   "b200q_dequant_packed": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
   "b200q_gemv": (c_int, [POINTER(GemvArgs), c_void_p]),
+  "b200q_mailbox_reduce": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+  "b200q_ipc_export": (c_int, [c_void_p, c_void_p]),
+  "b200q_ipc_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+  "b200q_ipc_close": (c_int, [c_void_p]),
+  "b200q_ep_publish_counts": (c_int, [POINTER(EpArgs), c_void_p]),
+  "b200q_ep_plan": (c_int, [POINTER(EpArgs), c_void_p]),
+  "b200q_ep_dispatch": (c_int, [POINTER(EpArgs), c_void_p, c_void_p]),
+  "b200q_ep_wait": (c_int, [POINTER(EpArgs), c_int, c_int, c_void_p]),
+  "b200q_ep_signal_results": (c_int, [POINTER(EpArgs), c_void_p]),
+  "b200q_ep_combine": (c_int, [POINTER(EpArgs), c_void_p, c_void_p, c_void_p]),
   "b200q_silu_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
   "b200q_tg_gemv": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
   "b200q_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),

@@ -114,3 +114,25 @@ extern "C" int b200q_graph_launch(void* graph_exec, void* stream) {
   return B200Q_OK;
 }
 extern "C" int b200q_graph_destroy(void* graph_exec) { B200Q_CHECK_CUDA(cudaGraphExecDestroy((cudaGraphExec_t)graph_exec)); return B200Q_OK; }
+
+// ---- memory shared between the processes of one node (one process per GPU) ----
+extern "C" int b200q_ipc_export(void* device_ptr, void* handle64_out) {
+  if (!device_ptr || !handle64_out) return B200Q_ERR_BAD_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+  cudaIpcMemHandle_t h;
+  B200Q_CHECK_CUDA(cudaIpcGetMemHandle(&h, device_ptr));
+  memcpy(handle64_out, &h, sizeof(h));
+  return B200Q_OK;
+}
+extern "C" int b200q_ipc_open(const void* handle64, void** device_ptr) {
+  if (!handle64 || !device_ptr) return B200Q_ERR_BAD_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  B200Q_CHECK_CUDA(cudaIpcOpenMemHandle(device_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return B200Q_OK;
+}
+extern "C" int b200q_ipc_close(void* device_ptr) {
+  if (!device_ptr) return B200Q_ERR_BAD_ARG;
+  B200Q_CHECK_CUDA(cudaIpcCloseMemHandle(device_ptr));
+  return B200Q_OK;
+}

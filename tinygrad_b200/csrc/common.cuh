@@ -28,6 +28,8 @@ struct PerDeviceFlag {
 // reads and clears the status word of the decode-step kernels (decode.cu); folded into b200q_status_read_clear
 int b200q_decode_status_take(int* status);
 int b200q_decode_step_status_take(int* status);   // the same for the whole-step kernel (decode_step.cu)
+int b200q_peer_status_take(int* status);          // the same for the peer-memory collectives (peer.cu)
+int b200q_ep_status_take(int* status);            // the same for the expert-parallel exchange (ep.cu)
 // current device index, or -1 (with the CUDA error recorded) if it cannot be had or is past the tables
 int b200q_current_device();
 // SM count of the current device (cached per device); 0 on error
@@ -59,6 +61,19 @@ static inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 blo
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// ---- mailboxes in peer memory ---------------------------------------------------------------------------------------
+// A mailbox word is 32 bits: the fp32 value, or MAILBOX_EMPTY.  One aligned 32-bit store / load is atomic, so a word is either
+// empty or complete: the reader polls the data itself, no flag and no fence, and puts MAILBOX_EMPTY back when it has read it.
+// The all-ones pattern is a NaN no arithmetic produces (results that are NaN travel as the canonical quiet NaN).
+constexpr uint32_t MAILBOX_EMPTY = 0xFFFFFFFFu;
+__device__ __forceinline__ uint32_t mailbox_bits(float v) { const uint32_t b = __float_as_uint(v); return b == MAILBOX_EMPTY ? 0x7FC00000u : b; }
+__device__ __forceinline__ void mailbox_store(uint32_t* p, uint32_t bits) { asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(bits) : "memory"); }
+__device__ __forceinline__ uint32_t mailbox_load(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

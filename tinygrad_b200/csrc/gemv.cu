@@ -46,6 +46,10 @@ struct GemvParams {
   const __half* out_norm_w; // multiplied into the output before it is quantised (the next GEMV's norm weight)
   float* ss_out;            // one partial sum of squares per 32 outputs
   int unit, n_units;        // row tiles are dealt to CTAs in runs of `unit` (one run = 32 outputs when xq_out is set)
+  // tensor / vocabulary parallel: the output row goes, as self-validating words, into slot `peer_rank` of a mailbox on EVERY rank
+  // (peer memory over NVLink; see peer.cu), where a small kernel sums the ranks' slots (all-reduce) or copies them (all-gather)
+  uint32_t* peer[B200Q_MAX_PEERS];
+  int n_peers, peer_rank;
 };
 
 // Tunables (overridable at compile time for experiments).
@@ -287,6 +291,10 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
               if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(v);
               else reinterpret_cast<float*>(p.y)[(size_t)m * p.n_out + row] = v;
             }
+            if (p.n_peers) {
+              const uint32_t bits = mailbox_bits(v);
+              for (int d = 0; d < p.n_peers; d++) mailbox_store(p.peer[d] + (size_t)p.peer_rank * p.n_out + row, bits);
+            }
           }
           if (XQ_OUT && lane < 16) ubuf[ti * 16 + lane] = v;
         } else {
@@ -354,13 +362,17 @@ extern "C" int b200q_status_read_clear(int* status) {
   const int rc2 = b200q_decode_step_status_take(&step);
   if (rc2 != B200Q_OK) return rc2;
   if (step && !*status) *status = step;
+  int peer = 0;
+  const int rc3 = b200q_peer_status_take(&peer);
+  if (rc3 != B200Q_OK) return rc3;
+  if (peer && !*status) *status = peer;
   return B200Q_OK;
 }
 
 extern "C" size_t b200q_xq_bytes(int n) { return n > 0 ? xq_record_bytes(n) : 0; }
 
 extern "C" int b200q_gemv(const b200q_gemv_args* a, void* stream) {
-  if (!a || !a->w_packed || (!a->x && !a->xq_in) || (!a->y && !a->xq_out)) return B200Q_ERR_BAD_ARG;
+  if (!a || !a->w_packed || (!a->x && !a->xq_in) || (!a->y && !a->xq_out && !a->n_peers)) return B200Q_ERR_BAD_ARG;
   if (a->qtype == B200Q_Q6_K) return B200Q_ERR_UNSUPPORTED;
   if (a->qtype != B200Q_Q4_0 && a->qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
   if (a->n_out <= 0 || a->n_in <= 0 || a->m <= 0 || a->m > 65535) return B200Q_ERR_BAD_ARG;
@@ -385,6 +397,16 @@ extern "C" int b200q_gemv(const b200q_gemv_args* a, void* stream) {
   p.x_f16 = a->x_dtype == B200Q_F16; p.y_f16 = a->y_dtype == B200Q_F16; p.epilogue = a->epilogue; p.eps = a->norm_eps;
   p.xq_in = a->xq_in; p.ss_in = a->ss_in; p.ss_count = a->ss_count;
   p.xq_out = a->xq_out; p.out_norm_w = (const __half*)a->xq_out_norm_weight; p.ss_out = a->ss_out;
+  p.n_peers = 0; p.peer_rank = 0;
+  if (a->n_peers) {
+    if (a->n_peers < 0 || a->n_peers > B200Q_MAX_PEERS || a->peer_rank < 0 || a->peer_rank >= a->n_peers || !a->peer_mailboxes) return B200Q_ERR_BAD_ARG;
+    if (a->m != 1 || a->epilogue != B200Q_EPI_LINEAR) return B200Q_ERR_UNSUPPORTED;
+    for (int d = 0; d < a->n_peers; d++) {
+      if (!a->peer_mailboxes[d] || ((uintptr_t)a->peer_mailboxes[d] & 3)) return B200Q_ERR_BAD_ARG;
+      p.peer[d] = (uint32_t*)a->peer_mailboxes[d];
+    }
+    p.n_peers = a->n_peers; p.peer_rank = a->peer_rank;
+  }
   p.unit = a->xq_out ? (a->epilogue == B200Q_EPI_SILU_MUL ? 4 : 2) : 1;
   p.n_units = ceil_div(p.n_row_tiles, p.unit);
   const bool xi = a->xq_in != nullptr, xo = a->xq_out != nullptr;

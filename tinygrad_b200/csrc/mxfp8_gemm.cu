@@ -280,6 +280,10 @@ extern "C" int b200q_mx_status_read_clear(int* status) {
   int zero = 0;
   B200Q_CHECK_CUDA(cudaMemcpyFromSymbol(status, g_mx_status, sizeof(int)));
   B200Q_CHECK_CUDA(cudaMemcpyToSymbol(g_mx_status, &zero, sizeof(int)));
+  int ep = 0;
+  const int rc = b200q_ep_status_take(&ep);       // the exchange kernels around the expert GEMMs report through the same word
+  if (rc) return rc;
+  if (*status == 0) *status = ep;
   return B200Q_OK;
 }
 

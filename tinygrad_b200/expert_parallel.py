@@ -161,3 +161,123 @@ class ExpertParallelMoE:
     t.cuda.synchronize()
     self.last_plan = plan
     return b["out"]
+
+
+class PeerExpertParallelMoE:
+  """One rank's part of an expert-parallel MXFP8 MoE FFN whose exchange runs over peer memory and is planned on the device
+  (csrc/ep.cu): no communication library, no host read and no synchronisation inside a call -- a call enqueues kernels only.
+  Weights as `ExpertParallelMoE`.  `group` gives rank / size and a host channel for the set-up (`TPGroup`, or anything with
+  rank, size, exchange(blob) and barrier()); `connect()` maps every rank's buffers into this process over CUDA IPC, or takes the
+  pointer tables directly (ranks that live in one process, as in the one-GPU tests)."""
+  SHARED = ("counts_all", "a_q", "a_e8", "y", "flags")
+  exchange_kind = "device-planned over peer memory: counts mailbox, remote dispatch-quantise stores, flags, pull-combine (no library call, no host read)"
+
+  def __init__(self, group, w_gate: np.ndarray, w_up: np.ndarray, w_down: np.ndarray, n_experts: int, k: int, n_tokens_total: int, mode: int = 1):
+    from . import moe, _lib
+    from ._lib import check
+    from .runtime import DeviceBuffer, synchronize
+    self.group, self.rank, self.size = group, group.rank, group.size
+    self.E, self.k, self.mode = n_experts, k, mode
+    self.E_l, self.F, self.D = w_gate.shape
+    assert self.E_l * self.size == n_experts and self.D % 256 == 0
+    self.local = moe.MxMoE(w_gate, w_up, w_down, k, mode)          # holds the quantised expert shard; its own routing is not used
+    self.m_max = m_local_max(n_tokens_total, self.E_l, k)
+    m = self.m_max
+    self.buf = dict(counts_all=DeviceBuffer(4 * self.size * n_experts), a_q=DeviceBuffer.empty((m, self.D), np.uint8, zero=True),
+                    a_e8=DeviceBuffer.empty((m, self.D // 32), np.uint8, zero=True), y=DeviceBuffer.empty((m, self.D), np.uint16, zero=True),
+                    flags=DeviceBuffer.empty((2, self.size), np.uint32, zero=True))
+    check(_lib.load().b200q_memset(self.buf["counts_all"].ptr, 0xFF, self.buf["counts_all"].nbytes, None))
+    self.h = DeviceBuffer.empty((m, 2 * self.F), np.uint16, zero=True)
+    self.act_q, self.act_e8 = DeviceBuffer.empty((m, self.F), np.uint8, zero=True), DeviceBuffer.empty((m, self.F // 32), np.uint8, zero=True)
+    self.send_base, self.off_local = DeviceBuffer.empty((n_experts,), np.int32, zero=True), DeviceBuffer.empty((self.E_l + 1,), np.int32, zero=True)
+    self.scratch = DeviceBuffer.empty((1,), np.uint32, zero=True)
+    synchronize()
+    self._per_T, self.tables = {}, None
+
+  def connect(self, tables: dict | None = None) -> None:
+    """tables: name -> list of device pointers by rank, for every name of SHARED; None = exchange CUDA IPC handles through the group."""
+    import ctypes
+    if tables is None:
+      from .tensor_parallel import share_buffer
+      tables = {name: share_buffer(self.group, self.buf[name]) for name in self.SHARED}
+      self.group.barrier()                       # nobody stores into buffers that are not initialised yet
+    self.tables = {name: (ctypes.c_void_p * self.size)(*tables[name]) for name in self.SHARED}
+
+  def _args(self, T: int):
+    b = self._per_T.get(T)
+    if b is None:
+      from . import _lib
+      from .runtime import DeviceBuffer
+      assert self.tables is not None, "connect() first"
+      n = T * self.k
+      b = dict(topi=DeviceBuffer.empty((T, self.k), np.int32), w=DeviceBuffer.empty((T, self.k), np.float32), dest=DeviceBuffer.empty((n,), np.int32),
+               off=DeviceBuffer.empty((self.E + 1,), np.int32), counts=DeviceBuffer.empty((self.E,), np.int32, zero=True),
+               rscratch=DeviceBuffer(_lib.load().b200q_moe_route_scratch_bytes(T, self.E, self.k)), remote_row=DeviceBuffer.empty((n,), np.int32, zero=True),
+               out=DeviceBuffer.empty((T, self.D), np.uint16))
+      t = self.tables
+      b["args"] = _lib.EpArgs(n_ranks=self.size, rank=self.rank, n_experts=self.E, k=self.k, d_model=self.D, n_tokens=T, m_max=self.m_max,
+                              topi=b["topi"].ptr, dest=b["dest"].ptr, off=b["off"].ptr, counts=b["counts"].ptr, counts_all=t["counts_all"], a_q=t["a_q"],
+                              a_e8=t["a_e8"], y=t["y"], flags=t["flags"], send_base=self.send_base.ptr, off_local=self.off_local.ptr,
+                              remote_row=b["remote_row"].ptr, scratch=self.scratch.ptr)
+      self._per_T[T] = b
+    return b
+
+  # The four stretches of a call between which another rank's progress is needed.  A rank runs them back to back on one stream; ranks
+  # that share a GPU (tests) run stretch i for every rank before stretch i + 1, so that no kernel ever waits for a launch behind it.
+  def route_publish(self, logits, T: int, stream=None) -> None:
+    from . import _lib
+    from ._lib import check
+    from .runtime import ptr_of, stream_ptr
+    lib, s, b = _lib.load(), stream_ptr(stream), self._args(T)
+    check(lib.b200q_moe_route_pad(ptr_of(logits), T, self.E, self.k, self.mode, 1, b["topi"].ptr, b["w"].ptr, b["dest"].ptr, b["off"].ptr, b["counts"].ptr,
+                                  b["rscratch"].ptr, s))
+    check(lib.b200q_ep_publish_counts(b["args"], s))
+
+  def plan_dispatch(self, x_bf16, T: int, stream=None) -> None:
+    from . import _lib
+    from ._lib import check
+    from .runtime import ptr_of, stream_ptr
+    lib, s, b = _lib.load(), stream_ptr(stream), self._args(T)
+    check(lib.b200q_ep_plan(b["args"], s))
+    check(lib.b200q_ep_dispatch(b["args"], ptr_of(x_bf16), s))
+
+  def experts_signal(self, T: int, stream=None, spin_limit: int = 0) -> None:
+    from . import _lib
+    from ._lib import check
+    from .runtime import stream_ptr
+    lib, s, b, m, loc = _lib.load(), stream_ptr(stream), self._args(T), self.local, self.m_max
+    a_q, a_e8, y, off_l = self.buf["a_q"].ptr, self.buf["a_e8"].ptr, self.buf["y"].ptr, self.off_local.ptr
+    check(lib.b200q_ep_wait(b["args"], 0, spin_limit, s))
+    if m.fused:
+      check(lib.b200q_grouped_mxfp8_gemm_swiglu(a_q, a_e8, m.gu_q.ptr, m.gu_e8.ptr, off_l, self.E_l, loc, 2 * self.F, self.D, self.act_q.ptr, self.act_e8.ptr, s))
+    else:
+      check(lib.b200q_grouped_mxfp8_gemm(a_q, a_e8, m.gu_q.ptr, m.gu_e8.ptr, off_l, self.E_l, loc, 2 * self.F, self.D, self.h.ptr, s))
+      check(lib.b200q_swiglu_quantize_mxfp8(self.h.ptr, loc, off_l + 4 * self.E_l, self.F, self.act_q.ptr, self.act_e8.ptr, s))
+    check(lib.b200q_grouped_mxfp8_gemm(self.act_q.ptr, self.act_e8.ptr, m.dn_q.ptr, m.dn_e8.ptr, off_l, self.E_l, loc, self.D, self.F, y, s))
+    check(lib.b200q_ep_signal_results(b["args"], s))
+
+  def combine(self, T: int, stream=None, spin_limit: int = 0):
+    from . import _lib
+    from ._lib import check
+    from .runtime import stream_ptr
+    lib, s, b = _lib.load(), stream_ptr(stream), self._args(T)
+    check(lib.b200q_ep_wait(b["args"], 1, spin_limit, s))
+    check(lib.b200q_ep_combine(b["args"], b["w"].ptr, b["out"].ptr, s))
+    return b["out"]
+
+  def __call__(self, x_bf16, logits, n_tokens: int, stream=None):
+    """-> DeviceBuffer (T_l, D) bf16, enqueued on `stream`; nothing is synchronised."""
+    self.route_publish(logits, n_tokens, stream)
+    self.plan_dispatch(x_bf16, n_tokens, stream)
+    self.experts_signal(n_tokens, stream)
+    return self.combine(n_tokens, stream)
+
+  def timed(self, x_bf16, logits, n_tokens: int, reps: int) -> float:
+    """Milliseconds per call over `reps` calls, CUDA events on the stream the layer runs on (the default stream)."""
+    from .runtime import Event
+    e0, e1 = Event(), Event()
+    e0.record(None)
+    for _ in range(reps): self(x_bf16, logits, n_tokens)
+    e1.record(None)
+    e1.synchronize()
+    return e0.elapsed_ms(e1) / reps

@@ -87,7 +87,8 @@ class Transformer:
     self.gemv_max_ctas = gemv_max_ctas
     self.n_split = n_split or _lib.load().b200q_attn_min_split(c.max_context)
     self.max_context = c.max_context
-    self.stream = Stream(tp.stream_ptr()) if tp is not None else Stream()
+    self.stream = Stream(tp.stream_ptr()) if (tp is not None and tp.stream_ptr() is not None) else Stream()
+    self.tp_peer = tp is not None and tp.kind_id == "peer"
     sd = state_dict
     qkv_rows = self.q_dim + 2 * self.kv_dim
     assert self.q_dim % 16 == 0 and self.kv_dim % 16 == 0, "q/k/v are packed back to back in whole 16-row tiles"
@@ -180,6 +181,11 @@ class Transformer:
     self.act = DeviceBuffer.empty((c.hidden_dim,), np.float32, zero=True)
     if tp is not None: self.logits_part, self.logits = tp.empty_f32(c.vocab_size), tp.empty_f32(vocab_full)
     else: self.logits = self.logits_part = DeviceBuffer.empty((c.vocab_size,), np.float32, zero=True)
+    if self.tp_peer and isinstance(self.output, quant.DenseWeight): raise NotImplementedError("sharded models need a Q4_0 / Q8_0 head")
+    if self.tp_peer:      # two alternating mailboxes for the row-split linears (O, down), one for the vocabulary slices of the head
+      from .tensor_parallel import PeerMailbox
+      self.mb_o, self.mb_down = PeerMailbox(tp, tp.size, c.dim), PeerMailbox(tp, tp.size, c.dim)
+      self.mb_logits = PeerMailbox(tp, 1, vocab_full)
     self.batch = batch
     assert batch >= 1 and (batch == 1 or tp is None), "batched decode runs on one GPU"
     self.tokens = DeviceBuffer.empty((batch, c.max_context + 1), np.int32, zero=True)     # sequence 0 is the single-sequence state
@@ -249,8 +255,12 @@ class Transformer:
     tp = self.tp
     # A launch that follows an NCCL call is fully stream-ordered: the programmatic-launch attribute right behind the
     # event waits NCCL leaves in the stream was measured to let the kernel start before the reduced vector is there.
-    kw_after_coll = dict(kw, flags=0) if tp is not None else kw
+    peer = self.tp_peer
+    kw_after_coll = dict(kw, flags=0) if (tp is not None and not peer) else kw
     rkw = dict(residual=self.x, residual_scale=1.0 / tp.size) if tp is not None else dict(residual=self.x)   # row-split shards add residual / n_ranks
+    # peer-memory collectives: the row-split GEMV stores its partial row into every rank's mailbox; the reducer adds the residual once
+    rkw_o = dict(peers=self.mb_o.targets, peer_rank=tp.rank) if peer else rkw
+    rkw_d = dict(peers=self.mb_down.targets, peer_rank=tp.rank) if peer else rkw
     vocab_full = self.full_config.vocab_size
     e, nss = self.edges, c.dim // 32
     qkv_rows = self.q_dim + 2 * self.kv_dim
@@ -286,26 +296,30 @@ class Transformer:
                           c.n_heads, c.n_kv_heads, c.head_dim, c.rope_dim, c.max_context, self.n_split, fl,
                           self.xq_attn.ptr if "attn_o" in e else None)
         check(lib.b200q_attn_decode(ctypes.byref(a), s))
-      quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, None if in_attn else self.attn, self.x, **rkw,
+      quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, None if in_attn else self.attn, None if peer else self.x, **rkw_o,
                  **in_attn, **out_b, **kw)
-      if tp is not None: tp.all_reduce(self.x)
+      if peer: self.mb_o.reduce(self.x, residual=self.x, flags=fl, stream=s)
+      elif tp is not None: tp.all_reduce(self.x)
       quant.gemv(b.gate_up.buf.ptr, self.qtype, c.hidden_dim, c.dim, None if in_b else self.x, None if out_act else self.act,
                  norm_weight=b.ffn_norm, norm_eps=c.norm_eps, epilogue=EPI_SILU_MUL, **in_b, **out_act, **kw_after_coll)
-      quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, None if in_act else self.act, self.x, **rkw,
+      quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, None if in_act else self.act, None if peer else self.x, **rkw_d,
                  **in_act, **out_a, **kw)
-      if tp is not None: tp.all_reduce(self.x)
+      if peer: self.mb_down.reduce(self.x, residual=self.x, flags=fl, stream=s)
+      elif tp is not None: tp.all_reduce(self.x)
     if with_head:
       if isinstance(self.output, quant.DenseWeight):
         quant.gemv_dense(self.output.buf, self.output.dtype, c.vocab_size, c.dim, self.x, self.logits_part, norm_weight=self.output_norm,
                          norm_eps=c.norm_eps, flags=kw_after_coll["flags"], stream=s)
       else:
         quant.gemv(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, None if in_a else self.x, self.logits_part,
-                   norm_weight=self.output_norm, norm_eps=c.norm_eps, **in_a, **kw_after_coll)
-      if tp is not None: tp.all_gather(self.logits, self.logits_part)
+                   norm_weight=self.output_norm, norm_eps=c.norm_eps, **in_a, **kw_after_coll,
+                   **(dict(peers=self.mb_logits.targets, peer_rank=tp.rank) if peer else {}))
+      if peer: self.mb_logits.reduce(self.logits, flags=fl, stream=s)          # every rank's vocabulary slice, handed over
+      elif tp is not None: tp.all_gather(self.logits, self.logits_part)
       if tail: check(lib.b200q_argmax_advance(self.logits.ptr, vocab_full, self.tokens.ptr, self.pos.ptr, c.max_context, self.argmax_scratch.ptr,
-                                              0 if tp is not None else fl, s))
+                                              0 if (tp is not None and not peer) else fl, s))
     elif tail:
-      check(lib.b200q_advance(self.pos.ptr, c.max_context, 0 if tp is not None else fl, s))
+      check(lib.b200q_advance(self.pos.ptr, c.max_context, 0 if (tp is not None and not peer) else fl, s))
 
   # ---- several prompt tokens at once: tcgen05 dequant GEMMs + batched causal attention ----
   def _prefill_buffers(self):

@@ -83,7 +83,8 @@ def dense_model_raw(cfg, ggml_type: int = Q4_0, seed: int = 0, embd_std: float =
   sd = {}
   for name, n_out, n_in in linear_names(cfg):
     kw = {} if scale_std is None else {"scale_std": scale_std}
-    sd[name + ".weight"] = BLOCK_MAKERS[ggml_type](n_out, n_in, np.random.default_rng(name_seed(name, seed)), **kw)
+    make = BLOCK_MAKERS.get(ggml_type) or (lambda o, i, rng, **k: random_blocks(ggml_type, o, i, rng, **k))
+    sd[name + ".weight"] = make(n_out, n_in, np.random.default_rng(name_seed(name, seed)), **kw)
     if cfg.qkv_bias and name.split(".")[-1] in ("attn_q", "attn_k", "attn_v"):
       sd[name + ".bias"] = (np.random.default_rng(name_seed(name + ".bias", seed)).standard_normal(n_out, dtype=np.float32) * bias_std).astype(np.float16)
   rng = np.random.default_rng(name_seed("token_embd", seed))
