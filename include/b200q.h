@@ -96,7 +96,7 @@ int b200q_graph_destroy(void* graph_exec);
  * tinygrad/llm/model.py:376). */
 int b200q_dequant_raw(int qtype, const void* device_raw, void* device_out, int64_t n_elems, int out_dtype, void* stream);
 
-/* Packed weight layout used by the GEMV kernels (Q4_0, Q8_0).  A [n_out, n_in]
+/* Packed weight layout used by the GEMV kernels (Q4_0, Q8_0, Q6_K).  A [n_out, n_in]
  * weight (blocks running along n_in, as GGUF stores a Linear weight,
  * tinygrad/llm/gguf.py:148) is re-tiled ONCE at load time, losslessly, into
  * tiles of 16 rows x 128 columns (4 quant blocks per row), ordered
@@ -108,7 +108,12 @@ int b200q_dequant_raw(int qtype, const void* device_raw, void* device_out, int64
  *                       [entry e=2*(l/4)+h: scales of rows l/4 and l/4+8, blocks 2h and 2h+1] x16 (8 B each)
  *   Q8_0 tile = 2176 B: as above with the 32 quant bytes of a (row, block) pair in two 16-byte halves
  *                       (rows 0-7: halves at +0 and +512; rows 8-15: at +1024 and +1536), then the same scale entries.
- * The bytes per weight element are exactly the GGUF format's (18 or 34 bytes per 32).
+ *   Q6_K tile = 1696 B (n_in a multiple of 256; a tile row is half a super-block, tinygrad/llm/gguf.py:68-72):
+ *                       [lane l: the low nibbles of (row l/4, block l%4): byte i = element i | element i+16 << 4] x32, the same for rows +8,
+ *                       [lane l: 8 bytes of high bit pairs: byte k of word 0 holds elements k, 4+k, 8+k, 12+k at bits 0, 2, 4, 6;
+ *                        word 1 the same for elements 16..31] x32, the same for rows +8,
+ *                       int8 sub-block scales [16 rows][8], fp16 super-block scales [16 rows]  (106 bytes per row against 105 in the file).
+ * The bytes per weight element are exactly the GGUF format's for Q4_0 / Q8_0 (18 or 34 bytes per 32).
  * n_out is padded up to a multiple of 16 and n_in to a multiple of 128 with zero-scale blocks.
  * With raw1 != NULL two matrices of equal shape are interleaved 8 rows at a
  * time (rows 0-7 of each tile from raw0, rows 8-15 from raw1) for the fused
@@ -129,7 +134,7 @@ int b200q_dequant_packed(int qtype, const void* device_packed, void* device_out,
  * (error ~3e-5 relative, far inside the 1e-2 tolerance of this path); products and sums inside a block
  * are exact integers, accumulation across blocks is fp32. */
 typedef struct b200q_gemv_args {
-  int qtype;                /* B200Q_Q4_0 | B200Q_Q8_0 */
+  int qtype;                /* B200Q_Q4_0 | B200Q_Q8_0 | B200Q_Q6_K (plain linears: EPI_LINEAR, no xq_in; n_in a multiple of 256) */
   int n_out;                /* logical output features (for EPI_SILU_MUL: features of gate == up) */
   int n_in;                 /* input features, multiple of 32 */
   int m;                    /* activation rows (1 at decode) */

@@ -59,7 +59,8 @@ def test_packed_bytes(lib):
   assert lib.b200q_packed_bytes(_lib.Q4_0, 4096, 4096) == 4096 * 4096 // 32 * 18   # exactly the GGUF bytes
   assert lib.b200q_packed_bytes(_lib.Q8_0, 4096, 4096) == 4096 * 4096 // 32 * 34
   assert lib.b200q_packed_bytes(_lib.Q4_0, 17, 96) == 2 * 1 * 1152                 # padded to 32 rows x 128 columns
-  assert lib.b200q_packed_bytes(_lib.Q6_K, 16, 256) == 0
+  assert lib.b200q_packed_bytes(_lib.Q6_K, 16, 256) == 2 * 1696                     # 106 bytes per row and half super-block
+  assert lib.b200q_packed_bytes(_lib.Q6_K, 16, 128) == 0 and lib.b200q_packed_bytes(12, 16, 256) == 0   # not whole super-blocks; no fused Q4_K
   assert lib.b200q_packed_bytes(_lib.Q4_0, 0, 128) == 0
 
 
@@ -71,7 +72,8 @@ def test_bad_arguments_are_rejected_without_a_device(lib):
   assert lib.b200q_repack(_lib.Q4_0, None, None, 16, 16, 32, None) == -1
   assert lib.b200q_repack(_lib.Q4_0, 16, None, 16, 16, 48, None) == -2
   assert lib.b200q_repack(_lib.Q4_0, 16, None, 8, 16, 32, None) == -3        # packed buffer must be 16-byte aligned
-  assert lib.b200q_repack(_lib.Q6_K, 16, None, 16, 16, 256, None) == -4
+  assert lib.b200q_repack(_lib.Q6_K, 16, 16, 16, 16, 256, None) == -4        # no interleaved gate / up tiles for Q6_K
+  assert lib.b200q_repack(_lib.Q6_K, 16, None, 16, 16, 128, None) == -2
   a = _lib.GemvArgs(_lib.Q4_0, 16, 128, 1, 16, 16, _lib.F32, _lib.F32, None, 0.0, 0, None, None, 16, 0, 0, None, None, 0, None, None, None, 0.0)
   a.n_in = 100
   assert lib.b200q_gemv(ctypes.byref(a), None) == -2

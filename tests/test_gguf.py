@@ -84,3 +84,10 @@ def test_rope_row_permutation_is_the_reference_rearrange():
     np.testing.assert_array_equal(got[h, :prefix], src[h, :prefix])
     rot = src[h, prefix:]
     np.testing.assert_array_equal(got[h, prefix:], np.concatenate([rot[0::2], rot[1::2]]))
+
+
+def test_lazy_state_answers_membership_without_making_tensors():
+  sd = synth.LazyDenseState(_tiny(), 2, seed=0)
+  assert "blk.1.ffn_down.weight" in sd and "output.weight" in sd and "token_embd.weight" in sd and "blk.0.attn_norm.weight" in sd
+  assert "blk.0.attn_q.bias" not in sd and "blk.0.ffn_gate_inp.weight" not in sd and 3 not in sd
+  assert sd["blk.1.ffn_down.weight"].dtype == np.uint8

@@ -47,14 +47,15 @@ def test_dequant_empty_and_errors():
   with pytest.raises(_lib.B200QError): quant.dequantize(np.zeros(18, np.uint8), 31, 2)
 
 
-@pytest.mark.parametrize("tag,n_out,n_in", [("q4_0", 64, 256), ("q4_0", 40, 96), ("q4_0", 16, 32), ("q8_0", 48, 384), ("q8_0", 17, 160)])
+@pytest.mark.parametrize("tag,n_out,n_in", [("q4_0", 64, 256), ("q4_0", 40, 96), ("q4_0", 16, 32), ("q8_0", 48, 384), ("q8_0", 17, 160),
+                                             ("q6_k", 64, 512), ("q6_k", 40, 256), ("q6_k", 17, 1024)])
 def test_repack_is_lossless(tag, n_out, n_in):
   from tinygrad_b200 import quant
   typ = TAGS[tag]
   raw = synth.BLOCK_MAKERS[typ](n_out, n_in, np.random.default_rng(n_out * 1000 + n_in))
   ref = gq.weight_matrix(raw, n_out, n_in, typ)
   pw = quant.repack(raw, n_out, n_in, typ)
-  assert pw.buf.nbytes == -(-n_out // 16) * -(-n_in // 128) * (1152 if typ == 2 else 2176)
+  assert pw.buf.nbytes == -(-n_out // 16) * -(-n_in // 128) * {2: 1152, 8: 2176, 14: 1696}[typ]
   np.testing.assert_array_equal(pw.dequantize(np.float32).numpy().view(np.uint32), ref.view(np.uint32))
   np.testing.assert_array_equal(pw.dequantize(np.float16).numpy().view(np.uint16), ref.astype(np.float16).view(np.uint16))
 
@@ -93,7 +94,9 @@ def test_single_q4_0_linear_4096_fp16():
 
 
 @pytest.mark.parametrize("tag,n_out,n_in,m", [("q4_0", 256, 1024, 1), ("q4_0", 40, 96, 3), ("q4_0", 16, 32, 1), ("q4_0", 4096, 14336, 1),
-                                               ("q8_0", 512, 3584, 1), ("q8_0", 33, 160, 2), ("q4_0", 128, 128 * 9, 1)])
+                                               ("q8_0", 512, 3584, 1), ("q8_0", 33, 160, 2), ("q4_0", 128, 128 * 9, 1),
+                                               ("q6_k", 256, 1024, 1), ("q6_k", 33, 256, 3), ("q6_k", 4096, 4096, 1), ("q6_k", 1000, 14336, 2),
+                                               ("q6_k", 48, 768, 5)])
 def test_linear_fp32_matches_oracle(tag, n_out, n_in, m):
   typ = TAGS[tag]
   x = np.random.default_rng(3).standard_normal((m, n_in)).astype(np.float32)
@@ -149,6 +152,34 @@ def test_fused_norm_residual_and_swiglu():
   assert_close(dres.numpy(), x + llm.linear(act_full[None], wd)[0], what="down + residual")
 
 
+def test_q6_k_head_with_fused_norm_bias_and_residual():
+  """The fused Q6_K GEMV in the role it has in K-quant files (the vocabulary head behind the output RMSNorm), plus bias / residual / fp16."""
+  from tinygrad_b200 import quant
+  from tinygrad_b200.runtime import DeviceBuffer
+  rng = np.random.default_rng(9)
+  n_out, n_in = 1000, 2048
+  raw = synth.q6_k_blocks(n_out, n_in, rng)
+  w = gq.weight_matrix(raw, n_out, n_in, 14)
+  x = rng.standard_normal(n_in).astype(np.float32) * 2
+  nw = (1 + 0.1 * rng.standard_normal(n_in)).astype(np.float16)
+  bias = rng.standard_normal(n_out).astype(np.float16)
+  res = rng.standard_normal(n_out).astype(np.float32)
+  pw = quant.repack(raw, n_out, n_in, 14)
+  dy = DeviceBuffer.from_numpy(res.copy())
+  quant.gemv(pw.buf.ptr, 14, n_out, n_in, DeviceBuffer.from_numpy(x), dy, norm_weight=DeviceBuffer.from_numpy(nw), norm_eps=1e-5,
+             bias=DeviceBuffer.from_numpy(bias), residual=dy)
+  ref = res + llm.linear(llm.rmsnorm(x[None], nw, 1e-5), w, bias)[0]
+  assert_close(dy.numpy(), ref, what="norm + Q6_K linear + bias + residual")
+  x16 = x.astype(np.float16)
+  y16 = DeviceBuffer.empty((n_out,), np.float16)
+  quant.gemv(pw.buf.ptr, 14, n_out, n_in, DeviceBuffer.from_numpy(x16), y16, x_dtype=quant.F16, y_dtype=quant.F16)
+  assert_close(y16.numpy(), llm.linear(x16[None].astype(np.float32), w)[0], what="fp16 in / out")
+  # what the format cannot do is refused, not approximated
+  from tinygrad_b200 import _lib
+  with pytest.raises(_lib.B200QError): quant.gemv(pw.buf.ptr, 14, n_out, n_in, DeviceBuffer.from_numpy(x), dy, epilogue=_lib.EPI_SILU_MUL)
+  with pytest.raises(ValueError): quant.repack(synth.q6_k_blocks(16, 256, rng), 16, 128, 14)
+
+
 def test_no_kernel_wait_ran_out():
   """The bounded mbarrier waits of the GEMV pipeline must never expire in normal operation."""
   from tinygrad_b200 import runtime
@@ -190,13 +221,20 @@ def test_tensor_core_gemm_matches_fp16_operand_reference(tag, m, n_out, n_in, x_
 @pytest.mark.parametrize("kind,n_out,n_in,m", [("f16", 64, 2048, 1), ("f32", 100, 256, 3), ("bf16", 37, 512, 4), ("q6_k", 48, 1024, 2),
                                               ("f16", 8, 4096, 6)])
 def test_dense_weight_linear(kind, n_out, n_in, m):
-  """Linears whose weights stay unquantised (F16 / F32 / BF16 tensors) or are Q6_K: the dense GEMV against the oracle's linear."""
+  """Linears whose weights stay unquantised (F16 / F32 / BF16 tensors): the dense GEMV against the oracle's linear.  Q6_K through the same
+  front door takes the fused kernel (exact block values, activations quantised to 15 bits) and, as `DenseWeight`, the fp16 cast."""
   from tinygrad_b200 import quant, moe
   from tinygrad_b200.runtime import DeviceBuffer
   rng = np.random.default_rng(11)
   if kind == "q6_k":
     raw, typ = synth.q6_k_blocks(n_out, n_in, rng), 14
-    w = gq.dequantize(raw, n_out * n_in, 14).astype(np.float16).astype(np.float32).reshape(n_out, n_in)
+    w = gq.dequantize(raw, n_out * n_in, 14).reshape(n_out, n_in)
+    dw = quant.DenseWeight(raw, n_out, n_in, 14)                 # the reference's own treatment: every tensor cast to fp16 (model.py:376)
+    x = rng.standard_normal((m, n_in)).astype(np.float32)
+    y = DeviceBuffer.empty((m, n_out), np.float32)
+    quant.gemv_dense(dw.buf, dw.dtype, n_out, n_in, DeviceBuffer.from_numpy(x), y, m=m)
+    ref16 = llm.linear(x, w.astype(np.float16).astype(np.float32))
+    assert np.abs(y.numpy() - ref16).max() <= 1e-5 * max(1.0, np.abs(ref16).max())
   else:
     w = (rng.standard_normal((n_out, n_in)) * 0.05).astype(np.float32)
     if kind == "f16": raw, typ, w = w.astype(np.float16), quant.GGML_F16, w.astype(np.float16).astype(np.float32)
@@ -210,7 +248,8 @@ def test_dense_weight_linear(kind, n_out, n_in, m):
     assert y.dtype == dt and y.shape == (m, n_out)
     ref = llm.linear(x.astype(np.float32), w, bias)
     assert_close(y, ref, tol=1e-2)
-    assert np.abs(y.astype(np.float32) - ref).max() <= (2e-3 if dt == np.float16 else 1e-5) * max(1.0, np.abs(ref).max())
+    bound = 2e-3 if dt == np.float16 else (5e-4 if kind == "q6_k" else 1e-5)
+    assert np.abs(y.astype(np.float32) - ref).max() <= bound * max(1.0, np.abs(ref).max())
 
 
 def test_dense_fused_norm_and_residual():

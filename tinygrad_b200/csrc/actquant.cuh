@@ -39,7 +39,9 @@ __device__ __forceinline__ void xq_store_words(const XqDst& d, int b, int q, uin
 }
 
 // Block b of 32 values held by 8 consecutive lanes, 4 values each (q = lane & 7 gives elements 4q..4q+3).
-__device__ __forceinline__ void quant_block_8x4(float4 v, int q, int b, const XqDst& d) {
+// sub16 (optional): [block][2] floats, 32 * s * (sum of q over elements 0..15 / 16..31): what removes Q6_K's offset of 32 per 16-element
+// sub-block (a sub-block has its own weight scale, so the block sum is not enough).
+__device__ __forceinline__ void quant_block_8x4(float4 v, int q, int b, const XqDst& d, float* sub16 = nullptr) {
   float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
@@ -50,6 +52,7 @@ __device__ __forceinline__ void quant_block_8x4(float4 v, int q, int b, const Xq
   int qsum = i0 + i1 + i2 + i3;
   qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
   qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+  if (sub16 && (q & 3) == 0) sub16[b * 2 + (q >> 2)] = 32.f * s * (float)qsum;
   qsum += __shfl_xor_sync(0xffffffffu, qsum, 4);
   const int h0 = (i0 + 64) >> 7, h1 = (i1 + 64) >> 7, h2 = (i2 + 64) >> 7, h3 = (i3 + 64) >> 7;
   const uint32_t hiw = (h0 & 0xFF) | ((h1 & 0xFF) << 8) | ((h2 & 0xFF) << 16) | ((uint32_t)(h3 & 0xFF) << 24);

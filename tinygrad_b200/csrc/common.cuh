@@ -37,10 +37,10 @@ int b200q_sm_count();
 
 // ---- packed weight layout (see include/b200q.h for the byte-level description)
 constexpr int TILE_ROWS = 16;       // output rows per tile (one mma.m16n8k16 A operand)
-constexpr int GROUP_ELEMS = 128;    // K elements per tile: 4 quant blocks of 32 (Q4_0/Q8_0)
+constexpr int GROUP_ELEMS = 128;    // K elements per tile: 4 quant blocks of 32 (Q4_0/Q8_0), half a super-block (Q6_K)
 
 __host__ __device__ constexpr int tile_bytes(int qtype) {
-  return qtype == B200Q_Q4_0 ? 1152 : qtype == B200Q_Q8_0 ? 2176 : 0;
+  return qtype == B200Q_Q4_0 ? 1152 : qtype == B200Q_Q8_0 ? 2176 : qtype == B200Q_Q6_K ? 1696 : 0;
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

@@ -74,9 +74,10 @@ constexpr int STAGE_GROUPS = B200Q_STAGE_GROUPS; // weight tiles (16 rows x 128 
 #endif
 constexpr int COPY_GROUPS = B200Q_COPY_GROUPS;   // weight tiles per bulk copy
 
-template <int QT> struct Cfg;
-template <> struct Cfg<B200Q_Q4_0> { static constexpr int NS = B200Q_NS_Q4; };   // ring depth (stage = STAGE_GROUPS x 1152 B)
-template <> struct Cfg<B200Q_Q8_0> { static constexpr int NS = 2; };   // stage = STAGE_GROUPS x 2176 B
+template <int QT> struct Cfg;      // NS: ring depth, SG: weight tiles per stage, XSUB: bytes per column group of per-sub-block offsets behind the record
+template <> struct Cfg<B200Q_Q4_0> { static constexpr int NS = B200Q_NS_Q4, SG = STAGE_GROUPS, XSUB = 0; };   // stage = SG x 1152 B
+template <> struct Cfg<B200Q_Q8_0> { static constexpr int NS = 2, SG = STAGE_GROUPS, XSUB = 0; };             // stage = SG x 2176 B
+template <> struct Cfg<B200Q_Q6_K> { static constexpr int NS = 3, SG = CONS_WARPS, XSUB = 32; };              // stage = SG x 1696 B
 
 __device__ __forceinline__ void cons_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONS_THREADS) : "memory"); }
 
@@ -104,13 +105,15 @@ __device__ __noinline__ void emit_output_record(const GemvParams& p, const float
 // XQ_IN / XQ_OUT: compiled-in use of a ready-made input record / production of an output record.
 template <int QT, bool XQ_IN, bool XQ_OUT>
 __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(const GemvParams p) {
-  constexpr int NS = Cfg<QT>::NS, TB = tile_bytes(QT), STAGE_BYTES = STAGE_GROUPS * TB;
+  constexpr int NS = Cfg<QT>::NS, SG = Cfg<QT>::SG, XSUB = Cfg<QT>::XSUB, TB = tile_bytes(QT), STAGE_BYTES = SG * TB;
+  static_assert(!(XQ_IN && XSUB), "a ready-made record carries no per-sub-block sums");
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* ring = smem;
   unsigned char* record = smem + NS * STAGE_BYTES;
   const uint4* xq = reinterpret_cast<const uint4*>(record);
   const float4* xsc = reinterpret_cast<const float4*>(record + (size_t)p.kgroups * 256);
-  uint4* zero = reinterpret_cast<uint4*>(record + (size_t)p.kgroups * XQ_GROUP_BYTES);
+  float* sub16 = reinterpret_cast<float*>(record + (size_t)p.kgroups * XQ_GROUP_BYTES);        // [kgroups][4 blocks][2 halves], Q6_K only
+  uint4* zero = reinterpret_cast<uint4*>(record + (size_t)p.kgroups * (XQ_GROUP_BYTES + XSUB));
   float* red = reinterpret_cast<float*>(zero + 1);
   float* ssq = red + 2 * CONS_WARPS * 16;
   float* ubuf = ssq + CONS_WARPS;
@@ -119,7 +122,7 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + NS), xbar = smem_u32(bars + 2 * NS);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int m = blockIdx.y;
-  const int stages_per_tile = (p.kgroups + STAGE_GROUPS - 1) / STAGE_GROUPS;
+  const int stages_per_tile = (p.kgroups + SG - 1) / SG;
 
   if (tid == 0) {
     for (int s = 0; s < NS; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, CONS_WARPS); }
@@ -153,7 +156,7 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
           if (rt >= p.n_row_tiles) break;
           const uint8_t* src = p.w + (size_t)rt * p.kgroups * TB;
           for (int s = 0; s < stages_per_tile; s++, it++) {
-            const int slot = it % NS, groups = min(STAGE_GROUPS, p.kgroups - s * STAGE_GROUPS);
+            const int slot = it % NS, groups = min(SG, p.kgroups - s * SG);
             if (it == NS && !x_issued) after_prefetch();
             if (!mbar_wait(empty0 + 8 * slot, ((it / NS) & 1) ^ 1)) { ok = false; break; }
             mbar_expect_tx(full0 + 8 * slot, groups * TB);
@@ -220,7 +223,7 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
         if (b0 + u * BSTEP < nblk_pad) {      // uniform over the 8 lanes of a block (and over the warp: 4 consecutive blocks)
           ss = fmaf(v[u].x, v[u].x, fmaf(v[u].y, v[u].y, fmaf(v[u].z, v[u].z, fmaf(v[u].w, v[u].w, ss))));
           const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&nw[u].x)), c = __half22float2(*reinterpret_cast<const __half2*>(&nw[u].y));
-          quant_block_8x4(make_float4(v[u].x * a.x, v[u].y * a.y, v[u].z * c.x, v[u].w * c.y), q, b0 + u * BSTEP, dst);
+          quant_block_8x4(make_float4(v[u].x * a.x, v[u].y * a.y, v[u].z * c.x, v[u].w * c.y), q, b0 + u * BSTEP, dst, XSUB ? sub16 : nullptr);
         }
       }
     }
@@ -248,17 +251,23 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
       if (rt >= p.n_row_tiles) break;
       float acc0 = 0.f, acc1 = 0.f;
       for (int s = 0; s < stages_per_tile; s++, it++) {
-        const int slot = it % NS, groups = min(STAGE_GROUPS, p.kgroups - s * STAGE_GROUPS);
+        const int slot = it % NS, groups = min(SG, p.kgroups - s * SG);
         if (!mbar_wait(full0 + 8 * slot, (it / NS) & 1)) { *s_abort = 1; break; }
         const uint8_t* stage = ring + slot * STAGE_BYTES;
 #pragma unroll
-        for (int u = 0; u < STAGE_GROUPS / CONS_WARPS; u++) {
+        for (int u = 0; u < SG / CONS_WARPS; u++) {
           const int gi = warp + u * CONS_WARPS;
           if (gi < groups) {
-            const int j = s * STAGE_GROUPS + gi;
+            const int j = s * SG + gi;
             const uint4 bq0 = diag ? xq[(j * 2 + 0) * 8 + g] : *zero, bq1 = diag ? xq[(j * 2 + 1) * 8 + g] : *zero;
             const float4 st = xsc[(j * 2 + (t >> 1)) * 2 + (t & 1)];
-            tile_mac<QT>(stage + gi * TB, lane, bq0, bq1, st, acc0, acc1);
+            if constexpr (QT == B200Q_Q6_K) {
+              // the offsets belong to the high digits only (their columns sit on the lanes t < 2)
+              const float4 sub = t < 2 ? *reinterpret_cast<const float4*>(sub16 + j * 8 + t * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+              tile_mac_q6k(stage + gi * TB, lane, bq0, bq1, st, sub, acc0, acc1);
+            } else {
+              tile_mac<QT>(stage + gi * TB, lane, bq0, bq1, st, acc0, acc1);
+            }
           }
         }
         __syncwarp();
@@ -320,7 +329,7 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
 template <int QT, bool XQ_IN, bool XQ_OUT>
 int launch_gemv(const b200q_gemv_args* a, const GemvParams& p, cudaStream_t stream) {
   constexpr int NS = Cfg<QT>::NS;
-  const size_t smem = (size_t)NS * STAGE_GROUPS * tile_bytes(QT) + (size_t)p.kgroups * XQ_GROUP_BYTES + 16 +
+  const size_t smem = (size_t)NS * Cfg<QT>::SG * tile_bytes(QT) + (size_t)p.kgroups * (XQ_GROUP_BYTES + Cfg<QT>::XSUB) + 16 +
                       (2 * CONS_WARPS * 16 + CONS_WARPS + 32) * sizeof(float) + (2 * NS + 1) * sizeof(uint64_t) + 16;
   if (smem > 220 * 1024) return B200Q_ERR_TOO_LARGE;
   auto kern = qgemv_kernel<QT, XQ_IN, XQ_OUT>;
@@ -373,10 +382,11 @@ extern "C" size_t b200q_xq_bytes(int n) { return n > 0 ? xq_record_bytes(n) : 0;
 
 extern "C" int b200q_gemv(const b200q_gemv_args* a, void* stream) {
   if (!a || !a->w_packed || (!a->x && !a->xq_in) || (!a->y && !a->xq_out && !a->n_peers)) return B200Q_ERR_BAD_ARG;
-  if (a->qtype == B200Q_Q6_K) return B200Q_ERR_UNSUPPORTED;
-  if (a->qtype != B200Q_Q4_0 && a->qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
+  if (a->qtype != B200Q_Q4_0 && a->qtype != B200Q_Q8_0 && a->qtype != B200Q_Q6_K) return B200Q_ERR_BAD_ARG;
   if (a->n_out <= 0 || a->n_in <= 0 || a->m <= 0 || a->m > 65535) return B200Q_ERR_BAD_ARG;
-  if (a->n_in % 32) return B200Q_ERR_BAD_SHAPE;
+  if (a->n_in % (a->qtype == B200Q_Q6_K ? 256 : 32)) return B200Q_ERR_BAD_SHAPE;
+  // Q6_K: plain linears only, and the kernel quantises the activations itself (it needs sums per 16-element sub-block)
+  if (a->qtype == B200Q_Q6_K && (a->epilogue != B200Q_EPI_LINEAR || a->xq_in)) return B200Q_ERR_UNSUPPORTED;
   if ((a->x_dtype != B200Q_F32 && a->x_dtype != B200Q_F16) || (a->y_dtype != B200Q_F32 && a->y_dtype != B200Q_F16)) return B200Q_ERR_BAD_ARG;
   if (a->epilogue != B200Q_EPI_LINEAR && a->epilogue != B200Q_EPI_SILU_MUL) return B200Q_ERR_BAD_ARG;
   if (a->epilogue == B200Q_EPI_SILU_MUL && (a->bias || a->residual)) return B200Q_ERR_UNSUPPORTED;
@@ -414,6 +424,8 @@ extern "C" int b200q_gemv(const b200q_gemv_args* a, void* stream) {
     if (xi) return xo ? launch_gemv<B200Q_Q4_0, true, true>(a, p, (cudaStream_t)stream) : launch_gemv<B200Q_Q4_0, true, false>(a, p, (cudaStream_t)stream);
     return xo ? launch_gemv<B200Q_Q4_0, false, true>(a, p, (cudaStream_t)stream) : launch_gemv<B200Q_Q4_0, false, false>(a, p, (cudaStream_t)stream);
   }
+  if (a->qtype == B200Q_Q6_K)
+    return xo ? launch_gemv<B200Q_Q6_K, false, true>(a, p, (cudaStream_t)stream) : launch_gemv<B200Q_Q6_K, false, false>(a, p, (cudaStream_t)stream);
   if (xi) return xo ? launch_gemv<B200Q_Q8_0, true, true>(a, p, (cudaStream_t)stream) : launch_gemv<B200Q_Q8_0, true, false>(a, p, (cudaStream_t)stream);
   return xo ? launch_gemv<B200Q_Q8_0, false, true>(a, p, (cudaStream_t)stream) : launch_gemv<B200Q_Q8_0, false, false>(a, p, (cudaStream_t)stream);
 }

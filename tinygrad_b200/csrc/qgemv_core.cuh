@@ -92,4 +92,45 @@ __device__ __forceinline__ void tile_mac(const uint8_t* tile, int lane, const ui
   acc1 = fmaf(v2, d1.x, fmaf(v3, d1.y, acc1));
 }
 
+// One Q6_K weight tile (16 rows x 128 columns = half a super-block per row) against the same activation digits.
+// Tile bytes: uint4 L[2][32] low nibbles of the 6-bit quants (lane (g, t) of half h: row 8h + g, block t; byte i = element i | element
+// i + 16 << 4), uint2 H[2][32] their high 2 bits (.x byte k: bits 2m, 2m+1 = element 4m + k, m = 0..3; .y the same for elements
+// 16..31), int8 SC[16][8] sub-block scales (sub-block = 2 * block + half of the block), fp16 D[16] super-block scales.
+// The quants stay unsigned (0..63) in the MMA; `sub` = the four offsets {block A first half, second half, block B first, second} of
+// the lane's two columns (zero on the lanes that hold the low digits).  Weight value = d * scale * (q - 32)
+// (tinygrad/llm/gguf.py:68-72).
+__device__ __forceinline__ void tile_mac_q6k(const uint8_t* tile, int lane, const uint4& bq0, const uint4& bq1, const float4& st, const float4& sub,
+                                             float& acc0, float& acc1) {
+  const uint4* lp = reinterpret_cast<const uint4*>(tile);
+  const uint2* hp = reinterpret_cast<const uint2*>(tile + 1024);
+  const uint4 l0 = lp[lane], l1 = lp[32 + lane];      // rows g and g + 8
+  const uint2 h0 = hp[lane], h1 = hp[32 + lane];
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t s0 = *reinterpret_cast<const uint32_t*>(tile + 1536 + g * 8 + (t & 1) * 4);
+  const uint32_t s1 = *reinterpret_cast<const uint32_t*>(tile + 1536 + (g + 8) * 8 + (t & 1) * 4);
+  const __half* dp = reinterpret_cast<const __half*>(tile + 1664);
+  const float d0 = __half2float(dp[g]), d1 = __half2float(dp[g + 8]);
+  const uint32_t M = 0x0F0F0F0Fu, H = 0x30303030u;
+  int c0[4], c1[4];
+  // first halves of the blocks (elements 0..15): two MMAs into c0; second halves into c1
+  imma0<B200Q_Q4_0>(c0, (l0.x & M) | ((h0.x << 4) & H), (l1.x & M) | ((h1.x << 4) & H), (l0.y & M) | ((h0.x << 2) & H), (l1.y & M) | ((h1.x << 2) & H),
+                    bq0.x, bq0.z);
+  imma<B200Q_Q4_0>(c0, (l0.z & M) | (h0.x & H), (l1.z & M) | (h1.x & H), (l0.w & M) | ((h0.x >> 2) & H), (l1.w & M) | ((h1.x >> 2) & H), bq1.x, bq1.z);
+  imma0<B200Q_Q4_0>(c1, ((l0.x >> 4) & M) | ((h0.y << 4) & H), ((l1.x >> 4) & M) | ((h1.y << 4) & H), ((l0.y >> 4) & M) | ((h0.y << 2) & H),
+                    ((l1.y >> 4) & M) | ((h1.y << 2) & H), bq0.y, bq0.w);
+  imma<B200Q_Q4_0>(c1, ((l0.z >> 4) & M) | (h0.y & H), ((l1.z >> 4) & M) | (h1.y & H), ((l0.w >> 4) & M) | ((h0.y >> 2) & H),
+                   ((l1.w >> 4) & M) | ((h1.y >> 2) & H), bq1.y, bq1.w);
+  // columns of this lane: blocks A = 2 * (t & 1) and B = A + 1 (high digits on t < 2, low digits on t >= 2)
+  const float a0 = fmaf((float)c0[0], st.x, -sub.x), a1 = fmaf((float)c1[0], st.x, -sub.y);      // row g, block A, halves 0 / 1
+  const float b0 = fmaf((float)c0[1], st.z, -sub.z), b1 = fmaf((float)c1[1], st.z, -sub.w);      // row g, block B
+  const float e0 = fmaf((float)c0[2], st.x, -sub.x), e1 = fmaf((float)c1[2], st.x, -sub.y);      // row g + 8
+  const float f0 = fmaf((float)c0[3], st.z, -sub.z), f1 = fmaf((float)c1[3], st.z, -sub.w);
+  const float v0 = fmaf(a0, (float)(int8_t)(s0 & 0xFF), fmaf(a1, (float)(int8_t)((s0 >> 8) & 0xFF), fmaf(b0, (float)(int8_t)((s0 >> 16) & 0xFF),
+                        b1 * (float)(int8_t)(s0 >> 24))));
+  const float v1 = fmaf(e0, (float)(int8_t)(s1 & 0xFF), fmaf(e1, (float)(int8_t)((s1 >> 8) & 0xFF), fmaf(f0, (float)(int8_t)((s1 >> 16) & 0xFF),
+                        f1 * (float)(int8_t)(s1 >> 24))));
+  acc0 = fmaf(v0, d0, acc0);
+  acc1 = fmaf(v1, d1, acc1);
+}
+
 }  // namespace

@@ -106,6 +106,68 @@ __global__ void repack_kernel(int qtype, const uint8_t* __restrict__ raw0, const
   sp[(2 * g + (t >> 1)) * 4 + h * 2 + (t & 1)] = scale;
 }
 
+// Q6_K re-tiling (tile layout: tile_mac_q6k, qgemv_core.cuh).  One thread per (tile, half, lane) = one (row, 32-element block).
+// Element e of a super-block: low nibble ql[(e >> 7) * 64 + (e & 63)] >> 4 * ((e >> 6) & 1), high bits qh[(e >> 7) * 32 + (e & 31)] >>
+// 2 * ((e >> 5) & 3), scale scales[e >> 4] (tinygrad/llm/gguf.py:68-72).
+__device__ __forceinline__ int q6k_quant(const uint8_t* b, int e) {
+  const int hh = e >> 7, m = e & 127;
+  const int xl = (b[hh * 64 + (m & 63)] >> ((m >> 6) * 4)) & 0xF, xh = (b[128 + hh * 32 + (m & 31)] >> ((m >> 5) * 2)) & 3;
+  return xl | (xh << 4);
+}
+__global__ void repack_q6k_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ packed, int n_out, int nsb, int n_row_tiles, int kgroups) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t total = (int64_t)n_row_tiles * kgroups * 64;
+  if (idx >= total) return;
+  const int l = (int)(idx & 31), h = (int)((idx >> 5) & 1);
+  const int64_t tile = idx >> 6;
+  const int j = (int)(tile % kgroups), rt = (int)(tile / kgroups);
+  const int g = l >> 2, t = l & 3, row = rt * 16 + h * 8 + g, sb = j >> 1, e0 = (j & 1) * 128 + t * 32;
+  uint8_t* tp = packed + tile * 1696;
+  uint32_t lw[4] = {0u, 0u, 0u, 0u}, hw[2] = {0u, 0u};
+  int sc0 = 0, sc1 = 0;
+  unsigned short d = 0;          // a padded row contributes nothing
+  if (row < n_out && sb < nsb) {
+    const uint8_t* b = raw + ((int64_t)row * nsb + sb) * 210;
+    for (int i = 0; i < 16; i++) {
+      const int qa = q6k_quant(b, e0 + i), qb = q6k_quant(b, e0 + 16 + i);
+      lw[i >> 2] |= (uint32_t)((qa & 15) | ((qb & 15) << 4)) << ((i & 3) * 8);
+      hw[0] |= (uint32_t)(qa >> 4) << ((i & 3) * 8 + (i >> 2) * 2);
+      hw[1] |= (uint32_t)(qb >> 4) << ((i & 3) * 8 + (i >> 2) * 2);
+    }
+    sc0 = b[192 + (e0 >> 4)]; sc1 = b[192 + (e0 >> 4) + 1];
+    d = (unsigned short)(b[208] | (b[209] << 8));
+  }
+  reinterpret_cast<uint4*>(tp)[h * 32 + l] = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+  reinterpret_cast<uint2*>(tp + 1024)[h * 32 + l] = make_uint2(hw[0], hw[1]);
+  tp[1536 + (h * 8 + g) * 8 + t * 2] = (uint8_t)sc0;
+  tp[1536 + (h * 8 + g) * 8 + t * 2 + 1] = (uint8_t)sc1;
+  if (t == 0) reinterpret_cast<unsigned short*>(tp + 1664)[h * 8 + g] = d;
+}
+
+template <typename OutT>
+__global__ void dequant_packed_q6k_kernel(const uint8_t* __restrict__ packed, OutT* __restrict__ out, int rows, int n_in, int n_row_tiles, int kgroups) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t total = (int64_t)n_row_tiles * kgroups * 64;
+  if (idx >= total) return;
+  const int l = (int)(idx & 31), h = (int)((idx >> 5) & 1);
+  const int64_t tile = idx >> 6;
+  const int j = (int)(tile % kgroups), rt = (int)(tile / kgroups);
+  const int g = l >> 2, t = l & 3, row = rt * 16 + h * 8 + g, blk = j * 4 + t;
+  if (row >= rows || blk * 32 >= n_in) return;
+  const uint8_t* tp = packed + tile * 1696;
+  const uint4 lq = reinterpret_cast<const uint4*>(tp)[h * 32 + l];
+  const uint2 hq = reinterpret_cast<const uint2*>(tp + 1024)[h * 32 + l];
+  const uint32_t lw[4] = {lq.x, lq.y, lq.z, lq.w}, hw[2] = {hq.x, hq.y};
+  const float d = __half2float(__ushort_as_half(reinterpret_cast<const unsigned short*>(tp + 1664)[h * 8 + g]));
+  OutT* o = out + (int64_t)row * n_in + blk * 32;
+  for (int e = 0; e < 32; e++) {
+    const int i = e & 15, hf = e >> 4;
+    const int lo = (lw[i >> 2] >> ((i & 3) * 8 + hf * 4)) & 0xF, hi = (hw[hf] >> ((i & 3) * 8 + (i >> 2) * 2)) & 3;
+    const float sc = (float)(int8_t)tp[1536 + (h * 8 + g) * 8 + t * 2 + hf];
+    store_val<OutT>(o, e, __fmul_rn(__fmul_rn(d, (float)((lo | (hi << 4)) - 32)), sc));      // (d * q) * scales, in that order
+  }
+}
+
 // packed -> row-major values, rows in packed order.  One thread per (row, block).
 template <typename OutT>
 __global__ void dequant_packed_kernel(int qtype, const uint8_t* __restrict__ packed, OutT* __restrict__ out, int rows, int n_in,
@@ -162,16 +224,24 @@ extern "C" int b200q_dequant_raw(int qtype, const void* raw, void* out, int64_t 
 }
 
 extern "C" size_t b200q_packed_bytes(int qtype, int n_out, int n_in) {
-  if ((qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0) || n_out <= 0 || n_in <= 0) return 0;
+  if ((qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0 && qtype != B200Q_Q6_K) || n_out <= 0 || n_in <= 0) return 0;
+  if (qtype == B200Q_Q6_K && n_in % 256) return 0;
   return (size_t)ceil_div(n_out, TILE_ROWS) * ceil_div(n_in, GROUP_ELEMS) * tile_bytes(qtype);
 }
 
 extern "C" int b200q_repack(int qtype, const void* raw0, const void* raw1, void* packed, int n_out, int n_in, void* stream) {
-  if (qtype == B200Q_Q6_K) return B200Q_ERR_UNSUPPORTED;
-  if (qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
+  if (qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0 && qtype != B200Q_Q6_K) return B200Q_ERR_BAD_ARG;
   if (!raw0 || !packed || n_out <= 0 || n_in <= 0) return B200Q_ERR_BAD_ARG;
-  if (n_in % 32) return B200Q_ERR_BAD_SHAPE;
+  if (n_in % (qtype == B200Q_Q6_K ? 256 : 32)) return B200Q_ERR_BAD_SHAPE;
   if ((uintptr_t)packed & 15) return B200Q_ERR_MISALIGNED;
+  if (qtype == B200Q_Q6_K) {
+    if (raw1) return B200Q_ERR_UNSUPPORTED;       // no interleaved gate / up tiles for this format
+    const int nrt = ceil_div(n_out, TILE_ROWS), kg = n_in / GROUP_ELEMS;
+    const int64_t tot = (int64_t)nrt * kg * 64;
+    repack_q6k_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint8_t*)raw0, (uint8_t*)packed, n_out, n_in / 256, nrt, kg);
+    B200Q_CHECK_CUDA(cudaGetLastError());
+    return B200Q_OK;
+  }
   int rows = raw1 ? 2 * ceil_div(n_out, 8) * 8 : n_out;       // interleaved: tiles of 8+8 rows
   int n_row_tiles = raw1 ? ceil_div(n_out, 8) : ceil_div(n_out, TILE_ROWS), kgroups = ceil_div(n_in, GROUP_ELEMS);
   (void)rows;
@@ -183,14 +253,19 @@ extern "C" int b200q_repack(int qtype, const void* raw0, const void* raw1, void*
 }
 
 extern "C" int b200q_dequant_packed(int qtype, const void* packed, void* out, int n_out, int n_in, int out_dtype, void* stream) {
-  if (qtype == B200Q_Q6_K) return B200Q_ERR_UNSUPPORTED;
-  if (qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
+  if (qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0 && qtype != B200Q_Q6_K) return B200Q_ERR_BAD_ARG;
   if (!packed || !out || n_out <= 0 || n_in <= 0 || (out_dtype != B200Q_F32 && out_dtype != B200Q_F16)) return B200Q_ERR_BAD_ARG;
-  if (n_in % 32) return B200Q_ERR_BAD_SHAPE;
+  if (n_in % (qtype == B200Q_Q6_K ? 256 : 32)) return B200Q_ERR_BAD_SHAPE;
   if ((uintptr_t)packed & 15) return B200Q_ERR_MISALIGNED;
   int n_row_tiles = ceil_div(n_out, TILE_ROWS), kgroups = ceil_div(n_in, GROUP_ELEMS);
   int64_t total = (int64_t)n_row_tiles * kgroups * 64;
   unsigned blocks = (unsigned)((total + 255) / 256);
+  if (qtype == B200Q_Q6_K) {
+    if (out_dtype == B200Q_F32) dequant_packed_q6k_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)packed, (float*)out, n_out, n_in, n_row_tiles, kgroups);
+    else dequant_packed_q6k_kernel<__half><<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)packed, (__half*)out, n_out, n_in, n_row_tiles, kgroups);
+    B200Q_CHECK_CUDA(cudaGetLastError());
+    return B200Q_OK;
+  }
   if (out_dtype == B200Q_F32)
     dequant_packed_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>(qtype, (const uint8_t*)packed, (float*)out, n_out, n_in, n_row_tiles, kgroups);
   else

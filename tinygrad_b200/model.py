@@ -64,7 +64,7 @@ class Transformer:
     """state_dict: the reference's tensor names -> numpy arrays; Linear weights as raw
     GGUF block bytes (uint8), embeddings / norms / biases as fp16.
     tp: a tensor_parallel.TPGroup; `config` is then the FULL model and `state_dict` this rank's shard (shard_state_dict).
-    output_type: GGML type of `output.weight` when it differs from the block Linears' (Q6_K / F16 / F32 heads run the dense GEMV).
+    output_type: GGML type of `output.weight` when it differs from the block Linears' (F16 / BF16 / F32 heads run the dense GEMV).
     prefill_rows: prompts with at least this many uncached tokens go through the tensor-core GEMM path, `prefill_chunk` rows at a
     time (0: always one token per step, whose fp32-activation numerics are the reference's own); shorter ones take decode steps.
     engine: how a one-token step runs.  "step": one persistent kernel for the whole step (b200q_decode_step); "chain": five launches per
@@ -97,7 +97,7 @@ class Transformer:
     lt = dict(linear_types or {})
     names7 = ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")
     self.dense_blocks = ggml_type not in (_lib.Q4_0, _lib.Q8_0) or any(lt.get(f"blk.{i}.{n}.weight", ggml_type) != ggml_type
-                                                                      for i in range(c.num_blocks) for n in names7 if f"blk.{i}.{n}.weight" in sd)
+                                                                      for i in range(c.num_blocks) for n in names7)
     if self.dense_blocks:
       assert tp is None and batch == 1 and not c.num_experts, "the dense-weight path serves single-sequence dense models on one GPU"
       def dense16(name, n_out, n_in):       # -> fp16 [n_out, n_in] on the device, whatever the tensor's type
@@ -165,7 +165,8 @@ class Transformer:
       self.weight_bytes += (qkv_rows * c.dim + c.dim * self.q_dim + (0 if c.num_experts else 3 * c.hidden_dim * c.dim)) // nel * nby
     if self.dense_blocks: self.up_buf = DeviceBuffer.empty((c.hidden_dim,), np.float32, zero=True)
     self.output_type = ggml_type if output_type is None else output_type
-    if self.output_type in (_lib.Q4_0, _lib.Q8_0):
+    # a Q6_K head (the usual companion of K-quant blocks) runs the fused GEMV too; several sequences at once go through the dense GEMV
+    if self.output_type in (_lib.Q4_0, _lib.Q8_0) or (self.output_type == _lib.Q6_K and batch == 1 and c.dim % 256 == 0):
       self.output = quant.repack(sd["output.weight"], c.vocab_size, c.dim, self.output_type)
       self.weight_bytes += c.vocab_size * c.dim // quant.GGML_QUANT[self.output_type][0] * quant.GGML_QUANT[self.output_type][1]
     else:
@@ -311,8 +312,9 @@ class Transformer:
         quant.gemv_dense(self.output.buf, self.output.dtype, c.vocab_size, c.dim, self.x, self.logits_part, norm_weight=self.output_norm,
                          norm_eps=c.norm_eps, flags=kw_after_coll["flags"], stream=s)
       else:
-        quant.gemv(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, None if in_a else self.x, self.logits_part,
-                   norm_weight=self.output_norm, norm_eps=c.norm_eps, **in_a, **kw_after_coll,
+        in_h = {} if self.output_type == _lib.Q6_K else in_a       # the Q6_K kernel quantises the row itself
+        quant.gemv(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, None if in_h else self.x, self.logits_part,
+                   norm_weight=self.output_norm, norm_eps=c.norm_eps, **in_h, **kw_after_coll,
                    **(dict(peers=self.mb_logits.targets, peer_rank=tp.rank) if peer else {}))
       if peer: self.mb_logits.reduce(self.logits, flags=fl, stream=s)          # every rank's vocabulary slice, handed over
       elif tp is not None: tp.all_gather(self.logits, self.logits_part)

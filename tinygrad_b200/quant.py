@@ -153,11 +153,11 @@ class QuantLinear:
   on activations of shape (..., in_features), fp16 or fp32, returns
   (..., out_features) in the activation dtype, as
   `x.linear(weight.transpose(), bias)` does (tinygrad/nn/__init__.py:177).
-  Q4_0 / Q8_0 weights run the fused dequant kernels (GEMV below 4 rows, tcgen05 GEMM from 4 rows on); F32 / F16 / BF16 and
-  Q6_K weights run the dense GEMV, 4 activation rows per launch."""
+  Q4_0 / Q8_0 weights run the fused dequant kernels (GEMV below 4 rows, tcgen05 GEMM from 4 rows on); Q6_K weights (in_features a
+  multiple of 256) the fused GEMV for any number of rows; F32 / F16 / BF16 weights the dense GEMV, 4 activation rows per launch."""
   def __init__(self, in_features: int, out_features: int, ggml_type: int, raw, bias=None):
     self.in_features, self.out_features, self.ggml_type = in_features, out_features, ggml_type
-    self.fused = ggml_type in (Q4_0, Q8_0)
+    self.fused = ggml_type in (Q4_0, Q8_0) or (ggml_type == Q6_K and in_features % 256 == 0)
     self.weight = repack(raw, out_features, in_features, ggml_type) if self.fused else DenseWeight(raw, out_features, in_features, ggml_type)
     self.bias = None if bias is None else DeviceBuffer.from_numpy(np.asarray(bias, dtype=np.float16))
 
@@ -170,7 +170,7 @@ class QuantLinear:
     if not self.fused:
       if m: gemv_dense(self.weight.buf, self.weight.dtype, self.out_features, self.in_features, x, y, m=m, x_dtype=dt, y_dtype=dt, bias=self.bias,
                        stream=stream)
-    elif m >= GEMM_MIN_ROWS:
+    elif m >= GEMM_MIN_ROWS and self.ggml_type != Q6_K:
       qgemm(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m, x_dtype=dt, y_dtype=dt, bias=self.bias, stream=stream)
     elif m:
       gemv(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m=m, x_dtype=dt, y_dtype=dt, bias=self.bias, stream=stream)

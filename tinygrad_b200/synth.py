@@ -109,6 +109,12 @@ class LazyDenseState:
     self.embd_vocab, self.linear_seed = embd_vocab or cfg.vocab_size, seed if linear_seed is None else linear_seed
     self.shapes = {n: (o, i) for n, o, i in linear_names(cfg)}
 
+  def __contains__(self, key) -> bool:
+    if not isinstance(key, str) or "." not in key: return False
+    name, kind = key.rsplit(".", 1)
+    if kind == "bias": return self.cfg.qkv_bias and name in self.shapes and name.split(".")[-1] in ("attn_q", "attn_k", "attn_v")
+    return kind == "weight" and (name in self.shapes or name == "token_embd" or name.endswith("_norm"))
+
   def __getitem__(self, key: str) -> np.ndarray:
     if self.distinct_blocks and key.startswith("blk."):
       _, i, rest = key.split(".", 2)
