@@ -410,6 +410,10 @@ int b200q_moe_route_pad(const float* logits, int n_tokens, int n_experts, int k,
  * Tables and scratch as b200q_moe_route_pad. */
 int b200q_moe_route_gating(const float* logits, const float* sel_bias, int n_tokens, int n_experts, int k, int gating, int normalize, float scale,
                            int pad, int32_t* topi, float* weights, int32_t* dest_row, int32_t* off, int32_t* counts, void* scratch, void* stream);
+/* The grouping tables alone, for a selection the caller already has (`ExpertWeights.__call__(sel, x)`, tinygrad/llm/model.py:21-27):
+ * topi [n_tokens, k] expert ids (entries outside 0..n_experts-1 must not occur) -> dest_row / off / counts as b200q_moe_route_pad. */
+int b200q_moe_route_tables(const int32_t* topi, int n_tokens, int n_experts, int k, int pad, int32_t* dest_row, int32_t* off, int32_t* counts,
+                           void* scratch, void* stream);
 /* Rows of row_bytes bytes (a multiple of 4) moved through an index table: gather = 0: dst[idx[i]] = src[i]; gather = 1:
  * dst[i] = src[idx[i]]; negative entries are skipped.  The regrouping step on both sides of the expert-parallel exchange
  * (`dispatch` / `combine` across ranks, extra/gemm/moe_routing.py:124-131). */

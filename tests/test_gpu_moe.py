@@ -182,6 +182,29 @@ def test_moe_ffn_matches_composed_oracle():
     assert_close(out, ref, tol=1e-2, what=f"MoE FFN mode {mode}")
 
 
+@pytest.mark.parametrize("per_slot", [False, True])
+def test_expert_weights_call_matches_the_reference_semantics(per_slot):
+  """`ExpertWeights.__call__(sel, x)` (tinygrad/llm/model.py:21-27): out[t, j] = x[t, j or 0] @ weight[sel[t, j]].T, here on MXFP8 operands:
+  against the dequantised-operands product the reference tests its MX GEMM with (test/backend/test_asm_gemm.py:289-292)."""
+  from tinygrad_b200 import moe
+  from tinygrad_b200.runtime import DeviceBuffer
+  rng = np.random.default_rng(31)
+  T, k, E, n_in, n_out = 37, 3, 6, 256, 512
+  w = (rng.standard_normal((E, n_out, n_in)) * 0.05).astype(np.float32)
+  sel = np.stack([rng.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+  sel[5] = [4, 4, 1]                                               # the same expert twice for one token is a legal selection
+  x = moe.from_bf16_bits(moe.to_bf16_bits(rng.standard_normal((T, k if per_slot else 1, n_in)).astype(np.float32)))
+  ew = moe.ExpertWeights(w)
+  out = moe.from_bf16_bits(ew(DeviceBuffer.from_numpy(sel), DeviceBuffer.from_numpy(moe.to_bf16_bits(x))).numpy())
+  assert out.shape == (T, k, n_out)
+  w_q, w_e8 = mx.quantize_mxfp8(w)
+  w_dq = mx.dequantize_mxfp8(w_q, w_e8)
+  x_dq = mx.dequantize_mxfp8(*mx.quantize_mxfp8(x))
+  ref = np.stack([[x_dq[t, j if per_slot else 0] @ w_dq[sel[t, j]].T for j in range(k)] for t in range(T)])
+  assert_close(out, mx.to_bf16(ref), tol=1e-2, what="ExpertWeights(sel, x)")
+  with pytest.raises(ValueError): moe.ExpertWeights(np.zeros((2, 100, 128), np.float32))
+
+
 def test_no_tensor_core_wait_ran_out():
   import ctypes
   from tinygrad_b200 import _lib

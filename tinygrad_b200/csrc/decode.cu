@@ -99,6 +99,15 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
 }
 
+#ifdef B200Q_GEMV_PROF
+__device__ unsigned long long g_attn_prof[4096 * 8];
+__device__ unsigned g_attn_prof_n;
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define ASTAMP(i) do { if (threadIdx.x == 0) g_attn_prof[prof_slot * 8 + (i)] = gtime(); } while (0)
+#else
+#define ASTAMP(i) do {} while (0)
+#endif
+
 template <typename KV>
 __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_attn_args a) {
   constexpr int VEC = KvIO<KV>::VEC;
@@ -112,6 +121,16 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
   __shared__ int s_last;
   const int kvh = blockIdx.x, split = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#ifdef B200Q_GEMV_PROF
+  __shared__ unsigned s_prof_slot;
+  if (threadIdx.x == 0) {
+    s_prof_slot = (unsigned)a.flags >> 16;           // experiment builds: the host puts the launch's slot into the upper half of flags
+    if (blockIdx.x == 0 && blockIdx.y == 0) g_attn_prof[s_prof_slot * 8 + 0] = gtime();
+  }
+  __syncthreads();
+  const unsigned prof_slot = s_prof_slot;
+  const bool prof_cta = blockIdx.x == 0 && blockIdx.y == 0;
+#endif
   pdl_launch_dependents();
   const int lo = split * ATTN_CHUNK;
   KV* kc = reinterpret_cast<KV*>(a.k_cache) + (size_t)kvh * a.max_context * hd;
@@ -132,6 +151,9 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
   const int pos_early = min(max(__ldcg(a.pos), 0), a.max_context - 1);
   fetch_rows(pos_early);
   pdl_wait();
+#ifdef B200Q_GEMV_PROF
+  if (prof_cta) ASTAMP(1);
+#endif
   const int pos = __ldcg(a.pos);
   if (pos < 0 || pos >= a.max_context) {        // no cache row for this position: touch nothing (uniform over the grid)
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -143,6 +165,9 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
     __syncthreads();
     fetch_rows(pos);
   }
+#ifdef B200Q_GEMV_PROF
+  if (prof_cta) ASTAMP(5);
+#endif
   const int n_ctx = pos + 1;
   if (lo >= n_ctx) { asm volatile("cp.async.wait_group 0;" ::: "memory"); return; }
   const int n = min(ATTN_CHUNK, n_ctx - lo);
@@ -171,6 +196,9 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
+#ifdef B200Q_GEMV_PROF
+  if (prof_cta) ASTAMP(6);
+#endif
 
   const int d0 = lane * 4;
   const bool dl = d0 < hd;
@@ -183,9 +211,15 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
     float lmax = -INFINITY;
     for (int i = lane; i < n; i += 32) {
       const KV* kr = s_k + i * rstride;
-      float s = 0.f;
-#pragma unroll 4
-      for (int d = 0; d < hd; d += VEC) s += KvIO<KV>::dot(kr + d, q + d);
+      // four running sums: a lane's dot product is a dependent chain otherwise, and this warp has its scheduler to itself
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      int d = 0;
+      for (; d + 4 * VEC <= hd; d += 4 * VEC) {
+        s0 += KvIO<KV>::dot(kr + d, q + d); s1 += KvIO<KV>::dot(kr + d + VEC, q + d + VEC);
+        s2 += KvIO<KV>::dot(kr + d + 2 * VEC, q + d + 2 * VEC); s3 += KvIO<KV>::dot(kr + d + 3 * VEC, q + d + 3 * VEC);
+      }
+      for (; d < hd; d += VEC) s0 += KvIO<KV>::dot(kr + d, q + d);
+      float s = (s0 + s1) + (s2 + s3);
       s *= scale;
       sc[i] = s;
       lmax = fmaxf(lmax, s);
@@ -198,12 +232,21 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
     float4 o = make_float4(0, 0, 0, 0);
     if (dl) {
       const KV* vr = s_v + d0;
-#pragma unroll 8
-      for (int i = 0; i < n; i++) {
+      float4 o2 = make_float4(0, 0, 0, 0);      // even / odd positions in two independent sums
+      int i = 0;
+#pragma unroll 4
+      for (; i + 2 <= n; i += 2) {
+        const float pr = sc[i], pr2 = sc[i + 1];
+        const float4 v = KvIO<KV>::load4(vr + i * rstride), v2 = KvIO<KV>::load4(vr + (i + 1) * rstride);
+        o.x = fmaf(pr, v.x, o.x); o.y = fmaf(pr, v.y, o.y); o.z = fmaf(pr, v.z, o.z); o.w = fmaf(pr, v.w, o.w);
+        o2.x = fmaf(pr2, v2.x, o2.x); o2.y = fmaf(pr2, v2.y, o2.y); o2.z = fmaf(pr2, v2.z, o2.z); o2.w = fmaf(pr2, v2.w, o2.w);
+      }
+      if (i < n) {
         const float pr = sc[i];
         const float4 v = KvIO<KV>::load4(vr + i * rstride);
         o.x = fmaf(pr, v.x, o.x); o.y = fmaf(pr, v.y, o.y); o.z = fmaf(pr, v.z, o.z); o.w = fmaf(pr, v.w, o.w);
       }
+      o.x += o2.x; o.y += o2.y; o.z += o2.z; o.w += o2.w;
     }
     if (n_active == 1) {   // short context: this CTA holds the whole softmax
       const float inv = 1.f / den;
@@ -217,6 +260,10 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
     }
   }
   if (n_active == 1) return;
+#ifdef B200Q_GEMV_PROF
+  if (prof_cta) ASTAMP(2);
+  if (threadIdx.x == 0) atomicMax(&g_attn_prof[prof_slot * 8 + 7], gtime());      // this slot is re-used: max over CTAs of "partials done"
+#endif
   // last CTA of this KV head merges the slices
   __threadfence();
   __syncthreads();
@@ -229,6 +276,9 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
   __syncthreads();
   if (!s_last) return;
   __threadfence();
+#ifdef B200Q_GEMV_PROF
+  if (kvh == 0) { if (threadIdx.x == 0) g_attn_prof[prof_slot * 8 + 3] = gtime(); }
+#endif
   if (warp < n_rep) {
     const float* hp = partial + (size_t)(kvh * n_rep + warp) * a.n_split * pstride;
     // Batches of 16 slices: the statistics (one slice per lane) and every lane's 4 output dims of all 16 slices are
@@ -260,7 +310,25 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
     if (dl) *reinterpret_cast<float4*>(a.out + (size_t)(kvh * n_rep + warp) * hd + d0) = r;
     if (a.xq_out) quant_block_8x4(r, lane & 7, (kvh * n_rep + warp) * 4 + (lane >> 3), XqDst(a.xq_out, a.n_heads));
   }
+#ifdef B200Q_GEMV_PROF
+  if (kvh == 0) { __syncthreads(); if (threadIdx.x == 0) g_attn_prof[prof_slot * 8 + 4] = gtime(); }
+#endif
 }
+
+#ifdef B200Q_GEMV_PROF
+}  // namespace
+extern "C" int b200q_attn_prof_read(unsigned long long* out, int max_slots, unsigned* n) {
+  B200Q_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_attn_prof, sizeof(unsigned long long) * 8 * (max_slots < 4096 ? max_slots : 4096)));
+  B200Q_CHECK_CUDA(cudaMemcpyFromSymbol(n, g_attn_prof_n, sizeof(unsigned)));
+  return B200Q_OK;
+}
+extern "C" int b200q_attn_prof_reset(void) {
+  static unsigned long long zeros[4096 * 8];
+  B200Q_CHECK_CUDA(cudaMemcpyToSymbol(g_attn_prof, zeros, sizeof(zeros)));
+  return B200Q_OK;
+}
+namespace {
+#endif
 
 // ---------------------------------------------------------------------------
 // arg-max with the lowest index winning ties, then tokens[pos+1] = it and pos += 1.
@@ -384,6 +452,12 @@ extern "C" int b200q_attn_decode(const b200q_attn_args* a, void* stream) {
     B200Q_CHECK_CUDA(cudaFuncSetAttribute(attn_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
     attr_set.set(dev);
   }
+#ifdef B200Q_GEMV_PROF
+  static int prof_counter = 0;
+  b200q_attn_args ap = *a;
+  ap.flags = (ap.flags & 0xFFFF) | ((prof_counter++ & 4095) << 16);
+  a = &ap;
+#endif
   if (a->kv_dtype == B200Q_F16) B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<__half>, grid, block, smem, (cudaStream_t)stream, pdl, *a));
   else B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<float>, grid, block, smem, (cudaStream_t)stream, pdl, *a));
   return B200Q_OK;

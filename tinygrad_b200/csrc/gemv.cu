@@ -50,6 +50,7 @@ struct GemvParams {
   // (peer memory over NVLink; see peer.cu), where a small kernel sums the ranks' slots (all-reduce) or copies them (all-gather)
   uint32_t* peer[B200Q_MAX_PEERS];
   int n_peers, peer_rank;
+  int prof_id;              // experiment builds only: the launch's slot in the time-stamp table
 };
 
 // Tunables (overridable at compile time for experiments).
@@ -78,6 +79,16 @@ template <int QT> struct Cfg;      // NS: ring depth, SG: weight tiles per stage
 template <> struct Cfg<B200Q_Q4_0> { static constexpr int NS = B200Q_NS_Q4, SG = STAGE_GROUPS, XSUB = 0; };   // stage = SG x 1152 B
 template <> struct Cfg<B200Q_Q8_0> { static constexpr int NS = 2, SG = STAGE_GROUPS, XSUB = 0; };             // stage = SG x 2176 B
 template <> struct Cfg<B200Q_Q6_K> { static constexpr int NS = 3, SG = CONS_WARPS, XSUB = 32; };              // stage = SG x 1696 B
+
+#ifdef B200Q_GEMV_PROF
+// experiment build only: per-launch time stamps of CTA 0 (entry, dependency resolved, row staged, first stage landed, tiles done, exit)
+__device__ unsigned long long g_gemv_prof[4096 * 8];
+__device__ unsigned g_gemv_prof_n;
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define PSTAMP(i) do { if (blockIdx.x == 0 && tid == 0) g_gemv_prof[prof_slot * 8 + (i)] = gtime(); } while (0)
+#else
+#define PSTAMP(i) do {} while (0)
+#endif
 
 __device__ __forceinline__ void cons_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONS_THREADS) : "memory"); }
 
@@ -123,6 +134,16 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int m = blockIdx.y;
   const int stages_per_tile = (p.kgroups + SG - 1) / SG;
+#ifdef B200Q_GEMV_PROF
+  __shared__ unsigned s_prof_slot;
+  if (tid == 0) {
+    s_prof_slot = (unsigned)p.prof_id & 4095u;
+    if (blockIdx.x == 0) {
+      g_gemv_prof[s_prof_slot * 8 + 6] = ((unsigned long long)p.n_out << 32) | (unsigned)p.n_in;
+      g_gemv_prof[s_prof_slot * 8 + 0] = gtime();
+    }
+  }
+#endif
 
   if (tid == 0) {
     for (int s = 0; s < NS; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, CONS_WARPS); }
@@ -131,6 +152,9 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+#ifdef B200Q_GEMV_PROF
+  const unsigned prof_slot = s_prof_slot;
+#endif
   pdl_launch_dependents();
 
   if (warp == CONS_WARPS) {
@@ -143,9 +167,11 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
       auto after_prefetch = [&]() {
         pdl_wait();
         if (XQ_IN) {
-          const uint32_t bytes = (uint32_t)p.kgroups * XQ_GROUP_BYTES;
+          // the record in pieces on one barrier: a single bulk copy is served slowly, several overlap
+          const uint32_t bytes = (uint32_t)p.kgroups * XQ_GROUP_BYTES, piece = 8 * XQ_GROUP_BYTES;
           mbar_expect_tx(xbar, bytes);
-          bulk_g2s(smem_u32(record), p.xq_in, bytes, xbar);
+          for (uint32_t o = 0; o < bytes; o += piece)
+            bulk_g2s(smem_u32(record) + o, reinterpret_cast<const unsigned char*>(p.xq_in) + o, min(piece, bytes - o), xbar);
         }
         x_issued = true;
       };
@@ -180,6 +206,7 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
 
   // -------------------------------- consumers --------------------------------
   pdl_wait();
+  PSTAMP(1);
   const int g = lane >> 2, t = lane & 3;
   // warp 0 finishes every row tile: fetch the addends of the CTA's first tile now, so their latency hides behind the MMAs
   float pre_add = 0.f;
@@ -196,7 +223,10 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
   } else {
     // quantise the activation row here: 8 threads per block of 32, 4 elements each.  The loads of PF blocks are issued
     // before any is used, so a batch costs one L2 round trip instead of one per block.
-    constexpr int PF = 4, BSTEP = CONS_THREADS / 8;
+#ifndef B200Q_XPF
+#define B200Q_XPF 4
+#endif
+    constexpr int PF = B200Q_XPF, BSTEP = CONS_THREADS / 8;
     const int nblk_pad = p.kgroups * 4, q = tid & 7;
     const XqDst dst(record, p.kgroups);
     for (int b0 = tid >> 3; b0 < nblk_pad; b0 += PF * BSTEP) {
@@ -234,6 +264,7 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
   }
   if (XQ_IN && !mbar_wait(xbar, 0)) *s_abort = 1;
   cons_bar_sync();
+  PSTAMP(2);
   float rs = 1.f;
   if (p.norm_w) {
     float tot = 0.f;
@@ -253,6 +284,7 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
       for (int s = 0; s < stages_per_tile; s++, it++) {
         const int slot = it % NS, groups = min(SG, p.kgroups - s * SG);
         if (!mbar_wait(full0 + 8 * slot, (it / NS) & 1)) { *s_abort = 1; break; }
+        if (it == 0) PSTAMP(3);
         const uint8_t* stage = ring + slot * STAGE_BYTES;
 #pragma unroll
         for (int u = 0; u < SG / CONS_WARPS; u++) {
@@ -273,6 +305,7 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + 8 * slot);
       }
+      PSTAMP(4);
       // quad lanes hold the columns {blocks 0,1 hi}, {2,3 hi}, {0,1 lo}, {2,3 lo}: add them
       acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1); acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
       acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1); acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
@@ -324,7 +357,27 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
       }
     }
   }
+  PSTAMP(5);
+#ifdef B200Q_GEMV_PROF
+  if (tid == 0) atomicMax(&g_gemv_prof[prof_slot * 8 + 7], gtime());      // the last CTA's exit
+#endif
 }
+
+#ifdef B200Q_GEMV_PROF
+}  // namespace
+extern "C" int b200q_gemv_prof_read(unsigned long long* out, int max_slots, unsigned* n) {
+  B200Q_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_gemv_prof, sizeof(unsigned long long) * 8 * (max_slots < 4096 ? max_slots : 4096)));
+  B200Q_CHECK_CUDA(cudaMemcpyFromSymbol(n, g_gemv_prof_n, sizeof(unsigned)));
+  return B200Q_OK;
+}
+extern "C" int b200q_gemv_prof_reset(void) {
+  static unsigned long long zeros[4096 * 8];
+  B200Q_CHECK_CUDA(cudaMemcpyToSymbol(g_gemv_prof, zeros, sizeof(zeros)));
+  return B200Q_OK;
+}
+int g_gemv_prof_host_counter = 0;
+namespace {
+#endif
 
 template <int QT, bool XQ_IN, bool XQ_OUT>
 int launch_gemv(const b200q_gemv_args* a, const GemvParams& p, cudaStream_t stream) {
@@ -352,6 +405,12 @@ int launch_gemv(const b200q_gemv_args* a, const GemvParams& p, cudaStream_t stre
   }
   const int max_ctas = a->max_ctas > 0 ? a->max_ctas : (int)(oc & 0xFF) * sm_count;
   const int grid_x = p.n_units < max_ctas ? p.n_units : max_ctas;
+#ifdef B200Q_GEMV_PROF
+  GemvParams pp = p;
+  pp.prof_id = g_gemv_prof_host_counter++;
+  B200Q_CHECK_CUDA(launch_k(kern, dim3(grid_x, a->m), dim3(NTHREADS), smem, stream, (a->flags & B200Q_FLAG_PDL) != 0, pp));
+  return B200Q_OK;
+#endif
   B200Q_CHECK_CUDA(launch_k(kern, dim3(grid_x, a->m), dim3(NTHREADS), smem, stream, (a->flags & B200Q_FLAG_PDL) != 0, p));
   return B200Q_OK;
 }
@@ -407,7 +466,7 @@ extern "C" int b200q_gemv(const b200q_gemv_args* a, void* stream) {
   p.x_f16 = a->x_dtype == B200Q_F16; p.y_f16 = a->y_dtype == B200Q_F16; p.epilogue = a->epilogue; p.eps = a->norm_eps;
   p.xq_in = a->xq_in; p.ss_in = a->ss_in; p.ss_count = a->ss_count;
   p.xq_out = a->xq_out; p.out_norm_w = (const __half*)a->xq_out_norm_weight; p.ss_out = a->ss_out;
-  p.n_peers = 0; p.peer_rank = 0;
+  p.n_peers = 0; p.peer_rank = 0; p.prof_id = 0;
   if (a->n_peers) {
     if (a->n_peers < 0 || a->n_peers > B200Q_MAX_PEERS || a->peer_rank < 0 || a->peer_rank >= a->n_peers || !a->peer_mailboxes) return B200Q_ERR_BAD_ARG;
     if (a->m != 1 || a->epilogue != B200Q_EPI_LINEAR) return B200Q_ERR_UNSUPPORTED;

@@ -373,6 +373,19 @@ extern "C" int b200q_moe_route_pad(const float* logits, int n_tokens, int n_expe
   return B200Q_OK;
 }
 
+extern "C" int b200q_moe_route_tables(const int32_t* topi, int n_tokens, int n_experts, int k, int pad, int32_t* dest_row, int32_t* off, int32_t* counts,
+                                      void* scratch, void* stream) {
+  if (!topi || !dest_row || !off || !scratch || pad <= 0 || n_tokens <= 0 || n_experts <= 0 || k <= 0) return B200Q_ERR_BAD_ARG;
+  if (n_experts > 32 * MAX_E_PER_LANE) return B200Q_ERR_BAD_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n = n_tokens * k, n_chunks = ceil_div(n, ROUTE_CHUNK);
+  route_count_kernel<<<n_chunks, ROUTE_CHUNK, n_experts * sizeof(int), st>>>(topi, n, n_experts, (int32_t*)scratch);
+  route_scan_kernel<<<1, 256, n_experts * sizeof(int), st>>>((int32_t*)scratch, n_chunks, n_experts, off, pad, counts);
+  route_place_kernel<<<n_chunks, ROUTE_CHUNK, 32 * n_experts * sizeof(int), st>>>(topi, n, n_experts, (const int32_t*)scratch, off, dest_row);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
 extern "C" int b200q_moe_route_gating(const float* logits, const float* sel_bias, int n_tokens, int n_experts, int k, int gating, int normalize, float scale,
                                       int pad, int32_t* topi, float* weights, int32_t* dest_row, int32_t* off, int32_t* counts, void* scratch, void* stream) {
   if (!logits || !topi || !weights || !dest_row || !off || !scratch || pad <= 0) return B200Q_ERR_BAD_ARG;

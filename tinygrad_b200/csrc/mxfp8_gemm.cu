@@ -13,21 +13,35 @@
 //              32-lane sub-partition, column r / 32: the layout the MMA reads), issues tcgen05.mma kind::mxf8f6f4.block_scale
 //              (scale_vec::1X, 128 x 256 x 32 per instruction, the tensor core applies both block scales), four per K step, and
 //              commits each step to the stage's "empty" mbarrier;
-//   warps 0-3, 9-12  epilogue: tcgen05.ld the fp32 accumulator (256 tensor-memory columns; two warps per 32-lane sub-partition,
-//              128 columns each), round to bf16, store.
-// Loaders run ahead across tile boundaries; only the accumulator hand-over (one buffer) serialises epilogue and next tile.
+//   warps 0-3, 9-20  epilogue: tcgen05.ld the fp32 accumulator (256 tensor-memory columns; four warps per 32-lane sub-partition,
+//              64 columns each) into registers, release the accumulator, then round to bf16 and store (or SwiGLU + requantise).
+// Loaders run ahead across tile boundaries; the accumulator (one buffer: 2 x 256 columns + the scale columns do not fit the 512 of
+// tensor memory) is handed back after one tensor-memory round trip, the epilogue's arithmetic and stores overlap the next tile's MMAs.
 // Every mbarrier wait is bounded; a wait that runs out raises a status word and makes every role leave.
 #include "common.cuh"
 #include "mxq.cuh"
+#include <cuda.h>
 #include <cuda_bf16.h>
+
+#ifndef B200Q_MX_TMA
+#define B200Q_MX_TMA 1      // 1: the A / B tiles of a K step arrive by two tensor-map (TMA) copies; 0: by 16-byte cp.async of 128 threads
+#endif
 
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 128, STAGES = 4;
-constexpr int EPI_WARPS = 4, LOAD_WARPS = 4, THREADS = (2 * EPI_WARPS + LOAD_WARPS + 1) * 32;   // warps 0-3 and 9-12 share the epilogue
+#ifndef B200Q_MX_STAGES
+#define B200Q_MX_STAGES 4
+#endif
+constexpr int BM = 128, BN = 256, BK = 128, STAGES = B200Q_MX_STAGES;
+constexpr int EPI_WARPS = 4, LOAD_WARPS = 4, EPI_Q = 4;      // epilogue: warps 0-3 and 9-20, EPI_Q warps per 32-lane sub-partition (64 columns each)
+constexpr int THREADS = (EPI_Q * EPI_WARPS + LOAD_WARPS + 1) * 32;
 constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, SF_BYTES = 2048;                    // scale chunks: A 512 B, B 2 x 512 B
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;                               // 50 KB, a multiple of 1024
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;                                 // + room to align the ring to 1024 B
+#ifndef B200Q_MX_STAGED_EPI
+#define B200Q_MX_STAGED_EPI 0     // 1: the bf16 epilogue goes through 4 KB of shared memory per warp so that its global stores are whole 128-byte row segments
+#endif
+constexpr int EPI_STAGE_BYTES = B200Q_MX_STAGED_EPI ? 16 * 4096 : 0;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + EPI_STAGE_BYTES;               // + room to align the ring to 1024 B
 constexpr int TMEM_COLS = 512;            // 256 accumulator columns + scale columns, rounded up to a power of two
 constexpr int SFA_COL = 256, SFB_COL = 256 + 4 * STAGES;   // per stage 4 columns (A: 128 rows) and 8 columns (B: 256 rows)
 constexpr int MAX_EXPERTS = 1024;
@@ -69,11 +83,55 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 }
 __device__ __forceinline__ void arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 
+// 32 consecutive accumulator columns of this thread's row (tensor-memory lane) -> registers; the caller waits (tcgen05.wait::ld)
+__device__ __forceinline__ void tmem_ld32(uint32_t ta, uint32_t (&v)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+                 "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+                 "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+                 "=r"(v[31])
+               : "r"(ta));
+}
+__device__ __forceinline__ void bf16_store32(const uint32_t (&v)[32], __nv_bfloat16* dst) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint4 pk;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+    for (int q = 0; q < 4; q++) h[q] = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * q]), __uint_as_float(v[j + 2 * q + 1]));
+    *reinterpret_cast<uint4*>(dst + j) = pk;
+  }
+}
+// one MX block of the activation: gate / up accumulators of 32 columns -> silu(gate) * up -> E4M3 codes + block exponent at [row, col..col+31]
+__device__ __forceinline__ void swiglu_quant_store(const uint32_t (&vg)[32], const uint32_t (&vu)[32], uint8_t* act_q, uint8_t* act_e8, size_t row, int f,
+                                                   int col) {
+  float v[32];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
+    const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vg[j]))), u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vu[j])));
+    v[j] = __bfloat162float(__float2bfloat16_rn((g / (1.f + expf(-g))) * u));
+    amax = fmaxf(amax, fabsf(v[j]));
+  }
+  const uint8_t e = mx_scale_exponent(amax);
+  uint2 pk[4];
+#pragma unroll
+  for (int q = 0; q < 4; q++) {
+    const float v8[8] = {v[8 * q], v[8 * q + 1], v[8 * q + 2], v[8 * q + 3], v[8 * q + 4], v[8 * q + 5], v[8 * q + 6], v[8 * q + 7]};
+    pk[q] = mx_quant8(v8, e);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(act_q + row * f + col);
+  dst[0] = make_uint4(pk[0].x, pk[0].y, pk[1].x, pk[1].y);
+  dst[1] = make_uint4(pk[2].x, pk[2].y, pk[3].x, pk[3].y);
+  act_e8[row * (f >> 5) + (col >> 5)] = e;
+}
+
 __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint8_t* __restrict__ a_q, const uint8_t* __restrict__ a_e8,
                                                                       const uint8_t* __restrict__ b_q, const uint8_t* __restrict__ b_e8,
                                                                       const int32_t* __restrict__ off, int n_experts, int m_total, int n, int k,
                                                                       __nv_bfloat16* __restrict__ c, uint8_t* __restrict__ act_q,
-                                                                      uint8_t* __restrict__ act_e8) {
+                                                                      uint8_t* __restrict__ act_e8, const __grid_constant__ CUtensorMap tm_a,
+                                                                      const __grid_constant__ CUtensorMap tm_b) {
   extern __shared__ unsigned char sm_raw[];
   __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_acc_full, bar_acc_empty, bar_drain;
   __shared__ uint32_t tmem_base;
@@ -82,11 +140,11 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&bar_full[s])), "r"(LOAD_WARPS * 32));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&bar_full[s])), "r"(LOAD_WARPS * 32 + B200Q_MX_TMA));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bar_empty[s])));
     }
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bar_acc_full)));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&bar_acc_empty)), "r"(2 * EPI_WARPS * 32));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(&bar_acc_empty)), "r"(EPI_Q * EPI_WARPS * 32));
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bar_drain)));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_abort = 0;
@@ -112,6 +170,7 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
     const int r0 = lt >> 3, ch = lt & 7;            // this thread copies chunk ch of rows r0 + 16 j
     const uint32_t t_off = (uint32_t)(r0 * 128 + ((ch ^ (r0 & 7)) << 4));
     const uint32_t sf_off = (uint32_t)((lt & 31) * 16 + (lt >> 5) * 4);      // scale word of row lt (A), rows lt and lt + 128 (B)
+    int b_row0 = 0;       // first row of the tile's B operand inside [n_experts * n, k]
     auto tile_ptrs = [&](int t, const uint8_t*& ap, const uint8_t*& bp, const uint8_t*& ae, const uint8_t*& be) {
       const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
       int lo = 0, hi = n_experts - 1;
@@ -120,6 +179,7 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
       bp = b_q + ((size_t)lo * n + n0 + r0) * k + ch * 16;
       ae = a_e8 + (size_t)(m0 + lt) * kb_total;
       be = b_e8 + ((size_t)lo * n + n0 + lt) * kb_total;
+      b_row0 = lo * n + n0;
     };
     uint32_t g = 0;
     bool ok = true;
@@ -132,10 +192,23 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
         const uint32_t sA = ring + slot * STAGE_BYTES, sB = sA + A_BYTES, sF = sB + B_BYTES;
         const uint8_t* pa = ap + kt * BK;
         const uint8_t* pb = bp + kt * BK;
+#if B200Q_MX_TMA
+        if (lt == 0) {
+          // the 128-byte-swizzle tiled copy writes exactly the layout above (chunk c of row r at c ^ (r & 7)); no multicast
+          const uint32_t fb = s32(&bar_full[slot]);
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fb), "r"(A_BYTES + B_BYTES) : "memory");
+          asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                       ::"r"(sA), "l"(&tm_a), "r"(kt * BK), "r"((t / tiles_n) * BM), "r"(fb) : "memory");
+          asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                       ::"r"(sB), "l"(&tm_b), "r"(kt * BK), "r"(b_row0), "r"(fb) : "memory");
+        }
+        (void)pa; (void)pb; (void)t_off;
+#else
 #pragma unroll
         for (int j = 0; j < BM / 16; j++) cp16(sA + t_off + j * 2048, pa + (size_t)(16 * j) * k);
 #pragma unroll
         for (int j = 0; j < BN / 16; j++) cp16(sB + t_off + j * 2048, pb + (size_t)(16 * j) * k);
+#endif
         cp4(sF + sf_off, ae + kt * 4);
         cp4(sF + 512 + sf_off, be + kt * 4);
         cp4(sF + 1024 + sf_off, be + (size_t)128 * kb_total + kt * 4);
@@ -143,6 +216,18 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
+#if B200Q_MX_TMA
+    // nothing of this thread's tensor-map copies may still be landing when the CTA leaves (they are all consumed unless a wait ran out)
+    if (lt == 0)
+      for (uint32_t j = g > STAGES ? g - STAGES : 0; j < g; j++) {
+        const uint32_t fb = s32(&bar_full[j % STAGES]), par = (j / STAGES) & 1;
+        for (int i = 0; i < SPIN; i++) {
+          uint32_t done;
+          asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(done) : "r"(fb), "r"(par) : "memory");
+          if (done) break;
+        }
+      }
+#endif
   } else if (warp == EPI_WARPS + LOAD_WARPS) {
     // ---------------------------------------------------------------- MMA issue (one thread)
     if (lane == 0) {
@@ -186,82 +271,68 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
     }
   } else {
     // ---------------------------------------------------------------- epilogue: accumulator row r = tensor-memory lane r
+    // Four warps per 32-lane sub-partition (a warp reaches only the lanes of sub-partition warp % 4), 64 columns each.  A warp brings
+    // its columns into registers with two loads in flight and ONE wait, releases the accumulator, and only then does its arithmetic
+    // and stores: the next tile's MMAs wait for one tensor-memory round trip, not for the epilogue.
+    const int sub = warp & 3, cq = warp < EPI_WARPS ? 0 : 1 + (warp - (EPI_WARPS + LOAD_WARPS + 1)) / 4;      // column quarter 0..3
     uint32_t tile_i = 0;
     for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, tile_i++) {
       if (!wait_bar(s32(&bar_acc_full), tile_i & 1, abort_flag)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
-      const int sub = warp & 3, cbase = warp < EPI_WARPS ? 0 : BN / 2;     // sub-partition = warp % 4; two warps split its 256 columns
+      const uint32_t ta = taddr + ((uint32_t)(sub * 32) << 16);
+      const size_t row = (size_t)(m0 + sub * 32 + lane);
+      uint32_t v0[32], v1[32];
       if (act_q) {
         // Fused activation between the expert GEMMs: the B rows of this tile are 128 gate rows followed by the 128 matching up rows
         // (the caller interleaves them so), so accumulator columns c and 128 + c belong together.  A thread holds 32 consecutive
         // outputs of its row = one MX block: bf16-round gate and up (what the unfused path stores), silu(gate) * up in fp32,
         // bf16-round, block exponent from the amax, E4M3 codes -- the arithmetic of swiglu_quant_kernel, with no trip through HBM.
-        const int f = n >> 1, c_lo = warp < EPI_WARPS ? 0 : 64;
-        const size_t row = (size_t)(m0 + sub * 32 + lane);
-#pragma unroll 1
-        for (int c0 = c_lo; c0 < c_lo + 64; c0 += 32) {
-          uint32_t vg[32], vu[32];
-          const uint32_t ta = taddr + ((uint32_t)(sub * 32) << 16);
-          asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                       : "=r"(vg[0]), "=r"(vg[1]), "=r"(vg[2]), "=r"(vg[3]), "=r"(vg[4]), "=r"(vg[5]), "=r"(vg[6]), "=r"(vg[7]), "=r"(vg[8]), "=r"(vg[9]), "=r"(vg[10]), "=r"(vg[11]), "=r"(vg[12]), "=r"(vg[13]), "=r"(vg[14]), "=r"(vg[15]), "=r"(vg[16]), "=r"(vg[17]), "=r"(vg[18]), "=r"(vg[19]), "=r"(vg[20]), "=r"(vg[21]), "=r"(vg[22]), "=r"(vg[23]), "=r"(vg[24]), "=r"(vg[25]), "=r"(vg[26]), "=r"(vg[27]), "=r"(vg[28]), "=r"(vg[29]), "=r"(vg[30]), "=r"(vg[31])
-                       : "r"(ta + c0));
-          asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                       : "=r"(vu[0]), "=r"(vu[1]), "=r"(vu[2]), "=r"(vu[3]), "=r"(vu[4]), "=r"(vu[5]), "=r"(vu[6]), "=r"(vu[7]), "=r"(vu[8]), "=r"(vu[9]), "=r"(vu[10]), "=r"(vu[11]), "=r"(vu[12]), "=r"(vu[13]), "=r"(vu[14]), "=r"(vu[15]), "=r"(vu[16]), "=r"(vu[17]), "=r"(vu[18]), "=r"(vu[19]), "=r"(vu[20]), "=r"(vu[21]), "=r"(vu[22]), "=r"(vu[23]), "=r"(vu[24]), "=r"(vu[25]), "=r"(vu[26]), "=r"(vu[27]), "=r"(vu[28]), "=r"(vu[29]), "=r"(vu[30]), "=r"(vu[31])
-                       : "r"(ta + BN / 2 + c0));
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (c0 + 32 == c_lo + 64) {      // this warp's part of the accumulator is in registers
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            arrive(s32(&bar_acc_empty));
-          }
-          float v[32];
-          float amax = 0.f;
-#pragma unroll
-          for (int j = 0; j < 32; j++) {
-            const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vg[j]))), u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vu[j])));
-            v[j] = __bfloat162float(__float2bfloat16_rn((g / (1.f + expf(-g))) * u));
-            amax = fmaxf(amax, fabsf(v[j]));
-          }
-          const uint8_t e = mx_scale_exponent(amax);
-          uint2 pk[4];
-#pragma unroll
-          for (int q = 0; q < 4; q++) {
-            const float v8[8] = {v[8 * q], v[8 * q + 1], v[8 * q + 2], v[8 * q + 3], v[8 * q + 4], v[8 * q + 5], v[8 * q + 6], v[8 * q + 7]};
-            pk[q] = mx_quant8(v8, e);
-          }
-          const int col = (n0 >> 1) + c0;                              // column of the activation matrix [m, f]
-          uint4* dst = reinterpret_cast<uint4*>(act_q + row * f + col);
-          dst[0] = make_uint4(pk[0].x, pk[0].y, pk[1].x, pk[1].y);
-          dst[1] = make_uint4(pk[2].x, pk[2].y, pk[3].x, pk[3].y);
-          act_e8[row * (f >> 5) + (col >> 5)] = e;
-        }
+        tmem_ld32(ta + cq * 32, v0); tmem_ld32(ta + BN / 2 + cq * 32, v1);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        arrive(s32(&bar_acc_empty));
+        swiglu_quant_store(v0, v1, act_q, act_e8, row, n >> 1, (n0 >> 1) + cq * 32);
         continue;
       }
-      __nv_bfloat16* out_row = c + (size_t)(m0 + sub * 32 + lane) * n + n0;
-#pragma unroll 1
-      for (int j0 = cbase; j0 < cbase + BN / 2; j0 += 32) {
-        uint32_t v[32];
-        const uint32_t ta = taddr + ((uint32_t)(sub * 32) << 16) + j0;
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
-                       "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-                       "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
-                       "=r"(v[31])
-                     : "r"(ta));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (j0 + 32 == cbase + BN / 2) {      // the accumulator is in registers: the next tile may overwrite it
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          arrive(s32(&bar_acc_empty));
-        }
+      tmem_ld32(ta + cq * 64, v0); tmem_ld32(ta + cq * 64 + 32, v1);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      arrive(s32(&bar_acc_empty));
+      __nv_bfloat16* out_row = c + row * n + n0 + cq * 64;
+#if B200Q_MX_STAGED_EPI
+      {
+        // row `lane`, 64 columns = eight 16-byte packets -> this warp's staging rows (packet p of row r at p ^ (r & 7): conflict-free
+        // both ways) -> read back four rows x 128 contiguous bytes per instruction and store those
+        unsigned char* stg = sm_raw + (ring - s32(sm_raw)) + STAGES * STAGE_BYTES + (warp < EPI_WARPS ? warp : warp - (LOAD_WARPS + 1)) * 4096;
 #pragma unroll
-        for (int j = 0; j < 32; j += 8) {
+        for (int p8 = 0; p8 < 8; p8++) {
           uint4 pk;
           __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-          for (int q = 0; q < 4; q++) h[q] = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * q]), __uint_as_float(v[j + 2 * q + 1]));
-          *reinterpret_cast<uint4*>(out_row + j0 + j) = pk;
+          for (int q = 0; q < 4; q++) {
+            const int j = p8 * 8 + 2 * q;
+            h[q] = j < 32 ? __floats2bfloat162_rn(__uint_as_float(v0[j]), __uint_as_float(v0[j + 1]))
+                          : __floats2bfloat162_rn(__uint_as_float(v1[j - 32]), __uint_as_float(v1[j - 31]));
+          }
+          *reinterpret_cast<uint4*>(stg + lane * 128 + ((p8 ^ (lane & 7)) << 4)) = pk;
         }
+        __syncwarp();
+        __nv_bfloat16* out_tile = c + (size_t)(m0 + sub * 32) * n + n0 + cq * 64;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const int r = 4 * i + (lane >> 3), p8 = lane & 7;
+          const uint4 pk = *reinterpret_cast<const uint4*>(stg + r * 128 + ((p8 ^ (r & 7)) << 4));
+          *reinterpret_cast<uint4*>(out_tile + (size_t)r * n + p8 * 8) = pk;
+        }
+        __syncwarp();
+        (void)out_row;
       }
+#elif !defined(B200Q_MX_EXP_NOSTORE)
+      bf16_store32(v0, out_row); bf16_store32(v1, out_row + 32);
+#else
+      if (v0[0] == 0x12345678u && v1[5] == 0x9abcdef0u) bf16_store32(v0, out_row);
+#endif
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -287,6 +358,26 @@ extern "C" int b200q_mx_status_read_clear(int* status) {
   return B200Q_OK;
 }
 
+// [rows, k] bytes, row-major -> tiled tensor map with boxes of `box_rows` rows x 128 bytes in the 128-byte-swizzle shared-memory layout.
+// The encoder is a driver entry point; it is looked up through the runtime so that the library links against cudart only.
+static int make_map(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t k, uint32_t box_rows) {
+  typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static encode_fn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    B200Q_CHECK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    if (!p || q != cudaDriverEntryPointSuccess) return B200Q_ERR_UNSUPPORTED;
+    fn = (encode_fn)p;
+  }
+  const cuuint64_t dims[2] = {k, rows}, strides[1] = {k};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows}, estr[2] = {1, 1};
+  const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200Q_OK : B200Q_ERR_BAD_ARG;
+}
+
 static int grouped_launch(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts, int m_total, int n, int k,
                           void* c_bf16, void* act_q, void* act_e8, void* stream) {
   if (!a_q || !a_e8 || !b_q || !b_e8 || !off || (!c_bf16 && !act_q) || n_experts <= 0 || m_total <= 0 || n <= 0 || k <= 0) return B200Q_ERR_BAD_ARG;
@@ -303,8 +394,15 @@ static int grouped_launch(const void* a_q, const void* a_e8, const void* b_q, co
   }
   const long long tiles = (long long)(m_total / BM) * (n / BN);
   const int grid = (int)(tiles < n_sm ? tiles : n_sm);
+  alignas(64) CUtensorMap tm_a, tm_b;
+  memset(&tm_a, 0, sizeof(tm_a)); memset(&tm_b, 0, sizeof(tm_b));
+#if B200Q_MX_TMA
+  int rc = make_map(&tm_a, a_q, (uint64_t)m_total, (uint64_t)k, BM);
+  if (rc == B200Q_OK) rc = make_map(&tm_b, b_q, (uint64_t)n_experts * n, (uint64_t)k, BN);
+  if (rc != B200Q_OK) return rc;
+#endif
   grouped_mxfp8_tc_kernel<<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>((const uint8_t*)a_q, (const uint8_t*)a_e8, (const uint8_t*)b_q, (const uint8_t*)b_e8, off,
-                                                            n_experts, m_total, n, k, (__nv_bfloat16*)c_bf16, (uint8_t*)act_q, (uint8_t*)act_e8);
+                                                            n_experts, m_total, n, k, (__nv_bfloat16*)c_bf16, (uint8_t*)act_q, (uint8_t*)act_e8, tm_a, tm_b);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

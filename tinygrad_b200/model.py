@@ -84,7 +84,7 @@ class Transformer:
     assert c.max_context > 0 and c.n_heads % c.n_kv_heads == 0
     self.qtype, self.flags, self.use_graph = ggml_type, (FLAG_PDL if use_pdl else 0), use_graph
     self.q_dim, self.kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
-    self.gemv_max_ctas = gemv_max_ctas
+    self.gemv_max_ctas = gemv_max_ctas if isinstance(gemv_max_ctas, dict) else {"*": gemv_max_ctas}   # per Linear ("qkv", "o", "gate_up", "down", "head") or one for all
     self.n_split = n_split or _lib.load().b200q_attn_min_split(c.max_context)
     self.max_context = c.max_context
     self.stream = Stream(tp.stream_ptr()) if (tp is not None and tp.stream_ptr() is not None) else Stream()
@@ -252,7 +252,8 @@ class Transformer:
   def _enqueue_step(self, with_head: bool, attention: bool = True, tail: bool = True) -> None:
     c, lib, s, fl = self.config, _lib.load(), self.stream.ptr, self.flags
     kvdt = F16 if c.kv_dtype == "float16" else F32
-    kw = dict(flags=fl, max_ctas=self.gemv_max_ctas, stream=s)
+    grid = lambda name: self.gemv_max_ctas.get(name, self.gemv_max_ctas.get("*", 0))
+    kw = dict(flags=fl, stream=s)
     tp = self.tp
     # A launch that follows an NCCL call is fully stream-ordered: the programmatic-launch attribute right behind the
     # event waits NCCL leaves in the stream was measured to let the kernel start before the reduced vector is there.
@@ -291,20 +292,20 @@ class Transformer:
       out_act = dict(xq_out=self.xq_act) if "gateup_down" in e else {}
       out_a = dict(xq_out=self.xq_a, xq_out_norm_weight=nxt_norm, ss_out=self.ss_a) if "down_qkv" in e else {}
       quant.gemv(b.qkv.ptr, self.qtype, qkv_rows, c.dim, None if in_a else self.x, self.qkv, norm_weight=b.attn_norm, norm_eps=c.norm_eps,
-                 bias=b.qkv_bias, **in_a, **(kw_after_coll if i > 0 else kw))
+                 bias=b.qkv_bias, max_ctas=grid("qkv"), **in_a, **(kw_after_coll if i > 0 else kw))
       if attention:
         a = _lib.AttnArgs(self.qkv.ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, self.pos.ptr, self.attn.ptr, self.attn_scratch.ptr,
                           c.n_heads, c.n_kv_heads, c.head_dim, c.rope_dim, c.max_context, self.n_split, fl,
                           self.xq_attn.ptr if "attn_o" in e else None)
         check(lib.b200q_attn_decode(ctypes.byref(a), s))
       quant.gemv(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, None if in_attn else self.attn, None if peer else self.x, **rkw_o,
-                 **in_attn, **out_b, **kw)
+                 **in_attn, **out_b, max_ctas=grid("o"), **kw)
       if peer: self.mb_o.reduce(self.x, residual=self.x, flags=fl, stream=s)
       elif tp is not None: tp.all_reduce(self.x)
       quant.gemv(b.gate_up.buf.ptr, self.qtype, c.hidden_dim, c.dim, None if in_b else self.x, None if out_act else self.act,
-                 norm_weight=b.ffn_norm, norm_eps=c.norm_eps, epilogue=EPI_SILU_MUL, **in_b, **out_act, **kw_after_coll)
+                 norm_weight=b.ffn_norm, norm_eps=c.norm_eps, epilogue=EPI_SILU_MUL, max_ctas=grid("gate_up"), **in_b, **out_act, **kw_after_coll)
       quant.gemv(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, None if in_act else self.act, None if peer else self.x, **rkw_d,
-                 **in_act, **out_a, **kw)
+                 **in_act, **out_a, max_ctas=grid("down"), **kw)
       if peer: self.mb_down.reduce(self.x, residual=self.x, flags=fl, stream=s)
       elif tp is not None: tp.all_reduce(self.x)
     if with_head:
@@ -314,7 +315,7 @@ class Transformer:
       else:
         in_h = {} if self.output_type == _lib.Q6_K else in_a       # the Q6_K kernel quantises the row itself
         quant.gemv(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, None if in_h else self.x, self.logits_part,
-                   norm_weight=self.output_norm, norm_eps=c.norm_eps, **in_h, **kw_after_coll,
+                   norm_weight=self.output_norm, norm_eps=c.norm_eps, max_ctas=grid("head"), **in_h, **kw_after_coll,
                    **(dict(peers=self.mb_logits.targets, peer_rank=tp.rank) if peer else {}))
       if peer: self.mb_logits.reduce(self.logits, flags=fl, stream=s)          # every rank's vocabulary slice, handed over
       elif tp is not None: tp.all_gather(self.logits, self.logits_part)

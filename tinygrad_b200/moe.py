@@ -98,7 +98,10 @@ class MxMoE:
     if self._ws is None:
       r = Routing(n_tokens, self.E, self.k, self.mode)
       m = r.m_l
-      self._ws = self._wss[n_tokens] = dict(T=n_tokens, r=r, a_q=DeviceBuffer.empty((m, self.D), np.uint8), a_e8=DeviceBuffer.empty((m, self.D // 32), np.uint8),
+      # a_q / a_e8 are zeroed once, here: the rows between the groups (padding to 256) feed only output rows that nobody reads, and what a
+      # later call leaves there is an earlier call's quantised row (finite codes, valid exponents), never an uninitialised pattern
+      self._ws = self._wss[n_tokens] = dict(T=n_tokens, r=r, a_q=DeviceBuffer.empty((m, self.D), np.uint8, zero=True),
+                      a_e8=DeviceBuffer.empty((m, self.D // 32), np.uint8, zero=True),
                       h=DeviceBuffer.empty((m, 2 * self.F), np.uint16, zero=True), act_q=DeviceBuffer.empty((m, self.F), np.uint8),
                       act_e8=DeviceBuffer.empty((m, self.F // 32), np.uint8), y=DeviceBuffer.empty((m, self.D), np.uint16, zero=True),
                       out=DeviceBuffer.empty((n_tokens, self.D), np.uint16))
@@ -108,7 +111,6 @@ class MxMoE:
     """x (T, D) bf16, router logits (T, E) fp32 -> (T, D) bf16."""
     lib, s, w = _lib.load(), stream_ptr(stream), self._workspace(n_tokens)
     r = w["r"].run(logits, stream)
-    w["a_q"].zero_(stream); w["a_e8"].zero_(stream)                        # rows nobody is routed to stay zero (dispatch zero-fills)
     check(lib.b200q_quantize_mxfp8(x_bf16.ptr, BF16, n_tokens, self.D, r.dest_row.ptr, self.k, w["a_q"].ptr, w["a_e8"].ptr, s))
     if self.fused:
       check(lib.b200q_grouped_mxfp8_gemm_swiglu(w["a_q"].ptr, w["a_e8"].ptr, self.gu_q.ptr, self.gu_e8.ptr, r.off.ptr, self.E, r.m_l, 2 * self.F, self.D,
@@ -128,7 +130,6 @@ class MxMoE:
     lib, s, w, T = _lib.load(), stream_ptr(stream), self._workspace(n_tokens), n_tokens
     r = w["r"]
     ph = {"route": lambda: r.run(logits, stream),
-          "zero_fill": lambda: (w["a_q"].zero_(stream), w["a_e8"].zero_(stream)),
           "dispatch_quantize": lambda: lib.b200q_quantize_mxfp8(x_bf16.ptr, BF16, T, self.D, r.dest_row.ptr, self.k, w["a_q"].ptr, w["a_e8"].ptr, s)}
     if self.fused:
       ph["gate_up_gemm_swiglu"] = lambda: lib.b200q_grouped_mxfp8_gemm_swiglu(w["a_q"].ptr, w["a_e8"].ptr, self.gu_q.ptr, self.gu_e8.ptr, r.off.ptr, self.E,
@@ -141,3 +142,37 @@ class MxMoE:
                                                           self.F, w["y"].ptr, s)
     ph["combine"] = lambda: lib.b200q_moe_combine(w["y"].ptr, r.dest_row.ptr, r.weights.ptr, T, self.k, self.D, w["out"].ptr, s)
     return ph
+
+
+class ExpertWeights:
+  """`ExpertWeights` of tinygrad/llm/model.py:21-27 on MXFP8 operands: weight (num_experts, out_features, in_features), and
+  `__call__(sel, x)` with sel (T, k) int32 and x (T, 1, in) or (T, k, in) bf16 -> (T, k, out) bf16, row (t, j) = x[t, j or 0] @ weight[sel[t, j]].T.
+  The rows are grouped by expert (b200q_moe_route_tables), quantised into the groups, multiplied by one grouped GEMM and gathered back
+  into (t, j) order.  out_features must be a multiple of 256 and in_features of 128 (the grouped GEMM's tile sizes)."""
+  def __init__(self, weight: np.ndarray):
+    self.num_experts, self.out_features, self.in_features = weight.shape
+    if self.out_features % 256 or self.in_features % 128: raise ValueError("out_features % 256 == in_features % 128 == 0 is required")
+    self.w_q, self.w_e8 = quantize_mxfp8(DeviceBuffer.from_numpy(np.ascontiguousarray(weight, dtype=np.float32)), self.num_experts * self.out_features,
+                                         self.in_features, F32)
+    self._ws = {}
+
+  def __call__(self, sel: DeviceBuffer, x: DeviceBuffer, stream=None) -> DeviceBuffer:
+    T, k = sel.shape
+    fan_in = x.shape[-2] if len(x.shape) == 3 else 1
+    if x.shape[0] != T or x.shape[-1] != self.in_features or fan_in not in (1, k): raise ValueError(f"x {x.shape} does not match sel {sel.shape}")
+    lib, s, E = _lib.load(), stream_ptr(stream), self.num_experts
+    w = self._ws.get((T, k))
+    if w is None:
+      m = lib.b200q_moe_rows_max(T, E, k)
+      w = self._ws[(T, k)] = dict(m=m, dest=DeviceBuffer.empty((T * k,), np.int32), off=DeviceBuffer.empty((E + 1,), np.int32),
+                                  scratch=DeviceBuffer(lib.b200q_moe_route_scratch_bytes(T, E, k)),
+                                  a_q=DeviceBuffer.empty((m, self.in_features), np.uint8, zero=True), a_e8=DeviceBuffer.empty((m, self.in_features // 32), np.uint8, zero=True),
+                                  y=DeviceBuffer.empty((m, self.out_features), np.uint16, zero=True), out=DeviceBuffer.empty((T, k, self.out_features), np.uint16))
+    check(lib.b200q_moe_route_tables(sel.ptr, T, E, k, 256, w["dest"].ptr, w["off"].ptr, None, w["scratch"].ptr, s))
+    # x (T, 1, in): one row fans out to its k destinations; x (T, k, in): row (t, j) goes to its own destination
+    rows, fan = (T, k) if fan_in == 1 else (T * k, 1)
+    check(lib.b200q_quantize_mxfp8(x.ptr, BF16, rows, self.in_features, w["dest"].ptr, fan, w["a_q"].ptr, w["a_e8"].ptr, s))
+    check(lib.b200q_grouped_mxfp8_gemm(w["a_q"].ptr, w["a_e8"].ptr, self.w_q.ptr, self.w_e8.ptr, w["off"].ptr, E, w["m"], self.out_features, self.in_features,
+                                       w["y"].ptr, s))
+    check(lib.b200q_permute_rows(w["y"].ptr, w["dest"].ptr, T * k, 2 * self.out_features, w["out"].ptr, 1, s))
+    return w["out"]
