@@ -30,7 +30,7 @@
 namespace {
 
 #ifndef B200Q_MX_STAGES
-#define B200Q_MX_STAGES 4
+#define B200Q_MX_STAGES 3
 #endif
 constexpr int BM = 128, BN = 256, BK = 128, STAGES = B200Q_MX_STAGES;
 constexpr int EPI_WARPS = 4, LOAD_WARPS = 4, EPI_Q = 4;      // epilogue: warps 0-3 and 9-20, EPI_Q warps per 32-lane sub-partition (64 columns each)
@@ -38,8 +38,8 @@ constexpr int THREADS = (EPI_Q * EPI_WARPS + LOAD_WARPS + 1) * 32;
 constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, SF_BYTES = 2048;                    // scale chunks: A 512 B, B 2 x 512 B
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SF_BYTES;                               // 50 KB, a multiple of 1024
 #ifndef B200Q_MX_STAGED_EPI
-#define B200Q_MX_STAGED_EPI 0     // 1: the bf16 epilogue goes through 4 KB of shared memory per warp so that its global stores are whole 128-byte row segments
-#endif
+#define B200Q_MX_STAGED_EPI 2     // bf16 epilogue: 0 = each thread stores its own row (16-byte pieces of 32 different rows per instruction); 1 = through
+#endif                            // 4 KB of shared memory per warp, stores of whole 128-byte row segments; 2 = the same, stored by one tensor-map copy
 constexpr int EPI_STAGE_BYTES = B200Q_MX_STAGED_EPI ? 16 * 4096 : 0;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + EPI_STAGE_BYTES;               // + room to align the ring to 1024 B
 constexpr int TMEM_COLS = 512;            // 256 accumulator columns + scale columns, rounded up to a power of two
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
                                                                       const int32_t* __restrict__ off, int n_experts, int m_total, int n, int k,
                                                                       __nv_bfloat16* __restrict__ c, uint8_t* __restrict__ act_q,
                                                                       uint8_t* __restrict__ act_e8, const __grid_constant__ CUtensorMap tm_a,
-                                                                      const __grid_constant__ CUtensorMap tm_b) {
+                                                                      const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_c) {
   extern __shared__ unsigned char sm_raw[];
   __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_acc_full, bar_acc_empty, bar_drain;
   __shared__ uint32_t tmem_base;
@@ -317,6 +317,18 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
           }
           *reinterpret_cast<uint4*>(stg + lane * 128 + ((p8 ^ (lane & 7)) << 4)) = pk;
         }
+#if B200Q_MX_STAGED_EPI == 2
+        // the staging rows are in the 128-byte-swizzle layout a tiled tensor-map store reads: one copy per warp and tile
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                       ::"l"(&tm_c), "r"(n0 + cq * 64), "r"(m0 + sub * 32), "r"(s32(stg)) : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the rows may be overwritten for the next tile
+        }
+        __syncwarp();
+#else
         __syncwarp();
         __nv_bfloat16* out_tile = c + (size_t)(m0 + sub * 32) * n + n0 + cq * 64;
 #pragma unroll
@@ -326,6 +338,7 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
           *reinterpret_cast<uint4*>(out_tile + (size_t)r * n + p8 * 8) = pk;
         }
         __syncwarp();
+#endif
         (void)out_row;
       }
 #elif !defined(B200Q_MX_EXP_NOSTORE)
@@ -334,6 +347,9 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
       if (v0[0] == 0x12345678u && v1[5] == 0x9abcdef0u) bf16_store32(v0, out_row);
 #endif
     }
+#if B200Q_MX_STAGED_EPI == 2
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // this warp's stores have left before the CTA does
+#endif
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -360,7 +376,7 @@ extern "C" int b200q_mx_status_read_clear(int* status) {
 
 // [rows, k] bytes, row-major -> tiled tensor map with boxes of `box_rows` rows x 128 bytes in the 128-byte-swizzle shared-memory layout.
 // The encoder is a driver entry point; it is looked up through the runtime so that the library links against cudart only.
-static int make_map(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t k, uint32_t box_rows) {
+static int make_map(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t k, uint32_t box_rows, bool bf16 = false) {
   typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
   static encode_fn fn = nullptr;
@@ -371,10 +387,11 @@ static int make_map(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t k
     if (!p || q != cudaDriverEntryPointSuccess) return B200Q_ERR_UNSUPPORTED;
     fn = (encode_fn)p;
   }
-  const cuuint64_t dims[2] = {k, rows}, strides[1] = {k};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows}, estr[2] = {1, 1};
-  const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  // bf16: `k` counts elements, a box row is 64 of them (128 bytes); else bytes, a box row is BK = 128 of them
+  const cuuint64_t dims[2] = {k, rows}, strides[1] = {bf16 ? 2 * k : k};
+  const cuuint32_t box[2] = {(cuuint32_t)(bf16 ? 64 : BK), box_rows}, estr[2] = {1, 1};
+  const CUresult r = fn(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? B200Q_OK : B200Q_ERR_BAD_ARG;
 }
 
@@ -394,15 +411,18 @@ static int grouped_launch(const void* a_q, const void* a_e8, const void* b_q, co
   }
   const long long tiles = (long long)(m_total / BM) * (n / BN);
   const int grid = (int)(tiles < n_sm ? tiles : n_sm);
-  alignas(64) CUtensorMap tm_a, tm_b;
-  memset(&tm_a, 0, sizeof(tm_a)); memset(&tm_b, 0, sizeof(tm_b));
+  alignas(64) CUtensorMap tm_a, tm_b, tm_c;
+  memset(&tm_a, 0, sizeof(tm_a)); memset(&tm_b, 0, sizeof(tm_b)); memset(&tm_c, 0, sizeof(tm_c));
+#if B200Q_MX_STAGED_EPI == 2
+  if (c_bf16) { const int rcc = make_map(&tm_c, c_bf16, (uint64_t)m_total, (uint64_t)n, 32, true); if (rcc != B200Q_OK) return rcc; }
+#endif
 #if B200Q_MX_TMA
   int rc = make_map(&tm_a, a_q, (uint64_t)m_total, (uint64_t)k, BM);
   if (rc == B200Q_OK) rc = make_map(&tm_b, b_q, (uint64_t)n_experts * n, (uint64_t)k, BN);
   if (rc != B200Q_OK) return rc;
 #endif
   grouped_mxfp8_tc_kernel<<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>((const uint8_t*)a_q, (const uint8_t*)a_e8, (const uint8_t*)b_q, (const uint8_t*)b_e8, off,
-                                                            n_experts, m_total, n, k, (__nv_bfloat16*)c_bf16, (uint8_t*)act_q, (uint8_t*)act_e8, tm_a, tm_b);
+                                                            n_experts, m_total, n, k, (__nv_bfloat16*)c_bf16, (uint8_t*)act_q, (uint8_t*)act_e8, tm_a, tm_b, tm_c);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
