@@ -271,6 +271,7 @@ def main():
   ap.add_argument("--engine", default=None, choices=["step", "chain"], help="one-token engine (default: the whole-step kernel where it takes the model)")
   ap.add_argument("--only", default="", help="comma list of records to run besides the headline (moe, ep_moe, tp70b); default: all that apply")
   ap.add_argument("--skip-cpu-baseline", action="store_true")
+  ap.add_argument("--workload", default="decode", choices=["decode", "moe"], help="moe: only the MoE layer record (short runs for profiling)")
   args = ap.parse_args()
   rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
   if args.impl == "reference": return run_reference(args, rank)
@@ -280,6 +281,10 @@ def main():
   from tinygrad_b200 import build, runtime, synth, _lib
   from tinygrad_b200.model import Transformer
   build.build_lib()
+  if args.workload == "moe":
+    runtime.set_device(local)
+    print(json.dumps({"moe": moe_record(reps=max(args.steps, 1))}), flush=True)
+    return
   from tinygrad_b200.replicas import Ranks
   ranks = Ranks(backend="nccl")
   runtime.set_device(local)

@@ -118,6 +118,7 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
   KV* s_v = s_k + ATTN_CHUNK * rstride;                   // [ATTN_CHUNK][rstride]
   float* s_q = reinterpret_cast<float*>(s_v + ATTN_CHUNK * rstride);   // [n_rep][hd] roped queries
   float* s_sc = s_q + n_rep * hd;                         // [n_rep][ATTN_CHUNK] scores, then probabilities
+  float* s_part = s_sc + n_rep * ATTN_CHUNK;              // [n_rep][hd + 4] what a head's second warp hands to its first (rows stay 16-byte aligned)
   __shared__ int s_last;
   const int kvh = blockIdx.x, split = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -205,13 +206,19 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
   const float scale = 1.0f / sqrtf((float)hd);
   float* partial = reinterpret_cast<float*>(a.scratch);
   const int pstride = hd + 4;   // keeps every record 16-byte aligned
-  if (warp < n_rep) {
-    float* sc = s_sc + warp * ATTN_CHUNK;
-    const float* q = s_q + warp * hd;
+  // A head's positions are shared by `ws` warps (blockDim = ws * n_rep warps; ws = 2 when the block has room): warp w works on head
+  // w % n_rep and on the positions 32 * (w / n_rep) + 32 * ws * j + lane.  Each has its own running max / denominator / output; the
+  // head's first warp merges them (the same merge as across slices) and carries on alone.
+  const int ws = (int)(blockDim.x >> 5) / n_rep, head = warp % n_rep, part = warp / n_rep;
+  float mx = -INFINITY, den = 0.f;
+  float4 o = make_float4(0, 0, 0, 0);
+  {
+    float* sc = s_sc + head * ATTN_CHUNK;
+    const float* q = s_q + head * hd;
     float lmax = -INFINITY;
-    for (int i = lane; i < n; i += 32) {
+    for (int i = 32 * part + lane; i < n; i += 32 * ws) {
       const KV* kr = s_k + i * rstride;
-      // four running sums: a lane's dot product is a dependent chain otherwise, and this warp has its scheduler to itself
+      // four running sums: a lane's dot product is a dependent chain otherwise
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       int d = 0;
       for (; d + 4 * VEC <= hd; d += 4 * VEC) {
@@ -224,37 +231,59 @@ __global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_a
       sc[i] = s;
       lmax = fmaxf(lmax, s);
     }
-    const float mx = warp_max(lmax);
+    mx = warp_max(lmax);
     float lsum = 0.f;
-    for (int i = lane; i < n; i += 32) { const float pr = __expf(sc[i] - mx); sc[i] = pr; lsum += pr; }
-    const float den = warp_sum(lsum);
+    for (int i = 32 * part + lane; i < n; i += 32 * ws) { const float pr = __expf(sc[i] - mx); sc[i] = pr; lsum += pr; }
+    den = warp_sum(lsum);
     __syncwarp();
-    float4 o = make_float4(0, 0, 0, 0);
     if (dl) {
       const KV* vr = s_v + d0;
-      float4 o2 = make_float4(0, 0, 0, 0);      // even / odd positions in two independent sums
-      int i = 0;
+      float4 o2 = make_float4(0, 0, 0, 0);      // two independent sums
+      for (int b0 = 32 * part; b0 < n; b0 += 32 * ws) {      // this warp's runs of 32 positions
+        const int e = min(n, b0 + 32);
+        int i = b0;
 #pragma unroll 4
-      for (; i + 2 <= n; i += 2) {
-        const float pr = sc[i], pr2 = sc[i + 1];
-        const float4 v = KvIO<KV>::load4(vr + i * rstride), v2 = KvIO<KV>::load4(vr + (i + 1) * rstride);
-        o.x = fmaf(pr, v.x, o.x); o.y = fmaf(pr, v.y, o.y); o.z = fmaf(pr, v.z, o.z); o.w = fmaf(pr, v.w, o.w);
-        o2.x = fmaf(pr2, v2.x, o2.x); o2.y = fmaf(pr2, v2.y, o2.y); o2.z = fmaf(pr2, v2.z, o2.z); o2.w = fmaf(pr2, v2.w, o2.w);
-      }
-      if (i < n) {
-        const float pr = sc[i];
-        const float4 v = KvIO<KV>::load4(vr + i * rstride);
-        o.x = fmaf(pr, v.x, o.x); o.y = fmaf(pr, v.y, o.y); o.z = fmaf(pr, v.z, o.z); o.w = fmaf(pr, v.w, o.w);
+        for (; i + 2 <= e; i += 2) {
+          const float pr = sc[i], pr2 = sc[i + 1];
+          const float4 v = KvIO<KV>::load4(vr + i * rstride), v2 = KvIO<KV>::load4(vr + (i + 1) * rstride);
+          o.x = fmaf(pr, v.x, o.x); o.y = fmaf(pr, v.y, o.y); o.z = fmaf(pr, v.z, o.z); o.w = fmaf(pr, v.w, o.w);
+          o2.x = fmaf(pr2, v2.x, o2.x); o2.y = fmaf(pr2, v2.y, o2.y); o2.z = fmaf(pr2, v2.z, o2.z); o2.w = fmaf(pr2, v2.w, o2.w);
+        }
+        if (i < e) {
+          const float pr = sc[i];
+          const float4 v = KvIO<KV>::load4(vr + i * rstride);
+          o.x = fmaf(pr, v.x, o.x); o.y = fmaf(pr, v.y, o.y); o.z = fmaf(pr, v.z, o.z); o.w = fmaf(pr, v.w, o.w);
+        }
       }
       o.x += o2.x; o.y += o2.y; o.z += o2.z; o.w += o2.w;
     }
+  }
+  if (ws > 1) {
+    float* hp = s_part + head * (hd + 4);
+    if (part == 1) {
+      if (dl) *reinterpret_cast<float4*>(hp + d0) = o;
+      if (lane == 0) { hp[hd] = mx; hp[hd + 1] = den; }
+    }
+    __syncthreads();
+    if (part == 0) {
+      const float m1 = hp[hd], l1 = hp[hd + 1];
+      const float gm = fmaxf(mx, m1);                       // the first warp always holds position 0 of the slice: mx is finite
+      const float c0 = __expf(mx - gm), c1 = l1 > 0.f ? __expf(m1 - gm) : 0.f;
+      float4 o1 = make_float4(0, 0, 0, 0);
+      if (dl) o1 = *reinterpret_cast<const float4*>(hp + d0);
+      o.x = o.x * c0 + o1.x * c1; o.y = o.y * c0 + o1.y * c1; o.z = o.z * c0 + o1.z * c1; o.w = o.w * c0 + o1.w * c1;
+      den = den * c0 + l1 * c1;
+      mx = gm;
+    }
+  }
+  if (part == 0) {
     if (n_active == 1) {   // short context: this CTA holds the whole softmax
       const float inv = 1.f / den;
       const float4 r = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
-      if (dl) *reinterpret_cast<float4*>(a.out + (size_t)(kvh * n_rep + warp) * hd + d0) = r;
-      if (a.xq_out) quant_block_8x4(r, lane & 7, (kvh * n_rep + warp) * 4 + (lane >> 3), XqDst(a.xq_out, a.n_heads));   // head_dim 128: one group per head
+      if (dl) *reinterpret_cast<float4*>(a.out + (size_t)(kvh * n_rep + head) * hd + d0) = r;
+      if (a.xq_out) quant_block_8x4(r, lane & 7, (kvh * n_rep + head) * 4 + (lane >> 3), XqDst(a.xq_out, a.n_heads));   // head_dim 128: one group per head
     } else {
-      float* pp = partial + ((size_t)(kvh * n_rep + warp) * a.n_split + split) * pstride;
+      float* pp = partial + ((size_t)(kvh * n_rep + head) * a.n_split + split) * pstride;
       if (dl) *reinterpret_cast<float4*>(pp + d0) = o;
       if (lane == 0) { pp[hd] = mx; pp[hd + 1] = den; }
     }
@@ -440,10 +469,11 @@ extern "C" int b200q_attn_decode(const b200q_attn_args* a, void* stream) {
   if (!a->scratch) return B200Q_ERR_BAD_ARG;
   if ((uintptr_t)a->scratch & 15) return B200Q_ERR_MISALIGNED;
   int n_rep = a->n_heads / a->n_kv_heads;
-  dim3 grid(a->n_kv_heads, a->n_split), block(n_rep * 32);
+  const int ws = 2 * n_rep <= MAX_REP ? 2 : 1;              // warps per head
+  dim3 grid(a->n_kv_heads, a->n_split), block(ws * n_rep * 32);
   bool pdl = (a->flags & B200Q_FLAG_PDL) != 0;
   const int esz = a->kv_dtype == B200Q_F16 ? 2 : 4, vec = 16 / esz;
-  size_t smem = (size_t)2 * ATTN_CHUNK * (a->head_dim + vec) * esz + (size_t)n_rep * (a->head_dim + ATTN_CHUNK) * sizeof(float);
+  size_t smem = (size_t)2 * ATTN_CHUNK * (a->head_dim + vec) * esz + (size_t)n_rep * (a->head_dim + ATTN_CHUNK + a->head_dim + 4) * sizeof(float);
   static PerDeviceFlag attr_set;
   const int dev = b200q_current_device();
   if (dev < 0) return B200Q_ERR_CUDA;
