@@ -433,6 +433,20 @@ int b200q_grouped_mxfp8_gemm_swiglu(const void* a_q, const void* a_e8, const voi
                                     int m_total, int n, int k, void* act_q, void* act_e8, void* stream);
 int b200q_grouped_mxfp8_gemm(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts,
                              int m_total, int n, int k, void* c_bf16, void* stream);
+/* The same product with the unrounded fp32 sums as the result (what the per-tensor FP8 linear below scales afterwards). */
+int b200q_grouped_mxfp8_gemm_f32(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts,
+                                 int m_total, int n, int k, float* c_f32, void* stream);
+
+/* ---- per-tensor FP8 linear: `FP8Linear` / `quantize_to_fp8` (extra/fp8/fp8_linear.py:4-16,43-63) ------------------------
+ * quantize_to_fp8(x): scale = 448 / (max|x| + 1e-8) over the whole tensor, q = e4m3(clamp(x * scale, +-448)), factor = 1 / scale.
+ *   b200q_fp8_absmax: amax (one device float, overwritten) = max|x|;  b200q_fp8_quantize: q [n] E4M3 codes and the factor (one device float).
+ * FP8Linear.__call__: y = (x_q . w_q^T with fp32 accumulation) * w_factor * x_factor (+ bias), cast to the activation dtype.  The
+ *   contraction is b200q_grouped_mxfp8_gemm_f32 with one group and all E8M0 scale bytes 127 (= 1.0); b200q_fp8_scale_bias is the rest.
+ * x / y dtypes: B200Q_F32 | B200Q_F16 | B200Q_BF16; bias fp32 [n] or NULL. */
+int b200q_fp8_absmax(const void* x, int x_dtype, int64_t n, float* amax, void* stream);
+int b200q_fp8_quantize(const void* x, int x_dtype, int64_t n, const float* amax, void* q, float* factor, void* stream);
+int b200q_fp8_scale_bias(const float* acc, int64_t rows, int n, const float* factor_w, const float* factor_x, const float* bias, void* y, int y_dtype,
+                         void* stream);
 
 /* ---- expert-parallel exchange over peer memory (NVLink), planned on the device ------------------------------------------
  * `dispatch` / `combine` (extra/gemm/moe_routing.py:124-131) ACROSS ranks: experts split contiguously over the ranks (rank r owns

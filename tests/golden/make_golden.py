@@ -225,3 +225,24 @@ if "dequant2" in groups:
     out[f"{tag}_raw"], out[f"{tag}_f32"] = raw, t.numpy()
     out[f"{tag}_f16"] = t.cast(dtypes.float16).numpy()
   save("dequant2", **out)
+
+
+if "fp8linear" in groups:
+  # `quantize_to_fp8` and the forward of `FP8Linear` (extra/fp8/fp8_linear.py:4-16,43-63).  The class's custom kernel does not build at this
+  # revision of the reference (`output.size // SEQ` on a method, fp8_linear.py:23), so the contraction it states -- the product of the two
+  # FP8 tensors cast to float, summed over the input features -- is evaluated with ordinary tensor ops; everything else is the class's code.
+  from extra.fp8.fp8_linear import quantize_to_fp8
+  rng = np.random.default_rng(900)
+  out = {}
+  for tag, (m, n_in, n_out) in (("a", (5, 128, 256)), ("b", (1, 256, 256))):
+    # values on coarse grids (the file compresses; the FP8 rounding still has all its cases: the scales are not powers of two)
+    x = (rng.integers(-400, 401, (m, n_in)) / 128).astype(np.float32)
+    w = (rng.integers(-90, 91, (n_out, n_in)) / 1024).astype(np.float32)
+    bias = rng.standard_normal(n_out).astype(np.float32)
+    xq, xf = quantize_to_fp8(Tensor(x))
+    wq, wf = quantize_to_fp8(Tensor(w))
+    y = (xq.cast(dtypes.float).reshape(m, 1, n_in) * wq.cast(dtypes.float).reshape(1, n_out, n_in)).sum(axis=-1)
+    y = y * wf * xf + Tensor(bias)
+    out.update({f"{tag}_x": x, f"{tag}_w": w, f"{tag}_bias": bias, f"{tag}_xq": xq.bitcast(dtypes.uint8).numpy(), f"{tag}_wq": wq.bitcast(dtypes.uint8).numpy(),
+                f"{tag}_xf": xf.numpy(), f"{tag}_wf": wf.numpy(), f"{tag}_y": y.numpy()})
+  save("fp8linear", **out)

@@ -205,6 +205,34 @@ def test_expert_weights_call_matches_the_reference_semantics(per_slot):
   with pytest.raises(ValueError): moe.ExpertWeights(np.zeros((2, 100, 128), np.float32))
 
 
+@pytest.mark.parametrize("dt", [np.float32, np.float16])
+def test_fp8_linear_matches_reference_golden_and_oracle(golden, dt):
+  """`FP8Linear` (extra/fp8/fp8_linear.py:43-63) through the tcgen05 GEMM with fp32 output: codes and factors bit-exact, outputs like the reference."""
+  from tinygrad_b200 import fp8, _lib
+  from tinygrad_b200.runtime import DeviceBuffer
+  from oracle import fp8_linear as f8
+  g = golden("fp8linear")
+  for tag in "ab":
+    x, w, bias = g[f"{tag}_x"], g[f"{tag}_w"], g[f"{tag}_bias"]
+    q, f = fp8.quantize_to_fp8(DeviceBuffer.from_numpy(x), x.size, _lib.F32)
+    np.testing.assert_array_equal(q.numpy().reshape(x.shape), g[f"{tag}_xq"])
+    assert f.numpy().view(np.uint32)[0] == g[f"{tag}_xf"].view(np.uint32)
+    lin = fp8.FP8Linear(w.shape[1], w.shape[0], w, bias)
+    np.testing.assert_array_equal(lin.w_q.numpy().reshape(w.shape), g[f"{tag}_wq"])
+    xd = x.astype(dt)
+    y = lin(DeviceBuffer.from_numpy(xd)).numpy()
+    assert y.dtype == dt and y.shape == (x.shape[0], w.shape[0])
+    ref = g[f"{tag}_y"] if dt == np.float32 else f8.fp8_linear(xd.astype(np.float32), w, bias)
+    assert_close(y, ref, tol=2e-3 if dt == np.float16 else 1e-5, what=f"FP8Linear {tag}")
+  # a larger ragged batch against the oracle, no bias
+  rng = np.random.default_rng(5)
+  x, w = rng.standard_normal((3, 67, 384)).astype(np.float32), (rng.standard_normal((512, 384)) * 0.05).astype(np.float32)
+  y = fp8.FP8Linear(384, 512, w)(DeviceBuffer.from_numpy(x)).numpy()
+  assert y.shape == (3, 67, 512)
+  assert_close(y, f8.fp8_linear(x, w), tol=1e-4, what="FP8Linear, 201 rows")
+  with pytest.raises(ValueError): fp8.FP8Linear(100, 256, np.zeros((256, 100), np.float32))
+
+
 def test_no_tensor_core_wait_ran_out():
   import ctypes
   from tinygrad_b200 import _lib

@@ -192,3 +192,16 @@ def test_other_block_formats_match_reference_and_gguf_py(golden, tag):
   ref = gguf.dequantize(blocks.reshape(-1, nby), gguf.GGMLQuantizationType(typ)).reshape(-1).astype(np.float32)
   np.testing.assert_array_equal(gq.dequantize(blocks, 32 * nel, typ), ref)
   np.testing.assert_array_equal(cpu_gemv.dequantize(blocks, 32 * nel, typ), ref)
+
+
+def test_fp8_linear_matches_the_reference(golden):
+  """`quantize_to_fp8` and the forward of `FP8Linear` (extra/fp8/fp8_linear.py:4-16,43-63): codes and factors bit-exact, outputs to fp32 rounding."""
+  from oracle import fp8_linear as f8
+  g = golden("fp8linear")
+  for tag in "ab":
+    for nm in ("x", "w"):
+      q, f = f8.quantize_to_fp8(g[f"{tag}_{nm}"])
+      np.testing.assert_array_equal(q, g[f"{tag}_{nm}q"])
+      assert f.view(np.uint32) == g[f"{tag}_{nm}f"].view(np.uint32)
+    y = f8.fp8_linear(g[f"{tag}_x"], g[f"{tag}_w"], g[f"{tag}_bias"])
+    np.testing.assert_allclose(y, g[f"{tag}_y"], rtol=0, atol=2e-6 * np.abs(g[f"{tag}_y"]).max())      # the sum order is free

@@ -136,6 +136,10 @@ SIGNATURES = {
   "b200q_moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
   "b200q_mx_status_read_clear": (c_int, [POINTER(c_int)]),
   "b200q_grouped_mxfp8_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+  "b200q_grouped_mxfp8_gemm_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+  "b200q_fp8_absmax": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p]),
+  "b200q_fp8_quantize": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+  "b200q_fp8_scale_bias": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
   "b200q_grouped_mxfp8_gemm_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                              c_void_p]),
 }

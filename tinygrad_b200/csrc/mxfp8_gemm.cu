@@ -131,7 +131,8 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
                                                                       const int32_t* __restrict__ off, int n_experts, int m_total, int n, int k,
                                                                       __nv_bfloat16* __restrict__ c, uint8_t* __restrict__ act_q,
                                                                       uint8_t* __restrict__ act_e8, const __grid_constant__ CUtensorMap tm_a,
-                                                                      const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_c) {
+                                                                      const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_c,
+                                                                      int c_f32) {
   extern __shared__ unsigned char sm_raw[];
   __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_acc_full, bar_acc_empty, bar_drain;
   __shared__ uint32_t tmem_base;
@@ -299,6 +300,15 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_mxfp8_tc_kernel(const uint
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       arrive(s32(&bar_acc_empty));
+      if (c_f32) {      // unrounded sums (the per-tensor FP8 linear scales them afterwards): each thread stores its own row
+        float4* o4 = reinterpret_cast<float4*>(reinterpret_cast<float*>(c) + row * n + n0 + cq * 64);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          o4[j] = make_float4(__uint_as_float(v0[4 * j]), __uint_as_float(v0[4 * j + 1]), __uint_as_float(v0[4 * j + 2]), __uint_as_float(v0[4 * j + 3]));
+          o4[8 + j] = make_float4(__uint_as_float(v1[4 * j]), __uint_as_float(v1[4 * j + 1]), __uint_as_float(v1[4 * j + 2]), __uint_as_float(v1[4 * j + 3]));
+        }
+        continue;
+      }
       __nv_bfloat16* out_row = c + row * n + n0 + cq * 64;
 #if B200Q_MX_STAGED_EPI
       {
@@ -396,7 +406,7 @@ static int make_map(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t k
 }
 
 static int grouped_launch(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts, int m_total, int n, int k,
-                          void* c_bf16, void* act_q, void* act_e8, void* stream) {
+                          void* c_bf16, void* act_q, void* act_e8, void* stream, bool c_f32 = false) {
   if (!a_q || !a_e8 || !b_q || !b_e8 || !off || (!c_bf16 && !act_q) || n_experts <= 0 || m_total <= 0 || n <= 0 || k <= 0) return B200Q_ERR_BAD_ARG;
   if (act_q && (!act_e8 || (((uintptr_t)act_q) & 15))) return B200Q_ERR_BAD_ARG;
   if (m_total % 256 || n % BN || k % BK) return B200Q_ERR_BAD_SHAPE;       // the reference asks M % 256 == N % 256 == K % 128 == 0 (moe_gemm.py:120)
@@ -414,7 +424,7 @@ static int grouped_launch(const void* a_q, const void* a_e8, const void* b_q, co
   alignas(64) CUtensorMap tm_a, tm_b, tm_c;
   memset(&tm_a, 0, sizeof(tm_a)); memset(&tm_b, 0, sizeof(tm_b)); memset(&tm_c, 0, sizeof(tm_c));
 #if B200Q_MX_STAGED_EPI == 2
-  if (c_bf16) { const int rcc = make_map(&tm_c, c_bf16, (uint64_t)m_total, (uint64_t)n, 32, true); if (rcc != B200Q_OK) return rcc; }
+  if (c_bf16 && !c_f32) { const int rcc = make_map(&tm_c, c_bf16, (uint64_t)m_total, (uint64_t)n, 32, true); if (rcc != B200Q_OK) return rcc; }
 #endif
 #if B200Q_MX_TMA
   int rc = make_map(&tm_a, a_q, (uint64_t)m_total, (uint64_t)k, BM);
@@ -422,7 +432,7 @@ static int grouped_launch(const void* a_q, const void* a_e8, const void* b_q, co
   if (rc != B200Q_OK) return rc;
 #endif
   grouped_mxfp8_tc_kernel<<<grid, THREADS, SMEM_BYTES, (cudaStream_t)stream>>>((const uint8_t*)a_q, (const uint8_t*)a_e8, (const uint8_t*)b_q, (const uint8_t*)b_e8, off,
-                                                            n_experts, m_total, n, k, (__nv_bfloat16*)c_bf16, (uint8_t*)act_q, (uint8_t*)act_e8, tm_a, tm_b, tm_c);
+                                                            n_experts, m_total, n, k, (__nv_bfloat16*)c_bf16, (uint8_t*)act_q, (uint8_t*)act_e8, tm_a, tm_b, tm_c, c_f32 ? 1 : 0);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }
@@ -431,6 +441,12 @@ extern "C" int b200q_grouped_mxfp8_gemm(const void* a_q, const void* a_e8, const
                                         int m_total, int n, int k, void* c_bf16, void* stream) {
   if (!c_bf16) return B200Q_ERR_BAD_ARG;
   return grouped_launch(a_q, a_e8, b_q, b_e8, off, n_experts, m_total, n, k, c_bf16, nullptr, nullptr, stream);
+}
+
+extern "C" int b200q_grouped_mxfp8_gemm_f32(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts,
+                                            int m_total, int n, int k, float* c_f32, void* stream) {
+  if (!c_f32) return B200Q_ERR_BAD_ARG;
+  return grouped_launch(a_q, a_e8, b_q, b_e8, off, n_experts, m_total, n, k, c_f32, nullptr, nullptr, stream, true);
 }
 
 extern "C" int b200q_grouped_mxfp8_gemm_swiglu(const void* a_q, const void* a_e8, const void* b_q, const void* b_e8, const int32_t* off, int n_experts,
