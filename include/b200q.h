@@ -344,6 +344,13 @@ int b200q_gemm_f16(const void* a_f16, const void* w_f16, float* c, int m, int n,
  * x rows must be 16-byte aligned (any n_in % 32 == 0 is). */
 int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue, void* y,
                 int y_dtype, int m, int n_out, int n_in, void* stream);
+/* The same Linear on the pipelined kernel: the activations are first split once into fp16 hi / lo tiles in `workspace`
+ * (b200q_qgemm_workspace_bytes(m, n_in) bytes, 16-byte aligned; contents are scratch), which the GEMM's CTAs read by bulk copies while
+ * their threads only unpack weights, three 64-column stages in flight.  Same arguments, same numerics (the order of the fp32
+ * additions inside the tensor core aside), same epilogues.  Two launches. */
+size_t b200q_qgemm_workspace_bytes(int m, int n_in);
+int b200q_qgemm_ws(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue, void* y,
+                   int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes, void* stream);
 /* The same Linear for a few activation rows (m <= 32: batched decode), the weight-streaming shape: the operands swap roles on the
  * tensor core (weight rows = M, activation rows = N = 32), K is split over CTAs so that every layer fills the GPU, partial sums go
  * through `workspace` (b200q_qgemm_skinny_workspace_bytes) and are added in a fixed order by a second kernel that also applies

@@ -64,6 +64,14 @@ def test_packed_bytes(lib):
   assert lib.b200q_packed_bytes(_lib.Q4_0, 0, 128) == 0
 
 
+def test_workspace_sizes(lib):
+  assert lib.b200q_qgemm_workspace_bytes(511, 4096) == 4 * 32 * 2 * 32768      # 4 row tiles x 32 column groups x (hi, lo) x 32 KB
+  assert lib.b200q_qgemm_workspace_bytes(1, 96) == 2 * 32768 and lib.b200q_qgemm_workspace_bytes(0, 4096) == 0
+  assert lib.b200q_qgemm_ws(_lib.Q4_0, 16, 16, _lib.F32, None, None, 0, 16, _lib.F32, 4, 16, 128, 16, 100, None) == -6     # workspace too small
+  assert lib.b200q_qgemm_ws(_lib.Q4_0, 16, 16, _lib.F32, None, None, 0, 16, _lib.F32, 4, 16, 128, None, 1 << 20, None) == -1
+  assert lib.b200q_fp8_absmax(None, _lib.F32, 8, 16, None) == -1 and lib.b200q_fp8_scale_bias(16, 0, 8, 16, 16, None, 16, _lib.F32, None) == -1
+
+
 def test_bad_arguments_are_rejected_without_a_device(lib):
   assert lib.b200q_dequant_raw(5, 16, 16, 32, _lib.F32, None) == -1          # unknown type
   assert lib.b200q_dequant_raw(_lib.Q4_0, 16, 16, 33, _lib.F32, None) == -2  # not whole blocks

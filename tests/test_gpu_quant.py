@@ -202,8 +202,13 @@ def test_tensor_core_gemm_matches_fp16_operand_reference(tag, m, n_out, n_in, x_
   x = rng.standard_normal((m, n_in)).astype(x_dtype)
   b = rng.standard_normal(n_out).astype(np.float16) if bias else None
   lin = quant.QuantLinear(n_in, n_out, typ, raw, bias=b)
-  y = lin(DeviceBuffer.from_numpy(x)).numpy()
+  y = lin(DeviceBuffer.from_numpy(x)).numpy()                     # the pipelined kernel (pre-split activations in a workspace)
   assert y.dtype == x_dtype and y.shape == (m, n_out)
+  # the single-buffered kernel computes the same products; only the order of the fp32 additions inside the tensor core may differ
+  y_old = DeviceBuffer.empty((m, n_out), x_dtype)
+  dt = quant.F32 if x_dtype == np.float32 else quant.F16
+  quant.qgemm(lin.weight.buf.ptr, typ, n_out, n_in, DeviceBuffer.from_numpy(x), y_old, m, x_dtype=dt, y_dtype=dt, bias=lin.bias)
+  np.testing.assert_allclose(y.astype(np.float32), y_old.numpy().astype(np.float32), rtol=0, atol=(2e-3 if x_dtype == np.float16 else 2e-5) * max(1.0, float(np.abs(y).max())))
   ref32 = llm.linear(x.astype(np.float32), gq.weight_matrix(raw, n_out, n_in, typ), b)
   if x_dtype == np.float32:
     assert_close(y, ref32, tol=1e-2, what="tcgen05 GEMM vs fp32 reference")

@@ -109,6 +109,8 @@ SIGNATURES = {
   "b200q_advance": (c_int, [c_void_p, c_int, c_int, c_void_p]),
   "b200q_gemm_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
   "b200q_qgemm": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+  "b200q_qgemm_workspace_bytes": (c_size_t, [c_int, c_int]),
+  "b200q_qgemm_ws": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
   "b200q_qgemm_skinny_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
   "b200q_qgemm_skinny": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
                                 c_void_p]),

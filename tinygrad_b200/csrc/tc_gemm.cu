@@ -590,6 +590,242 @@ __global__ void skinny_reduce_kernel(const float* __restrict__ part, int n_split
   if (y_f16) reinterpret_cast<__half*>(y)[i] = __float2half_rn(o); else reinterpret_cast<float*>(y)[i] = o;
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Pipelined dequant GEMM (prompt chunks).  The kernel above converts the same activation rows once per column tile and moves all its
+// warps in lock-step through convert -> unpack -> barrier -> MMA -> wait.  Here the activations are split ONCE per GEMM into fp16
+// hi / lo tiles laid out as the tensor core reads them (split_rows_kernel: per 128 rows x 128 columns one 32 KB tile per half, in a
+// workspace), so a CTA brings its A operand in by bulk copies; a stage is 64 columns of K (A hi / lo 32 KB by bulk copy, W hi / lo
+// 32 KB unpacked by the 512 threads, 16 weights each); the weight slots are double-buffered (the MMAs of a step run while the threads unpack
+// the next one) and the activation copies run two steps ahead in a ring of four slots; weight words are fetched two steps ahead too.
+constexpr int P_BK = 64, P_A_SLOTS = 4;               // K columns per step; activation slots (copies run two steps ahead); two weight slots
+constexpr int P_HALF = BM * P_BK * 2;                 // 16 KB: one operand half (hi or lo) of a step
+constexpr int P_SMEM = (P_A_SLOTS + 2) * 2 * P_HALF;  // 4 x (A hi, A lo) + 2 x (W hi, W lo) = 192 KB
+constexpr int WS_TILE = BM * QBK * 2;                 // 32 KB: 128 rows x 128 columns of fp16 in core-matrix order
+
+template <typename T>
+__global__ void __launch_bounds__(QGEMM_THREADS) split_rows_kernel(const T* __restrict__ x, int m, int n_in, int kgroups, unsigned char* __restrict__ ws,
+                                                                   int with_lo) {
+  const int kg = blockIdx.x, mt = blockIdx.y, tid = threadIdx.x;
+  unsigned char* hi = ws + ((size_t)(mt * kgroups + kg) * 2) * WS_TILE;
+  unsigned char* lo = hi + WS_TILE;
+#pragma unroll
+  for (int j = 0; j < BM * (QBK / 8) / QGEMM_THREADS; j++) {
+    const int i = tid + j * QGEMM_THREADS, r = i / (QBK / 8), kc = (i % (QBK / 8)) * 8, row = mt * BM + r, k = kg * QBK + kc;
+    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (row < m && k < n_in) {
+      if (sizeof(T) == 2) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(x) + (size_t)row * n_in + k);
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int q = 0; q < 4; q++) { const float2 t2 = __half22float2(h[q]); f[2 * q] = t2.x; f[2 * q + 1] = t2.y; }
+      } else {
+        const float* src = reinterpret_cast<const float*>(x) + (size_t)row * n_in + k;
+        const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+      }
+    }
+    // element order inside a core: [0,2,1,3,4,6,5,7], the order the weight unpack delivers
+    __half2 o[4] = {__floats2half2_rn(f[0], f[2]), __floats2half2_rn(f[1], f[3]), __floats2half2_rn(f[4], f[6]), __floats2half2_rn(f[5], f[7])};
+    *reinterpret_cast<uint4*>(hi + tile_off(r, kc, BM)) = *reinterpret_cast<const uint4*>(o);
+    if (with_lo) {
+      const float2 h0 = __half22float2(o[0]), h1 = __half22float2(o[1]), h2 = __half22float2(o[2]), h3 = __half22float2(o[3]);
+      __half2 lo2[4] = {__floats2half2_rn(f[0] - h0.x, f[2] - h0.y), __floats2half2_rn(f[1] - h1.x, f[3] - h1.y),
+                        __floats2half2_rn(f[4] - h2.x, f[6] - h2.y), __floats2half2_rn(f[5] - h3.x, f[7] - h3.y)};
+      *reinterpret_cast<uint4*>(lo + tile_off(r, kc, BM)) = *reinterpret_cast<const uint4*>(lo2);
+    }
+  }
+}
+
+__device__ __forceinline__ void p_bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+template <int QT>
+__global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_pipe_kernel(const QGemmParams p, const unsigned char* __restrict__ ws) {
+  extern __shared__ __align__(128) unsigned char psm[];
+  __shared__ __align__(8) uint64_t full[P_A_SLOTS], empty[2], done;
+  __shared__ uint32_t tmem_base;
+  constexpr int TB = tile_bytes(QT);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int mt = blockIdx.y, m0 = mt * BM, rt0 = blockIdx.x * (BN / 16);
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&tmem_base)), "r"(BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+    for (int i = 0; i < P_A_SLOTS; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&full[i])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&empty[0])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&empty[1])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&done)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = tid; i < P_SMEM / 16; i += QGEMM_THREADS) reinterpret_cast<uint4*>(psm)[i] = make_uint4(0, 0, 0, 0);   // weight rows past n_out stay zero
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t taddr = tmem_base;
+  const uint32_t idesc = make_idesc(BM, BN);
+  const int n_steps = 2 * p.kgroups;
+  const uint32_t a_bytes = p.x_f16 ? P_HALF : 2 * P_HALF;
+  unsigned char* const b_ring = psm + P_A_SLOTS * 2 * P_HALF;
+  // this thread's 16 weights of a step: row r of the 128, block b of the step's two, half h of the block's 32 (8 quant bytes)
+  const int r = tid >> 2, b = (tid >> 1) & 1, h = tid & 1;
+  const int w_tl = r >> 4, h8 = (r >> 3) & 1, g = r & 7;
+  const bool w_on = rt0 + w_tl < p.n_row_tiles;
+  struct WRegs { uint2 q4; uint4 q8; uint32_t d2; };
+  WRegs wa = {make_uint2(0, 0), make_uint4(0, 0, 0, 0), 0u}, wb = wa;      // weights of the step in hand and of the one after it
+  auto load_regs = [&](int step, WRegs& w) {
+    if (!w_on || step >= n_steps) return;
+    const int t = (step & 1) * 2 + b;
+    const uint8_t* tile = p.w + ((size_t)(rt0 + w_tl) * p.kgroups + (step >> 1)) * TB;
+    const unsigned short dbits = reinterpret_cast<const unsigned short*>(tile + (TB - 128))[(2 * g + (t >> 1)) * 4 + h8 * 2 + (t & 1)];
+    w.d2 = (uint32_t)dbits | ((uint32_t)dbits << 16);
+    if (QT == B200Q_Q4_0) w.q4 = ldg_stream(reinterpret_cast<const uint2*>(tile) + (h8 * 32 + g * 4 + t) * 2 + h);
+    else w.q8 = ldg_stream(reinterpret_cast<const uint4*>(tile) + (2 * h8 + h) * 32 + g * 4 + t);
+  };
+  auto issue_a = [&](int step) {       // thread 0: the activation halves of `step` into its slot of the A ring
+    const int slot = step % P_A_SLOTS;
+    const uint32_t fb = s32(&full[slot]), dst = s32(psm + slot * 2 * P_HALF);
+    const unsigned char* src = ws + ((size_t)(mt * p.kgroups + (step >> 1)) * 2) * WS_TILE + (step & 1) * P_HALF;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fb), "r"(a_bytes) : "memory");
+    p_bulk_g2s(dst, src, P_HALF, fb);
+    if (!p.x_f16) p_bulk_g2s(dst + P_HALF, src + WS_TILE, P_HALF, fb);
+  };
+  bool ok = true;
+  int a_issued = 0;                    // thread 0: highest step whose activation copy is out
+  load_regs(0, wa); load_regs(1, wb);
+  if (tid == 0) { issue_a(0); if (n_steps > 1) { issue_a(1); a_issued = 1; } }
+  // One step: (1) the MMAs of step - 2 are done -> their W slot (this step's) and their A slot (step + 2's) are free; (2) thread 0 sends
+  // for the activations of step + 2; (3) everybody unpacks this step's weights and asks for those of step + 2; (4) thread 0 issues the MMAs.
+  auto do_step = [&](int step, WRegs& w) -> bool {
+    if (step >= 2) {
+      bool free_ok = true;
+      if (tid == 0) free_ok = wait_bar(s32(&empty[step & 1]), ((step - 2) >> 1) & 1);
+      if (!__syncthreads_and(free_ok)) return false;
+    }
+    if (tid == 0 && step + 2 < n_steps) { issue_a(step + 2); a_issued = step + 2; }
+    unsigned char* sBh = b_ring + (step & 1) * 2 * P_HALF;
+    unsigned char* sBl = sBh + P_HALF;
+    if (w_on) {
+      uint4 lo0, lo1, c0, c1;
+      int k0, k1;
+      if (QT == B200Q_Q4_0) {      // low nibbles: elements 8h .. 8h+7, high nibbles: 16 + 8h ..
+        c0 = q4_core<false>(w.q4.x, w.q4.y, w.d2, lo0); c1 = q4_core<true>(w.q4.x, w.q4.y, w.d2, lo1);
+        k0 = b * 32 + 8 * h; k1 = k0 + 16;
+      } else {                     // bytes 16h .. 16h+15
+        c0 = q8_core(w.q8.x, w.q8.y, w.d2, lo0); c1 = q8_core(w.q8.z, w.q8.w, w.d2, lo1);
+        k0 = b * 32 + 16 * h; k1 = k0 + 8;
+      }
+#ifndef B200Q_PX_NOSTORE
+      *reinterpret_cast<uint4*>(sBh + tile_off(r, k0, BN)) = c0;
+      *reinterpret_cast<uint4*>(sBh + tile_off(r, k1, BN)) = c1;
+      if (!p.x_f16) {
+        *reinterpret_cast<uint4*>(sBl + tile_off(r, k0, BN)) = lo0;
+        *reinterpret_cast<uint4*>(sBl + tile_off(r, k1, BN)) = lo1;
+      }
+#else
+      if (c0.x == 0x12345678u && lo1.y == 0x9abcdef0u) *reinterpret_cast<uint4*>(sBh + tile_off(r, k0, BN)) = c1;
+      (void)lo0;
+#endif
+    }
+    load_regs(step + 2, w);
+#ifndef B200Q_PX_NOFENCE
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
+    __syncthreads();
+    if (tid == 0) {
+      const int slot = step % P_A_SLOTS;
+      if (wait_bar(s32(&full[slot]), (step / P_A_SLOTS) & 1)) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t sA = s32(psm + slot * 2 * P_HALF), sA2 = sA + P_HALF, sB = s32(sBh), sB2 = sB + P_HALF;
+#ifndef B200Q_PX_NOMMA
+#pragma unroll
+        for (int kk = 0; kk < P_BK / 16; kk++) {
+          const uint64_t da = make_desc(sA + kk * 2 * (BM * 16), BM * 16, 128), db = make_desc(sB + kk * 2 * (BN * 16), BN * 16, 128);
+          const uint32_t acc = (step > 0 || kk > 0) ? 1u : 0u;
+          asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                       ::"r"(taddr), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+          if (!p.x_f16) {
+            const uint64_t da2 = make_desc(sA2 + kk * 2 * (BM * 16), BM * 16, 128), db2 = make_desc(sB2 + kk * 2 * (BN * 16), BN * 16, 128);
+            asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                         ::"r"(taddr), "l"(da2), "l"(db), "r"(idesc), "r"(1u) : "memory");
+            asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                         ::"r"(taddr), "l"(da), "l"(db2), "r"(idesc), "r"(1u) : "memory");
+          }
+        }
+#else
+        (void)sA2; (void)sB2; (void)sB; (void)sA;
+#endif
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&empty[step & 1])) : "memory");
+        if (step == n_steps - 1) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&done)) : "memory");
+      }
+    }
+    return true;
+  };
+  for (int step = 0; step < n_steps && ok; step += 2) {      // n_steps is even: two steps per K group
+    ok = do_step(step, wa);
+    if (ok) ok = do_step(step + 1, wb);
+  }
+  // all MMAs done (or a wait ran out: then every copy and MMA issued so far is drained before the tensor memory goes back)
+  bool fin = true;
+  if (tid == 0) {
+    if (ok) fin = wait_bar(s32(&done), 0);       // the last step's copies were waited for before its MMAs were issued
+    if (!ok) {      // left the loop early: drain the MMAs issued so far and the (at most two) activation copies still in flight
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&done)) : "memory");
+      wait_bar(s32(&done), 0);
+      for (int st = max(0, a_issued - 2); st <= a_issued; st++) wait_bar(s32(&full[st % P_A_SLOTS]), (st / P_A_SLOTS) & 1);
+    }
+  }
+  ok = __syncthreads_and(ok && fin);
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (ok) {
+    const int sub = warp & 3;
+    const int row = m0 + sub * 32 + (tid & 31);
+    const int j0 = (warp >> 2) * 32;
+    uint32_t v[32];
+    const uint32_t ta = taddr + ((uint32_t)(sub * 32) << 16) + j0;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+                   "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+                   "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+                   "=r"(v[31])
+                 : "r"(ta));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    if (row < p.m && p.silu_mul) {
+#pragma unroll
+      for (int t2 = 0; t2 < 2; t2++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const int acol = (rt0 + j0 / 16 + t2) * 8 + j;
+          if (acol < p.n_out / 2) {
+            const float gte = __uint_as_float(v[t2 * 16 + j]), up = __uint_as_float(v[t2 * 16 + 8 + j]);
+            const float o = (gte / (1.f + expf(-gte))) * up;
+            if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)row * (p.n_out / 2) + acol] = __float2half_rn(o);
+            else reinterpret_cast<float*>(p.y)[(size_t)row * (p.n_out / 2) + acol] = o;
+          }
+        }
+    } else if (row < p.m) {
+#pragma unroll
+      for (int j = 0; j < 32; j++) {
+        const int col = rt0 * 16 + j0 + j;
+        if (col < p.n_out) {
+          float o = __uint_as_float(v[j]);
+          if (p.bias) o += __half2float(p.bias[col]);
+          const size_t at = (size_t)row * p.n_out + col;
+          if (p.residual) o += p.y_f16 ? __half2float(reinterpret_cast<const __half*>(p.residual)[at]) : reinterpret_cast<const float*>(p.residual)[at];
+          if (p.y_f16) reinterpret_cast<__half*>(p.y)[at] = __float2half_rn(o);
+          else reinterpret_cast<float*>(p.y)[at] = o;
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(BN) : "memory");
+}
+
 }  // namespace
 
 extern "C" int b200q_tc_status_read_clear(int* status) {
@@ -636,6 +872,46 @@ extern "C" int b200q_qgemm(int qtype, const void* w_packed, const void* x, int x
   }
   if (qtype == B200Q_Q4_0) tc_qgemm_kernel<B200Q_Q4_0><<<grid, QGEMM_THREADS, QGEMM_SMEM, (cudaStream_t)stream>>>(p);
   else tc_qgemm_kernel<B200Q_Q8_0><<<grid, QGEMM_THREADS, QGEMM_SMEM, (cudaStream_t)stream>>>(p);
+  B200Q_CHECK_CUDA(cudaGetLastError());
+  return B200Q_OK;
+}
+
+extern "C" size_t b200q_qgemm_workspace_bytes(int m, int n_in) {
+  if (m <= 0 || n_in <= 0) return 0;
+  return (size_t)ceil_div(m, BM) * ceil_div(n_in, GROUP_ELEMS) * 2 * WS_TILE;
+}
+
+extern "C" int b200q_qgemm_ws(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue,
+                              void* y, int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!w_packed || !x || !y || !workspace || m <= 0 || n_out <= 0 || n_in <= 0) return B200Q_ERR_BAD_ARG;
+  if (epilogue != B200Q_EPI_LINEAR && epilogue != B200Q_EPI_SILU_MUL) return B200Q_ERR_BAD_ARG;
+  if (epilogue == B200Q_EPI_SILU_MUL && (bias_f16 || residual || n_out % 16)) return B200Q_ERR_BAD_ARG;
+  if (qtype == B200Q_Q6_K) return B200Q_ERR_UNSUPPORTED;
+  if (qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
+  if ((x_dtype != B200Q_F32 && x_dtype != B200Q_F16) || (y_dtype != B200Q_F32 && y_dtype != B200Q_F16)) return B200Q_ERR_BAD_ARG;
+  if (n_in % 32) return B200Q_ERR_BAD_SHAPE;
+  if (((uintptr_t)w_packed | (uintptr_t)x | (uintptr_t)workspace) & 15) return B200Q_ERR_MISALIGNED;
+  if (workspace_bytes < b200q_qgemm_workspace_bytes(m, n_in)) return B200Q_ERR_TOO_LARGE;
+  QGemmParams p;
+  p.w = (const uint8_t*)w_packed; p.x = x; p.bias = (const __half*)bias_f16; p.residual = residual; p.y = y;
+  p.silu_mul = epilogue == B200Q_EPI_SILU_MUL;
+  p.m = m; p.n_out = n_out; p.n_in = n_in; p.kgroups = ceil_div(n_in, GROUP_ELEMS); p.n_row_tiles = ceil_div(n_out, TILE_ROWS);
+  p.x_f16 = x_dtype == B200Q_F16; p.y_f16 = y_dtype == B200Q_F16;
+  static PerDeviceFlag attr;
+  const int dev = b200q_current_device();
+  if (dev < 0) return B200Q_ERR_CUDA;
+  if (!attr.test(dev)) {
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_pipe_kernel<B200Q_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM));
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(tc_qgemm_pipe_kernel<B200Q_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM));
+    attr.set(dev);
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const dim3 sgrid(p.kgroups, ceil_div(m, BM));
+  if (p.x_f16) split_rows_kernel<__half><<<sgrid, QGEMM_THREADS, 0, st>>>((const __half*)x, m, n_in, p.kgroups, (unsigned char*)workspace, 0);
+  else split_rows_kernel<float><<<sgrid, QGEMM_THREADS, 0, st>>>((const float*)x, m, n_in, p.kgroups, (unsigned char*)workspace, 1);
+  const dim3 grid(ceil_div(p.n_row_tiles, BN / 16), ceil_div(m, BM));
+  if (qtype == B200Q_Q4_0) tc_qgemm_pipe_kernel<B200Q_Q4_0><<<grid, QGEMM_THREADS, P_SMEM, st>>>(p, (const unsigned char*)workspace);
+  else tc_qgemm_pipe_kernel<B200Q_Q8_0><<<grid, QGEMM_THREADS, P_SMEM, st>>>(p, (const unsigned char*)workspace);
   B200Q_CHECK_CUDA(cudaGetLastError());
   return B200Q_OK;
 }

@@ -60,7 +60,7 @@ DEFAULT_HANDOVER = ("attn_o",)
 class Transformer:
   def __init__(self, config: TransformerConfig, state_dict: dict, ggml_type: int = _lib.Q4_0, n_split: int = 0, use_pdl: bool = True,
                use_graph: bool = True, gemv_max_ctas: int = 0, handover=None, tp=None, output_type: int = None, prefill_rows: int = 64,
-               prefill_chunk: int = 512, batch: int = 1, engine: str = None, linear_types: dict = None):
+               prefill_chunk: int = 512, batch: int = 1, engine: str = None, linear_types: dict = None, pipelined_gemm: bool = True):
     """state_dict: the reference's tensor names -> numpy arrays; Linear weights as raw
     GGUF block bytes (uint8), embeddings / norms / biases as fp16.
     tp: a tensor_parallel.TPGroup; `config` is then the FULL model and `state_dict` this rank's shard (shard_state_dict).
@@ -84,6 +84,7 @@ class Transformer:
     assert c.max_context > 0 and c.n_heads % c.n_kv_heads == 0
     self.qtype, self.flags, self.use_graph = ggml_type, (FLAG_PDL if use_pdl else 0), use_graph
     self.q_dim, self.kv_dim = c.n_heads * c.head_dim, c.n_kv_heads * c.head_dim
+    self.pipelined_gemm = pipelined_gemm      # prompt GEMMs on the pipelined kernel (False: the single-buffered one)
     self.gemv_max_ctas = gemv_max_ctas if isinstance(gemv_max_ctas, dict) else {"*": gemv_max_ctas}   # per Linear ("qkv", "o", "gate_up", "down", "head") or one for all
     self.n_split = n_split or _lib.load().b200q_attn_min_split(c.max_context)
     self.max_context = c.max_context
@@ -331,7 +332,9 @@ class Transformer:
       self._pf = dict(x=DeviceBuffer.empty((T, c.dim), np.float32), xn=DeviceBuffer.empty((T, c.dim), np.float32),
                       qkv=DeviceBuffer.empty((T, self.q_dim + 2 * self.kv_dim), np.float32), q16=DeviceBuffer.empty((T, self.q_dim), np.float32),
                       att=DeviceBuffer.empty((T, self.q_dim), np.float32),
-                      act=DeviceBuffer.empty((T, max(c.hidden_dim, c.shared_expert_dim, 1)), np.float32))
+                      act=DeviceBuffer.empty((T, max(c.hidden_dim, c.shared_expert_dim, 1)), np.float32),
+                      # activation tiles of the pipelined GEMM (split once per GEMM, read by every column tile's CTA)
+                      ws=DeviceBuffer(quant.qgemm_workspace_bytes(T, max(c.dim, self.q_dim, c.hidden_dim, c.shared_expert_dim, 1))) if self.pipelined_gemm else None)
       if self.is_moe:
         self._pf.update(xb=DeviceBuffer.empty((T, c.dim), np.uint16), logits=DeviceBuffer.empty((T, c.num_experts), np.float32))
         if c.shared_expert_dim: self._pf.update(sh=DeviceBuffer.empty((T, c.dim), np.float32), shg=DeviceBuffer.empty((T,), np.float32))
@@ -351,11 +354,11 @@ class Transformer:
                                  self.full_config.vocab_size, f["x"].ptr, s))
       for b in self.blk:
         check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.attn_norm.ptr, c.norm_eps, T, c.dim, f["xn"].ptr, F32, s))
-        quant.qgemm(b.qkv.ptr, self.qtype, qkv_rows, c.dim, f["xn"], f["qkv"], T, x_dtype=F32, y_dtype=F32, bias=b.qkv_bias, stream=s)
+        quant.qgemm(b.qkv.ptr, self.qtype, qkv_rows, c.dim, f["xn"], f["qkv"], T, x_dtype=F32, y_dtype=F32, bias=b.qkv_bias, stream=s, workspace=f["ws"])
         check(lib.b200q_attn_prefill(f["qkv"].ptr, b.k_cache.ptr + seq * self.seq_cache_bytes, b.v_cache.ptr + seq * self.seq_cache_bytes, kvdt,
                                      self.rope.ptr, p0, T, c.n_heads, c.n_kv_heads, c.head_dim,
                                      c.rope_dim, c.max_context, f["q16"].ptr, f["att"].ptr, F32, s))
-        quant.qgemm(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, f["att"], f["x"], T, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s)
+        quant.qgemm(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, f["att"], f["x"], T, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s, workspace=f["ws"])
         check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.ffn_norm.ptr, c.norm_eps, T, c.dim, f["xn"].ptr, F32, s))
         if b.moe is not None:
           # router on the fp32 normed rows, experts on their bf16 rounding (the activation dtype of the MXFP8 path); bf16 result + residual
@@ -364,15 +367,15 @@ class Transformer:
           y = b.moe(f["xb"], f["logits"], T, stream=s)
           if b.sh_gate_up is not None:      # shared expert on the fp32 normed rows (model.py:131-134), added before x moves
             quant.qgemm(b.sh_gate_up.buf.ptr, self.qtype, 2 * c.shared_expert_dim, c.dim, f["xn"], f["act"], T, x_dtype=F32, y_dtype=F32,
-                        epilogue=EPI_SILU_MUL, stream=s)
-            quant.qgemm(b.sh_down.buf.ptr, self.qtype, c.dim, c.shared_expert_dim, f["act"], f["sh"], T, x_dtype=F32, y_dtype=F32, stream=s)
+                        epilogue=EPI_SILU_MUL, stream=s, workspace=f["ws"])
+            quant.qgemm(b.sh_down.buf.ptr, self.qtype, c.dim, c.shared_expert_dim, f["act"], f["sh"], T, x_dtype=F32, y_dtype=F32, stream=s, workspace=f["ws"])
             if b.sh_inp is not None: quant.gemv_dense(b.sh_inp.buf, b.sh_inp.dtype, 1, c.dim, f["xn"], f["shg"], m=T, stream=s)
             check(lib.b200q_add_rows_gated(f["x"].ptr, f["sh"].ptr, f["shg"].ptr if b.sh_inp is not None else None, T, c.dim, s))
           check(lib.b200q_add_rows_bf16(f["x"].ptr, y.ptr, T * c.dim, s))
           continue
         quant.qgemm(b.gate_up.buf.ptr, self.qtype, 2 * c.hidden_dim, c.dim, f["xn"], f["act"], T, x_dtype=F32, y_dtype=F32, epilogue=EPI_SILU_MUL,
-                    stream=s)
-        quant.qgemm(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, f["act"], f["x"], T, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s)
+                    stream=s, workspace=f["ws"])
+        quant.qgemm(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, f["act"], f["x"], T, x_dtype=F32, y_dtype=F32, residual=f["x"], stream=s, workspace=f["ws"])
     if sync:
       self.stream.synchronize()
       self.pos.copy_from(np.array([start_pos + n], dtype=np.int32), offset=4 * seq)

@@ -85,11 +85,25 @@ def gemv(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int = 1, x_dtyp
   check(_lib.load().b200q_gemv(ctypes.byref(a), stream_ptr(stream)))
 
 
+import os
+PIPELINED_GEMM = os.environ.get("B200Q_PIPELINED_GEMM", "1") == "1"   # qgemm uses the pipelined kernel when it is handed a workspace
+
+
+def qgemm_workspace_bytes(m: int, n_in: int) -> int:
+  return int(_lib.load().b200q_qgemm_workspace_bytes(m, n_in))
+
+
 def qgemm(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int, x_dtype=F32, y_dtype=F32, bias=None, residual=None,
-          epilogue: int = EPI_LINEAR, stream=None) -> None:
-  """Batched / prefill linear on the tcgen05 tensor cores: the weights are streamed once per 128 activation rows."""
-  check(_lib.load().b200q_qgemm(qtype, w_ptr, ptr_of(x), x_dtype, ptr_of(bias), ptr_of(residual), epilogue, ptr_of(y), y_dtype, m, n_out, n_in,
-                                stream_ptr(stream)))
+          epilogue: int = EPI_LINEAR, stream=None, workspace: DeviceBuffer = None) -> None:
+  """Batched / prefill linear on the tcgen05 tensor cores: the weights are streamed once per 128 activation rows.  With a `workspace`
+  (qgemm_workspace_bytes(m, n_in) bytes) the pipelined kernel runs: activations pre-split once, bulk-copied operands, MMAs under the unpacking."""
+  lib = _lib.load()
+  if workspace is not None and PIPELINED_GEMM:
+    check(lib.b200q_qgemm_ws(qtype, w_ptr, ptr_of(x), x_dtype, ptr_of(bias), ptr_of(residual), epilogue, ptr_of(y), y_dtype, m, n_out, n_in,
+                             workspace.ptr, workspace.nbytes, stream_ptr(stream)))
+    return
+  check(lib.b200q_qgemm(qtype, w_ptr, ptr_of(x), x_dtype, ptr_of(bias), ptr_of(residual), epilogue, ptr_of(y), y_dtype, m, n_out, n_in,
+                        stream_ptr(stream)))
 
 
 def qgemm_skinny_workspace_bytes(m: int, n_out: int, n_in: int) -> int:
@@ -160,6 +174,7 @@ class QuantLinear:
     self.fused = ggml_type in (Q4_0, Q8_0) or (ggml_type == Q6_K and in_features % 256 == 0)
     self.weight = repack(raw, out_features, in_features, ggml_type) if self.fused else DenseWeight(raw, out_features, in_features, ggml_type)
     self.bias = None if bias is None else DeviceBuffer.from_numpy(np.asarray(bias, dtype=np.float16))
+    self._ws = None      # activation tiles of the pipelined GEMM, grown on demand
 
   def __call__(self, x: DeviceBuffer, stream=None) -> DeviceBuffer:
     if x.dtype not in _DT: raise TypeError(f"activations must be float16 or float32, got {x.dtype}")
@@ -171,7 +186,10 @@ class QuantLinear:
       if m: gemv_dense(self.weight.buf, self.weight.dtype, self.out_features, self.in_features, x, y, m=m, x_dtype=dt, y_dtype=dt, bias=self.bias,
                        stream=stream)
     elif m >= GEMM_MIN_ROWS and self.ggml_type != Q6_K:
-      qgemm(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m, x_dtype=dt, y_dtype=dt, bias=self.bias, stream=stream)
+      need = qgemm_workspace_bytes(m, self.in_features)
+      if self._ws is None or self._ws.nbytes < need: self._ws = DeviceBuffer(need)
+      qgemm(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m, x_dtype=dt, y_dtype=dt, bias=self.bias, stream=stream,
+            workspace=self._ws)
     elif m:
       gemv(self.weight.buf.ptr, self.ggml_type, self.out_features, self.in_features, x, y, m=m, x_dtype=dt, y_dtype=dt, bias=self.bias, stream=stream)
     return y
