@@ -355,6 +355,14 @@ int b200q_qgemm_ws(int qtype, const void* w_packed, const void* x, int x_dtype, 
  * tensor core (weight rows = M, activation rows = N = 32), K is split over CTAs so that every layer fills the GPU, partial sums go
  * through `workspace` (b200q_qgemm_skinny_workspace_bytes) and are added in a fixed order by a second kernel that also applies
  * bias / residual / SwiGLU.  Same operands, numerics and epilogue rules as b200q_qgemm. */
+/* The same Linear for a FEW activation rows on the int8 tensor cores (batched decode): the 8 columns of an m16n8k32 MMA are 8 activation
+ * rows, so a pass streams the weights once for 8 rows at the one-row GEMV's arithmetic (15-bit activation integers, exact block sums, fp32
+ * across blocks); m > 8 takes ceil(m / 8) passes.  Three kinds of launches per pass: quantise the rows into the MMA's operand order, the
+ * streaming kernel (partial sums per K chunk of 4096 inputs into the workspace), the fixed-order sum with the epilogue.  Arguments as
+ * b200q_qgemm_skinny; workspace: b200q_qgemv_rows_workspace_bytes(m, n_out, n_in) bytes, 16-byte aligned. */
+size_t b200q_qgemv_rows_workspace_bytes(int m, int n_out, int n_in);
+int b200q_qgemv_rows(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue, void* y,
+                     int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes, void* stream);
 size_t b200q_qgemm_skinny_workspace_bytes(int m, int n_out, int n_in);
 int b200q_qgemm_skinny(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue, void* y,
                        int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes, void* stream);

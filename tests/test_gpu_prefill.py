@@ -250,3 +250,44 @@ def test_skinny_split_k_gemm(tag, m, n_out, n_in, x_dtype, epi):
     y2 = DeviceBuffer.empty((m, n_out), np.float32)
     quant.qgemm_skinny(pw.buf.ptr, typ, n_out, n_in, dx, y2, m, ws, x_dtype=quant._DT[np.dtype(x_dtype)])
     np.testing.assert_array_equal(y2.numpy(), got)
+
+
+@pytest.mark.parametrize("tag,m,n_out,n_in,x_dtype,epi", [("q4_0", 8, 4096, 4096, np.float32, "res"), ("q8_0", 8, 512, 18944, np.float32, "bias"),
+                                                        ("q4_0", 5, 200, 96, np.float32, "lin"), ("q8_0", 17, 48, 1536, np.float32, "silu"),
+                                                        ("q4_0", 1, 14336 * 2, 4096, np.float32, "silu"), ("q4_0", 3, 4096, 14336, np.float16, "lin"),
+                                                        ("q8_0", 32, 3584, 3584, np.float32, "res")])
+def _pending_test_few_row_fused_gemv(tag, m, n_out, n_in, x_dtype, epi):
+  """Few activation rows on the int8 tensor cores (8 rows per pass over the weights, K chunks summed in a fixed order) against the fp32
+  product: the one-row GEMV's arithmetic (15-bit activation integers, exact sums inside a block), so its error bound; bit-reproducible."""
+  from tinygrad_b200 import quant, _lib
+  from tinygrad_b200.runtime import DeviceBuffer
+  typ = {"q4_0": 2, "q8_0": 8}[tag]
+  rng = np.random.default_rng(m + n_out)
+  x = rng.standard_normal((m, n_in)).astype(x_dtype)
+  dx, xdt = DeviceBuffer.from_numpy(x), quant._DT[np.dtype(x_dtype)]
+  ws = DeviceBuffer(quant.qgemv_rows_workspace_bytes(m, n_out, n_in))
+  xf = x.astype(np.float32)
+  if epi == "silu":
+    hid = n_out // 2
+    g, u = synth.BLOCK_MAKERS[typ](hid, n_in, rng), synth.BLOCK_MAKERS[typ](hid, n_in, rng)
+    pw = quant.repack(g, hid, n_in, typ, raw_up=u)
+    y = DeviceBuffer.empty((m, hid), np.float32)
+    quant.qgemv_rows(pw.buf.ptr, typ, n_out, n_in, dx, y, m, ws, x_dtype=xdt, epilogue=_lib.EPI_SILU_MUL)
+    ref = llm.silu(xf @ gq.weight_matrix(g, hid, n_in, typ).T) * (xf @ gq.weight_matrix(u, hid, n_in, typ).T)
+  else:
+    raw = synth.BLOCK_MAKERS[typ](n_out, n_in, rng)
+    pw = quant.repack(raw, n_out, n_in, typ)
+    bias = rng.standard_normal(n_out).astype(np.float16) if epi == "bias" else None
+    res = rng.standard_normal((m, n_out)).astype(np.float32) if epi == "res" else None
+    db = DeviceBuffer.from_numpy(bias) if bias is not None else None
+    y = DeviceBuffer.from_numpy(res) if res is not None else DeviceBuffer.empty((m, n_out), np.float32)
+    quant.qgemv_rows(pw.buf.ptr, typ, n_out, n_in, dx, y, m, ws, x_dtype=xdt, bias=db, residual=y if res is not None else None)
+    ref = xf @ gq.weight_matrix(raw, n_out, n_in, typ).T + (bias.astype(np.float32) if bias is not None else 0.0) + (res if res is not None else 0.0)
+  got = y.numpy()
+  assert np.abs(got - ref).max() <= 5e-4 * max(1.0, np.abs(ref).max())
+  if epi == "lin":
+    y2 = DeviceBuffer.empty((m, n_out), np.float32)
+    quant.qgemv_rows(pw.buf.ptr, typ, n_out, n_in, dx, y2, m, ws, x_dtype=xdt)
+    np.testing.assert_array_equal(got.view(np.uint32), y2.numpy().view(np.uint32))
+  from tinygrad_b200 import runtime
+  assert runtime.device_status() == 0

@@ -4,7 +4,7 @@ import os, pathlib, shutil, subprocess, sys
 PKG = pathlib.Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libb200q.so"
-SOURCES = ["api.cu", "quant_pack.cu", "gemv.cu", "decode.cu", "decode_step.cu", "mxfp8.cu", "mxfp8_gemm.cu", "tc_gemm.cu", "dense.cu", "prefill.cu", "tg_kernels.cu", "peer.cu", "ep.cu", "fp8.cu"]
+SOURCES = ["api.cu", "quant_pack.cu", "gemv.cu", "decode.cu", "decode_step.cu", "mxfp8.cu", "mxfp8_gemm.cu", "tc_gemm.cu", "dense.cu", "prefill.cu", "tg_kernels.cu", "peer.cu", "ep.cu", "fp8.cu", "gemv_rows.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
               "-Xcompiler", "-fPIC", "-cudart", "shared"]
 

@@ -1,0 +1,332 @@
+// Weight-dequant-fused linear for a FEW activation rows (batched decode: up to 8 sequences per pass), on the int8 tensor cores.
+//
+// Replaces `Linear.__call__` on a GGUF weight when the model runs B sequences in lock-step (tokens [B, 1], tinygrad/llm/model.py:358-367).
+// The one-row GEMV (gemv.cu) spends one MMA column per (quant block, digit); here the 8 MMA columns are 8 activation ROWS: for every
+// quant block of a 16 x 128 weight tile one m16n8k32 MMA per activation digit (high / low 7 bits of a 15-bit integer) yields the exact
+// integer dot products of 16 weight rows with 8 activation rows, which are scaled by (activation scale x fp16 weight scale) and added
+// up in fp32 -- the weights are streamed ONCE for all 8 rows.  A weight tile keeps (row, block) pairs per lane, an MMA wants one
+// block across the quad's lanes: a 4 x 4 word transpose inside each quad (three shuffles) bridges the two.
+//
+// Pre-pass (rows_record_kernel): the activation rows are quantised once (per block of 32: fp32 scale, 15-bit integers split in two int8
+// digits) into the B-operand order of the MMA, per K chunk of 32 column groups.  Main kernel: grid (CTAs over row tiles, K chunks);
+// a CTA brings its chunk's record into shared memory by bulk copies, then streams its row tiles' chunk of weights through a ring of
+// bulk-copied stages (one stage = one tile's chunk), 16 consumer warps, 2 column groups per warp and stage; partial sums go to a
+// workspace [chunk][row][n_out] and a last kernel adds the chunks in a fixed order and applies bias / residual / SwiGLU (no
+// floating-point atomics: bit-reproducible).  Every mbarrier wait is bounded (status word on expiry, see gemv.cu).
+#include "common.cuh"
+#include "qgemv_core.cuh"
+
+namespace {
+
+constexpr int R_WARPS = 16, R_THREADS = R_WARPS * 32 + 32;      // consumers + the producer warp
+constexpr int R_CG = 32;                                        // column groups (of 128 inputs) per K chunk = per ring stage
+__host__ __device__ constexpr int rows_ns(int qtype) { return qtype == B200Q_Q4_0 ? 3 : 2; }      // ring depth (a stage is 36 KB of Q4_0, 68 KB of Q8_0)
+constexpr int R_TOK = 8;                                        // activation rows per pass = MMA columns
+constexpr int REC_GROUP = 32 * 64;                              // record bytes per column group: 32 lanes x 16 words
+constexpr int SC_GROUP = R_TOK * 4 * 8;                         // scale bytes per column group: [row][block]{scale, offset}
+
+struct RowsParams {
+  const uint8_t* w; const unsigned char* record; float* part;
+  int m, n_out, kgroups, n_row_tiles, n_chunks;
+};
+
+// ---- pre-pass: x [m, n_in] -> per chunk c and group j:  words [c][j][lane = 4 * row + t][b * 4 + {hi0, hi1, lo0, lo1}]  (row < 8: zero rows
+// past m), hi0 / lo0 = the digits of elements 4t..4t+3 of block b, hi1 / lo1 = of elements 16+4t..16+4t+3 (the k order of m16n8k32's B
+// fragment); then  float2 [c][j][row][b] = {scale, 8 * scale * sum(q)}  (the second removes Q4_0's offset of 8).  One warp per (row, block).
+template <typename T>
+__global__ void __launch_bounds__(256) rows_record_kernel(const T* __restrict__ x, int m, int n_in, int kgroups, unsigned char* __restrict__ record) {
+  const int lane = threadIdx.x & 31, wid = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int total = kgroups * 4 * R_TOK;                         // (group, block, row) triples
+  if (wid >= total) return;
+  const int row = wid % R_TOK, blk = (wid / R_TOK) % 4, j = wid / (R_TOK * 4);
+  const int k = j * GROUP_ELEMS + blk * 32 + lane;
+  float v = 0.f;
+  if (row < m && k < n_in) v = sizeof(T) == 2 ? __half2float(reinterpret_cast<const __half*>(x)[(size_t)row * n_in + k]) : reinterpret_cast<const float*>(x)[(size_t)row * n_in + k];
+  const float amax = warp_max(fabsf(v));
+  const bool live = amax > 0.f && amax < INFINITY;
+  const float inv = live ? 16256.f / amax : 0.f, s = live ? amax / 16256.f : 0.f;
+  const int q = __float2int_rn(v * inv);
+  int qsum = q;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
+  const int h = (q + 64) >> 7;
+  const uint32_t hb = h & 0xFF, lb = (q - (h << 7)) & 0xFF;
+  const uint32_t hiw = hb | (__shfl_down_sync(0xffffffffu, hb, 1) << 8) | (__shfl_down_sync(0xffffffffu, hb, 2) << 16) | (__shfl_down_sync(0xffffffffu, hb, 3) << 24);
+  const uint32_t low = lb | (__shfl_down_sync(0xffffffffu, lb, 1) << 8) | (__shfl_down_sync(0xffffffffu, lb, 2) << 16) | (__shfl_down_sync(0xffffffffu, lb, 3) << 24);
+  const int chunk = j / R_CG, jj = j % R_CG;
+  const int cg = min(R_CG, kgroups - chunk * R_CG);              // groups of this chunk
+  unsigned char* base = record + (size_t)chunk * R_CG * (REC_GROUP + SC_GROUP);     // chunk c: its words, then its scales
+  if ((lane & 3) == 0) {
+    const int e4 = lane >> 2, t = e4 & 3, half = e4 >> 2;        // elements 4 e4 .. 4 e4 + 3
+    uint32_t* wp = reinterpret_cast<uint32_t*>(base + (size_t)jj * REC_GROUP) + (row * 4 + t) * 16 + blk * 4;
+    wp[half] = hiw; wp[2 + half] = low;
+  }
+  if (lane == 0) {
+    float2* sp = reinterpret_cast<float2*>(base + (size_t)cg * REC_GROUP + (size_t)jj * SC_GROUP) + row * 4 + blk;
+    *sp = make_float2(s, 8.f * s * (float)qsum);
+  }
+}
+
+// words t of the four lanes of a quad: lane t ends up with word t of lane 0, 1, 2, 3 (out.x .. out.w)
+__device__ __forceinline__ uint4 quad_transpose(const uint4 r, int t) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+  uint32_t got[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    // the lane that reads from me in round j is lane t ^ j and wants its own word index, t ^ j
+    const int want = t ^ j;
+    const uint32_t send = want == 0 ? w[0] : want == 1 ? w[1] : want == 2 ? w[2] : w[3];
+    got[j] = j == 0 ? send : __shfl_xor_sync(0xffffffffu, send, j);      // = word t of lane t ^ j
+  }
+  // got[j] came from lane b = t ^ j: out[b] = got[t ^ b]
+  uint4 o;
+  o.x = (t ^ 0) == 0 ? got[0] : (t ^ 0) == 1 ? got[1] : (t ^ 0) == 2 ? got[2] : got[3];
+  o.y = (t ^ 1) == 0 ? got[0] : (t ^ 1) == 1 ? got[1] : (t ^ 1) == 2 ? got[2] : got[3];
+  o.z = (t ^ 2) == 0 ? got[0] : (t ^ 2) == 1 ? got[1] : (t ^ 2) == 2 ? got[2] : got[3];
+  o.w = (t ^ 3) == 0 ? got[0] : (t ^ 3) == 1 ? got[1] : (t ^ 3) == 2 ? got[2] : got[3];
+  return o;
+}
+
+__device__ __forceinline__ void imma_u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void imma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// One weight tile (16 rows x 4 blocks) against 8 activation rows.  xw: this lane's 16 record words of the column group, xs: the
+// {scale, offset} pairs of the lane's two activation rows (2t, 2t + 1) for the 4 blocks.  acc: rows g / g + 8 x activation rows 2t / 2t + 1.
+template <int QT>
+__device__ __forceinline__ void tile_mac_rows(const uint8_t* tile, int lane, const uint4 (&xw)[4], const float4 (&xs)[4], float (&acc)[4]) {
+  const int g = lane >> 2, t = lane & 3;
+  const uint4* tp = reinterpret_cast<const uint4*>(tile);
+  const uint32_t M = 0x0F0F0F0Fu;
+  uint32_t a[4][4];      // [block][a0..a3]
+  if (QT == B200Q_Q4_0) {
+    const uint4 w0 = quad_transpose(tp[lane], t), w1 = quad_transpose(tp[32 + lane], t);      // rows g, g + 8: word t of blocks 0..3
+    const uint32_t r0[4] = {w0.x, w0.y, w0.z, w0.w}, r1[4] = {w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int b = 0; b < 4; b++) { a[b][0] = r0[b] & M; a[b][1] = r1[b] & M; a[b][2] = (r0[b] >> 4) & M; a[b][3] = (r1[b] >> 4) & M; }
+  } else {
+    const uint4 w0 = quad_transpose(tp[lane], t), w2 = quad_transpose(tp[32 + lane], t);      // row g: elements 0..15, 16..31 of the lane's block
+    const uint4 w1 = quad_transpose(tp[64 + lane], t), w3 = quad_transpose(tp[96 + lane], t); // row g + 8
+    const uint32_t r0[4] = {w0.x, w0.y, w0.z, w0.w}, r2[4] = {w2.x, w2.y, w2.z, w2.w}, r1[4] = {w1.x, w1.y, w1.z, w1.w}, r3[4] = {w3.x, w3.y, w3.z, w3.w};
+#pragma unroll
+    for (int b = 0; b < 4; b++) { a[b][0] = r0[b]; a[b][1] = r1[b]; a[b][2] = r2[b]; a[b][3] = r3[b]; }
+  }
+  // fp16 weight scales: entry 2g + p holds {block 2p row g, block 2p+1 row g, block 2p row g+8, block 2p+1 row g+8}
+  const uint2* sp = reinterpret_cast<const uint2*>(tile + (QT == B200Q_Q4_0 ? 1024 : 2048));
+  const uint2 s01 = sp[2 * g], s23 = sp[2 * g + 1];
+  const float2 d01a = __half22float2(*reinterpret_cast<const __half2*>(&s01.x)), d01b = __half22float2(*reinterpret_cast<const __half2*>(&s01.y));
+  const float2 d23a = __half22float2(*reinterpret_cast<const __half2*>(&s23.x)), d23b = __half22float2(*reinterpret_cast<const __half2*>(&s23.y));
+  const float da[4] = {d01a.x, d01a.y, d23a.x, d23a.y}, db[4] = {d01b.x, d01b.y, d23b.x, d23b.y};      // rows g and g + 8
+  const uint32_t xwv[16] = {xw[0].x, xw[0].y, xw[0].z, xw[0].w, xw[1].x, xw[1].y, xw[1].z, xw[1].w, xw[2].x, xw[2].y, xw[2].z, xw[2].w,
+                            xw[3].x, xw[3].y, xw[3].z, xw[3].w};
+  // xs: [0] = row 2t blocks 0,1 {s, o, s, o}; [1] = row 2t blocks 2,3; [2], [3] = the same for row 2t + 1
+  const float se[4] = {xs[0].x, xs[0].z, xs[1].x, xs[1].z}, oe[4] = {xs[0].y, xs[0].w, xs[1].y, xs[1].w};
+  const float so[4] = {xs[2].x, xs[2].z, xs[3].x, xs[3].z}, oo[4] = {xs[2].y, xs[2].w, xs[3].y, xs[3].w};
+#pragma unroll
+  for (int b = 0; b < 4; b++) {
+    int ch[4], cl[4];
+    if (QT == B200Q_Q4_0) {
+      imma_u8(ch, a[b][0], a[b][1], a[b][2], a[b][3], xwv[b * 4 + 0], xwv[b * 4 + 1]);
+      imma_u8(cl, a[b][0], a[b][1], a[b][2], a[b][3], xwv[b * 4 + 2], xwv[b * 4 + 3]);
+    } else {
+      imma_s8(ch, a[b][0], a[b][1], a[b][2], a[b][3], xwv[b * 4 + 0], xwv[b * 4 + 1]);
+      imma_s8(cl, a[b][0], a[b][1], a[b][2], a[b][3], xwv[b * 4 + 2], xwv[b * 4 + 3]);
+    }
+    const float oe_b = QT == B200Q_Q4_0 ? oe[b] : 0.f, oo_b = QT == B200Q_Q4_0 ? oo[b] : 0.f;      // only Q4_0 stores value + 8
+    const float v0 = fmaf((float)(ch[0] * 128 + cl[0]), se[b], -oe_b), v1 = fmaf((float)(ch[1] * 128 + cl[1]), so[b], -oo_b);
+    const float v2 = fmaf((float)(ch[2] * 128 + cl[2]), se[b], -oe_b), v3 = fmaf((float)(ch[3] * 128 + cl[3]), so[b], -oo_b);
+    acc[0] = fmaf(v0, da[b], acc[0]); acc[1] = fmaf(v1, da[b], acc[1]);
+    acc[2] = fmaf(v2, db[b], acc[2]); acc[3] = fmaf(v3, db[b], acc[3]);
+  }
+}
+
+__device__ __forceinline__ void rows_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(R_WARPS * 32) : "memory"); }
+
+template <int QT>
+__global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsParams p) {
+  constexpr int TB = tile_bytes(QT), STAGE = R_CG * TB, R_NS = rows_ns(QT);
+  extern __shared__ __align__(128) unsigned char rsm[];
+  unsigned char* ring = rsm;
+  unsigned char* rec = rsm + R_NS * STAGE;                       // words of the chunk's groups, then their scales
+  float* red = reinterpret_cast<float*>(rec + R_CG * (REC_GROUP + SC_GROUP));      // [2][R_WARPS][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red + 2 * R_WARPS * 128);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 2 * R_NS + 1);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + R_NS), rbar = smem_u32(bars + 2 * R_NS);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int chunk = blockIdx.y, cg = min(R_CG, p.kgroups - chunk * R_CG);
+  if (tid == 0) {
+    for (int s = 0; s < R_NS; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, R_WARPS); }
+    mbar_init(rbar, 1);
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+  if (warp == R_WARPS) {
+    // ------------------------------ producer: weights do not depend on the previous kernel, the record does
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true, rec_issued = false;
+      auto fetch_record = [&]() {
+        pdl_wait();
+        const uint32_t bytes = (uint32_t)cg * (REC_GROUP + SC_GROUP);
+        const unsigned char* src = p.record + (size_t)chunk * R_CG * (REC_GROUP + SC_GROUP);
+        mbar_expect_tx(rbar, bytes);
+        for (uint32_t o = 0; o < bytes; o += 8192) bulk_g2s(smem_u32(rec) + o, src + o, min(8192u, bytes - o), rbar);
+        rec_issued = true;
+      };
+      for (int rt = blockIdx.x; rt < p.n_row_tiles && ok; rt += gridDim.x, it++) {
+        const int slot = it % R_NS;
+        if (it == R_NS && !rec_issued) fetch_record();
+        if (!mbar_wait(empty0 + 8 * slot, ((it / R_NS) & 1) ^ 1)) { ok = false; break; }
+        const uint8_t* src = p.w + ((size_t)rt * p.kgroups + (size_t)chunk * R_CG) * TB;
+        mbar_expect_tx(full0 + 8 * slot, cg * TB);
+        for (int g0 = 0; g0 < cg; g0 += 4) {
+          const int gn = min(4, cg - g0);
+          bulk_g2s(smem_u32(ring + slot * STAGE + g0 * TB), src + (size_t)g0 * TB, gn * TB, full0 + 8 * slot);
+        }
+      }
+      if (!rec_issued) fetch_record();
+      for (int j = max(0, it - R_NS); j < it; j++) mbar_wait(full0 + 8 * (j % R_NS), (j / R_NS) & 1);      // nothing may still be landing at exit
+      mbar_wait(rbar, 0);
+    } else {
+      pdl_wait();
+    }
+    return;
+  }
+  // -------------------------------- consumers
+  pdl_wait();
+  const int g = lane >> 2, t = lane & 3;
+  if (!mbar_wait(rbar, 0)) *s_abort = 1;
+  rows_bar_sync();
+  bool live = *s_abort == 0;
+  const uint4* recw = reinterpret_cast<const uint4*>(rec);
+  const float4* recs = reinterpret_cast<const float4*>(rec + (size_t)cg * REC_GROUP);
+  int it = 0, par = 0;
+  for (int rt = blockIdx.x; rt < p.n_row_tiles && live; rt += gridDim.x, it++, par ^= 1) {
+    const int slot = it % R_NS;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (!mbar_wait(full0 + 8 * slot, (it / R_NS) & 1)) { *s_abort = 1; }
+    else {
+      const uint8_t* stage = ring + slot * STAGE;
+#pragma unroll
+      for (int u = 0; u < R_CG / R_WARPS; u++) {
+        const int jj = warp + u * R_WARPS;
+        if (jj < cg) {
+          uint4 xw[4];
+          float4 xs[4];
+#pragma unroll
+          for (int i = 0; i < 4; i++) xw[i] = recw[(jj * 32 + lane) * 4 + i];
+          // scales of activation rows 2t and 2t + 1: [row][block]{s, o} = 8 floats per row
+          const float4* sc = recs + (size_t)jj * (SC_GROUP / 16);
+          xs[0] = sc[(2 * t) * 2]; xs[1] = sc[(2 * t) * 2 + 1]; xs[2] = sc[(2 * t + 1) * 2]; xs[3] = sc[(2 * t + 1) * 2 + 1];
+          tile_mac_rows<QT>(stage + jj * TB, lane, xw, xs, acc);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * slot);
+    }
+    // cross-warp sum in a fixed order: rb[warp][lane * 4 + i]
+    float* rb = red + par * R_WARPS * 128;
+    *reinterpret_cast<float4*>(rb + warp * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    rows_bar_sync();
+    live = *s_abort == 0;
+    if (!live) break;
+    if (warp < 4) {
+      const int o = warp * 32 + lane;                            // output o of the tile: lane' = o / 4, i = o % 4
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < R_WARPS; w++) v += rb[w * 128 + o];
+      const int ln = o >> 2, i = o & 3, row = rt * 16 + (ln >> 2) + (i >> 1) * 8, tok = 2 * (ln & 3) + (i & 1);
+      if (row < p.n_out && tok < p.m) p.part[((size_t)chunk * p.m + tok) * p.n_out + row] = v;
+    }
+  }
+}
+
+// y = sum over K chunks (fixed order) + bias + residual, or the SwiGLU product of interleaved gate / up columns
+__global__ void rows_reduce_kernel(const float* __restrict__ part, int n_chunks, int m, int n_out, const __half* __restrict__ bias,
+                                   const void* __restrict__ residual, void* __restrict__ y, int y_f16, int silu_mul) {
+  pdl_wait();
+  const int n_y = silu_mul ? n_out / 2 : n_out;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)m * n_y) return;
+  const int row = (int)(i / n_y), c = (int)(i - (size_t)row * n_y);
+  auto total = [&](int col) { float s = 0.f; for (int z = 0; z < n_chunks; z++) s += part[((size_t)z * m + row) * n_out + col]; return s; };
+  float o;
+  if (silu_mul) {
+    const int col = (c >> 3) * 16 + (c & 7);                     // 8 gate rows then 8 up rows per 16-row tile
+    const float gte = total(col), up = total(col + 8);
+    o = (gte / (1.f + expf(-gte))) * up;
+  } else {
+    o = total(c);
+    if (bias) o += __half2float(bias[c]);
+    if (residual) o += y_f16 ? __half2float(reinterpret_cast<const __half*>(residual)[i]) : reinterpret_cast<const float*>(residual)[i];
+  }
+  if (y_f16) reinterpret_cast<__half*>(y)[i] = __float2half_rn(o); else reinterpret_cast<float*>(y)[i] = o;
+}
+
+size_t rows_smem(int qtype) {
+  return (size_t)rows_ns(qtype) * R_CG * tile_bytes(qtype) + (size_t)R_CG * (REC_GROUP + SC_GROUP) + 2 * R_WARPS * 128 * sizeof(float) + (2 * rows_ns(qtype) + 1) * sizeof(uint64_t) + 16;
+}
+size_t rows_record_bytes(int kgroups) { return (size_t)ceil_div(kgroups, R_CG) * R_CG * (REC_GROUP + SC_GROUP); }
+
+}  // namespace
+
+extern "C" size_t b200q_qgemv_rows_workspace_bytes(int m, int n_out, int n_in) {
+  if (m <= 0 || n_out <= 0 || n_in <= 0) return 0;
+  const int kgroups = ceil_div(n_in, GROUP_ELEMS), passes = ceil_div(m, R_TOK);
+  return rows_record_bytes(kgroups) + (size_t)ceil_div(kgroups, R_CG) * (size_t)(passes > 1 ? R_TOK : m) * n_out * sizeof(float);
+}
+
+extern "C" int b200q_qgemv_rows(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue,
+                                void* y, int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!w_packed || !x || !y || !workspace || m <= 0 || n_out <= 0 || n_in <= 0) return B200Q_ERR_BAD_ARG;
+  if (qtype == B200Q_Q6_K) return B200Q_ERR_UNSUPPORTED;
+  if (qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
+  if ((x_dtype != B200Q_F32 && x_dtype != B200Q_F16) || (y_dtype != B200Q_F32 && y_dtype != B200Q_F16)) return B200Q_ERR_BAD_ARG;
+  if (epilogue != B200Q_EPI_LINEAR && epilogue != B200Q_EPI_SILU_MUL) return B200Q_ERR_BAD_ARG;
+  if (epilogue == B200Q_EPI_SILU_MUL && (bias_f16 || residual || n_out % 16)) return B200Q_ERR_BAD_ARG;
+  if (n_in % 32) return B200Q_ERR_BAD_SHAPE;
+  if (((uintptr_t)w_packed | (uintptr_t)x | (uintptr_t)workspace) & 15) return B200Q_ERR_MISALIGNED;
+  if (workspace_bytes < b200q_qgemv_rows_workspace_bytes(m, n_out, n_in)) return B200Q_ERR_TOO_LARGE;
+  const int n_sm = b200q_sm_count(), dev = b200q_current_device();
+  if (n_sm <= 0 || dev < 0) return B200Q_ERR_CUDA;
+  static PerDeviceFlag attr;
+  if (!attr.test(dev)) {
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(qgemv_rows_kernel<B200Q_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rows_smem(B200Q_Q4_0)));
+    B200Q_CHECK_CUDA(cudaFuncSetAttribute(qgemv_rows_kernel<B200Q_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rows_smem(B200Q_Q8_0)));
+    attr.set(dev);
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const int kgroups = ceil_div(n_in, GROUP_ELEMS), n_chunks = ceil_div(kgroups, R_CG), n_row_tiles = ceil_div(n_out, TILE_ROWS);
+  unsigned char* record = (unsigned char*)workspace;
+  float* part = reinterpret_cast<float*>(record + rows_record_bytes(kgroups));
+  const size_t esz = x_dtype == B200Q_F16 ? 2 : 4, ysz = y_dtype == B200Q_F16 ? 2 : 4;
+  const int n_y = epilogue == B200Q_EPI_SILU_MUL ? n_out / 2 : n_out;
+  for (int r0 = 0; r0 < m; r0 += R_TOK) {                        // 8 activation rows per pass over the weights
+    const int mm = min(R_TOK, m - r0);
+    const unsigned char* xr = (const unsigned char*)x + (size_t)r0 * n_in * esz;
+    const int rec_warps = kgroups * 4 * R_TOK;
+    if (x_dtype == B200Q_F16) rows_record_kernel<__half><<<ceil_div(rec_warps, 8), 256, 0, st>>>((const __half*)xr, mm, n_in, kgroups, record);
+    else rows_record_kernel<float><<<ceil_div(rec_warps, 8), 256, 0, st>>>((const float*)xr, mm, n_in, kgroups, record);
+    RowsParams p;
+    p.w = (const uint8_t*)w_packed; p.record = record; p.part = part; p.m = mm; p.n_out = n_out; p.kgroups = kgroups; p.n_row_tiles = n_row_tiles;
+    p.n_chunks = n_chunks;
+    int gx = n_sm / n_chunks; if (gx < 1) gx = 1; if (gx > n_row_tiles) gx = n_row_tiles;
+    const dim3 grid(gx, n_chunks);
+    const size_t smem = rows_smem(qtype);
+    if (qtype == B200Q_Q4_0) B200Q_CHECK_CUDA(launch_k(qgemv_rows_kernel<B200Q_Q4_0>, grid, dim3(R_THREADS), smem, st, true, p));
+    else B200Q_CHECK_CUDA(launch_k(qgemv_rows_kernel<B200Q_Q8_0>, grid, dim3(R_THREADS), smem, st, true, p));
+    const size_t total = (size_t)mm * n_y;
+    const unsigned char* res = residual ? (const unsigned char*)residual + (size_t)r0 * n_out * ysz : nullptr;
+    B200Q_CHECK_CUDA(launch_k(rows_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), (size_t)0, st, true, (const float*)part, n_chunks, mm, n_out,
+                              (const __half*)bias_f16, (const void*)res, (void*)((unsigned char*)y + (size_t)r0 * n_y * ysz), (int)(y_dtype == B200Q_F16),
+                              (int)(epilogue == B200Q_EPI_SILU_MUL)));
+  }
+  return B200Q_OK;
+}

@@ -718,29 +718,21 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_pipe_kernel(const QGem
         c0 = q8_core(w.q8.x, w.q8.y, w.d2, lo0); c1 = q8_core(w.q8.z, w.q8.w, w.d2, lo1);
         k0 = b * 32 + 16 * h; k1 = k0 + 8;
       }
-#ifndef B200Q_PX_NOSTORE
       *reinterpret_cast<uint4*>(sBh + tile_off(r, k0, BN)) = c0;
       *reinterpret_cast<uint4*>(sBh + tile_off(r, k1, BN)) = c1;
       if (!p.x_f16) {
         *reinterpret_cast<uint4*>(sBl + tile_off(r, k0, BN)) = lo0;
         *reinterpret_cast<uint4*>(sBl + tile_off(r, k1, BN)) = lo1;
       }
-#else
-      if (c0.x == 0x12345678u && lo1.y == 0x9abcdef0u) *reinterpret_cast<uint4*>(sBh + tile_off(r, k0, BN)) = c1;
-      (void)lo0;
-#endif
     }
     load_regs(step + 2, w);
-#ifndef B200Q_PX_NOFENCE
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
     __syncthreads();
     if (tid == 0) {
       const int slot = step % P_A_SLOTS;
       if (wait_bar(s32(&full[slot]), (step / P_A_SLOTS) & 1)) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t sA = s32(psm + slot * 2 * P_HALF), sA2 = sA + P_HALF, sB = s32(sBh), sB2 = sB + P_HALF;
-#ifndef B200Q_PX_NOMMA
 #pragma unroll
         for (int kk = 0; kk < P_BK / 16; kk++) {
           const uint64_t da = make_desc(sA + kk * 2 * (BM * 16), BM * 16, 128), db = make_desc(sB + kk * 2 * (BN * 16), BN * 16, 128);
@@ -755,9 +747,6 @@ __global__ void __launch_bounds__(QGEMM_THREADS) tc_qgemm_pipe_kernel(const QGem
                          ::"r"(taddr), "l"(da), "l"(db2), "r"(idesc), "r"(1u) : "memory");
           }
         }
-#else
-        (void)sA2; (void)sB2; (void)sB; (void)sA;
-#endif
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&empty[step & 1])) : "memory");
         if (step == n_steps - 1) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&done)) : "memory");
       }

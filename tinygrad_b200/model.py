@@ -402,7 +402,12 @@ class Transformer:
     kvdt = F16 if c.kv_dtype == "float16" else F32
     qkv_rows = self.q_dim + 2 * self.kv_dim
     head_q = not isinstance(self.output, quant.DenseWeight)
-    if B <= 32:      # the weight-streaming GEMM shape (swapped operands, split K); its partial sums go through one workspace
+    if B <= 16 and quant.FEW_ROW_FUSED:      # 8 rows per pass on the int8 tensor cores at the one-row GEMV's arithmetic (weights streamed once per pass)
+      if self._skinny_ws is None:
+        shapes = [(qkv_rows, c.dim), (c.dim, self.q_dim), (2 * c.hidden_dim, c.dim), (c.dim, c.hidden_dim)] + ([(c.vocab_size, c.dim)] if head_q else [])
+        self._skinny_ws = DeviceBuffer(max(quant.qgemv_rows_workspace_bytes(B, o, i) for o, i in shapes))
+      def gemm(w, qt, n_out, n_in, x, y, **kw): quant.qgemv_rows(w, qt, n_out, n_in, x, y, B, self._skinny_ws, x_dtype=F32, y_dtype=F32, stream=s, **kw)
+    elif B <= 32:    # the weight-streaming GEMM shape (swapped operands, split K); its partial sums go through one workspace
       if self._skinny_ws is None:
         shapes = [(qkv_rows, c.dim), (c.dim, self.q_dim), (2 * c.hidden_dim, c.dim), (c.dim, c.hidden_dim)] + ([(c.vocab_size, c.dim)] if head_q else [])
         self._skinny_ws = DeviceBuffer(max(quant.qgemm_skinny_workspace_bytes(B, o, i) for o, i in shapes))

@@ -106,6 +106,20 @@ def qgemm(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int, x_dtype=F
                         stream_ptr(stream)))
 
 
+FEW_ROW_FUSED = os.environ.get("B200Q_FEW_ROW_FUSED", "0") == "1"      # batched decode with at most 16 rows: the int8-MMA few-row kernel
+
+
+def qgemv_rows_workspace_bytes(m: int, n_out: int, n_in: int) -> int:
+  return int(_lib.load().b200q_qgemv_rows_workspace_bytes(m, n_out, n_in))
+
+
+def qgemv_rows(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int, workspace: DeviceBuffer, x_dtype=F32, y_dtype=F32, bias=None, residual=None,
+               epilogue: int = EPI_LINEAR, stream=None) -> None:
+  """The same Linear for a few activation rows (batched decode) on the int8 tensor cores: weights streamed once per 8 rows."""
+  check(_lib.load().b200q_qgemv_rows(qtype, w_ptr, ptr_of(x), x_dtype, ptr_of(bias), ptr_of(residual), epilogue, ptr_of(y), y_dtype, m, n_out, n_in,
+                                     workspace.ptr, workspace.nbytes, stream_ptr(stream)))
+
+
 def qgemm_skinny_workspace_bytes(m: int, n_out: int, n_in: int) -> int:
   return int(_lib.load().b200q_qgemm_skinny_workspace_bytes(m, n_out, n_in))
 
