@@ -202,7 +202,9 @@ def test_batched_decode_matches_oracle_per_sequence(typ, B):
   sd = synth.dense_model_raw(cfg, typ, seed=19, embd_std=0.3, scale_std=0.02 if typ == 2 else 0.0015)
   shapes = {n: (o, i) for n, o, i in synth.linear_names(cfg)}
   w = {k: (gq.weight_matrix(v, *shapes[k[:-len(".weight")]], typ) if v.dtype == np.uint8 else v) for k, v in sd.items()}
-  rng = np.random.default_rng(4)
+  # prompts whose greedy choices are decided by a margin: with this seed the top-2 logit gap of every step is >= 3.7e-3 of the logit scale
+  # (seed 4 has a step with a gap of 3e-6, which no arithmetic other than the oracle's own can be expected to reproduce)
+  rng = np.random.default_rng(6)
   prompts = [[int(t) for t in rng.integers(0, 2000, 24)] for _ in range(B)]
   want = [llm.Transformer(llm.Config(**kw), w).generate(p, 10) for p in prompts]
   m = Transformer(cfg, sd, ggml_type=typ, batch=B)
@@ -256,7 +258,7 @@ def test_skinny_split_k_gemm(tag, m, n_out, n_in, x_dtype, epi):
                                                         ("q4_0", 5, 200, 96, np.float32, "lin"), ("q8_0", 17, 48, 1536, np.float32, "silu"),
                                                         ("q4_0", 1, 14336 * 2, 4096, np.float32, "silu"), ("q4_0", 3, 4096, 14336, np.float16, "lin"),
                                                         ("q8_0", 32, 3584, 3584, np.float32, "res")])
-def _pending_test_few_row_fused_gemv(tag, m, n_out, n_in, x_dtype, epi):
+def test_few_row_fused_gemv(tag, m, n_out, n_in, x_dtype, epi):
   """Few activation rows on the int8 tensor cores (8 rows per pass over the weights, K chunks summed in a fixed order) against the fp32
   product: the one-row GEMV's arithmetic (15-bit activation integers, exact sums inside a block), so its error bound; bit-reproducible."""
   from tinygrad_b200 import quant, _lib

@@ -18,9 +18,21 @@
 
 namespace {
 
-constexpr int R_WARPS = 16, R_THREADS = R_WARPS * 32 + 32;      // consumers + the producer warp
-constexpr int R_CG = 32;                                        // column groups (of 128 inputs) per K chunk = per ring stage
-__host__ __device__ constexpr int rows_ns(int qtype) { return qtype == B200Q_Q4_0 ? 3 : 2; }      // ring depth (a stage is 36 KB of Q4_0, 68 KB of Q8_0)
+#ifndef B200Q_R_WARPS
+#define B200Q_R_WARPS 16
+#endif
+#ifndef B200Q_R_CG
+#define B200Q_R_CG 32
+#endif
+#ifndef B200Q_R_NS4
+#define B200Q_R_NS4 3
+#endif
+#ifndef B200Q_R_NS8
+#define B200Q_R_NS8 2
+#endif
+constexpr int R_WARPS = B200Q_R_WARPS, R_THREADS = R_WARPS * 32 + 32;      // consumers + the producer warp
+constexpr int R_CG = B200Q_R_CG;                                // column groups (of 128 inputs) per K chunk = per ring stage
+__host__ __device__ constexpr int rows_ns(int qtype) { return qtype == B200Q_Q4_0 ? B200Q_R_NS4 : B200Q_R_NS8; }      // ring depth (a stage is 36 KB of Q4_0, 68 KB of Q8_0)
 constexpr int R_TOK = 8;                                        // activation rows per pass = MMA columns
 constexpr int REC_GROUP = 32 * 64;                              // record bytes per column group: 32 lanes x 16 words
 constexpr int SC_GROUP = R_TOK * 4 * 8;                         // scale bytes per column group: [row][block]{scale, offset}
@@ -215,7 +227,7 @@ __global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsPara
     else {
       const uint8_t* stage = ring + slot * STAGE;
 #pragma unroll
-      for (int u = 0; u < R_CG / R_WARPS; u++) {
+      for (int u = 0; u < (R_CG + R_WARPS - 1) / R_WARPS; u++) {
         const int jj = warp + u * R_WARPS;
         if (jj < cg) {
           uint4 xw[4];

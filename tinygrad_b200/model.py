@@ -402,7 +402,7 @@ class Transformer:
     kvdt = F16 if c.kv_dtype == "float16" else F32
     qkv_rows = self.q_dim + 2 * self.kv_dim
     head_q = not isinstance(self.output, quant.DenseWeight)
-    if B <= 16 and quant.FEW_ROW_FUSED:      # 8 rows per pass on the int8 tensor cores at the one-row GEMV's arithmetic (weights streamed once per pass)
+    if B <= 8 and quant.FEW_ROW_FUSED:       # 8 rows per pass on the int8 tensor cores at the one-row GEMV's arithmetic (weights streamed once per pass)
       if self._skinny_ws is None:
         shapes = [(qkv_rows, c.dim), (c.dim, self.q_dim), (2 * c.hidden_dim, c.dim), (c.dim, c.hidden_dim)] + ([(c.vocab_size, c.dim)] if head_q else [])
         self._skinny_ws = DeviceBuffer(max(quant.qgemv_rows_workspace_bytes(B, o, i) for o, i in shapes))

@@ -106,7 +106,7 @@ def qgemm(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int, x_dtype=F
                         stream_ptr(stream)))
 
 
-FEW_ROW_FUSED = os.environ.get("B200Q_FEW_ROW_FUSED", "0") == "1"      # batched decode with at most 16 rows: the int8-MMA few-row kernel
+FEW_ROW_FUSED = os.environ.get("B200Q_FEW_ROW_FUSED", "1") == "1"      # batched decode with at most 8 rows: the int8-MMA few-row kernel
 
 
 def qgemv_rows_workspace_bytes(m: int, n_out: int, n_in: int) -> int:
