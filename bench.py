@@ -8,6 +8,7 @@ synthetic data of the configuration's shapes and distributions (no checkpoint or
 torch.distributed.run) every rank decodes its own sequence on its own GPU for the headline metric (the model fits one GPU:
 replicas, no data-path collective); the sharded configurations run over all N ranks and are reported in their own records:
   "moe"     configs[3], one OLMoE-shaped MXFP8 MoE layer over 4096 tokens on one GPU (N == 1)
+  "batched" configs[2] shape, Qwen2-7B-shaped Q8_0 decode with 8 sequences in lock-step on one GPU (N == 1)
   "ep_moe"  the same layer expert-parallel over the N ranks (N > 1)
   "tp70b"   configs[4], Llama-3-70B-shaped Q4_0 decode at batch 1: unsharded on one GPU at N == 1, tensor-parallel over N ranks else
 Prints ONE JSON line on rank 0.
@@ -180,6 +181,32 @@ def moe_record(reps: int = 30) -> dict:
           "contraction": "tcgen05.mma kind::mxf8f6f4.block_scale, TMEM accumulators", "wait_status": status}
 
 
+def batched_record(B: int = 8, steps: int = 32) -> dict:
+  """configs[2] shape (Qwen2-7B, Q8_0) decoding B sequences in lock-step after 128-token prompts: every Linear streams its weights once per step
+  for all B rows (few-row fused GEMV on the int8 tensor cores), attention and arg-max per sequence; one CUDA graph per step."""
+  from tinygrad_b200 import runtime, synth
+  from tinygrad_b200.model import Transformer, TransformerConfig
+  cfg = TransformerConfig(num_blocks=28, dim=3584, hidden_dim=18944, n_heads=28, n_kv_heads=4, norm_eps=1e-6, vocab_size=152064, head_dim=128,
+                          rope_theta=1000000.0, rope_dim=128, v_head_dim=128, max_context=1024, kv_dtype="float16", qkv_bias=True)
+  model = Transformer(cfg, synth.LazyDenseState(cfg, synth.Q8_0, seed=0, distinct_blocks=4), ggml_type=synth.Q8_0, batch=B)
+  rng = np.random.default_rng(5)
+  prompts = [[int(t) for t in rng.integers(0, cfg.vocab_size, 128)] for _ in range(B)]
+  gen = model.generate_batch(prompts)
+  for _ in range(4): next(gen)
+  e0, e1 = runtime.Event(), runtime.Event()
+  model.stream.synchronize()
+  e0.record(model.stream)
+  for _ in range(steps): model.decode_batch_step()
+  e1.record(model.stream); model.stream.synchronize()
+  ms = e0.elapsed_ms(e1) / steps
+  pk = measured_peaks()
+  kv = 2 * cfg.n_kv_heads * cfg.head_dim * 2 * cfg.num_blocks * (128 + 4 + steps // 2) * B
+  gbs = (model.weight_bytes + kv) / ms / 1e6
+  return {"workload": f"configs[2] shape: Qwen2-7B-shaped Q8_0 decode, batch {B} in lock-step, prompt 128 per sequence, greedy", "ms_per_step": round(ms, 3),
+          "tokens_per_s": round(B * 1e3 / ms, 1), "step_hbm_gbs": round(gbs, 1), "step_frac_of_peak": round(gbs / pk["hbm_gbs"], 4),
+          "wait_status": runtime.device_status()}
+
+
 def ep_moe_record(ranks, reps: int = 10) -> dict:
   """configs[3] expert-parallel over all ranks: experts split contiguously, tokens split at the input; device time of the slowest rank.
   Every rank also computes its token shard on one GPU alone and compares bit for bit."""
@@ -269,14 +296,14 @@ def main():
   ap.add_argument("--warmup", type=int, default=8)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--engine", default=None, choices=["step", "chain"], help="one-token engine (default: the whole-step kernel where it takes the model)")
-  ap.add_argument("--only", default="", help="comma list of records to run besides the headline (moe, ep_moe, tp70b); default: all that apply")
+  ap.add_argument("--only", default="", help="comma list of records to run besides the headline (moe, batched, ep_moe, tp70b); default: all that apply")
   ap.add_argument("--skip-cpu-baseline", action="store_true")
-  ap.add_argument("--workload", default="decode", choices=["decode", "moe"], help="moe: only the MoE layer record (short runs for profiling)")
+  ap.add_argument("--workload", default="decode", choices=["decode", "moe", "batch"], help="moe / batch: only that record (short runs for profiling)")
   args = ap.parse_args()
   rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
   if args.impl == "reference": return run_reference(args, rank)
   if args.warmup < 3: args.warmup = 3
-  extras = set(args.only.split(",")) - {""} if args.only else {"moe", "ep_moe", "tp70b"}
+  extras = set(args.only.split(",")) - {""} if args.only else {"moe", "batched", "ep_moe", "tp70b"}
 
   from tinygrad_b200 import build, runtime, synth, _lib
   from tinygrad_b200.model import Transformer
@@ -284,6 +311,10 @@ def main():
   if args.workload == "moe":
     runtime.set_device(local)
     print(json.dumps({"moe": moe_record(reps=max(args.steps, 1))}), flush=True)
+    return
+  if args.workload == "batch":
+    runtime.set_device(local)
+    print(json.dumps({"batched": batched_record(steps=max(min(args.steps, 64), 1))}), flush=True)
     return
   from tinygrad_b200.replicas import Ranks
   ranks = Ranks(backend="nccl")
@@ -382,6 +413,7 @@ def main():
   del model
   # ---- the other configurations of the path, each in its own record
   if world == 1 and "moe" in extras: out["moe"] = moe_record()
+  if world == 1 and "batched" in extras: out["batched"] = batched_record()
   if world > 1 and "ep_moe" in extras: out["ep_moe"] = ep_moe_record(ranks)
   if "tp70b" in extras: out["tp70b"] = tp70b_record(ranks, min(args.steps, 64), args.warmup)
   if rank == 0 and not args.skip_cpu_baseline and world == 1:

@@ -357,12 +357,18 @@ int b200q_qgemm_ws(int qtype, const void* w_packed, const void* x, int x_dtype, 
  * bias / residual / SwiGLU.  Same operands, numerics and epilogue rules as b200q_qgemm. */
 /* The same Linear for a FEW activation rows on the int8 tensor cores (batched decode): the 8 columns of an m16n8k32 MMA are 8 activation
  * rows, so a pass streams the weights once for 8 rows at the one-row GEMV's arithmetic (15-bit activation integers, exact block sums, fp32
- * across blocks); m > 8 takes ceil(m / 8) passes.  Three kinds of launches per pass: quantise the rows into the MMA's operand order, the
- * streaming kernel (partial sums per K chunk of 4096 inputs into the workspace), the fixed-order sum with the epilogue.  Arguments as
+ * across blocks); m > 8 takes ceil(m / 8) passes.  Launches per pass: quantise the rows into the MMA's operand order; the streaming
+ * kernel, which applies the epilogue itself when n_in <= 4096 and otherwise leaves partial sums per K chunk of 4096 inputs in the
+ * workspace; then (n_in > 4096 only) the fixed-order sum with the epilogue.  Arguments as
  * b200q_qgemm_skinny; workspace: b200q_qgemv_rows_workspace_bytes(m, n_out, n_in) bytes, 16-byte aligned. */
 size_t b200q_qgemv_rows_workspace_bytes(int m, int n_out, int n_in);
 int b200q_qgemv_rows(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue, void* y,
                      int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes, void* stream);
+/* The same with the block's RMSNorm folded into the quantising pre-pass (`self.attn_norm(x)` / `self.ffn_norm(x)` in front of the Linear,
+ * tinygrad/llm/model.py:159,167,200): x fp32 [m, n_in] is the un-normed residual stream, norm_weight_f16 [n_in] (NULL: no norm). */
+int b200q_qgemv_rows_norm(int qtype, const void* w_packed, const void* x, int x_dtype, const void* norm_weight_f16, float norm_eps, const void* bias_f16,
+                          const void* residual, int epilogue, void* y, int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes,
+                          void* stream);
 size_t b200q_qgemm_skinny_workspace_bytes(int m, int n_out, int n_in);
 int b200q_qgemm_skinny(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue, void* y,
                        int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes, void* stream);

@@ -293,3 +293,24 @@ def test_few_row_fused_gemv(tag, m, n_out, n_in, x_dtype, epi):
     np.testing.assert_array_equal(got.view(np.uint32), y2.numpy().view(np.uint32))
   from tinygrad_b200 import runtime
   assert runtime.device_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tag,m,n_out,n_in", [("q8_0", 8, 512, 3584), ("q4_0", 5, 272, 8192)])
+def test_few_row_fused_gemv_folds_rmsnorm(tag, m, n_out, n_in):
+  """`Linear(norm(x))` (tinygrad/llm/model.py:159,167): the RMSNorm inside the quantising pre-pass against the norm applied in fp32."""
+  from tinygrad_b200 import quant, runtime
+  from tinygrad_b200.runtime import DeviceBuffer
+  typ = {"q4_0": 2, "q8_0": 8}[tag]
+  rng = np.random.default_rng(n_in)
+  x = (rng.standard_normal((m, n_in)) * rng.uniform(0.2, 5.0, (m, 1))).astype(np.float32)
+  nw = rng.uniform(0.5, 1.5, n_in).astype(np.float16)
+  raw = synth.BLOCK_MAKERS[typ](n_out, n_in, rng)
+  pw = quant.repack(raw, n_out, n_in, typ)
+  ws = DeviceBuffer(quant.qgemv_rows_workspace_bytes(m, n_out, n_in))
+  y = DeviceBuffer.empty((m, n_out), np.float32)
+  quant.qgemv_rows(pw.buf.ptr, typ, n_out, n_in, DeviceBuffer.from_numpy(x), y, m, ws, norm_weight=DeviceBuffer.from_numpy(nw), norm_eps=1e-5)
+  xn = x / np.sqrt((x.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-5).astype(np.float32) * nw.astype(np.float32)
+  ref = xn @ gq.weight_matrix(raw, n_out, n_in, typ).T
+  assert np.abs(y.numpy() - ref).max() <= 5e-4 * max(1.0, np.abs(ref).max())
+  assert runtime.device_status() == 0

@@ -114,6 +114,8 @@ SIGNATURES = {
   "b200q_qgemv_rows_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
   "b200q_qgemv_rows": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
                                c_void_p]),
+  "b200q_qgemv_rows_norm": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
+                                   c_void_p]),
   "b200q_qgemm_skinny_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
   "b200q_qgemm_skinny": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
                                 c_void_p]),

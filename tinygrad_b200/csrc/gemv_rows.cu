@@ -5,7 +5,7 @@
 // quant block of a 16 x 128 weight tile one m16n8k32 MMA per activation digit (high / low 7 bits of a 15-bit integer) yields the exact
 // integer dot products of 16 weight rows with 8 activation rows, which are scaled by (activation scale x fp16 weight scale) and added
 // up in fp32 -- the weights are streamed ONCE for all 8 rows.  A weight tile keeps (row, block) pairs per lane, an MMA wants one
-// block across the quad's lanes: a 4 x 4 word transpose inside each quad (three shuffles) bridges the two.
+// block across the quad's lanes: a 4 x 4 word transpose inside each quad (four shuffles) bridges the two.
 //
 // Pre-pass (rows_record_kernel): the activation rows are quantised once (per block of 32: fp32 scale, 15-bit integers split in two int8
 // digits) into the B-operand order of the MMA, per K chunk of 32 column groups.  Main kernel: grid (CTAs over row tiles, K chunks);
@@ -37,23 +37,56 @@ constexpr int R_TOK = 8;                                        // activation ro
 constexpr int REC_GROUP = 32 * 64;                              // record bytes per column group: 32 lanes x 16 words
 constexpr int SC_GROUP = R_TOK * 4 * 8;                         // scale bytes per column group: [row][block]{scale, offset}
 
+#ifdef B200Q_ROWS_PROF
+// experiment builds only: per CTA {start, record in, end (globaltimer ns), clocks waiting for weights, computing, in the cross-warp sum, producer waiting for a free slot, stages}
+__device__ unsigned long long g_rows_prof[1024 * 8];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define RSTAMP(i, v) do { if (lane == 0) g_rows_prof[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (i)] = (v); } while (0)
+#endif
+
 struct RowsParams {
   const uint8_t* w; const unsigned char* record; float* part;
   int m, n_out, kgroups, n_row_tiles, n_chunks;
+  // one K chunk: the epilogue runs in the streaming kernel (no partial sums, no third launch)
+  const __half* bias; const void* residual; void* y; int y_f16, silu_mul;
 };
 
-// ---- pre-pass: x [m, n_in] -> per chunk c and group j:  words [c][j][lane = 4 * row + t][b * 4 + {hi0, hi1, lo0, lo1}]  (row < 8: zero rows
+// ---- pre-pass: x [m, n_in] -> per chunk c and group j:  words [c][j][b][lane = 4 * row + t][{hi0, hi1, lo0, lo1}]  (row < 8: zero rows
 // past m), hi0 / lo0 = the digits of elements 4t..4t+3 of block b, hi1 / lo1 = of elements 16+4t..16+4t+3 (the k order of m16n8k32's B
 // fragment); then  float2 [c][j][row][b] = {scale, 8 * scale * sum(q)}  (the second removes Q4_0's offset of 8).  One warp per (row, block).
 template <typename T>
-__global__ void __launch_bounds__(256) rows_record_kernel(const T* __restrict__ x, int m, int n_in, int kgroups, unsigned char* __restrict__ record) {
-  const int lane = threadIdx.x & 31, wid = blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int total = kgroups * 4 * R_TOK;                         // (group, block, row) triples
-  if (wid >= total) return;
-  const int row = wid % R_TOK, blk = (wid / R_TOK) % 4, j = wid / (R_TOK * 4);
+__global__ void __launch_bounds__(256) rows_record_kernel(const T* __restrict__ x, int m, int n_in, int kgroups, unsigned char* __restrict__ record,
+                                                          const __half* __restrict__ norm_w, float norm_eps) {
+  // a CTA = 8 warps on 8 consecutive blocks of ONE activation row, so that the row's RMS (norm_w: RMSNorm folded into the quantisation,
+  // x * rsqrt(mean(x^2) + eps) * w as tinygrad/llm/model.py:159 applies before every Linear of a block) is computed once per CTA
+  __shared__ float s_ss[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x % R_TOK, bi = (blockIdx.x / R_TOK) * 8 + warp;      // block index along K
+  pdl_wait();
+  pdl_launch_dependents();
+  float sc = 1.f;
+  if (norm_w) {                                                  // fp32 rows only (checked by the host)
+    float ss = 0.f;
+    if (row < m) {
+      const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + (size_t)row * n_in);
+      for (int i = threadIdx.x; i < n_in / 4; i += 256) { const float4 v4 = xr[i]; ss += v4.x * v4.x + v4.y * v4.y + v4.z * v4.z + v4.w * v4.w; }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) s_ss[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += s_ss[i];
+    sc = 1.0f / sqrtf(tot / (float)n_in + norm_eps);
+  }
+  if (bi >= kgroups * 4) return;
+  const int blk = bi & 3, j = bi >> 2;
   const int k = j * GROUP_ELEMS + blk * 32 + lane;
   float v = 0.f;
-  if (row < m && k < n_in) v = sizeof(T) == 2 ? __half2float(reinterpret_cast<const __half*>(x)[(size_t)row * n_in + k]) : reinterpret_cast<const float*>(x)[(size_t)row * n_in + k];
+  if (row < m && k < n_in) {
+    v = sizeof(T) == 2 ? __half2float(reinterpret_cast<const __half*>(x)[(size_t)row * n_in + k]) : reinterpret_cast<const float*>(x)[(size_t)row * n_in + k];
+    if (norm_w) v = v * sc * __half2float(norm_w[k]);
+  }
   const float amax = warp_max(fabsf(v));
   const bool live = amax > 0.f && amax < INFINITY;
   const float inv = live ? 16256.f / amax : 0.f, s = live ? amax / 16256.f : 0.f;
@@ -70,7 +103,7 @@ __global__ void __launch_bounds__(256) rows_record_kernel(const T* __restrict__ 
   unsigned char* base = record + (size_t)chunk * R_CG * (REC_GROUP + SC_GROUP);     // chunk c: its words, then its scales
   if ((lane & 3) == 0) {
     const int e4 = lane >> 2, t = e4 & 3, half = e4 >> 2;        // elements 4 e4 .. 4 e4 + 3
-    uint32_t* wp = reinterpret_cast<uint32_t*>(base + (size_t)jj * REC_GROUP) + (row * 4 + t) * 16 + blk * 4;
+    uint32_t* wp = reinterpret_cast<uint32_t*>(base + (size_t)jj * REC_GROUP) + (blk * 32 + row * 4 + t) * 4;
     wp[half] = hiw; wp[2 + half] = low;
   }
   if (lane == 0) {
@@ -79,23 +112,17 @@ __global__ void __launch_bounds__(256) rows_record_kernel(const T* __restrict__ 
   }
 }
 
-// words t of the four lanes of a quad: lane t ends up with word t of lane 0, 1, 2, 3 (out.x .. out.w)
+// 4 x 4 word transpose inside a quad: lane t ends up with word t of lanes 0, 1, 2, 3 (out.x .. out.w).  Two butterfly steps (2 x 2
+// words between lanes t and t ^ 1, then 2 x 2 pairs between t and t ^ 2): four shuffles and twelve selects on two lane-constant bits.
 __device__ __forceinline__ uint4 quad_transpose(const uint4 r, int t) {
-  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-  uint32_t got[4];
-#pragma unroll
-  for (int j = 0; j < 4; j++) {
-    // the lane that reads from me in round j is lane t ^ j and wants its own word index, t ^ j
-    const int want = t ^ j;
-    const uint32_t send = want == 0 ? w[0] : want == 1 ? w[1] : want == 2 ? w[2] : w[3];
-    got[j] = j == 0 ? send : __shfl_xor_sync(0xffffffffu, send, j);      // = word t of lane t ^ j
-  }
-  // got[j] came from lane b = t ^ j: out[b] = got[t ^ b]
+  const bool b0 = (t & 1) != 0, b1 = (t & 2) != 0;
+  uint32_t s0 = b0 ? r.x : r.y, s1 = b0 ? r.z : r.w;             // odd lanes give away words 0, 2; even lanes words 1, 3
+  s0 = __shfl_xor_sync(0xffffffffu, s0, 1); s1 = __shfl_xor_sync(0xffffffffu, s1, 1);
+  const uint32_t x = b0 ? s0 : r.x, y = b0 ? r.y : s0, z = b0 ? s1 : r.z, w = b0 ? r.w : s1;
+  uint32_t u0 = b1 ? x : z, u1 = b1 ? y : w;                     // lanes 2, 3 give away the first pair, lanes 0, 1 the second
+  u0 = __shfl_xor_sync(0xffffffffu, u0, 2); u1 = __shfl_xor_sync(0xffffffffu, u1, 2);
   uint4 o;
-  o.x = (t ^ 0) == 0 ? got[0] : (t ^ 0) == 1 ? got[1] : (t ^ 0) == 2 ? got[2] : got[3];
-  o.y = (t ^ 1) == 0 ? got[0] : (t ^ 1) == 1 ? got[1] : (t ^ 1) == 2 ? got[2] : got[3];
-  o.z = (t ^ 2) == 0 ? got[0] : (t ^ 2) == 1 ? got[1] : (t ^ 2) == 2 ? got[2] : got[3];
-  o.w = (t ^ 3) == 0 ? got[0] : (t ^ 3) == 1 ? got[1] : (t ^ 3) == 2 ? got[2] : got[3];
+  o.x = b1 ? u0 : x; o.y = b1 ? u1 : y; o.z = b1 ? z : u0; o.w = b1 ? w : u1;
   return o;
 }
 
@@ -184,6 +211,9 @@ __global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsPara
     if (lane == 0) {
       int it = 0;
       bool ok = true, rec_issued = false;
+#ifdef B200Q_ROWS_PROF
+      long long p_wait = 0;
+#endif
       auto fetch_record = [&]() {
         pdl_wait();
         const uint32_t bytes = (uint32_t)cg * (REC_GROUP + SC_GROUP);
@@ -195,7 +225,13 @@ __global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsPara
       for (int rt = blockIdx.x; rt < p.n_row_tiles && ok; rt += gridDim.x, it++) {
         const int slot = it % R_NS;
         if (it == R_NS && !rec_issued) fetch_record();
+#ifdef B200Q_ROWS_PROF
+        const long long pc0 = clock64();
+#endif
         if (!mbar_wait(empty0 + 8 * slot, ((it / R_NS) & 1) ^ 1)) { ok = false; break; }
+#ifdef B200Q_ROWS_PROF
+        p_wait += clock64() - pc0;
+#endif
         const uint8_t* src = p.w + ((size_t)rt * p.kgroups + (size_t)chunk * R_CG) * TB;
         mbar_expect_tx(full0 + 8 * slot, cg * TB);
         for (int g0 = 0; g0 < cg; g0 += 4) {
@@ -206,6 +242,9 @@ __global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsPara
       if (!rec_issued) fetch_record();
       for (int j = max(0, it - R_NS); j < it; j++) mbar_wait(full0 + 8 * (j % R_NS), (j / R_NS) & 1);      // nothing may still be landing at exit
       mbar_wait(rbar, 0);
+#ifdef B200Q_ROWS_PROF
+      RSTAMP(6, (unsigned long long)p_wait);
+#endif
     } else {
       pdl_wait();
     }
@@ -214,8 +253,15 @@ __global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsPara
   // -------------------------------- consumers
   pdl_wait();
   const int g = lane >> 2, t = lane & 3;
+#ifdef B200Q_ROWS_PROF
+  long long c_wait = 0, c_mac = 0, c_red = 0;
+  if (warp == 0) RSTAMP(0, gtime());
+#endif
   if (!mbar_wait(rbar, 0)) *s_abort = 1;
   rows_bar_sync();
+#ifdef B200Q_ROWS_PROF
+  if (warp == 0) RSTAMP(1, gtime());
+#endif
   bool live = *s_abort == 0;
   const uint4* recw = reinterpret_cast<const uint4*>(rec);
   const float4* recs = reinterpret_cast<const float4*>(rec + (size_t)cg * REC_GROUP);
@@ -223,7 +269,14 @@ __global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsPara
   for (int rt = blockIdx.x; rt < p.n_row_tiles && live; rt += gridDim.x, it++, par ^= 1) {
     const int slot = it % R_NS;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    if (!mbar_wait(full0 + 8 * slot, (it / R_NS) & 1)) { *s_abort = 1; }
+#ifdef B200Q_ROWS_PROF
+    const long long k0 = clock64();
+#endif
+    const bool arrived = mbar_wait(full0 + 8 * slot, (it / R_NS) & 1);
+#ifdef B200Q_ROWS_PROF
+    const long long k1 = clock64();
+#endif
+    if (!arrived) { *s_abort = 1; }
     else {
       const uint8_t* stage = ring + slot * STAGE;
 #pragma unroll
@@ -233,7 +286,7 @@ __global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsPara
           uint4 xw[4];
           float4 xs[4];
 #pragma unroll
-          for (int i = 0; i < 4; i++) xw[i] = recw[(jj * 32 + lane) * 4 + i];
+          for (int i = 0; i < 4; i++) xw[i] = recw[(jj * 4 + i) * 32 + lane];      // block i: 32 consecutive 16-byte words, no bank conflict
           // scales of activation rows 2t and 2t + 1: [row][block]{s, o} = 8 floats per row
           const float4* sc = recs + (size_t)jj * (SC_GROUP / 16);
           xs[0] = sc[(2 * t) * 2]; xs[1] = sc[(2 * t) * 2 + 1]; xs[2] = sc[(2 * t + 1) * 2]; xs[3] = sc[(2 * t + 1) * 2 + 1];
@@ -243,6 +296,9 @@ __global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsPara
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * slot);
     }
+#ifdef B200Q_ROWS_PROF
+    const long long k2 = clock64();
+#endif
     // cross-warp sum in a fixed order: rb[warp][lane * 4 + i]
     float* rb = red + par * R_WARPS * 128;
     *reinterpret_cast<float4*>(rb + warp * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
@@ -255,9 +311,29 @@ __global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsPara
 #pragma unroll
       for (int w = 0; w < R_WARPS; w++) v += rb[w * 128 + o];
       const int ln = o >> 2, i = o & 3, row = rt * 16 + (ln >> 2) + (i >> 1) * 8, tok = 2 * (ln & 3) + (i & 1);
-      if (row < p.n_out && tok < p.m) p.part[((size_t)chunk * p.m + tok) * p.n_out + row] = v;
+      if (p.n_chunks > 1) {
+        if (row < p.n_out && tok < p.m) p.part[((size_t)chunk * p.m + tok) * p.n_out + row] = v;
+      } else if (p.silu_mul) {                                   // rows g / g + 8 of a tile are a gate row and its up row: i and i + 2 of one quad
+        const float up = __shfl_down_sync(0xffffffffu, v, 2);
+        if (i < 2 && row < p.n_out && tok < p.m) {
+          const size_t at = (size_t)tok * (p.n_out >> 1) + rt * 8 + (ln >> 2);
+          const float r = (v / (1.f + expf(-v))) * up;
+          if (p.y_f16) reinterpret_cast<__half*>(p.y)[at] = __float2half_rn(r); else reinterpret_cast<float*>(p.y)[at] = r;
+        }
+      } else if (row < p.n_out && tok < p.m) {
+        const size_t at = (size_t)tok * p.n_out + row;
+        if (p.bias) v += __half2float(p.bias[row]);
+        if (p.residual) v += p.y_f16 ? __half2float(reinterpret_cast<const __half*>(p.residual)[at]) : reinterpret_cast<const float*>(p.residual)[at];
+        if (p.y_f16) reinterpret_cast<__half*>(p.y)[at] = __float2half_rn(v); else reinterpret_cast<float*>(p.y)[at] = v;
+      }
     }
+#ifdef B200Q_ROWS_PROF
+    c_wait += k1 - k0; c_mac += k2 - k1; c_red += clock64() - k2;
+#endif
   }
+#ifdef B200Q_ROWS_PROF
+  if (warp == 0) { RSTAMP(2, gtime()); RSTAMP(3, (unsigned long long)c_wait); RSTAMP(4, (unsigned long long)c_mac); RSTAMP(5, (unsigned long long)c_red); RSTAMP(7, (unsigned long long)it); }
+#endif
 }
 
 // y = sum over K chunks (fixed order) + bias + residual, or the SwiGLU product of interleaved gate / up columns
@@ -289,20 +365,29 @@ size_t rows_record_bytes(int kgroups) { return (size_t)ceil_div(kgroups, R_CG) *
 
 }  // namespace
 
+#ifdef B200Q_ROWS_PROF
+extern "C" int b200q_rows_prof_read(unsigned long long* out, int n_ctas) {
+  B200Q_CHECK_CUDA(cudaMemcpyFromSymbol(out, g_rows_prof, sizeof(unsigned long long) * 8 * (n_ctas < 1024 ? n_ctas : 1024)));
+  return B200Q_OK;
+}
+#endif
+
 extern "C" size_t b200q_qgemv_rows_workspace_bytes(int m, int n_out, int n_in) {
   if (m <= 0 || n_out <= 0 || n_in <= 0) return 0;
   const int kgroups = ceil_div(n_in, GROUP_ELEMS), passes = ceil_div(m, R_TOK);
   return rows_record_bytes(kgroups) + (size_t)ceil_div(kgroups, R_CG) * (size_t)(passes > 1 ? R_TOK : m) * n_out * sizeof(float);
 }
 
-extern "C" int b200q_qgemv_rows(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue,
-                                void* y, int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes, void* stream) {
+extern "C" int b200q_qgemv_rows_norm(int qtype, const void* w_packed, const void* x, int x_dtype, const void* norm_weight_f16, float norm_eps, const void* bias_f16,
+                                     const void* residual, int epilogue, void* y, int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes,
+                                     void* stream) {
   if (!w_packed || !x || !y || !workspace || m <= 0 || n_out <= 0 || n_in <= 0) return B200Q_ERR_BAD_ARG;
   if (qtype == B200Q_Q6_K) return B200Q_ERR_UNSUPPORTED;
   if (qtype != B200Q_Q4_0 && qtype != B200Q_Q8_0) return B200Q_ERR_BAD_ARG;
   if ((x_dtype != B200Q_F32 && x_dtype != B200Q_F16) || (y_dtype != B200Q_F32 && y_dtype != B200Q_F16)) return B200Q_ERR_BAD_ARG;
   if (epilogue != B200Q_EPI_LINEAR && epilogue != B200Q_EPI_SILU_MUL) return B200Q_ERR_BAD_ARG;
   if (epilogue == B200Q_EPI_SILU_MUL && (bias_f16 || residual || n_out % 16)) return B200Q_ERR_BAD_ARG;
+  if (norm_weight_f16 && (x_dtype != B200Q_F32 || n_in % 4)) return B200Q_ERR_BAD_ARG;
   if (n_in % 32) return B200Q_ERR_BAD_SHAPE;
   if (((uintptr_t)w_packed | (uintptr_t)x | (uintptr_t)workspace) & 15) return B200Q_ERR_MISALIGNED;
   if (workspace_bytes < b200q_qgemv_rows_workspace_bytes(m, n_out, n_in)) return B200Q_ERR_TOO_LARGE;
@@ -323,22 +408,33 @@ extern "C" int b200q_qgemv_rows(int qtype, const void* w_packed, const void* x, 
   for (int r0 = 0; r0 < m; r0 += R_TOK) {                        // 8 activation rows per pass over the weights
     const int mm = min(R_TOK, m - r0);
     const unsigned char* xr = (const unsigned char*)x + (size_t)r0 * n_in * esz;
-    const int rec_warps = kgroups * 4 * R_TOK;
-    if (x_dtype == B200Q_F16) rows_record_kernel<__half><<<ceil_div(rec_warps, 8), 256, 0, st>>>((const __half*)xr, mm, n_in, kgroups, record);
-    else rows_record_kernel<float><<<ceil_div(rec_warps, 8), 256, 0, st>>>((const float*)xr, mm, n_in, kgroups, record);
+    const dim3 rec_grid(R_TOK * ceil_div(kgroups * 4, 8));
+    if (x_dtype == B200Q_F16)
+      B200Q_CHECK_CUDA(launch_k(rows_record_kernel<__half>, rec_grid, dim3(256), (size_t)0, st, true, (const __half*)xr, mm, n_in, kgroups, record, (const __half*)nullptr, 0.f));
+    else
+      B200Q_CHECK_CUDA(launch_k(rows_record_kernel<float>, rec_grid, dim3(256), (size_t)0, st, true, (const float*)xr, mm, n_in, kgroups, record,
+                                (const __half*)norm_weight_f16, norm_eps));
+    const unsigned char* res = residual ? (const unsigned char*)residual + (size_t)r0 * n_out * ysz : nullptr;
+    void* yr = (void*)((unsigned char*)y + (size_t)r0 * n_y * ysz);
     RowsParams p;
     p.w = (const uint8_t*)w_packed; p.record = record; p.part = part; p.m = mm; p.n_out = n_out; p.kgroups = kgroups; p.n_row_tiles = n_row_tiles;
     p.n_chunks = n_chunks;
+    p.bias = (const __half*)bias_f16; p.residual = res; p.y = yr; p.y_f16 = y_dtype == B200Q_F16; p.silu_mul = epilogue == B200Q_EPI_SILU_MUL;
     int gx = n_sm / n_chunks; if (gx < 1) gx = 1; if (gx > n_row_tiles) gx = n_row_tiles;
     const dim3 grid(gx, n_chunks);
     const size_t smem = rows_smem(qtype);
     if (qtype == B200Q_Q4_0) B200Q_CHECK_CUDA(launch_k(qgemv_rows_kernel<B200Q_Q4_0>, grid, dim3(R_THREADS), smem, st, true, p));
     else B200Q_CHECK_CUDA(launch_k(qgemv_rows_kernel<B200Q_Q8_0>, grid, dim3(R_THREADS), smem, st, true, p));
-    const size_t total = (size_t)mm * n_y;
-    const unsigned char* res = residual ? (const unsigned char*)residual + (size_t)r0 * n_out * ysz : nullptr;
-    B200Q_CHECK_CUDA(launch_k(rows_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), (size_t)0, st, true, (const float*)part, n_chunks, mm, n_out,
-                              (const __half*)bias_f16, (const void*)res, (void*)((unsigned char*)y + (size_t)r0 * n_y * ysz), (int)(y_dtype == B200Q_F16),
-                              (int)(epilogue == B200Q_EPI_SILU_MUL)));
+    if (n_chunks > 1) {
+      const size_t total = (size_t)mm * n_y;
+      B200Q_CHECK_CUDA(launch_k(rows_reduce_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), (size_t)0, st, true, (const float*)part, n_chunks, mm, n_out,
+                                (const __half*)bias_f16, (const void*)res, yr, (int)(y_dtype == B200Q_F16), (int)(epilogue == B200Q_EPI_SILU_MUL)));
+    }
   }
   return B200Q_OK;
+}
+
+extern "C" int b200q_qgemv_rows(int qtype, const void* w_packed, const void* x, int x_dtype, const void* bias_f16, const void* residual, int epilogue,
+                                void* y, int y_dtype, int m, int n_out, int n_in, void* workspace, size_t workspace_bytes, void* stream) {
+  return b200q_qgemv_rows_norm(qtype, w_packed, x, x_dtype, nullptr, 0.f, bias_f16, residual, epilogue, y, y_dtype, m, n_out, n_in, workspace, workspace_bytes, stream);
 }

@@ -416,19 +416,27 @@ class Transformer:
       def gemm(w, qt, n_out, n_in, x, y, **kw): quant.qgemm(w, qt, n_out, n_in, x, y, B, x_dtype=F32, y_dtype=F32, stream=s, **kw)
     # the position comes from the device (sequence 0's counter; all sequences move together), so the launch sequence can be replayed as a graph
     check(lib.b200q_embed_rows(self.token_embd.ptr, self.tokens.ptr, c.max_context + 1, self.pos.ptr, B, c.dim, c.vocab_size, f["x"].ptr, s))
+    fold = B <= 8 and quant.FEW_ROW_FUSED     # the few-row kernel's pre-pass applies the RMSNorm itself: no norm launches
+    def normed(norm):
+      if fold: return f["x"], {"norm_weight": norm, "norm_eps": c.norm_eps}
+      check(lib.b200q_rmsnorm_rows(f["x"].ptr, norm.ptr, c.norm_eps, B, c.dim, f["xn"].ptr, F32, s))
+      return f["xn"], {}
     for b in self.blk:
-      check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.attn_norm.ptr, c.norm_eps, B, c.dim, f["xn"].ptr, F32, s))
-      gemm(b.qkv.ptr, self.qtype, qkv_rows, c.dim, f["xn"], f["qkv"], bias=b.qkv_bias)
+      xin, kw = normed(b.attn_norm)
+      gemm(b.qkv.ptr, self.qtype, qkv_rows, c.dim, xin, f["qkv"], bias=b.qkv_bias, **kw)
       check(lib.b200q_attn_decode_batch(f["qkv"].ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, 0, self.pos.ptr, B, c.n_heads, c.n_kv_heads, c.head_dim,
                                         c.rope_dim, c.max_context, f["q16"].ptr, f["att"].ptr, F32, s))
       gemm(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, f["att"], f["x"], residual=f["x"])
-      check(lib.b200q_rmsnorm_rows(f["x"].ptr, b.ffn_norm.ptr, c.norm_eps, B, c.dim, f["xn"].ptr, F32, s))
-      gemm(b.gate_up.buf.ptr, self.qtype, 2 * c.hidden_dim, c.dim, f["xn"], f["act"], epilogue=EPI_SILU_MUL)
+      xin, kw = normed(b.ffn_norm)
+      gemm(b.gate_up.buf.ptr, self.qtype, 2 * c.hidden_dim, c.dim, xin, f["act"], epilogue=EPI_SILU_MUL, **kw)
       gemm(b.ffn_down.buf.ptr, self.qtype, c.dim, c.hidden_dim, f["act"], f["x"], residual=f["x"])
-    check(lib.b200q_rmsnorm_rows(f["x"].ptr, self.output_norm.ptr, c.norm_eps, B, c.dim, f["xn"].ptr, F32, s))
     if self._batch_logits is None: self._batch_logits = DeviceBuffer.empty((B, c.vocab_size), np.float32)
-    if head_q: gemm(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, f["xn"], self._batch_logits)
-    else: quant.gemv_dense(self.output.buf, self.output.dtype, c.vocab_size, c.dim, f["xn"], self._batch_logits, m=B, stream=s)
+    if head_q and fold:
+      gemm(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, f["x"], self._batch_logits, norm_weight=self.output_norm, norm_eps=c.norm_eps)
+    else:
+      check(lib.b200q_rmsnorm_rows(f["x"].ptr, self.output_norm.ptr, c.norm_eps, B, c.dim, f["xn"].ptr, F32, s))
+      if head_q: gemm(self.output.buf.ptr, self.output_type, c.vocab_size, c.dim, f["xn"], self._batch_logits)
+      else: quant.gemv_dense(self.output.buf, self.output.dtype, c.vocab_size, c.dim, f["xn"], self._batch_logits, m=B, stream=s)
     for i in range(B):
       check(lib.b200q_argmax_advance(self._batch_logits.ptr + 4 * i * c.vocab_size, c.vocab_size, self.tokens.ptr + 4 * i * (c.max_context + 1),
                                      self.pos.ptr + 4 * i, c.max_context, self.argmax_scratch.ptr, 0, s))

@@ -114,10 +114,11 @@ def qgemv_rows_workspace_bytes(m: int, n_out: int, n_in: int) -> int:
 
 
 def qgemv_rows(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int, workspace: DeviceBuffer, x_dtype=F32, y_dtype=F32, bias=None, residual=None,
-               epilogue: int = EPI_LINEAR, stream=None) -> None:
-  """The same Linear for a few activation rows (batched decode) on the int8 tensor cores: weights streamed once per 8 rows."""
-  check(_lib.load().b200q_qgemv_rows(qtype, w_ptr, ptr_of(x), x_dtype, ptr_of(bias), ptr_of(residual), epilogue, ptr_of(y), y_dtype, m, n_out, n_in,
-                                     workspace.ptr, workspace.nbytes, stream_ptr(stream)))
+               epilogue: int = EPI_LINEAR, norm_weight=None, norm_eps: float = 0.0, stream=None) -> None:
+  """The same Linear for a few activation rows (batched decode) on the int8 tensor cores: weights streamed once per 8 rows.
+  norm_weight (fp16 [n_in]): the RMSNorm in front of the Linear, folded into the quantising pre-pass (x is then the un-normed fp32 rows)."""
+  check(_lib.load().b200q_qgemv_rows_norm(qtype, w_ptr, ptr_of(x), x_dtype, ptr_of(norm_weight), norm_eps, ptr_of(bias), ptr_of(residual), epilogue, ptr_of(y),
+                                          y_dtype, m, n_out, n_in, workspace.ptr, workspace.nbytes, stream_ptr(stream)))
 
 
 def qgemm_skinny_workspace_bytes(m: int, n_out: int, n_in: int) -> int:
