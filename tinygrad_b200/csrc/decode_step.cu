@@ -447,7 +447,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) decode_step_kernel(const __grid
       float* my_red = wred + warp * DS_MAXT * 16;
       for (int a = w0; a < w1; a++) {
         if (!mbar_wait(bars_u + 8 * c_slot, c_par)) { *s_abort = 1; atomicExch(p.ctrl + 2, 1u); break; }
-        const uint4 bq0 = diag ? xq[(j * 2 + 0) * 8 + g] : *zero, bq1 = diag ? xq[(j * 2 + 1) * 8 + g] : *zero;
+        const uint4* q0 = diag ? xq + (j * 2 + 0) * 8 + g : zero;      // select the address, not the loaded value (no branch around the loads)
+        const uint4* q1 = diag ? xq + (j * 2 + 1) * 8 + g : zero;
+        const uint4 bq0 = *q0, bq1 = *q1;
         const float4 st = xsc[(j * 2 + (t >> 1)) * 2 + (t & 1)];
         tile_mac<QT>(ring + c_slot * TB, lane, bq0, bq1, st, acc0, acc1);
         pend = true;

@@ -70,7 +70,9 @@ __global__ void rope_kv_rows_kernel(const float* __restrict__ qkv, const float* 
   const int row = (n_heads + 2 * n_kv) * hd;
   const float* src = qkv + (size_t)t * row;
   const float* rp = rope + (size_t)pos * rope_dim;
-  for (int i = threadIdx.x; i < (n_heads + n_kv) * hd; i += blockDim.x) {
+  // gridDim.y CTAs share a row (few rows, as in batched decode: one element per thread instead of a long loop per CTA)
+  const int tid = blockIdx.y * blockDim.x + threadIdx.x, nthr = gridDim.y * blockDim.x;
+  for (int i = tid; i < (n_heads + n_kv) * hd; i += nthr) {
     const int h = i / hd, d = i - h * hd;
     const float* v = src + (size_t)h * hd;
     float o = v[d];
@@ -80,7 +82,7 @@ __global__ void rope_kv_rows_kernel(const float* __restrict__ qkv, const float* 
     else k_cache[((size_t)(h - n_heads) * max_context + pos) * hd + d] = kv_cast<KV>(o);
   }
   const float* vs = src + (size_t)(n_heads + n_kv) * hd;
-  for (int i = threadIdx.x; i < n_kv * hd; i += blockDim.x) {
+  for (int i = tid; i < n_kv * hd; i += nthr) {
     const int h = i / hd, d = i - h * hd;
     v_cache[((size_t)h * max_context + pos) * hd + d] = kv_cast<KV>(vs[i]);
   }
@@ -119,7 +121,8 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const float* _
   const KV* kc = k_cache + seq_off + (size_t)kvh * max_context * HD;
   const KV* vc = v_cache + seq_off + (size_t)kvh * max_context * HD;
   // queries of this tile (rows past n_rows read as zero)
-  for (int i = tid; i < PQ * (HD / 8); i += PF_THREADS) {
+  const int q_rows = batch ? 16 : PQ;                    // batch: only warp 0's 16 rows are read (one of them live)
+  for (int i = tid; i < q_rows * (HD / 8); i += PF_THREADS) {
     const int r = i / (HD / 8), c = (i - r * (HD / 8)) * 8;
     uint4 hi4 = make_uint4(0, 0, 0, 0), lo4 = make_uint4(0, 0, 0, 0);
     if (q0 + r < rows_end) {
@@ -143,7 +146,7 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const float* _
   // q = hi + lo (both fp16): the scores keep the fp32 query's precision, as the one-token kernel's fp32 dot products do
   uint32_t qa[HD / 16][4], ql[HD / 16][4];
   {
-    const __half* qr = s_q + (warp * 16 + g) * STRIDE + tq * 2;
+    const __half* qr = s_q + ((batch ? 0 : warp * 16) + g) * STRIDE + tq * 2;
     const __half* qs = qr + PQ * STRIDE;
 #pragma unroll
     for (int kk = 0; kk < HD / 16; kk++) {
@@ -186,6 +189,7 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const float* _
     }
     __syncthreads();
     if (k0 > pos0 + warp * 16 + 15) continue;  // every key of the chunk is after this warp's last query
+    if (batch && warp > 0) continue;           // one query row per CTA: warps 1..3 only help to stage the keys and values
     // S = Q K^T for 16 rows x 64 keys
     float s[PK / 8][4];
 #pragma unroll
@@ -341,9 +345,11 @@ static int attn_rows(const float* qkv, void* k_cache, void* v_cache, int kv_dtyp
   if (head_dim != 16 && head_dim != 32 && head_dim != 64 && head_dim != 128) return B200Q_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   const bool h = kv_dtype == B200Q_F16;
-  if (h) rope_kv_rows_kernel<__half><<<n_rows, 256, 0, st>>>(qkv, rope, start_pos, n_heads, n_kv_heads, head_dim, rope_dim, max_context, (__half*)k_cache,
+  const int row_ctas = n_rows >= 64 ? 1 : ceil_div((n_heads + n_kv_heads) * head_dim, 256);
+  const dim3 rgrid(n_rows, row_ctas);
+  if (h) rope_kv_rows_kernel<__half><<<rgrid, 256, 0, st>>>(qkv, rope, start_pos, n_heads, n_kv_heads, head_dim, rope_dim, max_context, (__half*)k_cache,
                                                            (__half*)v_cache, (float*)q_scratch, batch, pos_dev);
-  else rope_kv_rows_kernel<float><<<n_rows, 256, 0, st>>>(qkv, rope, start_pos, n_heads, n_kv_heads, head_dim, rope_dim, max_context, (float*)k_cache,
+  else rope_kv_rows_kernel<float><<<rgrid, 256, 0, st>>>(qkv, rope, start_pos, n_heads, n_kv_heads, head_dim, rope_dim, max_context, (float*)k_cache,
                                                         (float*)v_cache, (float*)q_scratch, batch, pos_dev);
   B200Q_CHECK_CUDA(cudaGetLastError());
   cudaError_t e;

@@ -20,9 +20,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {   // suspends the thread for a bounded, hardware-chosen time
+// Suspends the thread for a bounded time.  With the time hint the waiting warps come back less often and leave the issue slots to the
+// warps that have a tile (measured: 1.8 % on the decode step; 500 ns .. 20 us all the same).
+#ifndef B200Q_MBAR_HINT_NS
+#define B200Q_MBAR_HINT_NS 2000
+#endif
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+#if B200Q_MBAR_HINT_NS > 0
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity), "r"(B200Q_MBAR_HINT_NS) : "memory");
+#else
   asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+#endif
   return ok != 0;
 }
 // Bounded wait: false (and the status word set) if the phase did not complete in time.
@@ -86,8 +95,9 @@ __device__ __forceinline__ void tile_mac(const uint8_t* tile, int lane, const ui
   }
   const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&sc.x)), d1 = __half22float2(*reinterpret_cast<const __half2*>(&sc.y));
   const float oa = QT == B200Q_Q4_0 ? st.y : 0.f, ob = QT == B200Q_Q4_0 ? st.w : 0.f;   // only Q4_0 stores value + 8
-  const float v0 = fmaf((float)c[0], st.x, -oa), v1 = fmaf((float)c[1], st.z, -ob);
-  const float v2 = fmaf((float)c[2], st.x, -oa), v3 = fmaf((float)c[3], st.z, -ob);
+  const float f0 = (float)c[0], f1 = (float)c[1], f2 = (float)c[2], f3 = (float)c[3];
+  const float v0 = fmaf(f0, st.x, -oa), v1 = fmaf(f1, st.z, -ob);
+  const float v2 = fmaf(f2, st.x, -oa), v3 = fmaf(f3, st.z, -ob);
   acc0 = fmaf(v0, d0.x, fmaf(v1, d0.y, acc0));
   acc1 = fmaf(v2, d1.x, fmaf(v3, d1.y, acc1));
 }
