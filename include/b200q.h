@@ -247,6 +247,12 @@ typedef struct b200q_attn_args {
 int b200q_attn_min_split(int max_context);
 size_t b200q_attn_scratch_bytes(int n_heads, int n_kv_heads, int head_dim, int n_split);
 int b200q_attn_decode(const b200q_attn_args* args, void* stream);
+/* The same for `n_seqs` sequences that decode in lock-step (tokens [B, 1]: tinygrad/llm/model.py:366-367 with B > 1), one launch: sequence s
+ * reads row s of qkv [n_seqs][(n_heads + 2 n_kv_heads) * head_dim], its own caches [n_seqs][n_kv_heads][max_context][head_dim], its
+ * position pos[s], writes row s of out [n_seqs][n_heads * head_dim] and uses scratch + s * b200q_attn_seq_scratch_stride(...)
+ * (n_seqs strides, zero-initialised once).  xq_out must be NULL. */
+size_t b200q_attn_seq_scratch_stride(int n_heads, int n_kv_heads, int head_dim, int n_split);
+int b200q_attn_decode_seqs(const b200q_attn_args* args, int n_seqs, void* stream);
 
 /* b200q_attn_decode for callers that must not allocate device memory (no counterpart in the reference, which
  * always allocates through its own allocator).  Meant for hosts that own all device memory themselves -- a frozen

@@ -121,6 +121,44 @@ def test_attention_decode_matches_oracle(kv_dtype, n_heads, n_kv, hd, rope_dim, 
   np.testing.assert_array_equal(d["kc"].numpy()[:, mask], kc[:, mask])        # nothing else touched
 
 
+def test_attention_of_several_sequences_in_one_launch():
+  """b200q_attn_decode_seqs (sequences in lock-step, each at its own position of its own cache) gives, bit for bit, what one
+  b200q_attn_decode per sequence gives: outputs and appended cache rows."""
+  from tinygrad_b200 import _lib, runtime
+  from tinygrad_b200.runtime import DeviceBuffer
+  from tinygrad_b200.model import precompute_freqs_cis
+  lib = _lib.load()
+  rng = np.random.default_rng(11)
+  B, n_heads, n_kv, hd, ctx = 3, 14, 2, 128, 200
+  n_split = lib.b200q_attn_min_split(ctx)
+  row = (n_heads + 2 * n_kv) * hd
+  qkv = rng.standard_normal((B, row)).astype(np.float32)
+  kc = (rng.standard_normal((B, n_kv, ctx, hd)) * 0.5).astype(np.float16); vc = rng.standard_normal((B, n_kv, ctx, hd)).astype(np.float16)
+  pos = np.array([150, 3, 64], np.int32)
+  fc = DeviceBuffer.from_numpy(precompute_freqs_cis(hd, ctx, 10000.0))
+  # one launch per sequence
+  outs, kcs, vcs = [], [], []
+  for s in range(B):
+    d = {n: DeviceBuffer.from_numpy(np.ascontiguousarray(a)) for n, a in (("qkv", qkv[s]), ("kc", kc[s]), ("vc", vc[s]), ("pos", pos[s:s + 1]))}
+    out = DeviceBuffer.empty((n_heads * hd,), np.float32)
+    scratch = DeviceBuffer(lib.b200q_attn_scratch_bytes(n_heads, n_kv, hd, n_split), zero=True)
+    a = _lib.AttnArgs(d["qkv"].ptr, d["kc"].ptr, d["vc"].ptr, _lib.F16, fc.ptr, d["pos"].ptr, out.ptr, scratch.ptr, n_heads, n_kv, hd, hd, ctx, n_split, 0, None)
+    _lib.check(lib.b200q_attn_decode(ctypes.byref(a), None))
+    outs.append(out.numpy()); kcs.append(d["kc"].numpy()); vcs.append(d["vc"].numpy())
+  # all of them at once
+  d = {n: DeviceBuffer.from_numpy(a) for n, a in (("qkv", qkv), ("kc", kc), ("vc", vc), ("pos", pos))}
+  out = DeviceBuffer.empty((B, n_heads * hd), np.float32)
+  scratch = DeviceBuffer(B * lib.b200q_attn_seq_scratch_stride(n_heads, n_kv, hd, n_split), zero=True)
+  a = _lib.AttnArgs(d["qkv"].ptr, d["kc"].ptr, d["vc"].ptr, _lib.F16, fc.ptr, d["pos"].ptr, out.ptr, scratch.ptr, n_heads, n_kv, hd, hd, ctx, n_split, 0, None)
+  for _ in range(2):
+    _lib.check(lib.b200q_attn_decode_seqs(ctypes.byref(a), B, None))
+    np.testing.assert_array_equal(out.numpy().view(np.uint32), np.stack(outs).view(np.uint32))
+  np.testing.assert_array_equal(d["kc"].numpy(), np.stack(kcs)); np.testing.assert_array_equal(d["vc"].numpy(), np.stack(vcs))
+  assert runtime.device_status() == 0
+  a.xq_out = 16
+  assert lib.b200q_attn_decode_seqs(ctypes.byref(a), B, None) == -1      # no quantised record in the multi-sequence form
+
+
 def test_attention_at_the_last_cache_row_and_refusal_past_it():
   """pos == max_context - 1 with a context that is not a multiple of the 64-position slice is served; pos == max_context
   touches nothing (cache and output unchanged) and raises status 2; embed / arg-max / advance stop at the table's end."""

@@ -99,6 +99,8 @@ SIGNATURES = {
   "b200q_attn_min_split": (c_int, [c_int]),
   "b200q_attn_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
   "b200q_attn_decode": (c_int, [POINTER(AttnArgs), c_void_p]),
+  "b200q_attn_seq_scratch_stride": (c_size_t, [c_int, c_int, c_int, c_int]),
+  "b200q_attn_decode_seqs": (c_int, [POINTER(AttnArgs), c_int, c_void_p]),
   "b200q_attn_decode_static_capacity": (c_size_t, []),
   "b200q_attn_decode_static": (c_int, [POINTER(AttnArgs), c_void_p]),
   "b200q_decode_step_supported": (c_int, [POINTER(DecodeStepArgs)]),

@@ -108,9 +108,19 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 #define ASTAMP(i) do {} while (0)
 #endif
 
+// Sequence blockIdx.z of a batch in lock-step: element strides between consecutive sequences (all zero for one sequence)
+struct SeqStride { size_t qkv, cache, out, scratch_bytes; int pos; };
+
 template <typename KV>
-__global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_attn_args a) {
+__global__ void __launch_bounds__(MAX_REP * 32) attn_decode_kernel(const b200q_attn_args a_in, const SeqStride sq) {
   constexpr int VEC = KvIO<KV>::VEC;
+  b200q_attn_args a = a_in;
+  if (blockIdx.z) {
+    const size_t z = blockIdx.z;
+    a.qkv += z * sq.qkv; a.out += z * sq.out; a.pos += z * sq.pos;
+    a.k_cache = reinterpret_cast<KV*>(a.k_cache) + z * sq.cache; a.v_cache = reinterpret_cast<KV*>(a.v_cache) + z * sq.cache;
+    a.scratch = reinterpret_cast<unsigned char*>(a.scratch) + z * sq.scratch_bytes;
+  }
   extern __shared__ __align__(16) unsigned char asmem[];
   const int hd = a.head_dim, n_rep = a.n_heads / a.n_kv_heads, half_r = a.rope_dim >> 1;
   const int rstride = hd + VEC;                           // padded row: lanes reading different rows hit different banks
@@ -463,14 +473,24 @@ static int attn_validate(const b200q_attn_args* a) {
   return B200Q_OK;
 }
 
-extern "C" int b200q_attn_decode(const b200q_attn_args* a, void* stream) {
+extern "C" size_t b200q_attn_seq_scratch_stride(int n_heads, int n_kv_heads, int head_dim, int n_split) {
+  return (b200q_attn_scratch_bytes(n_heads, n_kv_heads, head_dim, n_split) + 255) & ~(size_t)255;
+}
+
+static int attn_decode_launch(const b200q_attn_args* a, int n_seqs, void* stream) {
   const int rc = attn_validate(a);
   if (rc != B200Q_OK) return rc;
   if (!a->scratch) return B200Q_ERR_BAD_ARG;
   if ((uintptr_t)a->scratch & 15) return B200Q_ERR_MISALIGNED;
   int n_rep = a->n_heads / a->n_kv_heads;
   const int ws = 2 * n_rep <= MAX_REP ? 2 : 1;              // warps per head
-  dim3 grid(a->n_kv_heads, a->n_split), block(ws * n_rep * 32);
+  dim3 grid(a->n_kv_heads, a->n_split, n_seqs), block(ws * n_rep * 32);
+  SeqStride sq = {};
+  if (n_seqs > 1) {
+    sq.qkv = (size_t)(a->n_heads + 2 * a->n_kv_heads) * a->head_dim; sq.cache = (size_t)a->n_kv_heads * a->max_context * a->head_dim;
+    sq.out = (size_t)a->n_heads * a->head_dim; sq.pos = 1;
+    sq.scratch_bytes = b200q_attn_seq_scratch_stride(a->n_heads, a->n_kv_heads, a->head_dim, a->n_split);
+  }
   bool pdl = (a->flags & B200Q_FLAG_PDL) != 0;
   const int esz = a->kv_dtype == B200Q_F16 ? 2 : 4, vec = 16 / esz;
   size_t smem = (size_t)2 * ATTN_CHUNK * (a->head_dim + vec) * esz + (size_t)n_rep * (a->head_dim + ATTN_CHUNK + a->head_dim + 4) * sizeof(float);
@@ -488,9 +508,16 @@ extern "C" int b200q_attn_decode(const b200q_attn_args* a, void* stream) {
   ap.flags = (ap.flags & 0xFFFF) | ((prof_counter++ & 4095) << 16);
   a = &ap;
 #endif
-  if (a->kv_dtype == B200Q_F16) B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<__half>, grid, block, smem, (cudaStream_t)stream, pdl, *a));
-  else B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<float>, grid, block, smem, (cudaStream_t)stream, pdl, *a));
+  if (a->kv_dtype == B200Q_F16) B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<__half>, grid, block, smem, (cudaStream_t)stream, pdl, *a, sq));
+  else B200Q_CHECK_CUDA(launch_k(attn_decode_kernel<float>, grid, block, smem, (cudaStream_t)stream, pdl, *a, sq));
   return B200Q_OK;
+}
+
+extern "C" int b200q_attn_decode(const b200q_attn_args* a, void* stream) { return attn_decode_launch(a, 1, stream); }
+
+extern "C" int b200q_attn_decode_seqs(const b200q_attn_args* a, int n_seqs, void* stream) {
+  if (n_seqs <= 0 || (a && a->xq_out)) return B200Q_ERR_BAD_ARG;
+  return attn_decode_launch(a, n_seqs, stream);
 }
 
 extern "C" size_t b200q_argmax_scratch_bytes(void) { return ARGMAX_CTAS * (sizeof(float) + sizeof(int)) + sizeof(unsigned); }

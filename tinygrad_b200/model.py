@@ -13,7 +13,11 @@ import numpy as np
 from . import _lib, quant
 from ._lib import check, F32, F16, EPI_LINEAR, EPI_SILU_MUL, FLAG_PDL
 from .runtime import DeviceBuffer, Stream, Graph, Event, synchronize as runtime_sync
-import ctypes
+import ctypes, os
+
+# batched decode: attention of all sequences in one launch of the one-token kernel instead of the prompt-pass kernels with one query row
+# per CTA (measured 1.4 % slower at 8 sequences x 130 positions: off unless asked for)
+SEQ_ATTENTION = os.environ.get("B200Q_SEQ_ATTENTION", "0") == "1"
 
 
 @dataclass(frozen=True)
@@ -215,6 +219,7 @@ class Transformer:
     self._cached_tokens: list = []
     self.prefill_rows = prefill_rows if (tp is None and not self.dense_blocks and c.hidden_dim % 8 == 0 and c.head_dim in (16, 32, 64, 128)) else 0
     self.prefill_chunk, self._pf, self._batch_logits, self._skinny_ws, self._batch_graph = max(1, prefill_chunk), None, None, None, None
+    self._seq_attn_scratch = None
     self.is_moe, self._host_pos = c.num_experts > 0, 0
     if self.is_moe:
       assert tp is None and c.head_dim in (16, 32, 64, 128), "the mixture-of-experts model runs on the row path of one GPU"
@@ -417,6 +422,10 @@ class Transformer:
     # the position comes from the device (sequence 0's counter; all sequences move together), so the launch sequence can be replayed as a graph
     check(lib.b200q_embed_rows(self.token_embd.ptr, self.tokens.ptr, c.max_context + 1, self.pos.ptr, B, c.dim, c.vocab_size, f["x"].ptr, s))
     fold = B <= 8 and quant.FEW_ROW_FUSED     # the few-row kernel's pre-pass applies the RMSNorm itself: no norm launches
+    seq_attn = SEQ_ATTENTION and c.n_heads // c.n_kv_heads <= 8 and c.head_dim % 8 == 0 and c.head_dim <= 128
+    if seq_attn and self._seq_attn_scratch is None:
+      stride = lib.b200q_attn_seq_scratch_stride(c.n_heads, c.n_kv_heads, c.head_dim, self.n_split)
+      self._seq_attn_scratch = DeviceBuffer(B * stride, zero=True)
     def normed(norm):
       if fold: return f["x"], {"norm_weight": norm, "norm_eps": c.norm_eps}
       check(lib.b200q_rmsnorm_rows(f["x"].ptr, norm.ptr, c.norm_eps, B, c.dim, f["xn"].ptr, F32, s))
@@ -424,8 +433,13 @@ class Transformer:
     for b in self.blk:
       xin, kw = normed(b.attn_norm)
       gemm(b.qkv.ptr, self.qtype, qkv_rows, c.dim, xin, f["qkv"], bias=b.qkv_bias, **kw)
-      check(lib.b200q_attn_decode_batch(f["qkv"].ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, 0, self.pos.ptr, B, c.n_heads, c.n_kv_heads, c.head_dim,
-                                        c.rope_dim, c.max_context, f["q16"].ptr, f["att"].ptr, F32, s))
+      if seq_attn:     # the one-token kernel over (KV head, slice, sequence): RoPE, cache append and attention in one launch
+        a = _lib.AttnArgs(f["qkv"].ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, self.pos.ptr, f["att"].ptr, self._seq_attn_scratch.ptr,
+                          c.n_heads, c.n_kv_heads, c.head_dim, c.rope_dim, c.max_context, self.n_split, _lib.FLAG_PDL, None)
+        check(lib.b200q_attn_decode_seqs(ctypes.byref(a), B, s))
+      else:
+        check(lib.b200q_attn_decode_batch(f["qkv"].ptr, b.k_cache.ptr, b.v_cache.ptr, kvdt, self.rope.ptr, 0, self.pos.ptr, B, c.n_heads, c.n_kv_heads,
+                                          c.head_dim, c.rope_dim, c.max_context, f["q16"].ptr, f["att"].ptr, F32, s))
       gemm(b.attn_output.buf.ptr, self.qtype, c.dim, self.q_dim, f["att"], f["x"], residual=f["x"])
       xin, kw = normed(b.ffn_norm)
       gemm(b.gate_up.buf.ptr, self.qtype, 2 * c.hidden_dim, c.dim, xin, f["act"], epilogue=EPI_SILU_MUL, **kw)
