@@ -172,6 +172,12 @@ typedef struct b200q_gemv_args {
    * then sums the slots (row-split linear: all-reduce) or copies them out (column-split: all-gather).  `y` may be NULL. */
   void* const* peer_mailboxes;   /* host array [n_peers] of device pointers */
   int n_peers, peer_rank;
+  /* xq_out without a constraint on how row tiles are dealt to CTAs: device uint32 [n_out + n_out / 32], the first n_out words the
+   * all-ones pattern, the rest zero, set once (the kernel leaves them so).  Without it a CTA takes runs of 2 (4 with the SwiGLU
+   * epilogue) consecutive row tiles so that it holds whole blocks of 32 outputs, which loads the grid unevenly; with it tiles go
+   * out one by one, every tile leaves its outputs in this row as self-validating words and counts into its block's counter, and
+   * the CTA that counts last collects and quantises the block.  Same record either way. */
+  void* xq_out_stage;
 } b200q_gemv_args;
 int b200q_gemv(const b200q_gemv_args* args, void* stream);
 size_t b200q_xq_bytes(int n);

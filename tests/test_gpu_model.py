@@ -49,12 +49,18 @@ def test_greedy_stream_identical_to_reference(golden, name, mode):
 @pytest.mark.parametrize("typ,kv,hd,handover", [(2, "float16", 64, None), (8, "float16", 64, None), (2, "float32", 64, None),
                                                  (2, "float16", 128, True), (8, "float16", 128, True), (2, "float16", 128, False),
                                                  (2, "float16", 128, None), (2, "float16", 128, "gateup_down,down_qkv"),
+                                                 (2, "float16", 128, "unstaged"), (8, "float16", 128, "unstaged"),
                                                  (2, "float16", 64, "step"), (8, "float16", 64, "step"), (2, "float32", 64, "step"),
                                                  (2, "float16", 128, "step"), (8, "float32", 128, "step"), (8, "float16", 32, "step")])
-def test_mid_size_model_matches_oracle(typ, kv, hd, handover):
+def test_mid_size_model_matches_oracle(typ, kv, hd, handover, monkeypatch):
   """A model too big for the reference's interpreter: logits within tolerance of the oracle at every step,
-  identical greedy stream, and KV-prefix reuse gives the same continuation."""
+  identical greedy stream, and KV-prefix reuse gives the same continuation.  handover True: every GEMV hands its output row to the
+  next one as a quantised record, blocks collected through the staging row; "unstaged": the same with runs of row tiles per CTA."""
+  from tinygrad_b200 import model as model_mod
   from tinygrad_b200.model import Transformer, TransformerConfig
+  if handover == "unstaged":
+    monkeypatch.setattr(model_mod, "STAGED_HANDOVER", False)
+    handover = True
   kw = dict(num_blocks=3, dim=512, hidden_dim=1408, n_heads=512 // hd, n_kv_heads=2, norm_eps=1e-5, vocab_size=2000, head_dim=hd, rope_theta=500000.0,
             rope_dim=hd, max_context=160, qkv_bias=(typ == 8), kv_dtype=kv)
   cfg = TransformerConfig(**kw)

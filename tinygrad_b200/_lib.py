@@ -17,7 +17,8 @@ class GemvArgs(Structure):
               ("x_dtype", c_int), ("y_dtype", c_int), ("norm_weight", c_void_p), ("norm_eps", c_float), ("epilogue", c_int),
               ("bias", c_void_p), ("residual", c_void_p), ("y", c_void_p), ("flags", c_int), ("max_ctas", c_int),
               ("xq_in", c_void_p), ("ss_in", c_void_p), ("ss_count", c_int), ("xq_out", c_void_p), ("xq_out_norm_weight", c_void_p),
-              ("ss_out", c_void_p), ("residual_scale", c_float), ("peer_mailboxes", POINTER(c_void_p)), ("n_peers", c_int), ("peer_rank", c_int)]
+              ("ss_out", c_void_p), ("residual_scale", c_float), ("peer_mailboxes", POINTER(c_void_p)), ("n_peers", c_int), ("peer_rank", c_int),
+              ("xq_out_stage", c_void_p)]
 
 
 class AttnArgs(Structure):

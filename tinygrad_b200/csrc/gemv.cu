@@ -45,7 +45,8 @@ struct GemvParams {
   void* xq_out;             // record of the OUTPUT row for the next GEMV
   const __half* out_norm_w; // multiplied into the output before it is quantised (the next GEMV's norm weight)
   float* ss_out;            // one partial sum of squares per 32 outputs
-  int unit, n_units;        // row tiles are dealt to CTAs in runs of `unit` (one run = 32 outputs when xq_out is set)
+  int unit, n_units;        // row tiles are dealt to CTAs in runs of `unit` (one run = 32 outputs when xq_out is set without a staging row)
+  uint32_t* out_stage;      // xq_out with a staging row: tiles go to CTAs one by one; the CTA of a block's last tile collects the 32 outputs
   // tensor / vocabulary parallel: the output row goes, as self-validating words, into slot `peer_rank` of a mailbox on EVERY rank
   // (peer memory over NVLink; see peer.cu), where a small kernel sums the ranks' slots (all-reduce) or copies them (all-gather)
   uint32_t* peer[B200Q_MAX_PEERS];
@@ -68,7 +69,7 @@ struct GemvParams {
 #endif
 constexpr int CONS_WARPS = B200Q_CONS_WARPS;
 constexpr int CONS_THREADS = CONS_WARPS * 32;
-constexpr int NTHREADS = CONS_THREADS + 32;      // + producer warp
+constexpr int NTHREADS = CONS_THREADS + 64;      // + the producer warp + the finisher warp
 constexpr int STAGE_GROUPS = B200Q_STAGE_GROUPS; // weight tiles (16 rows x 128 columns) per ring stage
 #ifndef B200Q_COPY_GROUPS
 #define B200Q_COPY_GROUPS 4
@@ -90,6 +91,14 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 #define PSTAMP(i) do {} while (0)
 #endif
 
+// words of the hand-over staging row: relaxed, device scope (they are polled across CTAs)
+__device__ __forceinline__ void stage_store(uint32_t* p, uint32_t bits) { asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(bits) : "memory"); }
+__device__ __forceinline__ uint32_t stage_load(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ void cons_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONS_THREADS) : "memory"); }
 
 // Shared-memory plan (dynamic):
@@ -99,8 +108,8 @@ __device__ __forceinline__ void cons_bar_sync() { asm volatile("bar.sync 1, %0;"
 //   red    [2][CONS_WARPS][16] float              cross-warp partial sums, double-buffered over row tiles
 //   ssq    [CONS_WARPS] float
 //   ubuf   [32] float                             the 32 finished outputs of a run, before they are quantised for the next GEMV
-//   bars   full[NS], empty[NS], xbar
-//   abort  int                                    set by a consumer warp whose wait ran out; all warps leave at the next row tile
+//   bars   full[NS], empty[NS], xbar, red_full[2], red_empty[2]
+//   abort  int                                    set by a warp whose wait ran out; the others leave at their next row tile or wait
 // Hands the 32 finished outputs of a run to the next GEMV already quantised (block index = run index).
 // Kept out of line: it runs once per 32 outputs and must not weigh on the register budget of the MMA loop.
 __device__ __noinline__ void emit_output_record(const GemvParams& p, const float* ubuf, int unit, int lane) {
@@ -111,6 +120,32 @@ __device__ __noinline__ void emit_output_record(const GemvParams& p, const float
   }
   const float uq = p.out_norm_w ? u * __half2float(p.out_norm_w[unit * 32 + lane]) : u;
   quant_block_32x1(uq, lane, unit, XqDst(p.xq_out, p.n_out / GROUP_ELEMS));
+}
+
+// The count a finisher made for block `pend_blk` one tile ago has come back in lane 0's `pend_prev`: the last of the block's `per`
+// tiles collects the 32 words (bounded polling: they were stored before the counts, so they are on their way), leaves the row and
+// the counter empty for the next launch and emits the record.
+__device__ __noinline__ void settle_handover(const GemvParams& p, float* ubuf, int& pend_blk, unsigned pend_prev, int per, int lane) {
+  if (pend_blk < 0) return;
+  const unsigned prev = __shfl_sync(0xffffffffu, pend_prev, 0);
+  const int blk = pend_blk;
+  pend_blk = -1;
+  if (prev != (unsigned)per - 1) return;
+  uint32_t* word = p.out_stage + (size_t)blk * 32 + lane;
+  uint32_t w = MAILBOX_EMPTY;
+  for (int i = 0; i < SPIN_LIMIT; i++) {
+    w = stage_load(word);
+    if (w != MAILBOX_EMPTY) break;
+    if (i > 64) __nanosleep(64);
+  }
+  const bool all = __all_sync(0xffffffffu, w != MAILBOX_EMPTY);
+  if (w != MAILBOX_EMPTY) stage_store(word, MAILBOX_EMPTY);
+  if (lane == 0) p.out_stage[p.n_out + blk] = 0;
+  if (!all) { if (lane == 0) atomicExch(&g_status, 1); return; }
+  ubuf[lane] = __uint_as_float(w);
+  __syncwarp();
+  emit_output_record(p, ubuf, blk, lane);
+  __syncwarp();
 }
 
 // XQ_IN / XQ_OUT: compiled-in use of a ready-made input record / production of an output record.
@@ -129,8 +164,9 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
   float* ssq = red + 2 * CONS_WARPS * 16;
   float* ubuf = ssq + CONS_WARPS;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ubuf + 32);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 2 * NS + 1);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 2 * NS + 5);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + NS), xbar = smem_u32(bars + 2 * NS);
+  const uint32_t rfull0 = smem_u32(bars + 2 * NS + 1), rempty0 = smem_u32(bars + 2 * NS + 3);      // the two buffers of `red`
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int m = blockIdx.y;
   const int stages_per_tile = (p.kgroups + SG - 1) / SG;
@@ -148,6 +184,7 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
   if (tid == 0) {
     for (int s = 0; s < NS; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, CONS_WARPS); }
     mbar_init(xbar, 1);
+    for (int b = 0; b < 2; b++) { mbar_init(rfull0 + 8 * b, CONS_WARPS); mbar_init(rempty0 + 8 * b, 1); }
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -204,17 +241,103 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
     return;
   }
 
+  if (warp == CONS_WARPS + 1) {
+    // ------------------------------ finisher ------------------------------
+    // Takes every row tile's cross-warp sum and epilogue off the consumers: they leave their partial sums in `red` (two buffers,
+    // a full / empty barrier pair each) and go on with the next tile; nothing in a tile's MMAs waits for the previous tile's
+    // stores, residual loads or hand-over bookkeeping.
+    pdl_wait();
+    float pre_add = 0.f;
+    const int first_rt = blockIdx.x * (XQ_OUT ? p.unit : 1);
+    if (lane < 16 && p.epilogue == B200Q_EPI_LINEAR && first_rt * 16 + lane < p.n_out) {      // addends of the first tile: their latency hides behind its MMAs
+      if (p.residual) pre_add = p.residual[(size_t)m * p.n_out + first_rt * 16 + lane] * p.residual_scale;
+      if (p.bias) pre_add += __half2float(p.bias[first_rt * 16 + lane]);
+    }
+    float rs = 1.f;
+    int n = 0, pend_blk = -1;
+    unsigned pend_prev = 0;
+    bool ok = true;
+    const int run = XQ_OUT ? p.unit : 1;
+    for (int unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x) {
+      for (int ti = 0; ti < run; ti++, n++) {
+        const int rt = unit * run + ti;
+        if (rt >= p.n_row_tiles) break;
+        const int par = n & 1;
+        if (!mbar_wait(rfull0 + 8 * par, (n >> 1) & 1)) { *s_abort = 1; ok = false; break; }
+        if (n == 0 && p.norm_w) {                                // the consumers left their sums of squares before their first tile
+          float tot = 0.f;
+#pragma unroll
+          for (int w = 0; w < CONS_WARPS; w++) tot += ssq[w];
+          rs = rsqrtf(tot / (float)p.n_in + p.eps);
+        }
+        const float* rb = red + par * CONS_WARPS * 16;
+        float v = 0.f;
+        if (lane < 16) {
+#pragma unroll
+          for (int w = 0; w < CONS_WARPS; w++) v += rb[w * 16 + lane];
+          v *= rs;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(rempty0 + 8 * par);           // the buffer may be written again (by the tile after next)
+        if (p.epilogue == B200Q_EPI_LINEAR) {
+          const int row = rt * 16 + lane;
+          if (lane < 16 && row < p.n_out) {
+            if (rt == first_rt) v += pre_add;
+            else {
+              if (p.bias) v += __half2float(p.bias[row]);
+              if (p.residual) v = fmaf(p.residual[(size_t)m * p.n_out + row], p.residual_scale, v);
+            }
+            if (p.y) {
+              if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(v);
+              else reinterpret_cast<float*>(p.y)[(size_t)m * p.n_out + row] = v;
+            }
+            if (p.n_peers) {
+              const uint32_t bits = mailbox_bits(v);
+              for (int d = 0; d < p.n_peers; d++) mailbox_store(p.peer[d] + (size_t)p.peer_rank * p.n_out + row, bits);
+            }
+          }
+          if (XQ_OUT && lane < 16) ubuf[ti * 16 + lane] = v;
+        } else {
+          const float up = __shfl_down_sync(0xffffffffu, v, 8);     // rows 8..15 of the tile are the `up` rows
+          const int row = rt * 8 + lane;
+          const float o = (v / (1.f + __expf(-v))) * up;
+          if (lane < 8 && row < p.n_out && p.y) {
+            if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(o);
+            else reinterpret_cast<float*>(p.y)[(size_t)m * p.n_out + row] = o;
+          }
+          if (XQ_OUT && lane < 8) ubuf[ti * 8 + lane] = o;
+        }
+        if (XQ_OUT && p.out_stage) {
+          // A block of 32 outputs spans `per` row tiles, which may sit on different CTAs.  Every tile leaves its outputs in the
+          // staging row as self-validating words (empty or complete: no flag, no fence) and counts into the block's counter; the
+          // one that counts last collects the block and quantises it (the record is a function of the 32 values alone).  The
+          // count's answer is looked at one tile later, so its round trip stays off this warp's path, and the collector's wait for
+          // words that are still on their way depends on no other CTA's progress.
+          const int per = p.epilogue == B200Q_EPI_LINEAR ? 2 : 4, cnt = 32 / per, blk = rt / per, sub = rt - blk * per;
+          __syncwarp();
+          const float mine = ubuf[lane & 15];                    // ubuf[0 .. cnt) = this tile's outputs
+          settle_handover(p, ubuf, pend_blk, pend_prev, per, lane);
+          if (lane < cnt) stage_store(p.out_stage + (size_t)blk * 32 + sub * cnt + lane, mailbox_bits(mine));
+          if (lane == 0) pend_prev = atomicAdd(p.out_stage + p.n_out + blk, 1u);
+          pend_blk = blk;
+        } else if (XQ_OUT && ti == run - 1) {
+          __syncwarp();
+          emit_output_record(p, ubuf, unit, lane);     // the run's 32 outputs are complete
+          __syncwarp();
+        }
+      }
+    }
+    if (XQ_OUT && p.out_stage) settle_handover(p, ubuf, pend_blk, pend_prev, p.epilogue == B200Q_EPI_LINEAR ? 2 : 4, lane);
+#ifdef B200Q_GEMV_PROF
+    if (lane == 0) atomicMax(&g_gemv_prof[prof_slot * 8 + 7], gtime());      // the last CTA's exit
+#endif
+    return;
+  }
+
   // -------------------------------- consumers --------------------------------
   pdl_wait();
   PSTAMP(1);
   const int g = lane >> 2, t = lane & 3;
-  // warp 0 finishes every row tile: fetch the addends of the CTA's first tile now, so their latency hides behind the MMAs
-  float pre_add = 0.f;
-  const int first_rt = blockIdx.x * (XQ_OUT ? p.unit : 1);
-  if (warp == 0 && lane < 16 && p.epilogue == B200Q_EPI_LINEAR && first_rt * 16 + lane < p.n_out) {
-    if (p.residual) pre_add = p.residual[(size_t)m * p.n_out + first_rt * 16 + lane] * p.residual_scale;
-    if (p.bias) pre_add += __half2float(p.bias[first_rt * 16 + lane]);
-  }
   if (tid == 0) *zero = make_uint4(0, 0, 0, 0);
   float ss = 0.f;
   if (XQ_IN) {
@@ -265,19 +388,12 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
   if (XQ_IN && !mbar_wait(xbar, 0)) *s_abort = 1;
   cons_bar_sync();
   PSTAMP(2);
-  float rs = 1.f;
-  if (p.norm_w) {
-    float tot = 0.f;
-#pragma unroll
-    for (int w = 0; w < CONS_WARPS; w++) tot += ssq[w];
-    rs = rsqrtf(tot / (float)p.n_in + p.eps);
-  }
   const bool diag = (t == (g & 3));
-  int it = 0, par = 0;
+  int it = 0, n = 0;
   bool live = *s_abort == 0;
   const int run = XQ_OUT ? p.unit : 1;
   for (int unit = blockIdx.x; unit < p.n_units && live; unit += gridDim.x) {
-    for (int ti = 0; ti < run; ti++, par ^= 1) {
+    for (int ti = 0; ti < run; ti++, n++) {
       const int rt = unit * run + ti;
       if (rt >= p.n_row_tiles) break;
       float acc0 = 0.f, acc1 = 0.f;
@@ -313,58 +429,18 @@ __global__ void __launch_bounds__(NTHREADS, B200Q_CTAS_PER_SM) qgemv_kernel(cons
       // quad lanes hold the columns {blocks 0,1 hi}, {2,3 hi}, {0,1 lo}, {2,3 lo}: add them
       acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1); acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
       acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1); acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+      // hand the partial sums to the finisher: buffer n & 1, free again once the finisher has read tile n - 2
+      const int par = n & 1;
+      if (n >= 2 && !mbar_wait(rempty0 + 8 * par, ((n >> 1) - 1) & 1)) *s_abort = 1;
+      live = *s_abort == 0;
+      if (!live) break;
       float* rb = red + par * CONS_WARPS * 16;
       if (t == 0) { rb[warp * 16 + g] = acc0; rb[warp * 16 + 8 + g] = acc1; }
-      cons_bar_sync();
-      live = *s_abort == 0;      // uniform over the consumer warps: read after the barrier that follows every write
-      if (!live) break;
-      if (warp == 0) {
-        float v = 0.f;
-        if (lane < 16) {
-#pragma unroll
-          for (int w = 0; w < CONS_WARPS; w++) v += rb[w * 16 + lane];
-          v *= rs;
-        }
-        if (p.epilogue == B200Q_EPI_LINEAR) {
-          const int row = rt * 16 + lane;
-          if (lane < 16 && row < p.n_out) {
-            if (rt == first_rt) v += pre_add;
-            else {
-              if (p.bias) v += __half2float(p.bias[row]);
-              if (p.residual) v = fmaf(p.residual[(size_t)m * p.n_out + row], p.residual_scale, v);
-            }
-            if (p.y) {
-              if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(v);
-              else reinterpret_cast<float*>(p.y)[(size_t)m * p.n_out + row] = v;
-            }
-            if (p.n_peers) {
-              const uint32_t bits = mailbox_bits(v);
-              for (int d = 0; d < p.n_peers; d++) mailbox_store(p.peer[d] + (size_t)p.peer_rank * p.n_out + row, bits);
-            }
-          }
-          if (XQ_OUT && lane < 16) ubuf[ti * 16 + lane] = v;
-        } else {
-          const float up = __shfl_down_sync(0xffffffffu, v, 8);     // rows 8..15 of the tile are the `up` rows
-          const int row = rt * 8 + lane;
-          const float o = (v / (1.f + __expf(-v))) * up;
-          if (lane < 8 && row < p.n_out && p.y) {
-            if (p.y_f16) reinterpret_cast<__half*>(p.y)[(size_t)m * p.n_out + row] = __float2half_rn(o);
-            else reinterpret_cast<float*>(p.y)[(size_t)m * p.n_out + row] = o;
-          }
-          if (XQ_OUT && lane < 8) ubuf[ti * 8 + lane] = o;
-        }
-        if (XQ_OUT && ti == run - 1) {
-          __syncwarp();
-          emit_output_record(p, ubuf, unit, lane);     // the run's 32 outputs are complete
-          __syncwarp();
-        }
-      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(rfull0 + 8 * par);
     }
   }
   PSTAMP(5);
-#ifdef B200Q_GEMV_PROF
-  if (tid == 0) atomicMax(&g_gemv_prof[prof_slot * 8 + 7], gtime());      // the last CTA's exit
-#endif
 }
 
 #ifdef B200Q_GEMV_PROF
@@ -387,7 +463,7 @@ template <int QT, bool XQ_IN, bool XQ_OUT>
 int launch_gemv(const b200q_gemv_args* a, const GemvParams& p, cudaStream_t stream) {
   constexpr int NS = Cfg<QT>::NS;
   const size_t smem = (size_t)NS * Cfg<QT>::SG * tile_bytes(QT) + (size_t)p.kgroups * (XQ_GROUP_BYTES + Cfg<QT>::XSUB) + 16 +
-                      (2 * CONS_WARPS * 16 + CONS_WARPS + 32) * sizeof(float) + (2 * NS + 1) * sizeof(uint64_t) + 16;
+                      (2 * CONS_WARPS * 16 + CONS_WARPS + 32) * sizeof(float) + (2 * NS + 5) * sizeof(uint64_t) + 16;
   if (smem > 220 * 1024) return B200Q_ERR_TOO_LARGE;
   auto kern = qgemv_kernel<QT, XQ_IN, XQ_OUT>;
   // per device (and per instantiation): the shared-memory attribute, and the last occupancy answer packed as (smem << 8) | blocks
@@ -462,6 +538,7 @@ extern "C" int b200q_gemv(const b200q_gemv_args* a, void* stream) {
   if ((a->xq_in || a->xq_out) && a->m != 1) return B200Q_ERR_UNSUPPORTED;
   if (a->xq_in && a->norm_weight && (!a->ss_in || a->ss_count <= 0)) return B200Q_ERR_BAD_ARG;   // the norm weight is already inside the record
   if (a->xq_out && a->n_out % GROUP_ELEMS) return B200Q_ERR_BAD_SHAPE;
+  if (a->xq_out_stage && (!a->xq_out || ((uintptr_t)a->xq_out_stage & 3))) return B200Q_ERR_BAD_ARG;
   GemvParams p;
   p.w = (const uint8_t*)a->w_packed; p.x = a->x; p.norm_w = (const __half*)a->norm_weight; p.bias = (const __half*)a->bias;
   p.residual = (const float*)a->residual; p.residual_scale = a->residual_scale == 0.f ? 1.f : a->residual_scale; p.y = a->y;
@@ -480,7 +557,8 @@ extern "C" int b200q_gemv(const b200q_gemv_args* a, void* stream) {
     }
     p.n_peers = a->n_peers; p.peer_rank = a->peer_rank;
   }
-  p.unit = a->xq_out ? (a->epilogue == B200Q_EPI_SILU_MUL ? 4 : 2) : 1;
+  p.out_stage = (uint32_t*)a->xq_out_stage;
+  p.unit = (a->xq_out && !a->xq_out_stage) ? (a->epilogue == B200Q_EPI_SILU_MUL ? 4 : 2) : 1;
   p.n_units = ceil_div(p.n_row_tiles, p.unit);
   const bool xi = a->xq_in != nullptr, xo = a->xq_out != nullptr;
   if (a->qtype == B200Q_Q4_0) {

@@ -58,7 +58,8 @@ class _Block:
 
 
 # hand-over edges used when the caller does not choose (see Transformer.__init__): the ones that measured faster
-DEFAULT_HANDOVER = ("attn_o",)
+DEFAULT_HANDOVER = tuple(e for e in os.environ.get("B200Q_HANDOVER", "attn_o").split(",") if e)
+STAGED_HANDOVER = os.environ.get("B200Q_STAGED_HANDOVER", "1") == "1"
 
 
 class Transformer:
@@ -215,6 +216,12 @@ class Transformer:
     if "o_gateup" in self.edges: self.xq_b, self.ss_b = DeviceBuffer(xqb(c.dim), zero=True), DeviceBuffer.empty((c.dim // 32,), np.float32, zero=True)
     if "attn_o" in self.edges: self.xq_attn = DeviceBuffer(xqb(self.q_dim), zero=True)
     if "gateup_down" in self.edges: self.xq_act = DeviceBuffer(xqb(c.hidden_dim), zero=True)
+    # staging row of the producing GEMVs (32-bit words, all-ones = empty; the kernels leave it empty): row tiles stay dealt to CTAs
+    # one by one.  Without it a producing CTA takes runs of 2 / 4 consecutive tiles, which leaves the grid unevenly loaded.
+    self.ho_stage = None
+    if self.edges and STAGED_HANDOVER:
+      self.ho_stage = {n: DeviceBuffer.from_numpy(np.concatenate([np.full(n, 0xFFFFFFFF, np.uint32), np.zeros(n // 32, np.uint32)]))
+                       for n in {c.dim, c.hidden_dim}}      # [n_out words | n_out / 32 counters] per producing width
     self._graphs = {}
     self._cached_tokens: list = []
     self.prefill_rows = prefill_rows if (tp is None and not self.dense_blocks and c.hidden_dim % 8 == 0 and c.head_dim in (16, 32, 64, 128)) else 0
@@ -294,9 +301,10 @@ class Transformer:
       quant.gemv_dense(b.down_w, F16, c.dim, c.hidden_dim, self.act, self.x, residual=self.x, flags=fl, stream=s)
     for i, b in enumerate(() if self.dense_blocks else self.blk):
       nxt_norm = self.blk[i + 1].attn_norm if i + 1 < len(self.blk) else self.output_norm
-      out_b = dict(xq_out=self.xq_b, xq_out_norm_weight=b.ffn_norm, ss_out=self.ss_b) if "o_gateup" in e else {}
-      out_act = dict(xq_out=self.xq_act) if "gateup_down" in e else {}
-      out_a = dict(xq_out=self.xq_a, xq_out_norm_weight=nxt_norm, ss_out=self.ss_a) if "down_qkv" in e else {}
+      st = (lambda n: dict(xq_out_stage=self.ho_stage[n])) if self.ho_stage is not None else (lambda n: {})
+      out_b = dict(xq_out=self.xq_b, xq_out_norm_weight=b.ffn_norm, ss_out=self.ss_b, **st(c.dim)) if "o_gateup" in e else {}
+      out_act = dict(xq_out=self.xq_act, **st(c.hidden_dim)) if "gateup_down" in e else {}
+      out_a = dict(xq_out=self.xq_a, xq_out_norm_weight=nxt_norm, ss_out=self.ss_a, **st(c.dim)) if "down_qkv" in e else {}
       quant.gemv(b.qkv.ptr, self.qtype, qkv_rows, c.dim, None if in_a else self.x, self.qkv, norm_weight=b.attn_norm, norm_eps=c.norm_eps,
                  bias=b.qkv_bias, max_ctas=grid("qkv"), **in_a, **(kw_after_coll if i > 0 else kw))
       if attention:

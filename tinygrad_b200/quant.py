@@ -76,12 +76,14 @@ def repack(raw, n_out: int, n_in: int, qtype: int, raw_up=None, out: DeviceBuffe
 
 def gemv(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int = 1, x_dtype=F32, y_dtype=F32, norm_weight=None, norm_eps: float = 0.0,
          epilogue: int = EPI_LINEAR, bias=None, residual=None, flags: int = 0, max_ctas: int = 0, stream=None, xq_in=None, ss_in=None,
-         ss_count: int = 0, xq_out=None, xq_out_norm_weight=None, ss_out=None, residual_scale: float = 1.0, peers=None, peer_rank: int = 0) -> None:
+         ss_count: int = 0, xq_out=None, xq_out_norm_weight=None, ss_out=None, residual_scale: float = 1.0, peers=None, peer_rank: int = 0,
+         xq_out_stage=None) -> None:
   """One launch of the fused dequant-GEMV (all pointers raw device addresses or buffers).  peers: a ctypes array of every rank's
   mailbox pointer (tensor_parallel.PeerMailbox.targets): the output row also goes into slot `peer_rank` of each."""
   a = _lib.GemvArgs(qtype, n_out, n_in, m, w_ptr, ptr_of(x), x_dtype, y_dtype, ptr_of(norm_weight), norm_eps, epilogue, ptr_of(bias),
                     ptr_of(residual), ptr_of(y), flags, max_ctas, ptr_of(xq_in), ptr_of(ss_in), ss_count, ptr_of(xq_out),
-                    ptr_of(xq_out_norm_weight), ptr_of(ss_out), residual_scale, peers, len(peers) if peers is not None else 0, peer_rank)
+                    ptr_of(xq_out_norm_weight), ptr_of(ss_out), residual_scale, peers, len(peers) if peers is not None else 0, peer_rank,
+                    ptr_of(xq_out_stage))
   check(_lib.load().b200q_gemv(ctypes.byref(a), stream_ptr(stream)))
 
 
