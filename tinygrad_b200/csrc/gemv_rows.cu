@@ -10,8 +10,9 @@
 // Pre-pass (rows_record_kernel): the activation rows are quantised once (per block of 32: fp32 scale, 15-bit integers split in two int8
 // digits) into the B-operand order of the MMA, per K chunk of 32 column groups.  Main kernel: grid (CTAs over row tiles, K chunks);
 // a CTA brings its chunk's record into shared memory by bulk copies, then streams its row tiles' chunk of weights through a ring of
-// bulk-copied stages (one stage = one tile's chunk), 16 consumer warps, 2 column groups per warp and stage; partial sums go to a
-// workspace [chunk][row][n_out] and a last kernel adds the chunks in a fixed order and applies bias / residual / SwiGLU (no
+// bulk-copied stages (one stage = one tile's chunk), 16 consumer warps, 2 column groups per warp and stage; four finisher warps add the
+// consumers' partial sums of a tile in a fixed order while the consumers are on the next tile, and apply the epilogue (one K chunk) or
+// leave partial sums in a workspace [chunk][row][n_out] that a last kernel adds in a fixed order with bias / residual / SwiGLU (no
 // floating-point atomics: bit-reproducible).  Every mbarrier wait is bounded (status word on expiry, see gemv.cu).
 #include "common.cuh"
 #include "qgemv_core.cuh"
@@ -30,7 +31,8 @@ namespace {
 #ifndef B200Q_R_NS8
 #define B200Q_R_NS8 2
 #endif
-constexpr int R_WARPS = B200Q_R_WARPS, R_THREADS = R_WARPS * 32 + 32;      // consumers + the producer warp
+constexpr int R_FIN = 4;                                        // finisher warps: 128 outputs (16 weight rows x 8 activation rows) per row tile
+constexpr int R_WARPS = B200Q_R_WARPS, R_THREADS = R_WARPS * 32 + 32 + R_FIN * 32;      // consumers + the producer warp + the finishers
 constexpr int R_CG = B200Q_R_CG;                                // column groups (of 128 inputs) per K chunk = per ring stage
 __host__ __device__ constexpr int rows_ns(int qtype) { return qtype == B200Q_Q4_0 ? B200Q_R_NS4 : B200Q_R_NS8; }      // ring depth (a stage is 36 KB of Q4_0, 68 KB of Q8_0)
 constexpr int R_TOK = 8;                                        // activation rows per pass = MMA columns
@@ -194,13 +196,15 @@ __global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsPara
   unsigned char* rec = rsm + R_NS * STAGE;                       // words of the chunk's groups, then their scales
   float* red = reinterpret_cast<float*>(rec + R_CG * (REC_GROUP + SC_GROUP));      // [2][R_WARPS][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(red + 2 * R_WARPS * 128);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 2 * R_NS + 1);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 2 * R_NS + 5);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + R_NS), rbar = smem_u32(bars + 2 * R_NS);
+  const uint32_t rfull0 = smem_u32(bars + 2 * R_NS + 1), rempty0 = smem_u32(bars + 2 * R_NS + 3);      // the two buffers of `red`
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int chunk = blockIdx.y, cg = min(R_CG, p.kgroups - chunk * R_CG);
   if (tid == 0) {
     for (int s = 0; s < R_NS; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, R_WARPS); }
     mbar_init(rbar, 1);
+    for (int b = 0; b < 2; b++) { mbar_init(rfull0 + 8 * b, R_WARPS); mbar_init(rempty0 + 8 * b, R_FIN); }
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -247,6 +251,40 @@ __global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsPara
 #endif
     } else {
       pdl_wait();
+    }
+    return;
+  }
+  if (warp > R_WARPS) {
+    // -------------------------------- finishers: the cross-warp sum (fixed order) and the epilogue of every row tile, off the consumers' path
+    const int fw = warp - R_WARPS - 1;
+    pdl_wait();
+    int it = 0;
+    for (int rt = blockIdx.x; rt < p.n_row_tiles; rt += gridDim.x, it++) {
+      const int par = it & 1;
+      if (!mbar_wait(rfull0 + 8 * par, (it >> 1) & 1)) { *s_abort = 1; break; }
+      const float* rb = red + par * R_WARPS * 128;
+      const int o = fw * 32 + lane;                              // output o of the tile: lane' = o / 4, i = o % 4
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < R_WARPS; w++) v += rb[w * 128 + o];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(rempty0 + 8 * par);             // the buffer may be written again (by the tile after next)
+      const int ln = o >> 2, i = o & 3, row = rt * 16 + (ln >> 2) + (i >> 1) * 8, tok = 2 * (ln & 3) + (i & 1);
+      if (p.n_chunks > 1) {
+        if (row < p.n_out && tok < p.m) p.part[((size_t)chunk * p.m + tok) * p.n_out + row] = v;
+      } else if (p.silu_mul) {                                   // rows g / g + 8 of a tile are a gate row and its up row: i and i + 2 of one quad
+        const float up = __shfl_down_sync(0xffffffffu, v, 2);
+        if (i < 2 && row < p.n_out && tok < p.m) {
+          const size_t at = (size_t)tok * (p.n_out >> 1) + rt * 8 + (ln >> 2);
+          const float r = (v / (1.f + expf(-v))) * up;
+          if (p.y_f16) reinterpret_cast<__half*>(p.y)[at] = __float2half_rn(r); else reinterpret_cast<float*>(p.y)[at] = r;
+        }
+      } else if (row < p.n_out && tok < p.m) {
+        const size_t at = (size_t)tok * p.n_out + row;
+        if (p.bias) v += __half2float(p.bias[row]);
+        if (p.residual) v += p.y_f16 ? __half2float(reinterpret_cast<const __half*>(p.residual)[at]) : reinterpret_cast<const float*>(p.residual)[at];
+        if (p.y_f16) reinterpret_cast<__half*>(p.y)[at] = __float2half_rn(v); else reinterpret_cast<float*>(p.y)[at] = v;
+      }
     }
     return;
   }
@@ -299,34 +337,14 @@ __global__ void __launch_bounds__(R_THREADS, 1) qgemv_rows_kernel(const RowsPara
 #ifdef B200Q_ROWS_PROF
     const long long k2 = clock64();
 #endif
-    // cross-warp sum in a fixed order: rb[warp][lane * 4 + i]
-    float* rb = red + par * R_WARPS * 128;
-    *reinterpret_cast<float4*>(rb + warp * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    rows_bar_sync();
+    // partial sums to the finishers: rb[warp][lane * 4 + i] in buffer it & 1, free again once tile it - 2 has been summed
+    if (it >= 2 && !mbar_wait(rempty0 + 8 * par, ((it >> 1) - 1) & 1)) *s_abort = 1;
     live = *s_abort == 0;
     if (!live) break;
-    if (warp < 4) {
-      const int o = warp * 32 + lane;                            // output o of the tile: lane' = o / 4, i = o % 4
-      float v = 0.f;
-#pragma unroll
-      for (int w = 0; w < R_WARPS; w++) v += rb[w * 128 + o];
-      const int ln = o >> 2, i = o & 3, row = rt * 16 + (ln >> 2) + (i >> 1) * 8, tok = 2 * (ln & 3) + (i & 1);
-      if (p.n_chunks > 1) {
-        if (row < p.n_out && tok < p.m) p.part[((size_t)chunk * p.m + tok) * p.n_out + row] = v;
-      } else if (p.silu_mul) {                                   // rows g / g + 8 of a tile are a gate row and its up row: i and i + 2 of one quad
-        const float up = __shfl_down_sync(0xffffffffu, v, 2);
-        if (i < 2 && row < p.n_out && tok < p.m) {
-          const size_t at = (size_t)tok * (p.n_out >> 1) + rt * 8 + (ln >> 2);
-          const float r = (v / (1.f + expf(-v))) * up;
-          if (p.y_f16) reinterpret_cast<__half*>(p.y)[at] = __float2half_rn(r); else reinterpret_cast<float*>(p.y)[at] = r;
-        }
-      } else if (row < p.n_out && tok < p.m) {
-        const size_t at = (size_t)tok * p.n_out + row;
-        if (p.bias) v += __half2float(p.bias[row]);
-        if (p.residual) v += p.y_f16 ? __half2float(reinterpret_cast<const __half*>(p.residual)[at]) : reinterpret_cast<const float*>(p.residual)[at];
-        if (p.y_f16) reinterpret_cast<__half*>(p.y)[at] = __float2half_rn(v); else reinterpret_cast<float*>(p.y)[at] = v;
-      }
-    }
+    float* rb = red + par * R_WARPS * 128;
+    *reinterpret_cast<float4*>(rb + warp * 128 + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(rfull0 + 8 * par);
 #ifdef B200Q_ROWS_PROF
     c_wait += k1 - k0; c_mac += k2 - k1; c_red += clock64() - k2;
 #endif
@@ -359,7 +377,7 @@ __global__ void rows_reduce_kernel(const float* __restrict__ part, int n_chunks,
 }
 
 size_t rows_smem(int qtype) {
-  return (size_t)rows_ns(qtype) * R_CG * tile_bytes(qtype) + (size_t)R_CG * (REC_GROUP + SC_GROUP) + 2 * R_WARPS * 128 * sizeof(float) + (2 * rows_ns(qtype) + 1) * sizeof(uint64_t) + 16;
+  return (size_t)rows_ns(qtype) * R_CG * tile_bytes(qtype) + (size_t)R_CG * (REC_GROUP + SC_GROUP) + 2 * R_WARPS * 128 * sizeof(float) + (2 * rows_ns(qtype) + 5) * sizeof(uint64_t) + 16;
 }
 size_t rows_record_bytes(int kgroups) { return (size_t)ceil_div(kgroups, R_CG) * R_CG * (REC_GROUP + SC_GROUP); }
 
