@@ -20,6 +20,7 @@ ROOT = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 METRIC, UNIT = "decode tokens/s (8B-shape Q4_0, bs1)", "tokens/s"
+NCU_TRAFFIC_RATIO = 1.006      # dram__bytes_read + write per launch / algorithmic bytes, from the committed ncu summary of qgemv_kernel
 WORKLOAD = "configs[1]: Llama-3-8B-shaped decode, Q4_0 linears, fp16 embeddings/norms, fp16 KV cache, batch 1, prompt 512 random ids, greedy"
 PROMPT_LEN, MAX_CONTEXT = 512, 2048
 
@@ -397,7 +398,10 @@ def main():
     shapes = model.gemv_launches()
     gemv_bytes = sum(o * i // 32 * 18 + 4 * i + 4 * o for o, i in shapes)
     achieved = gemv_bytes / (ms_gemv * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+    # DRAM bytes per launch are not measured here (that takes ncu): the captures of this kernel inside a decode step read 1.005-1.007 x
+    # the algorithmic bytes from DRAM (profiles/qgemv_q4_0_o_proj_and_gate_up_in_decode_step.md), which is what `traffic` scales by
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_RATIO * gemv_bytes / len(shapes), "traffic_source": f"ncu capture of two launches: dram bytes = {NCU_TRAFFIC_RATIO} x algorithmic",
                 "kernel": "qgemv_kernel<Q4_0> (the GEMV launches of a step alone, chained)", "peak_source": pk["source"], "launches_timed": len(shapes) * 20,
                 "bytes_per_launch_avg": gemv_bytes / len(shapes), "us_per_launch_avg": 1e3 * ms_gemv / len(shapes)}
     launches = model.launches_per_step * args.steps
