@@ -192,9 +192,10 @@ def test_moe_transformer_matches_mx_oracle(variant):
     if len(got) == 6: break
 
 
-@pytest.mark.parametrize("typ,B", [(2, 3), (8, 5)])
+@pytest.mark.parametrize("typ,B", [(2, 3), (8, 5), (2, 11)])
 def test_batched_decode_matches_oracle_per_sequence(typ, B):
-  """B sequences in lock-step (tokens [B, 1] per step): each stream equals the oracle's own run of that sequence."""
+  """B sequences in lock-step (tokens [B, 1] per step): each stream equals the oracle's own run of that sequence.  11 sequences: two
+  passes of the few-row kernel (8 + 3 rows) per Linear."""
   from tinygrad_b200.model import Transformer, TransformerConfig
   kw = dict(num_blocks=2, dim=512, hidden_dim=1408, n_heads=8, n_kv_heads=2, norm_eps=1e-5, vocab_size=2000, head_dim=64, rope_theta=500000.0,
             rope_dim=64, max_context=96, qkv_bias=(typ == 8), kv_dtype="float16")
@@ -296,7 +297,7 @@ def test_few_row_fused_gemv(tag, m, n_out, n_in, x_dtype, epi):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("tag,m,n_out,n_in", [("q8_0", 8, 512, 3584), ("q4_0", 5, 272, 8192)])
+@pytest.mark.parametrize("tag,m,n_out,n_in", [("q8_0", 8, 512, 3584), ("q4_0", 5, 272, 8192), ("q8_0", 19, 160, 4096)])
 def test_few_row_fused_gemv_folds_rmsnorm(tag, m, n_out, n_in):
   """`Linear(norm(x))` (tinygrad/llm/model.py:159,167): the RMSNorm inside the quantising pre-pass against the norm applied in fp32."""
   from tinygrad_b200 import quant, runtime

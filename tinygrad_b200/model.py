@@ -415,7 +415,7 @@ class Transformer:
     kvdt = F16 if c.kv_dtype == "float16" else F32
     qkv_rows = self.q_dim + 2 * self.kv_dim
     head_q = not isinstance(self.output, quant.DenseWeight)
-    if B <= 8 and quant.FEW_ROW_FUSED:       # 8 rows per pass on the int8 tensor cores at the one-row GEMV's arithmetic (weights streamed once per pass)
+    if B <= quant.FEW_ROW_MAX and quant.FEW_ROW_FUSED:       # 8 rows per pass on the int8 tensor cores at the one-row GEMV's arithmetic (weights streamed once per pass)
       if self._skinny_ws is None:
         shapes = [(qkv_rows, c.dim), (c.dim, self.q_dim), (2 * c.hidden_dim, c.dim), (c.dim, c.hidden_dim)] + ([(c.vocab_size, c.dim)] if head_q else [])
         self._skinny_ws = DeviceBuffer(max(quant.qgemv_rows_workspace_bytes(B, o, i) for o, i in shapes))
@@ -429,7 +429,7 @@ class Transformer:
       def gemm(w, qt, n_out, n_in, x, y, **kw): quant.qgemm(w, qt, n_out, n_in, x, y, B, x_dtype=F32, y_dtype=F32, stream=s, **kw)
     # the position comes from the device (sequence 0's counter; all sequences move together), so the launch sequence can be replayed as a graph
     check(lib.b200q_embed_rows(self.token_embd.ptr, self.tokens.ptr, c.max_context + 1, self.pos.ptr, B, c.dim, c.vocab_size, f["x"].ptr, s))
-    fold = B <= 8 and quant.FEW_ROW_FUSED     # the few-row kernel's pre-pass applies the RMSNorm itself: no norm launches
+    fold = B <= quant.FEW_ROW_MAX and quant.FEW_ROW_FUSED     # the few-row kernel's pre-pass applies the RMSNorm itself: no norm launches
     seq_attn = SEQ_ATTENTION and c.n_heads // c.n_kv_heads <= 8 and c.head_dim % 8 == 0 and c.head_dim <= 128
     if seq_attn and self._seq_attn_scratch is None:
       stride = lib.b200q_attn_seq_scratch_stride(c.n_heads, c.n_kv_heads, c.head_dim, self.n_split)

@@ -108,7 +108,10 @@ def qgemm(w_ptr: int, qtype: int, n_out: int, n_in: int, x, y, m: int, x_dtype=F
                         stream_ptr(stream)))
 
 
-FEW_ROW_FUSED = os.environ.get("B200Q_FEW_ROW_FUSED", "1") == "1"      # batched decode with at most 8 rows: the int8-MMA few-row kernel
+FEW_ROW_FUSED = os.environ.get("B200Q_FEW_ROW_FUSED", "1") == "1"      # batched decode with few rows: the int8-MMA few-row kernel
+# ... up to this many rows, 8 per pass over the weights (measured at 16 / 32 sequences of the 7B Q8_0 shape: 5.1 / 10.2 ms per step
+# against 10.5 / 11.9 on the tcgen05 few-row GEMM, whose unpacking to fp16 halves costs more than streaming the weights again)
+FEW_ROW_MAX = int(os.environ.get("B200Q_FEW_ROW_MAX", "32"))
 
 
 def qgemv_rows_workspace_bytes(m: int, n_out: int, n_in: int) -> int:
